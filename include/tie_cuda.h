@@ -1,0 +1,172 @@
+/*
+ * tie_cuda.h — C ABI of the B200 (sm_100a) backend for TIE's Qwen3-MoE feed-forward path.
+ *
+ * The library replaces the `if (ctx->model->is_moe)` branch of transformer_layer_qwen3
+ * (model_qwen3.c:403-471) and supplies CUDA rows for the math_dispatch.c operator tables.
+ * Plain C: opaque handle, pointers and sizes only; every entry point returns 0 or a negative
+ * TIE_CUDA_E* code and never calls exit().  There is no CPU fallback: an unsupported type or
+ * shape is an error.  One context per GPU; a context is used from one thread at a time (the
+ * reference calls transformer_layer from its single model thread, main.c:660).
+ *
+ * Citations are file:line into the reference (szemzoa/tie).
+ */
+#ifndef TIE_CUDA_H
+#define TIE_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* GGMLType values used on this path (gguf.h:7-40). */
+#define TIE_GGML_TYPE_F32 0
+#define TIE_GGML_TYPE_Q4_K 12
+#define TIE_GGML_TYPE_Q6_K 14
+
+#define TIE_CUDA_SILU_TABLE_SIZE 8192 /* SILU_TABLE_SIZE, engine.h:10 */
+
+/* error codes */
+#define TIE_CUDA_OK 0
+#define TIE_CUDA_EINVAL (-1)   /* bad argument (null pointer, size out of range, layer not uploaded) */
+#define TIE_CUDA_ENOTSUP (-2)  /* tensor type / shape this backend has no kernel for */
+#define TIE_CUDA_ENOMEM (-3)   /* device or pinned-host allocation failed */
+#define TIE_CUDA_ECUDA (-4)    /* a CUDA runtime call or kernel failed; see tie_cuda_last_cuda_error */
+#define TIE_CUDA_ENODEV (-5)   /* no usable sm_100 device */
+#define TIE_CUDA_EKERNEL (-6)  /* a kernel reported an internal check failure (device status word) */
+
+/* flags for the x / out pointers of the compute entry points */
+#define TIE_CUDA_HOST 0u         /* pointers are host memory (the drop-in case: ctx->mem.* buffers) */
+#define TIE_CUDA_DEVICE 1u       /* pointers are device memory on the context's GPU */
+#define TIE_CUDA_NO_SYNC 2u      /* device pointers only: enqueue on the context's stream and return */
+/* expert-kernel selection (default: chosen from n_tokens) */
+#define TIE_CUDA_PATH_AUTO 0u
+#define TIE_CUDA_PATH_STREAM (1u << 8) /* CUDA-core streaming kernels (decode / small batches) */
+#define TIE_CUDA_PATH_TENSOR (2u << 8) /* tcgen05 grouped GEMM (prefill) */
+#define TIE_CUDA_PATH_MASK (3u << 8)
+
+typedef struct tie_cuda_ctx tie_cuda_ctx;
+
+typedef struct {
+	int device;	/* CUDA device ordinal */
+	int hidden;	/* embed_dim          (qwen3moe: 2048) — multiple of 256 */
+	int n_expert;	/* expert_count       (128) */
+	int top_k;	/* expert_used_count  (8), <= 8 */
+	int ffn_dim;	/* expert_ffn_dim     (768) — multiple of 256 */
+	int n_layers;	/* number of layer slots */
+	int max_tokens; /* largest n_tokens of any call (MAX_PROMPT_BATCH_SIZE 4096, config.h:16) */
+	float norm_eps; /* RMSNorm epsilon for tie_cuda_moe_block_inplace */
+	/* The reference's silu_table[] (engine.c:12, filled by silu_table_init, engine.c:297-303):
+	 * TIE_CUDA_SILU_TABLE_SIZE floats, copied at init.  NULL = tie_cuda_silu_table_default(). */
+	const float *silu_table;
+	/* Expert parallelism: this context holds experts [ep_rank*n_expert/ep_size, +n_expert/ep_size).
+	 * ep_size 1 = all experts.  The exchange between ranks is the caller's (see
+	 * tie_cuda_moe_expert_rows / tie_cuda_moe_combine). */
+	int ep_rank, ep_size;
+} tie_cuda_config;
+
+/* ---- lifetime ---- */
+int tie_cuda_init(tie_cuda_ctx **out, const tie_cuda_config *cfg);
+void tie_cuda_destroy(tie_cuda_ctx *c);
+const char *tie_cuda_strerror(int code);
+/* Text of the last CUDA runtime error seen by this context ("" if none). */
+const char *tie_cuda_last_cuda_error(const tie_cuda_ctx *c);
+/* Run all work of this context on the given cudaStream_t (NULL = the context's own stream). */
+int tie_cuda_set_stream(tie_cuda_ctx *c, void *cuda_stream);
+int tie_cuda_synchronize(tie_cuda_ctx *c);
+
+/* The table silu_table_init (engine.c:297-303, expf_fast engine.c:204-225) defines, evaluated
+ * with IEEE division.  (The reference as built with -ffast-math uses a reciprocal estimate for
+ * that division, so its own table differs from this one, and between CPU models, by a few ulp;
+ * a drop-in caller passes its own table in tie_cuda_config.) */
+void tie_cuda_silu_table_default(float *out /* [TIE_CUDA_SILU_TABLE_SIZE] */);
+
+/* ---- weights: replaces the residency step of model_load_tensor (model.c:198-235) ----
+ * Called once per layer after the loader has the four MoE tensors of LayerWeights
+ * (engine.h:77-81) in host memory (mmapped or read).  Copies them to HBM; the host memory may be
+ * unmapped afterwards.  Layouts are the GGUF ones the reference slices in process_expert_task
+ * (engine.c:929-950): router F32 [n_expert][hidden]; gate/up [n_expert][ffn_dim][hidden/256]
+ * blocks; down [n_expert][hidden][ffn_dim/256] blocks.  Types: gate/up/down each Q4_K or Q6_K.
+ * With ep_size > 1 the three expert pointers address ONLY this rank's experts (the slice
+ * starting at expert ep_rank*n_expert/ep_size); the router is always whole.
+ * ffn_norm_w ([hidden] F32, LayerWeights.ffn_norm) may be NULL when
+ * tie_cuda_moe_block_inplace is not used for the layer. */
+int tie_cuda_upload_moe_layer(tie_cuda_ctx *c, int layer, const void *router_w_f32, const void *gate_exps,
+			      int gate_type, const void *up_exps, int up_type, const void *down_exps, int down_type,
+			      const float *ffn_norm_w);
+/* Bytes of HBM holding weights of this context. */
+size_t tie_cuda_weight_bytes(const tie_cuda_ctx *c);
+
+/* ---- the MoE feed-forward call: replaces model_qwen3.c:403-471 ----
+ * x   = ctx->mem.normed_ffn_input  fp32 [n_tokens][hidden]
+ * out = ctx->mem.ffn_down_output   fp32 [n_tokens][hidden]
+ * flags: TIE_CUDA_HOST or TIE_CUDA_DEVICE (| TIE_CUDA_NO_SYNC) (| TIE_CUDA_PATH_*).
+ * Requires ep_size == 1. */
+int tie_cuda_moe_ffn(tie_cuda_ctx *c, int layer, const float *x, float *out, int n_tokens, unsigned flags);
+
+/* hidden += MoE(RMSNorm(hidden) * ffn_norm_w): the FFN half of a layer, model_qwen3.c:392-401
+ * (rms_norm, math_avx2.c:56-97), 403-471, 491 (residual, math_avx2.c:731-751), with the
+ * residual stream resident on the device.  hidden_dev: device fp32 [n_tokens][hidden]. */
+int tie_cuda_moe_block_inplace(tie_cuda_ctx *c, int layer, float *hidden_dev, int n_tokens, unsigned flags);
+
+/* Router only: dispatch_mat_vec on ffn_gate_inp (model_qwen3.c:431, math_avx2.c:228-256),
+ * find_top_k (engine.c:891-914), softmax over the selected logits (engine.c:864-888).
+ * router_bias ([n_expert], may be NULL; not used by the Qwen3 path) is added to the logits
+ * before selection.  topk_idx/topk_w: [n_tokens][top_k] in descending-score order; logits
+ * ([n_tokens][n_expert], may be NULL).  All pointers host or all device per flags. */
+int tie_cuda_moe_route(tie_cuda_ctx *c, int layer, const float *x, int n_tokens, const float *router_bias,
+		       int *topk_idx, float *topk_w, float *logits, unsigned flags);
+/* Same as tie_cuda_moe_ffn with a router bias (skewed-load workloads). */
+int tie_cuda_moe_ffn_biased(tie_cuda_ctx *c, int layer, const float *x, float *out, int n_tokens,
+			    const float *router_bias, unsigned flags);
+
+/* ---- expert-parallel building blocks (the reference has no counterpart: it is one process) ----
+ * y_rows[r] = FFN_{row_expert[r]}(x_rows[r]) = process_expert_task (engine.c:916-964) applied
+ * to independent rows, unweighted.  row_expert holds GLOBAL expert ids, all owned by this
+ * context.  fp32 [n_rows][hidden]; device pointers. */
+int tie_cuda_moe_expert_rows(tie_cuda_ctx *c, int layer, const float *x_rows, const int *row_expert, int n_rows,
+			     float *y_rows, unsigned flags);
+/* out[t] = sum_j w[t][j] * y_rows[t*top_k + j], j ascending, fused multiply-add from zero
+ * (model_qwen3.c:458-467).  Device pointers. */
+int tie_cuda_moe_combine(tie_cuda_ctx *c, const float *y_rows, const float *topk_w, int n_tokens, float *out,
+			 unsigned flags);
+
+/* ---- math_dispatch.c rows (accel = 2) ----
+ * Same argument meaning as the reference's kernels are CALLED with (math_dispatch.c:224,254):
+ * (X, W_data, O, in_dim, start_row, end_row); X, O host fp32.  W must point into (or at) a
+ * host tensor registered by tie_cuda_upload_moe_layer / tie_cuda_register_tensor; the device
+ * copy is found by host address.  They use the context made current by tie_cuda_make_current
+ * (the reference's dispatch signatures carry no context) and return nothing, like the
+ * reference's; failures are reported through tie_cuda_dispatch_status(). */
+int tie_cuda_make_current(tie_cuda_ctx *c);
+/* Upload a stand-alone weight tensor (rows of in_dim inputs; F32, Q4_K or Q6_K) so that the rows
+ * below can find it by host address (model_load_tensor, model.c:198-235, for non-MoE tensors). */
+int tie_cuda_register_tensor(tie_cuda_ctx *c, const void *host_ptr, size_t n_bytes, int ggml_type, int in_dim);
+void tie_cuda_mat_vec_row_f32_q4k_f32(const void *X, const void *W, void *O, int in_dim, int start_row, int end_row);
+void tie_cuda_mat_vec_row_f32_q6k_f32(const void *X, const void *W, void *O, int in_dim, int start_row, int end_row);
+void tie_cuda_mat_vec_row_f32_f32_f32(const void *X, const void *W, void *O, int in_dim, int start_row, int end_row);
+/* swiglu_fn (math_dispatch.h:20; math_avx2.c:908-950): gate[i] = silu_table_lookup(gate[i]) * up[i]. */
+void tie_cuda_swiglu_f32_f32(void *gate, const void *up, int size);
+int tie_cuda_dispatch_status(void); /* 0, or the TIE_CUDA_E* of the last failing dispatch-row call */
+
+/* ---- introspection for tests and benchmarks ---- */
+/* Number of kernels this context has launched since init (all entry points). */
+uint64_t tie_cuda_launch_count(const tie_cuda_ctx *c);
+/* Distinct experts that received at least one row in the last tie_cuda_moe_ffn* / _expert_rows
+ * call (read back from the device; synchronises). */
+int tie_cuda_last_active_experts(tie_cuda_ctx *c);
+/* Per-phase device times of a call, from CUDA events on the context's stream (off by default).
+ * phase_ms[TIE_CUDA_N_PHASES]: router, dispatch sort, input split, gate/up product (+SwiGLU),
+ * down product, combine — of the most recent tie_cuda_moe_ffn* / _block_inplace call.
+ * tie_cuda_get_profile synchronises; returns 1 if that call used the tensor-core kernels, 0 if
+ * the streaming kernels, negative on error. */
+#define TIE_CUDA_N_PHASES 6
+int tie_cuda_set_profiling(tie_cuda_ctx *c, int on);
+int tie_cuda_get_profile(tie_cuda_ctx *c, float *phase_ms);
+const char *tie_cuda_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TIE_CUDA_H */

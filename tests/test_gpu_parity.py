@@ -1,0 +1,293 @@
+"""GPU parity tests: every call goes through the C ABI (tie_b200.moe -> libtie_cuda.so) and is
+checked against the CPU restatement (oracle/) and against the golden vectors produced by the
+reference's own compiled code.
+
+Parity bound of this path: top-k expert ids identical, in order; outputs within 1e-3 per token,
+measured as max_k |gpu - ref| / rms_k(ref) (fp32 accumulation on both sides).
+"""
+import numpy as np
+import pytest
+
+from tie_b200 import synth, workloads
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-3
+
+
+def bits(a):
+    return np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+
+
+@pytest.fixture(scope="module")
+def be(layer0, ref_silu_table):
+    from tie_b200 import moe
+    b = moe.MoeBackend(max_tokens=512, silu_table=ref_silu_table, n_layers=2)
+    b.upload_layer(0, layer0, keep_host=True)
+    yield b
+    b.close()
+
+
+@pytest.fixture(scope="module")
+def port0(port_lib, layer0, ref_silu_table):
+    return port_lib.PortMoe(layer0, silu=ref_silu_table)
+
+
+@pytest.fixture(scope="module")
+def be_small(small_layer, small_shape, ref_silu_table):
+    from tie_b200 import moe
+    s = small_shape
+    b = moe.MoeBackend(hidden=s.hidden, n_expert=s.n_expert, top_k=s.top_k, ffn_dim=s.ffn_dim, max_tokens=256,
+                       silu_table=ref_silu_table)
+    b.upload_layer(0, small_layer, keep_host=True)
+    yield b
+    b.close()
+
+
+# ---------------- router: bit-exact ----------------
+
+@pytest.mark.parametrize("n_tokens", [1, 3, 8, 9, 64, 512])
+def test_route_bit_exact(be, port0, n_tokens):
+    x = synth.make_x(0, n_tokens)
+    idx, w, logits = be.route(0, x)
+    i_r, w_r, l_r = port0.route(x)
+    assert np.array_equal(bits(logits), bits(l_r)), "router logits must replay the AVX2 summation order bit for bit"
+    assert np.array_equal(idx, i_r)
+    assert np.abs(w - w_r).max() <= 2e-7  # expf: CUDA vs glibc, <= 2 ulp of values <= 1
+
+
+def test_route_golden_and_bias(be, golden):
+    g = golden("decode1.npz")
+    idx, w, logits = be.route(0, synth.make_x(0, 1))
+    assert np.array_equal(bits(logits), bits(g["logits"])) and np.array_equal(idx, g["idx"])
+    gs = golden("batch64_skew.npz")
+    idx, w, _ = be.route(0, synth.make_x(0, 64), router_bias=gs["bias"])
+    assert np.array_equal(idx, gs["idx"])
+    assert np.abs(w - gs["w"]).max() <= 2e-7
+
+
+def test_route_tie_rule(be_small, small_shape):
+    """Exact ties resolve to the lower expert id (find_top_k uses strict '>')."""
+    s = small_shape
+    x = np.zeros((2, s.hidden), dtype=np.float32)  # all logits 0 -> all tied
+    bias = np.zeros(s.n_expert, dtype=np.float32)
+    bias[[5, 17]] = 1.0
+    idx, w, logits = be_small.route(0, x, router_bias=bias)
+    assert idx[0].tolist() == [5, 17, 0, 1] and idx[1].tolist() == [5, 17, 0, 1]
+    assert abs(w[0].sum() - 1.0) < 1e-6
+
+
+# ---------------- the MoE feed-forward call ----------------
+
+def _check_ffn(out, ref_out, tol=TOL):
+    err = workloads.rel_rms_err(out, ref_out)
+    assert np.isfinite(out).all()
+    assert err.max() <= tol, f"max rel-rms error {err.max():.3e} at token {int(err.argmax())}"
+    return float(err.max())
+
+
+def test_decode1_matches_reference_golden(be, golden):
+    from tie_b200 import moe
+    g = golden("decode1.npz")
+    out = be.moe_ffn(0, synth.make_x(0, 1))
+    e = _check_ffn(out, g["out"])
+    assert e < 1e-5  # fp32 CUDA-core path: summation-order noise only
+    assert be.last_active_experts() == 8
+
+
+@pytest.mark.parametrize("path", ["stream", "tensor"])
+def test_batch64_uniform_and_skewed(be, golden, port0, path):
+    from tie_b200 import moe
+    p = moe.PATH_STREAM if path == "stream" else moe.PATH_TENSOR
+    x = synth.make_x(0, 64)
+    ref_out, _, _ = port0.moe_ffn(x)
+    g = golden("batch64.npz")
+    assert np.array_equal(bits(ref_out[g["rows"]]), bits(g["out_rows"]))  # restatement == reference
+    out = be.moe_ffn(0, x, path=p)
+    _check_ffn(out, ref_out)
+    gs = golden("batch64_skew.npz")
+    ref_s, _, _ = port0.moe_ffn(x, router_bias=gs["bias"])
+    out_s = be.moe_ffn(0, x, router_bias=gs["bias"], path=p)
+    _check_ffn(out_s, ref_s)
+    _check_ffn(out_s[gs["rows"]], gs["out_rows"])
+
+
+@pytest.mark.parametrize("path", ["tensor", "stream"])
+def test_prefill512(be, golden, port0, path):
+    from tie_b200 import moe
+    p = moe.PATH_STREAM if path == "stream" else moe.PATH_TENSOR
+    x = synth.make_x(0, 512)
+    g = golden("prefill512.npz")
+    out = be.moe_ffn(0, x, path=p)
+    _check_ffn(out[g["rows"]], g["out_rows"])
+    rms = np.sqrt((out.astype(np.float64) ** 2).mean(1))
+    assert np.abs(rms / g["rms"] - 1).max() < 1e-4  # every token, via the golden per-token rms
+    ref_out, _, _ = port0.moe_ffn(x)
+    _check_ffn(out, ref_out)
+
+
+def test_auto_path_and_determinism(be):
+    x = synth.make_x(0, 512)
+    a = be.moe_ffn(0, x)
+    b = be.moe_ffn(0, x)
+    assert np.array_equal(bits(a), bits(b)), "two runs must be bit-identical (no atomics on the data path)"
+
+
+@pytest.mark.parametrize("n_tokens", [2, 5, 17, 33, 130])
+def test_ragged_token_counts_small_shape(be_small, small_layer, small_shape, port_lib, ref_silu_table, n_tokens):
+    from tie_b200 import moe
+    P = port_lib.PortMoe(small_layer, silu=ref_silu_table)
+    x = synth.make_x(workloads.BASE_SEED + 1, n_tokens, small_shape.hidden)
+    ref_out, _, _ = P.moe_ffn(x)
+    for p in (moe.PATH_STREAM, moe.PATH_TENSOR, moe.PATH_AUTO):
+        _check_ffn(be_small.moe_ffn(0, x, path=p), ref_out)
+
+
+def test_small_shape_golden(be_small, small_shape, golden):
+    g = golden("small.npz")
+    x = synth.make_x(workloads.BASE_SEED + 1, 24, small_shape.hidden)
+    idx, w, logits = be_small.route(0, x)
+    assert np.array_equal(bits(logits), bits(g["logits"])) and np.array_equal(idx, g["idx"])
+    _check_ffn(be_small.moe_ffn(0, x), g["out"])
+
+
+def test_all_tokens_to_the_same_experts(be_small, small_layer, small_shape, port_lib, ref_silu_table):
+    """Maximum imbalance: a large bias sends every token to the same top-k experts (most experts
+    receive nothing, a few receive every row — more than one token tile)."""
+    from tie_b200 import moe
+    s = small_shape
+    bias = np.zeros(s.n_expert, dtype=np.float32)
+    bias[[2, 3, 11, 30]] = 100.0
+    x = synth.make_x(workloads.BASE_SEED + 1, 200, s.hidden)
+    P = port_lib.PortMoe(small_layer, silu=ref_silu_table)
+    ref_out, idx, _ = P.moe_ffn(x, router_bias=bias)
+    assert set(np.unique(idx).tolist()) == {2, 3, 11, 30}
+    for p in (moe.PATH_STREAM, moe.PATH_TENSOR):
+        _check_ffn(be_small.moe_ffn(0, x, router_bias=bias, path=p), ref_out)
+        assert be_small.last_active_experts() == 4
+
+
+def test_down_tensor_as_q4k_and_gate_up_as_q6k(small_shape, ref_silu_table, port_lib):
+    """Real Q4_K_M files mix types per tensor; any of the three may be Q4_K or Q6_K."""
+    from tie_b200 import moe
+    s = small_shape
+    seed = 99
+    gu_blocks = s.ffn_dim * (s.hidden // 256)
+    dn_blocks = s.hidden * (s.ffn_dim // 256)
+    router = synth.normal_f32(seed, synth.STREAM_ROUTER, s.n_expert * s.hidden, 0.02).reshape(s.n_expert, s.hidden)
+    layer = synth.MoeLayer(s, router,
+                           synth.q6k_blocks(seed, synth.STREAM_GATE, s.n_expert * gu_blocks),
+                           synth.q6k_blocks(seed, synth.STREAM_UP, s.n_expert * gu_blocks),
+                           synth.q4k_blocks(seed, synth.STREAM_DOWN, s.n_expert * dn_blocks),
+                           gate_type=synth.GGML_Q6_K, up_type=synth.GGML_Q6_K, down_type=synth.GGML_Q4_K)
+    P = port_lib.PortMoe(layer, silu=ref_silu_table)
+    x = synth.make_x(seed, 40, s.hidden)
+    ref_out, _, _ = P.moe_ffn(x)
+    b = moe.MoeBackend(hidden=s.hidden, n_expert=s.n_expert, top_k=s.top_k, ffn_dim=s.ffn_dim, max_tokens=64,
+                       silu_table=ref_silu_table)
+    try:
+        b.upload_layer(0, layer)
+        for p in (moe.PATH_STREAM, moe.PATH_TENSOR):
+            _check_ffn(b.moe_ffn(0, x, path=p), ref_out)
+    finally:
+        b.close()
+
+
+# ---------------- the FFN half of a layer, residual stream on the device ----------------
+
+def test_block_inplace(be, layer0, golden):
+    import torch
+    from tie_b200 import moe
+    g = golden("block_inplace.npz")
+    be.upload_layer(1, layer0, ffn_norm_w=g["norm_w"])
+    h = torch.from_numpy(g["hidden_in"].copy()).cuda()
+    be.moe_block_inplace_ptr(1, h, h.shape[0], moe.DEVICE)
+    out = h.cpu().numpy()
+    _check_ffn(out, g["hidden_out"], tol=TOL)
+
+
+# ---------------- expert-parallel building blocks ----------------
+
+def test_expert_rows_and_combine(be, port0, golden):
+    import torch
+    from tie_b200 import moe
+    g = golden("batch64.npz")
+    x = synth.make_x(0, 64)
+    K = 8
+    rows = np.repeat(x, K, axis=0)
+    row_expert = g["idx"].reshape(-1).astype(np.int32)
+    y_ref = port0.expert_rows(rows, row_expert)
+    xr = torch.from_numpy(rows).cuda()
+    re = torch.from_numpy(row_expert).cuda()
+    for p in (moe.PATH_STREAM, moe.PATH_TENSOR):
+        y = torch.empty_like(xr)
+        be.expert_rows_ptr(0, xr, re, rows.shape[0], y, moe.DEVICE | p)
+        _check_ffn(y.cpu().numpy(), y_ref)
+    w = torch.from_numpy(g["w"]).cuda()
+    out = torch.empty(64, 2048, device="cuda")
+    be.combine_ptr(y, w, 64, out, moe.DEVICE)
+    ref_out, _, _ = port0.moe_ffn(x)
+    _check_ffn(out.cpu().numpy(), ref_out)
+
+
+def test_expert_parallel_shard_rejects_foreign_experts(layer0, ref_silu_table):
+    import torch
+    from tie_b200 import moe
+    part = synth.make_layer(0, layer0.shape, first_expert=16, n_local_expert=16)
+    b = moe.MoeBackend(max_tokens=16, silu_table=ref_silu_table, ep_rank=1, ep_size=8)
+    try:
+        b.upload_layer(0, part)
+        x = torch.zeros(4, 2048, device="cuda")
+        y = torch.empty_like(x)
+        ok = torch.tensor([16, 20, 31, 17], dtype=torch.int32, device="cuda")
+        b.expert_rows_ptr(0, x, ok, 4, y, moe.DEVICE)
+        bad = torch.tensor([16, 3, 31, 17], dtype=torch.int32, device="cuda")
+        with pytest.raises(moe.TieCudaError) as ei:
+            b.expert_rows_ptr(0, x, bad, 4, y, moe.DEVICE | moe.PATH_TENSOR)
+        assert ei.value.code == moe.EKERNEL
+        b.expert_rows_ptr(0, x, ok, 4, y, moe.DEVICE)  # the context stays usable
+    finally:
+        b.close()
+
+
+# ---------------- math_dispatch rows ----------------
+
+def test_dispatch_rows(be, layer0, port_lib, ref_silu_table):
+    be.make_current()
+    s = layer0.shape
+    x = synth.make_x(0, 1)[0]
+    e = 5
+    gsz, dsz = s.gate_bytes_per_expert, s.down_bytes_per_expert
+    g_ref = port_lib.mat_vec(x, layer0.gate[e * gsz:(e + 1) * gsz], 12, 2048, 768)
+    u_ref = port_lib.mat_vec(x, layer0.up[e * gsz:(e + 1) * gsz], 12, 2048, 768)
+    g = be.dispatch_mat_vec(x, layer0.gate.ctypes.data + e * gsz, 12, 2048, 0, 768)
+    u = be.dispatch_mat_vec(x, layer0.up.ctypes.data + e * gsz, 12, 2048, 0, 768)
+    assert np.abs(g - g_ref).max() <= 1e-5 * np.sqrt((g_ref ** 2).mean())
+    assert np.abs(u - u_ref).max() <= 1e-5 * np.sqrt((u_ref ** 2).mean())
+    # a row range, as the threaded dispatcher would call it (math_dispatch.c:262-283)
+    part = be.dispatch_mat_vec(x, layer0.gate.ctypes.data + e * gsz, 12, 2048, 96, 192)
+    assert np.array_equal(part[:96], np.zeros(96, dtype=np.float32)) and np.array_equal(bits(part[96:192]), bits(g[96:192]))
+    h_ref = port_lib.swiglu(ref_silu_table, g_ref, u_ref)
+    h = be.dispatch_swiglu(g_ref, u_ref)
+    assert np.array_equal(bits(h), bits(h_ref)), "table SwiGLU is bit-exact given equal inputs"
+    d_ref = port_lib.mat_vec(h_ref, layer0.down[e * dsz:(e + 1) * dsz], 14, 768, 2048)
+    d = be.dispatch_mat_vec(h_ref, layer0.down.ctypes.data + e * dsz, 14, 768, 0, 2048)
+    assert np.abs(d - d_ref).max() <= 1e-5 * np.sqrt((d_ref ** 2).mean())
+    lg_ref = port_lib.mat_vec(x, layer0.router_w, 0, 2048, 128)
+    lg = be.dispatch_mat_vec(x, layer0.router_w.ctypes.data, 0, 2048, 0, 128)
+    assert np.array_equal(bits(lg), bits(lg_ref))
+
+
+def test_errors_are_codes_not_exits(be):
+    from tie_b200 import moe
+    x = np.zeros((1, 2048), dtype=np.float32)
+    with pytest.raises(moe.TieCudaError) as ei:
+        be.moe_ffn(7, x)  # layer never uploaded / out of range
+    assert ei.value.code == moe.EINVAL
+    with pytest.raises(moe.TieCudaError) as ei:
+        be.moe_ffn(0, np.zeros((513, 2048), dtype=np.float32))  # more tokens than max_tokens
+    assert ei.value.code == moe.EINVAL
+    be.make_current()
+    with pytest.raises(moe.TieCudaError):
+        be.dispatch_mat_vec(x[0], x.ctypes.data, 12, 2048, 0, 8)  # W is not an uploaded tensor
+    assert be.launch_count > 0

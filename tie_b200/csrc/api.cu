@@ -1,0 +1,815 @@
+// C ABI of the library (include/tie_cuda.h): context, weight residency, the MoE feed-forward
+// call and the math_dispatch rows.  Host logic only; kernels live in the other translation units.
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "kernels.cuh"
+
+using namespace tie;
+
+namespace {
+
+tie_cuda_ctx *g_current = nullptr;
+int g_dispatch_status = 0;
+std::mutex g_mutex;
+
+size_t block_bytes(int ggml_type)
+{
+	return ggml_type == TIE_GGML_TYPE_Q4_K ? Q4K_BYTES : (ggml_type == TIE_GGML_TYPE_Q6_K ? Q6K_BYTES : 0);
+}
+
+template <typename T>
+int dev_alloc(tie_cuda_ctx *c, T **p, size_t n)
+{
+	TIE_CUDA_TRY(c, cudaMalloc(reinterpret_cast<void **>(p), n * sizeof(T)));
+	return TIE_CUDA_OK;
+}
+
+#define TRY(expr)                 \
+	do {                      \
+		int _rc = (expr); \
+		if (_rc)          \
+			return _rc; \
+	} while (0)
+
+int alloc_scratch(tie_cuda_ctx *c)
+{
+	Scratch &s = c->s;
+	const size_t T = c->cfg.max_tokens, H = c->cfg.hidden, E = c->cfg.n_expert, K = c->cfg.top_k, F = c->cfg.ffn_dim;
+	const size_t R = T * K;
+	s.rows_cap = R;
+	s.rows_pad = R + 256;
+	TRY(dev_alloc(c, &s.x, T * H));
+	TRY(dev_alloc(c, &s.out, T * H));
+	TRY(dev_alloc(c, &s.logits, T * E));
+	TRY(dev_alloc(c, &s.bias, E));
+	TRY(dev_alloc(c, &s.topk_idx, R));
+	TRY(dev_alloc(c, &s.topk_w, R));
+	TRY(dev_alloc(c, &s.counts, E));
+	TRY(dev_alloc(c, &s.offsets, E + 1));
+	TRY(dev_alloc(c, &s.tile_start, E + 1));
+	TRY(dev_alloc(c, &s.active, E));
+	TRY(dev_alloc(c, &s.n_active, 1));
+	TRY(dev_alloc(c, &s.perm, R));
+	TRY(dev_alloc(c, &s.h, R * F));
+	TRY(dev_alloc(c, &s.y, R * H));
+	TRY(dev_alloc(c, &s.xs_hi, s.rows_pad * H));
+	TRY(dev_alloc(c, &s.xs_lo, s.rows_pad * H));
+	TRY(dev_alloc(c, &s.hs_hi, s.rows_pad * F));
+	TRY(dev_alloc(c, &s.hs_lo, s.rows_pad * F));
+	TRY(dev_alloc(c, &s.status, 1));
+	TRY(dev_alloc(c, &s.row_expert, R));
+	TIE_CUDA_TRY(c, cudaMemset(s.status, 0, sizeof(unsigned)));
+	TIE_CUDA_TRY(c, cudaMemset(s.n_active, 0, sizeof(int)));
+	// rows past the last real one are read (never used) by the tensor path: keep them finite
+	TIE_CUDA_TRY(c, cudaMemset(s.xs_hi, 0, s.rows_pad * H * sizeof(__half)));
+	TIE_CUDA_TRY(c, cudaMemset(s.xs_lo, 0, s.rows_pad * H * sizeof(__half)));
+	TIE_CUDA_TRY(c, cudaMemset(s.hs_hi, 0, s.rows_pad * F * sizeof(__half)));
+	TIE_CUDA_TRY(c, cudaMemset(s.hs_lo, 0, s.rows_pad * F * sizeof(__half)));
+	TIE_CUDA_TRY(c, cudaMallocHost(reinterpret_cast<void **>(&c->pin_x), T * H * sizeof(float)));
+	TIE_CUDA_TRY(c, cudaMallocHost(reinterpret_cast<void **>(&c->pin_out), T * H * sizeof(float)));
+	TIE_CUDA_TRY(c, cudaMallocHost(reinterpret_cast<void **>(&c->pin_idx), R * sizeof(int)));
+	TIE_CUDA_TRY(c, cudaMallocHost(reinterpret_cast<void **>(&c->pin_w), R * sizeof(float)));
+	TIE_CUDA_TRY(c, cudaMallocHost(reinterpret_cast<void **>(&c->pin_logits), T * E * sizeof(float)));
+	return TIE_CUDA_OK;
+}
+
+void free_tensor(DevTensor &t)
+{
+	if (t.ptr)
+		cudaFree(t.ptr);
+	t = DevTensor();
+}
+
+// Copy one stacked expert tensor to the device (re-ordering Q6_K into R8).
+int upload_tensor(tie_cuda_ctx *c, DevTensor &t, const void *host, int type, int rows, int k)
+{
+	const size_t bb = block_bytes(type);
+	if (!bb)
+		return TIE_CUDA_ENOTSUP;
+	if (k % QK_K || rows % 8)
+		return TIE_CUDA_ENOTSUP;
+	const int nb = k / QK_K;
+	free_tensor(t);
+	t.ggml_type = type;
+	t.kind = (type == TIE_GGML_TYPE_Q4_K) ? W_Q4K : W_Q6K_R8;
+	t.rows = rows;
+	t.k = k;
+	t.expert_stride = (size_t)rows * nb * bb;
+	t.bytes = t.expert_stride * c->n_local;
+	t.host_ptr = host;
+	TIE_CUDA_TRY(c, cudaMalloc(reinterpret_cast<void **>(&t.ptr), t.bytes));
+	if (t.kind == W_Q4K) {
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(t.ptr, host, t.bytes, cudaMemcpyHostToDevice, c->stream));
+	} else {
+		uint8_t *raw = nullptr;
+		TIE_CUDA_TRY(c, cudaMalloc(reinterpret_cast<void **>(&raw), t.bytes));
+		cudaError_t e = cudaMemcpyAsync(raw, host, t.bytes, cudaMemcpyHostToDevice, c->stream);
+		int rc = TIE_CUDA_OK;
+		if (e == cudaSuccess)
+			rc = launch_repack_q6k_r8(c, raw, t.ptr, (size_t)rows * c->n_local, nb);
+		cudaStreamSynchronize(c->stream);
+		cudaFree(raw);
+		if (e != cudaSuccess) {
+			snprintf(c->cuda_err, sizeof(c->cuda_err), "upload: %s", cudaGetErrorString(e));
+			return TIE_CUDA_ECUDA;
+		}
+		if (rc)
+			return rc;
+	}
+	TIE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+	c->weight_bytes += t.bytes;
+	return TIE_CUDA_OK;
+}
+
+int add_reg(tie_cuda_ctx *c, const void *host, size_t bytes, const uint8_t *dev, int type, WKind kind, int rows, int k)
+{
+	if (c->n_regs == c->cap_regs) {
+		int nc = c->cap_regs ? c->cap_regs * 2 : 64;
+		void *p = realloc(c->regs, nc * sizeof(*c->regs));
+		if (!p)
+			return TIE_CUDA_ENOMEM;
+		c->regs = static_cast<decltype(c->regs)>(p);
+		c->cap_regs = nc;
+	}
+	c->regs[c->n_regs++] = {host, bytes, dev, type, kind, rows, k};
+	return TIE_CUDA_OK;
+}
+
+bool is_pinned_host(const void *p)
+{
+	cudaPointerAttributes a;
+	if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+		cudaGetLastError();
+		return false;
+	}
+	return a.type == cudaMemoryTypeHost;
+}
+
+int check_status(tie_cuda_ctx *c)
+{
+	unsigned st = 0;
+	TIE_CUDA_TRY(c, cudaMemcpyAsync(&st, c->s.status, sizeof(st), cudaMemcpyDeviceToHost, c->stream));
+	TIE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+	if (st) {
+		snprintf(c->cuda_err, sizeof(c->cuda_err), "device status word 0x%x (%s%s%s)", st,
+			 (st & ST_BAD_EXPERT) ? "expert id out of range " : "", (st & ST_WAIT_TIMEOUT) ? "barrier wait timed out " : "",
+			 (st & ST_BAD_TILE) ? "tile bookkeeping " : "");
+		cudaMemsetAsync(c->s.status, 0, sizeof(unsigned), c->stream);
+		return TIE_CUDA_EKERNEL;
+	}
+	return TIE_CUDA_OK;
+}
+
+// Phase marks: 0 start, 1 router done, 2 dispatch sort done, 3 input split done, 4 gate/up done,
+// 5 down done, 6 combine done.
+void prof_mark(tie_cuda_ctx *c, int id)
+{
+	if (!c->prof_on)
+		return;
+	if (id == 0)
+		for (int i = 0; i < 8; i++)
+			c->prof_set[i] = false;
+	if (cudaEventRecord(c->prof_ev[id], c->stream) == cudaSuccess)
+		c->prof_set[id] = true;
+}
+
+// The expert part on device rows.  x_src: fp32 rows; row r reads x_src[r / src_div].
+// row_expert [n_rows] (device) gives the global expert of every row; y [n_rows][H] receives
+// the unweighted expert outputs in row order.
+int run_experts(tie_cuda_ctx *c, const Layer &L, const float *x_src, int src_div, const int *row_expert, int n_rows, float *y,
+		unsigned flags)
+{
+	const unsigned path = flags & TIE_CUDA_PATH_MASK;
+	bool use_tc;
+	if (path == TIE_CUDA_PATH_TENSOR) {
+		if (!tc_supported(c, L))
+			return TIE_CUDA_ENOTSUP;
+		use_tc = true;
+	} else if (path == TIE_CUDA_PATH_STREAM) {
+		use_tc = false;
+	} else {
+		use_tc = tc_supported(c, L) && n_rows >= 16 * c->n_local;
+	}
+	const int direct = (!use_tc && n_rows <= c->cfg.top_k && src_div == c->cfg.top_k) ? 1 : 0;
+	const int n_tile = ((size_t)n_rows <= (size_t)48 * c->n_local) ? 64 : 128;
+	c->last_direct_rows = direct ? n_rows : -1;
+	c->last_used_tc = use_tc;
+	if (!direct)
+		TRY(launch_sort(c, row_expert, n_rows, n_tile));
+	prof_mark(c, 2);
+	if (use_tc) {
+		TRY(launch_split_rows(c, x_src, c->s.perm, src_div, n_rows, c->cfg.hidden, c->s.xs_hi, c->s.xs_lo));
+		prof_mark(c, 3);
+		TRY(launch_tc_gate_up(c, L, n_rows, n_tile));
+		prof_mark(c, 4);
+		TRY(launch_tc_down(c, L, n_rows, n_tile, y));
+		prof_mark(c, 5);
+	} else {
+		prof_mark(c, 3);
+		TRY(launch_stream_gate_up(c, L, x_src, src_div, row_expert, n_rows, direct));
+		prof_mark(c, 4);
+		TRY(launch_stream_down(c, L, y, row_expert, n_rows, direct));
+		prof_mark(c, 5);
+	}
+	return TIE_CUDA_OK;
+}
+
+int get_layer(tie_cuda_ctx *c, int layer, Layer **L)
+{
+	if (!c || layer < 0 || layer >= c->cfg.n_layers || !c->layers[layer].uploaded)
+		return TIE_CUDA_EINVAL;
+	*L = &c->layers[layer];
+	return TIE_CUDA_OK;
+}
+
+int moe_ffn_device(tie_cuda_ctx *c, Layer &L, const float *x, float *out, int n_tokens, const float *bias_dev,
+		   const float *residual, unsigned flags)
+{
+	Scratch &s = c->s;
+	prof_mark(c, 0);
+	TRY(launch_router(c, x, L.router_w, bias_dev, n_tokens, s.logits, s.topk_idx, s.topk_w));
+	prof_mark(c, 1);
+	TRY(run_experts(c, L, x, c->cfg.top_k, s.topk_idx, n_tokens * c->cfg.top_k, s.y, flags));
+	TRY(launch_combine(c, s.y, s.topk_w, n_tokens, residual, out));
+	prof_mark(c, 6);
+	return TIE_CUDA_OK;
+}
+
+int h2d(tie_cuda_ctx *c, void *dst, const void *src, size_t bytes, void *pin)
+{
+	if (is_pinned_host(src)) {
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, c->stream));
+	} else {
+		// the staging buffer is reused by the next call: make sure the previous copy out of it is done
+		TIE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+		memcpy(pin, src, bytes);
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(dst, pin, bytes, cudaMemcpyHostToDevice, c->stream));
+	}
+	return TIE_CUDA_OK;
+}
+
+// D2H into user memory; *staged tells the caller to memcpy from pin after synchronising.
+int d2h(tie_cuda_ctx *c, void *dst, const void *src, size_t bytes, void *pin, bool *staged)
+{
+	if (is_pinned_host(dst)) {
+		*staged = false;
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, c->stream));
+	} else {
+		*staged = true;
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(pin, src, bytes, cudaMemcpyDeviceToHost, c->stream));
+	}
+	return TIE_CUDA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char *tie_cuda_version(void)
+{
+	return "tie_cuda 0.1 (sm_100a)";
+}
+
+const char *tie_cuda_strerror(int code)
+{
+	switch (code) {
+	case TIE_CUDA_OK:
+		return "ok";
+	case TIE_CUDA_EINVAL:
+		return "invalid argument";
+	case TIE_CUDA_ENOTSUP:
+		return "unsupported tensor type or shape";
+	case TIE_CUDA_ENOMEM:
+		return "out of memory";
+	case TIE_CUDA_ECUDA:
+		return "CUDA error";
+	case TIE_CUDA_ENODEV:
+		return "no usable sm_100 device";
+	case TIE_CUDA_EKERNEL:
+		return "kernel reported an internal check failure";
+	default:
+		return "unknown error";
+	}
+}
+
+const char *tie_cuda_last_cuda_error(const tie_cuda_ctx *c)
+{
+	return c ? c->cuda_err : "";
+}
+
+// engine.c:204-225 (expf_fast) and engine.c:297-303 (silu_table_init), with IEEE division.
+void tie_cuda_silu_table_default(float *out)
+{
+	for (int i = 0; i < SILU_N; i++) {
+		float x = fmaf(20.0f * (float)i, 1.0f / 8191.0f, -10.0f);
+		float a = fmaxf(-88.37626266479492f, fminf(88.37626266479492f, -x));
+		union {
+			float f;
+			int32_t i;
+		} u;
+		u.i = (int32_t)fmaf(12102203.0f, a, 1065353216.0f);
+		float p = u.f;
+		p = p * fmaf(1.9875691500E-4f, p, 1.3981999507E-3f);
+		p = fmaf(p, p, p * fmaf(8.3334519073E-3f, p, 4.1665795894E-2f));
+		p = fmaf(p, p, p * fmaf(1.6666665459E-1f, p, 5.0000001201E-1f));
+		float e = fmaf(u.f, p, u.f);
+		out[i] = x / (1.0f + e);
+	}
+}
+
+int tie_cuda_init(tie_cuda_ctx **out, const tie_cuda_config *cfg)
+{
+	if (!out || !cfg)
+		return TIE_CUDA_EINVAL;
+	*out = nullptr;
+	if (cfg->hidden <= 0 || cfg->hidden % QK_K || cfg->ffn_dim <= 0 || cfg->ffn_dim % QK_K || cfg->n_expert <= 0 ||
+	    cfg->n_expert % 16 || cfg->n_expert > 256 || cfg->top_k <= 0 || cfg->top_k > MAX_TOP_K || cfg->top_k > cfg->n_expert ||
+	    cfg->n_layers <= 0 || cfg->max_tokens <= 0 || cfg->ep_size <= 0 || cfg->ep_rank < 0 || cfg->ep_rank >= cfg->ep_size ||
+	    cfg->n_expert % cfg->ep_size)
+		return TIE_CUDA_EINVAL;
+	int ndev = 0;
+	if (cudaGetDeviceCount(&ndev) != cudaSuccess || cfg->device < 0 || cfg->device >= ndev) {
+		cudaGetLastError();
+		return TIE_CUDA_ENODEV;
+	}
+	cudaDeviceProp prop;
+	if (cudaGetDeviceProperties(&prop, cfg->device) != cudaSuccess || prop.major != 10)
+		return TIE_CUDA_ENODEV;
+	tie_cuda_ctx *c = new (std::nothrow) tie_cuda_ctx();
+	if (!c)
+		return TIE_CUDA_ENOMEM;
+	c->cfg = *cfg;
+	c->cfg.silu_table = nullptr;
+	c->device = cfg->device;
+	c->sm_count = prop.multiProcessorCount;
+	c->n_local = cfg->n_expert / cfg->ep_size;
+	c->first_expert = cfg->ep_rank * c->n_local;
+	int rc = TIE_CUDA_OK;
+	auto fail = [&](int code) {
+		tie_cuda_destroy(c);
+		return code;
+	};
+	if (cudaSetDevice(c->device) != cudaSuccess)
+		return fail(TIE_CUDA_ECUDA);
+	if (cudaStreamCreateWithFlags(&c->own_stream, cudaStreamNonBlocking) != cudaSuccess)
+		return fail(TIE_CUDA_ECUDA);
+	c->stream = c->own_stream;
+	c->layers = new (std::nothrow) Layer[cfg->n_layers];
+	if (!c->layers)
+		return fail(TIE_CUDA_ENOMEM);
+	float *tab = static_cast<float *>(malloc(SILU_N * sizeof(float)));
+	if (!tab)
+		return fail(TIE_CUDA_ENOMEM);
+	if (cfg->silu_table)
+		memcpy(tab, cfg->silu_table, SILU_N * sizeof(float));
+	else
+		tie_cuda_silu_table_default(tab);
+	cudaError_t e = cudaMalloc(reinterpret_cast<void **>(&c->silu), SILU_N * sizeof(float));
+	if (e == cudaSuccess)
+		e = cudaMemcpy(c->silu, tab, SILU_N * sizeof(float), cudaMemcpyHostToDevice);
+	free(tab);
+	if (e != cudaSuccess)
+		return fail(e == cudaErrorMemoryAllocation ? TIE_CUDA_ENOMEM : TIE_CUDA_ECUDA);
+	if ((rc = alloc_scratch(c)) != TIE_CUDA_OK)
+		return fail(rc);
+	if ((rc = tc_setup(c)) != TIE_CUDA_OK)
+		return fail(rc);
+	*out = c;
+	return TIE_CUDA_OK;
+}
+
+void tie_cuda_destroy(tie_cuda_ctx *c)
+{
+	if (!c)
+		return;
+	cudaSetDevice(c->device);
+	if (c->stream)
+		cudaStreamSynchronize(c->stream);
+	{
+		std::lock_guard<std::mutex> lk(g_mutex);
+		if (g_current == c)
+			g_current = nullptr;
+	}
+	if (c->layers) {
+		for (int i = 0; i < c->cfg.n_layers; i++) {
+			Layer &L = c->layers[i];
+			if (L.router_w)
+				cudaFree(L.router_w);
+			if (L.norm_w)
+				cudaFree(L.norm_w);
+			free_tensor(L.gate);
+			free_tensor(L.up);
+			free_tensor(L.down);
+		}
+		delete[] c->layers;
+	}
+	Scratch &s = c->s;
+	void *dev_ptrs[] = {s.x,     s.out,   s.logits, s.bias,  s.topk_idx, s.topk_w, s.counts, s.offsets, s.tile_start, s.active, s.n_active,
+			    s.perm,  s.h,     s.y,	s.xs_hi, s.xs_lo,    s.hs_hi,  s.hs_lo,  s.status,  s.row_expert, c->silu,  c->row_x,
+			    c->row_o};
+	for (void *p : dev_ptrs)
+		if (p)
+			cudaFree(p);
+	void *pin_ptrs[] = {c->pin_x, c->pin_out, c->pin_idx, c->pin_w, c->pin_logits};
+	for (void *p : pin_ptrs)
+		if (p)
+			cudaFreeHost(p);
+	for (int i = 0; i < 8; i++)
+		if (c->prof_ev[i])
+			cudaEventDestroy(c->prof_ev[i]);
+	if (c->own_stream)
+		cudaStreamDestroy(c->own_stream);
+	for (int i = 0; i < c->n_extra; i++)
+		cudaFree(c->extra[i]);
+	free(c->extra);
+	free(c->regs);
+	delete c;
+}
+
+int tie_cuda_set_profiling(tie_cuda_ctx *c, int on)
+{
+	if (!c)
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	if (on && !c->prof_ev[0])
+		for (int i = 0; i < 8; i++)
+			TIE_CUDA_TRY(c, cudaEventCreate(&c->prof_ev[i]));
+	c->prof_on = on != 0;
+	return TIE_CUDA_OK;
+}
+
+int tie_cuda_get_profile(tie_cuda_ctx *c, float *phase_ms)
+{
+	if (!c || !phase_ms || !c->prof_ev[0])
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+	int prev = -1;
+	for (int i = 0; i < TIE_CUDA_N_PHASES; i++)
+		phase_ms[i] = 0.f;
+	for (int i = 0; i <= TIE_CUDA_N_PHASES; i++) {
+		if (!c->prof_set[i])
+			continue;
+		if (prev >= 0 && i >= 1) {
+			float ms = 0.f;
+			TIE_CUDA_TRY(c, cudaEventElapsedTime(&ms, c->prof_ev[prev], c->prof_ev[i]));
+			phase_ms[i - 1] = ms;
+		}
+		prev = i;
+	}
+	return c->last_used_tc ? 1 : 0;
+}
+
+int tie_cuda_set_stream(tie_cuda_ctx *c, void *cuda_stream)
+{
+	if (!c)
+		return TIE_CUDA_EINVAL;
+	c->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : c->own_stream;
+	return TIE_CUDA_OK;
+}
+
+int tie_cuda_synchronize(tie_cuda_ctx *c)
+{
+	if (!c)
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+	return check_status(c);
+}
+
+size_t tie_cuda_weight_bytes(const tie_cuda_ctx *c)
+{
+	return c ? c->weight_bytes : 0;
+}
+
+uint64_t tie_cuda_launch_count(const tie_cuda_ctx *c)
+{
+	return c ? c->launches : 0;
+}
+
+int tie_cuda_last_active_experts(tie_cuda_ctx *c)
+{
+	if (!c)
+		return TIE_CUDA_EINVAL;
+	if (c->last_direct_rows >= 0)
+		return c->last_direct_rows;
+	int n = 0;
+	TIE_CUDA_TRY(c, cudaMemcpyAsync(&n, c->s.n_active, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+	TIE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+	return n;
+}
+
+int tie_cuda_upload_moe_layer(tie_cuda_ctx *c, int layer, const void *router_w_f32, const void *gate_exps, int gate_type,
+			      const void *up_exps, int up_type, const void *down_exps, int down_type, const float *ffn_norm_w)
+{
+	if (!c || layer < 0 || layer >= c->cfg.n_layers || !router_w_f32 || !gate_exps || !up_exps || !down_exps)
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	Layer &L = c->layers[layer];
+	const int H = c->cfg.hidden, E = c->cfg.n_expert, F = c->cfg.ffn_dim;
+	if (!block_bytes(gate_type) || !block_bytes(up_type) || !block_bytes(down_type))
+		return TIE_CUDA_ENOTSUP;
+	L.uploaded = false;
+	if (!L.router_w)
+		TRY(dev_alloc(c, &L.router_w, (size_t)E * H));
+	TIE_CUDA_TRY(c, cudaMemcpyAsync(L.router_w, router_w_f32, (size_t)E * H * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+	L.router_host = router_w_f32;
+	c->weight_bytes += (size_t)E * H * sizeof(float);
+	if (ffn_norm_w) {
+		if (!L.norm_w)
+			TRY(dev_alloc(c, &L.norm_w, (size_t)H));
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(L.norm_w, ffn_norm_w, (size_t)H * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+	}
+	c->weight_bytes -= L.gate.bytes + L.up.bytes + L.down.bytes;
+	TRY(upload_tensor(c, L.gate, gate_exps, gate_type, F, H));
+	TRY(upload_tensor(c, L.up, up_exps, up_type, F, H));
+	TRY(upload_tensor(c, L.down, down_exps, down_type, H, F));
+	TIE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+	TRY(add_reg(c, router_w_f32, (size_t)E * H * sizeof(float), reinterpret_cast<const uint8_t *>(L.router_w), TIE_GGML_TYPE_F32,
+		    W_Q4K, E, H));
+	TRY(add_reg(c, gate_exps, L.gate.bytes, L.gate.ptr, gate_type, L.gate.kind, F, H));
+	TRY(add_reg(c, up_exps, L.up.bytes, L.up.ptr, up_type, L.up.kind, F, H));
+	TRY(add_reg(c, down_exps, L.down.bytes, L.down.ptr, down_type, L.down.kind, H, F));
+	L.uploaded = true;
+	return TIE_CUDA_OK;
+}
+
+int tie_cuda_moe_ffn_biased(tie_cuda_ctx *c, int layer, const float *x, float *out, int n_tokens, const float *router_bias,
+			    unsigned flags)
+{
+	Layer *L;
+	TRY(get_layer(c, layer, &L));
+	if (!x || !out || n_tokens <= 0 || n_tokens > c->cfg.max_tokens || c->cfg.ep_size != 1)
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	const size_t bytes = (size_t)n_tokens * c->cfg.hidden * sizeof(float);
+	const bool dev = flags & TIE_CUDA_DEVICE;
+	const float *bias_dev = nullptr;
+	if (router_bias) {
+		if (dev) {
+			bias_dev = router_bias;
+		} else {
+			TIE_CUDA_TRY(c, cudaMemcpyAsync(c->s.bias, router_bias, c->cfg.n_expert * sizeof(float), cudaMemcpyHostToDevice,
+							c->stream));
+			bias_dev = c->s.bias;
+		}
+	}
+	if (dev) {
+		TRY(moe_ffn_device(c, *L, x, out, n_tokens, bias_dev, nullptr, flags));
+		if (flags & TIE_CUDA_NO_SYNC)
+			return TIE_CUDA_OK;
+		return check_status(c);
+	}
+	bool staged = false;
+	TRY(h2d(c, c->s.x, x, bytes, c->pin_x));
+	TRY(moe_ffn_device(c, *L, c->s.x, c->s.out, n_tokens, bias_dev, nullptr, flags));
+	TRY(d2h(c, out, c->s.out, bytes, c->pin_out, &staged));
+	TRY(check_status(c));
+	if (staged)
+		memcpy(out, c->pin_out, bytes);
+	return TIE_CUDA_OK;
+}
+
+int tie_cuda_moe_ffn(tie_cuda_ctx *c, int layer, const float *x, float *out, int n_tokens, unsigned flags)
+{
+	return tie_cuda_moe_ffn_biased(c, layer, x, out, n_tokens, nullptr, flags);
+}
+
+int tie_cuda_moe_block_inplace(tie_cuda_ctx *c, int layer, float *hidden_dev, int n_tokens, unsigned flags)
+{
+	Layer *L;
+	TRY(get_layer(c, layer, &L));
+	if (!hidden_dev || n_tokens <= 0 || n_tokens > c->cfg.max_tokens || c->cfg.ep_size != 1)
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	TRY(launch_rms_norm(c, hidden_dev, L->norm_w, c->s.x, n_tokens));
+	TRY(moe_ffn_device(c, *L, c->s.x, hidden_dev, n_tokens, nullptr, hidden_dev, flags));
+	if (flags & TIE_CUDA_NO_SYNC)
+		return TIE_CUDA_OK;
+	return check_status(c);
+}
+
+int tie_cuda_moe_route(tie_cuda_ctx *c, int layer, const float *x, int n_tokens, const float *router_bias, int *topk_idx,
+		       float *topk_w, float *logits, unsigned flags)
+{
+	Layer *L;
+	TRY(get_layer(c, layer, &L));
+	if (!x || !topk_idx || !topk_w || n_tokens <= 0 || n_tokens > c->cfg.max_tokens)
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	const int H = c->cfg.hidden, E = c->cfg.n_expert, K = c->cfg.top_k;
+	Scratch &s = c->s;
+	if (flags & TIE_CUDA_DEVICE) {
+		TRY(launch_router(c, x, L->router_w, router_bias, n_tokens, logits ? logits : s.logits, topk_idx, topk_w));
+		if (flags & TIE_CUDA_NO_SYNC)
+			return TIE_CUDA_OK;
+		return check_status(c);
+	}
+	const float *bias_dev = nullptr;
+	if (router_bias) {
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(s.bias, router_bias, E * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+		bias_dev = s.bias;
+	}
+	TRY(h2d(c, s.x, x, (size_t)n_tokens * H * sizeof(float), c->pin_x));
+	TRY(launch_router(c, s.x, L->router_w, bias_dev, n_tokens, s.logits, s.topk_idx, s.topk_w));
+	TIE_CUDA_TRY(c, cudaMemcpyAsync(c->pin_idx, s.topk_idx, (size_t)n_tokens * K * sizeof(int), cudaMemcpyDeviceToHost, c->stream));
+	TIE_CUDA_TRY(c, cudaMemcpyAsync(c->pin_w, s.topk_w, (size_t)n_tokens * K * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+	if (logits)
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(c->pin_logits, s.logits, (size_t)n_tokens * E * sizeof(float), cudaMemcpyDeviceToHost,
+						c->stream));
+	TRY(check_status(c));
+	memcpy(topk_idx, c->pin_idx, (size_t)n_tokens * K * sizeof(int));
+	memcpy(topk_w, c->pin_w, (size_t)n_tokens * K * sizeof(float));
+	if (logits)
+		memcpy(logits, c->pin_logits, (size_t)n_tokens * E * sizeof(float));
+	return TIE_CUDA_OK;
+}
+
+int tie_cuda_moe_expert_rows(tie_cuda_ctx *c, int layer, const float *x_rows, const int *row_expert, int n_rows, float *y_rows,
+			     unsigned flags)
+{
+	Layer *L;
+	TRY(get_layer(c, layer, &L));
+	if (!(flags & TIE_CUDA_DEVICE) || !x_rows || !row_expert || !y_rows || n_rows < 0 || (size_t)n_rows > c->s.rows_cap)
+		return TIE_CUDA_EINVAL;
+	if (n_rows == 0)
+		return TIE_CUDA_OK;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	TRY(run_experts(c, *L, x_rows, 1, row_expert, n_rows, y_rows, flags));
+	if (flags & TIE_CUDA_NO_SYNC)
+		return TIE_CUDA_OK;
+	return check_status(c);
+}
+
+int tie_cuda_moe_combine(tie_cuda_ctx *c, const float *y_rows, const float *topk_w, int n_tokens, float *out, unsigned flags)
+{
+	if (!c || !(flags & TIE_CUDA_DEVICE) || !y_rows || !topk_w || !out || n_tokens <= 0)
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	TRY(launch_combine(c, y_rows, topk_w, n_tokens, nullptr, out));
+	if (flags & TIE_CUDA_NO_SYNC)
+		return TIE_CUDA_OK;
+	return check_status(c);
+}
+
+// ---- math_dispatch rows ----
+
+int tie_cuda_make_current(tie_cuda_ctx *c)
+{
+	std::lock_guard<std::mutex> lk(g_mutex);
+	g_current = c;
+	g_dispatch_status = 0;
+	return TIE_CUDA_OK;
+}
+
+int tie_cuda_dispatch_status(void)
+{
+	return g_dispatch_status;
+}
+
+int tie_cuda_register_tensor(tie_cuda_ctx *c, const void *host_ptr, size_t n_bytes, int ggml_type, int in_dim)
+{
+	if (!c || !host_ptr || !n_bytes || in_dim <= 0)
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	size_t row_bytes;
+	if (ggml_type == TIE_GGML_TYPE_F32) {
+		row_bytes = (size_t)in_dim * 4;
+	} else {
+		if (!block_bytes(ggml_type) || in_dim % QK_K)
+			return TIE_CUDA_ENOTSUP;
+		row_bytes = (size_t)(in_dim / QK_K) * block_bytes(ggml_type);
+	}
+	if (n_bytes % row_bytes)
+		return TIE_CUDA_EINVAL;
+	const size_t rows = n_bytes / row_bytes;
+	const WKind kind = (ggml_type == TIE_GGML_TYPE_Q6_K) ? W_Q6K_R8 : W_Q4K;
+	if (kind == W_Q6K_R8 && rows % 8)
+		return TIE_CUDA_ENOTSUP;
+	if (c->n_extra == c->cap_extra) {
+		int nc = c->cap_extra ? c->cap_extra * 2 : 16;
+		void *p = realloc(c->extra, nc * sizeof(uint8_t *));
+		if (!p)
+			return TIE_CUDA_ENOMEM;
+		c->extra = static_cast<uint8_t **>(p);
+		c->cap_extra = nc;
+	}
+	uint8_t *dev = nullptr;
+	TIE_CUDA_TRY(c, cudaMalloc(reinterpret_cast<void **>(&dev), n_bytes));
+	c->extra[c->n_extra++] = dev;
+	if (kind == W_Q6K_R8) {
+		uint8_t *raw = nullptr;
+		TIE_CUDA_TRY(c, cudaMalloc(reinterpret_cast<void **>(&raw), n_bytes));
+		cudaError_t e = cudaMemcpyAsync(raw, host_ptr, n_bytes, cudaMemcpyHostToDevice, c->stream);
+		int rc = (e == cudaSuccess) ? launch_repack_q6k_r8(c, raw, dev, rows, in_dim / QK_K) : TIE_CUDA_ECUDA;
+		cudaStreamSynchronize(c->stream);
+		cudaFree(raw);
+		if (rc)
+			return rc;
+	} else {
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(dev, host_ptr, n_bytes, cudaMemcpyHostToDevice, c->stream));
+		TIE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+	}
+	c->weight_bytes += n_bytes;
+	return add_reg(c, host_ptr, n_bytes, dev, ggml_type, kind, (int)rows, in_dim);
+}
+
+static int ensure_row_buffers(tie_cuda_ctx *c, size_t n)
+{
+	if (c->row_cap >= n)
+		return TIE_CUDA_OK;
+	if (c->row_x)
+		cudaFree(c->row_x);
+	if (c->row_o)
+		cudaFree(c->row_o);
+	c->row_x = c->row_o = nullptr;
+	c->row_cap = 0;
+	TRY(dev_alloc(c, &c->row_x, n));
+	TRY(dev_alloc(c, &c->row_o, n));
+	c->row_cap = n;
+	return TIE_CUDA_OK;
+}
+
+static int dispatch_mat_vec_row(const void *X, const void *W, void *O, int in_dim, int start_row, int end_row, int type)
+{
+	tie_cuda_ctx *c = g_current;
+	if (!c)
+		return TIE_CUDA_EINVAL;
+	if (!X || !W || !O || in_dim <= 0 || start_row < 0 || end_row <= start_row)
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	const uint8_t *w = static_cast<const uint8_t *>(W);
+	const tie_cuda_ctx::Reg *reg = nullptr;
+	for (int i = c->n_regs - 1; i >= 0; i--) {
+		const uint8_t *h = static_cast<const uint8_t *>(c->regs[i].host);
+		if (w >= h && w < h + c->regs[i].bytes) {
+			reg = &c->regs[i];
+			break;
+		}
+	}
+	if (!reg || reg->type != type || reg->k != in_dim)
+		return TIE_CUDA_EINVAL;
+	const size_t off = w - static_cast<const uint8_t *>(reg->host);
+	size_t row_bytes = (type == TIE_GGML_TYPE_F32) ? (size_t)in_dim * 4 : (size_t)(in_dim / QK_K) * block_bytes(type);
+	if (off % row_bytes)
+		return TIE_CUDA_EINVAL;
+	if (reg->kind == W_Q6K_R8 && type != TIE_GGML_TYPE_F32 && (off / row_bytes) % 8)
+		return TIE_CUDA_ENOTSUP;
+	if (off + (size_t)end_row * row_bytes > reg->bytes)
+		return TIE_CUDA_EINVAL;
+	size_t need = (size_t)((in_dim > end_row) ? in_dim : end_row);
+	TRY(ensure_row_buffers(c, need));
+	TIE_CUDA_TRY(c, cudaMemcpyAsync(c->row_x, X, (size_t)in_dim * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+	if (type == TIE_GGML_TYPE_F32)
+		TRY(launch_router_rows(c, c->row_x, reinterpret_cast<const float *>(reg->dev + off), end_row, in_dim, c->row_o));
+	else
+		TRY(launch_stream_matvec(c, reg->dev + off, reg->kind, in_dim, end_row, c->row_x, c->row_o));
+	TIE_CUDA_TRY(c, cudaMemcpyAsync(static_cast<float *>(O) + start_row, c->row_o + start_row,
+					(size_t)(end_row - start_row) * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+	return check_status(c);
+}
+
+void tie_cuda_mat_vec_row_f32_q4k_f32(const void *X, const void *W, void *O, int in_dim, int start_row, int end_row)
+{
+	int rc = dispatch_mat_vec_row(X, W, O, in_dim, start_row, end_row, TIE_GGML_TYPE_Q4_K);
+	if (rc)
+		g_dispatch_status = rc;
+}
+
+void tie_cuda_mat_vec_row_f32_q6k_f32(const void *X, const void *W, void *O, int in_dim, int start_row, int end_row)
+{
+	int rc = dispatch_mat_vec_row(X, W, O, in_dim, start_row, end_row, TIE_GGML_TYPE_Q6_K);
+	if (rc)
+		g_dispatch_status = rc;
+}
+
+void tie_cuda_mat_vec_row_f32_f32_f32(const void *X, const void *W, void *O, int in_dim, int start_row, int end_row)
+{
+	int rc = dispatch_mat_vec_row(X, W, O, in_dim, start_row, end_row, TIE_GGML_TYPE_F32);
+	if (rc)
+		g_dispatch_status = rc;
+}
+
+void tie_cuda_swiglu_f32_f32(void *gate, const void *up, int size)
+{
+	tie_cuda_ctx *c = g_current;
+	auto run = [&]() -> int {
+		if (!c || !gate || !up || size <= 0)
+			return TIE_CUDA_EINVAL;
+		TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+		TRY(ensure_row_buffers(c, (size_t)size));
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(c->row_x, gate, (size_t)size * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(c->row_o, up, (size_t)size * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+		TRY(launch_swiglu(c, c->row_x, c->row_o, size));
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(gate, c->row_x, (size_t)size * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+		return check_status(c);
+	};
+	int rc = run();
+	if (rc)
+		g_dispatch_status = rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,208 @@
+// Shared internals of the tie_cuda library (sm_100a only).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#include "../../include/tie_cuda.h"
+
+namespace tie {
+
+constexpr int QK_K = 256;	  // gguf.h:100
+constexpr int Q4K_BYTES = 144;	  // sizeof(block_q4_k), gguf.h:108-113
+constexpr int Q6K_BYTES = 210;	  // sizeof(block_q6_k), gguf.h:101-106
+constexpr int MAX_TOP_K = 8;
+constexpr int SILU_N = TIE_CUDA_SILU_TABLE_SIZE;
+
+// Device status word bits (set by kernels instead of trapping).
+constexpr unsigned ST_BAD_EXPERT = 1u;	  // expert id outside this context's range
+constexpr unsigned ST_WAIT_TIMEOUT = 2u;  // a bounded mbarrier wait gave up
+constexpr unsigned ST_BAD_TILE = 4u;	  // tile bookkeeping out of range
+
+// Weight storage kinds on the device.
+//  Q4_K is kept byte-for-byte as in the GGUF (144-byte blocks are 16-byte aligned).
+//  Q6_K is re-ordered at upload into groups of 8 rows ("R8", see repack.cu): same byte
+//  count, every 48-byte quant chunk 16-byte aligned.
+enum WKind : int { W_Q4K = 0, W_Q6K_R8 = 1 };
+
+struct DevTensor {
+	uint8_t *ptr = nullptr;	 // device
+	int ggml_type = -1;
+	WKind kind = W_Q4K;
+	int rows = 0;		 // output rows per expert
+	int k = 0;		 // input dim
+	size_t expert_stride = 0;  // bytes per expert
+	size_t bytes = 0;
+	const void *host_ptr = nullptr;	 // for the dispatch-row registry
+};
+
+struct Layer {
+	bool uploaded = false;
+	float *router_w = nullptr;  // [E][H] f32
+	float *norm_w = nullptr;    // [H] or null
+	DevTensor gate, up, down;
+	const void *router_host = nullptr;
+};
+
+// Scratch arena of one context, sized for max_tokens.
+struct Scratch {
+	float *x = nullptr;	    // [T][H]   staged input (host mode) / normed input (block mode)
+	float *out = nullptr;	    // [T][H]   staged output
+	float *logits = nullptr;    // [T][E]
+	float *bias = nullptr;	    // [E]
+	int *topk_idx = nullptr;    // [T][K]
+	float *topk_w = nullptr;    // [T][K]
+	int *counts = nullptr;	    // [E]
+	int *offsets = nullptr;	    // [E+1]
+	int *tile_start = nullptr;  // [E+1]
+	int *active = nullptr;	    // [E]  compact list of experts with rows
+	int *n_active = nullptr;    // [1]
+	int *perm = nullptr;	    // [R]  sorted position -> row id
+	float *h = nullptr;	    // [R][F]  fp32 activations (stream path), sorted order
+	float *y = nullptr;	    // [R][H]  per-row expert outputs, row-id order
+	__half *xs_hi = nullptr, *xs_lo = nullptr;  // [Rpad][H]  split inputs, sorted order
+	__half *hs_hi = nullptr, *hs_lo = nullptr;  // [Rpad][F]
+	unsigned *status = nullptr;		    // [1]
+	int *row_expert = nullptr;		    // [R] staging for expert_rows
+	size_t rows_cap = 0;			    // R capacity
+	size_t rows_pad = 0;			    // Rpad
+};
+
+}  // namespace tie
+
+struct tie_cuda_ctx {
+	tie_cuda_config cfg;
+	int device = 0;
+	int sm_count = 0;
+	cudaStream_t own_stream = nullptr;
+	cudaStream_t stream = nullptr;
+	float *silu = nullptr;	// device [8192]
+	tie::Layer *layers = nullptr;
+	tie::Scratch s;
+	int first_expert = 0, n_local = 0;
+	// pinned staging for host-pointer calls
+	float *pin_x = nullptr, *pin_out = nullptr;
+	int *pin_idx = nullptr;
+	float *pin_w = nullptr, *pin_logits = nullptr;
+	size_t weight_bytes = 0;
+	uint64_t launches = 0;
+	int last_direct_rows = -1;
+	// optional per-phase timing (tie_cuda_set_profiling): events around the kernel groups of a call
+	bool last_used_tc = false;
+	bool prof_on = false;
+	cudaEvent_t prof_ev[8] = {nullptr};
+	bool prof_set[8] = {false};
+	char cuda_err[256] = {0};
+	// tensor maps for the tcgen05 path: [array 0..3 = xs_hi, xs_lo, hs_hi, hs_lo][n_tile 0..1 = 64,128]
+	CUtensorMap tmap[4][2];
+	bool tmaps_ok = false;
+	// host registry for dispatch rows
+	struct Reg {
+		const void *host;
+		size_t bytes;
+		const uint8_t *dev;
+		int type;
+		tie::WKind kind;
+		int rows, k;
+	} *regs = nullptr;
+	int n_regs = 0, cap_regs = 0;
+	// standalone tensors uploaded through tie_cuda_register_tensor
+	uint8_t **extra = nullptr;
+	int n_extra = 0, cap_extra = 0;
+	// small per-call device buffers for the dispatch rows
+	float *row_x = nullptr, *row_o = nullptr;
+	size_t row_cap = 0;
+};
+
+namespace tie {
+
+// ---- launch bookkeeping ----
+#define TIE_CUDA_TRY(c, expr)                                                                    \
+	do {                                                                                     \
+		cudaError_t _e = (expr);                                                         \
+		if (_e != cudaSuccess) {                                                         \
+			snprintf((c)->cuda_err, sizeof((c)->cuda_err), "%s:%d %s: %s", __FILE__, \
+				 __LINE__, #expr, cudaGetErrorString(_e));                       \
+			return (_e == cudaErrorMemoryAllocation) ? TIE_CUDA_ENOMEM : TIE_CUDA_ECUDA; \
+		}                                                                                \
+	} while (0)
+
+#define TIE_CUDA_LAUNCHED(c)                             \
+	do {                                             \
+		(c)->launches++;                         \
+		TIE_CUDA_TRY(c, cudaGetLastError());     \
+	} while (0)
+
+// ---- device helpers ----
+__device__ __forceinline__ float warp_sum(float v)
+{
+#pragma unroll
+	for (int o = 16; o > 0; o >>= 1)
+		v += __shfl_xor_sync(0xffffffffu, v, o);
+	return v;
+}
+
+// get_scale_min_k4 (math_scalar.c:91-100) on the 12 packed bytes held as three 32-bit words.
+__device__ __forceinline__ void q4k_scale_min(const uint32_t sc[3], int j, int &s, int &m)
+{
+	// byte i of the 12-byte array = (sc[i/4] >> 8*(i%4)) & 0xff
+	auto byte = [&](int i) -> uint32_t { return (sc[i >> 2] >> (8 * (i & 3))) & 0xffu; };
+	if (j < 4) {
+		s = byte(j) & 63;
+		m = byte(j + 4) & 63;
+	} else {
+		s = (byte(j + 4) & 0xF) | ((byte(j - 4) >> 6) << 4);
+		m = (byte(j + 4) >> 4) | ((byte(j) >> 6) << 4);
+	}
+}
+
+// The reference's table-driven SwiGLU exactly as its AVX2 kernel evaluates it
+// (math_avx2.c:908-950, built with -ffast-math: the division by 20 is a multiply by 0.05f):
+// no range check — outside [-10,10] the first/last table segment is extrapolated.
+__device__ __forceinline__ float swiglu_lut(const float *__restrict__ tab, float g, float u)
+{
+	float pos = __fmul_rn(__fmul_rn(__fadd_rn(g, 10.0f), 8191.0f), 0.05f);
+	float r = rintf(pos);
+	int idx;
+	if (!(r >= -2147483648.0f && r < 2147483648.0f))
+		idx = 0;  // cvtps2dq yields INT_MIN for NaN/out-of-range, which the clamp maps to 0
+	else
+		idx = (int)r;
+	idx = max(0, min(idx, SILU_N - 2));
+	float frac = __fsub_rn(pos, (float)idx);
+	float y1 = tab[idx], y2 = tab[idx + 1];
+	return __fmul_rn(__fmaf_rn(__fsub_rn(y2, y1), frac, y1), u);
+}
+
+__device__ __forceinline__ float half_bits_to_float(uint32_t h16)
+{
+	return __half2float(__ushort_as_half((unsigned short)h16));
+}
+
+// Byte offset of (expert-local row, part) pieces in the Q6_K "R8" layout.
+//   group g = row/8 holds 8 rows; nb = blocks per row.
+//   [quant chunks: (r8, b, part) x 48 B][scales: (r8, b, part) x 4 B][d: (r8, b) x 2 B]
+//   part = n*2 + l16  (n = 128-element half of the block, l16 = 16-wide slice of l)
+//   chunk = ql[64n+16*l16 .. +16] | ql[64n+32+16*l16 .. +16] | qh[32n+16*l16 .. +16]
+//   scales = scales[8n + l16 + {0,2,4,6}]
+__host__ __device__ __forceinline__ size_t q6k_r8_group_bytes(int nb)
+{
+	return (size_t)8 * nb * Q6K_BYTES;
+}
+__host__ __device__ __forceinline__ size_t q6k_r8_chunk_off(int nb, int r8, int b, int part)
+{
+	return ((size_t)(r8 * nb + b) * 4 + part) * 48;
+}
+__host__ __device__ __forceinline__ size_t q6k_r8_scale_off(int nb, int r8, int b, int part)
+{
+	return (size_t)8 * nb * 192 + ((size_t)(r8 * nb + b) * 4 + part) * 4;
+}
+__host__ __device__ __forceinline__ size_t q6k_r8_d_off(int nb, int r8, int b)
+{
+	return (size_t)8 * nb * 208 + (size_t)(r8 * nb + b) * 2;
+}
+
+}  // namespace tie

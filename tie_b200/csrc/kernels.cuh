@@ -1,0 +1,32 @@
+// Launch entry points of the kernel translation units (all enqueue on c->stream).
+#pragma once
+#include "common.cuh"
+
+namespace tie {
+
+// router.cu
+int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *bias, int n_tokens, float *logits,
+		  int *topk_idx, float *topk_w);
+int launch_router_rows(tie_cuda_ctx *c, const float *x, const float *w, int n_rows, int in_dim, float *out);
+// sort.cu
+int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile);
+// stream.cu
+int launch_stream_gate_up(tie_cuda_ctx *c, const Layer &L, const float *xin, int src_div, const int *row_expert,
+			  int n_rows, int direct);
+int launch_stream_down(tie_cuda_ctx *c, const Layer &L, float *y, const int *row_expert, int n_rows, int direct);
+int launch_stream_matvec(tie_cuda_ctx *c, const uint8_t *wexp, WKind kind, int k, int rows_total, const float *x, float *o);
+// misc.cu
+int launch_rms_norm(tie_cuda_ctx *c, const float *x, const float *w, float *o, int n_tokens);
+int launch_combine(tie_cuda_ctx *c, const float *y, const float *topk_w, int n_tokens, const float *residual, float *out);
+int launch_split_rows(tie_cuda_ctx *c, const float *x, const int *perm, int src_div, int n_rows, int n_cols, __half *hi,
+		      __half *lo);
+int launch_swiglu(tie_cuda_ctx *c, float *gate, const float *up, int n);
+// tensor.cu
+int tc_setup(tie_cuda_ctx *c);
+bool tc_supported(const tie_cuda_ctx *c, const Layer &L);
+int launch_tc_gate_up(tie_cuda_ctx *c, const Layer &L, int n_rows, int n_tile);
+int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, int n_tile, float *y);
+// repack.cu
+int launch_repack_q6k_r8(tie_cuda_ctx *c, const uint8_t *raw, uint8_t *dst, size_t n_rows_total, int nb);
+
+}  // namespace tie

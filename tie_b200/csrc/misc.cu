@@ -1,0 +1,145 @@
+// Small element-wise kernels around the expert products: RMSNorm, weighted combine (+ residual),
+// the fp16 hi/lo split of activations for the tensor-core path, and the table SwiGLU on its own.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace tie {
+
+// rms_norm_f32_f32_f32_avx2 (math_avx2.c:56-97): 8 lanes of sequential fma(x,x,acc), hsum tree,
+// inv = 1/sqrtf(ss/n + eps), o = (x*w)*inv.  One warp per token: lane l < 8 runs lane l's chain
+// over a shared-memory copy of the row (bit-identical sum of squares); all 32 lanes then scale.
+__global__ void __launch_bounds__(128) rms_norm_rows(const float *__restrict__ x, const float *__restrict__ w,
+						     float *__restrict__ o, int n_tokens, int n, float eps)
+{
+	extern __shared__ float sm[];
+	const int wib = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	const int t = blockIdx.x * (blockDim.x >> 5) + wib;
+	if (t >= n_tokens)
+		return;
+	float *xs = sm + (size_t)wib * n;
+	const float *xr = x + (size_t)t * n;
+	for (int i = lane; i < n / 4; i += 32)
+		reinterpret_cast<float4 *>(xs)[i] = reinterpret_cast<const float4 *>(xr)[i];
+	__syncwarp();
+	float acc = 0.f;
+	if (lane < 8) {
+#pragma unroll 8
+		for (int i = 0; i < n / 8; i++) {
+			float v = xs[8 * i + lane];
+			acc = __fmaf_rn(v, v, acc);
+		}
+	}
+	float v4 = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 4));
+	float t2 = __fadd_rn(v4, __shfl_down_sync(0xffffffffu, v4, 1));
+	float ss = __fadd_rn(t2, __shfl_down_sync(0xffffffffu, t2, 2));
+	ss = __shfl_sync(0xffffffffu, ss, 0);
+	float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)n), eps)));
+	float *orow = o + (size_t)t * n;
+	for (int i = lane; i < n; i += 32)
+		orow[i] = __fmul_rn(__fmul_rn(xs[i], w ? w[i] : 1.0f), inv);
+}
+
+// model_qwen3.c:458-467: acc = 0; acc += w_j * y_j, j ascending (fused multiply-add, as the
+// reference compiles it).  residual != null: out = residual + acc (math_avx2.c:731-751).
+__global__ void __launch_bounds__(256) combine_rows(const float *__restrict__ y, const float *__restrict__ topk_w, int top_k,
+						    int hidden, const float *__restrict__ residual, float *__restrict__ out)
+{
+	const int t = blockIdx.x;
+	const float *yt = y + (size_t)t * top_k * hidden;
+	float wj[MAX_TOP_K];
+#pragma unroll
+	for (int j = 0; j < MAX_TOP_K; j++)
+		wj[j] = (j < top_k) ? topk_w[(size_t)t * top_k + j] : 0.f;
+	for (int k = threadIdx.x * 4; k < hidden; k += blockDim.x * 4) {
+		float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+		for (int j = 0; j < MAX_TOP_K; j++) {
+			if (j < top_k) {
+				float4 v = *reinterpret_cast<const float4 *>(yt + (size_t)j * hidden + k);
+				acc.x = __fmaf_rn(wj[j], v.x, acc.x);
+				acc.y = __fmaf_rn(wj[j], v.y, acc.y);
+				acc.z = __fmaf_rn(wj[j], v.z, acc.z);
+				acc.w = __fmaf_rn(wj[j], v.w, acc.w);
+			}
+		}
+		if (residual) {
+			float4 r = *reinterpret_cast<const float4 *>(residual + (size_t)t * hidden + k);
+			acc.x = __fadd_rn(r.x, acc.x);
+			acc.y = __fadd_rn(r.y, acc.y);
+			acc.z = __fadd_rn(r.z, acc.z);
+			acc.w = __fadd_rn(r.w, acc.w);
+		}
+		*reinterpret_cast<float4 *>(out + (size_t)t * hidden + k) = acc;
+	}
+}
+
+// Gather rows into expert-sorted order and split each fp32 value v into fp16 hi + lo
+// (hi = rn16(v), lo = rn16(v - hi)): hi+lo carries 22 significand bits, which the three-product
+// tensor-core scheme needs to stay within the 1e-3 parity bound.
+__global__ void __launch_bounds__(256) split_rows(const float *__restrict__ x, const int *__restrict__ perm, int src_div,
+						  int n_cols, __half *__restrict__ hi, __half *__restrict__ lo)
+{
+	const int p = blockIdx.x;
+	const int src = perm ? perm[p] / src_div : p;
+	const float *xr = x + (size_t)src * n_cols;
+	__half2 *hr = reinterpret_cast<__half2 *>(hi + (size_t)p * n_cols);
+	__half2 *lr = reinterpret_cast<__half2 *>(lo + (size_t)p * n_cols);
+	for (int k = threadIdx.x * 4; k < n_cols; k += blockDim.x * 4) {
+		float4 v = *reinterpret_cast<const float4 *>(xr + k);
+		__half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
+		float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+		__half2 l0 = __floats2half2_rn(v.x - f0.x, v.y - f0.y), l1 = __floats2half2_rn(v.z - f1.x, v.w - f1.y);
+		hr[k / 2] = h0;
+		hr[k / 2 + 1] = h1;
+		lr[k / 2] = l0;
+		lr[k / 2 + 1] = l1;
+	}
+}
+
+__global__ void __launch_bounds__(256) swiglu_kernel(float *__restrict__ gate, const float *__restrict__ up, int n,
+						     const float *__restrict__ silu)
+{
+	int i = blockIdx.x * blockDim.x + threadIdx.x;
+	if (i < n)
+		gate[i] = swiglu_lut(silu, gate[i], up[i]);
+}
+
+// Distinct experts with at least one row (for the traffic accounting of benchmarks).
+__global__ void copy_int(const int *src, int *dst)
+{
+	*dst = *src;
+}
+
+int launch_rms_norm(tie_cuda_ctx *c, const float *x, const float *w, float *o, int n_tokens)
+{
+	const int H = c->cfg.hidden;
+	const int wpb = 4;
+	size_t smem = (size_t)wpb * H * sizeof(float);
+	rms_norm_rows<<<(n_tokens + wpb - 1) / wpb, wpb * 32, smem, c->stream>>>(x, w, o, n_tokens, H, c->cfg.norm_eps);
+	TIE_CUDA_LAUNCHED(c);
+	return TIE_CUDA_OK;
+}
+
+int launch_combine(tie_cuda_ctx *c, const float *y, const float *topk_w, int n_tokens, const float *residual, float *out)
+{
+	combine_rows<<<n_tokens, 256, 0, c->stream>>>(y, topk_w, c->cfg.top_k, c->cfg.hidden, residual, out);
+	TIE_CUDA_LAUNCHED(c);
+	return TIE_CUDA_OK;
+}
+
+int launch_split_rows(tie_cuda_ctx *c, const float *x, const int *perm, int src_div, int n_rows, int n_cols, __half *hi,
+		      __half *lo)
+{
+	split_rows<<<n_rows, 256, 0, c->stream>>>(x, perm, src_div, n_cols, hi, lo);
+	TIE_CUDA_LAUNCHED(c);
+	return TIE_CUDA_OK;
+}
+
+int launch_swiglu(tie_cuda_ctx *c, float *gate, const float *up, int n)
+{
+	swiglu_kernel<<<(n + 255) / 256, 256, 0, c->stream>>>(gate, up, n, c->silu);
+	TIE_CUDA_LAUNCHED(c);
+	return TIE_CUDA_OK;
+}
+
+}  // namespace tie

@@ -1,0 +1,212 @@
+// Router: logits = x . W_router^T (bit-exact replay of the reference's AVX2 F32 mat-vec),
+// optional bias, top-k with the reference's tie rule, softmax over the selected logits.
+//
+// Reference: dispatch_mat_vec on ffn_gate_inp (model_qwen3.c:431) -> mat_vec_row_f32_f32_f32_avx2
+// (math_avx2.c:228-256): 8 independent lanes, lane l accumulates fma(x[8i+l], w[8i+l], acc_l)
+// for i = 0..in_dim/8-1 in order, then hsum (math_avx2.c:14-21):
+// ((l0+l4)+(l1+l5)) + ((l2+l6)+(l3+l7)).  Replaying that order gives bit-identical logits, which
+// is what makes the top-k selection identical (the 8th/9th logit gap can be a few ulp).
+// find_top_k: engine.c:891-914 (strict '>': ties keep the lower expert index, output sorted by
+// score descending).  softmax: engine.c:864-888 over the k selected raw logits.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace tie {
+
+// hsum over the 8 lanes of one expert held in 8 consecutive threads of a warp.
+__device__ __forceinline__ float hsum8_lanes(float acc)
+{
+	float v = __fadd_rn(acc, __shfl_down_sync(0xffffffffu, acc, 4, 8));  // lanes 0..3: l+l4
+	float t = __fadd_rn(v, __shfl_down_sync(0xffffffffu, v, 1, 8));	     // lane 0: s0+s1, lane 2: s2+s3
+	float r = __fadd_rn(t, __shfl_down_sync(0xffffffffu, t, 2, 8));	     // lane 0: (s0+s1)+(s2+s3)
+	return r;
+}
+
+// Large token counts: CTA = TT tokens x EPC experts; thread = (expert, lane); router weights come
+// straight from L2 (each loaded value feeds TT fused multiply-adds), x is staged in k-chunks.
+template <int TT, int EPC, int KC>
+__global__ void __launch_bounds__(EPC * 8) router_logits_tile(const float *__restrict__ x, const float *__restrict__ w,
+							      const float *__restrict__ bias, float *__restrict__ logits,
+							      int n_tokens, int hidden, int n_expert)
+{
+	__shared__ float xs[TT][KC];
+	const int t0 = blockIdx.x * TT;
+	const int e = blockIdx.y * EPC + (threadIdx.x >> 3);
+	const int l = threadIdx.x & 7;
+	const float *wr = w + (size_t)e * hidden;
+	float acc[TT];
+#pragma unroll
+	for (int i = 0; i < TT; i++)
+		acc[i] = 0.0f;
+	for (int k0 = 0; k0 < hidden; k0 += KC) {
+		__syncthreads();
+		for (int i = threadIdx.x; i < TT * (KC / 4); i += EPC * 8) {
+			int tt = i / (KC / 4), c = i % (KC / 4);
+			float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+			if (t0 + tt < n_tokens)
+				v = *reinterpret_cast<const float4 *>(x + (size_t)(t0 + tt) * hidden + k0 + 4 * c);
+			*reinterpret_cast<float4 *>(&xs[tt][4 * c]) = v;
+		}
+		__syncthreads();
+#pragma unroll 8
+		for (int i = 0; i < KC / 8; i++) {
+			float wv = __ldg(wr + k0 + 8 * i + l);
+#pragma unroll
+			for (int tt = 0; tt < TT; tt++)
+				acc[tt] = __fmaf_rn(xs[tt][8 * i + l], wv, acc[tt]);
+		}
+	}
+#pragma unroll
+	for (int tt = 0; tt < TT; tt++) {
+		float r = hsum8_lanes(acc[tt]);
+		if (l == 0 && t0 + tt < n_tokens) {
+			if (bias)
+				r = __fadd_rn(r, bias[e]);
+			logits[(size_t)(t0 + tt) * n_expert + e] = r;
+		}
+	}
+}
+
+// Decode-sized token counts (<= 8 tokens): one expert per CTA so the 1 MB of router weights is
+// pulled by many SMs at once; the row and the tokens are staged in shared memory with wide
+// loads, then thread (token, lane) runs the sequential chain.
+template <int MAXT>
+__global__ void __launch_bounds__(64) router_logits_decode(const float *__restrict__ x, const float *__restrict__ w,
+							   const float *__restrict__ bias, float *__restrict__ logits,
+							   int n_tokens, int hidden, int n_expert)
+{
+	extern __shared__ float sm[];
+	float *ws = sm;			  // [hidden]
+	float *xs = sm + hidden;	  // [n_tokens][hidden + 8]  (row pad spreads tokens over banks)
+	const int xstride = hidden + 8;
+	const int e = blockIdx.x;
+	const float4 *wr4 = reinterpret_cast<const float4 *>(w + (size_t)e * hidden);
+	for (int i = threadIdx.x; i < hidden / 4; i += 64)
+		reinterpret_cast<float4 *>(ws)[i] = __ldg(wr4 + i);
+	for (int i = threadIdx.x; i < n_tokens * (hidden / 4); i += 64) {
+		int tt = i / (hidden / 4), c4 = i % (hidden / 4);
+		*reinterpret_cast<float4 *>(xs + (size_t)tt * xstride + 4 * c4) =
+			*reinterpret_cast<const float4 *>(x + (size_t)tt * hidden + 4 * c4);
+	}
+	__syncthreads();
+	const int tt = threadIdx.x >> 3, l = threadIdx.x & 7;
+	float acc = 0.0f;
+	if (tt < n_tokens) {
+		const float *xr = xs + (size_t)tt * xstride;
+#pragma unroll 16
+		for (int i = 0; i < hidden / 8; i++)
+			acc = __fmaf_rn(xr[8 * i + l], ws[8 * i + l], acc);
+	}
+	float r = hsum8_lanes(acc);
+	if (l == 0 && tt < n_tokens) {
+		if (bias)
+			r = __fadd_rn(r, bias[e]);
+		logits[(size_t)tt * n_expert + e] = r;
+	}
+}
+
+// One warp per token: k rounds of warp arg-max with key (score desc, index asc), then the
+// softmax of the selected scores: max-subtract, expf, sequential sum, multiply by 1/sum.
+__global__ void __launch_bounds__(128) router_topk(const float *__restrict__ logits, int n_tokens, int n_expert, int top_k,
+						   int *__restrict__ topk_idx, float *__restrict__ topk_w)
+{
+	const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+	const int lane = threadIdx.x & 31;
+	if (warp >= n_tokens)
+		return;
+	const float *lg = logits + (size_t)warp * n_expert;
+	// lane holds experts lane, lane+32, ... (up to 8 per lane: n_expert <= 256)
+	float v[8];
+	const int per = (n_expert + 31) / 32;
+#pragma unroll
+	for (int i = 0; i < 8; i++) {
+		int e = lane + 32 * i;
+		v[i] = (i < per && e < n_expert) ? lg[e] : -INFINITY;
+	}
+	unsigned taken = 0;
+	float my_score = 0.0f;
+	int my_idx = -1;
+	for (int r = 0; r < top_k; r++) {
+		float best = -INFINITY;
+		int bi = 0x7fffffff;
+#pragma unroll
+		for (int i = 0; i < 8; i++) {
+			int e = lane + 32 * i;
+			bool ok = !(taken & (1u << i)) && i < per && e < n_expert;
+			// strictly greater wins; within a lane indices ascend, so ties keep the lower index
+			if (ok && (v[i] > best || bi == 0x7fffffff)) {
+				best = v[i];
+				bi = e;
+			}
+		}
+#pragma unroll
+		for (int o = 16; o > 0; o >>= 1) {
+			float ob = __shfl_xor_sync(0xffffffffu, best, o);
+			int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+			bool take = (oi != 0x7fffffff) && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi));
+			if (take) {
+				best = ob;
+				bi = oi;
+			}
+		}
+		if (bi != 0x7fffffff && (bi & 31) == lane)
+			taken |= 1u << (bi >> 5);
+		if (lane == r) {
+			my_score = best;
+			my_idx = (bi == 0x7fffffff) ? -1 : bi;
+		}
+	}
+	// softmax over lanes 0..top_k-1 (scores are already sorted descending: lane 0 is the max)
+	float mx = __shfl_sync(0xffffffffu, my_score, 0);
+	float ex = (lane < top_k) ? expf(__fsub_rn(my_score, mx)) : 0.0f;
+	float sum = 0.0f;
+	for (int j = 0; j < top_k; j++)
+		sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, ex, j));
+	float inv = __fdiv_rn(1.0f, sum);
+	if (lane < top_k) {
+		topk_idx[(size_t)warp * top_k + lane] = my_idx;
+		topk_w[(size_t)warp * top_k + lane] = __fmul_rn(ex, inv);
+	}
+}
+
+int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *bias, int n_tokens, float *logits,
+		  int *topk_idx, float *topk_w)
+{
+	const int H = c->cfg.hidden, E = c->cfg.n_expert, K = c->cfg.top_k;
+	if (n_tokens <= 8) {
+		size_t smem = ((size_t)H + (size_t)n_tokens * (H + 8)) * sizeof(float);
+		if (smem > 48 * 1024)
+			TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_logits_decode<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+							     (int)smem));
+		router_logits_decode<8><<<E, 64, smem, c->stream>>>(x, w, bias, logits, n_tokens, H, E);
+		TIE_CUDA_LAUNCHED(c);
+	} else if (n_tokens <= 512) {
+		constexpr int TT = 8, EPC = 16;
+		dim3 grid((n_tokens + TT - 1) / TT, E / EPC);
+		router_logits_tile<TT, EPC, 256><<<grid, EPC * 8, 0, c->stream>>>(x, w, bias, logits, n_tokens, H, E);
+		TIE_CUDA_LAUNCHED(c);
+	} else {
+		constexpr int TT = 32, EPC = 16;
+		dim3 grid((n_tokens + TT - 1) / TT, E / EPC);
+		router_logits_tile<TT, EPC, 256><<<grid, EPC * 8, 0, c->stream>>>(x, w, bias, logits, n_tokens, H, E);
+		TIE_CUDA_LAUNCHED(c);
+	}
+	const int warps_per_block = 4;
+	router_topk<<<(n_tokens + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0, c->stream>>>(
+		logits, n_tokens, E, K, topk_idx, topk_w);
+	TIE_CUDA_LAUNCHED(c);
+	return TIE_CUDA_OK;
+}
+
+// Plain F32 mat-vec over the first n_rows rows of w (the math_dispatch F32 row), one vector.
+int launch_router_rows(tie_cuda_ctx *c, const float *x, const float *w, int n_rows, int in_dim, float *out)
+{
+	size_t smem = ((size_t)in_dim + (size_t)(in_dim + 8)) * sizeof(float);
+	if (smem > 48 * 1024)
+		TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_logits_decode<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+	router_logits_decode<8><<<n_rows, 64, smem, c->stream>>>(x, w, nullptr, out, 1, in_dim, n_rows);
+	TIE_CUDA_LAUNCHED(c);
+	return TIE_CUDA_OK;
+}
+
+}  // namespace tie

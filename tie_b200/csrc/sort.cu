@@ -1,0 +1,134 @@
+// Token-to-expert dispatch: a counting sort of rows by expert id, deterministic and without
+// atomics on the output positions.
+//
+// The reference has no such step — it walks tokens one by one and fans the 8 selected experts
+// out to 8 pool threads (model_qwen3.c:415-456).  Here all (token, slot) rows are grouped by
+// expert so that each expert's weights are streamed once per call.
+//
+// Pass 1 (grid = experts): each CTA counts the rows of its expert (ballot + popc, plain sums).
+// Pass 2 (grid = experts): each CTA turns the counts into its exclusive offset (a warp scan over
+// all experts — every CTA repeats it, it is 128 values), then walks the rows in order and writes
+// its rows' ids at offset + rank, rank from a block-wide ballot prefix.  Rows of one expert keep
+// their original order (stable), so the result does not depend on scheduling.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace tie {
+
+constexpr int SORT_THREADS = 256;
+
+__global__ void __launch_bounds__(SORT_THREADS) sort_count(const int *__restrict__ row_expert, int n_rows, int first_expert,
+							   int n_local, int *__restrict__ counts, unsigned *__restrict__ status)
+{
+	__shared__ int wsum[SORT_THREADS / 32];
+	const int e = first_expert + blockIdx.x;
+	int cnt = 0;
+	bool bad = false;
+	for (int r = threadIdx.x; r < n_rows; r += SORT_THREADS) {
+		int re = row_expert[r];
+		cnt += (re == e);
+		if (blockIdx.x == 0 && (re < first_expert || re >= first_expert + n_local))
+			bad = true;
+	}
+	if (bad)
+		atomicOr(status, ST_BAD_EXPERT);
+#pragma unroll
+	for (int o = 16; o > 0; o >>= 1)
+		cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+	if ((threadIdx.x & 31) == 0)
+		wsum[threadIdx.x >> 5] = cnt;
+	__syncthreads();
+	if (threadIdx.x == 0) {
+		int t = 0;
+		for (int i = 0; i < SORT_THREADS / 32; i++)
+			t += wsum[i];
+		counts[blockIdx.x] = t;
+	}
+}
+
+__global__ void __launch_bounds__(SORT_THREADS) sort_place(const int *__restrict__ row_expert, int n_rows, int first_expert,
+							   int n_local, const int *__restrict__ counts, int n_tile,
+							   int *__restrict__ offsets, int *__restrict__ tile_start,
+							   int *__restrict__ active, int *__restrict__ n_active,
+							   int *__restrict__ perm)
+{
+	__shared__ int s_off, s_tile, s_act;
+	__shared__ int wcnt[SORT_THREADS / 32];
+	const int le = blockIdx.x;
+	const int e = first_expert + le;
+	// exclusive prefix over experts < le, by warp 0 (n_local <= 256: 8 per lane)
+	if (threadIdx.x < 32) {
+		int off = 0, tiles = 0, act = 0, tot = 0, ttiles = 0, tact = 0;
+		for (int i = threadIdx.x; i < n_local; i += 32) {
+			int cnt = counts[i];
+			int tl = (cnt + n_tile - 1) / n_tile;
+			if (i < le) {
+				off += cnt;
+				tiles += tl;
+				act += (cnt > 0);
+			}
+			tot += cnt;
+			ttiles += tl;
+			tact += (cnt > 0);
+		}
+#pragma unroll
+		for (int o = 16; o > 0; o >>= 1) {
+			off += __shfl_xor_sync(0xffffffffu, off, o);
+			tiles += __shfl_xor_sync(0xffffffffu, tiles, o);
+			act += __shfl_xor_sync(0xffffffffu, act, o);
+			tot += __shfl_xor_sync(0xffffffffu, tot, o);
+			ttiles += __shfl_xor_sync(0xffffffffu, ttiles, o);
+			tact += __shfl_xor_sync(0xffffffffu, tact, o);
+		}
+		if (threadIdx.x == 0) {
+			s_off = off;
+			s_tile = tiles;
+			s_act = act;
+			offsets[le] = off;
+			tile_start[le] = tiles;
+			if (counts[le] > 0)
+				active[act] = le;
+			if (le == n_local - 1) {
+				offsets[n_local] = tot;
+				tile_start[n_local] = ttiles;
+				*n_active = tact;
+			}
+		}
+	}
+	__syncthreads();
+	int base = s_off;
+	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+	for (int r0 = 0; r0 < n_rows; r0 += SORT_THREADS) {
+		int r = r0 + threadIdx.x;
+		bool mine = (r < n_rows) && (row_expert[r] == e);
+		unsigned b = __ballot_sync(0xffffffffu, mine);
+		if (lane == 0)
+			wcnt[warp] = __popc(b);
+		__syncthreads();
+		int before = 0, total = 0;
+#pragma unroll
+		for (int i = 0; i < SORT_THREADS / 32; i++) {
+			int cw = wcnt[i];
+			before += (i < warp) ? cw : 0;
+			total += cw;
+		}
+		if (mine)
+			perm[base + before + __popc(b & ((1u << lane) - 1u))] = r;
+		base += total;
+		__syncthreads();
+	}
+}
+
+int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile)
+{
+	Scratch &s = c->s;
+	sort_count<<<c->n_local, SORT_THREADS, 0, c->stream>>>(row_expert, n_rows, c->first_expert, c->n_local, s.counts,
+								s.status);
+	TIE_CUDA_LAUNCHED(c);
+	sort_place<<<c->n_local, SORT_THREADS, 0, c->stream>>>(row_expert, n_rows, c->first_expert, c->n_local, s.counts,
+								n_tile, s.offsets, s.tile_start, s.active, s.n_active, s.perm);
+	TIE_CUDA_LAUNCHED(c);
+	return TIE_CUDA_OK;
+}
+
+}  // namespace tie

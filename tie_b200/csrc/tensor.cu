@@ -1,0 +1,453 @@
+// Grouped expert GEMMs for prefill on the 5th-generation tensor cores (tcgen05.mma, accumulators
+// in tensor memory), fed from packed Q4_K / Q6_K super-blocks.
+//
+// Reference: the same arithmetic as process_expert_task (engine.c:916-964) — gate/up products
+// (math_avx2.c:535-604, 753-769), table SwiGLU (math_avx2.c:908-950), down product
+// (math_avx2.c:411-495, 771-787) — but for all tokens routed to an expert at once instead of one
+// token at a time (model_qwen3.c:415).
+//
+// Formulation: out^T = W . x^T.  The weight rows fill the 128-row M dimension of the MMA (expert
+// row counts are multiples of 128), the ragged token count of an expert is the N dimension.
+// A CTA owns one (expert, 128-row tile, token tile).  Per 64-wide k stage:
+//   * 8 producer warps read packed blocks (128-bit loads), dequantise to fp32 exactly as the
+//     reference does (q*(d*sc) - dmin*m, fused), split each weight into fp16 hi + lo and write two
+//     K-major, 128-byte-swizzled operand tiles into shared memory;
+//   * one thread issues TMA tile loads of the token operand (already split into hi/lo fp16, in
+//     expert-sorted row order) into the same swizzled layout;
+//   * one thread issues tcgen05.mma: D += A_hi.B_hi + A_lo.B_hi + A_hi.B_lo (fp32 accumulate in
+//     TMEM).  hi+lo carries 22 significand bits per operand; a single fp16 or bf16 product per
+//     element is NOT accurate enough for the 1e-3 parity bound on this path.
+// Stages are recycled through mbarriers (producers -> full -> MMA -> tcgen05.commit -> empty).
+// Epilogue: tcgen05.ld from TMEM; gate/up: SwiGLU via the table, scaled by 2^-8, split to fp16
+// hi/lo for the down GEMM; down: scaled back and scattered to the (token, slot) row.
+// Every barrier wait is bounded; on timeout the CTA raises ST_WAIT_TIMEOUT in the status word,
+// drains, frees its tensor memory and exits.
+#include "common.cuh"
+#include "kernels.cuh"
+#include "tc_ptx.cuh"
+
+namespace tie {
+
+constexpr int TC_BM = 128;
+constexpr int TC_BK = 64;
+constexpr int TC_PRODUCERS = 256;
+constexpr int TC_THREADS = TC_PRODUCERS + 64;  // + MMA warp + TMA warp
+constexpr int TC_A_TILE = TC_BM * TC_BK * 2;   // bytes of one fp16 operand tile (16 KB)
+constexpr uint64_t TC_WAIT_NS = 500ull * 1000 * 1000;
+constexpr float TC_H_SCALE = 1.0f / 256.0f;  // keeps SwiGLU outputs inside fp16 range; exact (power of two)
+
+template <int NMAT, int NT>
+struct TcCfg {
+	static constexpr int B_TILE = NT * TC_BK * 2;
+	static constexpr int STAGE = NMAT * 2 * TC_A_TILE + 2 * B_TILE;
+	static constexpr int STAGES_RAW = (225 * 1024) / STAGE;
+	static constexpr int STAGES = STAGES_RAW > 4 ? 4 : STAGES_RAW;
+	static constexpr int SMEM = STAGES * STAGE + 1024 /* alignment slack */ + 256 /* barriers */;
+	static constexpr int TMEM_COLS = (NMAT * NT) < 32 ? 32 : (NMAT * NT);
+	static_assert(STAGES >= 2, "need at least two stages");
+	static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns: power of two <= 512");
+};
+
+struct TcShared {
+	uint64_t full[4];
+	uint64_t empty[4];
+	uint64_t done;
+	uint32_t tmem_base;
+	uint32_t abort;
+};
+
+// Bounded wait: false (and the abort flag raised) when the barrier does not flip in time or
+// another CTA has already reported a timeout.
+__device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, unsigned *status)
+{
+	if (ptx::mbar_try_wait(bar, parity))
+		return true;
+	const uint64_t t0 = ptx::globaltimer_ns();
+	uint32_t spins = 0;
+	while (!ptx::mbar_try_wait(bar, parity)) {
+		if (*abort_flag)
+			return false;
+		if ((++spins & 255u) == 0) {
+			if (ptx::globaltimer_ns() - t0 > TC_WAIT_NS || (*(volatile unsigned *)status & ST_WAIT_TIMEOUT)) {
+				atomicOr(status, ST_WAIT_TIMEOUT);
+				*abort_flag = 1;
+				return false;
+			}
+		}
+	}
+	return true;
+}
+
+__device__ __forceinline__ void split_store8(const float w[8], uint32_t addr_hi, uint32_t addr_lo)
+{
+	uint32_t hi[4], lo[4];
+#pragma unroll
+	for (int i = 0; i < 4; i++) {
+		__half2 h = __floats2half2_rn(w[2 * i], w[2 * i + 1]);
+		float2 f = __half22float2(h);
+		__half2 l = __floats2half2_rn(w[2 * i] - f.x, w[2 * i + 1] - f.y);
+		hi[i] = *reinterpret_cast<uint32_t *>(&h);
+		lo[i] = *reinterpret_cast<uint32_t *>(&l);
+	}
+	asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr_hi), "r"(hi[0]), "r"(hi[1]), "r"(hi[2]), "r"(hi[3]) : "memory");
+	asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr_lo), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]) : "memory");
+}
+
+// 32 weights of one (row, half-slice) for k stage `it`: w[0..15] -> k_local 16*hs + i,
+// w[16..31] -> k_local 32 + 16*hs + i.
+template <WKind KIND>
+__device__ __forceinline__ void dequant32(const uint8_t *wexp, int nb, int row, int it, int hs, float w[32]);
+
+template <>
+__device__ __forceinline__ void dequant32<W_Q4K>(const uint8_t *wexp, int nb, int row, int it, int hs, float w[32])
+{
+	const int kb = it >> 2, q = it & 3;
+	const uint8_t *blk = wexp + ((size_t)row * nb + kb) * Q4K_BYTES;
+	const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
+	const uint4 qv = __ldg(reinterpret_cast<const uint4 *>(blk + 16 + 32 * q + 16 * hs));
+	const float d = half_bits_to_float(hdr.x & 0xffffu), dmin = half_bits_to_float(hdr.x >> 16);
+	const uint32_t sc[3] = {hdr.y, hdr.z, hdr.w};
+	int s_lo, m_lo, s_hi, m_hi;
+	q4k_scale_min(sc, 2 * q, s_lo, m_lo);
+	q4k_scale_min(sc, 2 * q + 1, s_hi, m_hi);
+	const float dl = __fmul_rn(d, (float)s_lo), ml = __fmul_rn(dmin, (float)m_lo);
+	const float dh = __fmul_rn(d, (float)s_hi), mh = __fmul_rn(dmin, (float)m_hi);
+	const uint32_t ww[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+	for (int k = 0; k < 4; k++) {
+#pragma unroll
+		for (int j = 0; j < 4; j++) {
+			uint32_t byte = (ww[k] >> (8 * j)) & 0xffu;
+			w[4 * k + j] = __fmaf_rn((float)(byte & 15u), dl, -ml);
+			w[16 + 4 * k + j] = __fmaf_rn((float)(byte >> 4), dh, -mh);
+		}
+	}
+}
+
+template <>
+__device__ __forceinline__ void dequant32<W_Q6K_R8>(const uint8_t *wexp, int nb, int row, int it, int hs, float w[32])
+{
+	const int kb = it >> 2, q = it & 3;
+	const int n = q >> 1, odd = q & 1;
+	const uint8_t *grp = wexp + (size_t)(row >> 3) * q6k_r8_group_bytes(nb);
+	const int r8 = row & 7, pp = n * 2 + hs;
+	const uint4 *ch = reinterpret_cast<const uint4 *>(grp + q6k_r8_chunk_off(nb, r8, kb, pp));
+	const uint4 a = __ldg(ch), b = __ldg(ch + 1), h = __ldg(ch + 2);
+	const uint32_t scw = __ldg(reinterpret_cast<const uint32_t *>(grp + q6k_r8_scale_off(nb, r8, kb, pp)));
+	const float d = half_bits_to_float(__ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb, r8, kb))));
+	const float sA = __fmul_rn(d, (float)(int)(signed char)((scw >> (16 * odd)) & 0xff));
+	const float sB = __fmul_rn(d, (float)(int)(signed char)((scw >> (16 * odd + 8)) & 0xff));
+	const uint32_t A[4] = {a.x, a.y, a.z, a.w}, B[4] = {b.x, b.y, b.z, b.w}, Hh[4] = {h.x, h.y, h.z, h.w};
+#pragma unroll
+	for (int k = 0; k < 4; k++) {
+		uint32_t qa, qb;
+		if (!odd) {
+			qa = (A[k] & 0x0F0F0F0Fu) | ((Hh[k] << 4) & 0x30303030u);
+			qb = (B[k] & 0x0F0F0F0Fu) | ((Hh[k] << 2) & 0x30303030u);
+		} else {
+			qa = ((A[k] >> 4) & 0x0F0F0F0Fu) | (Hh[k] & 0x30303030u);
+			qb = ((B[k] >> 4) & 0x0F0F0F0Fu) | ((Hh[k] >> 2) & 0x30303030u);
+		}
+#pragma unroll
+		for (int j = 0; j < 4; j++) {
+			w[4 * k + j] = __fmul_rn(sA, (float)((int)((qa >> (8 * j)) & 0xffu) - 32));
+			w[16 + 4 * k + j] = __fmul_rn(sB, (float)((int)((qb >> (8 * j)) & 0xffu) - 32));
+		}
+	}
+}
+
+template <WKind KIND, int NMAT, int NT>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__ CUtensorMap tm_lo,
+		const uint8_t *__restrict__ w0, const uint8_t *__restrict__ w1, size_t expert_stride, int k_dim,
+		const int *__restrict__ offsets, const int *__restrict__ tile_start, int n_local,
+		__half *__restrict__ h_hi, __half *__restrict__ h_lo, float *__restrict__ y, const int *__restrict__ perm,
+		int out_stride, const float *__restrict__ silu, unsigned *__restrict__ status)
+{
+	using Cfg = TcCfg<NMAT, NT>;
+	constexpr int S = Cfg::STAGES;
+	extern __shared__ uint8_t smem_raw[];
+
+	// ---- which (expert, token tile) is this CTA? ----
+	const int slot = blockIdx.y;
+	__shared__ int s_skip;
+	if (threadIdx.x == 0)
+		s_skip = (slot >= tile_start[n_local]) || (*(volatile unsigned *)status & ST_WAIT_TIMEOUT);
+	__syncthreads();
+	if (s_skip)
+		return;
+	int lo_e = 0, hi_e = n_local - 1;  // largest le with tile_start[le] <= slot (and a non-empty tile range)
+	while (lo_e < hi_e) {
+		int mid = (lo_e + hi_e + 1) >> 1;
+		if (tile_start[mid] <= slot)
+			lo_e = mid;
+		else
+			hi_e = mid - 1;
+	}
+	const int le = lo_e;
+	const int row0 = offsets[le] + (slot - tile_start[le]) * NT;
+	const int n_valid = min(NT, offsets[le + 1] - row0);
+	if (n_valid <= 0) {
+		if (threadIdx.x == 0)
+			atomicOr(status, ST_BAD_TILE);
+		return;
+	}
+	const int m0 = blockIdx.x * TC_BM;
+	const int nb = k_dim / QK_K;
+	const int k_iters = k_dim / TC_BK;
+
+	const uint32_t raw = ptx::smem_u32(smem_raw);
+	const uint32_t tiles = (raw + 1023u) & ~1023u;
+	TcShared *sh = reinterpret_cast<TcShared *>(smem_raw + (tiles - raw) + (size_t)S * Cfg::STAGE);
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+	auto a_tile = [&](int s, int m, int hl) -> uint32_t { return tiles + s * Cfg::STAGE + (m * 2 + hl) * TC_A_TILE; };
+	auto b_tile = [&](int s, int hl) -> uint32_t { return tiles + s * Cfg::STAGE + NMAT * 2 * TC_A_TILE + hl * Cfg::B_TILE; };
+
+	if (threadIdx.x == 0) {
+		for (int s = 0; s < S; s++) {
+			ptx::mbar_init(ptx::smem_u32(&sh->full[s]), TC_PRODUCERS + 1);
+			ptx::mbar_init(ptx::smem_u32(&sh->empty[s]), 1);
+		}
+		ptx::mbar_init(ptx::smem_u32(&sh->done), 1);
+		sh->abort = 0;
+		ptx::fence_barrier_init();
+		ptx::fence_proxy_async_smem();
+	}
+	if (warp == TC_PRODUCERS / 32) {  // MMA warp owns the tensor-memory allocation
+		ptx::tmem_alloc(ptx::smem_u32(&sh->tmem_base), Cfg::TMEM_COLS);
+		ptx::tmem_relinquish();
+	}
+	if (warp == TC_PRODUCERS / 32 + 1 && lane == 0) {
+		ptx::prefetch_tmap(&tm_hi);
+		ptx::prefetch_tmap(&tm_lo);
+	}
+	ptx::tc_fence_before();
+	__syncthreads();
+	ptx::tc_fence_after();
+	const uint32_t tmem = sh->tmem_base;
+	volatile uint32_t *abort_flag = &sh->abort;
+
+	if (warp < TC_PRODUCERS / 32) {
+		// ================= producers: dequantise A tiles =================
+		const int row = threadIdx.x & 127, hs = threadIdx.x >> 7;
+		const uint8_t *we[2] = {w0 + (size_t)le * expert_stride, (NMAT == 2) ? w1 + (size_t)le * expert_stride : nullptr};
+		const uint32_t row_off = row * 128;
+		const uint32_t sw = row & 7;
+		for (int it = 0; it < k_iters; it++) {
+			const int s = it % S;
+			if (it >= S && !tc_wait(ptx::smem_u32(&sh->empty[s]), ((it / S) & 1) ^ 1, abort_flag, status))
+				break;
+#pragma unroll
+			for (int m = 0; m < NMAT; m++) {
+				float w[32];
+				dequant32<KIND>(we[m], nb, m0 + row, it, hs, w);
+				const uint32_t ah = a_tile(s, m, 0) + row_off, al = a_tile(s, m, 1) + row_off;
+#pragma unroll
+				for (int cc = 0; cc < 4; cc++) {
+					// chunks 2hs, 2hs+1 (first 16 weights) and 4+2hs, 4+2hs+1 (second 16)
+					const uint32_t c = ((cc & 2) ? 4u : 0u) + 2u * hs + (cc & 1);
+					const uint32_t off = (c ^ sw) << 4;
+					split_store8(&w[8 * cc], ah + off, al + off);
+				}
+			}
+			ptx::fence_proxy_async_smem();
+			ptx::mbar_arrive(ptx::smem_u32(&sh->full[s]));
+		}
+	} else if (warp == TC_PRODUCERS / 32) {
+		// ================= MMA issuer =================
+		if (lane == 0) {
+			constexpr uint32_t idesc = ptx::umma_idesc_f16(TC_BM, NT);
+			bool ok = true;
+			for (int it = 0; it < k_iters && ok; it++) {
+				const int s = it % S;
+				ok = tc_wait(ptx::smem_u32(&sh->full[s]), (it / S) & 1, abort_flag, status);
+				if (!ok)
+					break;
+				ptx::tc_fence_after();
+#pragma unroll
+				for (int kk = 0; kk < TC_BK / 16; kk++) {
+					const uint64_t bh = ptx::umma_desc_sw128(b_tile(s, 0)) + 2 * kk;
+					const uint64_t bl = ptx::umma_desc_sw128(b_tile(s, 1)) + 2 * kk;
+#pragma unroll
+					for (int m = 0; m < NMAT; m++) {
+						const uint64_t ahd = ptx::umma_desc_sw128(a_tile(s, m, 0)) + 2 * kk;
+						const uint64_t ald = ptx::umma_desc_sw128(a_tile(s, m, 1)) + 2 * kk;
+						const uint32_t d = tmem + m * NT;
+						ptx::mma_f16_ss(d, ahd, bh, idesc, (it > 0 || kk > 0) ? 1u : 0u);
+						ptx::mma_f16_ss(d, ald, bh, idesc, 1u);
+						ptx::mma_f16_ss(d, ahd, bl, idesc, 1u);
+					}
+				}
+				ptx::mma_commit(ptx::smem_u32(&sh->empty[s]));
+			}
+			ptx::mma_commit(ptx::smem_u32(&sh->done));
+		}
+	} else {
+		// ================= TMA loader for the token operand =================
+		if (lane == 0) {
+			for (int it = 0; it < k_iters; it++) {
+				const int s = it % S;
+				if (it >= S && !tc_wait(ptx::smem_u32(&sh->empty[s]), ((it / S) & 1) ^ 1, abort_flag, status))
+					break;
+				const uint32_t fb = ptx::smem_u32(&sh->full[s]);
+				ptx::mbar_arrive_expect_tx(fb, 2 * Cfg::B_TILE);
+				ptx::tma_load_2d(b_tile(s, 0), &tm_hi, fb, it * TC_BK, row0);
+				ptx::tma_load_2d(b_tile(s, 1), &tm_lo, fb, it * TC_BK, row0);
+			}
+		}
+	}
+
+	// ================= epilogue: 8 warps, TMEM lane quadrant = warp % 4, columns split in two =================
+	if (warp < TC_PRODUCERS / 32) {
+		const bool ok = tc_wait(ptx::smem_u32(&sh->done), 0, abort_flag, status);
+		ptx::tc_fence_after();
+		if (ok) {
+			const int quad = warp & 3, chalf = warp >> 2;
+			const int mrow = m0 + quad * 32 + lane;
+			const uint32_t tlane = tmem + ((uint32_t)(quad * 32) << 16);
+			for (int c0 = chalf * (NT / 2); c0 < (chalf + 1) * (NT / 2); c0 += 16) {
+				if (c0 >= n_valid)
+					break;
+				uint32_t g[16], u[16];
+				ptx::tmem_ld16(tlane + c0, g);
+				if (NMAT == 2)
+					ptx::tmem_ld16(tlane + NT + c0, u);
+				ptx::tmem_ld_wait();
+#pragma unroll
+				for (int j = 0; j < 16; j++) {
+					const int n = c0 + j;
+					if (n < n_valid) {
+						if (NMAT == 2) {
+							float hv = swiglu_lut(silu, __uint_as_float(g[j]), __uint_as_float(u[j])) * TC_H_SCALE;
+							__half hh = __float2half_rn(hv);
+							__half hl = __float2half_rn(hv - __half2float(hh));
+							const size_t o = (size_t)(row0 + n) * out_stride + mrow;
+							h_hi[o] = hh;
+							h_lo[o] = hl;
+						} else {
+							const int rid = perm[row0 + n];
+							y[(size_t)rid * out_stride + mrow] = __uint_as_float(g[j]) * (1.0f / TC_H_SCALE);
+						}
+					}
+				}
+			}
+		}
+	}
+	if (*abort_flag) {
+		// give copies that may still be in flight time to land before the CTA's memory is released
+		for (int i = 0; i < 200; i++)
+			__nanosleep(1000);
+	}
+	ptx::tc_fence_before();
+	__syncthreads();
+	if (warp == TC_PRODUCERS / 32)
+		ptx::tmem_dealloc(tmem, Cfg::TMEM_COLS);
+}
+
+// ---- host side ----
+
+typedef CUresult (*PFN_encodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+				    const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+				    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static PFN_encodeTiled get_encode_fn()
+{
+	static PFN_encodeTiled fn = nullptr;
+	if (!fn) {
+		void *p = nullptr;
+		cudaDriverEntryPointQueryResult qres;
+		if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+		    qres == cudaDriverEntryPointSuccess)
+			fn = reinterpret_cast<PFN_encodeTiled>(p);
+	}
+	return fn;
+}
+
+// fp16 [rows][cols] row-major, box = 64 columns x box_rows rows, 128-byte swizzle.
+static int make_tmap(tie_cuda_ctx *c, CUtensorMap *tm, void *base, size_t rows, size_t cols, int box_rows)
+{
+	PFN_encodeTiled enc = get_encode_fn();
+	if (!enc) {
+		snprintf(c->cuda_err, sizeof(c->cuda_err), "cuTensorMapEncodeTiled entry point not found");
+		return TIE_CUDA_ECUDA;
+	}
+	cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+	cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+	cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+	cuuint32_t estr[2] = {1, 1};
+	CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+			 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+	if (r != CUDA_SUCCESS) {
+		snprintf(c->cuda_err, sizeof(c->cuda_err), "cuTensorMapEncodeTiled failed: %d", (int)r);
+		return TIE_CUDA_ECUDA;
+	}
+	return TIE_CUDA_OK;
+}
+
+int tc_setup(tie_cuda_ctx *c)
+{
+	Scratch &s = c->s;
+	void *bases[4] = {s.xs_hi, s.xs_lo, s.hs_hi, s.hs_lo};
+	size_t cols[4] = {(size_t)c->cfg.hidden, (size_t)c->cfg.hidden, (size_t)c->cfg.ffn_dim, (size_t)c->cfg.ffn_dim};
+	const int nts[2] = {64, 128};
+	for (int a = 0; a < 4; a++)
+		for (int n = 0; n < 2; n++) {
+			int rc = make_tmap(c, &c->tmap[a][n], bases[a], s.rows_pad, cols[a], nts[n]);
+			if (rc)
+				return rc;
+		}
+	c->tmaps_ok = true;
+	return TIE_CUDA_OK;
+}
+
+template <WKind KIND, int NMAT, int NT>
+static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1, const CUtensorMap &tmh, const CUtensorMap &tml,
+		       int n_rows, float *y)
+{
+	using Cfg = TcCfg<NMAT, NT>;
+	Scratch &s = c->s;
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_tc<KIND, NMAT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+	const int max_tiles = min(c->n_local, n_rows) + n_rows / NT;
+	dim3 grid(t0.rows / TC_BM, max_tiles);
+	grouped_gemm_tc<KIND, NMAT, NT><<<grid, TC_THREADS, Cfg::SMEM, c->stream>>>(
+		tmh, tml, t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride, t0.k, s.offsets, s.tile_start, c->n_local, s.hs_hi,
+		s.hs_lo, y, s.perm, t0.rows, c->silu, s.status);
+	TIE_CUDA_LAUNCHED(c);
+	return TIE_CUDA_OK;
+}
+
+template <int NMAT>
+static int launch_tc_n(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1, int arr, int n_tile, int n_rows, float *y)
+{
+	const int ni = (n_tile == 64) ? 0 : 1;
+	const CUtensorMap &tmh = c->tmap[arr][ni], &tml = c->tmap[arr + 1][ni];
+	if (t0.kind == W_Q4K) {
+		if (n_tile == 64)
+			return launch_tc_t<W_Q4K, NMAT, 64>(c, t0, t1, tmh, tml, n_rows, y);
+		return launch_tc_t<W_Q4K, NMAT, 128>(c, t0, t1, tmh, tml, n_rows, y);
+	}
+	if (n_tile == 64)
+		return launch_tc_t<W_Q6K_R8, NMAT, 64>(c, t0, t1, tmh, tml, n_rows, y);
+	return launch_tc_t<W_Q6K_R8, NMAT, 128>(c, t0, t1, tmh, tml, n_rows, y);
+}
+
+bool tc_supported(const tie_cuda_ctx *c, const Layer &L)
+{
+	return c->tmaps_ok && L.gate.kind == L.up.kind && L.gate.rows % TC_BM == 0 && L.down.rows % TC_BM == 0 &&
+	       L.gate.k % QK_K == 0 && L.down.k % QK_K == 0;
+}
+
+// xs_hi/xs_lo must hold the split inputs in sorted order; writes hs_hi/hs_lo.
+int launch_tc_gate_up(tie_cuda_ctx *c, const Layer &L, int n_rows, int n_tile)
+{
+	return launch_tc_n<2>(c, L.gate, &L.up, 0, n_tile, n_rows, nullptr);
+}
+
+// reads hs_hi/hs_lo; writes y[perm[p]].
+int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, int n_tile, float *y)
+{
+	return launch_tc_n<1>(c, L.down, nullptr, 2, n_tile, n_rows, y);
+}
+
+}  // namespace tie
