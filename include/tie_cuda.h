@@ -40,6 +40,11 @@ extern "C" {
 #define TIE_CUDA_HOST 0u         /* pointers are host memory (the drop-in case: ctx->mem.* buffers) */
 #define TIE_CUDA_DEVICE 1u       /* pointers are device memory on the context's GPU */
 #define TIE_CUDA_NO_SYNC 2u      /* device pointers only: enqueue on the context's stream and return */
+/* Record the call's copies and kernels into a CUDA graph the first time it is seen with these
+ * pointers, sizes and flags, and replay the graph afterwards (the reference calls the layer with
+ * the same ctx->mem buffers every step, so decode steps become one graph launch).  Ignored while
+ * the context runs on the legacy default stream or profiling is on. */
+#define TIE_CUDA_GRAPH 4u
 /* expert-kernel selection (default: chosen from n_tokens) */
 #define TIE_CUDA_PATH_AUTO 0u
 #define TIE_CUDA_PATH_STREAM (1u << 8) /* CUDA-core streaming kernels (decode / small batches) */
@@ -72,7 +77,8 @@ void tie_cuda_destroy(tie_cuda_ctx *c);
 const char *tie_cuda_strerror(int code);
 /* Text of the last CUDA runtime error seen by this context ("" if none). */
 const char *tie_cuda_last_cuda_error(const tie_cuda_ctx *c);
-/* Run all work of this context on the given cudaStream_t (NULL = the context's own stream). */
+/* Run all work of this context on the given cudaStream_t (NULL is the legacy default stream).
+ * Until this is called the context uses a non-blocking stream of its own. */
 int tie_cuda_set_stream(tie_cuda_ctx *c, void *cuda_stream);
 int tie_cuda_synchronize(tie_cuda_ctx *c);
 
@@ -131,6 +137,18 @@ int tie_cuda_moe_expert_rows(tie_cuda_ctx *c, int layer, const float *x_rows, co
  * (model_qwen3.c:458-467).  Device pointers. */
 int tie_cuda_moe_combine(tie_cuda_ctx *c, const float *y_rows, const float *topk_w, int n_tokens, float *out,
 			 unsigned flags);
+
+/* Dispatch for expert parallelism: group this rank's n_tokens*top_k (token, slot) rows by expert
+ * id (a stable counting sort; experts of one rank are contiguous, so the result is also grouped
+ * by destination rank).  send_rows[p] = x[token of row perm[p]] (fp32 [n_tokens*top_k][hidden]),
+ * send_expert[p] = its expert id, expert_counts[e] = rows for expert e (int [n_expert]).  The
+ * permutation stays in the context for tie_cuda_moe_ep_combine.  Device pointers. */
+int tie_cuda_moe_ep_dispatch(tie_cuda_ctx *c, const float *x, const int *topk_idx, int n_tokens, float *send_rows,
+			     int *send_expert, int *expert_counts, unsigned flags);
+/* out[t] = sum_j w[t][j] * y_sorted[position of row (t, j) in the last dispatch], j ascending
+ * (the combine of model_qwen3.c:458-467 on rows that came back in dispatch order). */
+int tie_cuda_moe_ep_combine(tie_cuda_ctx *c, const float *y_sorted, const float *topk_w, int n_tokens, float *out,
+			    unsigned flags);
 
 /* ---- math_dispatch.c rows (accel = 2) ----
  * Same argument meaning as the reference's kernels are CALLED with (math_dispatch.c:224,254):

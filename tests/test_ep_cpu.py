@@ -1,0 +1,79 @@
+"""CPU test of the expert-parallel exchange (tie_b200/ep.py) on two gloo ranks.
+
+The device ops are replaced by stand-ins built on the CPU restatement (oracle/), so what is
+tested is the bookkeeping: counts exchange, all-to-all splits, order of rows on the way back,
+combine through the dispatch permutation.  The result must equal the single-process oracle."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.abspath(os.path.join(os.path.dirname(__file__), ".."))
+
+WORKER = r"""
+import os, sys
+sys.path.insert(0, %(root)r)
+import numpy as np, torch, torch.distributed as dist
+from tie_b200 import synth, workloads, ep
+from oracle import port
+
+rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%(port)d", rank=rank, world_size=world)
+shape = synth.MoeShape(hidden=512, n_expert=32, top_k=4, ffn_dim=256)
+layer = synth.make_layer(workloads.BASE_SEED + 1, shape)
+P = port.PortMoe(layer)
+n_local = shape.n_expert // world
+
+class Ops:
+    K, H, E = shape.top_k, shape.hidden, shape.n_expert
+    def empty(self, shp, dtype): return torch.zeros(shp, dtype=dtype)
+    def route(self, x, idx, w):
+        i, ww, _ = P.route(x.numpy()); idx.copy_(torch.from_numpy(i)); w.copy_(torch.from_numpy(ww))
+    def dispatch(self, x, idx, send_rows, send_expert, counts):
+        flat = idx.numpy().reshape(-1)
+        perm = np.argsort(flat, kind="stable")
+        self.inv = np.empty_like(perm); self.inv[perm] = np.arange(perm.size)
+        send_rows.copy_(torch.from_numpy(x.numpy()[perm // self.K]))
+        send_expert.copy_(torch.from_numpy(flat[perm].astype(np.int32)))
+        counts.copy_(torch.from_numpy(np.bincount(flat, minlength=self.E).astype(np.int32)))
+    def expert_rows(self, rows, experts, n, y):
+        if n:
+            e = experts.numpy()[:n]
+            assert ((e >= rank * n_local) & (e < (rank + 1) * n_local)).all(), "row sent to the wrong rank"
+            y[:n].copy_(torch.from_numpy(P.expert_rows(rows.numpy()[:n], e)))
+    def combine(self, y_sorted, w, out):
+        ys = y_sorted.numpy()[self.inv].reshape(w.shape[0], self.K, self.H)
+        acc = np.zeros((w.shape[0], self.H), dtype=np.float32)
+        for j in range(self.K):
+            acc = (w.numpy()[:, j:j+1].astype(np.float64) * ys[:, j].astype(np.float64) + acc.astype(np.float64)).astype(np.float32)
+        out.copy_(torch.from_numpy(acc))
+
+T = %(tokens)d
+x = synth.make_x(workloads.BASE_SEED + 1, T, shape.hidden, first_token=rank * T)
+blk = ep.EpMoeBlock(Ops(), torch, dist)
+out = blk.forward(torch.from_numpy(x)).numpy()
+ref, _, _ = P.moe_ffn(x)
+err = float(workloads.rel_rms_err(out, ref).max())
+assert err < 1e-6, err
+assert sum(blk.last["send_counts"]) == T * shape.top_k
+tot = torch.tensor([blk.last["rows_received"]]); dist.all_reduce(tot)
+assert int(tot.item()) == world * T * shape.top_k
+dist.barrier(); dist.destroy_process_group()
+print("EP_OK", rank, err)
+"""
+
+
+@pytest.mark.parametrize("tokens", [1, 13])
+def test_exchange_matches_single_process_oracle(tokens, tmp_path):
+    import socket
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    code = WORKER % dict(root=ROOT, port=port, tokens=tokens)
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", OMP_NUM_THREADS="2")
+        procs.append(subprocess.Popen([sys.executable, "-c", code], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and "EP_OK" in o, f"rank {r}:\n{o[-3000:]}"

@@ -291,3 +291,70 @@ def test_errors_are_codes_not_exits(be):
     with pytest.raises(moe.TieCudaError):
         be.dispatch_mat_vec(x[0], x.ctypes.data, 12, 2048, 0, 8)  # W is not an uploaded tensor
     assert be.launch_count > 0
+
+
+# ---------------- expert-parallel dispatch / combine on one GPU ----------------
+
+def test_ep_dispatch_and_combine_roundtrip(be, port0):
+    """dispatch -> expert rows -> combine through the dispatch permutation == the plain call."""
+    import torch
+    from tie_b200 import moe
+    T, K, H, E = 48, 8, 2048, 128
+    x = synth.make_x(0, T, first_token=300)
+    ref_out, ref_idx, _ = port0.moe_ffn(x)
+    xd = torch.from_numpy(x).cuda()
+    idx = torch.empty(T, K, dtype=torch.int32, device="cuda")
+    w = torch.empty(T, K, dtype=torch.float32, device="cuda")
+    be.route_ptr(0, xd, T, idx, w, None, None, moe.DEVICE)
+    assert np.array_equal(idx.cpu().numpy(), ref_idx)
+    rows = torch.empty(T * K, H, device="cuda")
+    rexp = torch.empty(T * K, dtype=torch.int32, device="cuda")
+    counts = torch.empty(E, dtype=torch.int32, device="cuda")
+    be.ep_dispatch_ptr(xd, idx, T, rows, rexp, counts, moe.DEVICE)
+    e = rexp.cpu().numpy()
+    assert (np.diff(e) >= 0).all(), "rows must be grouped by expert id (hence by destination rank)"
+    assert np.array_equal(counts.cpu().numpy(), np.bincount(ref_idx.reshape(-1), minlength=E))
+    # stable: within an expert, rows keep (token, slot) order, and every row carries its token's x
+    flat = ref_idx.reshape(-1)
+    perm = np.argsort(flat, kind="stable")
+    assert np.array_equal(e, flat[perm])
+    assert np.array_equal(rows.cpu().numpy(), x[perm // K])
+    y = torch.empty_like(rows)
+    be.expert_rows_ptr(0, rows, rexp, T * K, y, moe.DEVICE)
+    out = torch.empty(T, H, device="cuda")
+    be.ep_combine_ptr(y, w, T, out, moe.DEVICE)
+    _check_ffn(out.cpu().numpy(), ref_out)
+
+
+# ---------------- graph replay ----------------
+
+def test_graph_replay_matches_direct_launches(be):
+    import torch
+    from tie_b200 import moe
+    s = torch.cuda.Stream()
+    be.set_stream(s.cuda_stream)
+    try:
+        for T in (1, 64):
+            xs = [torch.from_numpy(synth.make_x(0, T, first_token=o)).cuda() for o in (0, 700)]
+            buf = torch.empty_like(xs[0])
+            out = torch.empty_like(buf)
+            for x in xs:  # same buffers, new contents: the cached graph must see the new data
+                want = torch.empty_like(x)
+                be.moe_ffn_ptr(0, x, want, T, moe.DEVICE)
+                buf.copy_(x)
+                torch.cuda.synchronize()
+                be.moe_ffn_ptr(0, buf, out, T, moe.DEVICE | moe.GRAPH)
+                assert np.array_equal(bits(out.cpu().numpy()), bits(want.cpu().numpy()))
+        # host buffers through the graph path (pinned and pageable)
+        x = synth.make_x(0, 8)
+        want = be.moe_ffn(0, x)
+        xp = torch.from_numpy(x).pin_memory()
+        op = torch.empty_like(xp).pin_memory()
+        for _ in range(2):
+            be.moe_ffn_ptr(0, xp, op, 8, moe.HOST | moe.GRAPH)
+            assert np.array_equal(bits(op.numpy()), bits(want))
+        got = np.empty_like(x)
+        be.moe_ffn_ptr(0, x, got, 8, moe.HOST | moe.GRAPH)
+        assert np.array_equal(bits(got), bits(want))
+    finally:
+        be.set_stream(None)

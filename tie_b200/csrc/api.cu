@@ -63,6 +63,13 @@ int alloc_scratch(tie_cuda_ctx *c)
 	TRY(dev_alloc(c, &s.hs_lo, s.rows_pad * F));
 	TRY(dev_alloc(c, &s.status, 1));
 	TRY(dev_alloc(c, &s.row_expert, R));
+	TRY(dev_alloc(c, &s.ep_counts, E));
+	TRY(dev_alloc(c, &s.ep_offsets, E + 1));
+	TRY(dev_alloc(c, &s.ep_tile_start, E + 1));
+	TRY(dev_alloc(c, &s.ep_active, E));
+	TRY(dev_alloc(c, &s.ep_n_active, 1));
+	TRY(dev_alloc(c, &s.ep_perm, R));
+	TRY(dev_alloc(c, &s.ep_inv, R));
 	TIE_CUDA_TRY(c, cudaMemset(s.status, 0, sizeof(unsigned)));
 	TIE_CUDA_TRY(c, cudaMemset(s.n_active, 0, sizeof(int)));
 	// rows past the last real one are read (never used) by the tensor path: keep them finite
@@ -240,6 +247,68 @@ int moe_ffn_device(tie_cuda_ctx *c, Layer &L, const float *x, float *out, int n_
 	return TIE_CUDA_OK;
 }
 
+struct GraphKey {
+	int kind, layer, n;
+	const void *p0, *p1, *p2, *p3;
+	unsigned flags;
+};
+
+// Runs enqueue() either directly or, with TIE_CUDA_GRAPH, through a cached CUDA graph.
+template <class F>
+int run_maybe_graphed(tie_cuda_ctx *c, bool want_graph, const GraphKey &k, F enqueue)
+{
+	if (!want_graph || c->stream == nullptr || c->prof_on)
+		return enqueue();
+	for (int i = 0; i < c->n_graphs; i++) {
+		auto &g = c->graphs[i];
+		if (g.kind == k.kind && g.layer == k.layer && g.n == k.n && g.p0 == k.p0 && g.p1 == k.p1 && g.p2 == k.p2 &&
+		    g.p3 == k.p3 && g.flags == k.flags) {
+			g.stamp = ++c->graph_clock;
+			TIE_CUDA_TRY(c, cudaGraphLaunch(g.exec, c->stream));
+			c->launches += g.kernels;
+			return TIE_CUDA_OK;
+		}
+	}
+	const uint64_t before = c->launches;
+	TIE_CUDA_TRY(c, cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+	int rc = enqueue();
+	cudaGraph_t graph = nullptr;
+	cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+	const uint64_t kernels = c->launches - before;
+	c->launches = before;
+	if (rc || e != cudaSuccess || !graph) {
+		if (graph)
+			cudaGraphDestroy(graph);
+		cudaGetLastError();
+		if (rc)
+			return rc;
+		snprintf(c->cuda_err, sizeof(c->cuda_err), "stream capture failed: %s", cudaGetErrorString(e));
+		return TIE_CUDA_ECUDA;
+	}
+	cudaGraphExec_t exec = nullptr;
+	e = cudaGraphInstantiate(&exec, graph, 0);
+	cudaGraphDestroy(graph);
+	if (e != cudaSuccess) {
+		snprintf(c->cuda_err, sizeof(c->cuda_err), "cudaGraphInstantiate: %s", cudaGetErrorString(e));
+		return TIE_CUDA_ECUDA;
+	}
+	int slot = c->n_graphs;
+	const int cap = (int)(sizeof(c->graphs) / sizeof(c->graphs[0]));
+	if (slot == cap) {  // evict the least recently used
+		slot = 0;
+		for (int i = 1; i < cap; i++)
+			if (c->graphs[i].stamp < c->graphs[slot].stamp)
+				slot = i;
+		cudaGraphExecDestroy(c->graphs[slot].exec);
+	} else {
+		c->n_graphs++;
+	}
+	c->graphs[slot] = {k.kind, k.layer, k.n, k.p0, k.p1, k.p2, k.p3, k.flags, exec, kernels, ++c->graph_clock};
+	TIE_CUDA_TRY(c, cudaGraphLaunch(exec, c->stream));
+	c->launches += kernels;
+	return TIE_CUDA_OK;
+}
+
 int h2d(tie_cuda_ctx *c, void *dst, const void *src, size_t bytes, void *pin)
 {
 	if (is_pinned_host(src)) {
@@ -249,19 +318,6 @@ int h2d(tie_cuda_ctx *c, void *dst, const void *src, size_t bytes, void *pin)
 		TIE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
 		memcpy(pin, src, bytes);
 		TIE_CUDA_TRY(c, cudaMemcpyAsync(dst, pin, bytes, cudaMemcpyHostToDevice, c->stream));
-	}
-	return TIE_CUDA_OK;
-}
-
-// D2H into user memory; *staged tells the caller to memcpy from pin after synchronising.
-int d2h(tie_cuda_ctx *c, void *dst, const void *src, size_t bytes, void *pin, bool *staged)
-{
-	if (is_pinned_host(dst)) {
-		*staged = false;
-		TIE_CUDA_TRY(c, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, c->stream));
-	} else {
-		*staged = true;
-		TIE_CUDA_TRY(c, cudaMemcpyAsync(pin, src, bytes, cudaMemcpyDeviceToHost, c->stream));
 	}
 	return TIE_CUDA_OK;
 }
@@ -379,6 +435,8 @@ int tie_cuda_init(tie_cuda_ctx **out, const tie_cuda_config *cfg)
 		return fail(rc);
 	if ((rc = tc_setup(c)) != TIE_CUDA_OK)
 		return fail(rc);
+	if ((rc = router_setup(c)) != TIE_CUDA_OK)
+		return fail(rc);
 	*out = c;
 	return TIE_CUDA_OK;
 }
@@ -411,7 +469,7 @@ void tie_cuda_destroy(tie_cuda_ctx *c)
 	Scratch &s = c->s;
 	void *dev_ptrs[] = {s.x,     s.out,   s.logits, s.bias,  s.topk_idx, s.topk_w, s.counts, s.offsets, s.tile_start, s.active, s.n_active,
 			    s.perm,  s.h,     s.y,	s.xs_hi, s.xs_lo,    s.hs_hi,  s.hs_lo,  s.status,  s.row_expert, c->silu,  c->row_x,
-			    c->row_o};
+			    c->row_o, s.ep_counts, s.ep_offsets, s.ep_tile_start, s.ep_active, s.ep_n_active, s.ep_perm, s.ep_inv};
 	for (void *p : dev_ptrs)
 		if (p)
 			cudaFree(p);
@@ -419,6 +477,8 @@ void tie_cuda_destroy(tie_cuda_ctx *c)
 	for (void *p : pin_ptrs)
 		if (p)
 			cudaFreeHost(p);
+	for (int i = 0; i < c->n_graphs; i++)
+		cudaGraphExecDestroy(c->graphs[i].exec);
 	for (int i = 0; i < 8; i++)
 		if (c->prof_ev[i])
 			cudaEventDestroy(c->prof_ev[i]);
@@ -468,7 +528,7 @@ int tie_cuda_set_stream(tie_cuda_ctx *c, void *cuda_stream)
 {
 	if (!c)
 		return TIE_CUDA_EINVAL;
-	c->stream = cuda_stream ? static_cast<cudaStream_t>(cuda_stream) : c->own_stream;
+	c->stream = static_cast<cudaStream_t>(cuda_stream);
 	return TIE_CUDA_OK;
 }
 
@@ -547,6 +607,8 @@ int tie_cuda_moe_ffn_biased(tie_cuda_ctx *c, int layer, const float *x, float *o
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
 	const size_t bytes = (size_t)n_tokens * c->cfg.hidden * sizeof(float);
 	const bool dev = flags & TIE_CUDA_DEVICE;
+	const bool graph = flags & TIE_CUDA_GRAPH;
+	const unsigned kflags = flags & (TIE_CUDA_DEVICE | TIE_CUDA_PATH_MASK);
 	const float *bias_dev = nullptr;
 	if (router_bias) {
 		if (dev) {
@@ -558,17 +620,33 @@ int tie_cuda_moe_ffn_biased(tie_cuda_ctx *c, int layer, const float *x, float *o
 		}
 	}
 	if (dev) {
-		TRY(moe_ffn_device(c, *L, x, out, n_tokens, bias_dev, nullptr, flags));
+		GraphKey k = {1, layer, n_tokens, x, out, bias_dev, nullptr, kflags};
+		TRY(run_maybe_graphed(c, graph, k, [&]() { return moe_ffn_device(c, *L, x, out, n_tokens, bias_dev, nullptr, flags); }));
 		if (flags & TIE_CUDA_NO_SYNC)
 			return TIE_CUDA_OK;
 		return check_status(c);
 	}
-	bool staged = false;
-	TRY(h2d(c, c->s.x, x, bytes, c->pin_x));
-	TRY(moe_ffn_device(c, *L, c->s.x, c->s.out, n_tokens, bias_dev, nullptr, flags));
-	TRY(d2h(c, out, c->s.out, bytes, c->pin_out, &staged));
+	// host pointers: pinned user memory is copied directly, pageable memory goes through the
+	// context's pinned staging buffers
+	const bool x_pinned = is_pinned_host(x), out_pinned = is_pinned_host(out);
+	const void *src = x;
+	void *dst = out;
+	if (!x_pinned) {
+		TIE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+		memcpy(c->pin_x, x, bytes);
+		src = c->pin_x;
+	}
+	if (!out_pinned)
+		dst = c->pin_out;
+	GraphKey k = {2, layer, n_tokens, src, dst, bias_dev, nullptr, kflags};
+	TRY(run_maybe_graphed(c, graph, k, [&]() -> int {
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(c->s.x, src, bytes, cudaMemcpyHostToDevice, c->stream));
+		TRY(moe_ffn_device(c, *L, c->s.x, c->s.out, n_tokens, bias_dev, nullptr, flags));
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(dst, c->s.out, bytes, cudaMemcpyDeviceToHost, c->stream));
+		return TIE_CUDA_OK;
+	}));
 	TRY(check_status(c));
-	if (staged)
+	if (!out_pinned)
 		memcpy(out, c->pin_out, bytes);
 	return TIE_CUDA_OK;
 }
@@ -585,8 +663,11 @@ int tie_cuda_moe_block_inplace(tie_cuda_ctx *c, int layer, float *hidden_dev, in
 	if (!hidden_dev || n_tokens <= 0 || n_tokens > c->cfg.max_tokens || c->cfg.ep_size != 1)
 		return TIE_CUDA_EINVAL;
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
-	TRY(launch_rms_norm(c, hidden_dev, L->norm_w, c->s.x, n_tokens));
-	TRY(moe_ffn_device(c, *L, c->s.x, hidden_dev, n_tokens, nullptr, hidden_dev, flags));
+	GraphKey k = {3, layer, n_tokens, hidden_dev, nullptr, nullptr, nullptr, flags & TIE_CUDA_PATH_MASK};
+	TRY(run_maybe_graphed(c, flags & TIE_CUDA_GRAPH, k, [&]() -> int {
+		TRY(launch_rms_norm(c, hidden_dev, L->norm_w, c->s.x, n_tokens));
+		return moe_ffn_device(c, *L, c->s.x, hidden_dev, n_tokens, nullptr, hidden_dev, flags);
+	}));
 	if (flags & TIE_CUDA_NO_SYNC)
 		return TIE_CUDA_OK;
 	return check_status(c);
@@ -650,6 +731,35 @@ int tie_cuda_moe_combine(tie_cuda_ctx *c, const float *y_rows, const float *topk
 		return TIE_CUDA_EINVAL;
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
 	TRY(launch_combine(c, y_rows, topk_w, n_tokens, nullptr, out));
+	if (flags & TIE_CUDA_NO_SYNC)
+		return TIE_CUDA_OK;
+	return check_status(c);
+}
+
+int tie_cuda_moe_ep_dispatch(tie_cuda_ctx *c, const float *x, const int *topk_idx, int n_tokens, float *send_rows,
+			     int *send_expert, int *expert_counts, unsigned flags)
+{
+	if (!c || !(flags & TIE_CUDA_DEVICE) || !x || !topk_idx || !send_rows || !send_expert || !expert_counts || n_tokens <= 0 ||
+	    (size_t)n_tokens * c->cfg.top_k > c->s.rows_cap)
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	Scratch &s = c->s;
+	const int R = n_tokens * c->cfg.top_k;
+	SortBufs b = {expert_counts, s.ep_offsets, s.ep_tile_start, s.ep_active, s.ep_n_active, s.ep_perm};
+	TRY(launch_sort(c, topk_idx, R, 128, 0, c->cfg.n_expert, b));
+	TRY(launch_gather_rows(c, x, topk_idx, s.ep_perm, c->cfg.top_k, R, send_rows, send_expert, s.ep_inv));
+	if (flags & TIE_CUDA_NO_SYNC)
+		return TIE_CUDA_OK;
+	return check_status(c);
+}
+
+int tie_cuda_moe_ep_combine(tie_cuda_ctx *c, const float *y_sorted, const float *topk_w, int n_tokens, float *out, unsigned flags)
+{
+	if (!c || !(flags & TIE_CUDA_DEVICE) || !y_sorted || !topk_w || !out || n_tokens <= 0 ||
+	    (size_t)n_tokens * c->cfg.top_k > c->s.rows_cap)
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	TRY(launch_combine(c, y_sorted, topk_w, n_tokens, nullptr, out, c->s.ep_inv));
 	if (flags & TIE_CUDA_NO_SYNC)
 		return TIE_CUDA_OK;
 	return check_status(c);

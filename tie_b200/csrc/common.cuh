@@ -67,6 +67,9 @@ struct Scratch {
 	__half *hs_hi = nullptr, *hs_lo = nullptr;  // [Rpad][F]
 	unsigned *status = nullptr;		    // [1]
 	int *row_expert = nullptr;		    // [R] staging for expert_rows
+	// expert-parallel dispatch state (sort of this rank's rows over ALL experts)
+	int *ep_counts = nullptr, *ep_offsets = nullptr, *ep_tile_start = nullptr, *ep_active = nullptr, *ep_n_active = nullptr;
+	int *ep_perm = nullptr, *ep_inv = nullptr;
 	size_t rows_cap = 0;			    // R capacity
 	size_t rows_pad = 0;			    // Rpad
 };
@@ -112,6 +115,17 @@ struct tie_cuda_ctx {
 	// standalone tensors uploaded through tie_cuda_register_tensor
 	uint8_t **extra = nullptr;
 	int n_extra = 0, cap_extra = 0;
+	// cache of instantiated CUDA graphs for calls made with TIE_CUDA_GRAPH
+	struct GraphEntry {
+		int kind, layer, n;
+		const void *p0, *p1, *p2, *p3;
+		unsigned flags;
+		cudaGraphExec_t exec;
+		uint64_t kernels;  // kernel launches recorded in the graph
+		uint64_t stamp;
+	} graphs[32];
+	int n_graphs = 0;
+	uint64_t graph_clock = 0;
 	// small per-call device buffers for the dispatch rows
 	float *row_x = nullptr, *row_o = nullptr;
 	size_t row_cap = 0;

@@ -7,9 +7,15 @@ namespace tie {
 // router.cu
 int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *bias, int n_tokens, float *logits,
 		  int *topk_idx, float *topk_w);
+int router_setup(tie_cuda_ctx *c);
 int launch_router_rows(tie_cuda_ctx *c, const float *x, const float *w, int n_rows, int in_dim, float *out);
 // sort.cu
+struct SortBufs {
+	int *counts, *offsets, *tile_start, *active, *n_active, *perm;
+};
 int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile);
+int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile, int first_expert, int n_expert,
+		const SortBufs &b);
 // stream.cu
 int launch_stream_gate_up(tie_cuda_ctx *c, const Layer &L, const float *xin, int src_div, const int *row_expert,
 			  int n_rows, int direct);
@@ -17,7 +23,10 @@ int launch_stream_down(tie_cuda_ctx *c, const Layer &L, float *y, const int *row
 int launch_stream_matvec(tie_cuda_ctx *c, const uint8_t *wexp, WKind kind, int k, int rows_total, const float *x, float *o);
 // misc.cu
 int launch_rms_norm(tie_cuda_ctx *c, const float *x, const float *w, float *o, int n_tokens);
-int launch_combine(tie_cuda_ctx *c, const float *y, const float *topk_w, int n_tokens, const float *residual, float *out);
+int launch_combine(tie_cuda_ctx *c, const float *y, const float *topk_w, int n_tokens, const float *residual, float *out,
+		   const int *pos = nullptr);
+int launch_gather_rows(tie_cuda_ctx *c, const float *x, const int *row_expert, const int *perm, int src_div, int n_rows,
+		       float *rows_out, int *expert_out, int *inv);
 int launch_split_rows(tie_cuda_ctx *c, const float *x, const int *perm, int src_div, int n_rows, int n_cols, __half *hi,
 		      __half *lo);
 int launch_swiglu(tie_cuda_ctx *c, float *gate, const float *up, int n);

@@ -41,21 +41,25 @@ __global__ void __launch_bounds__(128) rms_norm_rows(const float *__restrict__ x
 
 // model_qwen3.c:458-467: acc = 0; acc += w_j * y_j, j ascending (fused multiply-add, as the
 // reference compiles it).  residual != null: out = residual + acc (math_avx2.c:731-751).
+// pos != null: the row of (t, j) is y[pos[t*top_k + j]] instead of y[t*top_k + j].
 __global__ void __launch_bounds__(256) combine_rows(const float *__restrict__ y, const float *__restrict__ topk_w, int top_k,
-						    int hidden, const float *__restrict__ residual, float *__restrict__ out)
+						    int hidden, const float *__restrict__ residual, float *__restrict__ out,
+						    const int *__restrict__ pos)
 {
 	const int t = blockIdx.x;
-	const float *yt = y + (size_t)t * top_k * hidden;
 	float wj[MAX_TOP_K];
+	size_t yrow[MAX_TOP_K];
 #pragma unroll
-	for (int j = 0; j < MAX_TOP_K; j++)
+	for (int j = 0; j < MAX_TOP_K; j++) {
 		wj[j] = (j < top_k) ? topk_w[(size_t)t * top_k + j] : 0.f;
+		yrow[j] = (j < top_k) ? (size_t)(pos ? pos[(size_t)t * top_k + j] : t * top_k + j) * hidden : 0;
+	}
 	for (int k = threadIdx.x * 4; k < hidden; k += blockDim.x * 4) {
 		float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
 		for (int j = 0; j < MAX_TOP_K; j++) {
 			if (j < top_k) {
-				float4 v = *reinterpret_cast<const float4 *>(yt + (size_t)j * hidden + k);
+				float4 v = *reinterpret_cast<const float4 *>(y + yrow[j] + k);
 				acc.x = __fmaf_rn(wj[j], v.x, acc.x);
 				acc.y = __fmaf_rn(wj[j], v.y, acc.y);
 				acc.z = __fmaf_rn(wj[j], v.z, acc.z);
@@ -96,6 +100,24 @@ __global__ void __launch_bounds__(256) split_rows(const float *__restrict__ x, c
 	}
 }
 
+// Expert-parallel dispatch payload: rows in expert-sorted order, their expert ids, and the
+// inverse permutation (row id -> sorted position) for the combine on the way back.
+__global__ void __launch_bounds__(256) gather_rows(const float *__restrict__ x, const int *__restrict__ row_expert,
+						   const int *__restrict__ perm, int src_div, int n_cols,
+						   float *__restrict__ rows_out, int *__restrict__ expert_out, int *__restrict__ inv)
+{
+	const int p = blockIdx.x;
+	const int rid = perm[p];
+	const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)(rid / src_div) * n_cols);
+	float4 *orow = reinterpret_cast<float4 *>(rows_out + (size_t)p * n_cols);
+	for (int k = threadIdx.x; k < n_cols / 4; k += blockDim.x)
+		orow[k] = xr[k];
+	if (threadIdx.x == 0) {
+		expert_out[p] = row_expert[rid];
+		inv[rid] = p;
+	}
+}
+
 __global__ void __launch_bounds__(256) swiglu_kernel(float *__restrict__ gate, const float *__restrict__ up, int n,
 						     const float *__restrict__ silu)
 {
@@ -120,9 +142,10 @@ int launch_rms_norm(tie_cuda_ctx *c, const float *x, const float *w, float *o, i
 	return TIE_CUDA_OK;
 }
 
-int launch_combine(tie_cuda_ctx *c, const float *y, const float *topk_w, int n_tokens, const float *residual, float *out)
+int launch_combine(tie_cuda_ctx *c, const float *y, const float *topk_w, int n_tokens, const float *residual, float *out,
+		   const int *pos)
 {
-	combine_rows<<<n_tokens, 256, 0, c->stream>>>(y, topk_w, c->cfg.top_k, c->cfg.hidden, residual, out);
+	combine_rows<<<n_tokens, 256, 0, c->stream>>>(y, topk_w, c->cfg.top_k, c->cfg.hidden, residual, out, pos);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
@@ -131,6 +154,14 @@ int launch_split_rows(tie_cuda_ctx *c, const float *x, const int *perm, int src_
 		      __half *lo)
 {
 	split_rows<<<n_rows, 256, 0, c->stream>>>(x, perm, src_div, n_cols, hi, lo);
+	TIE_CUDA_LAUNCHED(c);
+	return TIE_CUDA_OK;
+}
+
+int launch_gather_rows(tie_cuda_ctx *c, const float *x, const int *row_expert, const int *perm, int src_div, int n_rows,
+		       float *rows_out, int *expert_out, int *inv)
+{
+	gather_rows<<<n_rows, 256, 0, c->stream>>>(x, row_expert, perm, src_div, c->cfg.hidden, rows_out, expert_out, inv);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }

@@ -175,9 +175,6 @@ int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *
 	const int H = c->cfg.hidden, E = c->cfg.n_expert, K = c->cfg.top_k;
 	if (n_tokens <= 8) {
 		size_t smem = ((size_t)H + (size_t)n_tokens * (H + 8)) * sizeof(float);
-		if (smem > 48 * 1024)
-			TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_logits_decode<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-							     (int)smem));
 		router_logits_decode<8><<<E, 64, smem, c->stream>>>(x, w, bias, logits, n_tokens, H, E);
 		TIE_CUDA_LAUNCHED(c);
 	} else if (n_tokens <= 512) {
@@ -198,12 +195,19 @@ int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *
 	return TIE_CUDA_OK;
 }
 
+// Opt-in shared-memory sizes are set once per context (never inside a stream capture).
+int router_setup(tie_cuda_ctx *c)
+{
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_logits_decode<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+	return TIE_CUDA_OK;
+}
+
 // Plain F32 mat-vec over the first n_rows rows of w (the math_dispatch F32 row), one vector.
 int launch_router_rows(tie_cuda_ctx *c, const float *x, const float *w, int n_rows, int in_dim, float *out)
 {
 	size_t smem = ((size_t)in_dim + (size_t)(in_dim + 8)) * sizeof(float);
-	if (smem > 48 * 1024)
-		TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_logits_decode<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+	if (smem > 200 * 1024)
+		return TIE_CUDA_ENOTSUP;
 	router_logits_decode<8><<<n_rows, 64, smem, c->stream>>>(x, w, nullptr, out, 1, in_dim, n_rows);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;

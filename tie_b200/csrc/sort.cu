@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_place(const int *__restrict
 							   int *__restrict__ active, int *__restrict__ n_active,
 							   int *__restrict__ perm)
 {
-	__shared__ int s_off, s_tile, s_act;
+	__shared__ int s_off;
 	__shared__ int wcnt[SORT_THREADS / 32];
 	const int le = blockIdx.x;
 	const int e = first_expert + le;
@@ -82,8 +82,6 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_place(const int *__restrict
 		}
 		if (threadIdx.x == 0) {
 			s_off = off;
-			s_tile = tiles;
-			s_act = act;
 			offsets[le] = off;
 			tile_start[le] = tiles;
 			if (counts[le] > 0)
@@ -119,16 +117,22 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_place(const int *__restrict
 	}
 }
 
+int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile, int first_expert, int n_expert,
+		const SortBufs &b)
+{
+	sort_count<<<n_expert, SORT_THREADS, 0, c->stream>>>(row_expert, n_rows, first_expert, n_expert, b.counts, c->s.status);
+	TIE_CUDA_LAUNCHED(c);
+	sort_place<<<n_expert, SORT_THREADS, 0, c->stream>>>(row_expert, n_rows, first_expert, n_expert, b.counts, n_tile,
+							      b.offsets, b.tile_start, b.active, b.n_active, b.perm);
+	TIE_CUDA_LAUNCHED(c);
+	return TIE_CUDA_OK;
+}
+
 int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile)
 {
 	Scratch &s = c->s;
-	sort_count<<<c->n_local, SORT_THREADS, 0, c->stream>>>(row_expert, n_rows, c->first_expert, c->n_local, s.counts,
-								s.status);
-	TIE_CUDA_LAUNCHED(c);
-	sort_place<<<c->n_local, SORT_THREADS, 0, c->stream>>>(row_expert, n_rows, c->first_expert, c->n_local, s.counts,
-								n_tile, s.offsets, s.tile_start, s.active, s.n_active, s.perm);
-	TIE_CUDA_LAUNCHED(c);
-	return TIE_CUDA_OK;
+	SortBufs b = {s.counts, s.offsets, s.tile_start, s.active, s.n_active, s.perm};
+	return launch_sort(c, row_expert, n_rows, n_tile, c->first_expert, c->n_local, b);
 }
 
 }  // namespace tie

@@ -397,6 +397,18 @@ int tc_setup(tie_cuda_ctx *c)
 			if (rc)
 				return rc;
 		}
+#define TC_ATTR(KIND, NMAT, NT)                                                                                            \
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_tc<KIND, NMAT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+					     TcCfg<NMAT, NT>::SMEM))
+	TC_ATTR(W_Q4K, 1, 64);
+	TC_ATTR(W_Q4K, 1, 128);
+	TC_ATTR(W_Q4K, 2, 64);
+	TC_ATTR(W_Q4K, 2, 128);
+	TC_ATTR(W_Q6K_R8, 1, 64);
+	TC_ATTR(W_Q6K_R8, 1, 128);
+	TC_ATTR(W_Q6K_R8, 2, 64);
+	TC_ATTR(W_Q6K_R8, 2, 128);
+#undef TC_ATTR
 	c->tmaps_ok = true;
 	return TIE_CUDA_OK;
 }
@@ -407,7 +419,6 @@ static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1
 {
 	using Cfg = TcCfg<NMAT, NT>;
 	Scratch &s = c->s;
-	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_tc<KIND, NMAT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
 	const int max_tiles = min(c->n_local, n_rows) + n_rows / NT;
 	dim3 grid(t0.rows / TC_BM, max_tiles);
 	grouped_gemm_tc<KIND, NMAT, NT><<<grid, TC_THREADS, Cfg::SMEM, c->stream>>>(

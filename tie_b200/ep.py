@@ -1,0 +1,199 @@
+"""Expert parallelism for the MoE block: one process per GPU, experts sharded 128/G per rank,
+tokens data-parallel, dispatch and combine by all-to-all over NCCL (torch.distributed).
+
+The reference is a single process and has no counterpart.  Per block and rank:
+
+  route (local, router replicated)                       -> top-k ids, weights
+  dispatch: counting sort of the (token, slot) rows by expert id; since a rank owns a
+            contiguous expert range this also groups rows by destination rank
+  all-to-all of per-rank row counts, then of the rows and their expert ids
+  expert rows on the owner (grouped mat-vec / GEMM over its local experts)
+  all-to-all back in the same order
+  combine: out[t] = sum_j w[t][j] * y[(t, j)], j ascending
+
+The exchange logic is written against a small `ops` interface so that it can run on CPU ranks
+(gloo) with stand-in ops in the tests; on GPUs `CudaOps` forwards to the C ABI.
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+
+import numpy as np
+
+
+class CudaOps:
+    """Device ops of one rank, forwarding to libtie_cuda.so."""
+
+    def __init__(self, be, torch):
+        self.be, self.torch = be, torch
+        self.K, self.H, self.E = be.top_k, be.hidden, be.n_expert
+        self.device = torch.device("cuda", be.cfg.device)
+
+    def empty(self, shape, dtype):
+        return self.torch.empty(shape, dtype=dtype, device=self.device)
+
+    def route(self, x, idx, w):
+        from . import moe
+        self.be.route_ptr(0, x, x.shape[0], idx, w, None, None, moe.DEVICE | moe.NO_SYNC)
+
+    def dispatch(self, x, idx, send_rows, send_expert, counts):
+        from . import moe
+        self.be.ep_dispatch_ptr(x, idx, x.shape[0], send_rows, send_expert, counts, moe.DEVICE | moe.NO_SYNC)
+
+    def expert_rows(self, rows, experts, n_rows, y):
+        from . import moe
+        if n_rows:
+            self.be.expert_rows_ptr(0, rows, experts, n_rows, y, moe.DEVICE | moe.NO_SYNC)
+
+    def combine(self, y_sorted, w, out):
+        from . import moe
+        self.be.ep_combine_ptr(y_sorted, w, out.shape[0], out, moe.DEVICE | moe.NO_SYNC)
+
+
+class EpMoeBlock:
+    """One expert-parallel MoE block on this rank.  ops supplies route / dispatch / expert_rows /
+    combine; dist is torch.distributed (any backend with all_to_all_single)."""
+
+    def __init__(self, ops, torch, dist, group=None):
+        self.ops, self.torch, self.dist, self.group = ops, torch, dist, group
+        self.G = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.n_local = ops.E // self.G
+        self.last = {}
+
+    def forward(self, x, out=None):
+        torch, dist, ops = self.torch, self.dist, self.ops
+        T, K, H, G = x.shape[0], ops.K, ops.H, self.G
+        R = T * K
+        idx = ops.empty((T, K), torch.int32)
+        w = ops.empty((T, K), torch.float32)
+        ops.route(x, idx, w)
+        send_rows = ops.empty((R, H), torch.float32)
+        send_expert = ops.empty((R,), torch.int32)
+        counts = ops.empty((ops.E,), torch.int32)
+        ops.dispatch(x, idx, send_rows, send_expert, counts)
+        # rows per destination rank, exchanged so every rank knows what it will receive
+        send_counts = counts.view(G, self.n_local).sum(dim=1).to(torch.int64)
+        recv_counts = torch.empty_like(send_counts)
+        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+        sc = send_counts.tolist()  # host sync: the split sizes are host arguments of the collective
+        rc = recv_counts.tolist()
+        n_recv = int(sum(rc))
+        recv_rows = ops.empty((max(n_recv, 1), H), torch.float32)
+        recv_expert = ops.empty((max(n_recv, 1),), torch.int32)
+        dist.all_to_all_single(recv_rows[:n_recv], send_rows, rc, sc, group=self.group)
+        dist.all_to_all_single(recv_expert[:n_recv], send_expert, rc, sc, group=self.group)
+        y_recv = ops.empty((max(n_recv, 1), H), torch.float32)
+        ops.expert_rows(recv_rows, recv_expert, n_recv, y_recv)
+        y_sorted = ops.empty((R, H), torch.float32)
+        dist.all_to_all_single(y_sorted, y_recv[:n_recv], sc, rc, group=self.group)
+        if out is None:
+            out = ops.empty((T, H), torch.float32)
+        ops.combine(y_sorted, w, out)
+        self.last = {"rows_sent": R, "rows_received": n_recv, "send_counts": sc, "recv_counts": rc}
+        return out
+
+
+def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
+    """bench.py --gpus N under torchrun: weak scaling, `tokens_per_rank` tokens on every rank,
+    experts sharded.  Rank 0 prints the JSON line."""
+    import torch
+    import torch.distributed as dist
+
+    from . import moe, synth, workloads
+
+    world = int(os.environ["WORLD_SIZE"])
+    rank = int(os.environ["RANK"])
+    local_rank = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local_rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    shape = synth.MoeShape()
+    T = tokens_per_rank
+    n_local = shape.n_expert // world
+    layer = synth.make_layer(workloads.BASE_SEED, shape, first_expert=rank * n_local, n_local_expert=n_local)
+    be = moe.MoeBackend(max_tokens=T * world, device=local_rank, silu_table=moe.silu_table_default(), ep_rank=rank, ep_size=world)
+    be.upload_layer(0, layer)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    be.set_stream(stream.cuda_stream)
+    blk = EpMoeBlock(CudaOps(be, torch), torch, dist)
+
+    x_host = torch.from_numpy(synth.make_x(workloads.BASE_SEED, T, first_token=rank * T)).pin_memory()
+    out_host = torch.empty_like(x_host).pin_memory()
+    x_dev = x_host.cuda()
+    out_dev = torch.empty_like(x_dev)
+
+    def step():
+        blk.forward(x_dev, out_dev)
+
+    def step_e2e():
+        xd = x_host.to(x_dev.device, non_blocking=True)
+        o = blk.forward(xd)
+        out_host.copy_(o, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    l0 = be.launch_count
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+    dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    launches = be.launch_count - l0
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = float(ms.item())
+
+    for _ in range(args.warmup):
+        step_e2e()
+    dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step_e2e()
+    t1 = torch.tensor([time.perf_counter() - t0], device="cuda")
+    dist.all_reduce(t1, op=dist.ReduceOp.MAX)
+    e2e_s = float(t1.item()) / args.steps
+    be.synchronize()
+
+    if rank == 0:
+        peaks = load_peaks()
+        ms_per_step = total_ms / args.steps
+        value = T * world / (ms_per_step * 1e-3)
+        flops = workloads.algorithmic_flops(shape, T * world)
+        line = {
+            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "prefill_512_tokens_per_rank_one_block_expert_parallel", "tokens": T * world,
+                       "tokens_per_rank": T, "hidden": shape.hidden, "experts": shape.n_expert, "experts_per_rank": n_local,
+                       "top_k": shape.top_k, "ffn_dim": shape.ffn_dim, "weights": "Q4_K gate/up, Q6_K down (random valid super-blocks)",
+                       "l2": f"weights touched per step per rank ({392 // world} MB) plus exchanged rows; inputs rotate through all-to-all buffers",
+                       "parallelism": f"ep{world}", "collective": "NCCL all-to-all (torch.distributed) for dispatch and combine",
+                       "seed": workloads.BASE_SEED},
+            "clocks": clocks,
+            "e2e": {"value": T * world / e2e_s, "unit": unit, "h2d_bytes_per_step": T * shape.hidden * 4 * world,
+                    "d2h_bytes_per_step": T * shape.hidden * 4 * world, "ms_per_step": e2e_s * 1e3},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "achieved": None, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None, "traffic": None,
+                         "note": "per-kernel roofline is reported by the 1-GPU run; here: whole-block algorithmic TFLOP/s",
+                         "algorithmic_tflops": flops / (ms_per_step * 1e-3) / 1e12},
+            "cpu_baseline": None,
+            "exchange": {"rows_sent_rank0": blk.last.get("rows_sent"), "rows_received_rank0": blk.last.get("rows_received"),
+                         "bytes_per_row": shape.hidden * 4},
+        }
+        print(json.dumps(line), flush=True)
+    be.close()
+    dist.destroy_process_group()

@@ -14,7 +14,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libtie_cuda.so")
 
-HOST, DEVICE, NO_SYNC = 0, 1, 2
+HOST, DEVICE, NO_SYNC, GRAPH = 0, 1, 2, 4
 PATH_AUTO, PATH_STREAM, PATH_TENSOR = 0, 1 << 8, 2 << 8
 OK, EINVAL, ENOTSUP, ENOMEM, ECUDA, ENODEV, EKERNEL = 0, -1, -2, -3, -4, -5, -6
 
@@ -26,7 +26,8 @@ EXPORTS = [
     "tie_cuda_moe_expert_rows", "tie_cuda_moe_combine", "tie_cuda_make_current", "tie_cuda_register_tensor",
     "tie_cuda_mat_vec_row_f32_q4k_f32", "tie_cuda_mat_vec_row_f32_q6k_f32", "tie_cuda_mat_vec_row_f32_f32_f32",
     "tie_cuda_swiglu_f32_f32", "tie_cuda_dispatch_status", "tie_cuda_launch_count", "tie_cuda_last_active_experts",
-    "tie_cuda_version", "tie_cuda_set_profiling", "tie_cuda_get_profile",
+    "tie_cuda_version", "tie_cuda_set_profiling", "tie_cuda_get_profile", "tie_cuda_moe_ep_dispatch",
+    "tie_cuda_moe_ep_combine",
 ]
 PHASES = ["router", "sort", "split", "gate_up", "down", "combine"]
 
@@ -90,6 +91,10 @@ def load_library() -> ctypes.CDLL:
     L.tie_cuda_moe_expert_rows.argtypes = [vp, i32, vp, vp, i32, vp, u32]
     L.tie_cuda_moe_combine.restype = i32
     L.tie_cuda_moe_combine.argtypes = [vp, vp, vp, i32, vp, u32]
+    L.tie_cuda_moe_ep_dispatch.restype = i32
+    L.tie_cuda_moe_ep_dispatch.argtypes = [vp, vp, vp, i32, vp, vp, vp, u32]
+    L.tie_cuda_moe_ep_combine.restype = i32
+    L.tie_cuda_moe_ep_combine.argtypes = [vp, vp, vp, i32, vp, u32]
     L.tie_cuda_make_current.restype = i32
     L.tie_cuda_make_current.argtypes = [vp]
     L.tie_cuda_register_tensor.restype = i32
@@ -217,9 +222,11 @@ class MoeBackend:
             self._host_keep[layer_idx] = layer
 
     # -- compute: numpy in / numpy out (host pointers) --
-    def moe_ffn(self, layer_idx: int, x: np.ndarray, router_bias: np.ndarray | None = None, path: int = PATH_AUTO) -> np.ndarray:
+    def moe_ffn(self, layer_idx: int, x: np.ndarray, router_bias: np.ndarray | None = None, path: int = PATH_AUTO,
+                out: np.ndarray | None = None) -> np.ndarray:
         x = np.ascontiguousarray(x, dtype=np.float32)
-        out = np.empty_like(x)
+        if out is None:
+            out = np.empty_like(x)
         if router_bias is not None:
             router_bias = np.ascontiguousarray(router_bias, dtype=np.float32)
         rc = self.L.tie_cuda_moe_ffn_biased(self.h, layer_idx, x.ctypes.data, out.ctypes.data, x.shape[0],
@@ -261,6 +268,15 @@ class MoeBackend:
     def combine_ptr(self, y_rows, topk_w, n_tokens: int, out, flags: int = DEVICE):
         rc = self.L.tie_cuda_moe_combine(self.h, _ptr(y_rows), _ptr(topk_w), n_tokens, _ptr(out), flags)
         self._check(rc, "tie_cuda_moe_combine")
+
+    def ep_dispatch_ptr(self, x, topk_idx, n_tokens: int, send_rows, send_expert, expert_counts, flags: int = DEVICE):
+        rc = self.L.tie_cuda_moe_ep_dispatch(self.h, _ptr(x), _ptr(topk_idx), n_tokens, _ptr(send_rows), _ptr(send_expert),
+                                             _ptr(expert_counts), flags)
+        self._check(rc, "tie_cuda_moe_ep_dispatch")
+
+    def ep_combine_ptr(self, y_sorted, topk_w, n_tokens: int, out, flags: int = DEVICE):
+        rc = self.L.tie_cuda_moe_ep_combine(self.h, _ptr(y_sorted), _ptr(topk_w), n_tokens, _ptr(out), flags)
+        self._check(rc, "tie_cuda_moe_ep_combine")
 
     # -- math_dispatch rows --
     def make_current(self):
