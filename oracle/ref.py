@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import sys
 
 import numpy as np
 
@@ -48,7 +49,17 @@ class RefMoe:
         self.hidden, self.n_expert, self.top_k, self.ffn_dim = hidden, n_expert, top_k, ffn_dim
         if n_threads is None:
             n_threads = min(os.cpu_count() or 8, 32)
-        L.tieref_init(hidden, n_expert, top_k, ffn_dim, n_threads)
+        # math_dispatch_init() prints a banner to stdout; keep it out of callers' output
+        sys.stdout.flush()
+        saved = os.dup(1)
+        devnull = os.open(os.devnull, os.O_WRONLY)
+        try:
+            os.dup2(devnull, 1)
+            L.tieref_init(hidden, n_expert, top_k, ffn_dim, n_threads)
+        finally:
+            os.dup2(saved, 1)
+            os.close(saved)
+            os.close(devnull)
         self.n_threads = L.tieref_num_threads()
         self._keep = None
 
