@@ -35,6 +35,7 @@ extern "C" {
 #define TIE_CUDA_ECUDA (-4)    /* a CUDA runtime call or kernel failed; see tie_cuda_last_cuda_error */
 #define TIE_CUDA_ENODEV (-5)   /* no usable sm_100 device */
 #define TIE_CUDA_EKERNEL (-6)  /* a kernel reported an internal check failure (device status word) */
+#define TIE_CUDA_ETOOBIG (-7)  /* size exceeds the fixed scratch of tie_cuda_route_noalloc */
 
 /* flags for the x / out pointers of the compute entry points */
 #define TIE_CUDA_HOST 0u         /* pointers are host memory (the drop-in case: ctx->mem.* buffers) */
@@ -167,6 +168,35 @@ void tie_cuda_mat_vec_row_f32_f32_f32(const void *X, const void *W, void *O, int
 /* swiglu_fn (math_dispatch.h:20; math_avx2.c:908-950): gate[i] = silu_table_lookup(gate[i]) * up[i]. */
 void tie_cuda_swiglu_f32_f32(void *gate, const void *up, int size);
 int tie_cuda_dispatch_status(void); /* 0, or the TIE_CUDA_E* of the last failing dispatch-row call */
+
+/* ---- routing for callers that must not allocate ----
+ * No counterpart in the reference (it is a CPU program with malloc'd buffers).
+ *
+ * Same result as tie_cuda_moe_route on device pointers, but without a context and without a
+ * single allocation: no cudaMalloc / cudaFree / cudaMallocHost and no allocating library call,
+ * on any call.  It is meant for hosts that cannot allocate when they call in: a serving loop
+ * whose rules ban allocator calls once start-up is over (an allocation can block or fail at a
+ * bad moment), or an application that runs under a fixed memory budget and hands the library no
+ * allocator.  The logits scratch the router needs sits in a
+ * fixed array inside the library image (64 KiB on every GPU that loads the library, held until
+ * the process exits), so sizes are capped: n_tokens <= 64 and n_expert <= 256, and for
+ * n_tokens <= 8 also (1 + n_tokens) * hidden floats <= 200 KB of shared memory; anything larger
+ * returns TIE_CUDA_ETOOBIG.  hidden % 8 == 0 (% 256 when n_tokens > 8), n_expert % 16 == 0,
+ * top_k <= 8.
+ *
+ * The caller passes every input and output (device memory on the current device): x
+ * [n_tokens][hidden], router_w [n_expert][hidden], router_bias [n_expert] or NULL, topk_idx /
+ * topk_w [n_tokens][top_k].  Work is enqueued on cuda_stream (NULL = legacy default stream)
+ * and the call returns without synchronising.
+ *
+ * The first call on each device looks up the device address of the scratch array and sets a
+ * kernel attribute (the device must be current); that first call should come before any stream
+ * capture.  All calls on a device share the one scratch array: it keeps the previous call's
+ * contents (every element a call reads it has written first, so nothing needs clearing), and two
+ * calls whose kernels overlap on the GPU (for instance on different streams) race on it.
+ * Serialise them. */
+int tie_cuda_route_noalloc(const float *x_dev, const float *router_w_dev, const float *router_bias_dev, int n_tokens,
+			   int hidden, int n_expert, int top_k, int *topk_idx_dev, float *topk_w_dev, void *cuda_stream);
 
 /* ---- introspection for tests and benchmarks ---- */
 /* Number of kernels this context has launched since init (all entry points). */

@@ -46,7 +46,7 @@ def test_header_compiles_as_plain_c(tmp_path):
 
 def test_strerror_and_version(lib):
     assert lib.tie_cuda_strerror(0) == b"ok"
-    for code in range(-6, 0):
+    for code in range(-7, 0):
         assert lib.tie_cuda_strerror(code) not in (b"", b"unknown error")
     assert lib.tie_cuda_strerror(-99) == b"unknown error"
     assert b"sm_100a" in lib.tie_cuda_version()

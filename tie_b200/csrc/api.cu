@@ -348,6 +348,8 @@ const char *tie_cuda_strerror(int code)
 		return "no usable sm_100 device";
 	case TIE_CUDA_EKERNEL:
 		return "kernel reported an internal check failure";
+	case TIE_CUDA_ETOOBIG:
+		return "size exceeds the fixed scratch of the no-allocation entry point (n_tokens <= 64, n_expert <= 256)";
 	default:
 		return "unknown error";
 	}

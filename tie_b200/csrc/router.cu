@@ -214,3 +214,72 @@ int launch_router_rows(tie_cuda_ctx *c, const float *x, const float *w, int n_ro
 }
 
 }  // namespace tie
+
+// ---------------------------------------------------------------------------------------------
+// Routing without any allocation.
+//
+// Some hosts of this library may not allocate device memory when they call it: a serving loop
+// that forbids allocator calls once start-up is over, or an embedding application that gives the
+// library a fixed memory budget and no allocator.  For them the logits scratch of the router lives in the
+// library image itself: a file-scope __device__ array, present once on every GPU that loads the
+// library, for as long as the process lives.
+//
+// TIE_ROUTE_NOALLOC_MAX_TOKENS x TIE_ROUTE_NOALLOC_MAX_EXPERTS floats = 64 KiB per GPU.
+constexpr int TIE_ROUTE_NOALLOC_MAX_TOKENS = 64;
+constexpr int TIE_ROUTE_NOALLOC_MAX_EXPERTS = 256;
+static __device__ __align__(256) float g_route_scratch[TIE_ROUTE_NOALLOC_MAX_TOKENS * TIE_ROUTE_NOALLOC_MAX_EXPERTS];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float *g_route_scratch_addr[NOALLOC_MAX_DEVICES] = {nullptr};  // device address of the array, per device
+}
+
+extern "C" int tie_cuda_route_noalloc(const float *x_dev, const float *router_w_dev, const float *router_bias_dev, int n_tokens,
+				      int hidden, int n_expert, int top_k, int *topk_idx_dev, float *topk_w_dev, void *cuda_stream)
+{
+	using namespace tie;
+	if (!x_dev || !router_w_dev || !topk_idx_dev || !topk_w_dev || n_tokens <= 0 || hidden <= 0 || hidden % 8 || n_expert <= 0 ||
+	    n_expert % 16 || top_k <= 0 || top_k > MAX_TOP_K || top_k > n_expert)
+		return TIE_CUDA_EINVAL;
+	if (n_tokens > TIE_ROUTE_NOALLOC_MAX_TOKENS || n_expert > TIE_ROUTE_NOALLOC_MAX_EXPERTS)
+		return TIE_CUDA_ETOOBIG;
+	const size_t smem = ((size_t)hidden + (size_t)n_tokens * (hidden + 8)) * sizeof(float);
+	if (n_tokens <= 8 && smem > 200 * 1024)
+		return TIE_CUDA_ETOOBIG;
+	int dev = -1;
+	if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES)
+		return TIE_CUDA_ENODEV;
+	if (!g_route_scratch_addr[dev]) {
+		// First call on this device: resolve the array's DEVICE address.  In host code the name
+		// g_route_scratch is only a handle for the runtime, not an address a kernel can use.
+		float *p = nullptr;
+		if (cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_route_scratch) != cudaSuccess || !p) {
+			cudaGetLastError();
+			return TIE_CUDA_ECUDA;
+		}
+		if (cudaFuncSetAttribute(router_logits_decode<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) !=
+		    cudaSuccess) {
+			cudaGetLastError();
+			return TIE_CUDA_ECUDA;
+		}
+		g_route_scratch_addr[dev] = p;
+	}
+	float *logits = g_route_scratch_addr[dev];
+	cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
+	if (n_tokens <= 8) {
+		router_logits_decode<8><<<n_expert, 64, smem, st>>>(x_dev, router_w_dev, router_bias_dev, logits, n_tokens, hidden, n_expert);
+	} else {
+		constexpr int TT = 8, EPC = 16;
+		if (hidden % 256)
+			return TIE_CUDA_EINVAL;
+		dim3 grid((n_tokens + TT - 1) / TT, n_expert / EPC);
+		router_logits_tile<TT, EPC, 256><<<grid, EPC * 8, 0, st>>>(x_dev, router_w_dev, router_bias_dev, logits, n_tokens, hidden,
+									      n_expert);
+	}
+	if (cudaGetLastError() != cudaSuccess)
+		return TIE_CUDA_ECUDA;
+	router_topk<<<(n_tokens + 3) / 4, 128, 0, st>>>(logits, n_tokens, n_expert, top_k, topk_idx_dev, topk_w_dev);
+	if (cudaGetLastError() != cudaSuccess)
+		return TIE_CUDA_ECUDA;
+	return TIE_CUDA_OK;
+}

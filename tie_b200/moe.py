@@ -16,7 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libtie_cuda.so")
 
 HOST, DEVICE, NO_SYNC, GRAPH = 0, 1, 2, 4
 PATH_AUTO, PATH_STREAM, PATH_TENSOR = 0, 1 << 8, 2 << 8
-OK, EINVAL, ENOTSUP, ENOMEM, ECUDA, ENODEV, EKERNEL = 0, -1, -2, -3, -4, -5, -6
+OK, EINVAL, ENOTSUP, ENOMEM, ECUDA, ENODEV, EKERNEL, ETOOBIG = 0, -1, -2, -3, -4, -5, -6, -7
 
 # every symbol include/tie_cuda.h declares
 EXPORTS = [
@@ -27,7 +27,7 @@ EXPORTS = [
     "tie_cuda_mat_vec_row_f32_q4k_f32", "tie_cuda_mat_vec_row_f32_q6k_f32", "tie_cuda_mat_vec_row_f32_f32_f32",
     "tie_cuda_swiglu_f32_f32", "tie_cuda_dispatch_status", "tie_cuda_launch_count", "tie_cuda_last_active_experts",
     "tie_cuda_version", "tie_cuda_set_profiling", "tie_cuda_get_profile", "tie_cuda_moe_ep_dispatch",
-    "tie_cuda_moe_ep_combine",
+    "tie_cuda_moe_ep_combine", "tie_cuda_route_noalloc",
 ]
 PHASES = ["router", "sort", "split", "gate_up", "down", "combine"]
 
@@ -95,6 +95,8 @@ def load_library() -> ctypes.CDLL:
     L.tie_cuda_moe_ep_dispatch.argtypes = [vp, vp, vp, i32, vp, vp, vp, u32]
     L.tie_cuda_moe_ep_combine.restype = i32
     L.tie_cuda_moe_ep_combine.argtypes = [vp, vp, vp, i32, vp, u32]
+    L.tie_cuda_route_noalloc.restype = i32
+    L.tie_cuda_route_noalloc.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp, vp, vp]
     L.tie_cuda_make_current.restype = i32
     L.tie_cuda_make_current.argtypes = [vp]
     L.tie_cuda_register_tensor.restype = i32
