@@ -200,7 +200,7 @@ int run_experts(tie_cuda_ctx *c, const Layer &L, const float *x_src, int src_div
 	} else if (path == TIE_CUDA_PATH_STREAM) {
 		use_tc = false;
 	} else {
-		use_tc = tc_supported(c, L) && n_rows >= 16 * c->n_local;
+		use_tc = tc_supported(c, L) && n_rows >= 2 * c->n_local;
 	}
 	const int direct = (!use_tc && n_rows <= c->cfg.top_k && src_div == c->cfg.top_k) ? 1 : 0;
 	const int n_tile = ((size_t)n_rows <= (size_t)48 * c->n_local) ? 64 : 128;
@@ -433,6 +433,8 @@ int tie_cuda_init(tie_cuda_ctx **out, const tie_cuda_config *cfg)
 	free(tab);
 	if (e != cudaSuccess)
 		return fail(e == cudaErrorMemoryAllocation ? TIE_CUDA_ENOMEM : TIE_CUDA_ECUDA);
+	if (const char *e = getenv("TIE_CUDA_TC_OPERAND"))  // "smem": keep both MMA operands in shared memory
+		c->tc_a_in_tmem = strcmp(e, "smem") != 0;
 	if ((rc = alloc_scratch(c)) != TIE_CUDA_OK)
 		return fail(rc);
 	if ((rc = tc_setup(c)) != TIE_CUDA_OK)

@@ -90,9 +90,10 @@ __global__ void __launch_bounds__(256) split_rows(const float *__restrict__ x, c
 	__half2 *lr = reinterpret_cast<__half2 *>(lo + (size_t)p * n_cols);
 	for (int k = threadIdx.x * 4; k < n_cols; k += blockDim.x * 4) {
 		float4 v = *reinterpret_cast<const float4 *>(xr + k);
-		__half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
+		// stored order within a group of 4 is [k0, k2, k1, k3], the order the weight tiles use
+		__half2 h0 = __floats2half2_rn(v.x, v.z), h1 = __floats2half2_rn(v.y, v.w);
 		float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
-		__half2 l0 = __floats2half2_rn(v.x - f0.x, v.y - f0.y), l1 = __floats2half2_rn(v.z - f1.x, v.w - f1.y);
+		__half2 l0 = __floats2half2_rn(v.x - f0.x, v.z - f0.y), l1 = __floats2half2_rn(v.y - f1.x, v.w - f1.y);
 		hr[k / 2] = h0;
 		hr[k / 2 + 1] = h1;
 		lr[k / 2] = l0;

@@ -105,6 +105,28 @@ __device__ __forceinline__ void mma_f16_ss(uint32_t d_tmem, uint64_t adesc, uint
 		"l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
 		: "memory");
 }
+// Same with the A operand in tensor memory (lane = row, two 16-bit k elements per column).
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate)
+{
+	asm volatile(
+		"{\n\t"
+		".reg .pred p;\n\t"
+		"setp.ne.b32 p, %4, 0;\n\t"
+		"tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+		"}" ::"r"(d_tmem),
+		"r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+		: "memory");
+}
+// 4 consecutive 32-bit columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
+{
+	asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d)
+		     : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait()
+{
+	asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 // The mbarrier gets one arrival when all tcgen05 operations issued so far by this thread retire.
 __device__ __forceinline__ void mma_commit(uint32_t bar)
 {

@@ -24,6 +24,7 @@
 // drains, frees its tensor memory and exits.
 #include "common.cuh"
 #include "kernels.cuh"
+#include "tc_dequant.cuh"
 #include "tc_ptx.cuh"
 
 namespace tie {
@@ -36,14 +37,21 @@ constexpr int TC_A_TILE = TC_BM * TC_BK * 2;   // bytes of one fp16 operand tile
 constexpr uint64_t TC_WAIT_NS = 500ull * 1000 * 1000;
 constexpr float TC_H_SCALE = 1.0f / 256.0f;  // keeps SwiGLU outputs inside fp16 range; exact (power of two)
 
-template <int NMAT, int NT>
+// TM = false: both operands in shared memory.  TM = true: the dequantised weight tiles are written
+// to tensor memory (tcgen05.st) and the MMA takes A from TMEM; shared memory then only holds the
+// token operand, so the three products per k-step no longer re-read 4 KB of A from shared memory
+// each (which bounds the MMA rate when an expert has few tokens).
+template <int NMAT, int NT, bool TM>
 struct TcCfg {
 	static constexpr int B_TILE = NT * TC_BK * 2;
-	static constexpr int STAGE = NMAT * 2 * TC_A_TILE + 2 * B_TILE;
-	static constexpr int STAGES_RAW = (225 * 1024) / STAGE;
+	static constexpr int A_COLS = 32;  // TMEM columns of one 128 x 64 fp16 tile
+	static constexpr int STAGE = (TM ? 0 : NMAT * 2 * TC_A_TILE) + 2 * B_TILE;
+	static constexpr int ACC_COLS = NMAT * NT;
+	static constexpr int STAGES_TM = (512 - ACC_COLS) / (NMAT * 2 * A_COLS);
+	static constexpr int STAGES_RAW = TM ? STAGES_TM : (225 * 1024) / STAGE;
 	static constexpr int STAGES = STAGES_RAW > 4 ? 4 : STAGES_RAW;
 	static constexpr int SMEM = STAGES * STAGE + 1024 /* alignment slack */ + 256 /* barriers */;
-	static constexpr int TMEM_COLS = (NMAT * NT) < 32 ? 32 : (NMAT * NT);
+	static constexpr int TMEM_COLS = TM ? 512 : (ACC_COLS < 32 ? 32 : ACC_COLS);
 	static_assert(STAGES >= 2, "need at least two stages");
 	static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns: power of two <= 512");
 };
@@ -78,85 +86,146 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
 	return true;
 }
 
-__device__ __forceinline__ void split_store8(const float w[8], uint32_t addr_hi, uint32_t addr_lo)
+// One 8-wide k chunk (4 half2 words of hi, 4 of lo) of this thread's row goes either to the
+// swizzled shared-memory operand tiles (base = row address, c = 16-byte chunk index) or, when the
+// weight operand lives in tensor memory, to 4 TMEM columns of the thread's lane (base = tile
+// address with the warp's lane quadrant, 2 halves per 32-bit column).
+template <bool TM>
+__device__ __forceinline__ void put_chunk(uint32_t base_hi, uint32_t base_lo, uint32_t sw, uint32_t c, const uint32_t h0[2],
+					  const uint32_t h1[2], const uint32_t l0[2], const uint32_t l1[2])
 {
-	uint32_t hi[4], lo[4];
-#pragma unroll
-	for (int i = 0; i < 4; i++) {
-		__half2 h = __floats2half2_rn(w[2 * i], w[2 * i + 1]);
-		float2 f = __half22float2(h);
-		__half2 l = __floats2half2_rn(w[2 * i] - f.x, w[2 * i + 1] - f.y);
-		hi[i] = *reinterpret_cast<uint32_t *>(&h);
-		lo[i] = *reinterpret_cast<uint32_t *>(&l);
-	}
-	asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr_hi), "r"(hi[0]), "r"(hi[1]), "r"(hi[2]), "r"(hi[3]) : "memory");
-	asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr_lo), "r"(lo[0]), "r"(lo[1]), "r"(lo[2]), "r"(lo[3]) : "memory");
-}
-
-// 32 weights of one (row, half-slice) for k stage `it`: w[0..15] -> k_local 16*hs + i,
-// w[16..31] -> k_local 32 + 16*hs + i.
-template <WKind KIND>
-__device__ __forceinline__ void dequant32(const uint8_t *wexp, int nb, int row, int it, int hs, float w[32]);
-
-template <>
-__device__ __forceinline__ void dequant32<W_Q4K>(const uint8_t *wexp, int nb, int row, int it, int hs, float w[32])
-{
-	const int kb = it >> 2, q = it & 3;
-	const uint8_t *blk = wexp + ((size_t)row * nb + kb) * Q4K_BYTES;
-	const uint4 hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
-	const uint4 qv = __ldg(reinterpret_cast<const uint4 *>(blk + 16 + 32 * q + 16 * hs));
-	const float d = half_bits_to_float(hdr.x & 0xffffu), dmin = half_bits_to_float(hdr.x >> 16);
-	const uint32_t sc[3] = {hdr.y, hdr.z, hdr.w};
-	int s_lo, m_lo, s_hi, m_hi;
-	q4k_scale_min(sc, 2 * q, s_lo, m_lo);
-	q4k_scale_min(sc, 2 * q + 1, s_hi, m_hi);
-	const float dl = __fmul_rn(d, (float)s_lo), ml = __fmul_rn(dmin, (float)m_lo);
-	const float dh = __fmul_rn(d, (float)s_hi), mh = __fmul_rn(dmin, (float)m_hi);
-	const uint32_t ww[4] = {qv.x, qv.y, qv.z, qv.w};
-#pragma unroll
-	for (int k = 0; k < 4; k++) {
-#pragma unroll
-		for (int j = 0; j < 4; j++) {
-			uint32_t byte = (ww[k] >> (8 * j)) & 0xffu;
-			w[4 * k + j] = __fmaf_rn((float)(byte & 15u), dl, -ml);
-			w[16 + 4 * k + j] = __fmaf_rn((float)(byte >> 4), dh, -mh);
-		}
+	if (TM) {
+		ptx::tmem_st4(base_hi + 4 * c, h0[0], h0[1], h1[0], h1[1]);
+		ptx::tmem_st4(base_lo + 4 * c, l0[0], l0[1], l1[0], l1[1]);
+	} else {
+		const uint32_t off = (c ^ sw) << 4;
+		sts128(base_hi + off, h0[0], h0[1], h1[0], h1[1]);
+		sts128(base_lo + off, l0[0], l0[1], l1[0], l1[1]);
 	}
 }
 
-template <>
-__device__ __forceinline__ void dequant32<W_Q6K_R8>(const uint8_t *wexp, int nb, int row, int it, int hs, float w[32])
-{
-	const int kb = it >> 2, q = it & 3;
-	const int n = q >> 1, odd = q & 1;
-	const uint8_t *grp = wexp + (size_t)(row >> 3) * q6k_r8_group_bytes(nb);
-	const int r8 = row & 7, pp = n * 2 + hs;
-	const uint4 *ch = reinterpret_cast<const uint4 *>(grp + q6k_r8_chunk_off(nb, r8, kb, pp));
-	const uint4 a = __ldg(ch), b = __ldg(ch + 1), h = __ldg(ch + 2);
-	const uint32_t scw = __ldg(reinterpret_cast<const uint32_t *>(grp + q6k_r8_scale_off(nb, r8, kb, pp)));
-	const float d = half_bits_to_float(__ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb, r8, kb))));
-	const float sA = __fmul_rn(d, (float)(int)(signed char)((scw >> (16 * odd)) & 0xff));
-	const float sB = __fmul_rn(d, (float)(int)(signed char)((scw >> (16 * odd + 8)) & 0xff));
-	const uint32_t A[4] = {a.x, a.y, a.z, a.w}, B[4] = {b.x, b.y, b.z, b.w}, Hh[4] = {h.x, h.y, h.z, h.w};
+// Packed weights one producer thread needs for two consecutive k stages (128 k, "group" g) of
+// its matrix row.  With two matrices (gate/up) a thread owns all 64 k of a stage for one
+// (row, matrix); with one matrix (down) it owns the 32-k half-slice hs of a stage.
+template <WKind KIND, int NMAT>
+struct RawGroup;
+
+template <int NMAT>
+struct RawGroup<W_Q4K, NMAT> {
+	static constexpr int NQ = (NMAT == 2) ? 2 : 1;
+	uint4 hdr;
+	uint4 q[2][NQ];
+	__device__ __forceinline__ void load(const uint8_t *wexp, int nb, int row, int g, int hs)
+	{
+		const uint8_t *blk = wexp + ((size_t)row * nb + (g >> 1)) * Q4K_BYTES;
+		hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
 #pragma unroll
-	for (int k = 0; k < 4; k++) {
-		uint32_t qa, qb;
-		if (!odd) {
-			qa = (A[k] & 0x0F0F0F0Fu) | ((Hh[k] << 4) & 0x30303030u);
-			qb = (B[k] & 0x0F0F0F0Fu) | ((Hh[k] << 2) & 0x30303030u);
-		} else {
-			qa = ((A[k] >> 4) & 0x0F0F0F0Fu) | (Hh[k] & 0x30303030u);
-			qb = ((B[k] >> 4) & 0x0F0F0F0Fu) | ((Hh[k] >> 2) & 0x30303030u);
-		}
-#pragma unroll
-		for (int j = 0; j < 4; j++) {
-			w[4 * k + j] = __fmul_rn(sA, (float)((int)((qa >> (8 * j)) & 0xffu) - 32));
-			w[16 + 4 * k + j] = __fmul_rn(sB, (float)((int)((qb >> (8 * j)) & 0xffu) - 32));
+		for (int st = 0; st < 2; st++) {
+			const uint4 *base = reinterpret_cast<const uint4 *>(blk + 16 + 32 * ((g & 1) * 2 + st));
+			if (NMAT == 2) {
+				q[st][0] = __ldg(base);
+				q[st][NQ - 1] = __ldg(base + 1);
+			} else {
+				q[st][0] = __ldg(base + hs);
+			}
 		}
 	}
-}
+	// writes this thread's chunks of stage (2g + st) into the hi/lo tiles (row base addresses given)
+	template <bool TM>
+	__device__ __forceinline__ void emit(int g, int st, int hs, uint32_t row_hi, uint32_t row_lo, uint32_t sw) const
+	{
+		const int p = (g & 1) * 2 + st;
+		const float d = half_bits_to_float(hdr.x & 0xffffu), dmin = half_bits_to_float(hdr.x >> 16);
+		const uint32_t sc[3] = {hdr.y, hdr.z, hdr.w};
+		int s_lo, m_lo, s_hi, m_hi;
+		q4k_scale_min(sc, 2 * p, s_lo, m_lo);
+		q4k_scale_min(sc, 2 * p + 1, s_hi, m_hi);
+		const H2x4 cl = q4k_consts(__fmul_rn(d, (float)s_lo), __fmul_rn(dmin, (float)m_lo));
+		const H2x4 ch = q4k_consts(__fmul_rn(d, (float)s_hi), __fmul_rn(dmin, (float)m_hi));
+		constexpr int NWORD = 4 * NQ;
+		uint32_t w[NWORD];
+#pragma unroll
+		for (int i = 0; i < NQ; i++) {
+			w[4 * i] = q[st][i].x;
+			w[4 * i + 1] = q[st][i].y;
+			w[4 * i + 2] = q[st][i].z;
+			w[4 * i + 3] = q[st][i].w;
+		}
+		const uint32_t c0 = (NMAT == 2) ? 0u : 2u * hs;	 // first chunk of the low-nibble half
+#pragma unroll
+		for (int cc = 0; cc < NWORD / 2; cc++) {
+			uint32_t h0[2], l0[2], h1[2], l1[2];
+			q4k_word(w[2 * cc], 0, cl, h0, l0);
+			q4k_word(w[2 * cc + 1], 0, cl, h1, l1);
+			put_chunk<TM>(row_hi, row_lo, sw, c0 + cc, h0, h1, l0, l1);
+			q4k_word(w[2 * cc], 4, ch, h0, l0);
+			q4k_word(w[2 * cc + 1], 4, ch, h1, l1);
+			put_chunk<TM>(row_hi, row_lo, sw, 4u + c0 + cc, h0, h1, l0, l1);
+		}
+	}
+};
 
-template <WKind KIND, int NMAT, int NT>
+template <int NMAT>
+struct RawGroup<W_Q6K_R8, NMAT> {
+	static constexpr int NL = (NMAT == 2) ? 2 : 1;	// 16-wide l slices this thread owns
+	uint4 a[NL], b[NL], h[NL];
+	uint32_t scw[NL];
+	float d;
+	__device__ __forceinline__ void load(const uint8_t *wexp, int nb, int row, int g, int hs)
+	{
+		const uint8_t *grp = wexp + (size_t)(row >> 3) * q6k_r8_group_bytes(nb);
+		const int r8 = row & 7, kb = g >> 1, n = g & 1;
+#pragma unroll
+		for (int i = 0; i < NL; i++) {
+			const int l16 = (NMAT == 2) ? i : hs;
+			const int pp = n * 2 + l16;
+			const uint4 *ch = reinterpret_cast<const uint4 *>(grp + q6k_r8_chunk_off(nb, r8, kb, pp));
+			a[i] = __ldg(ch);
+			b[i] = __ldg(ch + 1);
+			h[i] = __ldg(ch + 2);
+			scw[i] = __ldg(reinterpret_cast<const uint32_t *>(grp + q6k_r8_scale_off(nb, r8, kb, pp)));
+		}
+		d = half_bits_to_float(__ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb, r8, kb))));
+	}
+	template <bool TM>
+	__device__ __forceinline__ void emit(int g, int st, int hs, uint32_t row_hi, uint32_t row_lo, uint32_t sw) const
+	{
+#pragma unroll
+		for (int i = 0; i < NL; i++) {
+			const uint32_t l16 = (NMAT == 2) ? (uint32_t)i : (uint32_t)hs;
+			const float sA = __fmul_rn(d, (float)(int)(signed char)((scw[i] >> (16 * st)) & 0xff));
+			const float sB = __fmul_rn(d, (float)(int)(signed char)((scw[i] >> (16 * st + 8)) & 0xff));
+			__half2 sAh, sAr, sBh, sBr;
+			q6k_consts(sA, sAh, sAr);
+			q6k_consts(sB, sBh, sBr);
+			const uint32_t A[4] = {a[i].x, a[i].y, a[i].z, a[i].w}, B[4] = {b[i].x, b[i].y, b[i].z, b[i].w};
+			const uint32_t Hh[4] = {h[i].x, h[i].y, h[i].z, h[i].w};
+			uint32_t qa[4], qb[4];
+#pragma unroll
+			for (int k = 0; k < 4; k++) {
+				if (st == 0) {
+					qa[k] = (A[k] & 0x0F0F0F0Fu) | ((Hh[k] << 4) & 0x30303030u);
+					qb[k] = (B[k] & 0x0F0F0F0Fu) | ((Hh[k] << 2) & 0x30303030u);
+				} else {
+					qa[k] = ((A[k] >> 4) & 0x0F0F0F0Fu) | (Hh[k] & 0x30303030u);
+					qb[k] = ((B[k] >> 4) & 0x0F0F0F0Fu) | ((Hh[k] >> 2) & 0x30303030u);
+				}
+			}
+#pragma unroll
+			for (int cc = 0; cc < 2; cc++) {
+				uint32_t h0[2], l0[2], h1[2], l1[2];
+				q6k_word(qa[2 * cc], sAh, sAr, h0, l0);
+				q6k_word(qa[2 * cc + 1], sAh, sAr, h1, l1);
+				put_chunk<TM>(row_hi, row_lo, sw, 2u * l16 + cc, h0, h1, l0, l1);
+				q6k_word(qb[2 * cc], sBh, sBr, h0, l0);
+				q6k_word(qb[2 * cc + 1], sBh, sBr, h1, l1);
+				put_chunk<TM>(row_hi, row_lo, sw, 4u + 2u * l16 + cc, h0, h1, l0, l1);
+			}
+		}
+	}
+};
+
+template <WKind KIND, int NMAT, int NT, bool TM>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__ CUtensorMap tm_lo,
 		const uint8_t *__restrict__ w0, const uint8_t *__restrict__ w1, size_t expert_stride, int k_dim,
@@ -164,7 +233,7 @@ grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 		__half *__restrict__ h_hi, __half *__restrict__ h_lo, float *__restrict__ y, const int *__restrict__ perm,
 		int out_stride, const float *__restrict__ silu, unsigned *__restrict__ status)
 {
-	using Cfg = TcCfg<NMAT, NT>;
+	using Cfg = TcCfg<NMAT, NT, TM>;
 	constexpr int S = Cfg::STAGES;
 	extern __shared__ uint8_t smem_raw[];
 
@@ -202,7 +271,13 @@ grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
 	auto a_tile = [&](int s, int m, int hl) -> uint32_t { return tiles + s * Cfg::STAGE + (m * 2 + hl) * TC_A_TILE; };
-	auto b_tile = [&](int s, int hl) -> uint32_t { return tiles + s * Cfg::STAGE + NMAT * 2 * TC_A_TILE + hl * Cfg::B_TILE; };
+	auto b_tile = [&](int s, int hl) -> uint32_t {
+		return tiles + s * Cfg::STAGE + (TM ? 0 : NMAT * 2 * TC_A_TILE) + hl * Cfg::B_TILE;
+	};
+	// TMEM column of weight tile (stage, matrix, hi/lo) when the A operand lives in tensor memory
+	auto a_col = [&](int s, int m, int hl) -> uint32_t {
+		return Cfg::ACC_COLS + (s * NMAT * 2 + m * 2 + hl) * Cfg::A_COLS;
+	};
 
 	if (threadIdx.x == 0) {
 		for (int s = 0; s < S; s++) {
@@ -230,34 +305,46 @@ grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 
 	if (warp < TC_PRODUCERS / 32) {
 		// ================= producers: dequantise A tiles =================
-		const int row = threadIdx.x & 127, hs = threadIdx.x >> 7;
-		const uint8_t *we[2] = {w0 + (size_t)le * expert_stride, (NMAT == 2) ? w1 + (size_t)le * expert_stride : nullptr};
+		// thread = (row, matrix) for gate/up, (row, half-slice) for down; the packed bytes of the
+		// next 128-k group are fetched into registers while the current group is expanded
+		const int row = threadIdx.x & 127, sel = threadIdx.x >> 7;
+		const int m = (NMAT == 2) ? sel : 0, hs = (NMAT == 2) ? 0 : sel;
+		const uint8_t *wexp = ((NMAT == 2 && sel) ? w1 : w0) + (size_t)le * expert_stride;
 		const uint32_t row_off = row * 128;
 		const uint32_t sw = row & 7;
-		for (int it = 0; it < k_iters; it++) {
-			const int s = it % S;
-			if (it >= S && !tc_wait(ptx::smem_u32(&sh->empty[s]), ((it / S) & 1) ^ 1, abort_flag, status))
-				break;
+		const int n_groups = k_iters >> 1;
+		RawGroup<KIND, NMAT> cur, nxt;
+		cur.load(wexp, nb, m0 + row, 0, hs);
+		bool alive = true;
+		for (int g = 0; g < n_groups && alive; g++) {
+			if (g + 1 < n_groups)
+				nxt.load(wexp, nb, m0 + row, g + 1, hs);
 #pragma unroll
-			for (int m = 0; m < NMAT; m++) {
-				float w[32];
-				dequant32<KIND>(we[m], nb, m0 + row, it, hs, w);
-				const uint32_t ah = a_tile(s, m, 0) + row_off, al = a_tile(s, m, 1) + row_off;
-#pragma unroll
-				for (int cc = 0; cc < 4; cc++) {
-					// chunks 2hs, 2hs+1 (first 16 weights) and 4+2hs, 4+2hs+1 (second 16)
-					const uint32_t c = ((cc & 2) ? 4u : 0u) + 2u * hs + (cc & 1);
-					const uint32_t off = (c ^ sw) << 4;
-					split_store8(&w[8 * cc], ah + off, al + off);
+			for (int st = 0; st < 2; st++) {
+				const int it = 2 * g + st;
+				const int s = it % S;
+				if (it >= S && !tc_wait(ptx::smem_u32(&sh->empty[s]), ((it / S) & 1) ^ 1, abort_flag, status)) {
+					alive = false;
+					break;
 				}
+				if (TM) {
+					const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+					cur.template emit<true>(g, st, hs, lane_base + a_col(s, m, 0), lane_base + a_col(s, m, 1), 0);
+					ptx::tmem_st_wait();
+					ptx::tc_fence_before();
+				} else {
+					cur.template emit<false>(g, st, hs, a_tile(s, m, 0) + row_off, a_tile(s, m, 1) + row_off, sw);
+					ptx::fence_proxy_async_smem();
+				}
+				ptx::mbar_arrive(ptx::smem_u32(&sh->full[s]));
 			}
-			ptx::fence_proxy_async_smem();
-			ptx::mbar_arrive(ptx::smem_u32(&sh->full[s]));
+			cur = nxt;
 		}
 	} else if (warp == TC_PRODUCERS / 32) {
 		// ================= MMA issuer =================
 		if (lane == 0) {
-			constexpr uint32_t idesc = ptx::umma_idesc_f16(TC_BM, NT);
+			// the MMA's N is the expert's token count in this tile rounded up to 16 (a runtime field)
+			const uint32_t idesc = ptx::umma_idesc_f16(TC_BM, min(NT, (n_valid + 15) & ~15));
 			bool ok = true;
 			for (int it = 0; it < k_iters && ok; it++) {
 				const int s = it % S;
@@ -271,12 +358,20 @@ grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 					const uint64_t bl = ptx::umma_desc_sw128(b_tile(s, 1)) + 2 * kk;
 #pragma unroll
 					for (int m = 0; m < NMAT; m++) {
-						const uint64_t ahd = ptx::umma_desc_sw128(a_tile(s, m, 0)) + 2 * kk;
-						const uint64_t ald = ptx::umma_desc_sw128(a_tile(s, m, 1)) + 2 * kk;
 						const uint32_t d = tmem + m * NT;
-						ptx::mma_f16_ss(d, ahd, bh, idesc, (it > 0 || kk > 0) ? 1u : 0u);
-						ptx::mma_f16_ss(d, ald, bh, idesc, 1u);
-						ptx::mma_f16_ss(d, ahd, bl, idesc, 1u);
+						const uint32_t acc = (it > 0 || kk > 0) ? 1u : 0u;
+						if (TM) {
+							const uint32_t ah = tmem + a_col(s, m, 0) + 8 * kk, al = tmem + a_col(s, m, 1) + 8 * kk;
+							ptx::mma_f16_ts(d, ah, bh, idesc, acc);
+							ptx::mma_f16_ts(d, al, bh, idesc, 1u);
+							ptx::mma_f16_ts(d, ah, bl, idesc, 1u);
+						} else {
+							const uint64_t ahd = ptx::umma_desc_sw128(a_tile(s, m, 0)) + 2 * kk;
+							const uint64_t ald = ptx::umma_desc_sw128(a_tile(s, m, 1)) + 2 * kk;
+							ptx::mma_f16_ss(d, ahd, bh, idesc, acc);
+							ptx::mma_f16_ss(d, ald, bh, idesc, 1u);
+							ptx::mma_f16_ss(d, ahd, bl, idesc, 1u);
+						}
 					}
 				}
 				ptx::mma_commit(ptx::smem_u32(&sh->empty[s]));
@@ -322,7 +417,7 @@ grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 							float hv = swiglu_lut(silu, __uint_as_float(g[j]), __uint_as_float(u[j])) * TC_H_SCALE;
 							__half hh = __float2half_rn(hv);
 							__half hl = __float2half_rn(hv - __half2float(hh));
-							const size_t o = (size_t)(row0 + n) * out_stride + mrow;
+							const size_t o = (size_t)(row0 + n) * out_stride + tc_kperm(mrow);
 							h_hi[o] = hh;
 							h_lo[o] = hl;
 						} else {
@@ -397,9 +492,11 @@ int tc_setup(tie_cuda_ctx *c)
 			if (rc)
 				return rc;
 		}
-#define TC_ATTR(KIND, NMAT, NT)                                                                                            \
-	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_tc<KIND, NMAT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-					     TcCfg<NMAT, NT>::SMEM))
+#define TC_ATTR(KIND, NMAT, NT)                                                                                                   \
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_tc<KIND, NMAT, NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+					     TcCfg<NMAT, NT, false>::SMEM));                                                      \
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_tc<KIND, NMAT, NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+					     TcCfg<NMAT, NT, true>::SMEM))
 	TC_ATTR(W_Q4K, 1, 64);
 	TC_ATTR(W_Q4K, 1, 128);
 	TC_ATTR(W_Q4K, 2, 64);
@@ -417,13 +514,17 @@ template <WKind KIND, int NMAT, int NT>
 static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1, const CUtensorMap &tmh, const CUtensorMap &tml,
 		       int n_rows, float *y)
 {
-	using Cfg = TcCfg<NMAT, NT>;
 	Scratch &s = c->s;
 	const int max_tiles = min(c->n_local, n_rows) + n_rows / NT;
 	dim3 grid(t0.rows / TC_BM, max_tiles);
-	grouped_gemm_tc<KIND, NMAT, NT><<<grid, TC_THREADS, Cfg::SMEM, c->stream>>>(
-		tmh, tml, t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride, t0.k, s.offsets, s.tile_start, c->n_local, s.hs_hi,
-		s.hs_lo, y, s.perm, t0.rows, c->silu, s.status);
+	if (c->tc_a_in_tmem)
+		grouped_gemm_tc<KIND, NMAT, NT, true><<<grid, TC_THREADS, TcCfg<NMAT, NT, true>::SMEM, c->stream>>>(
+			tmh, tml, t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride, t0.k, s.offsets, s.tile_start, c->n_local, s.hs_hi,
+			s.hs_lo, y, s.perm, t0.rows, c->silu, s.status);
+	else
+		grouped_gemm_tc<KIND, NMAT, NT, false><<<grid, TC_THREADS, TcCfg<NMAT, NT, false>::SMEM, c->stream>>>(
+			tmh, tml, t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride, t0.k, s.offsets, s.tile_start, c->n_local, s.hs_hi,
+			s.hs_lo, y, s.perm, t0.rows, c->silu, s.status);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
