@@ -433,8 +433,6 @@ int tie_cuda_init(tie_cuda_ctx **out, const tie_cuda_config *cfg)
 	free(tab);
 	if (e != cudaSuccess)
 		return fail(e == cudaErrorMemoryAllocation ? TIE_CUDA_ENOMEM : TIE_CUDA_ECUDA);
-	if (const char *e = getenv("TIE_CUDA_TC_OPERAND"))  // "smem": keep both MMA operands in shared memory
-		c->tc_a_in_tmem = strcmp(e, "smem") != 0;
 	if ((rc = alloc_scratch(c)) != TIE_CUDA_OK)
 		return fail(rc);
 	if ((rc = tc_setup(c)) != TIE_CUDA_OK)

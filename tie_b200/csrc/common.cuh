@@ -99,10 +99,9 @@ struct tie_cuda_ctx {
 	cudaEvent_t prof_ev[8] = {nullptr};
 	bool prof_set[8] = {false};
 	char cuda_err[256] = {0};
-	// tensor maps for the tcgen05 path: [array 0..3 = xs_hi, xs_lo, hs_hi, hs_lo][n_tile 0..1 = 64,128]
-	CUtensorMap tmap[4][2];
+	// tensor maps for the tcgen05 path: xs_hi, xs_lo, hs_hi, hs_lo (16-row boxes)
+	CUtensorMap tmap[4];
 	bool tmaps_ok = false;
-	bool tc_a_in_tmem = true;  // weight operand of the grouped GEMM in tensor memory (else shared memory)
 	// host registry for dispatch rows
 	struct Reg {
 		const void *host;

@@ -58,6 +58,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 	return ok != 0;
 }
 
+// ---- cp.async: per-thread asynchronous copies global -> shared ----
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void *src)
+{
+	asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void *src)
+{
+	asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit()
+{
+	asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait()
+{
+	asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // ---- TMA: 2-D tile load global -> shared, completion counted on an mbarrier ----
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tmap, uint32_t bar, int x, int y)
 {

@@ -1,5 +1,5 @@
 // Grouped expert GEMMs for prefill on the 5th-generation tensor cores (tcgen05.mma, accumulators
-// in tensor memory), fed from packed Q4_K / Q6_K super-blocks.
+// and the weight operand in tensor memory), fed from packed Q4_K / Q6_K super-blocks.
 //
 // Reference: the same arithmetic as process_expert_task (engine.c:916-964) — gate/up products
 // (math_avx2.c:535-604, 753-769), table SwiGLU (math_avx2.c:908-950), down product
@@ -9,14 +9,19 @@
 // Formulation: out^T = W . x^T.  The weight rows fill the 128-row M dimension of the MMA (expert
 // row counts are multiples of 128), the ragged token count of an expert is the N dimension.
 // A CTA owns one (expert, 128-row tile, token tile).  Per 64-wide k stage:
-//   * 8 producer warps read packed blocks (128-bit loads), dequantise to fp32 exactly as the
-//     reference does (q*(d*sc) - dmin*m, fused), split each weight into fp16 hi + lo and write two
-//     K-major, 128-byte-swizzled operand tiles into shared memory;
+//   * 8 producer warps read packed blocks (128-bit loads, prefetched one 128-k group ahead into
+//     registers), expand them in packed fp16 arithmetic to exact-hi + lo operand pairs
+//     (tc_dequant.cuh) and write them to TENSOR MEMORY with tcgen05.st — the A operand of the MMA
+//     is taken from TMEM, so shared memory carries only the token operand;
 //   * one thread issues TMA tile loads of the token operand (already split into hi/lo fp16, in
-//     expert-sorted row order) into the same swizzled layout;
-//   * one thread issues tcgen05.mma: D += A_hi.B_hi + A_lo.B_hi + A_hi.B_lo (fp32 accumulate in
-//     TMEM).  hi+lo carries 22 significand bits per operand; a single fp16 or bf16 product per
-//     element is NOT accurate enough for the 1e-3 parity bound on this path.
+//     expert-sorted row order, 16-row boxes: only rows the expert really has) into a ring that
+//     runs several k stages ahead of the weight stages;
+//   * one thread per weight matrix issues tcgen05.mma (kind::f16, fp32 accumulate in TMEM):
+//     D += A_hi.B_hi + A_hi.B_lo + A_lo.B_hi.  hi+lo carries ~22 significand bits per operand; a
+//     single fp16 or bf16 product per element is NOT accurate enough for the 1e-3 parity bound.
+//     When the accumulators fit, B_hi and B_lo are stacked along N so that A_hi needs one MMA of
+//     twice the width instead of two (fewer, larger instructions when an expert has few tokens);
+//     the two column ranges are added in the epilogue.
 // Stages are recycled through mbarriers (producers -> full -> MMA -> tcgen05.commit -> empty).
 // Epilogue: tcgen05.ld from TMEM; gate/up: SwiGLU via the table, scaled by 2^-8, split to fp16
 // hi/lo for the down GEMM; down: scaled back and scattered to the (token, slot) row.
@@ -32,51 +37,55 @@ namespace tie {
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;
 constexpr int TC_PRODUCERS = 256;
-constexpr int TC_THREADS = TC_PRODUCERS + 64;  // + MMA warp + TMA warp
-constexpr int TC_A_TILE = TC_BM * TC_BK * 2;   // bytes of one fp16 operand tile (16 KB)
-constexpr uint64_t TC_WAIT_NS = 500ull * 1000 * 1000;
+constexpr int TC_PWARPS = TC_PRODUCERS / 32;
+constexpr int TC_THREADS = TC_PRODUCERS + 96;  // + two MMA-issuer warps + TMA warp
+constexpr long long TC_WAIT_CYCLES = 1ll << 30;	 // about half a second of SM clocks
 constexpr float TC_H_SCALE = 1.0f / 256.0f;  // keeps SwiGLU outputs inside fp16 range; exact (power of two)
 
-// TM = false: both operands in shared memory.  TM = true: the dequantised weight tiles are written
-// to tensor memory (tcgen05.st) and the MMA takes A from TMEM; shared memory then only holds the
-// token operand, so the three products per k-step no longer re-read 4 KB of A from shared memory
-// each (which bounds the MMA rate when an expert has few tokens).
-template <int NMAT, int NT, bool TM>
+template <int NMAT, int NT>
 struct TcCfg {
-	static constexpr int B_TILE = NT * TC_BK * 2;
-	static constexpr int A_COLS = 32;  // TMEM columns of one 128 x 64 fp16 tile
-	static constexpr int STAGE = (TM ? 0 : NMAT * 2 * TC_A_TILE) + 2 * B_TILE;
-	static constexpr int ACC_COLS = NMAT * NT;
-	static constexpr int STAGES_TM = (512 - ACC_COLS) / (NMAT * 2 * A_COLS);
-	static constexpr int STAGES_RAW = TM ? STAGES_TM : (225 * 1024) / STAGE;
-	static constexpr int STAGES = STAGES_RAW > 4 ? 4 : STAGES_RAW;
-	static constexpr int SMEM = STAGES * STAGE + 1024 /* alignment slack */ + 256 /* barriers */;
-	static constexpr int TMEM_COLS = TM ? 512 : (ACC_COLS < 32 ? 32 : ACC_COLS);
-	static_assert(STAGES >= 2, "need at least two stages");
-	static_assert((TMEM_COLS & (TMEM_COLS - 1)) == 0 && TMEM_COLS <= 512, "TMEM columns: power of two <= 512");
+	static constexpr int B_TILE = NT * TC_BK * 2;  // bytes of one (hi or lo) token tile
+	static constexpr int B_STAGE = 2 * B_TILE;
+	static constexpr int A_COLS = 32;  // TMEM columns of one 128 x 64 fp16 weight tile
+	// stack B_hi / B_lo along N when the doubled accumulators still leave room for weight stages
+	static constexpr bool CONCAT = NMAT * 2 * NT <= 256;
+	static constexpr int ACC_PER_MAT = CONCAT ? 2 * NT : NT;
+	static constexpr int ACC_COLS = NMAT * ACC_PER_MAT;
+	static constexpr int STAGES_RAW = (512 - ACC_COLS) / (NMAT * 2 * A_COLS);
+	static constexpr int STAGES = STAGES_RAW > 4 ? 4 : STAGES_RAW;	// weight stages (tensor memory)
+	static constexpr int SB_RAW = (200 * 1024) / B_STAGE;
+	static constexpr int SB = SB_RAW > 8 ? 8 : SB_RAW;  // token-operand stages (shared memory)
+	static constexpr int SMEM = SB * B_STAGE + 1024 /* alignment slack */ + 512 /* barriers */;
+	static constexpr int TMEM_COLS = 512;
+	static_assert(STAGES >= 2 && SB >= 2, "need at least two stages");
+	static_assert(ACC_COLS + STAGES * NMAT * 2 * A_COLS <= 512, "tensor memory budget");
 };
 
 struct TcShared {
-	uint64_t full[4];
-	uint64_t empty[4];
+	uint64_t full[4];    // weight stage written by the producers
+	uint64_t empty[4];   // weight stage consumed by the MMAs
+	uint64_t bfull[8];   // token tiles landed (TMA transaction bytes)
+	uint64_t bempty[8];  // token tiles consumed
 	uint64_t done;
 	uint32_t tmem_base;
 	uint32_t abort;
 };
 
 // Bounded wait: false (and the abort flag raised) when the barrier does not flip in time or
-// another CTA has already reported a timeout.
+// another CTA has already reported a timeout.  The cycle counter is read only after many failed
+// polls.
 __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, unsigned *status)
 {
-	if (ptx::mbar_try_wait(bar, parity))
-		return true;
-	const uint64_t t0 = ptx::globaltimer_ns();
+	long long t0 = 0;
 	uint32_t spins = 0;
 	while (!ptx::mbar_try_wait(bar, parity)) {
-		if (*abort_flag)
-			return false;
-		if ((++spins & 255u) == 0) {
-			if (ptx::globaltimer_ns() - t0 > TC_WAIT_NS || (*(volatile unsigned *)status & ST_WAIT_TIMEOUT)) {
+		if ((++spins & 1023u) == 0) {
+			if (*abort_flag)
+				return false;
+			const long long now = clock64();
+			if (t0 == 0)
+				t0 = now;
+			if (now - t0 > TC_WAIT_CYCLES || (*(volatile unsigned *)status & ST_WAIT_TIMEOUT)) {
 				atomicOr(status, ST_WAIT_TIMEOUT);
 				*abort_flag = 1;
 				return false;
@@ -86,22 +95,13 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
 	return true;
 }
 
-// One 8-wide k chunk (4 half2 words of hi, 4 of lo) of this thread's row goes either to the
-// swizzled shared-memory operand tiles (base = row address, c = 16-byte chunk index) or, when the
-// weight operand lives in tensor memory, to 4 TMEM columns of the thread's lane (base = tile
-// address with the warp's lane quadrant, 2 halves per 32-bit column).
-template <bool TM>
-__device__ __forceinline__ void put_chunk(uint32_t base_hi, uint32_t base_lo, uint32_t sw, uint32_t c, const uint32_t h0[2],
-					  const uint32_t h1[2], const uint32_t l0[2], const uint32_t l1[2])
+// One 8-wide k chunk (4 half2 words of hi, 4 of lo) of this thread's row -> 4 TMEM columns of the
+// thread's lane in the hi and in the lo tile (2 halves per 32-bit column; c = chunk index 0..7).
+__device__ __forceinline__ void put_chunk(uint32_t tile_hi, uint32_t tile_lo, uint32_t c, const uint32_t h0[2], const uint32_t h1[2],
+					  const uint32_t l0[2], const uint32_t l1[2])
 {
-	if (TM) {
-		ptx::tmem_st4(base_hi + 4 * c, h0[0], h0[1], h1[0], h1[1]);
-		ptx::tmem_st4(base_lo + 4 * c, l0[0], l0[1], l1[0], l1[1]);
-	} else {
-		const uint32_t off = (c ^ sw) << 4;
-		sts128(base_hi + off, h0[0], h0[1], h1[0], h1[1]);
-		sts128(base_lo + off, l0[0], l0[1], l1[0], l1[1]);
-	}
+	ptx::tmem_st4(tile_hi + 4 * c, h0[0], h0[1], h1[0], h1[1]);
+	ptx::tmem_st4(tile_lo + 4 * c, l0[0], l0[1], l1[0], l1[1]);
 }
 
 // Packed weights one producer thread needs for two consecutive k stages (128 k, "group" g) of
@@ -130,9 +130,8 @@ struct RawGroup<W_Q4K, NMAT> {
 			}
 		}
 	}
-	// writes this thread's chunks of stage (2g + st) into the hi/lo tiles (row base addresses given)
-	template <bool TM>
-	__device__ __forceinline__ void emit(int g, int st, int hs, uint32_t row_hi, uint32_t row_lo, uint32_t sw) const
+	// writes this thread's chunks of stage (2g + st) into the hi/lo tiles
+	__device__ __forceinline__ void emit(int g, int st, int hs, uint32_t tile_hi, uint32_t tile_lo) const
 	{
 		const int p = (g & 1) * 2 + st;
 		const float d = half_bits_to_float(hdr.x & 0xffffu), dmin = half_bits_to_float(hdr.x >> 16);
@@ -157,10 +156,10 @@ struct RawGroup<W_Q4K, NMAT> {
 			uint32_t h0[2], l0[2], h1[2], l1[2];
 			q4k_word(w[2 * cc], 0, cl, h0, l0);
 			q4k_word(w[2 * cc + 1], 0, cl, h1, l1);
-			put_chunk<TM>(row_hi, row_lo, sw, c0 + cc, h0, h1, l0, l1);
+			put_chunk(tile_hi, tile_lo, c0 + cc, h0, h1, l0, l1);
 			q4k_word(w[2 * cc], 4, ch, h0, l0);
 			q4k_word(w[2 * cc + 1], 4, ch, h1, l1);
-			put_chunk<TM>(row_hi, row_lo, sw, 4u + c0 + cc, h0, h1, l0, l1);
+			put_chunk(tile_hi, tile_lo, 4u + c0 + cc, h0, h1, l0, l1);
 		}
 	}
 };
@@ -187,8 +186,7 @@ struct RawGroup<W_Q6K_R8, NMAT> {
 		}
 		d = half_bits_to_float(__ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb, r8, kb))));
 	}
-	template <bool TM>
-	__device__ __forceinline__ void emit(int g, int st, int hs, uint32_t row_hi, uint32_t row_lo, uint32_t sw) const
+	__device__ __forceinline__ void emit(int g, int st, int hs, uint32_t tile_hi, uint32_t tile_lo) const
 	{
 #pragma unroll
 		for (int i = 0; i < NL; i++) {
@@ -216,16 +214,16 @@ struct RawGroup<W_Q6K_R8, NMAT> {
 				uint32_t h0[2], l0[2], h1[2], l1[2];
 				q6k_word(qa[2 * cc], sAh, sAr, h0, l0);
 				q6k_word(qa[2 * cc + 1], sAh, sAr, h1, l1);
-				put_chunk<TM>(row_hi, row_lo, sw, 2u * l16 + cc, h0, h1, l0, l1);
+				put_chunk(tile_hi, tile_lo, 2u * l16 + cc, h0, h1, l0, l1);
 				q6k_word(qb[2 * cc], sBh, sBr, h0, l0);
 				q6k_word(qb[2 * cc + 1], sBh, sBr, h1, l1);
-				put_chunk<TM>(row_hi, row_lo, sw, 4u + 2u * l16 + cc, h0, h1, l0, l1);
+				put_chunk(tile_hi, tile_lo, 4u + 2u * l16 + cc, h0, h1, l0, l1);
 			}
 		}
 	}
 };
 
-template <WKind KIND, int NMAT, int NT, bool TM>
+template <WKind KIND, int NMAT, int NT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__ CUtensorMap tm_lo,
 		const uint8_t *__restrict__ w0, const uint8_t *__restrict__ w1, size_t expert_stride, int k_dim,
@@ -233,8 +231,9 @@ grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 		__half *__restrict__ h_hi, __half *__restrict__ h_lo, float *__restrict__ y, const int *__restrict__ perm,
 		int out_stride, const float *__restrict__ silu, unsigned *__restrict__ status)
 {
-	using Cfg = TcCfg<NMAT, NT, TM>;
-	constexpr int S = Cfg::STAGES;
+	using Cfg = TcCfg<NMAT, NT>;
+	constexpr int S = Cfg::STAGES, SB = Cfg::SB;
+	constexpr bool CONCAT = Cfg::CONCAT;
 	extern __shared__ uint8_t smem_raw[];
 
 	// ---- which (expert, token tile) is this CTA? ----
@@ -245,7 +244,7 @@ grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 	__syncthreads();
 	if (s_skip)
 		return;
-	int lo_e = 0, hi_e = n_local - 1;  // largest le with tile_start[le] <= slot (and a non-empty tile range)
+	int lo_e = 0, hi_e = n_local - 1;  // largest le with tile_start[le] <= slot
 	while (lo_e < hi_e) {
 		int mid = (lo_e + hi_e + 1) >> 1;
 		if (tile_start[mid] <= slot)
@@ -261,39 +260,42 @@ grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 			atomicOr(status, ST_BAD_TILE);
 		return;
 	}
+	const int n_mma = (n_valid + 15) & ~15;	 // N of the MMAs: the tile's tokens rounded up to 16
 	const int m0 = blockIdx.x * TC_BM;
 	const int nb = k_dim / QK_K;
 	const int k_iters = k_dim / TC_BK;
 
 	const uint32_t raw = ptx::smem_u32(smem_raw);
 	const uint32_t tiles = (raw + 1023u) & ~1023u;
-	TcShared *sh = reinterpret_cast<TcShared *>(smem_raw + (tiles - raw) + (size_t)S * Cfg::STAGE);
+	TcShared *sh = reinterpret_cast<TcShared *>(smem_raw + (tiles - raw) + (size_t)SB * Cfg::B_STAGE);
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-	auto a_tile = [&](int s, int m, int hl) -> uint32_t { return tiles + s * Cfg::STAGE + (m * 2 + hl) * TC_A_TILE; };
-	auto b_tile = [&](int s, int hl) -> uint32_t {
-		return tiles + s * Cfg::STAGE + (TM ? 0 : NMAT * 2 * TC_A_TILE) + hl * Cfg::B_TILE;
-	};
-	// TMEM column of weight tile (stage, matrix, hi/lo) when the A operand lives in tensor memory
-	auto a_col = [&](int s, int m, int hl) -> uint32_t {
-		return Cfg::ACC_COLS + (s * NMAT * 2 + m * 2 + hl) * Cfg::A_COLS;
-	};
+	// token tiles of ring stage sb: hi at the start; lo right behind the rows in use when the two
+	// are stacked along N, else in the second half of the stage
+	auto b_hi = [&](int sb) -> uint32_t { return tiles + sb * Cfg::B_STAGE; };
+	auto b_lo = [&](int sb) -> uint32_t { return tiles + sb * Cfg::B_STAGE + (CONCAT ? n_mma * 128 : Cfg::B_TILE); };
+	// TMEM column of weight tile (stage, matrix, hi/lo)
+	auto a_col = [&](int s, int m, int hl) -> uint32_t { return Cfg::ACC_COLS + (s * NMAT * 2 + m * 2 + hl) * Cfg::A_COLS; };
 
 	if (threadIdx.x == 0) {
 		for (int s = 0; s < S; s++) {
-			ptx::mbar_init(ptx::smem_u32(&sh->full[s]), TC_PRODUCERS + 1);
-			ptx::mbar_init(ptx::smem_u32(&sh->empty[s]), 1);
+			ptx::mbar_init(ptx::smem_u32(&sh->full[s]), TC_PWARPS);
+			ptx::mbar_init(ptx::smem_u32(&sh->empty[s]), NMAT);
 		}
-		ptx::mbar_init(ptx::smem_u32(&sh->done), 1);
+		for (int s = 0; s < SB; s++) {
+			ptx::mbar_init(ptx::smem_u32(&sh->bfull[s]), 1);
+			ptx::mbar_init(ptx::smem_u32(&sh->bempty[s]), NMAT);
+		}
+		ptx::mbar_init(ptx::smem_u32(&sh->done), NMAT);
 		sh->abort = 0;
 		ptx::fence_barrier_init();
 		ptx::fence_proxy_async_smem();
 	}
-	if (warp == TC_PRODUCERS / 32) {  // MMA warp owns the tensor-memory allocation
+	if (warp == TC_PWARPS) {  // first MMA warp owns the tensor-memory allocation
 		ptx::tmem_alloc(ptx::smem_u32(&sh->tmem_base), Cfg::TMEM_COLS);
 		ptx::tmem_relinquish();
 	}
-	if (warp == TC_PRODUCERS / 32 + 1 && lane == 0) {
+	if (warp == TC_PWARPS + 2 && lane == 0) {
 		ptx::prefetch_tmap(&tm_hi);
 		ptx::prefetch_tmap(&tm_lo);
 	}
@@ -303,15 +305,13 @@ grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 	const uint32_t tmem = sh->tmem_base;
 	volatile uint32_t *abort_flag = &sh->abort;
 
-	if (warp < TC_PRODUCERS / 32) {
-		// ================= producers: dequantise A tiles =================
-		// thread = (row, matrix) for gate/up, (row, half-slice) for down; the packed bytes of the
-		// next 128-k group are fetched into registers while the current group is expanded
+	if (warp < TC_PWARPS) {
+		// ================= producers: packed blocks -> hi/lo weight tiles in tensor memory =================
+		// thread = (row, matrix) for gate/up, (row, half-slice) for down
 		const int row = threadIdx.x & 127, sel = threadIdx.x >> 7;
 		const int m = (NMAT == 2) ? sel : 0, hs = (NMAT == 2) ? 0 : sel;
 		const uint8_t *wexp = ((NMAT == 2 && sel) ? w1 : w0) + (size_t)le * expert_stride;
-		const uint32_t row_off = row * 128;
-		const uint32_t sw = row & 7;
+		const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
 		const int n_groups = k_iters >> 1;
 		RawGroup<KIND, NMAT> cur, nxt;
 		cur.load(wexp, nb, m0 + row, 0, hs);
@@ -323,78 +323,82 @@ grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 			for (int st = 0; st < 2; st++) {
 				const int it = 2 * g + st;
 				const int s = it % S;
-				if (it >= S && !tc_wait(ptx::smem_u32(&sh->empty[s]), ((it / S) & 1) ^ 1, abort_flag, status)) {
-					alive = false;
-					break;
+				if (it >= S) {	// one lane polls the barrier for its warp
+					int ok = 1;
+					if (lane == 0)
+						ok = tc_wait(ptx::smem_u32(&sh->empty[s]), ((it / S) & 1) ^ 1, abort_flag, status) ? 1 : 0;
+					ok = __shfl_sync(0xffffffffu, ok, 0);
+					if (!ok) {
+						alive = false;
+						break;
+					}
+					ptx::tc_fence_after();
 				}
-				if (TM) {
-					const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-					cur.template emit<true>(g, st, hs, lane_base + a_col(s, m, 0), lane_base + a_col(s, m, 1), 0);
-					ptx::tmem_st_wait();
-					ptx::tc_fence_before();
-				} else {
-					cur.template emit<false>(g, st, hs, a_tile(s, m, 0) + row_off, a_tile(s, m, 1) + row_off, sw);
-					ptx::fence_proxy_async_smem();
-				}
-				ptx::mbar_arrive(ptx::smem_u32(&sh->full[s]));
+				cur.emit(g, st, hs, lane_base + a_col(s, m, 0), lane_base + a_col(s, m, 1));
+				ptx::tmem_st_wait();
+				ptx::tc_fence_before();
+				__syncwarp();
+				if (lane == 0)	// one arrival per producer warp
+					ptx::mbar_arrive(ptx::smem_u32(&sh->full[s]));
 			}
 			cur = nxt;
 		}
-	} else if (warp == TC_PRODUCERS / 32) {
-		// ================= MMA issuer =================
+	} else if (warp < TC_PWARPS + NMAT) {
+		// ================= MMA issuers: one thread per weight matrix =================
 		if (lane == 0) {
-			// the MMA's N is the expert's token count in this tile rounded up to 16 (a runtime field)
-			const uint32_t idesc = ptx::umma_idesc_f16(TC_BM, min(NT, (n_valid + 15) & ~15));
-			bool ok = true;
-			for (int it = 0; it < k_iters && ok; it++) {
-				const int s = it % S;
-				ok = tc_wait(ptx::smem_u32(&sh->full[s]), (it / S) & 1, abort_flag, status);
-				if (!ok)
+			const int m = warp - TC_PWARPS;
+			const uint32_t d = tmem + m * Cfg::ACC_PER_MAT;
+			const uint32_t idesc_n = ptx::umma_idesc_f16(TC_BM, n_mma);
+			const uint32_t idesc_2n = ptx::umma_idesc_f16(TC_BM, 2 * n_mma);
+			for (int it = 0; it < k_iters; it++) {
+				const int s = it % S, sb = it % SB;
+				if (!tc_wait(ptx::smem_u32(&sh->bfull[sb]), (it / SB) & 1, abort_flag, status))
+					break;
+				if (!tc_wait(ptx::smem_u32(&sh->full[s]), (it / S) & 1, abort_flag, status))
 					break;
 				ptx::tc_fence_after();
 #pragma unroll
 				for (int kk = 0; kk < TC_BK / 16; kk++) {
-					const uint64_t bh = ptx::umma_desc_sw128(b_tile(s, 0)) + 2 * kk;
-					const uint64_t bl = ptx::umma_desc_sw128(b_tile(s, 1)) + 2 * kk;
-#pragma unroll
-					for (int m = 0; m < NMAT; m++) {
-						const uint32_t d = tmem + m * NT;
-						const uint32_t acc = (it > 0 || kk > 0) ? 1u : 0u;
-						if (TM) {
-							const uint32_t ah = tmem + a_col(s, m, 0) + 8 * kk, al = tmem + a_col(s, m, 1) + 8 * kk;
-							ptx::mma_f16_ts(d, ah, bh, idesc, acc);
-							ptx::mma_f16_ts(d, al, bh, idesc, 1u);
-							ptx::mma_f16_ts(d, ah, bl, idesc, 1u);
-						} else {
-							const uint64_t ahd = ptx::umma_desc_sw128(a_tile(s, m, 0)) + 2 * kk;
-							const uint64_t ald = ptx::umma_desc_sw128(a_tile(s, m, 1)) + 2 * kk;
-							ptx::mma_f16_ss(d, ahd, bh, idesc, acc);
-							ptx::mma_f16_ss(d, ald, bh, idesc, 1u);
-							ptx::mma_f16_ss(d, ahd, bl, idesc, 1u);
-						}
+					const uint64_t bh = ptx::umma_desc_sw128(b_hi(sb)) + 2 * kk;
+					const uint32_t ah = tmem + a_col(s, m, 0) + 8 * kk, al = tmem + a_col(s, m, 1) + 8 * kk;
+					const uint32_t acc = (it > 0 || kk > 0) ? 1u : 0u;
+					if (CONCAT) {
+						// columns [0, n): A_hi.B_hi + A_lo.B_hi; columns [n, 2n): A_hi.B_lo
+						ptx::mma_f16_ts(d, ah, bh, idesc_2n, acc);
+						ptx::mma_f16_ts(d, al, bh, idesc_n, 1u);
+					} else {
+						const uint64_t bl = ptx::umma_desc_sw128(b_lo(sb)) + 2 * kk;
+						ptx::mma_f16_ts(d, ah, bh, idesc_n, acc);
+						ptx::mma_f16_ts(d, al, bh, idesc_n, 1u);
+						ptx::mma_f16_ts(d, ah, bl, idesc_n, 1u);
 					}
 				}
 				ptx::mma_commit(ptx::smem_u32(&sh->empty[s]));
+				ptx::mma_commit(ptx::smem_u32(&sh->bempty[sb]));
 			}
 			ptx::mma_commit(ptx::smem_u32(&sh->done));
 		}
-	} else {
+	} else if (warp == TC_PWARPS + 2) {
 		// ================= TMA loader for the token operand =================
 		if (lane == 0) {
+			const int n16 = n_mma >> 4;
 			for (int it = 0; it < k_iters; it++) {
-				const int s = it % S;
-				if (it >= S && !tc_wait(ptx::smem_u32(&sh->empty[s]), ((it / S) & 1) ^ 1, abort_flag, status))
+				const int sb = it % SB;
+				if (it >= SB && !tc_wait(ptx::smem_u32(&sh->bempty[sb]), ((it / SB) & 1) ^ 1, abort_flag, status))
 					break;
-				const uint32_t fb = ptx::smem_u32(&sh->full[s]);
-				ptx::mbar_arrive_expect_tx(fb, 2 * Cfg::B_TILE);
-				ptx::tma_load_2d(b_tile(s, 0), &tm_hi, fb, it * TC_BK, row0);
-				ptx::tma_load_2d(b_tile(s, 1), &tm_lo, fb, it * TC_BK, row0);
+				const uint32_t fb = ptx::smem_u32(&sh->bfull[sb]);
+				// only the rows the MMA will read: 16-row boxes (2 KB each, whole swizzle groups)
+				ptx::mbar_arrive_expect_tx(fb, (uint32_t)n16 * 2u * 16u * TC_BK * 2u);
+				for (int r = 0; r < n16; r++) {
+					ptx::tma_load_2d(b_hi(sb) + r * 2048, &tm_hi, fb, it * TC_BK, row0 + 16 * r);
+					ptx::tma_load_2d(b_lo(sb) + r * 2048, &tm_lo, fb, it * TC_BK, row0 + 16 * r);
+				}
 			}
 		}
 	}
 
 	// ================= epilogue: 8 warps, TMEM lane quadrant = warp % 4, columns split in two =================
-	if (warp < TC_PRODUCERS / 32) {
+	if (warp < TC_PWARPS) {
 		const bool ok = tc_wait(ptx::smem_u32(&sh->done), 0, abort_flag, status);
 		ptx::tc_fence_after();
 		if (ok) {
@@ -407,8 +411,22 @@ grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 				uint32_t g[16], u[16];
 				ptx::tmem_ld16(tlane + c0, g);
 				if (NMAT == 2)
-					ptx::tmem_ld16(tlane + NT + c0, u);
-				ptx::tmem_ld_wait();
+					ptx::tmem_ld16(tlane + Cfg::ACC_PER_MAT + c0, u);
+				if (CONCAT) {
+					uint32_t g2[16], u2[16];
+					ptx::tmem_ld16(tlane + n_mma + c0, g2);
+					if (NMAT == 2)
+						ptx::tmem_ld16(tlane + Cfg::ACC_PER_MAT + n_mma + c0, u2);
+					ptx::tmem_ld_wait();
+#pragma unroll
+					for (int j = 0; j < 16; j++) {
+						g[j] = __float_as_uint(__uint_as_float(g[j]) + __uint_as_float(g2[j]));
+						if (NMAT == 2)
+							u[j] = __float_as_uint(__uint_as_float(u[j]) + __uint_as_float(u2[j]));
+					}
+				} else {
+					ptx::tmem_ld_wait();
+				}
 #pragma unroll
 				for (int j = 0; j < 16; j++) {
 					const int n = c0 + j;
@@ -436,7 +454,7 @@ grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 	}
 	ptx::tc_fence_before();
 	__syncthreads();
-	if (warp == TC_PRODUCERS / 32)
+	if (warp == TC_PWARPS)
 		ptx::tmem_dealloc(tmem, Cfg::TMEM_COLS);
 }
 
@@ -459,8 +477,8 @@ static PFN_encodeTiled get_encode_fn()
 	return fn;
 }
 
-// fp16 [rows][cols] row-major, box = 64 columns x box_rows rows, 128-byte swizzle.
-static int make_tmap(tie_cuda_ctx *c, CUtensorMap *tm, void *base, size_t rows, size_t cols, int box_rows)
+// fp16 [rows][cols] row-major, box = 64 columns x 16 rows, 128-byte swizzle.
+static int make_tmap(tie_cuda_ctx *c, CUtensorMap *tm, void *base, size_t rows, size_t cols)
 {
 	PFN_encodeTiled enc = get_encode_fn();
 	if (!enc) {
@@ -469,7 +487,7 @@ static int make_tmap(tie_cuda_ctx *c, CUtensorMap *tm, void *base, size_t rows, 
 	}
 	cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
 	cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-	cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+	cuuint32_t box[2] = {(cuuint32_t)TC_BK, 16u};
 	cuuint32_t estr[2] = {1, 1};
 	CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
 			 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -485,18 +503,14 @@ int tc_setup(tie_cuda_ctx *c)
 	Scratch &s = c->s;
 	void *bases[4] = {s.xs_hi, s.xs_lo, s.hs_hi, s.hs_lo};
 	size_t cols[4] = {(size_t)c->cfg.hidden, (size_t)c->cfg.hidden, (size_t)c->cfg.ffn_dim, (size_t)c->cfg.ffn_dim};
-	const int nts[2] = {64, 128};
-	for (int a = 0; a < 4; a++)
-		for (int n = 0; n < 2; n++) {
-			int rc = make_tmap(c, &c->tmap[a][n], bases[a], s.rows_pad, cols[a], nts[n]);
-			if (rc)
-				return rc;
-		}
-#define TC_ATTR(KIND, NMAT, NT)                                                                                                   \
-	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_tc<KIND, NMAT, NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-					     TcCfg<NMAT, NT, false>::SMEM));                                                      \
-	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_tc<KIND, NMAT, NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
-					     TcCfg<NMAT, NT, true>::SMEM))
+	for (int a = 0; a < 4; a++) {
+		int rc = make_tmap(c, &c->tmap[a], bases[a], s.rows_pad, cols[a]);
+		if (rc)
+			return rc;
+	}
+#define TC_ATTR(KIND, NMAT, NT)                                                                                            \
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_tc<KIND, NMAT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+					     TcCfg<NMAT, NT>::SMEM))
 	TC_ATTR(W_Q4K, 1, 64);
 	TC_ATTR(W_Q4K, 1, 128);
 	TC_ATTR(W_Q4K, 2, 64);
@@ -517,14 +531,9 @@ static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1
 	Scratch &s = c->s;
 	const int max_tiles = min(c->n_local, n_rows) + n_rows / NT;
 	dim3 grid(t0.rows / TC_BM, max_tiles);
-	if (c->tc_a_in_tmem)
-		grouped_gemm_tc<KIND, NMAT, NT, true><<<grid, TC_THREADS, TcCfg<NMAT, NT, true>::SMEM, c->stream>>>(
-			tmh, tml, t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride, t0.k, s.offsets, s.tile_start, c->n_local, s.hs_hi,
-			s.hs_lo, y, s.perm, t0.rows, c->silu, s.status);
-	else
-		grouped_gemm_tc<KIND, NMAT, NT, false><<<grid, TC_THREADS, TcCfg<NMAT, NT, false>::SMEM, c->stream>>>(
-			tmh, tml, t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride, t0.k, s.offsets, s.tile_start, c->n_local, s.hs_hi,
-			s.hs_lo, y, s.perm, t0.rows, c->silu, s.status);
+	grouped_gemm_tc<KIND, NMAT, NT><<<grid, TC_THREADS, TcCfg<NMAT, NT>::SMEM, c->stream>>>(
+		tmh, tml, t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride, t0.k, s.offsets, s.tile_start, c->n_local, s.hs_hi, s.hs_lo,
+		y, s.perm, t0.rows, c->silu, s.status);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
@@ -532,8 +541,7 @@ static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1
 template <int NMAT>
 static int launch_tc_n(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1, int arr, int n_tile, int n_rows, float *y)
 {
-	const int ni = (n_tile == 64) ? 0 : 1;
-	const CUtensorMap &tmh = c->tmap[arr][ni], &tml = c->tmap[arr + 1][ni];
+	const CUtensorMap &tmh = c->tmap[arr], &tml = c->tmap[arr + 1];
 	if (t0.kind == W_Q4K) {
 		if (n_tile == 64)
 			return launch_tc_t<W_Q4K, NMAT, 64>(c, t0, t1, tmh, tml, n_rows, y);
