@@ -51,6 +51,7 @@ extern "C" {
 #define TIE_CUDA_PATH_STREAM (1u << 8) /* CUDA-core streaming kernels (decode / small batches) */
 #define TIE_CUDA_PATH_TENSOR (2u << 8) /* tcgen05 grouped GEMM (prefill) */
 #define TIE_CUDA_PATH_MASK (3u << 8)
+#define TIE_CUDA_PATH_LEGACY_STREAM (1u << 10) /* with PATH_STREAM: use the general streaming kernels even for 1-4 tokens */
 
 typedef struct tie_cuda_ctx tie_cuda_ctx;
 

@@ -95,6 +95,18 @@ def test_decode1_matches_reference_golden(be, golden):
     assert be.last_active_experts() == 8
 
 
+@pytest.mark.parametrize("n_tokens", [2, 3, 4, 5])
+def test_few_tokens_decode_kernels_and_general_streaming_kernels(be, port0, n_tokens):
+    """1-4 tokens take the bulk-staged decode kernels; the same inputs through the general
+    streaming kernels and through 5 tokens (first size past the decode path) must agree too."""
+    from tie_b200 import moe
+    x = synth.make_x(0, n_tokens, first_token=40)
+    ref_out, _, _ = port0.moe_ffn(x)
+    e = _check_ffn(be.moe_ffn(0, x), ref_out)
+    assert e < 1e-5
+    _check_ffn(be.moe_ffn(0, x, path=moe.PATH_STREAM | moe.PATH_LEGACY_STREAM), ref_out, tol=1e-5)
+
+
 @pytest.mark.parametrize("path", ["stream", "tensor"])
 def test_batch64_uniform_and_skewed(be, golden, port0, path):
     from tie_b200 import moe

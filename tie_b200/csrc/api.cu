@@ -62,6 +62,8 @@ int alloc_scratch(tie_cuda_ctx *c)
 	TRY(dev_alloc(c, &s.hs_hi, s.rows_pad * F));
 	TRY(dev_alloc(c, &s.hs_lo, s.rows_pad * F));
 	TRY(dev_alloc(c, &s.status, 1));
+	TRY(dev_alloc(c, &s.counter, 1));
+	TIE_CUDA_TRY(c, cudaMemset(s.counter, 0, sizeof(int)));
 	TRY(dev_alloc(c, &s.row_expert, R));
 	TRY(dev_alloc(c, &s.ep_counts, E));
 	TRY(dev_alloc(c, &s.ep_offsets, E + 1));
@@ -239,6 +241,22 @@ int moe_ffn_device(tie_cuda_ctx *c, Layer &L, const float *x, float *out, int n_
 {
 	Scratch &s = c->s;
 	prof_mark(c, 0);
+	// decode (1-4 tokens): three launches — router with fused selection, gate/up, down + combine
+	if ((flags & TIE_CUDA_PATH_MASK) != TIE_CUDA_PATH_TENSOR && !(flags & TIE_CUDA_PATH_LEGACY_STREAM) &&
+	    decode_supported(c, L, n_tokens)) {
+		TRY(launch_router_decode_fused(c, x, L.router_w, bias_dev, n_tokens, s.logits, s.topk_idx, s.topk_w));
+		prof_mark(c, 1);
+		c->last_used_tc = false;
+		c->last_direct_rows = n_tokens * c->cfg.top_k;
+		prof_mark(c, 2);
+		prof_mark(c, 3);
+		TRY(launch_decode_gate_up(c, L, x, n_tokens));
+		prof_mark(c, 4);
+		TRY(launch_decode_down_combine(c, L, n_tokens, residual, out));
+		prof_mark(c, 5);
+		prof_mark(c, 6);
+		return TIE_CUDA_OK;
+	}
 	TRY(launch_router(c, x, L.router_w, bias_dev, n_tokens, s.logits, s.topk_idx, s.topk_w));
 	prof_mark(c, 1);
 	TRY(run_experts(c, L, x, c->cfg.top_k, s.topk_idx, n_tokens * c->cfg.top_k, s.y, flags));
@@ -470,7 +488,7 @@ void tie_cuda_destroy(tie_cuda_ctx *c)
 	}
 	Scratch &s = c->s;
 	void *dev_ptrs[] = {s.x,     s.out,   s.logits, s.bias,  s.topk_idx, s.topk_w, s.counts, s.offsets, s.tile_start, s.active, s.n_active,
-			    s.perm,  s.h,     s.y,	s.xs_hi, s.xs_lo,    s.hs_hi,  s.hs_lo,  s.status,  s.row_expert, c->silu,  c->row_x,
+			    s.perm,  s.h,     s.y,	s.xs_hi, s.xs_lo,    s.hs_hi,  s.hs_lo,  s.status,  s.counter, s.row_expert, c->silu,  c->row_x,
 			    c->row_o, s.ep_counts, s.ep_offsets, s.ep_tile_start, s.ep_active, s.ep_n_active, s.ep_perm, s.ep_inv};
 	for (void *p : dev_ptrs)
 		if (p)

@@ -66,6 +66,7 @@ struct Scratch {
 	__half *xs_hi = nullptr, *xs_lo = nullptr;  // [Rpad][H]  split inputs, sorted order
 	__half *hs_hi = nullptr, *hs_lo = nullptr;  // [Rpad][F]
 	unsigned *status = nullptr;		    // [1]
+	int *counter = nullptr;			    // [1] last-CTA counter of the fused decode router (zero at rest)
 	int *row_expert = nullptr;		    // [R] staging for expert_rows
 	// expert-parallel dispatch state (sort of this rank's rows over ALL experts)
 	int *ep_counts = nullptr, *ep_offsets = nullptr, *ep_tile_start = nullptr, *ep_active = nullptr, *ep_n_active = nullptr;
@@ -123,7 +124,7 @@ struct tie_cuda_ctx {
 		cudaGraphExec_t exec;
 		uint64_t kernels;  // kernel launches recorded in the graph
 		uint64_t stamp;
-	} graphs[32];
+	} graphs[256];
 	int n_graphs = 0;
 	uint64_t graph_clock = 0;
 	// small per-call device buffers for the dispatch rows

@@ -8,6 +8,12 @@ namespace tie {
 int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *bias, int n_tokens, float *logits,
 		  int *topk_idx, float *topk_w);
 int router_setup(tie_cuda_ctx *c);
+int launch_router_decode_fused(tie_cuda_ctx *c, const float *x, const float *w, const float *bias, int n_tokens, float *logits,
+			       int *topk_idx, float *topk_w);
+// decode.cu
+bool decode_supported(const tie_cuda_ctx *c, const Layer &L, int n_tokens);
+int launch_decode_gate_up(tie_cuda_ctx *c, const Layer &L, const float *x, int n_tokens);
+int launch_decode_down_combine(tie_cuda_ctx *c, const Layer &L, int n_tokens, const float *residual, float *out);
 int launch_router_rows(tie_cuda_ctx *c, const float *x, const float *w, int n_rows, int in_dim, float *out);
 // sort.cu
 struct SortBufs {

@@ -67,6 +67,109 @@ __global__ void __launch_bounds__(EPC * 8) router_logits_tile(const float *__res
 	}
 }
 
+// Batched token counts: CTA = 16 tokens x 32 experts, thread = 2 tokens x 2 experts x all 8 lanes
+// (32 independent chains, each still a strict i-ascending sequence of fused multiply-adds, so
+// the result stays bit-identical).  Operands are staged in shared memory by cp.async in
+// 128-float k chunks (a 4-deep ring) and read as 128-bit words that most lanes of a warp
+// share, so every loaded float feeds 2 multiply-adds per thread from registers.
+constexpr int RMT_TT = 16, RMT_TE = 32, RMT_KC = 128, RMT_PITCH = RMT_KC + 4, RMT_THREADS = 128;
+constexpr int RMT_STAGES = 4;
+constexpr int RMT_SMEM = RMT_STAGES * (RMT_TT + RMT_TE) * RMT_PITCH * (int)sizeof(float);
+
+__global__ void __launch_bounds__(RMT_THREADS) router_logits_mt(const float *__restrict__ x, const float *__restrict__ w,
+							       const float *__restrict__ bias, float *__restrict__ logits,
+							       int n_tokens, int hidden, int n_expert)
+{
+	extern __shared__ __align__(16) float rsm[];
+	const int t0 = blockIdx.x * RMT_TT, e0 = blockIdx.y * RMT_TE;
+	const int tp = threadIdx.x & 7, ep = threadIdx.x >> 3;	// tokens (tp, tp+8), experts (ep, ep+16)
+	auto stage = [&](int buf, int k0) {
+		float *xs = rsm + buf * (RMT_TT + RMT_TE) * RMT_PITCH;
+		float *ws = xs + RMT_TT * RMT_PITCH;
+		for (int i = threadIdx.x; i < (RMT_TT + RMT_TE) * (RMT_KC / 4); i += RMT_THREADS) {
+			const int r = i / (RMT_KC / 4), c4 = i % (RMT_KC / 4);
+			const float *src;
+			float *dst;
+			if (r < RMT_TT) {
+				const int t = min(t0 + r, n_tokens - 1);  // rows past the end are computed and dropped
+				src = x + (size_t)t * hidden + k0 + 4 * c4;
+				dst = xs + r * RMT_PITCH + 4 * c4;
+			} else {
+				src = w + (size_t)(e0 + r - RMT_TT) * hidden + k0 + 4 * c4;
+				dst = ws + (r - RMT_TT) * RMT_PITCH + 4 * c4;
+			}
+			asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
+				     : "memory");
+		}
+		asm volatile("cp.async.commit_group;" ::: "memory");
+	};
+	float acc[2][2][8];
+#pragma unroll
+	for (int a = 0; a < 2; a++)
+#pragma unroll
+		for (int b = 0; b < 2; b++)
+#pragma unroll
+			for (int l = 0; l < 8; l++)
+				acc[a][b][l] = 0.0f;
+	const int n_chunks = hidden / RMT_KC;
+#pragma unroll
+	for (int c = 0; c < RMT_STAGES - 1; c++) {
+		if (c < n_chunks)
+			stage(c, c * RMT_KC);
+		else
+			asm volatile("cp.async.commit_group;" ::: "memory");
+	}
+	for (int c = 0; c < n_chunks; c++) {
+		if (c + RMT_STAGES - 1 < n_chunks)
+			stage((c + RMT_STAGES - 1) % RMT_STAGES, (c + RMT_STAGES - 1) * RMT_KC);
+		else
+			asm volatile("cp.async.commit_group;" ::: "memory");
+		asm volatile("cp.async.wait_group %0;" ::"n"(RMT_STAGES - 1) : "memory");
+		__syncthreads();
+		const float *xs = rsm + (c % RMT_STAGES) * (RMT_TT + RMT_TE) * RMT_PITCH;
+		const float *ws = xs + RMT_TT * RMT_PITCH;
+		// rows (tp, tp+8) and (ep, ep+16): the 4-float row skew then spreads a warp's reads over all banks
+		const float *x0 = xs + tp * RMT_PITCH, *x1 = x0 + 8 * RMT_PITCH;
+		const float *w0 = ws + ep * RMT_PITCH, *w1 = w0 + 16 * RMT_PITCH;
+#pragma unroll 4
+		for (int i = 0; i < RMT_KC / 8; i++) {
+			float xv[2][8], wv[2][8];
+			*reinterpret_cast<float4 *>(&xv[0][0]) = *reinterpret_cast<const float4 *>(x0 + 8 * i);
+			*reinterpret_cast<float4 *>(&xv[0][4]) = *reinterpret_cast<const float4 *>(x0 + 8 * i + 4);
+			*reinterpret_cast<float4 *>(&xv[1][0]) = *reinterpret_cast<const float4 *>(x1 + 8 * i);
+			*reinterpret_cast<float4 *>(&xv[1][4]) = *reinterpret_cast<const float4 *>(x1 + 8 * i + 4);
+			*reinterpret_cast<float4 *>(&wv[0][0]) = *reinterpret_cast<const float4 *>(w0 + 8 * i);
+			*reinterpret_cast<float4 *>(&wv[0][4]) = *reinterpret_cast<const float4 *>(w0 + 8 * i + 4);
+			*reinterpret_cast<float4 *>(&wv[1][0]) = *reinterpret_cast<const float4 *>(w1 + 8 * i);
+			*reinterpret_cast<float4 *>(&wv[1][4]) = *reinterpret_cast<const float4 *>(w1 + 8 * i + 4);
+#pragma unroll
+			for (int a = 0; a < 2; a++)
+#pragma unroll
+				for (int b = 0; b < 2; b++)
+#pragma unroll
+					for (int l = 0; l < 8; l++)
+						acc[a][b][l] = __fmaf_rn(xv[a][l], wv[b][l], acc[a][b][l]);
+		}
+		__syncthreads();
+	}
+#pragma unroll
+	for (int a = 0; a < 2; a++) {
+		const int t = t0 + tp + 8 * a;
+#pragma unroll
+		for (int b = 0; b < 2; b++) {
+			const int e = e0 + ep + 16 * b;
+			const float *l = acc[a][b];
+			// hsum (math_avx2.c:14-21): ((l0+l4)+(l1+l5)) + ((l2+l6)+(l3+l7))
+			float r = __fadd_rn(__fadd_rn(__fadd_rn(l[0], l[4]), __fadd_rn(l[1], l[5])),
+					    __fadd_rn(__fadd_rn(l[2], l[6]), __fadd_rn(l[3], l[7])));
+			if (bias)
+				r = __fadd_rn(r, bias[e]);
+			if (t < n_tokens)
+				logits[(size_t)t * n_expert + e] = r;
+		}
+	}
+}
+
 // Decode-sized token counts (<= 8 tokens): one expert per CTA so the 1 MB of router weights is
 // pulled by many SMs at once; the row and the tokens are staged in shared memory with wide
 // loads, then thread (token, lane) runs the sequential chain.
@@ -107,21 +210,17 @@ __global__ void __launch_bounds__(64) router_logits_decode(const float *__restri
 
 // One warp per token: k rounds of warp arg-max with key (score desc, index asc), then the
 // softmax of the selected scores: max-subtract, expf, sequential sum, multiply by 1/sum.
-__global__ void __launch_bounds__(128) router_topk(const float *__restrict__ logits, int n_tokens, int n_expert, int top_k,
-						   int *__restrict__ topk_idx, float *__restrict__ topk_w)
+__device__ __forceinline__ void topk_softmax_warp(const float *__restrict__ logits, int token, int lane, int n_expert, int top_k,
+						  int *__restrict__ topk_idx, float *__restrict__ topk_w)
 {
-	const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-	const int lane = threadIdx.x & 31;
-	if (warp >= n_tokens)
-		return;
-	const float *lg = logits + (size_t)warp * n_expert;
+	const float *lg = logits + (size_t)token * n_expert;
 	// lane holds experts lane, lane+32, ... (up to 8 per lane: n_expert <= 256)
 	float v[8];
 	const int per = (n_expert + 31) / 32;
 #pragma unroll
 	for (int i = 0; i < 8; i++) {
 		int e = lane + 32 * i;
-		v[i] = (i < per && e < n_expert) ? lg[e] : -INFINITY;
+		v[i] = (i < per && e < n_expert) ? __ldcg(lg + e) : -INFINITY;
 	}
 	unsigned taken = 0;
 	float my_score = 0.0f;
@@ -164,9 +263,99 @@ __global__ void __launch_bounds__(128) router_topk(const float *__restrict__ log
 		sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, ex, j));
 	float inv = __fdiv_rn(1.0f, sum);
 	if (lane < top_k) {
-		topk_idx[(size_t)warp * top_k + lane] = my_idx;
-		topk_w[(size_t)warp * top_k + lane] = __fmul_rn(ex, inv);
+		topk_idx[(size_t)token * top_k + lane] = my_idx;
+		topk_w[(size_t)token * top_k + lane] = __fmul_rn(ex, inv);
 	}
+}
+
+__global__ void __launch_bounds__(128) router_topk(const float *__restrict__ logits, int n_tokens, int n_expert, int top_k,
+						   int *__restrict__ topk_idx, float *__restrict__ topk_w)
+{
+	const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+	const int lane = threadIdx.x & 31;
+	if (warp >= n_tokens)
+		return;
+	topk_softmax_warp(logits, warp, lane, n_expert, top_k, topk_idx, topk_w);
+}
+
+// Decode: logits as in router_logits_decode, and the CTA that finishes last (a counter, no
+// waiting) runs the selection for all tokens, saving a launch on the latency-bound path.
+__global__ void __launch_bounds__(256) router_decode_fused(const float *__restrict__ x, const float *__restrict__ w,
+							   const float *__restrict__ bias, float *__restrict__ logits, int n_tokens,
+							   int hidden, int n_expert, int top_k, int *__restrict__ topk_idx,
+							   float *__restrict__ topk_w, int *__restrict__ counter)
+{
+	extern __shared__ float sm[];
+	__shared__ int s_last;
+	float *ws = sm;
+	float *xs = sm + hidden;
+	const int xstride = hidden + 8;
+	const int e = blockIdx.x;
+	// let a dependent-launched successor (the decode gate/up kernel) become resident now; it waits
+	// for this grid's results itself.  The wait below covers a predecessor that was itself
+	// launched the same way.
+	asm volatile("griddepcontrol.wait;" ::: "memory");
+	asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+	// all loads of the staging are issued before the first store (at most 8 wide loads per thread)
+	{
+		const float4 *wr4 = reinterpret_cast<const float4 *>(w + (size_t)e * hidden);
+		const int nw = hidden / 4, nx = n_tokens * (hidden / 4);
+		float4 v[8];
+#pragma unroll
+		for (int j = 0; j < 8; j++) {
+			const int i = threadIdx.x + 256 * j;
+			if (i < nw)
+				v[j] = __ldg(wr4 + i);
+			else if (i - nw < nx && i >= nw)
+				v[j] = __ldg(reinterpret_cast<const float4 *>(x) + (i - nw));
+		}
+#pragma unroll
+		for (int j = 0; j < 8; j++) {
+			const int i = threadIdx.x + 256 * j;
+			if (i < nw) {
+				reinterpret_cast<float4 *>(ws)[i] = v[j];
+			} else if (i - nw < nx) {
+				const int k = i - nw, tt = k / (hidden / 4), c4 = k % (hidden / 4);
+				*reinterpret_cast<float4 *>(xs + (size_t)tt * xstride + 4 * c4) = v[j];
+			}
+		}
+		for (int i = threadIdx.x + 2048; i < nw + nx; i += 256) {  // sizes beyond 8 loads per thread
+			if (i < nw) {
+				reinterpret_cast<float4 *>(ws)[i] = __ldg(wr4 + i);
+			} else {
+				const int k = i - nw, tt = k / (hidden / 4), c4 = k % (hidden / 4);
+				*reinterpret_cast<float4 *>(xs + (size_t)tt * xstride + 4 * c4) = __ldg(reinterpret_cast<const float4 *>(x) + k);
+			}
+		}
+	}
+	__syncthreads();
+	const int tt = threadIdx.x >> 3, l = threadIdx.x & 7;
+	float acc = 0.0f;
+	if (tt < n_tokens) {
+		const float *xr = xs + (size_t)tt * xstride;
+#pragma unroll 16
+		for (int i = 0; i < hidden / 8; i++)
+			acc = __fmaf_rn(xr[8 * i + l], ws[8 * i + l], acc);
+	}
+	float r = hsum8_lanes(acc);
+	if (l == 0 && tt < n_tokens) {
+		if (bias)
+			r = __fadd_rn(r, bias[e]);
+		__stcg(&logits[(size_t)tt * n_expert + e], r);
+	}
+	__threadfence();
+	__syncthreads();
+	if (threadIdx.x == 0)
+		s_last = (atomicAdd(counter, 1) == (int)gridDim.x - 1);
+	__syncthreads();
+	if (!s_last)
+		return;
+	__threadfence();
+	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+	for (int t = warp; t < n_tokens; t += 8)
+		topk_softmax_warp(logits, t, lane, n_expert, top_k, topk_idx, topk_w);
+	if (threadIdx.x == 0)
+		*counter = 0;
 }
 
 int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *bias, int n_tokens, float *logits,
@@ -176,6 +365,10 @@ int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *
 	if (n_tokens <= 8) {
 		size_t smem = ((size_t)H + (size_t)n_tokens * (H + 8)) * sizeof(float);
 		router_logits_decode<8><<<E, 64, smem, c->stream>>>(x, w, bias, logits, n_tokens, H, E);
+		TIE_CUDA_LAUNCHED(c);
+	} else if (E % RMT_TE == 0 && H % RMT_KC == 0) {
+		dim3 grid((n_tokens + RMT_TT - 1) / RMT_TT, E / RMT_TE);
+		router_logits_mt<<<grid, RMT_THREADS, RMT_SMEM, c->stream>>>(x, w, bias, logits, n_tokens, H, E);
 		TIE_CUDA_LAUNCHED(c);
 	} else if (n_tokens <= 512) {
 		constexpr int TT = 8, EPC = 16;
@@ -195,10 +388,22 @@ int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *
 	return TIE_CUDA_OK;
 }
 
+int launch_router_decode_fused(tie_cuda_ctx *c, const float *x, const float *w, const float *bias, int n_tokens, float *logits,
+			       int *topk_idx, float *topk_w)
+{
+	const int H = c->cfg.hidden, E = c->cfg.n_expert;
+	size_t smem = ((size_t)H + (size_t)n_tokens * (H + 8)) * sizeof(float);
+	router_decode_fused<<<E, 256, smem, c->stream>>>(x, w, bias, logits, n_tokens, H, E, c->cfg.top_k, topk_idx, topk_w, c->s.counter);
+	TIE_CUDA_LAUNCHED(c);
+	return TIE_CUDA_OK;
+}
+
 // Opt-in shared-memory sizes are set once per context (never inside a stream capture).
 int router_setup(tie_cuda_ctx *c)
 {
 	TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_logits_decode<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_decode_fused, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_logits_mt, cudaFuncAttributeMaxDynamicSharedMemorySize, RMT_SMEM));
 	return TIE_CUDA_OK;
 }
 

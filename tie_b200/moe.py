@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libtie_cuda.so")
 
 HOST, DEVICE, NO_SYNC, GRAPH = 0, 1, 2, 4
 PATH_AUTO, PATH_STREAM, PATH_TENSOR = 0, 1 << 8, 2 << 8
+PATH_LEGACY_STREAM = 1 << 10
 OK, EINVAL, ENOTSUP, ENOMEM, ECUDA, ENODEV, EKERNEL, ETOOBIG = 0, -1, -2, -3, -4, -5, -6, -7
 
 # every symbol include/tie_cuda.h declares
