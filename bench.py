@@ -152,6 +152,55 @@ def run_reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def run_stack(n_layers, silu, device, peaks, torch, prefill_tokens=4096, decode_steps=256):
+    """All blocks of a Qwen3-30B-A3B-shaped stack with independent seeded weights (18.85 GB of
+    packed experts at 48 blocks): one 4096-token prefill, then batch-1 decode steps, each block
+    h += MoE(RMSNorm(h)) with norm weight 1.  Attention is not part of this path."""
+    from tie_b200 import moe, synth, workloads
+    shape = synth.MoeShape()
+    be = moe.MoeBackend(max_tokens=prefill_tokens, device=device, silu_table=silu, n_layers=n_layers)
+    ones = np.ones(shape.hidden, dtype=np.float32)
+    t0 = time.perf_counter()
+    for l in range(n_layers):
+        be.upload_layer(l, synth.make_layer(workloads.STACK_BASE_SEED + l, shape), ffn_norm_w=ones)
+    t_load = time.perf_counter() - t0
+    stream = torch.cuda.current_stream()
+    be.set_stream(stream.cuda_stream)
+    flags = moe.DEVICE | moe.NO_SYNC | moe.GRAPH
+    res = {"layers": n_layers, "weight_bytes": be.weight_bytes, "load_seconds": t_load}
+    for name, T, reps in (("prefill", prefill_tokens, 3), ("decode", 1, decode_steps)):
+        h0 = torch.from_numpy(synth.make_x(workloads.STACK_BASE_SEED, T)).cuda()
+        h = h0.clone()
+        for _ in range(2):  # warm-up passes also record the graphs
+            h.copy_(h0)
+            for l in range(n_layers):
+                be.moe_block_inplace_ptr(l, h, T, flags)
+        be.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        h.copy_(h0)
+        e0.record()
+        for _ in range(reps):
+            for l in range(n_layers):
+                be.moe_block_inplace_ptr(l, h, T, flags)
+        e1.record()
+        torch.cuda.synchronize()
+        be.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        finite = bool(torch.isfinite(h).all().item())
+        if name == "prefill":
+            fl = workloads.algorithmic_flops(shape, T) * n_layers
+            res["prefill"] = {"tokens": T, "ms": ms, "tokens_per_s": T / (ms * 1e-3), "algorithmic_tflops": fl / (ms * 1e-3) / 1e12,
+                              "tensor_frac": fl / (ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"], "finite": finite}
+        else:
+            by = workloads.algorithmic_bytes(shape, 1, shape.top_k) * n_layers
+            res["decode"] = {"steps": reps, "us_per_token": ms * 1e3, "tokens_per_s": 1.0 / (ms * 1e-3),
+                             "algorithmic_bytes_per_token": by, "hbm_gbs": by / (ms * 1e-3) / 1e9,
+                             "hbm_frac": by / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "finite": finite,
+                             "l2": "48 blocks x 25.5 MB per token exceed L2; the residual stream feeds back, so routing changes every step"}
+    be.close()
+    return res
+
+
 def time_steps(fn, steps, torch, flush=None):
     """CUDA-event time of `steps` calls of fn on the current stream; optional untimed L2 flush
     before every call.  Returns total milliseconds."""
@@ -174,6 +223,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the decode / 64 / 4096-token side runs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--stack-layers", type=int, default=48, help="blocks of the stack side run (0 = skip)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -310,6 +360,10 @@ def main():
                            "algorithmic_tflops": fl_ops / (ms * 1e-3) / 1e12,
                            "tensor_frac": fl_ops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
                            "l2": "flushed between steps" if fl else "weights 392 MB > 126 MB L2"}
+
+    # ---- side run: the 48-block stack, h += MoE(RMSNorm(h)) per block, residual stream on the device ----
+    if not args.no_extra and args.stack_layers > 0:
+        extra["stack"] = run_stack(args.stack_layers, silu, local_rank, peaks, torch)
 
     # ---- CPU baseline on this box's host cores (bounded sample) ----
     cpu = None

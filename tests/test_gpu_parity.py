@@ -218,6 +218,30 @@ def test_block_inplace(be, layer0, golden):
     _check_ffn(out, g["hidden_out"], tol=TOL)
 
 
+def test_two_blocks_chained_teacher_forced(be, layer0, port_lib, ref_silu_table):
+    """Two blocks back to back on the device (prefill- and decode-sized), each block checked
+    against the oracle fed with the GPU's own input to that block (teacher forcing: a 1e-7
+    difference can flip a near-tie in a later block, which is drift, not error)."""
+    import torch
+    from tie_b200 import moe
+    layer1 = synth.make_layer(workloads.STACK_BASE_SEED + 1)
+    ones = np.ones(2048, dtype=np.float32)
+    b = moe.MoeBackend(max_tokens=64, silu_table=ref_silu_table, n_layers=2)
+    try:
+        b.upload_layer(0, layer0, ffn_norm_w=ones)
+        b.upload_layer(1, layer1, ffn_norm_w=ones)
+        ports = [port_lib.PortMoe(layer0, silu=ref_silu_table), port_lib.PortMoe(layer1, silu=ref_silu_table)]
+        for T in (1, 40):
+            h = torch.from_numpy(synth.make_x(workloads.STACK_BASE_SEED, T)).cuda()
+            for l in range(2):
+                h_in = h.cpu().numpy()
+                b.moe_block_inplace_ptr(l, h, T, moe.DEVICE)
+                want, _, _, _, _ = ports[l].moe_block_inplace(h_in, norm_w=ones, eps=1e-6)
+                _check_ffn(h.cpu().numpy(), want)
+    finally:
+        b.close()
+
+
 # ---------------- expert-parallel building blocks ----------------
 
 def test_expert_rows_and_combine(be, port0, golden):
