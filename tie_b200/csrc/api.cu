@@ -56,7 +56,7 @@ int alloc_scratch(tie_cuda_ctx *c)
 	TRY(dev_alloc(c, &s.n_active, 1));
 	TRY(dev_alloc(c, &s.perm, R));
 	TRY(dev_alloc(c, &s.h, R * F));
-	TRY(dev_alloc(c, &s.y, R * H));
+	TRY(dev_alloc(c, &s.y, R * (H > 2 * F ? H : 2 * F)));  // also holds the raw gate|up products of the tensor path
 	TRY(dev_alloc(c, &s.xs_hi, s.rows_pad * H));
 	TRY(dev_alloc(c, &s.xs_lo, s.rows_pad * H));
 	TRY(dev_alloc(c, &s.hs_hi, s.rows_pad * F));

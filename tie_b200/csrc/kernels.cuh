@@ -36,6 +36,7 @@ int launch_gather_rows(tie_cuda_ctx *c, const float *x, const int *row_expert, c
 int launch_split_rows(tie_cuda_ctx *c, const float *x, const int *perm, int src_div, int n_rows, int n_cols, __half *hi,
 		      __half *lo);
 int launch_swiglu(tie_cuda_ctx *c, float *gate, const float *up, int n);
+int launch_swiglu_split(tie_cuda_ctx *c, const float *gu, int n_rows, int ffn, float scale, __half *hi, __half *lo);
 // tensor.cu
 int tc_setup(tie_cuda_ctx *c);
 bool tc_supported(const tie_cuda_ctx *c, const Layer &L);

@@ -119,6 +119,29 @@ __global__ void __launch_bounds__(256) gather_rows(const float *__restrict__ x, 
 	}
 }
 
+// gu [row][gate(ffn) | up(ffn)] fp32 -> h = SwiGLU(gate, up) * scale, split into fp16 hi + lo and
+// stored in the k order of the tensor-core operand tiles ([k0, k2, k1, k3] per group of 4).
+__global__ void __launch_bounds__(256) swiglu_split_rows(const float *__restrict__ gu, int ffn, float scale,
+							 const float *__restrict__ silu, __half *__restrict__ hi,
+							 __half *__restrict__ lo)
+{
+	const size_t r = blockIdx.x;
+	const float *g = gu + r * 2 * ffn, *u = g + ffn;
+	__half2 *hr = reinterpret_cast<__half2 *>(hi + r * ffn);
+	__half2 *lr = reinterpret_cast<__half2 *>(lo + r * ffn);
+	for (int k = threadIdx.x * 4; k < ffn; k += blockDim.x * 4) {
+		const float4 gv = *reinterpret_cast<const float4 *>(g + k), uv = *reinterpret_cast<const float4 *>(u + k);
+		const float h0 = swiglu_lut(silu, gv.x, uv.x) * scale, h1 = swiglu_lut(silu, gv.y, uv.y) * scale;
+		const float h2 = swiglu_lut(silu, gv.z, uv.z) * scale, h3 = swiglu_lut(silu, gv.w, uv.w) * scale;
+		const __half2 a = __floats2half2_rn(h0, h2), b = __floats2half2_rn(h1, h3);
+		const float2 fa = __half22float2(a), fb = __half22float2(b);
+		hr[k / 2] = a;
+		hr[k / 2 + 1] = b;
+		lr[k / 2] = __floats2half2_rn(h0 - fa.x, h2 - fa.y);
+		lr[k / 2 + 1] = __floats2half2_rn(h1 - fb.x, h3 - fb.y);
+	}
+}
+
 __global__ void __launch_bounds__(256) swiglu_kernel(float *__restrict__ gate, const float *__restrict__ up, int n,
 						     const float *__restrict__ silu)
 {
@@ -163,6 +186,13 @@ int launch_gather_rows(tie_cuda_ctx *c, const float *x, const int *row_expert, c
 		       float *rows_out, int *expert_out, int *inv)
 {
 	gather_rows<<<n_rows, 256, 0, c->stream>>>(x, row_expert, perm, src_div, c->cfg.hidden, rows_out, expert_out, inv);
+	TIE_CUDA_LAUNCHED(c);
+	return TIE_CUDA_OK;
+}
+
+int launch_swiglu_split(tie_cuda_ctx *c, const float *gu, int n_rows, int ffn, float scale, __half *hi, __half *lo)
+{
+	swiglu_split_rows<<<n_rows, 256, 0, c->stream>>>(gu, ffn, scale, c->silu, hi, lo);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }

@@ -67,22 +67,30 @@ __global__ void __launch_bounds__(EPC * 8) router_logits_tile(const float *__res
 	}
 }
 
-// Batched token counts: CTA = 16 tokens x 32 experts, thread = 2 tokens x 2 experts x all 8 lanes
-// (32 independent chains, each still a strict i-ascending sequence of fused multiply-adds, so
-// the result stays bit-identical).  Operands are staged in shared memory by cp.async in
-// 128-float k chunks (a 4-deep ring) and read as 128-bit words that most lanes of a warp
-// share, so every loaded float feeds 2 multiply-adds per thread from registers.
-constexpr int RMT_TT = 16, RMT_TE = 32, RMT_KC = 128, RMT_PITCH = RMT_KC + 4, RMT_THREADS = 128;
+// Batched token counts: CTA = 16 tokens x 32 experts; thread = one AVX2 lane l of a 4-token x
+// 8-expert tile (32 chains, each a strict i-ascending sequence of fused multiply-adds, so the
+// result stays bit-identical).  The limit of this kernel is shared-memory-to-register bandwidth
+// (one float per lane per cycle), so every loaded float must feed several multiply-adds from
+// registers: 12 loads per 32 multiply-adds here.  Operands are staged by cp.async in 128-float k
+// chunks (a 4-deep ring); a row pitch of KC+8 floats puts the 4 token groups of a warp on
+// disjoint banks.
+constexpr int RMT_TT = 16, RMT_TE = 32, RMT_KC = 128, RMT_PITCH = RMT_KC + 8;
 constexpr int RMT_STAGES = 4;
 constexpr int RMT_SMEM = RMT_STAGES * (RMT_TT + RMT_TE) * RMT_PITCH * (int)sizeof(float);
 
-__global__ void __launch_bounds__(RMT_THREADS) router_logits_mt(const float *__restrict__ x, const float *__restrict__ w,
-							       const float *__restrict__ bias, float *__restrict__ logits,
-							       int n_tokens, int hidden, int n_expert)
+// EPT = experts per thread: 8 (128 threads) when there are enough tokens to fill the GPU with
+// such CTAs, 4 (256 threads, twice the warps per SM to hide latency) for a few hundred tokens.
+template <int EPT>
+__global__ void __launch_bounds__(8 * 4 * (RMT_TE / EPT)) router_logits_mt(const float *__restrict__ x, const float *__restrict__ w,
+									   const float *__restrict__ bias, float *__restrict__ logits,
+									   int n_tokens, int hidden, int n_expert)
 {
+	constexpr int RMT_THREADS = 8 * 4 * (RMT_TE / EPT);
 	extern __shared__ __align__(16) float rsm[];
 	const int t0 = blockIdx.x * RMT_TT, e0 = blockIdx.y * RMT_TE;
-	const int tp = threadIdx.x & 7, ep = threadIdx.x >> 3;	// tokens (tp, tp+8), experts (ep, ep+16)
+	const int l = threadIdx.x & 7;		// AVX2 lane
+	const int tg = (threadIdx.x >> 3) & 3;	// tokens tg, tg+4, tg+8, tg+12
+	const int eg = threadIdx.x >> 5;	// experts EPT*eg .. EPT*eg+EPT-1 (one warp per expert group)
 	auto stage = [&](int buf, int k0) {
 		float *xs = rsm + buf * (RMT_TT + RMT_TE) * RMT_PITCH;
 		float *ws = xs + RMT_TT * RMT_PITCH;
@@ -103,14 +111,12 @@ __global__ void __launch_bounds__(RMT_THREADS) router_logits_mt(const float *__r
 		}
 		asm volatile("cp.async.commit_group;" ::: "memory");
 	};
-	float acc[2][2][8];
+	float acc[4][EPT];  // [token j][expert b]
 #pragma unroll
-	for (int a = 0; a < 2; a++)
+	for (int j = 0; j < 4; j++)
 #pragma unroll
-		for (int b = 0; b < 2; b++)
-#pragma unroll
-			for (int l = 0; l < 8; l++)
-				acc[a][b][l] = 0.0f;
+		for (int b = 0; b < EPT; b++)
+			acc[j][b] = 0.0f;
 	const int n_chunks = hidden / RMT_KC;
 #pragma unroll
 	for (int c = 0; c < RMT_STAGES - 1; c++) {
@@ -128,44 +134,37 @@ __global__ void __launch_bounds__(RMT_THREADS) router_logits_mt(const float *__r
 		__syncthreads();
 		const float *xs = rsm + (c % RMT_STAGES) * (RMT_TT + RMT_TE) * RMT_PITCH;
 		const float *ws = xs + RMT_TT * RMT_PITCH;
-		// rows (tp, tp+8) and (ep, ep+16): the 4-float row skew then spreads a warp's reads over all banks
-		const float *x0 = xs + tp * RMT_PITCH, *x1 = x0 + 8 * RMT_PITCH;
-		const float *w0 = ws + ep * RMT_PITCH, *w1 = w0 + 16 * RMT_PITCH;
+		const float *xp = xs + tg * RMT_PITCH + l;
+		const float *wp = ws + (EPT * eg) * RMT_PITCH + l;
 #pragma unroll 4
 		for (int i = 0; i < RMT_KC / 8; i++) {
-			float xv[2][8], wv[2][8];
-			*reinterpret_cast<float4 *>(&xv[0][0]) = *reinterpret_cast<const float4 *>(x0 + 8 * i);
-			*reinterpret_cast<float4 *>(&xv[0][4]) = *reinterpret_cast<const float4 *>(x0 + 8 * i + 4);
-			*reinterpret_cast<float4 *>(&xv[1][0]) = *reinterpret_cast<const float4 *>(x1 + 8 * i);
-			*reinterpret_cast<float4 *>(&xv[1][4]) = *reinterpret_cast<const float4 *>(x1 + 8 * i + 4);
-			*reinterpret_cast<float4 *>(&wv[0][0]) = *reinterpret_cast<const float4 *>(w0 + 8 * i);
-			*reinterpret_cast<float4 *>(&wv[0][4]) = *reinterpret_cast<const float4 *>(w0 + 8 * i + 4);
-			*reinterpret_cast<float4 *>(&wv[1][0]) = *reinterpret_cast<const float4 *>(w1 + 8 * i);
-			*reinterpret_cast<float4 *>(&wv[1][4]) = *reinterpret_cast<const float4 *>(w1 + 8 * i + 4);
+			float xv[4], wv[EPT];
 #pragma unroll
-			for (int a = 0; a < 2; a++)
+			for (int j = 0; j < 4; j++)
+				xv[j] = xp[(4 * j) * RMT_PITCH + 8 * i];
 #pragma unroll
-				for (int b = 0; b < 2; b++)
+			for (int b = 0; b < EPT; b++)
+				wv[b] = wp[b * RMT_PITCH + 8 * i];
 #pragma unroll
-					for (int l = 0; l < 8; l++)
-						acc[a][b][l] = __fmaf_rn(xv[a][l], wv[b][l], acc[a][b][l]);
+			for (int j = 0; j < 4; j++)
+#pragma unroll
+				for (int b = 0; b < EPT; b++)
+					acc[j][b] = __fmaf_rn(xv[j], wv[b], acc[j][b]);
 		}
 		__syncthreads();
 	}
 #pragma unroll
-	for (int a = 0; a < 2; a++) {
-		const int t = t0 + tp + 8 * a;
+	for (int j = 0; j < 4; j++) {
+		const int t = t0 + tg + 4 * j;
 #pragma unroll
-		for (int b = 0; b < 2; b++) {
-			const int e = e0 + ep + 16 * b;
-			const float *l = acc[a][b];
-			// hsum (math_avx2.c:14-21): ((l0+l4)+(l1+l5)) + ((l2+l6)+(l3+l7))
-			float r = __fadd_rn(__fadd_rn(__fadd_rn(l[0], l[4]), __fadd_rn(l[1], l[5])),
-					    __fadd_rn(__fadd_rn(l[2], l[6]), __fadd_rn(l[3], l[7])));
-			if (bias)
-				r = __fadd_rn(r, bias[e]);
-			if (t < n_tokens)
+		for (int b = 0; b < EPT; b++) {
+			const int e = e0 + EPT * eg + b;
+			float r = hsum8_lanes(acc[j][b]);  // lanes l = 0..7 are 8 consecutive threads
+			if (l == 0 && t < n_tokens) {
+				if (bias)
+					r = __fadd_rn(r, bias[e]);
 				logits[(size_t)t * n_expert + e] = r;
+			}
 		}
 	}
 }
@@ -368,7 +367,10 @@ int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *
 		TIE_CUDA_LAUNCHED(c);
 	} else if (E % RMT_TE == 0 && H % RMT_KC == 0) {
 		dim3 grid((n_tokens + RMT_TT - 1) / RMT_TT, E / RMT_TE);
-		router_logits_mt<<<grid, RMT_THREADS, RMT_SMEM, c->stream>>>(x, w, bias, logits, n_tokens, H, E);
+		if (n_tokens <= 1024)
+			router_logits_mt<4><<<grid, 256, RMT_SMEM, c->stream>>>(x, w, bias, logits, n_tokens, H, E);
+		else
+			router_logits_mt<8><<<grid, 128, RMT_SMEM, c->stream>>>(x, w, bias, logits, n_tokens, H, E);
 		TIE_CUDA_LAUNCHED(c);
 	} else if (n_tokens <= 512) {
 		constexpr int TT = 8, EPC = 16;
@@ -403,7 +405,8 @@ int router_setup(tie_cuda_ctx *c)
 {
 	TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_logits_decode<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
 	TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_decode_fused, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-	TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_logits_mt, cudaFuncAttributeMaxDynamicSharedMemorySize, RMT_SMEM));
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_logits_mt<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, RMT_SMEM));
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_logits_mt<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, RMT_SMEM));
 	return TIE_CUDA_OK;
 }
 

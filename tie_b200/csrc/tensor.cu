@@ -51,14 +51,18 @@ struct TcCfg {
 	static constexpr bool CONCAT = NMAT * 2 * NT <= 256;
 	static constexpr int ACC_PER_MAT = CONCAT ? 2 * NT : NT;
 	static constexpr int ACC_COLS = NMAT * ACC_PER_MAT;
-	static constexpr int STAGES_RAW = (512 - ACC_COLS) / (NMAT * 2 * A_COLS);
+	// With one matrix and a 64-token tile the CTA needs only half of an SM's tensor memory and
+	// shared memory: two CTAs then share an SM and hide each other's latencies.
+	static constexpr bool HALF_SM = ACC_COLS + 2 * NMAT * 2 * A_COLS <= 256;
+	static constexpr int TMEM_COLS = HALF_SM ? 256 : 512;
+	static constexpr int STAGES_RAW = (TMEM_COLS - ACC_COLS) / (NMAT * 2 * A_COLS);
 	static constexpr int STAGES = STAGES_RAW > 4 ? 4 : STAGES_RAW;	// weight stages (tensor memory)
-	static constexpr int SB_RAW = (200 * 1024) / B_STAGE;
+	static constexpr int SB_RAW = ((HALF_SM ? 100 : 200) * 1024) / B_STAGE;
 	static constexpr int SB = SB_RAW > 8 ? 8 : SB_RAW;  // token-operand stages (shared memory)
 	static constexpr int SMEM = SB * B_STAGE + 1024 /* alignment slack */ + 512 /* barriers */;
-	static constexpr int TMEM_COLS = 512;
+	static constexpr int CTAS_PER_SM = HALF_SM ? 2 : 1;
 	static_assert(STAGES >= 2 && SB >= 2, "need at least two stages");
-	static_assert(ACC_COLS + STAGES * NMAT * 2 * A_COLS <= 512, "tensor memory budget");
+	static_assert(ACC_COLS + STAGES * NMAT * 2 * A_COLS <= TMEM_COLS, "tensor memory budget");
 };
 
 struct TcShared {
@@ -223,14 +227,18 @@ struct RawGroup<W_Q6K_R8, NMAT> {
 	}
 };
 
-template <WKind KIND, int NMAT, int NT>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+// RAW (one matrix only): the products are stored as fp32 in expert-sorted row order,
+// out[row0 + n][matrix * rows + mrow], for a separate SwiGLU pass; blockIdx.x then runs over the
+// row tiles of w0 followed by those of w1 (gate, up).
+template <WKind KIND, int NMAT, int NT, bool RAW>
+__global__ void __launch_bounds__(TC_THREADS, (TcCfg<NMAT, NT>::CTAS_PER_SM))
 grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__ CUtensorMap tm_lo,
 		const uint8_t *__restrict__ w0, const uint8_t *__restrict__ w1, size_t expert_stride, int k_dim,
 		const int *__restrict__ offsets, const int *__restrict__ tile_start, int n_local,
 		__half *__restrict__ h_hi, __half *__restrict__ h_lo, float *__restrict__ y, const int *__restrict__ perm,
-		int out_stride, const float *__restrict__ silu, unsigned *__restrict__ status)
+		int out_stride, const float *__restrict__ silu, unsigned *__restrict__ status, int rows_per_matrix)
 {
+	static_assert(!RAW || NMAT == 1, "raw output is for the one-matrix kernel");
 	using Cfg = TcCfg<NMAT, NT>;
 	constexpr int S = Cfg::STAGES, SB = Cfg::SB;
 	constexpr bool CONCAT = Cfg::CONCAT;
@@ -261,7 +269,8 @@ grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 		return;
 	}
 	const int n_mma = (n_valid + 15) & ~15;	 // N of the MMAs: the tile's tokens rounded up to 16
-	const int m0 = blockIdx.x * TC_BM;
+	const int mat_sel = RAW ? (int)(blockIdx.x * TC_BM) / rows_per_matrix : 0;  // RAW: 0 = w0 (gate), 1 = w1 (up)
+	const int m0 = blockIdx.x * TC_BM - mat_sel * rows_per_matrix;
 	const int nb = k_dim / QK_K;
 	const int k_iters = k_dim / TC_BK;
 
@@ -310,7 +319,7 @@ grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 		// thread = (row, matrix) for gate/up, (row, half-slice) for down
 		const int row = threadIdx.x & 127, sel = threadIdx.x >> 7;
 		const int m = (NMAT == 2) ? sel : 0, hs = (NMAT == 2) ? 0 : sel;
-		const uint8_t *wexp = ((NMAT == 2 && sel) ? w1 : w0) + (size_t)le * expert_stride;
+		const uint8_t *wexp = (((NMAT == 2 && sel) || (RAW && mat_sel)) ? w1 : w0) + (size_t)le * expert_stride;
 		const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
 		const int n_groups = k_iters >> 1;
 		RawGroup<KIND, NMAT> cur, nxt;
@@ -438,6 +447,8 @@ grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 							const size_t o = (size_t)(row0 + n) * out_stride + tc_kperm(mrow);
 							h_hi[o] = hh;
 							h_lo[o] = hl;
+						} else if (RAW) {
+							y[(size_t)(row0 + n) * out_stride + (size_t)mat_sel * rows_per_matrix + mrow] = __uint_as_float(g[j]);
 						} else {
 							const int rid = perm[row0 + n];
 							y[(size_t)rid * out_stride + mrow] = __uint_as_float(g[j]) * (1.0f / TC_H_SCALE);
@@ -508,48 +519,52 @@ int tc_setup(tie_cuda_ctx *c)
 		if (rc)
 			return rc;
 	}
-#define TC_ATTR(KIND, NMAT, NT)                                                                                            \
-	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_tc<KIND, NMAT, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+#define TC_ATTR(KIND, NMAT, NT, RAW)                                                                                            \
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_tc<KIND, NMAT, NT, RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
 					     TcCfg<NMAT, NT>::SMEM))
-	TC_ATTR(W_Q4K, 1, 64);
-	TC_ATTR(W_Q4K, 1, 128);
-	TC_ATTR(W_Q4K, 2, 64);
-	TC_ATTR(W_Q4K, 2, 128);
-	TC_ATTR(W_Q6K_R8, 1, 64);
-	TC_ATTR(W_Q6K_R8, 1, 128);
-	TC_ATTR(W_Q6K_R8, 2, 64);
-	TC_ATTR(W_Q6K_R8, 2, 128);
+	TC_ATTR(W_Q4K, 1, 64, false);
+	TC_ATTR(W_Q4K, 1, 128, false);
+	TC_ATTR(W_Q4K, 1, 64, true);
+	TC_ATTR(W_Q4K, 1, 128, true);
+	TC_ATTR(W_Q4K, 2, 64, false);
+	TC_ATTR(W_Q4K, 2, 128, false);
+	TC_ATTR(W_Q6K_R8, 1, 64, false);
+	TC_ATTR(W_Q6K_R8, 1, 128, false);
+	TC_ATTR(W_Q6K_R8, 1, 64, true);
+	TC_ATTR(W_Q6K_R8, 1, 128, true);
+	TC_ATTR(W_Q6K_R8, 2, 64, false);
+	TC_ATTR(W_Q6K_R8, 2, 128, false);
 #undef TC_ATTR
 	c->tmaps_ok = true;
 	return TIE_CUDA_OK;
 }
 
-template <WKind KIND, int NMAT, int NT>
+template <WKind KIND, int NMAT, int NT, bool RAW>
 static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1, const CUtensorMap &tmh, const CUtensorMap &tml,
 		       int n_rows, float *y)
 {
 	Scratch &s = c->s;
 	const int max_tiles = min(c->n_local, n_rows) + n_rows / NT;
-	dim3 grid(t0.rows / TC_BM, max_tiles);
-	grouped_gemm_tc<KIND, NMAT, NT><<<grid, TC_THREADS, TcCfg<NMAT, NT>::SMEM, c->stream>>>(
+	dim3 grid((RAW ? 2 : 1) * t0.rows / TC_BM, max_tiles);
+	grouped_gemm_tc<KIND, NMAT, NT, RAW><<<grid, TC_THREADS, TcCfg<NMAT, NT>::SMEM, c->stream>>>(
 		tmh, tml, t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride, t0.k, s.offsets, s.tile_start, c->n_local, s.hs_hi, s.hs_lo,
-		y, s.perm, t0.rows, c->silu, s.status);
+		y, s.perm, RAW ? 2 * t0.rows : t0.rows, c->silu, s.status, t0.rows);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
 
-template <int NMAT>
+template <int NMAT, bool RAW>
 static int launch_tc_n(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1, int arr, int n_tile, int n_rows, float *y)
 {
 	const CUtensorMap &tmh = c->tmap[arr], &tml = c->tmap[arr + 1];
 	if (t0.kind == W_Q4K) {
 		if (n_tile == 64)
-			return launch_tc_t<W_Q4K, NMAT, 64>(c, t0, t1, tmh, tml, n_rows, y);
-		return launch_tc_t<W_Q4K, NMAT, 128>(c, t0, t1, tmh, tml, n_rows, y);
+			return launch_tc_t<W_Q4K, NMAT, 64, RAW>(c, t0, t1, tmh, tml, n_rows, y);
+		return launch_tc_t<W_Q4K, NMAT, 128, RAW>(c, t0, t1, tmh, tml, n_rows, y);
 	}
 	if (n_tile == 64)
-		return launch_tc_t<W_Q6K_R8, NMAT, 64>(c, t0, t1, tmh, tml, n_rows, y);
-	return launch_tc_t<W_Q6K_R8, NMAT, 128>(c, t0, t1, tmh, tml, n_rows, y);
+		return launch_tc_t<W_Q6K_R8, NMAT, 64, RAW>(c, t0, t1, tmh, tml, n_rows, y);
+	return launch_tc_t<W_Q6K_R8, NMAT, 128, RAW>(c, t0, t1, tmh, tml, n_rows, y);
 }
 
 bool tc_supported(const tie_cuda_ctx *c, const Layer &L)
@@ -561,13 +576,21 @@ bool tc_supported(const tie_cuda_ctx *c, const Layer &L)
 // xs_hi/xs_lo must hold the split inputs in sorted order; writes hs_hi/hs_lo.
 int launch_tc_gate_up(tie_cuda_ctx *c, const Layer &L, int n_rows, int n_tile)
 {
-	return launch_tc_n<2>(c, L.gate, &L.up, 0, n_tile, n_rows, nullptr);
+	if (n_tile == 64) {
+		// few tokens per expert: gate and up as independent one-matrix tiles (two CTAs per SM),
+		// raw fp32 products to a scratch [row][gate | up], then one element-wise SwiGLU + split pass
+		int rc = launch_tc_n<1, true>(c, L.gate, &L.up, 0, n_tile, n_rows, c->s.y);
+		if (rc)
+			return rc;
+		return launch_swiglu_split(c, c->s.y, n_rows, L.gate.rows, TC_H_SCALE, c->s.hs_hi, c->s.hs_lo);
+	}
+	return launch_tc_n<2, false>(c, L.gate, &L.up, 0, n_tile, n_rows, nullptr);
 }
 
 // reads hs_hi/hs_lo; writes y[perm[p]].
 int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, int n_tile, float *y)
 {
-	return launch_tc_n<1>(c, L.down, nullptr, 2, n_tile, n_rows, y);
+	return launch_tc_n<1, false>(c, L.down, nullptr, 2, n_tile, n_rows, y);
 }
 
 }  // namespace tie
