@@ -52,6 +52,7 @@ int alloc_scratch(tie_cuda_ctx *c)
 	TRY(dev_alloc(c, &s.counts, E));
 	TRY(dev_alloc(c, &s.offsets, E + 1));
 	TRY(dev_alloc(c, &s.tile_start, E + 1));
+	TRY(dev_alloc(c, &s.tile_info, E + R / TC_TOKEN_TILE + 1));
 	TRY(dev_alloc(c, &s.active, E));
 	TRY(dev_alloc(c, &s.n_active, 1));
 	TRY(dev_alloc(c, &s.perm, R));
@@ -61,6 +62,11 @@ int alloc_scratch(tie_cuda_ctx *c)
 	TRY(dev_alloc(c, &s.xs_lo, s.rows_pad * H));
 	TRY(dev_alloc(c, &s.hs_hi, s.rows_pad * F));
 	TRY(dev_alloc(c, &s.hs_lo, s.rows_pad * F));
+	const size_t XH = xq_cols((int)H), XF = xq_cols((int)F);
+	TRY(dev_alloc(c, &s.xq_hi, s.rows_pad * XH));
+	TRY(dev_alloc(c, &s.xq_lo, s.rows_pad * XH));
+	TRY(dev_alloc(c, &s.hq_hi, s.rows_pad * XF));
+	TRY(dev_alloc(c, &s.hq_lo, s.rows_pad * XF));
 	TRY(dev_alloc(c, &s.status, 1));
 	TRY(dev_alloc(c, &s.counter, 1));
 	TIE_CUDA_TRY(c, cudaMemset(s.counter, 0, sizeof(int)));
@@ -79,6 +85,11 @@ int alloc_scratch(tie_cuda_ctx *c)
 	TIE_CUDA_TRY(c, cudaMemset(s.xs_lo, 0, s.rows_pad * H * sizeof(__half)));
 	TIE_CUDA_TRY(c, cudaMemset(s.hs_hi, 0, s.rows_pad * F * sizeof(__half)));
 	TIE_CUDA_TRY(c, cudaMemset(s.hs_lo, 0, s.rows_pad * F * sizeof(__half)));
+	// the padding columns of the sub-block sums are read by the tensor path and must stay zero
+	TIE_CUDA_TRY(c, cudaMemset(s.xq_hi, 0, s.rows_pad * XH * sizeof(__half)));
+	TIE_CUDA_TRY(c, cudaMemset(s.xq_lo, 0, s.rows_pad * XH * sizeof(__half)));
+	TIE_CUDA_TRY(c, cudaMemset(s.hq_hi, 0, s.rows_pad * XF * sizeof(__half)));
+	TIE_CUDA_TRY(c, cudaMemset(s.hq_lo, 0, s.rows_pad * XF * sizeof(__half)));
 	TIE_CUDA_TRY(c, cudaMallocHost(reinterpret_cast<void **>(&c->pin_x), T * H * sizeof(float)));
 	TIE_CUDA_TRY(c, cudaMallocHost(reinterpret_cast<void **>(&c->pin_out), T * H * sizeof(float)));
 	TIE_CUDA_TRY(c, cudaMallocHost(reinterpret_cast<void **>(&c->pin_idx), R * sizeof(int)));
@@ -205,18 +216,20 @@ int run_experts(tie_cuda_ctx *c, const Layer &L, const float *x_src, int src_div
 		use_tc = tc_supported(c, L) && n_rows >= 2 * c->n_local;
 	}
 	const int direct = (!use_tc && n_rows <= c->cfg.top_k && src_div == c->cfg.top_k) ? 1 : 0;
-	const int n_tile = ((size_t)n_rows <= (size_t)48 * c->n_local) ? 64 : 128;
+	const int n_tile = TC_TOKEN_TILE;
 	c->last_direct_rows = direct ? n_rows : -1;
 	c->last_used_tc = use_tc;
 	if (!direct)
 		TRY(launch_sort(c, row_expert, n_rows, n_tile));
 	prof_mark(c, 2);
 	if (use_tc) {
-		TRY(launch_split_rows(c, x_src, c->s.perm, src_div, n_rows, c->cfg.hidden, c->s.xs_hi, c->s.xs_lo));
+		const bool sums = L.gate.kind == W_Q4K;	 // the Q4_K "min" term needs the sub-block sums of the inputs
+		TRY(launch_split_rows(c, x_src, c->s.perm, src_div, n_rows, c->cfg.hidden, c->s.xs_hi, c->s.xs_lo,
+				      sums ? c->s.xq_hi : nullptr, sums ? c->s.xq_lo : nullptr));
 		prof_mark(c, 3);
-		TRY(launch_tc_gate_up(c, L, n_rows, n_tile));
+		TRY(launch_tc_gate_up(c, L, n_rows));
 		prof_mark(c, 4);
-		TRY(launch_tc_down(c, L, n_rows, n_tile, y));
+		TRY(launch_tc_down(c, L, n_rows, y));
 		prof_mark(c, 5);
 	} else {
 		prof_mark(c, 3);
@@ -489,7 +502,8 @@ void tie_cuda_destroy(tie_cuda_ctx *c)
 	Scratch &s = c->s;
 	void *dev_ptrs[] = {s.x,     s.out,   s.logits, s.bias,  s.topk_idx, s.topk_w, s.counts, s.offsets, s.tile_start, s.active, s.n_active,
 			    s.perm,  s.h,     s.y,	s.xs_hi, s.xs_lo,    s.hs_hi,  s.hs_lo,  s.status,  s.counter, s.row_expert, c->silu,  c->row_x,
-			    c->row_o, s.ep_counts, s.ep_offsets, s.ep_tile_start, s.ep_active, s.ep_n_active, s.ep_perm, s.ep_inv};
+			    c->row_o, s.ep_counts, s.ep_offsets, s.ep_tile_start, s.ep_active, s.ep_n_active, s.ep_perm, s.ep_inv,
+			    s.tile_info, s.xq_hi, s.xq_lo, s.hq_hi, s.hq_lo};
 	for (void *p : dev_ptrs)
 		if (p)
 			cudaFree(p);
@@ -765,7 +779,7 @@ int tie_cuda_moe_ep_dispatch(tie_cuda_ctx *c, const float *x, const int *topk_id
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
 	Scratch &s = c->s;
 	const int R = n_tokens * c->cfg.top_k;
-	SortBufs b = {expert_counts, s.ep_offsets, s.ep_tile_start, s.ep_active, s.ep_n_active, s.ep_perm};
+	SortBufs b = {expert_counts, s.ep_offsets, s.ep_tile_start, s.ep_active, s.ep_n_active, s.ep_perm, nullptr};
 	TRY(launch_sort(c, topk_idx, R, 128, 0, c->cfg.n_expert, b));
 	TRY(launch_gather_rows(c, x, topk_idx, s.ep_perm, c->cfg.top_k, R, send_rows, send_expert, s.ep_inv));
 	if (flags & TIE_CUDA_NO_SYNC)

@@ -15,6 +15,7 @@ constexpr int QK_K = 256;	  // gguf.h:100
 constexpr int Q4K_BYTES = 144;	  // sizeof(block_q4_k), gguf.h:108-113
 constexpr int Q6K_BYTES = 210;	  // sizeof(block_q6_k), gguf.h:101-106
 constexpr int MAX_TOP_K = 8;
+constexpr int TC_TOKEN_TILE = 64;  // rows of one expert per token tile of the tensor-core path
 constexpr int SILU_N = TIE_CUDA_SILU_TABLE_SIZE;
 
 // Device status word bits (set by kernels instead of trapping).
@@ -58,6 +59,7 @@ struct Scratch {
 	int *counts = nullptr;	    // [E]
 	int *offsets = nullptr;	    // [E+1]
 	int *tile_start = nullptr;  // [E+1]
+	int4 *tile_info = nullptr;  // [E + R/TC_TOKEN_TILE + 1]  token tiles: (expert, first sorted row, rows, 0)
 	int *active = nullptr;	    // [E]  compact list of experts with rows
 	int *n_active = nullptr;    // [1]
 	int *perm = nullptr;	    // [R]  sorted position -> row id
@@ -65,6 +67,9 @@ struct Scratch {
 	float *y = nullptr;	    // [R][H]  per-row expert outputs, row-id order
 	__half *xs_hi = nullptr, *xs_lo = nullptr;  // [Rpad][H]  split inputs, sorted order
 	__half *hs_hi = nullptr, *hs_lo = nullptr;  // [Rpad][F]
+	// sums of the rows above over 32-wide sub-blocks, split the same way; 64 columns per 2048 k
+	__half *xq_hi = nullptr, *xq_lo = nullptr;  // [Rpad][xq_cols(H)]
+	__half *hq_hi = nullptr, *hq_lo = nullptr;  // [Rpad][xq_cols(F)]
 	unsigned *status = nullptr;		    // [1]
 	int *counter = nullptr;			    // [1] last-CTA counter of the fused decode router (zero at rest)
 	int *row_expert = nullptr;		    // [R] staging for expert_rows
@@ -100,8 +105,8 @@ struct tie_cuda_ctx {
 	cudaEvent_t prof_ev[8] = {nullptr};
 	bool prof_set[8] = {false};
 	char cuda_err[256] = {0};
-	// tensor maps for the tcgen05 path: xs_hi, xs_lo, hs_hi, hs_lo (16-row boxes)
-	CUtensorMap tmap[4];
+	// tensor maps for the tcgen05 path: xs_hi, xs_lo, hs_hi, hs_lo, xq_hi, xq_lo, hq_hi, hq_lo (16-row boxes)
+	CUtensorMap tmap[8];
 	bool tmaps_ok = false;
 	// host registry for dispatch rows
 	struct Reg {
@@ -190,6 +195,12 @@ __device__ __forceinline__ float swiglu_lut(const float *__restrict__ tab, float
 	float frac = __fsub_rn(pos, (float)idx);
 	float y1 = tab[idx], y2 = tab[idx + 1];
 	return __fmul_rn(__fmaf_rn(__fsub_rn(y2, y1), frac, y1), u);
+}
+
+// Columns of the sub-block-sum arrays for an input dim k: k/32 sums, padded to whole 64-wide tiles.
+__host__ __device__ __forceinline__ int xq_cols(int k)
+{
+	return ((k / 32 + 63) / 64) * 64;
 }
 
 __device__ __forceinline__ float half_bits_to_float(uint32_t h16)

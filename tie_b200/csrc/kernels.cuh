@@ -18,6 +18,7 @@ int launch_router_rows(tie_cuda_ctx *c, const float *x, const float *w, int n_ro
 // sort.cu
 struct SortBufs {
 	int *counts, *offsets, *tile_start, *active, *n_active, *perm;
+	int4 *tile_info;  // optional: one entry per token tile (expert, first sorted row, rows, 0)
 };
 int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile);
 int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile, int first_expert, int n_expert,
@@ -34,14 +35,15 @@ int launch_combine(tie_cuda_ctx *c, const float *y, const float *topk_w, int n_t
 int launch_gather_rows(tie_cuda_ctx *c, const float *x, const int *row_expert, const int *perm, int src_div, int n_rows,
 		       float *rows_out, int *expert_out, int *inv);
 int launch_split_rows(tie_cuda_ctx *c, const float *x, const int *perm, int src_div, int n_rows, int n_cols, __half *hi,
-		      __half *lo);
+		      __half *lo, __half *q_hi, __half *q_lo);
 int launch_swiglu(tie_cuda_ctx *c, float *gate, const float *up, int n);
-int launch_swiglu_split(tie_cuda_ctx *c, const float *gu, int n_rows, int ffn, float scale, __half *hi, __half *lo);
+int launch_swiglu_split(tie_cuda_ctx *c, const float *gu, int n_rows, int ffn, float scale, __half *hi, __half *lo, __half *q_hi,
+			__half *q_lo);
 // tensor.cu
 int tc_setup(tie_cuda_ctx *c);
 bool tc_supported(const tie_cuda_ctx *c, const Layer &L);
-int launch_tc_gate_up(tie_cuda_ctx *c, const Layer &L, int n_rows, int n_tile);
-int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, int n_tile, float *y);
+int launch_tc_gate_up(tie_cuda_ctx *c, const Layer &L, int n_rows);
+int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, float *y);
 // repack.cu
 int launch_repack_q6k_r8(tie_cuda_ctx *c, const uint8_t *raw, uint8_t *dst, size_t n_rows_total, int nb);
 

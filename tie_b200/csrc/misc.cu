@@ -77,11 +77,28 @@ __global__ void __launch_bounds__(256) combine_rows(const float *__restrict__ y,
 	}
 }
 
+// Sum of v over the 8 lanes that hold one 32-wide sub-block (4 consecutive k per lane); the first
+// lane of the group stores it split into fp16 hi + lo.
+__device__ __forceinline__ void store_subblock_sum(float v, int k, __half *__restrict__ q_hi, __half *__restrict__ q_lo)
+{
+	v += __shfl_xor_sync(0xffffffffu, v, 1);
+	v += __shfl_xor_sync(0xffffffffu, v, 2);
+	v += __shfl_xor_sync(0xffffffffu, v, 4);
+	if ((threadIdx.x & 7) == 0) {
+		const __half h = __float2half_rn(v);
+		q_hi[k >> 5] = h;
+		q_lo[k >> 5] = __float2half_rn(v - __half2float(h));
+	}
+}
+
 // Gather rows into expert-sorted order and split each fp32 value v into fp16 hi + lo
-// (hi = rn16(v), lo = rn16(v - hi)): hi+lo carries 22 significand bits, which the three-product
-// tensor-core scheme needs to stay within the 1e-3 parity bound.
+// (hi = rn16(v), lo = rn16(v - hi)): hi+lo carries 22 significand bits, which the tensor-core
+// scheme needs to stay within the 1e-3 parity bound.  q_hi/q_lo (optional, q_cols per row): the
+// sums of the row over its 32-wide sub-blocks, split the same way (the Q4_K "min" term).
+// n_cols must be a multiple of 128 (whole warps per loop trip).
 __global__ void __launch_bounds__(256) split_rows(const float *__restrict__ x, const int *__restrict__ perm, int src_div,
-						  int n_cols, __half *__restrict__ hi, __half *__restrict__ lo)
+						  int n_cols, __half *__restrict__ hi, __half *__restrict__ lo,
+						  __half *__restrict__ q_hi, __half *__restrict__ q_lo, int q_cols)
 {
 	const int p = blockIdx.x;
 	const int src = perm ? perm[p] / src_div : p;
@@ -98,6 +115,8 @@ __global__ void __launch_bounds__(256) split_rows(const float *__restrict__ x, c
 		hr[k / 2 + 1] = h1;
 		lr[k / 2] = l0;
 		lr[k / 2 + 1] = l1;
+		if (q_hi)
+			store_subblock_sum((v.x + v.y) + (v.z + v.w), k, q_hi + (size_t)p * q_cols, q_lo + (size_t)p * q_cols);
 	}
 }
 
@@ -123,7 +142,8 @@ __global__ void __launch_bounds__(256) gather_rows(const float *__restrict__ x, 
 // stored in the k order of the tensor-core operand tiles ([k0, k2, k1, k3] per group of 4).
 __global__ void __launch_bounds__(256) swiglu_split_rows(const float *__restrict__ gu, int ffn, float scale,
 							 const float *__restrict__ silu, __half *__restrict__ hi,
-							 __half *__restrict__ lo)
+							 __half *__restrict__ lo, __half *__restrict__ q_hi,
+							 __half *__restrict__ q_lo, int q_cols)
 {
 	const size_t r = blockIdx.x;
 	const float *g = gu + r * 2 * ffn, *u = g + ffn;
@@ -139,6 +159,8 @@ __global__ void __launch_bounds__(256) swiglu_split_rows(const float *__restrict
 		hr[k / 2 + 1] = b;
 		lr[k / 2] = __floats2half2_rn(h0 - fa.x, h2 - fa.y);
 		lr[k / 2 + 1] = __floats2half2_rn(h1 - fb.x, h3 - fb.y);
+		if (q_hi)
+			store_subblock_sum((h0 + h1) + (h2 + h3), k, q_hi + r * q_cols, q_lo + r * q_cols);
 	}
 }
 
@@ -175,9 +197,9 @@ int launch_combine(tie_cuda_ctx *c, const float *y, const float *topk_w, int n_t
 }
 
 int launch_split_rows(tie_cuda_ctx *c, const float *x, const int *perm, int src_div, int n_rows, int n_cols, __half *hi,
-		      __half *lo)
+		      __half *lo, __half *q_hi, __half *q_lo)
 {
-	split_rows<<<n_rows, 256, 0, c->stream>>>(x, perm, src_div, n_cols, hi, lo);
+	split_rows<<<n_rows, 256, 0, c->stream>>>(x, perm, src_div, n_cols, hi, lo, q_hi, q_lo, xq_cols(n_cols));
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
@@ -190,9 +212,10 @@ int launch_gather_rows(tie_cuda_ctx *c, const float *x, const int *row_expert, c
 	return TIE_CUDA_OK;
 }
 
-int launch_swiglu_split(tie_cuda_ctx *c, const float *gu, int n_rows, int ffn, float scale, __half *hi, __half *lo)
+int launch_swiglu_split(tie_cuda_ctx *c, const float *gu, int n_rows, int ffn, float scale, __half *hi, __half *lo, __half *q_hi,
+			__half *q_lo)
 {
-	swiglu_split_rows<<<n_rows, 256, 0, c->stream>>>(gu, ffn, scale, c->silu, hi, lo);
+	swiglu_split_rows<<<n_rows, 256, 0, c->stream>>>(gu, ffn, scale, c->silu, hi, lo, q_hi, q_lo, xq_cols(ffn));
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }

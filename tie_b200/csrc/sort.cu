@@ -50,9 +50,9 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_place(const int *__restrict
 							   int n_local, const int *__restrict__ counts, int n_tile,
 							   int *__restrict__ offsets, int *__restrict__ tile_start,
 							   int *__restrict__ active, int *__restrict__ n_active,
-							   int *__restrict__ perm)
+							   int *__restrict__ perm, int4 *__restrict__ tile_info)
 {
-	__shared__ int s_off;
+	__shared__ int s_off, s_tiles;
 	__shared__ int wcnt[SORT_THREADS / 32];
 	const int le = blockIdx.x;
 	const int e = first_expert + le;
@@ -82,6 +82,7 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_place(const int *__restrict
 		}
 		if (threadIdx.x == 0) {
 			s_off = off;
+			s_tiles = tiles;
 			offsets[le] = off;
 			tile_start[le] = tiles;
 			if (counts[le] > 0)
@@ -95,6 +96,11 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_place(const int *__restrict
 	}
 	__syncthreads();
 	int base = s_off;
+	if (tile_info) {  // the token tiles of this expert
+		const int cnt = counts[le];
+		for (int j = threadIdx.x; j * n_tile < cnt; j += SORT_THREADS)
+			tile_info[s_tiles + j] = make_int4(le, base + j * n_tile, min(n_tile, cnt - j * n_tile), 0);
+	}
 	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 	for (int r0 = 0; r0 < n_rows; r0 += SORT_THREADS) {
 		int r = r0 + threadIdx.x;
@@ -123,7 +129,7 @@ int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile, 
 	sort_count<<<n_expert, SORT_THREADS, 0, c->stream>>>(row_expert, n_rows, first_expert, n_expert, b.counts, c->s.status);
 	TIE_CUDA_LAUNCHED(c);
 	sort_place<<<n_expert, SORT_THREADS, 0, c->stream>>>(row_expert, n_rows, first_expert, n_expert, b.counts, n_tile,
-							      b.offsets, b.tile_start, b.active, b.n_active, b.perm);
+							      b.offsets, b.tile_start, b.active, b.n_active, b.perm, b.tile_info);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
@@ -131,7 +137,7 @@ int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile, 
 int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile)
 {
 	Scratch &s = c->s;
-	SortBufs b = {s.counts, s.offsets, s.tile_start, s.active, s.n_active, s.perm};
+	SortBufs b = {s.counts, s.offsets, s.tile_start, s.active, s.n_active, s.perm, s.tile_info};
 	return launch_sort(c, row_expert, n_rows, n_tile, c->first_expert, c->n_local, b);
 }
 

@@ -1,30 +1,26 @@
-// Dequantisation of packed Q4_K / Q6_K weights straight into fp16 hi + lo MMA operand pairs,
-// in packed half2 arithmetic.
+// Packed Q4_K / Q6_K quants -> exact small-integer fp16 MMA operands, in packed half2 arithmetic.
 //
-// A weight of a 32-wide (Q4_K) or 16-wide (Q6_K) sub-block is affine in its small integer quant:
-//   Q4_K: w = s*q - m   (s = d*sc, m = dmin*mn, q in 0..15)      math_scalar.c:216-255
-//   Q6_K: w = s*(q-32)  (s = d*sc, q in 0..63)                    math_scalar.c:257-287
-// Per sub-block a power-of-two quantum u is chosen so that s_h = a*u and m_h = b*u with small
-// integers a, b make  hi = s_h*q - m_h  an integer multiple of u below 2049*u: EXACT in fp16, one
-// HFMA2 per two weights.  The remainders s_r = s - s_h, m_r = m - m_h (|.| <= u/2) give
-// lo = rn16(s_r*q - m_r), again one HFMA2.  hi + lo equals the reference's fp32 weight to about
-// 0.01*u, i.e. ~1e-5 of the sub-block's largest weight — the same order as the rounding of the
-// tensor-core accumulation and far inside the 1e-3 parity bound.
+// A weight of a super-block (256 k) factors as
+//   Q4_K: w = d * (sc_b * q) - dmin * m_b      (sc_b, m_b 6-bit, q 4-bit)   math_scalar.c:216-255
+//   Q6_K: w = d * (sc_b * (q - 32))            (sc_b int8, q 6-bit)         math_scalar.c:257-287
+// with d, dmin constant over the super-block.  The integer products sc_b*q (<= 945) and
+// sc_b*(q-32) are what the tensor cores multiply: they are EXACT in fp16 up to 2048 (the Q6_K
+// product can reach 4096; above 2048 an odd product is rounded to even, a relative 2^-12 on that
+// one weight).  The fp32 factors d and dmin are applied when a super-block's partial sums are
+// taken out of tensor memory, so no low-order operand is needed for the weights.
 //
-// Quants become halves without a conversion instruction: (bits & 0x000F000F) | 0x64006400 is the
-// half2 (1024+q_a, 1024+q_b); subtracting 1024 is exact.  The two lanes of such a half2 come from
-// bytes 0 and 2 (or 1 and 3) of a 32-bit word, so within every group of 4 consecutive k the
-// operand tiles hold the order [k0, k2, k1, k3]; the token operand is written in the same order
-// (split_rows and the gate/up epilogue), so the contraction is unchanged.
+// Quants become halves without conversion instructions: a 16-bit field 0x6400 | q is the half
+// 1024 + q, 0x6400 | (q << 4) is 1024 + 16 q, 0x5400 | (q << 4) is 64 + q (q < 64); one HFMA2 with
+// a per-sub-block scale and offset then yields sc*q resp. sc*(q-32) for two weights (the product
+// inside the fused multiply-add is exact, so the result is the exact integer).  The two halves of
+// such a pair come from bytes 0 and 2 (or 1 and 3) of a 32-bit word, so within every group of 4
+// consecutive k the operand tiles hold the order [k0, k2, k1, k3]; the token operand is written in
+// the same order (split_rows, swiglu_split_rows), so the contraction is unchanged.
 #pragma once
 
 #include "common.cuh"
 
 namespace tie {
-
-struct H2x4 {
-	__half2 sh, mh, sr, mr;
-};
 
 __device__ __forceinline__ uint32_t h2_bits(__half2 v)
 {
@@ -35,63 +31,40 @@ __device__ __forceinline__ __half2 bits_h2(uint32_t v)
 	return *reinterpret_cast<__half2 *>(&v);
 }
 
-// s, m: fp32 scale and min of a Q4_K sub-block.
-__device__ __forceinline__ H2x4 q4k_consts(float s, float m)
+// Scale constants of one Q4_K sub-block pair (low nibbles: sub-block 2p, high nibbles: 2p+1).
+struct Q4kConsts {
+	__half2 sl, cl;	 // low nibbles:  (1024 + q)    * s      - 1024 s
+	__half2 sh, ch;	 // high nibbles: (1024 + 16 q) * (s/16) -   64 s
+};
+
+__device__ __forceinline__ Q4kConsts q4k_int_consts(int s_lo, int s_hi)
 {
-	const float M = fmaxf(15.0f * fabsf(s), fabsf(m));
-	int eb = (__float_as_int(M) >> 23) & 0xff;
-	eb = max(eb - 9, 103);	// u = 2^(eb-127) >= 2^-24; M/u in [512, 1024)
-	const float u = __int_as_float(eb << 23), ui = __int_as_float((254 - eb) << 23);
-	const float s_h = rintf(s * ui) * u, m_h = rintf(m * ui) * u;
-	H2x4 c;
-	c.sh = __float2half2_rn(s_h);
-	c.mh = __float2half2_rn(-m_h);
-	c.sr = __float2half2_rn(s - s_h);
-	c.mr = __float2half2_rn(-(m - m_h));
+	Q4kConsts c;
+	const float fl = (float)s_lo, fh = (float)s_hi;
+	c.sl = __float2half2_rn(fl);
+	c.cl = __float2half2_rn(-1024.0f * fl);
+	c.sh = __float2half2_rn(fh * 0.0625f);
+	c.ch = __float2half2_rn(-64.0f * fh);
 	return c;
 }
 
-// s: fp32 scale of a Q6_K 16-wide sub-block (signed).
-__device__ __forceinline__ void q6k_consts(float s, __half2 &sh, __half2 &sr)
+// One 32-bit word of Q4_K quants (4 bytes = 4 low + 4 high nibbles) -> sc*q as half2 pairs:
+// lo[0] = bytes (0, 2), lo[1] = bytes (1, 3) of the low nibbles; hi[] the same of the high ones.
+__device__ __forceinline__ void q4k_int_word(uint32_t w, const Q4kConsts &c, uint32_t lo[2], uint32_t hi[2])
 {
-	int eb = (__float_as_int(fabsf(s)) >> 23) & 0xff;
-	eb = max(eb - 5, 103);	// |s|/u in [32, 64): |a*(q-32)| <= 2048
-	const float u = __int_as_float(eb << 23), ui = __int_as_float((254 - eb) << 23);
-	const float s_h = rintf(s * ui) * u;
-	sh = __float2half2_rn(s_h);
-	sr = __float2half2_rn(s - s_h);
+	const uint32_t w8 = w >> 8;
+	lo[0] = h2_bits(__hfma2(bits_h2((w & 0x000F000Fu) | 0x64006400u), c.sl, c.cl));
+	lo[1] = h2_bits(__hfma2(bits_h2((w8 & 0x000F000Fu) | 0x64006400u), c.sl, c.cl));
+	hi[0] = h2_bits(__hfma2(bits_h2((w & 0x00F000F0u) | 0x64006400u), c.sh, c.ch));
+	hi[1] = h2_bits(__hfma2(bits_h2((w8 & 0x00F000F0u) | 0x64006400u), c.sh, c.ch));
 }
 
-// Four low-nibble (shift 0) or high-nibble (shift 4) quants of a word -> hi/lo half2 pairs:
-// hi[0], lo[0] = bytes (0, 2); hi[1], lo[1] = bytes (1, 3).
-__device__ __forceinline__ void q4k_word(uint32_t w, int shift, const H2x4 &c, uint32_t hi[2], uint32_t lo[2])
+// Four 6-bit quants held as the bytes of q (0..63 each) -> sc*(q-32) pairs: out[0] = bytes (0, 2),
+// out[1] = bytes (1, 3).  s = half2(sc), c = half2(-96 sc).
+__device__ __forceinline__ void q6k_int_word(uint32_t q, __half2 s, __half2 c, uint32_t out[2])
 {
-	const __half2 k1024 = __float2half2_rn(1024.0f);
-	const uint32_t a = ((w >> shift) & 0x000F000Fu) | 0x64006400u;
-	const uint32_t b = ((w >> (shift + 8)) & 0x000F000Fu) | 0x64006400u;
-	const __half2 qa = __hsub2(bits_h2(a), k1024), qb = __hsub2(bits_h2(b), k1024);
-	hi[0] = h2_bits(__hfma2(qa, c.sh, c.mh));
-	hi[1] = h2_bits(__hfma2(qb, c.sh, c.mh));
-	lo[0] = h2_bits(__hfma2(qa, c.sr, c.mr));
-	lo[1] = h2_bits(__hfma2(qb, c.sr, c.mr));
-}
-
-// Four 6-bit quants held as the bytes of q (0..63 each) -> hi/lo pairs of s*(q-32).
-__device__ __forceinline__ void q6k_word(uint32_t q, __half2 sh, __half2 sr, uint32_t hi[2], uint32_t lo[2])
-{
-	const __half2 k1056 = __float2half2_rn(1056.0f);
-	const uint32_t a = (q & 0x00FF00FFu) | 0x64006400u;
-	const uint32_t b = ((q >> 8) & 0x00FF00FFu) | 0x64006400u;
-	const __half2 qa = __hsub2(bits_h2(a), k1056), qb = __hsub2(bits_h2(b), k1056);
-	hi[0] = h2_bits(__hmul2(qa, sh));
-	hi[1] = h2_bits(__hmul2(qb, sh));
-	lo[0] = h2_bits(__hmul2(qa, sr));
-	lo[1] = h2_bits(__hmul2(qb, sr));
-}
-
-__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
-{
-	asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+	out[0] = h2_bits(__hfma2(bits_h2(((q << 4) & 0x03F003F0u) | 0x54005400u), s, c));
+	out[1] = h2_bits(__hfma2(bits_h2(((q >> 4) & 0x03F003F0u) | 0x54005400u), s, c));
 }
 
 // Position of element k inside its group of 4 in the operand tiles: [k0, k2, k1, k3].

@@ -57,6 +57,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
 		: "memory");
 	return ok != 0;
 }
+// The same, allowing the hardware to suspend the thread for up to `ns` nanoseconds while the
+// phase is incomplete (a suspended thread issues nothing; it resumes when the phase completes).
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns)
+{
+	uint32_t ok;
+	asm volatile(
+		"{\n\t"
+		".reg .pred p;\n\t"
+		"mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+		"selp.u32 %0, 1, 0, p;\n\t"
+		"}"
+		: "=r"(ok)
+		: "r"(bar), "r"(parity), "r"(ns)
+		: "memory");
+	return ok != 0;
+}
 
 // ---- cp.async: per-thread asynchronous copies global -> shared ----
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src)
@@ -136,6 +152,20 @@ __device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uin
 		"r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
 		: "memory");
 }
+// The same, executed by a whole warp in uniform control flow: only lanes with issue != 0 issue.
+__device__ __forceinline__ void mma_f16_ts_if(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate,
+					      uint32_t issue)
+{
+	asm volatile(
+		"{\n\t"
+		".reg .pred p, q;\n\t"
+		"setp.ne.b32 p, %4, 0;\n\t"
+		"setp.ne.b32 q, %5, 0;\n\t"
+		"@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+		"}" ::"r"(d_tmem),
+		"r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(issue)
+		: "memory");
+}
 // 4 consecutive 32-bit columns of this thread's TMEM lane.
 __device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
 {
@@ -150,6 +180,17 @@ __device__ __forceinline__ void tmem_st_wait()
 __device__ __forceinline__ void mma_commit(uint32_t bar)
 {
 	asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mma_commit_if(uint32_t bar, uint32_t issue)
+{
+	asm volatile(
+		"{\n\t"
+		".reg .pred q;\n\t"
+		"setp.ne.b32 q, %1, 0;\n\t"
+		"@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+		"}" ::"r"(bar),
+		"r"(issue)
+		: "memory");
 }
 
 // 16 consecutive fp32 columns of this thread's TMEM lane.

@@ -1,32 +1,35 @@
-// Grouped expert GEMMs for prefill on the 5th-generation tensor cores (tcgen05.mma, accumulators
-// and the weight operand in tensor memory), fed from packed Q4_K / Q6_K super-blocks.
+// Grouped expert GEMMs for prefill on the 5th-generation tensor cores (tcgen05.mma with the
+// weight operand and the accumulators in tensor memory), fed from packed Q4_K / Q6_K super-blocks.
 //
 // Reference: the same arithmetic as process_expert_task (engine.c:916-964) — gate/up products
-// (math_avx2.c:535-604, 753-769), table SwiGLU (math_avx2.c:908-950), down product
-// (math_avx2.c:411-495, 771-787) — but for all tokens routed to an expert at once instead of one
-// token at a time (model_qwen3.c:415).
+// (math_avx2.c:535-604, 753-769), down product (math_avx2.c:411-495, 771-787) — but for all tokens
+// routed to an expert at once instead of one token at a time (model_qwen3.c:415).
 //
-// Formulation: out^T = W . x^T.  The weight rows fill the 128-row M dimension of the MMA (expert
-// row counts are multiples of 128), the ragged token count of an expert is the N dimension.
-// A CTA owns one (expert, 128-row tile, token tile).  Per 64-wide k stage:
-//   * 8 producer warps read packed blocks (128-bit loads, prefetched one 128-k group ahead into
-//     registers), expand them in packed fp16 arithmetic to exact-hi + lo operand pairs
-//     (tc_dequant.cuh) and write them to TENSOR MEMORY with tcgen05.st — the A operand of the MMA
-//     is taken from TMEM, so shared memory carries only the token operand;
-//   * one thread issues TMA tile loads of the token operand (already split into hi/lo fp16, in
-//     expert-sorted row order, 16-row boxes: only rows the expert really has) into a ring that
-//     runs several k stages ahead of the weight stages;
-//   * one thread per weight matrix issues tcgen05.mma (kind::f16, fp32 accumulate in TMEM):
-//     D += A_hi.B_hi + A_hi.B_lo + A_lo.B_hi.  hi+lo carries ~22 significand bits per operand; a
-//     single fp16 or bf16 product per element is NOT accurate enough for the 1e-3 parity bound.
-//     When the accumulators fit, B_hi and B_lo are stacked along N so that A_hi needs one MMA of
-//     twice the width instead of two (fewer, larger instructions when an expert has few tokens);
-//     the two column ranges are added in the epilogue.
-// Stages are recycled through mbarriers (producers -> full -> MMA -> tcgen05.commit -> empty).
-// Epilogue: tcgen05.ld from TMEM; gate/up: SwiGLU via the table, scaled by 2^-8, split to fp16
-// hi/lo for the down GEMM; down: scaled back and scattered to the (token, slot) row.
-// Every barrier wait is bounded; on timeout the CTA raises ST_WAIT_TIMEOUT in the status word,
-// drains, frees its tensor memory and exits.
+// Formulation: out^T = W . x^T.  Weight rows fill the 128-row M dimension of the MMA (expert row
+// counts are multiples of 128), the ragged token count of an expert is the N dimension (tiles of
+// up to 64 tokens).  A weight of a 256-wide super-block is d * (integer) - dmin * (integer)
+// (tc_dequant.cuh), so the tensor cores multiply EXACT small-integer fp16 weights with the
+// activations (split into fp16 hi + lo: 22 significand bits; one fp16 is not accurate enough
+// for the 1e-3 parity bound) and the fp32 block factors are applied once per super-block:
+//   out[r][n] = sum_B  d[r][B]    * sum_{k in B}  (sc*q)[r][k] * x[n][k]          ("P" partial sums)
+//                    - dmin[r][B] * sum_{b in B}  m[r][b] * xsum[n][b]            ("M" partial sums)
+// where xsum[n][b] is the sum of x[n] over the 32-wide sub-block b (Q4_K only; one extra 16-deep
+// MMA step per super-block).
+//
+// The kernel is persistent: one CTA per SM walks (token tile, 128-row tile) work items.  Roles:
+//   * 8 producer warps read packed blocks (128-bit loads, prefetched one 128-k group ahead, across
+//     work items too), expand them with one HFMA2 per two weights and write the A tiles to TENSOR
+//     MEMORY (tcgen05.st) into a ring of 64-k stages;
+//   * one thread issues TMA tile loads of the token operand (hi/lo fp16, expert-sorted rows,
+//     16-row boxes: only rows the expert really has) and of the sub-block sums into shared memory;
+//   * one thread issues tcgen05.mma (kind::f16, fp32 accumulate): per 16-wide k step
+//     P += A.B_hi, P += A.B_lo, into one of two accumulator buffers that alternate per super-block;
+//   * 8 drain warps take a finished super-block out of tensor memory (tcgen05.ld), fold it into
+//     fp32 registers with d / dmin, and after the last super-block of a work item store the rows —
+//     while the MMAs of the next super-block / work item already run.
+// All hand-offs go through mbarriers (tcgen05.commit on the MMA side).  Every wait is bounded: on
+// a timeout the CTA raises ST_WAIT_TIMEOUT in the status word, all roles leave their loops, tensor
+// memory is released and the kernel returns.
 #include "common.cuh"
 #include "kernels.cuh"
 #include "tc_dequant.cuh"
@@ -36,428 +39,619 @@ namespace tie {
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;
-constexpr int TC_PRODUCERS = 256;
-constexpr int TC_PWARPS = TC_PRODUCERS / 32;
-constexpr int TC_THREADS = TC_PRODUCERS + 96;  // + two MMA-issuer warps + TMA warp
+constexpr int TC_NT = TC_TOKEN_TILE;  // tokens per tile (N of the MMAs, at most)
+constexpr int TC_PWARPS = 8;		  // producer warps
+constexpr int TC_DWARPS = 8;		  // drain warps
+constexpr int TC_MWARPS = 2;		  // MMA issuer warps: one per accumulator buffer
+constexpr int TC_THREADS = (TC_PWARPS + TC_DWARPS + TC_MWARPS + 1) * 32;
+constexpr int TC_S = 7;	  // ring stages: weight tiles in tensor memory, token tiles in shared memory
+constexpr int TC_XT = 2;  // 64-wide tiles of sub-block sums per work item, at most (k <= 4096)
 constexpr long long TC_WAIT_CYCLES = 1ll << 30;	 // about half a second of SM clocks
-constexpr float TC_H_SCALE = 1.0f / 256.0f;  // keeps SwiGLU outputs inside fp16 range; exact (power of two)
+constexpr float TC_H_SCALE = 1.0f / 256.0f;	 // keeps SwiGLU outputs inside fp16 range; exact (power of two)
 
-template <int NMAT, int NT>
-struct TcCfg {
-	static constexpr int B_TILE = NT * TC_BK * 2;  // bytes of one (hi or lo) token tile
-	static constexpr int B_STAGE = 2 * B_TILE;
-	static constexpr int A_COLS = 32;  // TMEM columns of one 128 x 64 fp16 weight tile
-	// stack B_hi / B_lo along N when the doubled accumulators still leave room for weight stages
-	static constexpr bool CONCAT = NMAT * 2 * NT <= 256;
-	static constexpr int ACC_PER_MAT = CONCAT ? 2 * NT : NT;
-	static constexpr int ACC_COLS = NMAT * ACC_PER_MAT;
-	// With one matrix and a 64-token tile the CTA needs only half of an SM's tensor memory and
-	// shared memory: two CTAs then share an SM and hide each other's latencies.
-	static constexpr bool HALF_SM = ACC_COLS + 2 * NMAT * 2 * A_COLS <= 256;
-	static constexpr int TMEM_COLS = HALF_SM ? 256 : 512;
-	static constexpr int STAGES_RAW = (TMEM_COLS - ACC_COLS) / (NMAT * 2 * A_COLS);
-	static constexpr int STAGES = STAGES_RAW > 4 ? 4 : STAGES_RAW;	// weight stages (tensor memory)
-	static constexpr int SB_RAW = ((HALF_SM ? 100 : 200) * 1024) / B_STAGE;
-	static constexpr int SB = SB_RAW > 8 ? 8 : SB_RAW;  // token-operand stages (shared memory)
-	static constexpr int SMEM = SB * B_STAGE + 1024 /* alignment slack */ + 512 /* barriers */;
-	static constexpr int CTAS_PER_SM = HALF_SM ? 2 : 1;
-	static_assert(STAGES >= 2 && SB >= 2, "need at least two stages");
-	static_assert(ACC_COLS + STAGES * NMAT * 2 * A_COLS <= TMEM_COLS, "tensor memory budget");
-};
+// tensor-memory columns
+constexpr uint32_t TC_COL_P = 0;      // 2 x 64: P partial sums
+constexpr uint32_t TC_COL_M = 128;    // 2 x 64: M partial sums
+constexpr uint32_t TC_COL_AM = 256;   // 2 x 8:  A tile of the M step (8 mins + 8 zeros per row)
+constexpr uint32_t TC_COL_A = 288;    // TC_S x 32: A ring
+constexpr uint32_t TC_TMEM_COLS = 512;
+static_assert(TC_COL_A + TC_S * 32 <= TC_TMEM_COLS, "tensor memory budget");
+
+constexpr int TC_B_TILE = TC_NT * TC_BK * 2;  // bytes of one (hi or lo) token tile
+constexpr int TC_B_STAGE = 2 * TC_B_TILE;
+constexpr int TC_SMEM = TC_S * TC_B_STAGE + 2 * TC_XT * TC_B_STAGE + 1024 /* alignment slack */ + 512 /* barriers */;
 
 struct TcShared {
-	uint64_t full[4];    // weight stage written by the producers
-	uint64_t empty[4];   // weight stage consumed by the MMAs
-	uint64_t bfull[8];   // token tiles landed (TMA transaction bytes)
-	uint64_t bempty[8];  // token tiles consumed
-	uint64_t done;
+	uint64_t full[TC_S];	 // weight stage written by the producers
+	uint64_t bfull[TC_S];	 // token tiles of the stage landed (TMA transaction bytes)
+	uint64_t empty[TC_S];	 // stage consumed by the MMAs (both operands)
+	uint64_t pfull[2];	 // accumulator buffer complete (one super-block)
+	uint64_t pempty[2];	 // accumulator buffer read out by the drain warps
+	uint64_t xfull[2];	 // sub-block sums of a work item landed
+	uint64_t xempty[2];	 // ... and consumed
 	uint32_t tmem_base;
 	uint32_t abort;
 };
 
+// Optional cycle accounting per role (compile with -DTC_TIMING): lane 0 of one warp per role adds
+// its clock64() deltas to g_tc_cycles; tie_debug_tc_cycles() reads and clears them.
+#ifdef TC_TIMING
+__device__ unsigned long long g_tc_cycles[32];
+__device__ long long g_tc_trace[8][128];
+#define TCT_TRACE(r, i)                                             \
+	do {                                                        \
+		if (blockIdx.x == 0 && (i) < 128u && (lane) == 0)   \
+			g_tc_trace[r][i] = clock64();               \
+	} while (0)
+#define TCT_DECL(n) long long tct_[n] = {0}
+#define TCT_NOW() clock64()
+#define TCT_ADD(i, t0) tct_[i] += clock64() - (t0)
+#define TCT_FLUSH(base, n)                                                        \
+	do {                                                                      \
+		for (int i_ = 0; i_ < (n); i_++)                                  \
+			atomicAdd(&g_tc_cycles[(base) + i_], (unsigned long long)tct_[i_]); \
+	} while (0)
+#else
+#define TCT_DECL(n)
+#define TCT_NOW() 0ll
+#define TCT_ADD(i, t0) (void)(t0)
+#define TCT_FLUSH(base, n)
+#define TCT_TRACE(r, i)
+#endif
+
 // Bounded wait: false (and the abort flag raised) when the barrier does not flip in time or
-// another CTA has already reported a timeout.  The cycle counter is read only after many failed
-// polls.
+// another role / CTA has already reported a timeout.  After a first miss the thread lets the
+// hardware suspend it between polls, so that waiting roles do not take issue slots from the
+// producers.
 __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, unsigned *status)
 {
-	long long t0 = 0;
+	if (ptx::mbar_try_wait(bar, parity))
+		return true;
+	const long long t0 = clock64();
 	uint32_t spins = 0;
-	while (!ptx::mbar_try_wait(bar, parity)) {
-		if ((++spins & 1023u) == 0) {
-			if (*abort_flag)
-				return false;
-			const long long now = clock64();
-			if (t0 == 0)
-				t0 = now;
-			if (now - t0 > TC_WAIT_CYCLES || (*(volatile unsigned *)status & ST_WAIT_TIMEOUT)) {
-				atomicOr(status, ST_WAIT_TIMEOUT);
-				*abort_flag = 1;
-				return false;
-			}
+	while (!ptx::mbar_try_wait_suspend(bar, parity, 20000u)) {
+		if (*abort_flag)
+			return false;
+		if (clock64() - t0 > TC_WAIT_CYCLES || ((++spins & 255u) == 0 && (*(volatile unsigned *)status & ST_WAIT_TIMEOUT))) {
+			atomicOr(status, ST_WAIT_TIMEOUT);
+			*abort_flag = 1;
+			return false;
 		}
 	}
 	return true;
 }
 
-// One 8-wide k chunk (4 half2 words of hi, 4 of lo) of this thread's row -> 4 TMEM columns of the
-// thread's lane in the hi and in the lo tile (2 halves per 32-bit column; c = chunk index 0..7).
-__device__ __forceinline__ void put_chunk(uint32_t tile_hi, uint32_t tile_lo, uint32_t c, const uint32_t h0[2], const uint32_t h1[2],
-					  const uint32_t l0[2], const uint32_t l1[2])
+// One lane polls for its warp; the verdict is shared.
+__device__ __forceinline__ bool tc_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, unsigned *status, int lane)
 {
-	ptx::tmem_st4(tile_hi + 4 * c, h0[0], h0[1], h1[0], h1[1]);
-	ptx::tmem_st4(tile_lo + 4 * c, l0[0], l0[1], l1[0], l1[1]);
+	int ok = 1;
+	if (lane == 0)
+		ok = tc_wait(bar, parity, abort_flag, status) ? 1 : 0;
+	return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
-// Packed weights one producer thread needs for two consecutive k stages (128 k, "group" g) of
-// its matrix row.  With two matrices (gate/up) a thread owns all 64 k of a stage for one
-// (row, matrix); with one matrix (down) it owns the 32-k half-slice hs of a stage.
-template <WKind KIND, int NMAT>
+// A work item: token tile `slot` (expert le, sorted rows [row0, row0 + n_valid)) x 128-row tile.
+struct TcItem {
+	int le, row0, n_valid, n_mma;
+	int mat_sel, m0;  // which matrix (RAW: 0 gate, 1 up) and first row inside it
+};
+
+__device__ __forceinline__ TcItem tc_item(int t, int m_tiles, const int4 *__restrict__ tile_info, int rows_per_matrix)
+{
+	TcItem it;
+	const int slot = t / m_tiles, mt = t - slot * m_tiles;
+	const int4 ti = __ldg(tile_info + slot);
+	it.le = ti.x;
+	it.row0 = ti.y;
+	it.n_valid = ti.z;
+	it.n_mma = (ti.z + 15) & ~15;
+	it.mat_sel = (mt * TC_BM) / rows_per_matrix;
+	it.m0 = mt * TC_BM - it.mat_sel * rows_per_matrix;
+	return it;
+}
+
+// Packed weights one producer thread needs for two consecutive k stages (128 k, "group" g) of its
+// row: the thread owns the 32-k half-slice hs of each 64-k stage.
+template <WKind KIND>
 struct RawGroup;
 
-template <int NMAT>
-struct RawGroup<W_Q4K, NMAT> {
-	static constexpr int NQ = (NMAT == 2) ? 2 : 1;
-	uint4 hdr;
-	uint4 q[2][NQ];
+template <>
+struct RawGroup<W_Q4K> {
+	uint4 hdr;   // d | dmin, 12 bytes of 6-bit scales and mins
+	uint4 q[2];  // 16 bytes of quants per stage
 	__device__ __forceinline__ void load(const uint8_t *wexp, int nb, int row, int g, int hs)
 	{
 		const uint8_t *blk = wexp + ((size_t)row * nb + (g >> 1)) * Q4K_BYTES;
 		hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
 #pragma unroll
-		for (int st = 0; st < 2; st++) {
-			const uint4 *base = reinterpret_cast<const uint4 *>(blk + 16 + 32 * ((g & 1) * 2 + st));
-			if (NMAT == 2) {
-				q[st][0] = __ldg(base);
-				q[st][NQ - 1] = __ldg(base + 1);
-			} else {
-				q[st][0] = __ldg(base + hs);
-			}
-		}
+		for (int st = 0; st < 2; st++)
+			q[st] = __ldg(reinterpret_cast<const uint4 *>(blk + 16 + 32 * ((g & 1) * 2 + st)) + hs);
 	}
-	// writes this thread's chunks of stage (2g + st) into the hi/lo tiles
-	__device__ __forceinline__ void emit(int g, int st, int hs, uint32_t tile_hi, uint32_t tile_lo) const
+	// this thread's 32 weights of stage (2g + st) -> 16 columns of its lane in the A tile
+	__device__ __forceinline__ void emit(int g, int st, int hs, uint32_t tile) const
 	{
 		const int p = (g & 1) * 2 + st;
-		const float d = half_bits_to_float(hdr.x & 0xffffu), dmin = half_bits_to_float(hdr.x >> 16);
 		const uint32_t sc[3] = {hdr.y, hdr.z, hdr.w};
 		int s_lo, m_lo, s_hi, m_hi;
 		q4k_scale_min(sc, 2 * p, s_lo, m_lo);
 		q4k_scale_min(sc, 2 * p + 1, s_hi, m_hi);
-		const H2x4 cl = q4k_consts(__fmul_rn(d, (float)s_lo), __fmul_rn(dmin, (float)m_lo));
-		const H2x4 ch = q4k_consts(__fmul_rn(d, (float)s_hi), __fmul_rn(dmin, (float)m_hi));
-		constexpr int NWORD = 4 * NQ;
-		uint32_t w[NWORD];
+		const Q4kConsts c = q4k_int_consts(s_lo, s_hi);
+		const uint32_t w[4] = {q[st].x, q[st].y, q[st].z, q[st].w};
 #pragma unroll
-		for (int i = 0; i < NQ; i++) {
-			w[4 * i] = q[st][i].x;
-			w[4 * i + 1] = q[st][i].y;
-			w[4 * i + 2] = q[st][i].z;
-			w[4 * i + 3] = q[st][i].w;
+		for (int cc = 0; cc < 2; cc++) {
+			uint32_t l0[2], h0[2], l1[2], h1[2];
+			q4k_int_word(w[2 * cc], c, l0, h0);
+			q4k_int_word(w[2 * cc + 1], c, l1, h1);
+			ptx::tmem_st4(tile + 4u * (2u * hs + cc), l0[0], l0[1], l1[0], l1[1]);	     // k = 16 hs + 8 cc ..
+			ptx::tmem_st4(tile + 4u * (4u + 2u * hs + cc), h0[0], h0[1], h1[0], h1[1]);  // k = 32 + 16 hs + 8 cc ..
 		}
-		const uint32_t c0 = (NMAT == 2) ? 0u : 2u * hs;	 // first chunk of the low-nibble half
+	}
+	// A tile of the M step of super-block sbi: the 8 mins of the row in the half of the 16-deep
+	// step that belongs to this super-block (sub-block sums of two super-blocks share a step).
+	__device__ __forceinline__ void emit_mins(int sbi, uint32_t tile) const
+	{
+		const uint32_t sc[3] = {hdr.y, hdr.z, hdr.w};
+		uint32_t mm[4];
 #pragma unroll
-		for (int cc = 0; cc < NWORD / 2; cc++) {
-			uint32_t h0[2], l0[2], h1[2], l1[2];
-			q4k_word(w[2 * cc], 0, cl, h0, l0);
-			q4k_word(w[2 * cc + 1], 0, cl, h1, l1);
-			put_chunk(tile_hi, tile_lo, c0 + cc, h0, h1, l0, l1);
-			q4k_word(w[2 * cc], 4, ch, h0, l0);
-			q4k_word(w[2 * cc + 1], 4, ch, h1, l1);
-			put_chunk(tile_hi, tile_lo, 4u + c0 + cc, h0, h1, l0, l1);
+		for (int j = 0; j < 4; j++) {
+			int s0, m0, s1, m1;
+			q4k_scale_min(sc, 2 * j, s0, m0);
+			q4k_scale_min(sc, 2 * j + 1, s1, m1);
+			mm[j] = h2_bits(__floats2half2_rn((float)m0, (float)m1));
 		}
+		const uint32_t odd = (uint32_t)(sbi & 1);
+		ptx::tmem_st4(tile + 4u * odd, mm[0], mm[1], mm[2], mm[3]);
+		ptx::tmem_st4(tile + 4u * (odd ^ 1u), 0u, 0u, 0u, 0u);
 	}
 };
 
-template <int NMAT>
-struct RawGroup<W_Q6K_R8, NMAT> {
-	static constexpr int NL = (NMAT == 2) ? 2 : 1;	// 16-wide l slices this thread owns
-	uint4 a[NL], b[NL], h[NL];
-	uint32_t scw[NL];
-	float d;
+template <>
+struct RawGroup<W_Q6K_R8> {
+	uint4 a, b, h;
+	uint32_t scw;
 	__device__ __forceinline__ void load(const uint8_t *wexp, int nb, int row, int g, int hs)
 	{
 		const uint8_t *grp = wexp + (size_t)(row >> 3) * q6k_r8_group_bytes(nb);
-		const int r8 = row & 7, kb = g >> 1, n = g & 1;
-#pragma unroll
-		for (int i = 0; i < NL; i++) {
-			const int l16 = (NMAT == 2) ? i : hs;
-			const int pp = n * 2 + l16;
-			const uint4 *ch = reinterpret_cast<const uint4 *>(grp + q6k_r8_chunk_off(nb, r8, kb, pp));
-			a[i] = __ldg(ch);
-			b[i] = __ldg(ch + 1);
-			h[i] = __ldg(ch + 2);
-			scw[i] = __ldg(reinterpret_cast<const uint32_t *>(grp + q6k_r8_scale_off(nb, r8, kb, pp)));
-		}
-		d = half_bits_to_float(__ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb, r8, kb))));
+		const int r8 = row & 7, kb = g >> 1, pp = (g & 1) * 2 + hs;
+		const uint4 *ch = reinterpret_cast<const uint4 *>(grp + q6k_r8_chunk_off(nb, r8, kb, pp));
+		a = __ldg(ch);
+		b = __ldg(ch + 1);
+		h = __ldg(ch + 2);
+		scw = __ldg(reinterpret_cast<const uint32_t *>(grp + q6k_r8_scale_off(nb, r8, kb, pp)));
 	}
-	__device__ __forceinline__ void emit(int g, int st, int hs, uint32_t tile_hi, uint32_t tile_lo) const
+	__device__ __forceinline__ void emit(int g, int st, int hs, uint32_t tile) const
 	{
+		const float fA = (float)(int)(signed char)((scw >> (16 * st)) & 0xff);
+		const float fB = (float)(int)(signed char)((scw >> (16 * st + 8)) & 0xff);
+		const __half2 sA = __float2half2_rn(fA), cA = __float2half2_rn(-96.0f * fA);
+		const __half2 sB = __float2half2_rn(fB), cB = __float2half2_rn(-96.0f * fB);
+		const uint32_t A[4] = {a.x, a.y, a.z, a.w}, B[4] = {b.x, b.y, b.z, b.w}, Hh[4] = {h.x, h.y, h.z, h.w};
+		uint32_t qa[4], qb[4];
 #pragma unroll
-		for (int i = 0; i < NL; i++) {
-			const uint32_t l16 = (NMAT == 2) ? (uint32_t)i : (uint32_t)hs;
-			const float sA = __fmul_rn(d, (float)(int)(signed char)((scw[i] >> (16 * st)) & 0xff));
-			const float sB = __fmul_rn(d, (float)(int)(signed char)((scw[i] >> (16 * st + 8)) & 0xff));
-			__half2 sAh, sAr, sBh, sBr;
-			q6k_consts(sA, sAh, sAr);
-			q6k_consts(sB, sBh, sBr);
-			const uint32_t A[4] = {a[i].x, a[i].y, a[i].z, a[i].w}, B[4] = {b[i].x, b[i].y, b[i].z, b[i].w};
-			const uint32_t Hh[4] = {h[i].x, h[i].y, h[i].z, h[i].w};
-			uint32_t qa[4], qb[4];
-#pragma unroll
-			for (int k = 0; k < 4; k++) {
-				if (st == 0) {
-					qa[k] = (A[k] & 0x0F0F0F0Fu) | ((Hh[k] << 4) & 0x30303030u);
-					qb[k] = (B[k] & 0x0F0F0F0Fu) | ((Hh[k] << 2) & 0x30303030u);
-				} else {
-					qa[k] = ((A[k] >> 4) & 0x0F0F0F0Fu) | (Hh[k] & 0x30303030u);
-					qb[k] = ((B[k] >> 4) & 0x0F0F0F0Fu) | ((Hh[k] >> 2) & 0x30303030u);
-				}
-			}
-#pragma unroll
-			for (int cc = 0; cc < 2; cc++) {
-				uint32_t h0[2], l0[2], h1[2], l1[2];
-				q6k_word(qa[2 * cc], sAh, sAr, h0, l0);
-				q6k_word(qa[2 * cc + 1], sAh, sAr, h1, l1);
-				put_chunk(tile_hi, tile_lo, 2u * l16 + cc, h0, h1, l0, l1);
-				q6k_word(qb[2 * cc], sBh, sBr, h0, l0);
-				q6k_word(qb[2 * cc + 1], sBh, sBr, h1, l1);
-				put_chunk(tile_hi, tile_lo, 4u + 2u * l16 + cc, h0, h1, l0, l1);
+		for (int k = 0; k < 4; k++) {
+			if (st == 0) {
+				qa[k] = (A[k] & 0x0F0F0F0Fu) | ((Hh[k] << 4) & 0x30303030u);
+				qb[k] = (B[k] & 0x0F0F0F0Fu) | ((Hh[k] << 2) & 0x30303030u);
+			} else {
+				qa[k] = ((A[k] >> 4) & 0x0F0F0F0Fu) | (Hh[k] & 0x30303030u);
+				qb[k] = ((B[k] >> 4) & 0x0F0F0F0Fu) | ((Hh[k] >> 2) & 0x30303030u);
 			}
 		}
+#pragma unroll
+		for (int cc = 0; cc < 2; cc++) {
+			uint32_t v0[2], v1[2];
+			q6k_int_word(qa[2 * cc], sA, cA, v0);
+			q6k_int_word(qa[2 * cc + 1], sA, cA, v1);
+			ptx::tmem_st4(tile + 4u * (2u * hs + cc), v0[0], v0[1], v1[0], v1[1]);
+			q6k_int_word(qb[2 * cc], sB, cB, v0);
+			q6k_int_word(qb[2 * cc + 1], sB, cB, v1);
+			ptx::tmem_st4(tile + 4u * (4u + 2u * hs + cc), v0[0], v0[1], v1[0], v1[1]);
+		}
 	}
+	__device__ __forceinline__ void emit_mins(int, uint32_t) const {}
 };
 
-// RAW (one matrix only): the products are stored as fp32 in expert-sorted row order,
-// out[row0 + n][matrix * rows + mrow], for a separate SwiGLU pass; blockIdx.x then runs over the
-// row tiles of w0 followed by those of w1 (gate, up).
-template <WKind KIND, int NMAT, int NT, bool RAW>
-__global__ void __launch_bounds__(TC_THREADS, (TcCfg<NMAT, NT>::CTAS_PER_SM))
-grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__ CUtensorMap tm_lo,
-		const uint8_t *__restrict__ w0, const uint8_t *__restrict__ w1, size_t expert_stride, int k_dim,
-		const int *__restrict__ offsets, const int *__restrict__ tile_start, int n_local,
-		__half *__restrict__ h_hi, __half *__restrict__ h_lo, float *__restrict__ y, const int *__restrict__ perm,
-		int out_stride, const float *__restrict__ silu, unsigned *__restrict__ status, int rows_per_matrix)
+// fp32 block factors (d, dmin) of (row, super-block) for the drain warps.
+template <WKind KIND>
+__device__ __forceinline__ float2 tc_block_factors(const uint8_t *wexp, int nb, int row, int sbi)
 {
-	static_assert(!RAW || NMAT == 1, "raw output is for the one-matrix kernel");
-	using Cfg = TcCfg<NMAT, NT>;
-	constexpr int S = Cfg::STAGES, SB = Cfg::SB;
-	constexpr bool CONCAT = Cfg::CONCAT;
-	extern __shared__ uint8_t smem_raw[];
+	if (KIND == W_Q4K) {
+		const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(wexp + ((size_t)row * nb + sbi) * Q4K_BYTES));
+		return make_float2(half_bits_to_float(v & 0xffffu), half_bits_to_float(v >> 16));
+	}
+	const uint8_t *grp = wexp + (size_t)(row >> 3) * q6k_r8_group_bytes(nb);
+	const unsigned short v = __ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb, row & 7, sbi)));
+	return make_float2(half_bits_to_float(v), 0.0f);
+}
 
-	// ---- which (expert, token tile) is this CTA? ----
-	const int slot = blockIdx.y;
-	__shared__ int s_skip;
+// RAW: products are stored as fp32 in expert-sorted row order, y[row0 + n][matrix * rows + mrow]
+// (gate | up of one row side by side) for the SwiGLU pass; the 128-row tiles then run over w0
+// followed by w1.  Otherwise (down) rows are scattered to y[perm[row0 + n]][mrow] * out_scale.
+template <WKind KIND, bool RAW>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+grouped_gemm_sb(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__ CUtensorMap tm_lo,
+		const __grid_constant__ CUtensorMap tq_hi, const __grid_constant__ CUtensorMap tq_lo, const uint8_t *__restrict__ w0,
+		const uint8_t *__restrict__ w1, size_t expert_stride, int k_dim, const int4 *__restrict__ tile_info,
+		const int *__restrict__ tile_start, int n_local, int m_tiles, float *__restrict__ y, const int *__restrict__ perm,
+		int out_stride, float out_scale, unsigned *__restrict__ status, int rows_per_matrix)
+{
+	extern __shared__ uint8_t smem_raw[];
+	__shared__ int s_total;
 	if (threadIdx.x == 0)
-		s_skip = (slot >= tile_start[n_local]) || (*(volatile unsigned *)status & ST_WAIT_TIMEOUT);
+		s_total = (*(volatile unsigned *)status & ST_WAIT_TIMEOUT) ? 0 : tile_start[n_local] * m_tiles;
 	__syncthreads();
-	if (s_skip)
+	const int total = s_total;
+	if ((int)blockIdx.x >= total)
 		return;
-	int lo_e = 0, hi_e = n_local - 1;  // largest le with tile_start[le] <= slot
-	while (lo_e < hi_e) {
-		int mid = (lo_e + hi_e + 1) >> 1;
-		if (tile_start[mid] <= slot)
-			lo_e = mid;
-		else
-			hi_e = mid - 1;
-	}
-	const int le = lo_e;
-	const int row0 = offsets[le] + (slot - tile_start[le]) * NT;
-	const int n_valid = min(NT, offsets[le + 1] - row0);
-	if (n_valid <= 0) {
-		if (threadIdx.x == 0)
-			atomicOr(status, ST_BAD_TILE);
-		return;
-	}
-	const int n_mma = (n_valid + 15) & ~15;	 // N of the MMAs: the tile's tokens rounded up to 16
-	const int mat_sel = RAW ? (int)(blockIdx.x * TC_BM) / rows_per_matrix : 0;  // RAW: 0 = w0 (gate), 1 = w1 (up)
-	const int m0 = blockIdx.x * TC_BM - mat_sel * rows_per_matrix;
 	const int nb = k_dim / QK_K;
 	const int k_iters = k_dim / TC_BK;
+	const int xt_n = (nb + 7) >> 3;
 
 	const uint32_t raw = ptx::smem_u32(smem_raw);
 	const uint32_t tiles = (raw + 1023u) & ~1023u;
-	TcShared *sh = reinterpret_cast<TcShared *>(smem_raw + (tiles - raw) + (size_t)SB * Cfg::B_STAGE);
+	const uint32_t xq_base = tiles + TC_S * TC_B_STAGE;
+	TcShared *sh = reinterpret_cast<TcShared *>(smem_raw + (tiles - raw) + (size_t)(TC_S + 2 * TC_XT) * TC_B_STAGE);
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-	// token tiles of ring stage sb: hi at the start; lo right behind the rows in use when the two
-	// are stacked along N, else in the second half of the stage
-	auto b_hi = [&](int sb) -> uint32_t { return tiles + sb * Cfg::B_STAGE; };
-	auto b_lo = [&](int sb) -> uint32_t { return tiles + sb * Cfg::B_STAGE + (CONCAT ? n_mma * 128 : Cfg::B_TILE); };
-	// TMEM column of weight tile (stage, matrix, hi/lo)
-	auto a_col = [&](int s, int m, int hl) -> uint32_t { return Cfg::ACC_COLS + (s * NMAT * 2 + m * 2 + hl) * Cfg::A_COLS; };
+	auto b_hi = [&](int sb) -> uint32_t { return tiles + sb * TC_B_STAGE; };
+	auto b_lo = [&](int sb) -> uint32_t { return tiles + sb * TC_B_STAGE + TC_B_TILE; };
+	auto xq_tile = [&](int tp, int xt, int hl) -> uint32_t { return xq_base + ((tp * TC_XT + xt) * 2 + hl) * TC_B_TILE; };
 
 	if (threadIdx.x == 0) {
-		for (int s = 0; s < S; s++) {
+		for (int s = 0; s < TC_S; s++) {
 			ptx::mbar_init(ptx::smem_u32(&sh->full[s]), TC_PWARPS);
-			ptx::mbar_init(ptx::smem_u32(&sh->empty[s]), NMAT);
-		}
-		for (int s = 0; s < SB; s++) {
+			ptx::mbar_init(ptx::smem_u32(&sh->empty[s]), 1);
 			ptx::mbar_init(ptx::smem_u32(&sh->bfull[s]), 1);
-			ptx::mbar_init(ptx::smem_u32(&sh->bempty[s]), NMAT);
 		}
-		ptx::mbar_init(ptx::smem_u32(&sh->done), NMAT);
+		for (int s = 0; s < 2; s++) {
+			ptx::mbar_init(ptx::smem_u32(&sh->pfull[s]), 1);
+			ptx::mbar_init(ptx::smem_u32(&sh->pempty[s]), TC_DWARPS);
+			ptx::mbar_init(ptx::smem_u32(&sh->xfull[s]), 1);
+			ptx::mbar_init(ptx::smem_u32(&sh->xempty[s]), TC_MWARPS);
+		}
 		sh->abort = 0;
 		ptx::fence_barrier_init();
 		ptx::fence_proxy_async_smem();
 	}
-	if (warp == TC_PWARPS) {  // first MMA warp owns the tensor-memory allocation
-		ptx::tmem_alloc(ptx::smem_u32(&sh->tmem_base), Cfg::TMEM_COLS);
+	if (warp == TC_PWARPS + TC_DWARPS) {  // the MMA warp owns the tensor-memory allocation
+		ptx::tmem_alloc(ptx::smem_u32(&sh->tmem_base), TC_TMEM_COLS);
 		ptx::tmem_relinquish();
 	}
-	if (warp == TC_PWARPS + 2 && lane == 0) {
+	if (warp == TC_PWARPS + TC_DWARPS + TC_MWARPS && lane == 0) {
 		ptx::prefetch_tmap(&tm_hi);
 		ptx::prefetch_tmap(&tm_lo);
+		if (KIND == W_Q4K) {
+			ptx::prefetch_tmap(&tq_hi);
+			ptx::prefetch_tmap(&tq_lo);
+		}
 	}
 	ptx::tc_fence_before();
 	__syncthreads();
 	ptx::tc_fence_after();
 	const uint32_t tmem = sh->tmem_base;
 	volatile uint32_t *abort_flag = &sh->abort;
+	const int stride_t = gridDim.x;
 
 	if (warp < TC_PWARPS) {
-		// ================= producers: packed blocks -> hi/lo weight tiles in tensor memory =================
-		// thread = (row, matrix) for gate/up, (row, half-slice) for down
-		const int row = threadIdx.x & 127, sel = threadIdx.x >> 7;
-		const int m = (NMAT == 2) ? sel : 0, hs = (NMAT == 2) ? 0 : sel;
-		const uint8_t *wexp = (((NMAT == 2 && sel) || (RAW && mat_sel)) ? w1 : w0) + (size_t)le * expert_stride;
+		// ================= producers: packed blocks -> integer A tiles in tensor memory =================
+		const int row = threadIdx.x & 127, hs = threadIdx.x >> 7;
 		const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
 		const int n_groups = k_iters >> 1;
-		RawGroup<KIND, NMAT> cur, nxt;
-		cur.load(wexp, nb, m0 + row, 0, hs);
+		int s = 0;
+		uint32_t ph = 0, it = 0, g = 0;
+		// Load cursor: runs three 128-k groups (about 5000 cycles of work, several HBM latencies)
+		// ahead of the group being expanded, across work items.
+		int lt = blockIdx.x, lgi = 0;
+		TcItem litem = tc_item(lt, m_tiles, tile_info, rows_per_matrix);
+		const uint8_t *lwexp = (litem.mat_sel ? w1 : w0) + (size_t)litem.le * expert_stride;
+		bool lvalid = true;
+		auto fetch = [&](RawGroup<KIND> &dst) {
+			if (!lvalid)
+				return;
+			dst.load(lwexp, nb, litem.m0 + row, lgi, hs);
+			if (++lgi == n_groups) {
+				lgi = 0;
+				lt += stride_t;
+				lvalid = lt < total;
+				if (lvalid) {
+					litem = tc_item(lt, m_tiles, tile_info, rows_per_matrix);
+					lwexp = (litem.mat_sel ? w1 : w0) + (size_t)litem.le * expert_stride;
+				}
+			}
+		};
+		RawGroup<KIND> q0, q1, q2, fresh;
+		fetch(q0);
+		fetch(q1);
+		fetch(q2);
 		bool alive = true;
-		for (int g = 0; g < n_groups && alive; g++) {
-			if (g + 1 < n_groups)
-				nxt.load(wexp, nb, m0 + row, g + 1, hs);
+		TCT_DECL(5);
+		const long long tct_start = TCT_NOW();
+		int t = blockIdx.x, gi = 0;
+		while (alive) {
+			fetch(fresh);
 #pragma unroll
 			for (int st = 0; st < 2; st++) {
-				const int it = 2 * g + st;
-				const int s = it % S;
-				if (it >= S) {	// one lane polls the barrier for its warp
-					int ok = 1;
-					if (lane == 0)
-						ok = tc_wait(ptx::smem_u32(&sh->empty[s]), ((it / S) & 1) ^ 1, abort_flag, status) ? 1 : 0;
-					ok = __shfl_sync(0xffffffffu, ok, 0);
-					if (!ok) {
+				const long long tw = TCT_NOW();
+				if (it >= (uint32_t)TC_S) {
+					if (!tc_wait_warp(ptx::smem_u32(&sh->empty[s]), ph ^ 1u, abort_flag, status, lane)) {
 						alive = false;
 						break;
 					}
 					ptx::tc_fence_after();
 				}
-				cur.emit(g, st, hs, lane_base + a_col(s, m, 0), lane_base + a_col(s, m, 1));
+				TCT_ADD(0, tw);
+				if (warp == 0)
+					TCT_TRACE(0, it);
+				const long long te = TCT_NOW();
+				// first stage of a super-block: the A tile of its M step (rows are owned by the hs = 0 warps)
+				if (KIND == W_Q4K && st == 0 && (gi & 1) == 0 && hs == 0)
+					q0.emit_mins(gi >> 1, lane_base + TC_COL_AM + 8u * (g & 1u));
+				q0.emit(gi, st, hs, lane_base + TC_COL_A + 32u * s);
+				TCT_ADD(1, te);
+				const long long ts = TCT_NOW();
 				ptx::tmem_st_wait();
+				TCT_ADD(2, ts);
 				ptx::tc_fence_before();
 				__syncwarp();
-				if (lane == 0)	// one arrival per producer warp
+				if (lane == 0)
 					ptx::mbar_arrive(ptx::smem_u32(&sh->full[s]));
+				if (warp == 0)
+					TCT_TRACE(1, it);
+				if (warp == 7)
+					TCT_TRACE(2, it);
+				it++;
+				if (++s == TC_S) {
+					s = 0;
+					ph ^= 1u;
+				}
 			}
-			cur = nxt;
+			if (gi & 1)
+				g++;
+			q0 = q1;
+			q1 = q2;
+			q2 = fresh;
+			if (++gi == n_groups) {
+				gi = 0;
+				t += stride_t;
+				if (t >= total)
+					break;
+			}
 		}
-	} else if (warp < TC_PWARPS + NMAT) {
-		// ================= MMA issuers: one thread per weight matrix =================
-		if (lane == 0) {
-			const int m = warp - TC_PWARPS;
-			const uint32_t d = tmem + m * Cfg::ACC_PER_MAT;
-			const uint32_t idesc_n = ptx::umma_idesc_f16(TC_BM, n_mma);
-			const uint32_t idesc_2n = ptx::umma_idesc_f16(TC_BM, 2 * n_mma);
-			for (int it = 0; it < k_iters; it++) {
-				const int s = it % S, sb = it % SB;
-				if (!tc_wait(ptx::smem_u32(&sh->bfull[sb]), (it / SB) & 1, abort_flag, status))
+		TCT_ADD(3, tct_start);
+#ifdef TC_TIMING
+		tct_[4] = it;
+#endif
+		if (threadIdx.x == 0)
+			TCT_FLUSH(0, 5);
+	} else if (warp < TC_PWARPS + TC_DWARPS) {
+		// ================= drain warps: super-block partial sums -> fp32 rows =================
+		const int dw = warp - TC_PWARPS, quad = warp & 3, chalf = dw >> 2;
+		const int c0 = chalf * (TC_NT / 2);
+		const uint32_t tlane = tmem + ((uint32_t)(quad * 32) << 16);
+		uint32_t g = 0;
+		bool alive = true;
+		TCT_DECL(4);
+		const long long tct_start = TCT_NOW();
+		for (int t = blockIdx.x; t < total && alive; t += stride_t) {
+			const TcItem item = tc_item(t, m_tiles, tile_info, rows_per_matrix);
+			const uint8_t *wexp = (item.mat_sel ? w1 : w0) + (size_t)item.le * expert_stride;
+			const int mrow = item.m0 + quad * 32 + lane;
+			float acc[TC_NT / 2];
+#pragma unroll
+			for (int j = 0; j < TC_NT / 2; j++)
+				acc[j] = 0.0f;
+			float2 fnext = tc_block_factors<KIND>(wexp, nb, mrow, 0);
+			for (int sbi = 0; sbi < nb; sbi++) {
+				const float2 f = fnext;
+				if (sbi + 1 < nb)
+					fnext = tc_block_factors<KIND>(wexp, nb, mrow, sbi + 1);
+				const uint32_t buf = g & 1u;
+				const long long tw = TCT_NOW();
+				if (!tc_wait_warp(ptx::smem_u32(&sh->pfull[buf]), (g >> 1) & 1u, abort_flag, status, lane)) {
+					alive = false;
 					break;
-				if (!tc_wait(ptx::smem_u32(&sh->full[s]), (it / S) & 1, abort_flag, status))
-					break;
+				}
+				TCT_ADD(0, tw);
+				if (warp == TC_PWARPS)
+					TCT_TRACE(5, g);
+				const long long tl = TCT_NOW();
 				ptx::tc_fence_after();
 #pragma unroll
-				for (int kk = 0; kk < TC_BK / 16; kk++) {
-					const uint64_t bh = ptx::umma_desc_sw128(b_hi(sb)) + 2 * kk;
-					const uint32_t ah = tmem + a_col(s, m, 0) + 8 * kk, al = tmem + a_col(s, m, 1) + 8 * kk;
-					const uint32_t acc = (it > 0 || kk > 0) ? 1u : 0u;
-					if (CONCAT) {
-						// columns [0, n): A_hi.B_hi + A_lo.B_hi; columns [n, 2n): A_hi.B_lo
-						ptx::mma_f16_ts(d, ah, bh, idesc_2n, acc);
-						ptx::mma_f16_ts(d, al, bh, idesc_n, 1u);
-					} else {
-						const uint64_t bl = ptx::umma_desc_sw128(b_lo(sb)) + 2 * kk;
-						ptx::mma_f16_ts(d, ah, bh, idesc_n, acc);
-						ptx::mma_f16_ts(d, al, bh, idesc_n, 1u);
-						ptx::mma_f16_ts(d, ah, bl, idesc_n, 1u);
-					}
-				}
-				ptx::mma_commit(ptx::smem_u32(&sh->empty[s]));
-				ptx::mma_commit(ptx::smem_u32(&sh->bempty[sb]));
-			}
-			ptx::mma_commit(ptx::smem_u32(&sh->done));
-		}
-	} else if (warp == TC_PWARPS + 2) {
-		// ================= TMA loader for the token operand =================
-		if (lane == 0) {
-			const int n16 = n_mma >> 4;
-			for (int it = 0; it < k_iters; it++) {
-				const int sb = it % SB;
-				if (it >= SB && !tc_wait(ptx::smem_u32(&sh->bempty[sb]), ((it / SB) & 1) ^ 1, abort_flag, status))
-					break;
-				const uint32_t fb = ptx::smem_u32(&sh->bfull[sb]);
-				// only the rows the MMA will read: 16-row boxes (2 KB each, whole swizzle groups)
-				ptx::mbar_arrive_expect_tx(fb, (uint32_t)n16 * 2u * 16u * TC_BK * 2u);
-				for (int r = 0; r < n16; r++) {
-					ptx::tma_load_2d(b_hi(sb) + r * 2048, &tm_hi, fb, it * TC_BK, row0 + 16 * r);
-					ptx::tma_load_2d(b_lo(sb) + r * 2048, &tm_lo, fb, it * TC_BK, row0 + 16 * r);
-				}
-			}
-		}
-	}
-
-	// ================= epilogue: 8 warps, TMEM lane quadrant = warp % 4, columns split in two =================
-	if (warp < TC_PWARPS) {
-		const bool ok = tc_wait(ptx::smem_u32(&sh->done), 0, abort_flag, status);
-		ptx::tc_fence_after();
-		if (ok) {
-			const int quad = warp & 3, chalf = warp >> 2;
-			const int mrow = m0 + quad * 32 + lane;
-			const uint32_t tlane = tmem + ((uint32_t)(quad * 32) << 16);
-			for (int c0 = chalf * (NT / 2); c0 < (chalf + 1) * (NT / 2); c0 += 16) {
-				if (c0 >= n_valid)
-					break;
-				uint32_t g[16], u[16];
-				ptx::tmem_ld16(tlane + c0, g);
-				if (NMAT == 2)
-					ptx::tmem_ld16(tlane + Cfg::ACC_PER_MAT + c0, u);
-				if (CONCAT) {
-					uint32_t g2[16], u2[16];
-					ptx::tmem_ld16(tlane + n_mma + c0, g2);
-					if (NMAT == 2)
-						ptx::tmem_ld16(tlane + Cfg::ACC_PER_MAT + n_mma + c0, u2);
-					ptx::tmem_ld_wait();
+				for (int hf = 0; hf < 2; hf++) {
+					if (c0 + 16 * hf < item.n_mma) {  // warp-uniform
+						uint32_t p[16], m[16];
+						ptx::tmem_ld16(tlane + TC_COL_P + 64u * buf + c0 + 16 * hf, p);
+						if (KIND == W_Q4K)
+							ptx::tmem_ld16(tlane + TC_COL_M + 64u * buf + c0 + 16 * hf, m);
+						ptx::tmem_ld_wait();
 #pragma unroll
-					for (int j = 0; j < 16; j++) {
-						g[j] = __float_as_uint(__uint_as_float(g[j]) + __uint_as_float(g2[j]));
-						if (NMAT == 2)
-							u[j] = __float_as_uint(__uint_as_float(u[j]) + __uint_as_float(u2[j]));
-					}
-				} else {
-					ptx::tmem_ld_wait();
-				}
-#pragma unroll
-				for (int j = 0; j < 16; j++) {
-					const int n = c0 + j;
-					if (n < n_valid) {
-						if (NMAT == 2) {
-							float hv = swiglu_lut(silu, __uint_as_float(g[j]), __uint_as_float(u[j])) * TC_H_SCALE;
-							__half hh = __float2half_rn(hv);
-							__half hl = __float2half_rn(hv - __half2float(hh));
-							const size_t o = (size_t)(row0 + n) * out_stride + tc_kperm(mrow);
-							h_hi[o] = hh;
-							h_lo[o] = hl;
-						} else if (RAW) {
-							y[(size_t)(row0 + n) * out_stride + (size_t)mat_sel * rows_per_matrix + mrow] = __uint_as_float(g[j]);
-						} else {
-							const int rid = perm[row0 + n];
-							y[(size_t)rid * out_stride + mrow] = __uint_as_float(g[j]) * (1.0f / TC_H_SCALE);
+						for (int j = 0; j < 16; j++) {
+							float a = __fmaf_rn(f.x, __uint_as_float(p[j]), acc[16 * hf + j]);
+							if (KIND == W_Q4K)
+								a = __fmaf_rn(-f.y, __uint_as_float(m[j]), a);
+							acc[16 * hf + j] = a;
 						}
 					}
 				}
+				ptx::tc_fence_before();
+				__syncwarp();
+				if (lane == 0)
+					ptx::mbar_arrive(ptx::smem_u32(&sh->pempty[buf]));
+				TCT_ADD(1, tl);
+				if (warp == TC_PWARPS)
+					TCT_TRACE(6, g);
+				g++;
 			}
+			if (!alive)
+				break;
+			const long long tst = TCT_NOW();
+			// rows of this work item: lanes hold consecutive output columns (coalesced 128-byte stores)
+			int rid = 0;
+			if (!RAW && c0 + lane < item.n_valid)
+				rid = perm[item.row0 + c0 + lane];
+#pragma unroll
+			for (int j = 0; j < TC_NT / 2; j++) {
+				const int n = c0 + j;
+				const int rj = RAW ? 0 : __shfl_sync(0xffffffffu, rid, j);
+				if (n < item.n_valid) {
+					if (RAW)
+						y[(size_t)(item.row0 + n) * out_stride + (size_t)item.mat_sel * rows_per_matrix + mrow] = acc[j];
+					else
+						y[(size_t)rj * out_stride + mrow] = acc[j] * out_scale;
+				}
+			}
+			TCT_ADD(2, tst);
+		}
+		TCT_ADD(3, tct_start);
+		if (warp == TC_PWARPS && lane == 0)
+			TCT_FLUSH(8, 4);
+	} else if (warp < TC_PWARPS + TC_DWARPS + TC_MWARPS) {
+		// ================= MMA issuers =================
+		// One thread can issue a tcgen05.mma only every ~110-130 cycles whatever its N, so the
+		// super-blocks are dealt to TC_MWARPS issuer warps: warp w owns accumulator buffer w and the
+		// super-blocks that use it; MMAs of different issuers run concurrently on different buffers.
+		// The whole warp walks the loop (warp-uniform addresses and descriptors); lane 0 issues.
+		{
+			const uint32_t mw = warp - (TC_PWARPS + TC_DWARPS);
+			const uint32_t leader = (lane == 0) ? 1u : 0u;
+			int s = 0;
+			uint32_t ph = 0, g = 0, tl = 0;
+			bool alive = true;
+			TCT_DECL(5);
+			const long long tct_start = TCT_NOW();
+			for (int t = blockIdx.x; t < total && alive; t += stride_t, tl++) {
+				const TcItem item = tc_item(t, m_tiles, tile_info, rows_per_matrix);
+#ifdef TC_EXP_N
+				const uint32_t idesc = ptx::umma_idesc_f16(TC_BM, TC_EXP_N);
+#else
+				const uint32_t idesc = ptx::umma_idesc_f16(TC_BM, item.n_mma);
+#endif
+				const uint32_t tp = tl & 1u;
+				bool need_x = KIND == W_Q4K;  // this issuer has not yet seen the work item's sub-block sums
+				for (int sbi = 0; sbi < nb && alive; sbi++) {
+					const uint32_t buf = g & 1u;
+					if (buf != mw) {  // the other issuer's super-block: skip its stages
+						s += QK_K / TC_BK;
+						if (s >= TC_S) {
+							s -= TC_S;
+							ph ^= 1u;
+						}
+						g++;
+						continue;
+					}
+					const long long tpe = TCT_NOW();
+					if (g >= 2u) {
+						const bool ok = tc_wait(ptx::smem_u32(&sh->pempty[buf]), ((g >> 1) & 1u) ^ 1u, abort_flag, status);
+						if (!__all_sync(0xffffffffu, ok)) {
+							alive = false;
+							break;
+						}
+					}
+					TCT_ADD(0, tpe);
+					const uint32_t dP = tmem + TC_COL_P + 64u * buf;
+					for (int q4 = 0; q4 < QK_K / TC_BK; q4++) {
+						const long long tb = TCT_NOW();
+						bool ok = tc_wait(ptx::smem_u32(&sh->bfull[s]), ph, abort_flag, status);
+						TCT_ADD(1, tb);
+						const long long tf = TCT_NOW();
+						ok = ok && tc_wait(ptx::smem_u32(&sh->full[s]), ph, abort_flag, status);
+						if (need_x) {
+							ok = ok && tc_wait(ptx::smem_u32(&sh->xfull[tp]), (tl >> 1) & 1u, abort_flag, status);
+							need_x = false;
+						}
+						if (!__all_sync(0xffffffffu, ok)) {
+							alive = false;
+							break;
+						}
+						TCT_ADD(2, tf);
+						TCT_TRACE(3, g * 4u + q4);
+						const long long ti = TCT_NOW();
+						ptx::tc_fence_after();
+						if (KIND == W_Q4K && q4 == 0) {
+							// M step: mins (16-deep A tile) x sub-block sums of this super-block pair
+							const int xt = sbi >> 3, j = (sbi & 7) >> 1;
+							const uint32_t dM = tmem + TC_COL_M + 64u * buf, am = tmem + TC_COL_AM + 8u * buf;
+							ptx::mma_f16_ts_if(dM, am, ptx::umma_desc_sw128(xq_tile(tp, xt, 0)) + 2 * j, idesc, 0u, leader);
+							ptx::mma_f16_ts_if(dM, am, ptx::umma_desc_sw128(xq_tile(tp, xt, 1)) + 2 * j, idesc, 1u, leader);
+						}
+						const uint64_t bh = ptx::umma_desc_sw128(b_hi(s)), bl = ptx::umma_desc_sw128(b_lo(s));
+						const uint32_t a = tmem + TC_COL_A + 32u * s;
+#pragma unroll
+						for (int kk = 0; kk < TC_BK / 16; kk++) {
+							ptx::mma_f16_ts_if(dP, a + 8 * kk, bh + 2 * kk, idesc, (q4 > 0 || kk > 0) ? 1u : 0u, leader);
+#ifndef TC_EXP_NOLO
+							ptx::mma_f16_ts_if(dP, a + 8 * kk, bl + 2 * kk, idesc, 1u, leader);
+#endif
+						}
+						ptx::mma_commit_if(ptx::smem_u32(&sh->empty[s]), leader);
+						TCT_ADD(3, ti);
+						TCT_TRACE(4, g * 4u + q4);
+						if (++s == TC_S) {
+							s = 0;
+							ph ^= 1u;
+						}
+					}
+					if (!alive)
+						break;
+					ptx::mma_commit_if(ptx::smem_u32(&sh->pfull[buf]), leader);
+					g++;
+				}
+				if (KIND == W_Q4K && alive)
+					ptx::mma_commit_if(ptx::smem_u32(&sh->xempty[tp]), leader);
+			}
+			TCT_ADD(4, tct_start);
+			if (lane == 0 && mw == 0)
+				TCT_FLUSH(16, 5);
+		}
+	} else {
+		// ================= TMA loader: token operand and sub-block sums =================
+		if (lane == 0) {
+			int sb = 0;
+			uint32_t bph = 0, bit = 0, tl = 0;
+			bool alive = true;
+			TCT_DECL(2);
+			const long long tct_start = TCT_NOW();
+			for (int t = blockIdx.x; t < total && alive; t += stride_t, tl++) {
+				const TcItem item = tc_item(t, m_tiles, tile_info, rows_per_matrix);
+				const int n16 = item.n_mma >> 4;
+				if (KIND == W_Q4K) {
+					const uint32_t tp = tl & 1u;
+					if (tl >= 2u && !tc_wait(ptx::smem_u32(&sh->xempty[tp]), ((tl >> 1) & 1u) ^ 1u, abort_flag, status))
+						break;
+					const uint32_t xb = ptx::smem_u32(&sh->xfull[tp]);
+					ptx::mbar_arrive_expect_tx(xb, (uint32_t)(xt_n * n16) * 2u * 2048u);
+					for (int xt = 0; xt < xt_n; xt++)
+						for (int r = 0; r < n16; r++) {
+							ptx::tma_load_2d(xq_tile(tp, xt, 0) + r * 2048, &tq_hi, xb, xt * 64, item.row0 + 16 * r);
+							ptx::tma_load_2d(xq_tile(tp, xt, 1) + r * 2048, &tq_lo, xb, xt * 64, item.row0 + 16 * r);
+						}
+				}
+				for (int ki = 0; ki < k_iters; ki++) {
+					const long long tw = TCT_NOW();
+					if (bit >= (uint32_t)TC_S && !tc_wait(ptx::smem_u32(&sh->empty[sb]), bph ^ 1u, abort_flag, status)) {
+						alive = false;
+						break;
+					}
+					TCT_ADD(0, tw);
+					const uint32_t fb = ptx::smem_u32(&sh->bfull[sb]);
+					// only the rows the MMA will read: 16-row boxes (2 KB each, whole swizzle groups)
+					ptx::mbar_arrive_expect_tx(fb, (uint32_t)n16 * 2u * 2048u);
+					for (int r = 0; r < n16; r++) {
+						ptx::tma_load_2d(b_hi(sb) + r * 2048, &tm_hi, fb, ki * TC_BK, item.row0 + 16 * r);
+						ptx::tma_load_2d(b_lo(sb) + r * 2048, &tm_lo, fb, ki * TC_BK, item.row0 + 16 * r);
+					}
+					bit++;
+					if (++sb == TC_S) {
+						sb = 0;
+						bph ^= 1u;
+					}
+				}
+			}
+			TCT_ADD(1, tct_start);
+			TCT_FLUSH(24, 2);
 		}
 	}
+
 	if (*abort_flag) {
 		// give copies that may still be in flight time to land before the CTA's memory is released
 		for (int i = 0; i < 200; i++)
@@ -465,8 +659,8 @@ grouped_gemm_tc(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 	}
 	ptx::tc_fence_before();
 	__syncthreads();
-	if (warp == TC_PWARPS)
-		ptx::tmem_dealloc(tmem, Cfg::TMEM_COLS);
+	if (warp == TC_PWARPS + TC_DWARPS)
+		ptx::tmem_dealloc(tmem, TC_TMEM_COLS);
 }
 
 // ---- host side ----
@@ -512,85 +706,85 @@ static int make_tmap(tie_cuda_ctx *c, CUtensorMap *tm, void *base, size_t rows, 
 int tc_setup(tie_cuda_ctx *c)
 {
 	Scratch &s = c->s;
-	void *bases[4] = {s.xs_hi, s.xs_lo, s.hs_hi, s.hs_lo};
-	size_t cols[4] = {(size_t)c->cfg.hidden, (size_t)c->cfg.hidden, (size_t)c->cfg.ffn_dim, (size_t)c->cfg.ffn_dim};
-	for (int a = 0; a < 4; a++) {
+	const size_t H = c->cfg.hidden, F = c->cfg.ffn_dim;
+	void *bases[8] = {s.xs_hi, s.xs_lo, s.hs_hi, s.hs_lo, s.xq_hi, s.xq_lo, s.hq_hi, s.hq_lo};
+	size_t cols[8] = {H, H, F, F, (size_t)xq_cols((int)H), (size_t)xq_cols((int)H), (size_t)xq_cols((int)F), (size_t)xq_cols((int)F)};
+	for (int a = 0; a < 8; a++) {
 		int rc = make_tmap(c, &c->tmap[a], bases[a], s.rows_pad, cols[a]);
 		if (rc)
 			return rc;
 	}
-#define TC_ATTR(KIND, NMAT, NT, RAW)                                                                                            \
-	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_tc<KIND, NMAT, NT, RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-					     TcCfg<NMAT, NT>::SMEM))
-	TC_ATTR(W_Q4K, 1, 64, false);
-	TC_ATTR(W_Q4K, 1, 128, false);
-	TC_ATTR(W_Q4K, 1, 64, true);
-	TC_ATTR(W_Q4K, 1, 128, true);
-	TC_ATTR(W_Q4K, 2, 64, false);
-	TC_ATTR(W_Q4K, 2, 128, false);
-	TC_ATTR(W_Q6K_R8, 1, 64, false);
-	TC_ATTR(W_Q6K_R8, 1, 128, false);
-	TC_ATTR(W_Q6K_R8, 1, 64, true);
-	TC_ATTR(W_Q6K_R8, 1, 128, true);
-	TC_ATTR(W_Q6K_R8, 2, 64, false);
-	TC_ATTR(W_Q6K_R8, 2, 128, false);
+#define TC_ATTR(KIND, RAW) \
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_sb<KIND, RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM))
+	TC_ATTR(W_Q4K, false);
+	TC_ATTR(W_Q4K, true);
+	TC_ATTR(W_Q6K_R8, false);
+	TC_ATTR(W_Q6K_R8, true);
 #undef TC_ATTR
 	c->tmaps_ok = true;
 	return TIE_CUDA_OK;
 }
 
-template <WKind KIND, int NMAT, int NT, bool RAW>
-static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1, const CUtensorMap &tmh, const CUtensorMap &tml,
-		       int n_rows, float *y)
+// arr: 0 = the split inputs x (gate/up), 2 = the split activations h (down).
+template <WKind KIND, bool RAW>
+static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1, int arr, float *y, float out_scale)
 {
 	Scratch &s = c->s;
-	const int max_tiles = min(c->n_local, n_rows) + n_rows / NT;
-	dim3 grid((RAW ? 2 : 1) * t0.rows / TC_BM, max_tiles);
-	grouped_gemm_tc<KIND, NMAT, NT, RAW><<<grid, TC_THREADS, TcCfg<NMAT, NT>::SMEM, c->stream>>>(
-		tmh, tml, t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride, t0.k, s.offsets, s.tile_start, c->n_local, s.hs_hi, s.hs_lo,
-		y, s.perm, RAW ? 2 * t0.rows : t0.rows, c->silu, s.status, t0.rows);
+	const int m_tiles = (RAW ? 2 : 1) * t0.rows / TC_BM;
+	grouped_gemm_sb<KIND, RAW><<<c->sm_count, TC_THREADS, TC_SMEM, c->stream>>>(
+		c->tmap[arr], c->tmap[arr + 1], c->tmap[4 + arr], c->tmap[5 + arr], t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride, t0.k,
+		s.tile_info, s.tile_start, c->n_local, m_tiles, y, s.perm, RAW ? 2 * t0.rows : t0.rows, out_scale, s.status, t0.rows);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
-}
-
-template <int NMAT, bool RAW>
-static int launch_tc_n(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1, int arr, int n_tile, int n_rows, float *y)
-{
-	const CUtensorMap &tmh = c->tmap[arr], &tml = c->tmap[arr + 1];
-	if (t0.kind == W_Q4K) {
-		if (n_tile == 64)
-			return launch_tc_t<W_Q4K, NMAT, 64, RAW>(c, t0, t1, tmh, tml, n_rows, y);
-		return launch_tc_t<W_Q4K, NMAT, 128, RAW>(c, t0, t1, tmh, tml, n_rows, y);
-	}
-	if (n_tile == 64)
-		return launch_tc_t<W_Q6K_R8, NMAT, 64, RAW>(c, t0, t1, tmh, tml, n_rows, y);
-	return launch_tc_t<W_Q6K_R8, NMAT, 128, RAW>(c, t0, t1, tmh, tml, n_rows, y);
 }
 
 bool tc_supported(const tie_cuda_ctx *c, const Layer &L)
 {
 	return c->tmaps_ok && L.gate.kind == L.up.kind && L.gate.rows % TC_BM == 0 && L.down.rows % TC_BM == 0 &&
-	       L.gate.k % QK_K == 0 && L.down.k % QK_K == 0;
+	       L.gate.k % QK_K == 0 && L.down.k % QK_K == 0 && L.gate.k <= TC_XT * 2048 && L.down.k <= TC_XT * 2048;
 }
 
-// xs_hi/xs_lo must hold the split inputs in sorted order; writes hs_hi/hs_lo.
-int launch_tc_gate_up(tie_cuda_ctx *c, const Layer &L, int n_rows, int n_tile)
+// xs_hi/xs_lo (and xq_hi/xq_lo for Q4_K) must hold the split inputs in sorted order; the sort must
+// have been run with TC_TOKEN_TILE.  Writes hs_hi/hs_lo (and hq_hi/hq_lo when the down matrix is Q4_K).
+int launch_tc_gate_up(tie_cuda_ctx *c, const Layer &L, int n_rows)
 {
-	if (n_tile == 64) {
-		// few tokens per expert: gate and up as independent one-matrix tiles (two CTAs per SM),
-		// raw fp32 products to a scratch [row][gate | up], then one element-wise SwiGLU + split pass
-		int rc = launch_tc_n<1, true>(c, L.gate, &L.up, 0, n_tile, n_rows, c->s.y);
-		if (rc)
-			return rc;
-		return launch_swiglu_split(c, c->s.y, n_rows, L.gate.rows, TC_H_SCALE, c->s.hs_hi, c->s.hs_lo);
-	}
-	return launch_tc_n<2, false>(c, L.gate, &L.up, 0, n_tile, n_rows, nullptr);
+	// gate and up as independent 128-row tiles; raw fp32 products to a scratch [row][gate | up],
+	// then one element-wise SwiGLU + split pass
+	int rc = (L.gate.kind == W_Q4K) ? launch_tc_t<W_Q4K, true>(c, L.gate, &L.up, 0, c->s.y, 1.0f)
+					: launch_tc_t<W_Q6K_R8, true>(c, L.gate, &L.up, 0, c->s.y, 1.0f);
+	if (rc)
+		return rc;
+	const bool sums = L.down.kind == W_Q4K;
+	return launch_swiglu_split(c, c->s.y, n_rows, L.gate.rows, TC_H_SCALE, c->s.hs_hi, c->s.hs_lo, sums ? c->s.hq_hi : nullptr,
+				   sums ? c->s.hq_lo : nullptr);
 }
 
 // reads hs_hi/hs_lo; writes y[perm[p]].
-int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, int n_tile, float *y)
+int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, float *y)
 {
-	return launch_tc_n<1, false>(c, L.down, nullptr, 2, n_tile, n_rows, y);
+	(void)n_rows;
+	if (L.down.kind == W_Q4K)
+		return launch_tc_t<W_Q4K, false>(c, L.down, nullptr, 2, y, 1.0f / TC_H_SCALE);
+	return launch_tc_t<W_Q6K_R8, false>(c, L.down, nullptr, 2, y, 1.0f / TC_H_SCALE);
 }
 
 }  // namespace tie
+
+#ifdef TC_TIMING
+// Debug builds only: copies out and clears the role cycle counters (32 values).
+extern "C" int tie_debug_tc_cycles(unsigned long long *out)
+{
+	unsigned long long zero[32] = {0};
+	if (cudaDeviceSynchronize() != cudaSuccess)
+		return -1;
+	if (cudaMemcpyFromSymbol(out, tie::g_tc_cycles, sizeof(zero)) != cudaSuccess)
+		return -1;
+	return cudaMemcpyToSymbol(tie::g_tc_cycles, zero, sizeof(zero)) == cudaSuccess ? 0 : -1;
+}
+extern "C" int tie_debug_tc_trace(long long *out)
+{
+	if (cudaDeviceSynchronize() != cudaSuccess)
+		return -1;
+	return cudaMemcpyFromSymbol(out, tie::g_tc_trace, sizeof(long long) * 8 * 128) == cudaSuccess ? 0 : -1;
+}
+#endif
