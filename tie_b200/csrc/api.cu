@@ -58,15 +58,16 @@ int alloc_scratch(tie_cuda_ctx *c)
 	TRY(dev_alloc(c, &s.perm, R));
 	TRY(dev_alloc(c, &s.h, R * F));
 	TRY(dev_alloc(c, &s.y, R * (H > 2 * F ? H : 2 * F)));  // also holds the raw gate|up products of the tensor path
-	TRY(dev_alloc(c, &s.xs_hi, s.rows_pad * H));
-	TRY(dev_alloc(c, &s.xs_lo, s.rows_pad * H));
-	TRY(dev_alloc(c, &s.hs_hi, s.rows_pad * F));
-	TRY(dev_alloc(c, &s.hs_lo, s.rows_pad * F));
+	// hi and lo halves of each split array share one allocation (lo right behind hi): one 3-D TMA box fetches both
+	TRY(dev_alloc(c, &s.xs_hi, 2 * s.rows_pad * H));
+	s.xs_lo = s.xs_hi + s.rows_pad * H;
+	TRY(dev_alloc(c, &s.hs_hi, 2 * s.rows_pad * F));
+	s.hs_lo = s.hs_hi + s.rows_pad * F;
 	const size_t XH = xq_cols((int)H), XF = xq_cols((int)F);
-	TRY(dev_alloc(c, &s.xq_hi, s.rows_pad * XH));
-	TRY(dev_alloc(c, &s.xq_lo, s.rows_pad * XH));
-	TRY(dev_alloc(c, &s.hq_hi, s.rows_pad * XF));
-	TRY(dev_alloc(c, &s.hq_lo, s.rows_pad * XF));
+	TRY(dev_alloc(c, &s.xq_hi, 2 * s.rows_pad * XH));
+	s.xq_lo = s.xq_hi + s.rows_pad * XH;
+	TRY(dev_alloc(c, &s.hq_hi, 2 * s.rows_pad * XF));
+	s.hq_lo = s.hq_hi + s.rows_pad * XF;
 	TRY(dev_alloc(c, &s.status, 1));
 	TRY(dev_alloc(c, &s.counter, 1));
 	TIE_CUDA_TRY(c, cudaMemset(s.counter, 0, sizeof(int)));
@@ -143,7 +144,7 @@ int upload_tensor(tie_cuda_ctx *c, DevTensor &t, const void *host, int type, int
 	}
 	TIE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
 	c->weight_bytes += t.bytes;
-	return TIE_CUDA_OK;
+	return tc_make_weight_map(c, t);
 }
 
 int add_reg(tie_cuda_ctx *c, const void *host, size_t bytes, const uint8_t *dev, int type, WKind kind, int rows, int k)
@@ -501,9 +502,9 @@ void tie_cuda_destroy(tie_cuda_ctx *c)
 	}
 	Scratch &s = c->s;
 	void *dev_ptrs[] = {s.x,     s.out,   s.logits, s.bias,  s.topk_idx, s.topk_w, s.counts, s.offsets, s.tile_start, s.active, s.n_active,
-			    s.perm,  s.h,     s.y,	s.xs_hi, s.xs_lo,    s.hs_hi,  s.hs_lo,  s.status,  s.counter, s.row_expert, c->silu,  c->row_x,
+			    s.perm,  s.h,     s.y,	s.xs_hi, s.hs_hi,  s.status,  s.counter, s.row_expert, c->silu,  c->row_x,
 			    c->row_o, s.ep_counts, s.ep_offsets, s.ep_tile_start, s.ep_active, s.ep_n_active, s.ep_perm, s.ep_inv,
-			    s.tile_info, s.xq_hi, s.xq_lo, s.hq_hi, s.hq_lo};
+			    s.tile_info, s.xq_hi, s.hq_hi};
 	for (void *p : dev_ptrs)
 		if (p)
 			cudaFree(p);

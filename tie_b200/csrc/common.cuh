@@ -26,7 +26,7 @@ constexpr unsigned ST_BAD_TILE = 4u;	  // tile bookkeeping out of range
 // Weight storage kinds on the device.
 //  Q4_K is kept byte-for-byte as in the GGUF (144-byte blocks are 16-byte aligned).
 //  Q6_K is re-ordered at upload into groups of 8 rows ("R8", see repack.cu): same byte
-//  count, every 48-byte quant chunk 16-byte aligned.
+//  count, 208-byte (row, block) records with every 48-byte quant chunk 16-byte aligned.
 enum WKind : int { W_Q4K = 0, W_Q6K_R8 = 1 };
 
 struct DevTensor {
@@ -38,6 +38,8 @@ struct DevTensor {
 	size_t expert_stride = 0;  // bytes per expert
 	size_t bytes = 0;
 	const void *host_ptr = nullptr;	 // for the dispatch-row registry
+	CUtensorMap map;	 // Q4_K: byte map for the tensor-core path's weight loader
+	bool has_map = false;
 };
 
 struct Layer {
@@ -105,8 +107,8 @@ struct tie_cuda_ctx {
 	cudaEvent_t prof_ev[8] = {nullptr};
 	bool prof_set[8] = {false};
 	char cuda_err[256] = {0};
-	// tensor maps for the tcgen05 path: xs_hi, xs_lo, hs_hi, hs_lo, xq_hi, xq_lo, hq_hi, hq_lo (16-row boxes)
-	CUtensorMap tmap[8];
+	// tensor maps for the tcgen05 path: (x, h, sums of x, sums of h) x (16-, 32-, 64-row boxes)
+	CUtensorMap tmap[12];
 	bool tmaps_ok = false;
 	// host registry for dispatch rows
 	struct Reg {
@@ -210,25 +212,30 @@ __device__ __forceinline__ float half_bits_to_float(uint32_t h16)
 
 // Byte offset of (expert-local row, part) pieces in the Q6_K "R8" layout.
 //   group g = row/8 holds 8 rows; nb = blocks per row.
-//   [quant chunks: (r8, b, part) x 48 B][scales: (r8, b, part) x 4 B][d: (r8, b) x 2 B]
+//   [records: (r8, b) x 208 B][d: (r8, b) x 2 B]
+//   record = [quant chunks: part x 48 B][scales: part x 4 B]
 //   part = n*2 + l16  (n = 128-element half of the block, l16 = 16-wide slice of l)
 //   chunk = ql[64n+16*l16 .. +16] | ql[64n+32+16*l16 .. +16] | qh[32n+16*l16 .. +16]
 //   scales = scales[8n + l16 + {0,2,4,6}]
+// Every 48-byte chunk is 16-byte aligned; the 208-byte records of one row are contiguous, so a
+// (block, 8 rows, 16 groups) box of a 3-D tensor map fetches the packed weights of 128 rows with
+// one TMA instruction, and 208 = 13 x 16 keeps 16-byte reads by consecutive rows conflict-free.
+constexpr int Q6K_RECORD = 208;
 __host__ __device__ __forceinline__ size_t q6k_r8_group_bytes(int nb)
 {
 	return (size_t)8 * nb * Q6K_BYTES;
 }
 __host__ __device__ __forceinline__ size_t q6k_r8_chunk_off(int nb, int r8, int b, int part)
 {
-	return ((size_t)(r8 * nb + b) * 4 + part) * 48;
+	return (size_t)(r8 * nb + b) * Q6K_RECORD + (size_t)part * 48;
 }
 __host__ __device__ __forceinline__ size_t q6k_r8_scale_off(int nb, int r8, int b, int part)
 {
-	return (size_t)8 * nb * 192 + ((size_t)(r8 * nb + b) * 4 + part) * 4;
+	return (size_t)(r8 * nb + b) * Q6K_RECORD + 192 + (size_t)part * 4;
 }
 __host__ __device__ __forceinline__ size_t q6k_r8_d_off(int nb, int r8, int b)
 {
-	return (size_t)8 * nb * 208 + (size_t)(r8 * nb + b) * 2;
+	return (size_t)8 * nb * Q6K_RECORD + (size_t)(r8 * nb + b) * 2;
 }
 
 }  // namespace tie

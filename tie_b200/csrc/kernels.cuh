@@ -41,6 +41,7 @@ int launch_swiglu_split(tie_cuda_ctx *c, const float *gu, int n_rows, int ffn, f
 			__half *q_lo);
 // tensor.cu
 int tc_setup(tie_cuda_ctx *c);
+int tc_make_weight_map(tie_cuda_ctx *c, DevTensor &t);
 bool tc_supported(const tie_cuda_ctx *c, const Layer &L);
 int launch_tc_gate_up(tie_cuda_ctx *c, const Layer &L, int n_rows);
 int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, float *y);

@@ -101,6 +101,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *tma
 		"l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y)
 		: "memory");
 }
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *tmap, uint32_t bar, int x, int y, int z)
+{
+	asm volatile(
+		"cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+		"l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y), "r"(z)
+		: "memory");
+}
+// 1-D bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16 bytes).
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+	asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src),
+		     "r"(bytes), "r"(bar)
+		     : "memory");
+}
 __device__ __forceinline__ void prefetch_tmap(const CUtensorMap *tmap)
 {
 	asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");

@@ -17,16 +17,19 @@
 // MMA step per super-block).
 //
 // The kernel is persistent: one CTA per SM walks (token tile, 128-row tile) work items.  Roles:
-//   * 8 producer warps read packed blocks (128-bit loads, prefetched one 128-k group ahead, across
-//     work items too), expand them with one HFMA2 per two weights and write the A tiles to TENSOR
+//   * a weight loader thread brings the packed blocks of one super-block x 128 rows into shared
+//     memory with TMA (three super-blocks in flight: the HBM latency is hidden by the hardware,
+//     not by registers, and no thread issues scattered 16-byte loads);
+//   * 8 producer warps expand them (one HFMA2 per two weights) and write the A tiles to TENSOR
 //     MEMORY (tcgen05.st) into a ring of 64-k stages;
-//   * one thread issues TMA tile loads of the token operand (hi/lo fp16, expert-sorted rows,
-//     16-row boxes: only rows the expert really has) and of the sub-block sums into shared memory;
-//   * one thread issues tcgen05.mma (kind::f16, fp32 accumulate): per 16-wide k step
-//     P += A.B_hi, P += A.B_lo, into one of two accumulator buffers that alternate per super-block;
+//   * a token loader thread issues TMA tile loads of the token operand (hi/lo fp16, expert-sorted
+//     rows, 16-row boxes: only rows the expert really has) and of the sub-block sums;
+//   * two MMA issuer warps issue tcgen05.mma (kind::f16, fp32 accumulate), per 16-wide k step
+//     P += A.B_hi, P += A.B_lo.  A thread can issue only one MMA per ~110-130 cycles whatever its
+//     N, so consecutive super-blocks go to different issuers, each with its own accumulator buffer;
 //   * 8 drain warps take a finished super-block out of tensor memory (tcgen05.ld), fold it into
 //     fp32 registers with d / dmin, and after the last super-block of a work item store the rows —
-//     while the MMAs of the next super-block / work item already run.
+//     while the MMAs of the next super-blocks / work item already run.
 // All hand-offs go through mbarriers (tcgen05.commit on the MMA side).  Every wait is bounded: on
 // a timeout the CTA raises ST_WAIT_TIMEOUT in the status word, all roles leave their loops, tensor
 // memory is released and the kernel returns.
@@ -39,56 +42,67 @@ namespace tie {
 
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;
-constexpr int TC_NT = TC_TOKEN_TILE;  // tokens per tile (N of the MMAs, at most)
+constexpr int TC_SPB = QK_K / TC_BK;	  // stages per super-block
+constexpr int TC_NT = TC_TOKEN_TILE;	  // tokens per tile (N of the MMAs, at most)
 constexpr int TC_PWARPS = 8;		  // producer warps
 constexpr int TC_DWARPS = 8;		  // drain warps
 constexpr int TC_MWARPS = 2;		  // MMA issuer warps: one per accumulator buffer
-constexpr int TC_THREADS = (TC_PWARPS + TC_DWARPS + TC_MWARPS + 1) * 32;
-constexpr int TC_S = 7;	  // ring stages: weight tiles in tensor memory, token tiles in shared memory
-constexpr int TC_XT = 2;  // 64-wide tiles of sub-block sums per work item, at most (k <= 4096)
+constexpr int TC_THREADS = (TC_PWARPS + TC_DWARPS + TC_MWARPS + 2) * 32;  // + token loader + weight loader
+constexpr int TC_S = 7;	   // ring stages: weight tiles in tensor memory, token tiles in shared memory
+constexpr int TC_NWB = 3;  // packed super-blocks in flight (shared memory)
+constexpr int TC_NDS = 4;  // block-factor hand-off buffers (producers -> drain warps)
 constexpr long long TC_WAIT_CYCLES = 1ll << 30;	 // about half a second of SM clocks
 constexpr float TC_H_SCALE = 1.0f / 256.0f;	 // keeps SwiGLU outputs inside fp16 range; exact (power of two)
 
 // tensor-memory columns
-constexpr uint32_t TC_COL_P = 0;      // 2 x 64: P partial sums
-constexpr uint32_t TC_COL_M = 128;    // 2 x 64: M partial sums
-constexpr uint32_t TC_COL_AM = 256;   // 2 x 8:  A tile of the M step (8 mins + 8 zeros per row)
-constexpr uint32_t TC_COL_A = 288;    // TC_S x 32: A ring
+constexpr uint32_t TC_COL_P = 0;     // 2 x 64: P partial sums
+constexpr uint32_t TC_COL_M = 128;   // 2 x 64: M partial sums
+constexpr uint32_t TC_COL_AM = 256;  // 2 x 8:  A tile of the M step (8 mins + 8 zeros per row)
+constexpr uint32_t TC_COL_A = 288;   // TC_S x 32: A ring
 constexpr uint32_t TC_TMEM_COLS = 512;
 static_assert(TC_COL_A + TC_S * 32 <= TC_TMEM_COLS, "tensor memory budget");
 
+// shared memory
 constexpr int TC_B_TILE = TC_NT * TC_BK * 2;  // bytes of one (hi or lo) token tile
 constexpr int TC_B_STAGE = 2 * TC_B_TILE;
-constexpr int TC_SMEM = TC_S * TC_B_STAGE + 2 * TC_XT * TC_B_STAGE + 1024 /* alignment slack */ + 512 /* barriers */;
+// packed super-block of 128 rows: the 144-byte Q4_K blocks resp. the 208-byte Q6_K records
+// (192 bytes of quants + 16 bytes of scales) of the rows back to back, one TMA box.  Row strides
+// of 9 and 13 x 16 bytes: 16-byte reads by 32 consecutive rows are bank-conflict free.
+constexpr int TC_Q6_ROW = Q6K_RECORD;
+constexpr int TC_WBUF = 27 * 1024;
+static_assert(TC_BM * Q4K_BYTES <= TC_WBUF && TC_BM * TC_Q6_ROW <= TC_WBUF, "packed super-block buffer");
+constexpr int TC_OFF_W = TC_S * TC_B_STAGE;
+constexpr int TC_OFF_XQ = TC_OFF_W + TC_NWB * TC_WBUF;
+constexpr int TC_OFF_DS = TC_OFF_XQ + TC_B_STAGE;
+constexpr int TC_OFF_BAR = TC_OFF_DS + TC_NDS * TC_BM * 8;
+constexpr int TC_SMEM = TC_OFF_BAR + 512 + 1024 /* alignment slack */;
+static_assert(TC_SMEM <= 227 * 1024, "shared memory budget");
 
 struct TcShared {
-	uint64_t full[TC_S];	 // weight stage written by the producers
-	uint64_t bfull[TC_S];	 // token tiles of the stage landed (TMA transaction bytes)
-	uint64_t empty[TC_S];	 // stage consumed by the MMAs (both operands)
-	uint64_t pfull[2];	 // accumulator buffer complete (one super-block)
-	uint64_t pempty[2];	 // accumulator buffer read out by the drain warps
-	uint64_t xfull[2];	 // sub-block sums of a work item landed
-	uint64_t xempty[2];	 // ... and consumed
+	uint64_t full[TC_S];	  // weight stage written by the producers
+	uint64_t bfull[TC_S];	  // token tiles of the stage landed (TMA transaction bytes)
+	uint64_t empty[TC_S];	  // stage consumed by the MMAs (both operands)
+	uint64_t wfull[TC_NWB];	  // packed super-block landed
+	uint64_t wempty[TC_NWB];  // ... and expanded
+	uint64_t pfull[2];	  // accumulator buffer complete (one super-block)
+	uint64_t pempty[2];	  // accumulator buffer read out by the drain warps
+	uint64_t xfull;		  // sub-block sums of a work item landed
+	uint64_t xempty;	  // ... and consumed (by the last M step of each issuer)
 	uint32_t tmem_base;
 	uint32_t abort;
 };
+static_assert(sizeof(TcShared) <= 512, "barrier block");
 
 // Optional cycle accounting per role (compile with -DTC_TIMING): lane 0 of one warp per role adds
 // its clock64() deltas to g_tc_cycles; tie_debug_tc_cycles() reads and clears them.
 #ifdef TC_TIMING
 __device__ unsigned long long g_tc_cycles[32];
-__device__ long long g_tc_trace[8][128];
-#define TCT_TRACE(r, i)                                             \
-	do {                                                        \
-		if (blockIdx.x == 0 && (i) < 128u && (lane) == 0)   \
-			g_tc_trace[r][i] = clock64();               \
-	} while (0)
 #define TCT_DECL(n) long long tct_[n] = {0}
 #define TCT_NOW() clock64()
 #define TCT_ADD(i, t0) tct_[i] += clock64() - (t0)
-#define TCT_FLUSH(base, n)                                                        \
-	do {                                                                      \
-		for (int i_ = 0; i_ < (n); i_++)                                  \
+#define TCT_FLUSH(base, n)                                                          \
+	do {                                                                        \
+		for (int i_ = 0; i_ < (n); i_++)                                    \
 			atomicAdd(&g_tc_cycles[(base) + i_], (unsigned long long)tct_[i_]); \
 	} while (0)
 #else
@@ -96,7 +110,6 @@ __device__ long long g_tc_trace[8][128];
 #define TCT_NOW() 0ll
 #define TCT_ADD(i, t0) (void)(t0)
 #define TCT_FLUSH(base, n)
-#define TCT_TRACE(r, i)
 #endif
 
 // Bounded wait: false (and the abort flag raised) when the barrier does not flip in time or
@@ -133,6 +146,7 @@ __device__ __forceinline__ bool tc_wait_warp(uint32_t bar, uint32_t parity, vola
 // A work item: token tile `slot` (expert le, sorted rows [row0, row0 + n_valid)) x 128-row tile.
 struct TcItem {
 	int le, row0, n_valid, n_mma;
+	int n_box;	  // token rows fetched per stage: 16, 32 or 64 (one TMA box holds the hi and the lo rows)
 	int mat_sel, m0;  // which matrix (RAW: 0 gate, 1 up) and first row inside it
 };
 
@@ -145,38 +159,66 @@ __device__ __forceinline__ TcItem tc_item(int t, int m_tiles, const int4 *__rest
 	it.row0 = ti.y;
 	it.n_valid = ti.z;
 	it.n_mma = (ti.z + 15) & ~15;
+	it.n_box = ti.z <= 16 ? 16 : (ti.z <= 32 ? 32 : 64);
 	it.mat_sel = (mt * TC_BM) / rows_per_matrix;
 	it.m0 = mt * TC_BM - it.mat_sel * rows_per_matrix;
 	return it;
 }
 
-// Packed weights one producer thread needs for two consecutive k stages (128 k, "group" g) of its
-// row: the thread owns the 32-k half-slice hs of each 64-k stage.
+__device__ __forceinline__ uint4 lds128(uint32_t addr)
+{
+	uint4 v;
+	asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+	return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr)
+{
+	uint32_t v;
+	asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+	return v;
+}
+
+// half2 (1024 + b_i, 1024 + b_j) from two bytes of a word: each byte becomes the low mantissa
+// bits of 0x6400 | byte.  selector 0x7i5j picks bytes j (low half) and i (high half).
+__device__ __forceinline__ __half2 byte_pair_1024(uint32_t w, uint32_t selector)
+{
+	return bits_h2(__byte_perm(w, 0x64006400u, selector));
+}
+
+// Expansion of one packed super-block (already in shared memory) by the producer thread of
+// (row, half-slice hs): prepare() once per super-block, emit(p) for each of its four 64-k stages.
 template <WKind KIND>
-struct RawGroup;
+struct Expander;
 
 template <>
-struct RawGroup<W_Q4K> {
-	uint4 hdr;   // d | dmin, 12 bytes of 6-bit scales and mins
-	uint4 q[2];  // 16 bytes of quants per stage
-	__device__ __forceinline__ void load(const uint8_t *wexp, int nb, int row, int g, int hs)
+struct Expander<W_Q4K> {
+	uint32_t rowaddr;	  // this row's 144-byte block
+	uint32_t sc8[2], mn8[2];  // the 8 scales and 8 mins of the block as bytes (get_scale_min_k4, math_scalar.c:91-100)
+	float2 factors;		  // d, dmin
+	__device__ __forceinline__ void prepare(uint32_t wbuf, int row)
 	{
-		const uint8_t *blk = wexp + ((size_t)row * nb + (g >> 1)) * Q4K_BYTES;
-		hdr = __ldg(reinterpret_cast<const uint4 *>(blk));
-#pragma unroll
-		for (int st = 0; st < 2; st++)
-			q[st] = __ldg(reinterpret_cast<const uint4 *>(blk + 16 + 32 * ((g & 1) * 2 + st)) + hs);
+		rowaddr = wbuf + (uint32_t)row * Q4K_BYTES;
+		const uint4 hdr = lds128(rowaddr);
+		factors = make_float2(half_bits_to_float(hdr.x & 0xffffu), half_bits_to_float(hdr.x >> 16));
+		sc8[0] = hdr.y & 0x3F3F3F3Fu;
+		mn8[0] = hdr.z & 0x3F3F3F3Fu;
+		sc8[1] = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
+		mn8[1] = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
 	}
-	// this thread's 32 weights of stage (2g + st) -> 16 columns of its lane in the A tile
-	__device__ __forceinline__ void emit(int g, int st, int hs, uint32_t tile) const
+	// this thread's 32 weights of stage p -> 16 columns of its lane in the A tile
+	__device__ __forceinline__ void emit(int p, int hs, uint32_t tile) const
 	{
-		const int p = (g & 1) * 2 + st;
-		const uint32_t sc[3] = {hdr.y, hdr.z, hdr.w};
-		int s_lo, m_lo, s_hi, m_hi;
-		q4k_scale_min(sc, 2 * p, s_lo, m_lo);
-		q4k_scale_min(sc, 2 * p + 1, s_hi, m_hi);
-		const Q4kConsts c = q4k_int_consts(s_lo, s_hi);
-		const uint32_t w[4] = {q[st].x, q[st].y, q[st].z, q[st].w};
+		const __half2 k1024 = __float2half2_rn(1024.0f);
+		const uint32_t sw = sc8[p >> 1];
+		const __half2 s_lo = __hsub2(byte_pair_1024(sw, (p & 1) ? 0x7252u : 0x7050u), k1024);
+		const __half2 s_hi = __hsub2(byte_pair_1024(sw, (p & 1) ? 0x7353u : 0x7151u), k1024);
+		Q4kConsts c;
+		c.sl = s_lo;
+		c.cl = __hmul2(s_lo, __float2half2_rn(-1024.0f));
+		c.sh = __hmul2(s_hi, __float2half2_rn(0.0625f));
+		c.ch = __hmul2(s_hi, __float2half2_rn(-64.0f));
+		const uint4 q = lds128(rowaddr + 16u + 32u * p + 16u * hs);
+		const uint32_t w[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
 		for (int cc = 0; cc < 2; cc++) {
 			uint32_t l0[2], h0[2], l1[2], h1[2];
@@ -190,41 +232,39 @@ struct RawGroup<W_Q4K> {
 	// step that belongs to this super-block (sub-block sums of two super-blocks share a step).
 	__device__ __forceinline__ void emit_mins(int sbi, uint32_t tile) const
 	{
-		const uint32_t sc[3] = {hdr.y, hdr.z, hdr.w};
-		uint32_t mm[4];
-#pragma unroll
-		for (int j = 0; j < 4; j++) {
-			int s0, m0, s1, m1;
-			q4k_scale_min(sc, 2 * j, s0, m0);
-			q4k_scale_min(sc, 2 * j + 1, s1, m1);
-			mm[j] = h2_bits(__floats2half2_rn((float)m0, (float)m1));
-		}
+		const __half2 k1024 = __float2half2_rn(1024.0f);
+		const uint32_t m01 = h2_bits(__hsub2(byte_pair_1024(mn8[0], 0x7150u), k1024));
+		const uint32_t m23 = h2_bits(__hsub2(byte_pair_1024(mn8[0], 0x7352u), k1024));
+		const uint32_t m45 = h2_bits(__hsub2(byte_pair_1024(mn8[1], 0x7150u), k1024));
+		const uint32_t m67 = h2_bits(__hsub2(byte_pair_1024(mn8[1], 0x7352u), k1024));
 		const uint32_t odd = (uint32_t)(sbi & 1);
-		ptx::tmem_st4(tile + 4u * odd, mm[0], mm[1], mm[2], mm[3]);
+		ptx::tmem_st4(tile + 4u * odd, m01, m23, m45, m67);
 		ptx::tmem_st4(tile + 4u * (odd ^ 1u), 0u, 0u, 0u, 0u);
 	}
 };
 
 template <>
-struct RawGroup<W_Q6K_R8> {
-	uint4 a, b, h;
-	uint32_t scw;
-	__device__ __forceinline__ void load(const uint8_t *wexp, int nb, int row, int g, int hs)
+struct Expander<W_Q6K_R8> {
+	uint32_t rowaddr;  // this row's 4 x 48 bytes of quants
+	uint32_t scaddr;   // this row's 16 scale bytes
+	float2 factors;
+	__device__ __forceinline__ void prepare(uint32_t wbuf, int row)
 	{
-		const uint8_t *grp = wexp + (size_t)(row >> 3) * q6k_r8_group_bytes(nb);
-		const int r8 = row & 7, kb = g >> 1, pp = (g & 1) * 2 + hs;
-		const uint4 *ch = reinterpret_cast<const uint4 *>(grp + q6k_r8_chunk_off(nb, r8, kb, pp));
-		a = __ldg(ch);
-		b = __ldg(ch + 1);
-		h = __ldg(ch + 2);
-		scw = __ldg(reinterpret_cast<const uint32_t *>(grp + q6k_r8_scale_off(nb, r8, kb, pp)));
+		rowaddr = wbuf + (uint32_t)row * TC_Q6_ROW;
+		scaddr = rowaddr + 192u;
+		factors = make_float2(0.0f, 0.0f);
 	}
-	__device__ __forceinline__ void emit(int g, int st, int hs, uint32_t tile) const
+	__device__ __forceinline__ void emit(int p, int hs, uint32_t tile) const
 	{
-		const float fA = (float)(int)(signed char)((scw >> (16 * st)) & 0xff);
-		const float fB = (float)(int)(signed char)((scw >> (16 * st + 8)) & 0xff);
-		const __half2 sA = __float2half2_rn(fA), cA = __float2half2_rn(-96.0f * fA);
-		const __half2 sB = __float2half2_rn(fB), cB = __float2half2_rn(-96.0f * fB);
+		const int pp = (p >> 1) * 2 + hs, st = p & 1;
+		const uint32_t chunk = rowaddr + 48u * pp;
+		const uint4 a = lds128(chunk), b = lds128(chunk + 16u), h = lds128(chunk + 32u);
+		// scales of the part: bytes {0,1} for st = 0, {2,3} for st = 1; int8 -> half as 1024 + (s ^ 0x80) - 1152
+		const uint32_t scx = lds32(scaddr + 4u * pp) ^ 0x80808080u;
+		const __half2 k1152 = __float2half2_rn(1152.0f), km96 = __float2half2_rn(-96.0f);
+		const __half2 sA = __hsub2(byte_pair_1024(scx, st ? 0x7252u : 0x7050u), k1152);
+		const __half2 sB = __hsub2(byte_pair_1024(scx, st ? 0x7353u : 0x7151u), k1152);
+		const __half2 cA = __hmul2(sA, km96), cB = __hmul2(sB, km96);
 		const uint32_t A[4] = {a.x, a.y, a.z, a.w}, B[4] = {b.x, b.y, b.z, b.w}, Hh[4] = {h.x, h.y, h.z, h.w};
 		uint32_t qa[4], qb[4];
 #pragma unroll
@@ -251,32 +291,27 @@ struct RawGroup<W_Q6K_R8> {
 	__device__ __forceinline__ void emit_mins(int, uint32_t) const {}
 };
 
-// fp32 block factors (d, dmin) of (row, super-block) for the drain warps.
-template <WKind KIND>
-__device__ __forceinline__ float2 tc_block_factors(const uint8_t *wexp, int nb, int row, int sbi)
-{
-	if (KIND == W_Q4K) {
-		const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(wexp + ((size_t)row * nb + sbi) * Q4K_BYTES));
-		return make_float2(half_bits_to_float(v & 0xffffu), half_bits_to_float(v >> 16));
-	}
-	const uint8_t *grp = wexp + (size_t)(row >> 3) * q6k_r8_group_bytes(nb);
-	const unsigned short v = __ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb, row & 7, sbi)));
-	return make_float2(half_bits_to_float(v), 0.0f);
-}
-
 // RAW: products are stored as fp32 in expert-sorted row order, y[row0 + n][matrix * rows + mrow]
 // (gate | up of one row side by side) for the SwiGLU pass; the 128-row tiles then run over w0
 // followed by w1.  Otherwise (down) rows are scattered to y[perm[row0 + n]][mrow] * out_scale.
+// tm16/32/64: maps of the split token operand ([hi | lo][rows][k], box 64 k x 16/32/64 rows x 2);
+// tq16/32/64: the same of its sub-block sums; tw0 / tw1: byte maps of the two weight tensors,
+// box = packed super-block x 128 rows.
 template <WKind KIND, bool RAW>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-grouped_gemm_sb(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant__ CUtensorMap tm_lo,
-		const __grid_constant__ CUtensorMap tq_hi, const __grid_constant__ CUtensorMap tq_lo, const uint8_t *__restrict__ w0,
+grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant__ CUtensorMap tm32,
+		const __grid_constant__ CUtensorMap tm64, const __grid_constant__ CUtensorMap tq16,
+		const __grid_constant__ CUtensorMap tq32, const __grid_constant__ CUtensorMap tq64,
+		const __grid_constant__ CUtensorMap tw0, const __grid_constant__ CUtensorMap tw1, const uint8_t *__restrict__ w0,
 		const uint8_t *__restrict__ w1, size_t expert_stride, int k_dim, const int4 *__restrict__ tile_info,
 		const int *__restrict__ tile_start, int n_local, int m_tiles, float *__restrict__ y, const int *__restrict__ perm,
 		int out_stride, float out_scale, unsigned *__restrict__ status, int rows_per_matrix)
 {
 	extern __shared__ uint8_t smem_raw[];
 	__shared__ int s_total;
+#ifdef TC_TIMING
+	const long long tct_kernel_start = clock64();
+#endif
 	if (threadIdx.x == 0)
 		s_total = (*(volatile unsigned *)status & ST_WAIT_TIMEOUT) ? 0 : tile_start[n_local] * m_tiles;
 	__syncthreads();
@@ -285,17 +320,18 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 		return;
 	const int nb = k_dim / QK_K;
 	const int k_iters = k_dim / TC_BK;
-	const int xt_n = (nb + 7) >> 3;
 
 	const uint32_t raw = ptx::smem_u32(smem_raw);
 	const uint32_t tiles = (raw + 1023u) & ~1023u;
-	const uint32_t xq_base = tiles + TC_S * TC_B_STAGE;
-	TcShared *sh = reinterpret_cast<TcShared *>(smem_raw + (tiles - raw) + (size_t)(TC_S + 2 * TC_XT) * TC_B_STAGE);
+	uint8_t *smem = smem_raw + (tiles - raw);
+	TcShared *sh = reinterpret_cast<TcShared *>(smem + TC_OFF_BAR);
+	float2 *ds = reinterpret_cast<float2 *>(smem + TC_OFF_DS);  // [TC_NDS][128] (d, dmin) of the rows (Q4_K)
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-	auto b_hi = [&](int sb) -> uint32_t { return tiles + sb * TC_B_STAGE; };
-	auto b_lo = [&](int sb) -> uint32_t { return tiles + sb * TC_B_STAGE + TC_B_TILE; };
-	auto xq_tile = [&](int tp, int xt, int hl) -> uint32_t { return xq_base + ((tp * TC_XT + xt) * 2 + hl) * TC_B_TILE; };
+	// token tiles of ring stage s: n_box hi rows, directly followed by n_box lo rows
+	auto b_hi = [&](int s) -> uint32_t { return tiles + s * TC_B_STAGE; };
+	const uint32_t xq_hi = tiles + TC_OFF_XQ;
+	auto w_buf = [&](int wb) -> uint32_t { return tiles + TC_OFF_W + wb * TC_WBUF; };
 
 	if (threadIdx.x == 0) {
 		for (int s = 0; s < TC_S; s++) {
@@ -303,27 +339,39 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 			ptx::mbar_init(ptx::smem_u32(&sh->empty[s]), 1);
 			ptx::mbar_init(ptx::smem_u32(&sh->bfull[s]), 1);
 		}
+		for (int s = 0; s < TC_NWB; s++) {
+			ptx::mbar_init(ptx::smem_u32(&sh->wfull[s]), 1);
+			ptx::mbar_init(ptx::smem_u32(&sh->wempty[s]), TC_PWARPS);
+		}
 		for (int s = 0; s < 2; s++) {
 			ptx::mbar_init(ptx::smem_u32(&sh->pfull[s]), 1);
 			ptx::mbar_init(ptx::smem_u32(&sh->pempty[s]), TC_DWARPS);
-			ptx::mbar_init(ptx::smem_u32(&sh->xfull[s]), 1);
-			ptx::mbar_init(ptx::smem_u32(&sh->xempty[s]), TC_MWARPS);
 		}
+		ptx::mbar_init(ptx::smem_u32(&sh->xfull), 1);
+		ptx::mbar_init(ptx::smem_u32(&sh->xempty), TC_MWARPS);
 		sh->abort = 0;
 		ptx::fence_barrier_init();
 		ptx::fence_proxy_async_smem();
 	}
-	if (warp == TC_PWARPS + TC_DWARPS) {  // the MMA warp owns the tensor-memory allocation
+	constexpr int W_MMA0 = TC_PWARPS + TC_DWARPS, W_TOK = W_MMA0 + TC_MWARPS, W_WGT = W_TOK + 1;
+	if (warp == W_MMA0) {  // the first MMA warp owns the tensor-memory allocation
 		ptx::tmem_alloc(ptx::smem_u32(&sh->tmem_base), TC_TMEM_COLS);
 		ptx::tmem_relinquish();
 	}
-	if (warp == TC_PWARPS + TC_DWARPS + TC_MWARPS && lane == 0) {
-		ptx::prefetch_tmap(&tm_hi);
-		ptx::prefetch_tmap(&tm_lo);
+	if (warp == W_TOK && lane == 0) {
+		ptx::prefetch_tmap(&tm16);
+		ptx::prefetch_tmap(&tm32);
+		ptx::prefetch_tmap(&tm64);
 		if (KIND == W_Q4K) {
-			ptx::prefetch_tmap(&tq_hi);
-			ptx::prefetch_tmap(&tq_lo);
+			ptx::prefetch_tmap(&tq16);
+			ptx::prefetch_tmap(&tq32);
+			ptx::prefetch_tmap(&tq64);
 		}
+	}
+	if (warp == W_WGT && lane == 0) {
+		ptx::prefetch_tmap(&tw0);
+		if (RAW)
+			ptx::prefetch_tmap(&tw1);
 	}
 	ptx::tc_fence_before();
 	__syncthreads();
@@ -333,100 +381,82 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 	const int stride_t = gridDim.x;
 
 	if (warp < TC_PWARPS) {
-		// ================= producers: packed blocks -> integer A tiles in tensor memory =================
+		// ================= producers: packed blocks (shared memory) -> integer A tiles (tensor memory) =================
 		const int row = threadIdx.x & 127, hs = threadIdx.x >> 7;
 		const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-		const int n_groups = k_iters >> 1;
-		int s = 0;
-		uint32_t ph = 0, it = 0, g = 0;
-		// Load cursor: runs three 128-k groups (about 5000 cycles of work, several HBM latencies)
-		// ahead of the group being expanded, across work items.
-		int lt = blockIdx.x, lgi = 0;
-		TcItem litem = tc_item(lt, m_tiles, tile_info, rows_per_matrix);
-		const uint8_t *lwexp = (litem.mat_sel ? w1 : w0) + (size_t)litem.le * expert_stride;
-		bool lvalid = true;
-		auto fetch = [&](RawGroup<KIND> &dst) {
-			if (!lvalid)
-				return;
-			dst.load(lwexp, nb, litem.m0 + row, lgi, hs);
-			if (++lgi == n_groups) {
-				lgi = 0;
-				lt += stride_t;
-				lvalid = lt < total;
-				if (lvalid) {
-					litem = tc_item(lt, m_tiles, tile_info, rows_per_matrix);
-					lwexp = (litem.mat_sel ? w1 : w0) + (size_t)litem.le * expert_stride;
-				}
-			}
-		};
-		RawGroup<KIND> q0, q1, q2, fresh;
-		fetch(q0);
-		fetch(q1);
-		fetch(q2);
+		int s = 0, wb = 0;
+		uint32_t ph = 0, wph = 0, it = 0, g = 0;
 		bool alive = true;
 		TCT_DECL(5);
 		const long long tct_start = TCT_NOW();
-		int t = blockIdx.x, gi = 0;
-		while (alive) {
-			fetch(fresh);
-#pragma unroll
-			for (int st = 0; st < 2; st++) {
+		for (int t = blockIdx.x; t < total && alive; t += stride_t) {
+			for (int sbi = 0; sbi < nb && alive; sbi++) {
 				const long long tw = TCT_NOW();
-				if (it >= (uint32_t)TC_S) {
-					if (!tc_wait_warp(ptx::smem_u32(&sh->empty[s]), ph ^ 1u, abort_flag, status, lane)) {
-						alive = false;
-						break;
-					}
-					ptx::tc_fence_after();
+				if (!tc_wait_warp(ptx::smem_u32(&sh->wfull[wb]), wph, abort_flag, status, lane)) {
+					alive = false;
+					break;
 				}
 				TCT_ADD(0, tw);
-				if (warp == 0)
-					TCT_TRACE(0, it);
-				const long long te = TCT_NOW();
-				// first stage of a super-block: the A tile of its M step (rows are owned by the hs = 0 warps)
-				if (KIND == W_Q4K && st == 0 && (gi & 1) == 0 && hs == 0)
-					q0.emit_mins(gi >> 1, lane_base + TC_COL_AM + 8u * (g & 1u));
-				q0.emit(gi, st, hs, lane_base + TC_COL_A + 32u * s);
-				TCT_ADD(1, te);
-				const long long ts = TCT_NOW();
-				ptx::tmem_st_wait();
-				TCT_ADD(2, ts);
-				ptx::tc_fence_before();
+				Expander<KIND> ex;
+				ex.prepare(w_buf(wb), row);
+				if (KIND == W_Q4K && hs == 0)
+					ds[(g & (TC_NDS - 1)) * TC_BM + row] = ex.factors;
+#pragma unroll
+				for (int p = 0; p < TC_SPB; p++) {
+					const long long te = TCT_NOW();
+					if (it >= (uint32_t)TC_S) {
+						if (!tc_wait_warp(ptx::smem_u32(&sh->empty[s]), ph ^ 1u, abort_flag, status, lane)) {
+							alive = false;
+							break;
+						}
+						ptx::tc_fence_after();
+					}
+					TCT_ADD(1, te);
+					const long long tm = TCT_NOW();
+					// first stage of a super-block: the A tile of its M step (rows are owned by the hs = 0 warps)
+					if (KIND == W_Q4K && p == 0 && hs == 0)
+						ex.emit_mins(sbi, lane_base + TC_COL_AM + 8u * (g & 1u));
+					ex.emit(p, hs, lane_base + TC_COL_A + 32u * s);
+					ptx::tmem_st_wait();
+					TCT_ADD(2, tm);
+					ptx::tc_fence_before();
+					__syncwarp();
+					if (lane == 0)
+						ptx::mbar_arrive(ptx::smem_u32(&sh->full[s]));
+					it++;
+					if (++s == TC_S) {
+						s = 0;
+						ph ^= 1u;
+					}
+				}
+				if (!alive)
+					break;
+				// the packed super-block is expanded: hand the buffer back to the weight loader
 				__syncwarp();
 				if (lane == 0)
-					ptx::mbar_arrive(ptx::smem_u32(&sh->full[s]));
-				if (warp == 0)
-					TCT_TRACE(1, it);
-				if (warp == 7)
-					TCT_TRACE(2, it);
-				it++;
-				if (++s == TC_S) {
-					s = 0;
-					ph ^= 1u;
+					ptx::mbar_arrive(ptx::smem_u32(&sh->wempty[wb]));
+				if (++wb == TC_NWB) {
+					wb = 0;
+					wph ^= 1u;
 				}
-			}
-			if (gi & 1)
 				g++;
-			q0 = q1;
-			q1 = q2;
-			q2 = fresh;
-			if (++gi == n_groups) {
-				gi = 0;
-				t += stride_t;
-				if (t >= total)
-					break;
 			}
 		}
 		TCT_ADD(3, tct_start);
 #ifdef TC_TIMING
 		tct_[4] = it;
+		if (threadIdx.x == 0) {
+			atomicMax(&g_tc_cycles[28], (unsigned long long)tct_[3]);
+			atomicMax(&g_tc_cycles[29], (unsigned long long)it);
+			atomicMax(&g_tc_cycles[30], (unsigned long long)(clock64() - tct_kernel_start));
+		}
 #endif
 		if (threadIdx.x == 0)
 			TCT_FLUSH(0, 5);
-	} else if (warp < TC_PWARPS + TC_DWARPS) {
+	} else if (warp < W_MMA0) {
 		// ================= drain warps: super-block partial sums -> fp32 rows =================
 		const int dw = warp - TC_PWARPS, quad = warp & 3, chalf = dw >> 2;
-		const int c0 = chalf * (TC_NT / 2);
+		const int lrow = quad * 32 + lane;
 		const uint32_t tlane = tmem + ((uint32_t)(quad * 32) << 16);
 		uint32_t g = 0;
 		bool alive = true;
@@ -434,17 +464,29 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 		const long long tct_start = TCT_NOW();
 		for (int t = blockIdx.x; t < total && alive; t += stride_t) {
 			const TcItem item = tc_item(t, m_tiles, tile_info, rows_per_matrix);
-			const uint8_t *wexp = (item.mat_sel ? w1 : w0) + (size_t)item.le * expert_stride;
-			const int mrow = item.m0 + quad * 32 + lane;
+			const int mrow = item.m0 + lrow;
+			// Tokens of this warp: half of the tile's token range, in chunks of 16 accumulator columns.
+			// A tile of up to 32 tokens has its hi and lo products side by side in one accumulator
+			// (columns j and n_box + j, one MMA per k step); a larger tile has them summed by two MMAs.
+			const bool concat = item.n_box <= 32;
+			const int ntok = item.n_box == 64 ? 32 : 16;
+			const int tok0 = chalf * ntok;
 			float acc[TC_NT / 2];
 #pragma unroll
 			for (int j = 0; j < TC_NT / 2; j++)
 				acc[j] = 0.0f;
-			float2 fnext = tc_block_factors<KIND>(wexp, nb, mrow, 0);
+			// Q6_K: d of (row, super-block) straight from global memory, one super-block ahead
+			const uint8_t *grp = nullptr;
+			float dnext = 0.0f;
+			if (KIND == W_Q6K_R8) {
+				grp = (item.mat_sel ? w1 : w0) + (size_t)item.le * expert_stride + (size_t)(mrow >> 3) * q6k_r8_group_bytes(nb);
+				dnext = half_bits_to_float(__ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb, mrow & 7, 0))));
+			}
 			for (int sbi = 0; sbi < nb; sbi++) {
-				const float2 f = fnext;
-				if (sbi + 1 < nb)
-					fnext = tc_block_factors<KIND>(wexp, nb, mrow, sbi + 1);
+				float2 f = make_float2(dnext, 0.0f);
+				if (KIND == W_Q6K_R8 && sbi + 1 < nb)
+					dnext = half_bits_to_float(
+						__ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb, mrow & 7, sbi + 1))));
 				const uint32_t buf = g & 1u;
 				const long long tw = TCT_NOW();
 				if (!tc_wait_warp(ptx::smem_u32(&sh->pfull[buf]), (g >> 1) & 1u, abort_flag, status, lane)) {
@@ -452,24 +494,34 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 					break;
 				}
 				TCT_ADD(0, tw);
-				if (warp == TC_PWARPS)
-					TCT_TRACE(5, g);
 				const long long tl = TCT_NOW();
 				ptx::tc_fence_after();
+				if (KIND == W_Q4K)
+					f = ds[(g & (TC_NDS - 1)) * TC_BM + lrow];
 #pragma unroll
 				for (int hf = 0; hf < 2; hf++) {
-					if (c0 + 16 * hf < item.n_mma) {  // warp-uniform
-						uint32_t p[16], m[16];
-						ptx::tmem_ld16(tlane + TC_COL_P + 64u * buf + c0 + 16 * hf, p);
-						if (KIND == W_Q4K)
-							ptx::tmem_ld16(tlane + TC_COL_M + 64u * buf + c0 + 16 * hf, m);
+					const int col = tok0 + 16 * hf;
+					if (16 * hf < ntok && col < item.n_mma) {  // warp-uniform
+						uint32_t p[16], p2[16];
+						ptx::tmem_ld16(tlane + TC_COL_P + 64u * buf + col, p);
+						if (concat)
+							ptx::tmem_ld16(tlane + TC_COL_P + 64u * buf + item.n_box + col, p2);
 						ptx::tmem_ld_wait();
 #pragma unroll
 						for (int j = 0; j < 16; j++) {
-							float a = __fmaf_rn(f.x, __uint_as_float(p[j]), acc[16 * hf + j]);
-							if (KIND == W_Q4K)
-								a = __fmaf_rn(-f.y, __uint_as_float(m[j]), a);
-							acc[16 * hf + j] = a;
+							const float v = concat ? __uint_as_float(p[j]) + __uint_as_float(p2[j]) : __uint_as_float(p[j]);
+							acc[16 * hf + j] = __fmaf_rn(f.x, v, acc[16 * hf + j]);
+						}
+						if (KIND == W_Q4K) {
+							ptx::tmem_ld16(tlane + TC_COL_M + 64u * buf + col, p);
+							if (concat)
+								ptx::tmem_ld16(tlane + TC_COL_M + 64u * buf + item.n_box + col, p2);
+							ptx::tmem_ld_wait();
+#pragma unroll
+							for (int j = 0; j < 16; j++) {
+								const float v = concat ? __uint_as_float(p[j]) + __uint_as_float(p2[j]) : __uint_as_float(p[j]);
+								acc[16 * hf + j] = __fmaf_rn(-f.y, v, acc[16 * hf + j]);
+							}
 						}
 					}
 				}
@@ -478,8 +530,6 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 				if (lane == 0)
 					ptx::mbar_arrive(ptx::smem_u32(&sh->pempty[buf]));
 				TCT_ADD(1, tl);
-				if (warp == TC_PWARPS)
-					TCT_TRACE(6, g);
 				g++;
 			}
 			if (!alive)
@@ -487,13 +537,13 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 			const long long tst = TCT_NOW();
 			// rows of this work item: lanes hold consecutive output columns (coalesced 128-byte stores)
 			int rid = 0;
-			if (!RAW && c0 + lane < item.n_valid)
-				rid = perm[item.row0 + c0 + lane];
+			if (!RAW && lane < ntok && tok0 + lane < item.n_valid)
+				rid = perm[item.row0 + tok0 + lane];
 #pragma unroll
 			for (int j = 0; j < TC_NT / 2; j++) {
-				const int n = c0 + j;
+				const int n = tok0 + j;
 				const int rj = RAW ? 0 : __shfl_sync(0xffffffffu, rid, j);
-				if (n < item.n_valid) {
+				if (j < ntok && n < item.n_valid) {
 					if (RAW)
 						y[(size_t)(item.row0 + n) * out_stride + (size_t)item.mat_sel * rows_per_matrix + mrow] = acc[j];
 					else
@@ -505,150 +555,176 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 		TCT_ADD(3, tct_start);
 		if (warp == TC_PWARPS && lane == 0)
 			TCT_FLUSH(8, 4);
-	} else if (warp < TC_PWARPS + TC_DWARPS + TC_MWARPS) {
+	} else if (warp < W_TOK) {
 		// ================= MMA issuers =================
-		// One thread can issue a tcgen05.mma only every ~110-130 cycles whatever its N, so the
-		// super-blocks are dealt to TC_MWARPS issuer warps: warp w owns accumulator buffer w and the
-		// super-blocks that use it; MMAs of different issuers run concurrently on different buffers.
-		// The whole warp walks the loop (warp-uniform addresses and descriptors); lane 0 issues.
-		{
-			const uint32_t mw = warp - (TC_PWARPS + TC_DWARPS);
-			const uint32_t leader = (lane == 0) ? 1u : 0u;
-			int s = 0;
-			uint32_t ph = 0, g = 0, tl = 0;
-			bool alive = true;
-			TCT_DECL(5);
-			const long long tct_start = TCT_NOW();
-			for (int t = blockIdx.x; t < total && alive; t += stride_t, tl++) {
-				const TcItem item = tc_item(t, m_tiles, tile_info, rows_per_matrix);
-#ifdef TC_EXP_N
-				const uint32_t idesc = ptx::umma_idesc_f16(TC_BM, TC_EXP_N);
-#else
-				const uint32_t idesc = ptx::umma_idesc_f16(TC_BM, item.n_mma);
-#endif
-				const uint32_t tp = tl & 1u;
-				bool need_x = KIND == W_Q4K;  // this issuer has not yet seen the work item's sub-block sums
-				for (int sbi = 0; sbi < nb && alive; sbi++) {
-					const uint32_t buf = g & 1u;
-					if (buf != mw) {  // the other issuer's super-block: skip its stages
-						s += QK_K / TC_BK;
-						if (s >= TC_S) {
-							s -= TC_S;
-							ph ^= 1u;
-						}
-						g++;
-						continue;
+		// Warp w owns accumulator buffer w and the super-blocks that use it; MMAs of the two issuers
+		// run concurrently on different buffers.  The whole warp walks the loop (warp-uniform
+		// addresses and descriptors); lane 0 issues.
+		const uint32_t mw = warp - W_MMA0;
+		const uint32_t leader = (lane == 0) ? 1u : 0u;
+		int s = 0;
+		uint32_t ph = 0, g = 0, tl = 0;
+		bool alive = true;
+		TCT_DECL(5);
+		const long long tct_start = TCT_NOW();
+		for (int t = blockIdx.x; t < total && alive; t += stride_t, tl++) {
+			const TcItem item = tc_item(t, m_tiles, tile_info, rows_per_matrix);
+			// up to 32 tokens: hi and lo rows are one N = 2 n_box operand (one MMA per k step);
+			// more: two MMAs of N = n_mma on the hi rows and on the lo rows behind them
+			const bool concat = item.n_box <= 32;
+			const uint32_t idesc = ptx::umma_idesc_f16(TC_BM, concat ? 2 * item.n_box : item.n_mma);
+			const uint32_t lo_off = (uint32_t)item.n_box * 128u;
+			bool need_x = KIND == W_Q4K;  // this issuer has not yet seen the work item's sub-block sums
+			bool hold_x = KIND == W_Q4K;  // ... and has not yet released them
+			for (int sbi = 0; sbi < nb && alive; sbi++) {
+				const uint32_t buf = g & 1u;
+				if (buf != mw) {  // the other issuer's super-block: skip its stages
+					s += TC_SPB;
+					if (s >= TC_S) {
+						s -= TC_S;
+						ph ^= 1u;
 					}
-					const long long tpe = TCT_NOW();
-					if (g >= 2u) {
-						const bool ok = tc_wait(ptx::smem_u32(&sh->pempty[buf]), ((g >> 1) & 1u) ^ 1u, abort_flag, status);
-						if (!__all_sync(0xffffffffu, ok)) {
-							alive = false;
-							break;
-						}
-					}
-					TCT_ADD(0, tpe);
-					const uint32_t dP = tmem + TC_COL_P + 64u * buf;
-					for (int q4 = 0; q4 < QK_K / TC_BK; q4++) {
-						const long long tb = TCT_NOW();
-						bool ok = tc_wait(ptx::smem_u32(&sh->bfull[s]), ph, abort_flag, status);
-						TCT_ADD(1, tb);
-						const long long tf = TCT_NOW();
-						ok = ok && tc_wait(ptx::smem_u32(&sh->full[s]), ph, abort_flag, status);
-						if (need_x) {
-							ok = ok && tc_wait(ptx::smem_u32(&sh->xfull[tp]), (tl >> 1) & 1u, abort_flag, status);
-							need_x = false;
-						}
-						if (!__all_sync(0xffffffffu, ok)) {
-							alive = false;
-							break;
-						}
-						TCT_ADD(2, tf);
-						TCT_TRACE(3, g * 4u + q4);
-						const long long ti = TCT_NOW();
-						ptx::tc_fence_after();
-						if (KIND == W_Q4K && q4 == 0) {
-							// M step: mins (16-deep A tile) x sub-block sums of this super-block pair
-							const int xt = sbi >> 3, j = (sbi & 7) >> 1;
-							const uint32_t dM = tmem + TC_COL_M + 64u * buf, am = tmem + TC_COL_AM + 8u * buf;
-							ptx::mma_f16_ts_if(dM, am, ptx::umma_desc_sw128(xq_tile(tp, xt, 0)) + 2 * j, idesc, 0u, leader);
-							ptx::mma_f16_ts_if(dM, am, ptx::umma_desc_sw128(xq_tile(tp, xt, 1)) + 2 * j, idesc, 1u, leader);
-						}
-						const uint64_t bh = ptx::umma_desc_sw128(b_hi(s)), bl = ptx::umma_desc_sw128(b_lo(s));
-						const uint32_t a = tmem + TC_COL_A + 32u * s;
-#pragma unroll
-						for (int kk = 0; kk < TC_BK / 16; kk++) {
-							ptx::mma_f16_ts_if(dP, a + 8 * kk, bh + 2 * kk, idesc, (q4 > 0 || kk > 0) ? 1u : 0u, leader);
-#ifndef TC_EXP_NOLO
-							ptx::mma_f16_ts_if(dP, a + 8 * kk, bl + 2 * kk, idesc, 1u, leader);
-#endif
-						}
-						ptx::mma_commit_if(ptx::smem_u32(&sh->empty[s]), leader);
-						TCT_ADD(3, ti);
-						TCT_TRACE(4, g * 4u + q4);
-						if (++s == TC_S) {
-							s = 0;
-							ph ^= 1u;
-						}
-					}
-					if (!alive)
-						break;
-					ptx::mma_commit_if(ptx::smem_u32(&sh->pfull[buf]), leader);
 					g++;
+					continue;
 				}
-				if (KIND == W_Q4K && alive)
-					ptx::mma_commit_if(ptx::smem_u32(&sh->xempty[tp]), leader);
+				const long long tpe = TCT_NOW();
+				if (g >= 2u) {
+					const bool ok = tc_wait(ptx::smem_u32(&sh->pempty[buf]), ((g >> 1) & 1u) ^ 1u, abort_flag, status);
+					if (!__all_sync(0xffffffffu, ok)) {
+						alive = false;
+						break;
+					}
+				}
+				TCT_ADD(0, tpe);
+				const uint32_t dP = tmem + TC_COL_P + 64u * buf;
+				for (int q4 = 0; q4 < TC_SPB; q4++) {
+					const long long tb = TCT_NOW();
+					bool ok = tc_wait(ptx::smem_u32(&sh->bfull[s]), ph, abort_flag, status);
+					TCT_ADD(1, tb);
+					const long long tf = TCT_NOW();
+					ok = ok && tc_wait(ptx::smem_u32(&sh->full[s]), ph, abort_flag, status);
+					if (need_x) {
+						ok = ok && tc_wait(ptx::smem_u32(&sh->xfull), tl & 1u, abort_flag, status);
+						need_x = false;
+					}
+					if (!__all_sync(0xffffffffu, ok)) {
+						alive = false;
+						break;
+					}
+					TCT_ADD(2, tf);
+					const long long ti = TCT_NOW();
+					ptx::tc_fence_after();
+					if (KIND == W_Q4K && q4 == 0) {
+						// M step: mins (16-deep A tile) x sub-block sums of this super-block pair
+						const int j = sbi >> 1;
+						const uint32_t dM = tmem + TC_COL_M + 64u * buf, am = tmem + TC_COL_AM + 8u * buf;
+						ptx::mma_f16_ts_if(dM, am, ptx::umma_desc_sw128(xq_hi) + 2 * j, idesc, 0u, leader);
+						if (!concat)
+							ptx::mma_f16_ts_if(dM, am, ptx::umma_desc_sw128(xq_hi + lo_off) + 2 * j, idesc, 1u, leader);
+						if (sbi + TC_MWARPS >= nb) {  // this issuer's last M step of the work item
+							ptx::mma_commit_if(ptx::smem_u32(&sh->xempty), leader);
+							hold_x = false;
+						}
+					}
+					const uint64_t bh = ptx::umma_desc_sw128(b_hi(s)), bl = ptx::umma_desc_sw128(b_hi(s) + lo_off);
+					const uint32_t a = tmem + TC_COL_A + 32u * s;
+#pragma unroll
+					for (int kk = 0; kk < TC_BK / 16; kk++) {
+						ptx::mma_f16_ts_if(dP, a + 8 * kk, bh + 2 * kk, idesc, (q4 > 0 || kk > 0) ? 1u : 0u, leader);
+						if (!concat)
+							ptx::mma_f16_ts_if(dP, a + 8 * kk, bl + 2 * kk, idesc, 1u, leader);
+					}
+					ptx::mma_commit_if(ptx::smem_u32(&sh->empty[s]), leader);
+					TCT_ADD(3, ti);
+					if (++s == TC_S) {
+						s = 0;
+						ph ^= 1u;
+					}
+				}
+				if (!alive)
+					break;
+				ptx::mma_commit_if(ptx::smem_u32(&sh->pfull[buf]), leader);
+				g++;
 			}
-			TCT_ADD(4, tct_start);
-			if (lane == 0 && mw == 0)
-				TCT_FLUSH(16, 5);
+			if (hold_x && alive)  // no super-block of this work item was this issuer's
+				ptx::mma_commit_if(ptx::smem_u32(&sh->xempty), leader);
 		}
-	} else {
-		// ================= TMA loader: token operand and sub-block sums =================
+		TCT_ADD(4, tct_start);
+		if (lane == 0 && mw == 0)
+			TCT_FLUSH(16, 5);
+	} else if (warp == W_TOK) {
+		// ================= token loader: token operand and sub-block sums (TMA) =================
 		if (lane == 0) {
-			int sb = 0;
-			uint32_t bph = 0, bit = 0, tl = 0;
+			int s = 0;
+			uint32_t ph = 0, it = 0, tl = 0;
 			bool alive = true;
-			TCT_DECL(2);
+			TCT_DECL(3);
 			const long long tct_start = TCT_NOW();
 			for (int t = blockIdx.x; t < total && alive; t += stride_t, tl++) {
 				const TcItem item = tc_item(t, m_tiles, tile_info, rows_per_matrix);
-				const int n16 = item.n_mma >> 4;
+				const uint32_t box_bytes = 2u * (uint32_t)item.n_box * 128u;  // hi + lo rows of one 64-k box
+				const CUtensorMap *tmp = item.n_box == 16 ? &tm16 : (item.n_box == 32 ? &tm32 : &tm64);
 				if (KIND == W_Q4K) {
-					const uint32_t tp = tl & 1u;
-					if (tl >= 2u && !tc_wait(ptx::smem_u32(&sh->xempty[tp]), ((tl >> 1) & 1u) ^ 1u, abort_flag, status))
+					if (tl >= 1u && !tc_wait(ptx::smem_u32(&sh->xempty), (tl & 1u) ^ 1u, abort_flag, status))
 						break;
-					const uint32_t xb = ptx::smem_u32(&sh->xfull[tp]);
-					ptx::mbar_arrive_expect_tx(xb, (uint32_t)(xt_n * n16) * 2u * 2048u);
-					for (int xt = 0; xt < xt_n; xt++)
-						for (int r = 0; r < n16; r++) {
-							ptx::tma_load_2d(xq_tile(tp, xt, 0) + r * 2048, &tq_hi, xb, xt * 64, item.row0 + 16 * r);
-							ptx::tma_load_2d(xq_tile(tp, xt, 1) + r * 2048, &tq_lo, xb, xt * 64, item.row0 + 16 * r);
-						}
+					const uint32_t xb = ptx::smem_u32(&sh->xfull);
+					ptx::mbar_arrive_expect_tx(xb, box_bytes);
+					ptx::tma_load_3d(xq_hi, item.n_box == 16 ? &tq16 : (item.n_box == 32 ? &tq32 : &tq64), xb, 0, item.row0, 0);
 				}
 				for (int ki = 0; ki < k_iters; ki++) {
 					const long long tw = TCT_NOW();
-					if (bit >= (uint32_t)TC_S && !tc_wait(ptx::smem_u32(&sh->empty[sb]), bph ^ 1u, abort_flag, status)) {
+					if (it >= (uint32_t)TC_S && !tc_wait(ptx::smem_u32(&sh->empty[s]), ph ^ 1u, abort_flag, status)) {
 						alive = false;
 						break;
 					}
 					TCT_ADD(0, tw);
-					const uint32_t fb = ptx::smem_u32(&sh->bfull[sb]);
-					// only the rows the MMA will read: 16-row boxes (2 KB each, whole swizzle groups)
-					ptx::mbar_arrive_expect_tx(fb, (uint32_t)n16 * 2u * 2048u);
-					for (int r = 0; r < n16; r++) {
-						ptx::tma_load_2d(b_hi(sb) + r * 2048, &tm_hi, fb, ki * TC_BK, item.row0 + 16 * r);
-						ptx::tma_load_2d(b_lo(sb) + r * 2048, &tm_lo, fb, ki * TC_BK, item.row0 + 16 * r);
-					}
-					bit++;
-					if (++sb == TC_S) {
-						sb = 0;
-						bph ^= 1u;
+					const long long ti = TCT_NOW();
+					const uint32_t fb = ptx::smem_u32(&sh->bfull[s]);
+					// one box: 64 k x n_box rows x (hi, lo); a thread can issue a TMA only every ~100 cycles
+					ptx::mbar_arrive_expect_tx(fb, box_bytes);
+					ptx::tma_load_3d(b_hi(s), tmp, fb, ki * TC_BK, item.row0, 0);
+					TCT_ADD(1, ti);
+					it++;
+					if (++s == TC_S) {
+						s = 0;
+						ph ^= 1u;
 					}
 				}
 			}
-			TCT_ADD(1, tct_start);
-			TCT_FLUSH(24, 2);
+			TCT_ADD(2, tct_start);
+			TCT_FLUSH(24, 3);
+		}
+	} else {
+		// ================= weight loader: packed super-blocks -> shared memory =================
+		int wb = 0;
+		uint32_t wph = 0, wc = 0;
+		bool alive = true;
+		for (int t = blockIdx.x; t < total && alive; t += stride_t) {
+			const TcItem item = tc_item(t, m_tiles, tile_info, rows_per_matrix);
+			for (int sbi = 0; sbi < nb; sbi++) {
+				if (wc >= (uint32_t)TC_NWB && !tc_wait_warp(ptx::smem_u32(&sh->wempty[wb]), wph ^ 1u, abort_flag, status, lane)) {
+					alive = false;
+					break;
+				}
+				const uint32_t bar = ptx::smem_u32(&sh->wfull[wb]);
+				if (KIND == W_Q4K) {
+					if (lane == 0) {
+						ptx::mbar_arrive_expect_tx(bar, TC_BM * Q4K_BYTES);
+						ptx::tma_load_2d(w_buf(wb), item.mat_sel ? &tw1 : &tw0, bar, sbi * Q4K_BYTES,
+								 item.le * rows_per_matrix + item.m0);
+					}
+				} else if (lane == 0) {
+					// box = (one record, 8 rows of a group, 16 groups)
+					ptx::mbar_arrive_expect_tx(bar, TC_BM * TC_Q6_ROW);
+					ptx::tma_load_3d(w_buf(wb), item.mat_sel ? &tw1 : &tw0, bar, sbi * TC_Q6_ROW, 0,
+							 (item.le * rows_per_matrix + item.m0) >> 3);
+				}
+				wc++;
+				if (++wb == TC_NWB) {
+					wb = 0;
+					wph ^= 1u;
+				}
+			}
 		}
 	}
 
@@ -659,7 +735,7 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm_hi, const __grid_constant
 	}
 	ptx::tc_fence_before();
 	__syncthreads();
-	if (warp == TC_PWARPS + TC_DWARPS)
+	if (warp == W_MMA0)
 		ptx::tmem_dealloc(tmem, TC_TMEM_COLS);
 }
 
@@ -682,8 +758,8 @@ static PFN_encodeTiled get_encode_fn()
 	return fn;
 }
 
-// fp16 [rows][cols] row-major, box = 64 columns x 16 rows, 128-byte swizzle.
-static int make_tmap(tie_cuda_ctx *c, CUtensorMap *tm, void *base, size_t rows, size_t cols)
+static int encode_2d(tie_cuda_ctx *c, CUtensorMap *tm, CUtensorMapDataType type, size_t elem, void *base, size_t rows, size_t cols,
+		     unsigned box_cols, unsigned box_rows, CUtensorMapSwizzle swz)
 {
 	PFN_encodeTiled enc = get_encode_fn();
 	if (!enc) {
@@ -691,11 +767,11 @@ static int make_tmap(tie_cuda_ctx *c, CUtensorMap *tm, void *base, size_t rows, 
 		return TIE_CUDA_ECUDA;
 	}
 	cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-	cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-	cuuint32_t box[2] = {(cuuint32_t)TC_BK, 16u};
+	cuuint64_t strides[1] = {(cuuint64_t)cols * elem};
+	cuuint32_t box[2] = {box_cols, box_rows};
 	cuuint32_t estr[2] = {1, 1};
-	CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-			 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+	CUresult r = enc(tm, type, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+			 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
 	if (r != CUDA_SUCCESS) {
 		snprintf(c->cuda_err, sizeof(c->cuda_err), "cuTensorMapEncodeTiled failed: %d", (int)r);
 		return TIE_CUDA_ECUDA;
@@ -703,17 +779,75 @@ static int make_tmap(tie_cuda_ctx *c, CUtensorMap *tm, void *base, size_t rows, 
 	return TIE_CUDA_OK;
 }
 
+// Split fp16 operand [hi | lo][rows][cols] (lo array right behind hi), box = 64 columns x box_rows
+// rows x 2, 128-byte swizzle: hi rows land first in shared memory, the lo rows directly behind.
+static int make_tmap(tie_cuda_ctx *c, CUtensorMap *tm, void *base, size_t rows, size_t cols, unsigned box_rows)
+{
+	PFN_encodeTiled enc = get_encode_fn();
+	if (!enc) {
+		snprintf(c->cuda_err, sizeof(c->cuda_err), "cuTensorMapEncodeTiled entry point not found");
+		return TIE_CUDA_ECUDA;
+	}
+	cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, 2};
+	cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)rows * cols * 2};
+	cuuint32_t box[3] = {(cuuint32_t)TC_BK, box_rows, 2};
+	cuuint32_t estr[3] = {1, 1, 1};
+	CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+			 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+	if (r != CUDA_SUCCESS) {
+		snprintf(c->cuda_err, sizeof(c->cuda_err), "cuTensorMapEncodeTiled (token operand) failed: %d", (int)r);
+		return TIE_CUDA_ECUDA;
+	}
+	return TIE_CUDA_OK;
+}
+
+// Byte map of an expert tensor for the weight loader.  Q4_K: [experts x rows][row bytes], box = one
+// 144-byte block x 128 rows.  Q6_K: [groups][8 rows][row records], box = one 208-byte record x 8 x 16.
+int tc_make_weight_map(tie_cuda_ctx *c, DevTensor &t)
+{
+	t.has_map = false;
+	if (t.rows % TC_BM || t.k % QK_K)
+		return TIE_CUDA_OK;
+	const int nb = t.k / QK_K;
+	if (t.kind == W_Q4K) {
+		int rc = encode_2d(c, &t.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, t.ptr, (size_t)t.rows * c->n_local, (size_t)nb * Q4K_BYTES,
+				   Q4K_BYTES, TC_BM, CU_TENSOR_MAP_SWIZZLE_NONE);
+		if (rc)
+			return rc;
+	} else {
+		PFN_encodeTiled enc = get_encode_fn();
+		if (!enc) {
+			snprintf(c->cuda_err, sizeof(c->cuda_err), "cuTensorMapEncodeTiled entry point not found");
+			return TIE_CUDA_ECUDA;
+		}
+		cuuint64_t dims[3] = {(cuuint64_t)nb * Q6K_RECORD, 8, (cuuint64_t)t.rows * c->n_local / 8};
+		cuuint64_t strides[2] = {(cuuint64_t)nb * Q6K_RECORD, (cuuint64_t)q6k_r8_group_bytes(nb)};
+		cuuint32_t box[3] = {Q6K_RECORD, 8, TC_BM / 8};
+		cuuint32_t estr[3] = {1, 1, 1};
+		CUresult r = enc(&t.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, t.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+				 CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+		if (r != CUDA_SUCCESS) {
+			snprintf(c->cuda_err, sizeof(c->cuda_err), "cuTensorMapEncodeTiled (Q6_K weights) failed: %d", (int)r);
+			return TIE_CUDA_ECUDA;
+		}
+	}
+	t.has_map = true;
+	return TIE_CUDA_OK;
+}
+
 int tc_setup(tie_cuda_ctx *c)
 {
 	Scratch &s = c->s;
 	const size_t H = c->cfg.hidden, F = c->cfg.ffn_dim;
-	void *bases[8] = {s.xs_hi, s.xs_lo, s.hs_hi, s.hs_lo, s.xq_hi, s.xq_lo, s.hq_hi, s.hq_lo};
-	size_t cols[8] = {H, H, F, F, (size_t)xq_cols((int)H), (size_t)xq_cols((int)H), (size_t)xq_cols((int)F), (size_t)xq_cols((int)F)};
-	for (int a = 0; a < 8; a++) {
-		int rc = make_tmap(c, &c->tmap[a], bases[a], s.rows_pad, cols[a]);
-		if (rc)
-			return rc;
-	}
+	// tmap[array * 3 + box]: array 0 = x, 1 = h, 2 = sums of x, 3 = sums of h; box rows 16, 32, 64
+	void *bases[4] = {s.xs_hi, s.hs_hi, s.xq_hi, s.hq_hi};
+	size_t cols[4] = {H, F, (size_t)xq_cols((int)H), (size_t)xq_cols((int)F)};
+	for (int a = 0; a < 4; a++)
+		for (int b = 0; b < 3; b++) {
+			int rc = make_tmap(c, &c->tmap[a * 3 + b], bases[a], s.rows_pad, cols[a], 16u << b);
+			if (rc)
+				return rc;
+		}
 #define TC_ATTR(KIND, RAW) \
 	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_sb<KIND, RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM))
 	TC_ATTR(W_Q4K, false);
@@ -725,23 +859,31 @@ int tc_setup(tie_cuda_ctx *c)
 	return TIE_CUDA_OK;
 }
 
-// arr: 0 = the split inputs x (gate/up), 2 = the split activations h (down).
+// arr: 0 = the split inputs x (gate/up), 1 = the split activations h (down).
 template <WKind KIND, bool RAW>
 static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1, int arr, float *y, float out_scale)
 {
 	Scratch &s = c->s;
 	const int m_tiles = (RAW ? 2 : 1) * t0.rows / TC_BM;
+	const CUtensorMap &w0m = t0.map;
+	const CUtensorMap &w1m = t1 ? t1->map : t0.map;
 	grouped_gemm_sb<KIND, RAW><<<c->sm_count, TC_THREADS, TC_SMEM, c->stream>>>(
-		c->tmap[arr], c->tmap[arr + 1], c->tmap[4 + arr], c->tmap[5 + arr], t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride, t0.k,
-		s.tile_info, s.tile_start, c->n_local, m_tiles, y, s.perm, RAW ? 2 * t0.rows : t0.rows, out_scale, s.status, t0.rows);
+		c->tmap[arr * 3], c->tmap[arr * 3 + 1], c->tmap[arr * 3 + 2], c->tmap[(2 + arr) * 3], c->tmap[(2 + arr) * 3 + 1],
+		c->tmap[(2 + arr) * 3 + 2], w0m, w1m, t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride,
+		t0.k, s.tile_info, s.tile_start, c->n_local, m_tiles, y, s.perm, RAW ? 2 * t0.rows : t0.rows, out_scale, s.status, t0.rows);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
 
+static bool tc_tensor_ok(const DevTensor &t)
+{
+	// Q4_K needs all sub-block sums of a row in one 64-wide tile (k <= 2048)
+	return t.has_map && t.rows % TC_BM == 0 && t.k % QK_K == 0 && (t.kind != W_Q4K || t.k <= 2048);
+}
+
 bool tc_supported(const tie_cuda_ctx *c, const Layer &L)
 {
-	return c->tmaps_ok && L.gate.kind == L.up.kind && L.gate.rows % TC_BM == 0 && L.down.rows % TC_BM == 0 &&
-	       L.gate.k % QK_K == 0 && L.down.k % QK_K == 0 && L.gate.k <= TC_XT * 2048 && L.down.k <= TC_XT * 2048;
+	return c->tmaps_ok && L.gate.kind == L.up.kind && tc_tensor_ok(L.gate) && tc_tensor_ok(L.up) && tc_tensor_ok(L.down);
 }
 
 // xs_hi/xs_lo (and xq_hi/xq_lo for Q4_K) must hold the split inputs in sorted order; the sort must
@@ -764,8 +906,8 @@ int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, float *y)
 {
 	(void)n_rows;
 	if (L.down.kind == W_Q4K)
-		return launch_tc_t<W_Q4K, false>(c, L.down, nullptr, 2, y, 1.0f / TC_H_SCALE);
-	return launch_tc_t<W_Q6K_R8, false>(c, L.down, nullptr, 2, y, 1.0f / TC_H_SCALE);
+		return launch_tc_t<W_Q4K, false>(c, L.down, nullptr, 1, y, 1.0f / TC_H_SCALE);
+	return launch_tc_t<W_Q6K_R8, false>(c, L.down, nullptr, 1, y, 1.0f / TC_H_SCALE);
 }
 
 }  // namespace tie
@@ -780,11 +922,5 @@ extern "C" int tie_debug_tc_cycles(unsigned long long *out)
 	if (cudaMemcpyFromSymbol(out, tie::g_tc_cycles, sizeof(zero)) != cudaSuccess)
 		return -1;
 	return cudaMemcpyToSymbol(tie::g_tc_cycles, zero, sizeof(zero)) == cudaSuccess ? 0 : -1;
-}
-extern "C" int tie_debug_tc_trace(long long *out)
-{
-	if (cudaDeviceSynchronize() != cudaSuccess)
-		return -1;
-	return cudaMemcpyFromSymbol(out, tie::g_tc_trace, sizeof(long long) * 8 * 128) == cudaSuccess ? 0 : -1;
 }
 #endif
