@@ -11,10 +11,11 @@
 // (tc_dequant.cuh), so the tensor cores multiply EXACT small-integer fp16 weights with the
 // activations (split into fp16 hi + lo: 22 significand bits; one fp16 is not accurate enough
 // for the 1e-3 parity bound) and the fp32 block factors are applied once per super-block:
-//   out[r][n] = sum_B  d[r][B]    * sum_{k in B}  (sc*q)[r][k] * x[n][k]          ("P" partial sums)
-//                    - dmin[r][B] * sum_{b in B}  m[r][b] * xsum[n][b]            ("M" partial sums)
-// where xsum[n][b] is the sum of x[n] over the 32-wide sub-block b (Q4_K only; one extra 16-deep
-// MMA step per super-block).
+//   out[r][n] = sum_B d[r][B] * sum_{k in B} (sc*q)[r][k] * x[n][k]  -  sum_b (dmin*m)[r][b] * xsum[n][b]
+// where xsum[n][b] is the sum of x[n] over the 32-wide sub-block b (Q4_K only).  The second term
+// is one small extra GEMM per work item (k = number of sub-blocks, at most 64): its weights
+// dmin*m (17 significant bits) are split into fp16 hi + lo and it runs ahead of the super-blocks
+// as a "min phase" through the same ring and accumulator buffers.
 //
 // The kernel is persistent: one CTA per SM walks (token tile, 128-row tile) work items.  Roles:
 //   * a weight loader thread brings the packed blocks of one super-block x 128 rows into shared
@@ -25,11 +26,13 @@
 //   * a token loader thread issues TMA tile loads of the token operand (hi/lo fp16, expert-sorted
 //     rows, 16-row boxes: only rows the expert really has) and of the sub-block sums;
 //   * two MMA issuer warps issue tcgen05.mma (kind::f16, fp32 accumulate), per 16-wide k step
-//     P += A.B_hi, P += A.B_lo.  A thread can issue only one MMA per ~110-130 cycles whatever its
-//     N, so consecutive super-blocks go to different issuers, each with its own accumulator buffer;
+//     P += A.B_hi, P += A.B_lo (one MMA over the stacked hi and lo rows when the tile has at most
+//     32 tokens).  A thread can issue only one MMA per ~110-130 cycles whatever its N, so
+//     consecutive super-blocks go to different issuers, each with two of the four accumulator
+//     buffers;
 //   * 8 drain warps take a finished super-block out of tensor memory (tcgen05.ld), fold it into
-//     fp32 registers with d / dmin, and after the last super-block of a work item store the rows —
-//     while the MMAs of the next super-blocks / work item already run.
+//     fp32 registers with d (-1 for the min phase), and after the last super-block of a work item
+//     store the rows — while the MMAs of the next super-blocks / work item already run.
 // All hand-offs go through mbarriers (tcgen05.commit on the MMA side).  Every wait is bounded: on
 // a timeout the CTA raises ST_WAIT_TIMEOUT in the status word, all roles leave their loops, tensor
 // memory is released and the kernel returns.
@@ -48,19 +51,17 @@ constexpr int TC_PWARPS = 8;		  // producer warps
 constexpr int TC_DWARPS = 8;		  // drain warps
 constexpr int TC_MWARPS = 2;		  // MMA issuer warps: one per accumulator buffer
 constexpr int TC_THREADS = (TC_PWARPS + TC_DWARPS + TC_MWARPS + 2) * 32;  // + token loader + weight loader
-constexpr int TC_S = 7;	   // ring stages: weight tiles in tensor memory, token tiles in shared memory
-constexpr int TC_NWB = 3;  // packed super-blocks in flight (shared memory)
-constexpr int TC_NDS = 4;  // block-factor hand-off buffers (producers -> drain warps)
+constexpr int TC_S = 8;	    // ring stages: weight tiles in tensor memory, token tiles in shared memory
+constexpr int TC_NBUF = 4;  // accumulator buffers (two per MMA issuer)
+constexpr int TC_NDS = 8;   // block-factor hand-off buffers (producers -> drain warps)
 constexpr long long TC_WAIT_CYCLES = 1ll << 30;	 // about half a second of SM clocks
 constexpr float TC_H_SCALE = 1.0f / 256.0f;	 // keeps SwiGLU outputs inside fp16 range; exact (power of two)
 
 // tensor-memory columns
-constexpr uint32_t TC_COL_P = 0;     // 2 x 64: P partial sums
-constexpr uint32_t TC_COL_M = 128;   // 2 x 64: M partial sums
-constexpr uint32_t TC_COL_AM = 256;  // 2 x 8:  A tile of the M step (8 mins + 8 zeros per row)
-constexpr uint32_t TC_COL_A = 288;   // TC_S x 32: A ring
+constexpr uint32_t TC_COL_P = 0;    // TC_NBUF x 64: partial sums of one super-block (or of the min phase)
+constexpr uint32_t TC_COL_A = 256;  // TC_S x 32: A ring
 constexpr uint32_t TC_TMEM_COLS = 512;
-static_assert(TC_COL_A + TC_S * 32 <= TC_TMEM_COLS, "tensor memory budget");
+static_assert(TC_COL_A + TC_S * 32 <= TC_TMEM_COLS && TC_NBUF * 64 <= TC_COL_A, "tensor memory budget");
 
 // shared memory
 constexpr int TC_B_TILE = TC_NT * TC_BK * 2;  // bytes of one (hi or lo) token tile
@@ -69,25 +70,32 @@ constexpr int TC_B_STAGE = 2 * TC_B_TILE;
 // (192 bytes of quants + 16 bytes of scales) of the rows back to back, one TMA box.  Row strides
 // of 9 and 13 x 16 bytes: 16-byte reads by 32 consecutive rows are bank-conflict free.
 constexpr int TC_Q6_ROW = Q6K_RECORD;
-constexpr int TC_WBUF = 27 * 1024;
-static_assert(TC_BM * Q4K_BYTES <= TC_WBUF && TC_BM * TC_Q6_ROW <= TC_WBUF, "packed super-block buffer");
-constexpr int TC_OFF_W = TC_S * TC_B_STAGE;
-constexpr int TC_OFF_XQ = TC_OFF_W + TC_NWB * TC_WBUF;
-constexpr int TC_OFF_DS = TC_OFF_XQ + TC_B_STAGE;
-constexpr int TC_OFF_BAR = TC_OFF_DS + TC_NDS * TC_BM * 8;
-constexpr int TC_SMEM = TC_OFF_BAR + 512 + 1024 /* alignment slack */;
-static_assert(TC_SMEM <= 227 * 1024, "shared memory budget");
+constexpr int TC_NWB_MAX = 4;
+template <WKind KIND>
+struct TcSmem {
+	static constexpr bool Q4 = KIND == W_Q4K;
+	static constexpr int NWB = Q4 ? 4 : 3;	// packed super-blocks in flight
+	static constexpr int WBUF = TC_BM * (Q4 ? Q4K_BYTES : TC_Q6_ROW);
+	static constexpr int OFF_W = TC_S * TC_B_STAGE;
+	static constexpr int OFF_XQ = OFF_W + NWB * WBUF;		  // sub-block sums of the work item (Q4_K)
+	static constexpr int OFF_DS = OFF_XQ + (Q4 ? TC_B_STAGE : 0);	  // block factors (Q4_K)
+	static constexpr int OFF_BAR = OFF_DS + (Q4 ? TC_NDS * TC_BM * 8 : 0);
+	static constexpr int SMEM = OFF_BAR + 512 + 1024 /* alignment slack */;
+	static_assert(WBUF % 1024 == 0 && NWB <= TC_NWB_MAX, "packed super-block buffers");
+	static_assert(SMEM <= 227 * 1024, "shared memory budget");
+};
 
 struct TcShared {
-	uint64_t full[TC_S];	  // weight stage written by the producers
-	uint64_t bfull[TC_S];	  // token tiles of the stage landed (TMA transaction bytes)
-	uint64_t empty[TC_S];	  // stage consumed by the MMAs (both operands)
-	uint64_t wfull[TC_NWB];	  // packed super-block landed
-	uint64_t wempty[TC_NWB];  // ... and expanded
-	uint64_t pfull[2];	  // accumulator buffer complete (one super-block)
-	uint64_t pempty[2];	  // accumulator buffer read out by the drain warps
-	uint64_t xfull;		  // sub-block sums of a work item landed
-	uint64_t xempty;	  // ... and consumed (by the last M step of each issuer)
+	uint64_t full[TC_S];	      // weight stage written by its producer group
+	uint64_t bfull[TC_S];	      // token tiles of the stage landed (TMA transaction bytes)
+	uint64_t empty[TC_S];	      // stage consumed by the MMAs (both operands)
+	uint64_t wfull[TC_NWB_MAX];   // packed super-block landed
+	uint64_t wempty[TC_NWB_MAX];  // ... and expanded
+	uint64_t pfull[TC_NBUF];      // accumulator buffer complete (one super-block)
+	uint64_t pempty[TC_NBUF];     // accumulator buffer read out by the drain warps
+	uint64_t xfull;		      // sub-block sums of a work item landed
+	uint64_t xempty;	      // ... and consumed by the min phase
+	uint64_t msync;		      // producer warps have all written their part of the min-phase tiles
 	uint32_t tmem_base;
 	uint32_t abort;
 };
@@ -97,6 +105,12 @@ static_assert(sizeof(TcShared) <= 512, "barrier block");
 // its clock64() deltas to g_tc_cycles; tie_debug_tc_cycles() reads and clears them.
 #ifdef TC_TIMING
 __device__ unsigned long long g_tc_cycles[32];
+__device__ long long g_tc_trace[8][256];
+#define TCT_TRACE(r, i)                                            \
+	do {                                                       \
+		if (RAW && blockIdx.x == 0 && (i) < 256u && lane == 0)    \
+			g_tc_trace[r][i] = clock64();              \
+	} while (0)
 #define TCT_DECL(n) long long tct_[n] = {0}
 #define TCT_NOW() clock64()
 #define TCT_ADD(i, t0) tct_[i] += clock64() - (t0)
@@ -110,6 +124,7 @@ __device__ unsigned long long g_tc_cycles[32];
 #define TCT_NOW() 0ll
 #define TCT_ADD(i, t0) (void)(t0)
 #define TCT_FLUSH(base, n)
+#define TCT_TRACE(r, i)
 #endif
 
 // Bounded wait: false (and the abort flag raised) when the barrier does not flip in time or
@@ -150,11 +165,15 @@ struct TcItem {
 	int mat_sel, m0;  // which matrix (RAW: 0 gate, 1 up) and first row inside it
 };
 
-__device__ __forceinline__ TcItem tc_item(int t, int m_tiles, const int4 *__restrict__ tile_info, int rows_per_matrix)
+// tl: how many work items of this CTA precede t; the first TC_ITEMS token-tile records of a CTA
+// are staged in shared memory (s_items) when the kernel starts.
+constexpr int TC_ITEMS = 48;
+__device__ __forceinline__ TcItem tc_item(int t, int tl, const int4 *s_items, int m_tiles, const int4 *__restrict__ tile_info,
+					  int rows_per_matrix)
 {
 	TcItem it;
 	const int slot = t / m_tiles, mt = t - slot * m_tiles;
-	const int4 ti = __ldg(tile_info + slot);
+	const int4 ti = tl < TC_ITEMS ? s_items[tl] : __ldg(tile_info + slot);
 	it.le = ti.x;
 	it.row0 = ti.y;
 	it.n_valid = ti.z;
@@ -193,18 +212,18 @@ struct Expander;
 template <>
 struct Expander<W_Q4K> {
 	uint32_t rowaddr;	  // this row's 144-byte block
-	uint32_t sc8[2], mn8[2];  // the 8 scales and 8 mins of the block as bytes (get_scale_min_k4, math_scalar.c:91-100)
+	uint4 hdr;		  // its first 16 bytes: d | dmin, packed 6-bit scales and mins
+	uint32_t sc8[2];	  // the 8 scales of the block as bytes (get_scale_min_k4, math_scalar.c:91-100)
 	float2 factors;		  // d, dmin
 	__device__ __forceinline__ void prepare(uint32_t wbuf, int row)
 	{
 		rowaddr = wbuf + (uint32_t)row * Q4K_BYTES;
-		const uint4 hdr = lds128(rowaddr);
+		hdr = lds128(rowaddr);
 		factors = make_float2(half_bits_to_float(hdr.x & 0xffffu), half_bits_to_float(hdr.x >> 16));
 		sc8[0] = hdr.y & 0x3F3F3F3Fu;
-		mn8[0] = hdr.z & 0x3F3F3F3Fu;
 		sc8[1] = (hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u);
-		mn8[1] = ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u);
 	}
+	__device__ __forceinline__ uint4 header() const { return hdr; }
 	// this thread's 32 weights of stage p -> 16 columns of its lane in the A tile
 	__device__ __forceinline__ void emit(int p, int hs, uint32_t tile) const
 	{
@@ -228,18 +247,24 @@ struct Expander<W_Q4K> {
 			ptx::tmem_st4(tile + 4u * (4u + 2u * hs + cc), h0[0], h0[1], h1[0], h1[1]);  // k = 32 + 16 hs + 8 cc ..
 		}
 	}
-	// A tile of the M step of super-block sbi: the 8 mins of the row in the half of the 16-deep
-	// step that belongs to this super-block (sub-block sums of two super-blocks share a step).
-	__device__ __forceinline__ void emit_mins(int sbi, uint32_t tile) const
+	// Min phase: the products dmin * m of block B of this row (header hdr), exact in fp32 (11 x 6
+	// bits), split into fp16 hi + lo: columns 4B .. 4B+3 of the thread's lane in the two A tiles.
+	static __device__ __forceinline__ void emit_min_block(const uint4 &hdr, int B, uint32_t tile_hi, uint32_t tile_lo)
 	{
-		const __half2 k1024 = __float2half2_rn(1024.0f);
-		const uint32_t m01 = h2_bits(__hsub2(byte_pair_1024(mn8[0], 0x7150u), k1024));
-		const uint32_t m23 = h2_bits(__hsub2(byte_pair_1024(mn8[0], 0x7352u), k1024));
-		const uint32_t m45 = h2_bits(__hsub2(byte_pair_1024(mn8[1], 0x7150u), k1024));
-		const uint32_t m67 = h2_bits(__hsub2(byte_pair_1024(mn8[1], 0x7352u), k1024));
-		const uint32_t odd = (uint32_t)(sbi & 1);
-		ptx::tmem_st4(tile + 4u * odd, m01, m23, m45, m67);
-		ptx::tmem_st4(tile + 4u * (odd ^ 1u), 0u, 0u, 0u, 0u);
+		const float dmin = half_bits_to_float(hdr.x >> 16);
+		const uint32_t mn[2] = {hdr.z & 0x3F3F3F3Fu, ((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u)};
+		uint32_t hi[4], lo[4];
+#pragma unroll
+		for (int j = 0; j < 4; j++) {
+			const uint32_t w = mn[j >> 1] >> (16 * (j & 1));
+			const float p0 = dmin * (float)(w & 0xffu), p1 = dmin * (float)((w >> 8) & 0xffu);
+			const __half2 h = __floats2half2_rn(p0, p1);
+			const float2 f = __half22float2(h);
+			hi[j] = h2_bits(h);
+			lo[j] = h2_bits(__floats2half2_rn(p0 - f.x, p1 - f.y));
+		}
+		ptx::tmem_st4(tile_hi + 4u * B, hi[0], hi[1], hi[2], hi[3]);
+		ptx::tmem_st4(tile_lo + 4u * B, lo[0], lo[1], lo[2], lo[3]);
 	}
 };
 
@@ -248,6 +273,7 @@ struct Expander<W_Q6K_R8> {
 	uint32_t rowaddr;  // this row's 4 x 48 bytes of quants
 	uint32_t scaddr;   // this row's 16 scale bytes
 	float2 factors;
+	__device__ __forceinline__ uint4 header() const { return make_uint4(0, 0, 0, 0); }
 	__device__ __forceinline__ void prepare(uint32_t wbuf, int row)
 	{
 		rowaddr = wbuf + (uint32_t)row * TC_Q6_ROW;
@@ -288,7 +314,6 @@ struct Expander<W_Q6K_R8> {
 			ptx::tmem_st4(tile + 4u * (4u + 2u * hs + cc), v0[0], v0[1], v1[0], v1[1]);
 		}
 	}
-	__device__ __forceinline__ void emit_mins(int, uint32_t) const {}
 };
 
 // RAW: products are stored as fp32 in expert-sorted row order, y[row0 + n][matrix * rows + mrow]
@@ -297,6 +322,10 @@ struct Expander<W_Q6K_R8> {
 // tm16/32/64: maps of the split token operand ([hi | lo][rows][k], box 64 k x 16/32/64 rows x 2);
 // tq16/32/64: the same of its sub-block sums; tw0 / tw1: byte maps of the two weight tensors,
 // box = packed super-block x 128 rows.
+//
+// Every role walks the same sequence of "phases": per work item the min phase (Q4_K; two ring
+// stages: hi and lo tiles of dmin*m) and then the super-blocks (four ring stages each).  Phase
+// number g selects the accumulator buffer (g % 4) and the MMA issuer (g % 2).
 template <WKind KIND, bool RAW>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant__ CUtensorMap tm32,
@@ -307,8 +336,11 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 		const int *__restrict__ tile_start, int n_local, int m_tiles, float *__restrict__ y, const int *__restrict__ perm,
 		int out_stride, float out_scale, unsigned *__restrict__ status, int rows_per_matrix)
 {
+	using Sm = TcSmem<KIND>;
+	constexpr bool Q4 = KIND == W_Q4K;
 	extern __shared__ uint8_t smem_raw[];
 	__shared__ int s_total;
+	__shared__ int4 s_items[TC_ITEMS];
 #ifdef TC_TIMING
 	const long long tct_kernel_start = clock64();
 #endif
@@ -318,37 +350,44 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 	const int total = s_total;
 	if ((int)blockIdx.x >= total)
 		return;
+	if (threadIdx.x < TC_ITEMS) {
+		const int t = blockIdx.x + threadIdx.x * gridDim.x;
+		if (t < total)
+			s_items[threadIdx.x] = tile_info[t / m_tiles];
+	}
 	const int nb = k_dim / QK_K;
 	const int k_iters = k_dim / TC_BK;
+	const int min_k16 = (8 * nb + 15) >> 4;	 // 16-deep k steps of the min phase (8 sub-blocks per block)
 
 	const uint32_t raw = ptx::smem_u32(smem_raw);
 	const uint32_t tiles = (raw + 1023u) & ~1023u;
 	uint8_t *smem = smem_raw + (tiles - raw);
-	TcShared *sh = reinterpret_cast<TcShared *>(smem + TC_OFF_BAR);
-	float2 *ds = reinterpret_cast<float2 *>(smem + TC_OFF_DS);  // [TC_NDS][128] (d, dmin) of the rows (Q4_K)
+	TcShared *sh = reinterpret_cast<TcShared *>(smem + Sm::OFF_BAR);
+	float2 *ds = reinterpret_cast<float2 *>(smem + Sm::OFF_DS);  // [TC_NDS][128] (d, dmin) of the rows (Q4_K)
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
 	// token tiles of ring stage s: n_box hi rows, directly followed by n_box lo rows
 	auto b_hi = [&](int s) -> uint32_t { return tiles + s * TC_B_STAGE; };
-	const uint32_t xq_hi = tiles + TC_OFF_XQ;
-	auto w_buf = [&](int wb) -> uint32_t { return tiles + TC_OFF_W + wb * TC_WBUF; };
+	const uint32_t xq_hi = tiles + Sm::OFF_XQ;
+	auto w_buf = [&](int wb) -> uint32_t { return tiles + Sm::OFF_W + wb * Sm::WBUF; };
 
 	if (threadIdx.x == 0) {
 		for (int s = 0; s < TC_S; s++) {
-			ptx::mbar_init(ptx::smem_u32(&sh->full[s]), TC_PWARPS);
+			ptx::mbar_init(ptx::smem_u32(&sh->full[s]), TC_PWARPS / 2);
 			ptx::mbar_init(ptx::smem_u32(&sh->empty[s]), 1);
 			ptx::mbar_init(ptx::smem_u32(&sh->bfull[s]), 1);
 		}
-		for (int s = 0; s < TC_NWB; s++) {
+		for (int s = 0; s < Sm::NWB; s++) {
 			ptx::mbar_init(ptx::smem_u32(&sh->wfull[s]), 1);
 			ptx::mbar_init(ptx::smem_u32(&sh->wempty[s]), TC_PWARPS);
 		}
-		for (int s = 0; s < 2; s++) {
+		for (int s = 0; s < TC_NBUF; s++) {
 			ptx::mbar_init(ptx::smem_u32(&sh->pfull[s]), 1);
 			ptx::mbar_init(ptx::smem_u32(&sh->pempty[s]), TC_DWARPS);
 		}
 		ptx::mbar_init(ptx::smem_u32(&sh->xfull), 1);
-		ptx::mbar_init(ptx::smem_u32(&sh->xempty), TC_MWARPS);
+		ptx::mbar_init(ptx::smem_u32(&sh->xempty), 1);
+		ptx::mbar_init(ptx::smem_u32(&sh->msync), TC_PWARPS);
 		sh->abort = 0;
 		ptx::fence_barrier_init();
 		ptx::fence_proxy_async_smem();
@@ -362,7 +401,7 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 		ptx::prefetch_tmap(&tm16);
 		ptx::prefetch_tmap(&tm32);
 		ptx::prefetch_tmap(&tm64);
-		if (KIND == W_Q4K) {
+		if (Q4) {
 			ptx::prefetch_tmap(&tq16);
 			ptx::prefetch_tmap(&tq32);
 			ptx::prefetch_tmap(&tq64);
@@ -382,13 +421,30 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 
 	if (warp < TC_PWARPS) {
 		// ================= producers: packed blocks (shared memory) -> integer A tiles (tensor memory) =================
-		const int row = threadIdx.x & 127, hs = threadIdx.x >> 7;
+		// Two groups of four warps (one warp per 32-row quadrant of tensor memory): group j expands
+		// stages 2j and 2j+1 of every super-block, each thread all 64 k of its row per stage, so that
+		// a warp synchronises (ring barriers, tcgen05.wait::st) once per super-block instead of once
+		// per stage and the two groups work on different stages at the same time.
+		const int row = threadIdx.x & 127, grp = threadIdx.x >> 7;
 		const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-		int s = 0, wb = 0;
-		uint32_t ph = 0, wph = 0, it = 0, g = 0;
+		int s = 0, wb = 0;  // s: ring slot of the first stage of the next phase
+		uint32_t ph = 0, wph = 0, mph = 0, it = 0, g = 0;
 		bool alive = true;
 		TCT_DECL(5);
 		const long long tct_start = TCT_NOW();
+		// ring slot and barrier phase of the stage `off` stages after (s, ph)
+		auto slot_of = [&](int off, int &so, uint32_t &pho) {
+			so = s + off;
+			pho = ph;
+			if (so >= TC_S) {
+				so -= TC_S;
+				pho ^= 1u;
+			}
+		};
+		// min phase (after the super-blocks of a work item): this thread owns the blocks
+		// [grp * hb, grp * hb + hb) of its row and keeps their headers as the super-blocks pass by
+		const int hb = (nb + 1) >> 1;
+		uint4 mh[4];
 		for (int t = blockIdx.x; t < total && alive; t += stride_t) {
 			for (int sbi = 0; sbi < nb && alive; sbi++) {
 				const long long tw = TCT_NOW();
@@ -397,48 +453,108 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 					break;
 				}
 				TCT_ADD(0, tw);
+				if (warp == 0)
+					TCT_TRACE(6, g);
 				Expander<KIND> ex;
 				ex.prepare(w_buf(wb), row);
-				if (KIND == W_Q4K && hs == 0)
+				if (Q4 && grp == 0)
 					ds[(g & (TC_NDS - 1)) * TC_BM + row] = ex.factors;
+				if (Q4) {
 #pragma unroll
-				for (int p = 0; p < TC_SPB; p++) {
-					const long long te = TCT_NOW();
-					if (it >= (uint32_t)TC_S) {
-						if (!tc_wait_warp(ptx::smem_u32(&sh->empty[s]), ph ^ 1u, abort_flag, status, lane)) {
-							alive = false;
-							break;
-						}
-						ptx::tc_fence_after();
-					}
-					TCT_ADD(1, te);
-					const long long tm = TCT_NOW();
-					// first stage of a super-block: the A tile of its M step (rows are owned by the hs = 0 warps)
-					if (KIND == W_Q4K && p == 0 && hs == 0)
-						ex.emit_mins(sbi, lane_base + TC_COL_AM + 8u * (g & 1u));
-					ex.emit(p, hs, lane_base + TC_COL_A + 32u * s);
-					ptx::tmem_st_wait();
-					TCT_ADD(2, tm);
-					ptx::tc_fence_before();
-					__syncwarp();
-					if (lane == 0)
-						ptx::mbar_arrive(ptx::smem_u32(&sh->full[s]));
-					it++;
-					if (++s == TC_S) {
-						s = 0;
-						ph ^= 1u;
-					}
+					for (int i = 0; i < 4; i++)
+						if (sbi == grp * hb + i)
+							mh[i] = ex.header();
 				}
-				if (!alive)
+				// this group's two stages of the super-block
+				int sa, sb2;
+				uint32_t pha, phb;
+				slot_of(2 * grp, sa, pha);
+				slot_of(2 * grp + 1, sb2, phb);
+				const long long te = TCT_NOW();
+				bool ok = true;
+				if (it + 2 * grp >= (uint32_t)TC_S)
+					ok = tc_wait_warp(ptx::smem_u32(&sh->empty[sa]), pha ^ 1u, abort_flag, status, lane);
+				if (ok && it + 2 * grp + 1 >= (uint32_t)TC_S)
+					ok = tc_wait_warp(ptx::smem_u32(&sh->empty[sb2]), phb ^ 1u, abort_flag, status, lane);
+				if (!ok) {
+					alive = false;
 					break;
-				// the packed super-block is expanded: hand the buffer back to the weight loader
+				}
+				ptx::tc_fence_after();
+				TCT_ADD(1, te);
+				if ((warp & 3) == 0) {
+					TCT_TRACE(0, it + 2 * grp);
+					TCT_TRACE(0, it + 2 * grp + 1);
+				}
+				const long long tm = TCT_NOW();
+				ex.emit(2 * grp, 0, lane_base + TC_COL_A + 32u * sa);
+				ex.emit(2 * grp, 1, lane_base + TC_COL_A + 32u * sa);
+				ex.emit(2 * grp + 1, 0, lane_base + TC_COL_A + 32u * sb2);
+				ex.emit(2 * grp + 1, 1, lane_base + TC_COL_A + 32u * sb2);
+				ptx::tmem_st_wait();
+				TCT_ADD(2, tm);
+				ptx::tc_fence_before();
 				__syncwarp();
-				if (lane == 0)
+				if (lane == 0) {
+					ptx::mbar_arrive(ptx::smem_u32(&sh->full[sa]));
+					ptx::mbar_arrive(ptx::smem_u32(&sh->full[sb2]));
+					// the packed super-block is expanded by this warp: hand the buffer back to the weight loader
 					ptx::mbar_arrive(ptx::smem_u32(&sh->wempty[wb]));
-				if (++wb == TC_NWB) {
+				}
+				if ((warp & 3) == 0) {
+					TCT_TRACE(1, it + 2 * grp);
+					TCT_TRACE(1, it + 2 * grp + 1);
+				}
+				it += TC_SPB;
+				slot_of(TC_SPB, s, ph);
+				if (++wb == Sm::NWB) {
 					wb = 0;
 					wph ^= 1u;
 				}
+				g++;
+			}
+			if (Q4 && alive) {
+				// ---- min phase: two ring stages, the hi and the lo tile of dmin * m ----
+				int s0, s1;
+				uint32_t ph0, ph1;
+				slot_of(0, s0, ph0);
+				slot_of(1, s1, ph1);
+				bool ok = true;
+				if (it >= (uint32_t)TC_S)
+					ok = tc_wait_warp(ptx::smem_u32(&sh->empty[s0]), ph0 ^ 1u, abort_flag, status, lane);
+				if (ok && it + 1 >= (uint32_t)TC_S)
+					ok = tc_wait_warp(ptx::smem_u32(&sh->empty[s1]), ph1 ^ 1u, abort_flag, status, lane);
+				if (!ok) {
+					alive = false;
+					break;
+				}
+				ptx::tc_fence_after();
+				const uint32_t tile_hi = lane_base + TC_COL_A + 32u * s0, tile_lo = lane_base + TC_COL_A + 32u * s1;
+#pragma unroll
+				for (int i = 0; i < 4; i++) {
+					const int B = grp * hb + i;
+					if (i < hb && B < nb)
+						Expander<W_Q4K>::emit_min_block(mh[i], B, tile_hi, tile_lo);
+				}
+				if ((nb & 1) && grp == 1) {  // pad the last 16-deep k step with zeros
+					ptx::tmem_st4(tile_hi + 4u * nb, 0u, 0u, 0u, 0u);
+					ptx::tmem_st4(tile_lo + 4u * nb, 0u, 0u, 0u, 0u);
+				}
+				ptx::tmem_st_wait();
+				ptx::tc_fence_before();
+				// both tiles are written by all eight warps: meet (bounded wait), then group j reports tile j
+				__syncwarp();
+				if (lane == 0)
+					ptx::mbar_arrive(ptx::smem_u32(&sh->msync));
+				if (!tc_wait_warp(ptx::smem_u32(&sh->msync), mph, abort_flag, status, lane)) {
+					alive = false;
+					break;
+				}
+				mph ^= 1u;
+				if (lane == 0)
+					ptx::mbar_arrive(ptx::smem_u32(&sh->full[grp ? s1 : s0]));
+				it += 2;
+				slot_of(2, s, ph);
 				g++;
 			}
 		}
@@ -454,7 +570,7 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 		if (threadIdx.x == 0)
 			TCT_FLUSH(0, 5);
 	} else if (warp < W_MMA0) {
-		// ================= drain warps: super-block partial sums -> fp32 rows =================
+		// ================= drain warps: partial sums of a phase -> fp32 rows =================
 		const int dw = warp - TC_PWARPS, quad = warp & 3, chalf = dw >> 2;
 		const int lrow = quad * 32 + lane;
 		const uint32_t tlane = tmem + ((uint32_t)(quad * 32) << 16);
@@ -462,8 +578,9 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 		bool alive = true;
 		TCT_DECL(4);
 		const long long tct_start = TCT_NOW();
-		for (int t = blockIdx.x; t < total && alive; t += stride_t) {
-			const TcItem item = tc_item(t, m_tiles, tile_info, rows_per_matrix);
+		int dtl = 0;
+		for (int t = blockIdx.x; t < total && alive; t += stride_t, dtl++) {
+			const TcItem item = tc_item(t, dtl, s_items, m_tiles, tile_info, rows_per_matrix);
 			const int mrow = item.m0 + lrow;
 			// Tokens of this warp: half of the tile's token range, in chunks of 16 accumulator columns.
 			// A tile of up to 32 tokens has its hi and lo products side by side in one accumulator
@@ -478,50 +595,46 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 			// Q6_K: d of (row, super-block) straight from global memory, one super-block ahead
 			const uint8_t *grp = nullptr;
 			float dnext = 0.0f;
-			if (KIND == W_Q6K_R8) {
+			if (!Q4) {
 				grp = (item.mat_sel ? w1 : w0) + (size_t)item.le * expert_stride + (size_t)(mrow >> 3) * q6k_r8_group_bytes(nb);
 				dnext = half_bits_to_float(__ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb, mrow & 7, 0))));
 			}
-			for (int sbi = 0; sbi < nb; sbi++) {
-				float2 f = make_float2(dnext, 0.0f);
-				if (KIND == W_Q6K_R8 && sbi + 1 < nb)
+			// the phase after the last super-block is the min phase (Q4_K): its sums enter with factor -1
+			for (int sbi = 0; sbi < (Q4 ? nb + 1 : nb); sbi++) {
+				float scale = Q4 ? -1.0f : dnext;
+				if (!Q4 && sbi + 1 < nb)
 					dnext = half_bits_to_float(
 						__ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb, mrow & 7, sbi + 1))));
-				const uint32_t buf = g & 1u;
+				const uint32_t buf = g & (TC_NBUF - 1);
 				const long long tw = TCT_NOW();
-				if (!tc_wait_warp(ptx::smem_u32(&sh->pfull[buf]), (g >> 1) & 1u, abort_flag, status, lane)) {
+				if (!tc_wait_warp(ptx::smem_u32(&sh->pfull[buf]), (g / TC_NBUF) & 1u, abort_flag, status, lane)) {
 					alive = false;
 					break;
 				}
 				TCT_ADD(0, tw);
+				if (warp == TC_PWARPS)
+					TCT_TRACE(4, g);
 				const long long tl = TCT_NOW();
 				ptx::tc_fence_after();
-				if (KIND == W_Q4K)
-					f = ds[(g & (TC_NDS - 1)) * TC_BM + lrow];
+				if (Q4 && sbi < nb)
+					scale = ds[(g & (TC_NDS - 1)) * TC_BM + lrow].x;
+				const bool two = tok0 + 16 < item.n_mma && ntok == 32;	// second chunk of 16 columns in use
+				if (tok0 < item.n_mma) {				// warp-uniform
+					uint32_t p[16], p2[16];
+					ptx::tmem_ld16(tlane + TC_COL_P + 64u * buf + tok0, p);
+					if (concat)
+						ptx::tmem_ld16(tlane + TC_COL_P + 64u * buf + item.n_box + tok0, p2);
+					else if (two)
+						ptx::tmem_ld16(tlane + TC_COL_P + 64u * buf + tok0 + 16, p2);
+					ptx::tmem_ld_wait();
 #pragma unroll
-				for (int hf = 0; hf < 2; hf++) {
-					const int col = tok0 + 16 * hf;
-					if (16 * hf < ntok && col < item.n_mma) {  // warp-uniform
-						uint32_t p[16], p2[16];
-						ptx::tmem_ld16(tlane + TC_COL_P + 64u * buf + col, p);
-						if (concat)
-							ptx::tmem_ld16(tlane + TC_COL_P + 64u * buf + item.n_box + col, p2);
-						ptx::tmem_ld_wait();
-#pragma unroll
-						for (int j = 0; j < 16; j++) {
-							const float v = concat ? __uint_as_float(p[j]) + __uint_as_float(p2[j]) : __uint_as_float(p[j]);
-							acc[16 * hf + j] = __fmaf_rn(f.x, v, acc[16 * hf + j]);
-						}
-						if (KIND == W_Q4K) {
-							ptx::tmem_ld16(tlane + TC_COL_M + 64u * buf + col, p);
-							if (concat)
-								ptx::tmem_ld16(tlane + TC_COL_M + 64u * buf + item.n_box + col, p2);
-							ptx::tmem_ld_wait();
-#pragma unroll
-							for (int j = 0; j < 16; j++) {
-								const float v = concat ? __uint_as_float(p[j]) + __uint_as_float(p2[j]) : __uint_as_float(p[j]);
-								acc[16 * hf + j] = __fmaf_rn(-f.y, v, acc[16 * hf + j]);
-							}
+					for (int j = 0; j < 16; j++) {
+						if (concat) {
+							acc[j] = __fmaf_rn(scale, __uint_as_float(p[j]) + __uint_as_float(p2[j]), acc[j]);
+						} else {
+							acc[j] = __fmaf_rn(scale, __uint_as_float(p[j]), acc[j]);
+							if (two)
+								acc[16 + j] = __fmaf_rn(scale, __uint_as_float(p2[j]), acc[16 + j]);
 						}
 					}
 				}
@@ -530,6 +643,8 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 				if (lane == 0)
 					ptx::mbar_arrive(ptx::smem_u32(&sh->pempty[buf]));
 				TCT_ADD(1, tl);
+				if (warp == TC_PWARPS)
+					TCT_TRACE(5, g);
 				g++;
 			}
 			if (!alive)
@@ -557,39 +672,46 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 			TCT_FLUSH(8, 4);
 	} else if (warp < W_TOK) {
 		// ================= MMA issuers =================
-		// Warp w owns accumulator buffer w and the super-blocks that use it; MMAs of the two issuers
-		// run concurrently on different buffers.  The whole warp walks the loop (warp-uniform
+		// Issuer w owns the phases with g % 2 == w (accumulator buffers w and w + 2); MMAs of the two
+		// issuers run concurrently on different buffers.  The whole warp walks the loop (warp-uniform
 		// addresses and descriptors); lane 0 issues.
 		const uint32_t mw = warp - W_MMA0;
 		const uint32_t leader = (lane == 0) ? 1u : 0u;
 		int s = 0;
-		uint32_t ph = 0, g = 0, tl = 0;
+		uint32_t ph = 0, g = 0, tl = 0, gst = 0;
 		bool alive = true;
-		TCT_DECL(5);
+		TCT_DECL(8);
 		const long long tct_start = TCT_NOW();
+		auto advance = [&](int n) {
+			gst += n;
+			s += n;
+			if (s >= TC_S) {
+				s -= TC_S;
+				ph ^= 1u;
+			}
+		};
 		for (int t = blockIdx.x; t < total && alive; t += stride_t, tl++) {
-			const TcItem item = tc_item(t, m_tiles, tile_info, rows_per_matrix);
+			const long long tth = TCT_NOW();
+			const TcItem item = tc_item(t, (int)tl, s_items, m_tiles, tile_info, rows_per_matrix);
 			// up to 32 tokens: hi and lo rows are one N = 2 n_box operand (one MMA per k step);
 			// more: two MMAs of N = n_mma on the hi rows and on the lo rows behind them
 			const bool concat = item.n_box <= 32;
 			const uint32_t idesc = ptx::umma_idesc_f16(TC_BM, concat ? 2 * item.n_box : item.n_mma);
+			const uint32_t idesc_hi = ptx::umma_idesc_f16(TC_BM, concat ? item.n_box : item.n_mma);  // hi rows only
 			const uint32_t lo_off = (uint32_t)item.n_box * 128u;
-			bool need_x = KIND == W_Q4K;  // this issuer has not yet seen the work item's sub-block sums
-			bool hold_x = KIND == W_Q4K;  // ... and has not yet released them
-			for (int sbi = 0; sbi < nb && alive; sbi++) {
-				const uint32_t buf = g & 1u;
-				if (buf != mw) {  // the other issuer's super-block: skip its stages
-					s += TC_SPB;
-					if (s >= TC_S) {
-						s -= TC_S;
-						ph ^= 1u;
-					}
+			TCT_ADD(6, tth + (long long)(lo_off & 0u));
+			for (int sbi = 0; sbi < (Q4 ? nb + 1 : nb) && alive; sbi++) {
+				const uint32_t buf = g & (TC_NBUF - 1);
+				const bool min_phase = Q4 && sbi == nb;
+				const int n_st = min_phase ? 2 : TC_SPB;
+				if ((g & 1u) != mw) {  // the other issuer's phase: skip its stages
+					advance(n_st);
 					g++;
 					continue;
 				}
 				const long long tpe = TCT_NOW();
-				if (g >= 2u) {
-					const bool ok = tc_wait(ptx::smem_u32(&sh->pempty[buf]), ((g >> 1) & 1u) ^ 1u, abort_flag, status);
+				if (g >= (uint32_t)TC_NBUF) {
+					const bool ok = tc_wait(ptx::smem_u32(&sh->pempty[buf]), ((g / TC_NBUF) & 1u) ^ 1u, abort_flag, status);
 					if (!__all_sync(0xffffffffu, ok)) {
 						alive = false;
 						break;
@@ -597,35 +719,58 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 				}
 				TCT_ADD(0, tpe);
 				const uint32_t dP = tmem + TC_COL_P + 64u * buf;
+				if (min_phase) {
+					// ---- min phase: D = A_hi.[X_hi | X_lo] + A_lo.X_hi over the sub-block sums ----
+					const long long tmp0 = TCT_NOW();
+					const int s0 = s;
+					const uint32_t ph0 = ph;
+					advance(1);
+					const int s1 = s;
+					const uint32_t ph1 = ph;
+					advance(1);
+					bool ok = tc_wait(ptx::smem_u32(&sh->full[s0]), ph0, abort_flag, status);
+					ok = ok && tc_wait(ptx::smem_u32(&sh->full[s1]), ph1, abort_flag, status);
+					ok = ok && tc_wait(ptx::smem_u32(&sh->xfull), tl & 1u, abort_flag, status);
+					if (!__all_sync(0xffffffffu, ok)) {
+						alive = false;
+						break;
+					}
+					ptx::tc_fence_after();
+					TCT_ADD(5, tmp0);
+					TCT_TRACE(2, gst - 2);
+					TCT_TRACE(2, gst - 1);
+					const uint64_t xh = ptx::umma_desc_sw128(xq_hi), xl = ptx::umma_desc_sw128(xq_hi + lo_off);
+					const uint32_t ah = tmem + TC_COL_A + 32u * s0, al = tmem + TC_COL_A + 32u * s1;
+					for (int kk = 0; kk < min_k16; kk++) {
+						ptx::mma_f16_ts_if(dP, ah + 8 * kk, xh + 2 * kk, idesc, kk > 0 ? 1u : 0u, leader);
+						if (!concat)
+							ptx::mma_f16_ts_if(dP, ah + 8 * kk, xl + 2 * kk, idesc, 1u, leader);
+						ptx::mma_f16_ts_if(dP, al + 8 * kk, xh + 2 * kk, idesc_hi, 1u, leader);
+					}
+					ptx::mma_commit_if(ptx::smem_u32(&sh->empty[s0]), leader);
+					ptx::mma_commit_if(ptx::smem_u32(&sh->empty[s1]), leader);
+					ptx::mma_commit_if(ptx::smem_u32(&sh->xempty), leader);
+					ptx::mma_commit_if(ptx::smem_u32(&sh->pfull[buf]), leader);
+					TCT_TRACE(3, gst - 2);
+					TCT_TRACE(3, gst - 1);
+					TCT_ADD(7, tmp0);
+					g++;
+					continue;
+				}
 				for (int q4 = 0; q4 < TC_SPB; q4++) {
 					const long long tb = TCT_NOW();
 					bool ok = tc_wait(ptx::smem_u32(&sh->bfull[s]), ph, abort_flag, status);
 					TCT_ADD(1, tb);
 					const long long tf = TCT_NOW();
 					ok = ok && tc_wait(ptx::smem_u32(&sh->full[s]), ph, abort_flag, status);
-					if (need_x) {
-						ok = ok && tc_wait(ptx::smem_u32(&sh->xfull), tl & 1u, abort_flag, status);
-						need_x = false;
-					}
 					if (!__all_sync(0xffffffffu, ok)) {
 						alive = false;
 						break;
 					}
 					TCT_ADD(2, tf);
+					TCT_TRACE(2, gst);
 					const long long ti = TCT_NOW();
 					ptx::tc_fence_after();
-					if (KIND == W_Q4K && q4 == 0) {
-						// M step: mins (16-deep A tile) x sub-block sums of this super-block pair
-						const int j = sbi >> 1;
-						const uint32_t dM = tmem + TC_COL_M + 64u * buf, am = tmem + TC_COL_AM + 8u * buf;
-						ptx::mma_f16_ts_if(dM, am, ptx::umma_desc_sw128(xq_hi) + 2 * j, idesc, 0u, leader);
-						if (!concat)
-							ptx::mma_f16_ts_if(dM, am, ptx::umma_desc_sw128(xq_hi + lo_off) + 2 * j, idesc, 1u, leader);
-						if (sbi + TC_MWARPS >= nb) {  // this issuer's last M step of the work item
-							ptx::mma_commit_if(ptx::smem_u32(&sh->xempty), leader);
-							hold_x = false;
-						}
-					}
 					const uint64_t bh = ptx::umma_desc_sw128(b_hi(s)), bl = ptx::umma_desc_sw128(b_hi(s) + lo_off);
 					const uint32_t a = tmem + TC_COL_A + 32u * s;
 #pragma unroll
@@ -636,22 +781,18 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 					}
 					ptx::mma_commit_if(ptx::smem_u32(&sh->empty[s]), leader);
 					TCT_ADD(3, ti);
-					if (++s == TC_S) {
-						s = 0;
-						ph ^= 1u;
-					}
+					TCT_TRACE(3, gst);
+					advance(1);
 				}
 				if (!alive)
 					break;
 				ptx::mma_commit_if(ptx::smem_u32(&sh->pfull[buf]), leader);
 				g++;
 			}
-			if (hold_x && alive)  // no super-block of this work item was this issuer's
-				ptx::mma_commit_if(ptx::smem_u32(&sh->xempty), leader);
 		}
 		TCT_ADD(4, tct_start);
 		if (lane == 0 && mw == 0)
-			TCT_FLUSH(16, 5);
+			TCT_FLUSH(16, 8);
 	} else if (warp == W_TOK) {
 		// ================= token loader: token operand and sub-block sums (TMA) =================
 		if (lane == 0) {
@@ -661,17 +802,22 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 			TCT_DECL(3);
 			const long long tct_start = TCT_NOW();
 			for (int t = blockIdx.x; t < total && alive; t += stride_t, tl++) {
-				const TcItem item = tc_item(t, m_tiles, tile_info, rows_per_matrix);
+				const TcItem item = tc_item(t, (int)tl, s_items, m_tiles, tile_info, rows_per_matrix);
 				const uint32_t box_bytes = 2u * (uint32_t)item.n_box * 128u;  // hi + lo rows of one 64-k box
 				const CUtensorMap *tmp = item.n_box == 16 ? &tm16 : (item.n_box == 32 ? &tm32 : &tm64);
-				if (KIND == W_Q4K) {
-					if (tl >= 1u && !tc_wait(ptx::smem_u32(&sh->xempty), (tl & 1u) ^ 1u, abort_flag, status))
-						break;
-					const uint32_t xb = ptx::smem_u32(&sh->xfull);
-					ptx::mbar_arrive_expect_tx(xb, box_bytes);
-					ptx::tma_load_3d(xq_hi, item.n_box == 16 ? &tq16 : (item.n_box == 32 ? &tq32 : &tq64), xb, 0, item.row0, 0);
-				}
-				for (int ki = 0; ki < k_iters; ki++) {
+				// the two stages of the min phase (after the super-blocks) carry no token tiles: they only
+				// keep the barrier phases in step; the sub-block sums they need are fetched once the first
+				// super-block's tiles are on their way (the previous work item's min phase is long over then)
+				for (int ki = 0; ki < k_iters + (Q4 ? 2 : 0); ki++) {
+					if (Q4 && ki == (k_iters > TC_SPB ? TC_SPB : 0)) {
+						if (tl >= 1u && !tc_wait(ptx::smem_u32(&sh->xempty), (tl & 1u) ^ 1u, abort_flag, status)) {
+							alive = false;
+							break;
+						}
+						const uint32_t xb = ptx::smem_u32(&sh->xfull);
+						ptx::mbar_arrive_expect_tx(xb, box_bytes);
+						ptx::tma_load_3d(xq_hi, item.n_box == 16 ? &tq16 : (item.n_box == 32 ? &tq32 : &tq64), xb, 0, item.row0, 0);
+					}
 					const long long tw = TCT_NOW();
 					if (it >= (uint32_t)TC_S && !tc_wait(ptx::smem_u32(&sh->empty[s]), ph ^ 1u, abort_flag, status)) {
 						alive = false;
@@ -680,9 +826,13 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 					TCT_ADD(0, tw);
 					const long long ti = TCT_NOW();
 					const uint32_t fb = ptx::smem_u32(&sh->bfull[s]);
-					// one box: 64 k x n_box rows x (hi, lo); a thread can issue a TMA only every ~100 cycles
-					ptx::mbar_arrive_expect_tx(fb, box_bytes);
-					ptx::tma_load_3d(b_hi(s), tmp, fb, ki * TC_BK, item.row0, 0);
+					if (ki >= k_iters) {
+						ptx::mbar_arrive(fb);
+					} else {
+						// one box: 64 k x n_box rows x (hi, lo); a thread can issue a TMA only every ~100 cycles
+						ptx::mbar_arrive_expect_tx(fb, box_bytes);
+						ptx::tma_load_3d(b_hi(s), tmp, fb, ki * TC_BK, item.row0, 0);
+					}
 					TCT_ADD(1, ti);
 					it++;
 					if (++s == TC_S) {
@@ -699,28 +849,26 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 		int wb = 0;
 		uint32_t wph = 0, wc = 0;
 		bool alive = true;
-		for (int t = blockIdx.x; t < total && alive; t += stride_t) {
-			const TcItem item = tc_item(t, m_tiles, tile_info, rows_per_matrix);
+		int wtl = 0;
+		for (int t = blockIdx.x; t < total && alive; t += stride_t, wtl++) {
+			const TcItem item = tc_item(t, wtl, s_items, m_tiles, tile_info, rows_per_matrix);
 			for (int sbi = 0; sbi < nb; sbi++) {
-				if (wc >= (uint32_t)TC_NWB && !tc_wait_warp(ptx::smem_u32(&sh->wempty[wb]), wph ^ 1u, abort_flag, status, lane)) {
+				if (wc >= (uint32_t)Sm::NWB && !tc_wait_warp(ptx::smem_u32(&sh->wempty[wb]), wph ^ 1u, abort_flag, status, lane)) {
 					alive = false;
 					break;
 				}
 				const uint32_t bar = ptx::smem_u32(&sh->wfull[wb]);
-				if (KIND == W_Q4K) {
-					if (lane == 0) {
-						ptx::mbar_arrive_expect_tx(bar, TC_BM * Q4K_BYTES);
+				if (lane == 0) {
+					ptx::mbar_arrive_expect_tx(bar, Sm::WBUF);
+					if (Q4)	 // box = (one block, 128 rows)
 						ptx::tma_load_2d(w_buf(wb), item.mat_sel ? &tw1 : &tw0, bar, sbi * Q4K_BYTES,
 								 item.le * rows_per_matrix + item.m0);
-					}
-				} else if (lane == 0) {
-					// box = (one record, 8 rows of a group, 16 groups)
-					ptx::mbar_arrive_expect_tx(bar, TC_BM * TC_Q6_ROW);
-					ptx::tma_load_3d(w_buf(wb), item.mat_sel ? &tw1 : &tw0, bar, sbi * TC_Q6_ROW, 0,
-							 (item.le * rows_per_matrix + item.m0) >> 3);
+					else  // box = (one record, 8 rows of a group, 16 groups)
+						ptx::tma_load_3d(w_buf(wb), item.mat_sel ? &tw1 : &tw0, bar, sbi * TC_Q6_ROW, 0,
+								 (item.le * rows_per_matrix + item.m0) >> 3);
 				}
 				wc++;
-				if (++wb == TC_NWB) {
+				if (++wb == Sm::NWB) {
 					wb = 0;
 					wph ^= 1u;
 				}
@@ -849,7 +997,7 @@ int tc_setup(tie_cuda_ctx *c)
 				return rc;
 		}
 #define TC_ATTR(KIND, RAW) \
-	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_sb<KIND, RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM))
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_sb<KIND, RAW>, cudaFuncAttributeMaxDynamicSharedMemorySize, TcSmem<KIND>::SMEM))
 	TC_ATTR(W_Q4K, false);
 	TC_ATTR(W_Q4K, true);
 	TC_ATTR(W_Q6K_R8, false);
@@ -867,7 +1015,7 @@ static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1
 	const int m_tiles = (RAW ? 2 : 1) * t0.rows / TC_BM;
 	const CUtensorMap &w0m = t0.map;
 	const CUtensorMap &w1m = t1 ? t1->map : t0.map;
-	grouped_gemm_sb<KIND, RAW><<<c->sm_count, TC_THREADS, TC_SMEM, c->stream>>>(
+	grouped_gemm_sb<KIND, RAW><<<c->sm_count, TC_THREADS, TcSmem<KIND>::SMEM, c->stream>>>(
 		c->tmap[arr * 3], c->tmap[arr * 3 + 1], c->tmap[arr * 3 + 2], c->tmap[(2 + arr) * 3], c->tmap[(2 + arr) * 3 + 1],
 		c->tmap[(2 + arr) * 3 + 2], w0m, w1m, t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride,
 		t0.k, s.tile_info, s.tile_start, c->n_local, m_tiles, y, s.perm, RAW ? 2 * t0.rows : t0.rows, out_scale, s.status, t0.rows);
@@ -922,5 +1070,11 @@ extern "C" int tie_debug_tc_cycles(unsigned long long *out)
 	if (cudaMemcpyFromSymbol(out, tie::g_tc_cycles, sizeof(zero)) != cudaSuccess)
 		return -1;
 	return cudaMemcpyToSymbol(tie::g_tc_cycles, zero, sizeof(zero)) == cudaSuccess ? 0 : -1;
+}
+extern "C" int tie_debug_tc_trace(long long *out)
+{
+	if (cudaDeviceSynchronize() != cudaSuccess)
+		return -1;
+	return cudaMemcpyFromSymbol(out, tie::g_tc_trace, sizeof(long long) * 8 * 256) == cudaSuccess ? 0 : -1;
 }
 #endif
