@@ -314,7 +314,7 @@ def main():
     dom_flops = T * shape.top_k * (2 * 2 * shape.ffn_dim * shape.hidden if dom == "gate_up" else 2 * shape.ffn_dim * shape.hidden)
     achieved = dom_bytes / (phase[dom] * 1e-3) / 1e9
     roofline = {
-        "kernel": ("grouped_gemm_tc" if used_tc else "stream_rows") + f" ({dom})", "bound": "hbm", "achieved": achieved,
+        "kernel": ("grouped_gemm_sb" if used_tc else "stream_rows") + f" ({dom})", "bound": "hbm", "achieved": achieved,
         "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"], "traffic": None,
         "peak_source": peaks["source"], "algorithmic_bytes_per_launch": dom_bytes, "avg_launch_ms": phase[dom],
         "algorithmic_tflops": dom_flops / (phase[dom] * 1e-3) / 1e12,
@@ -324,13 +324,9 @@ def main():
                   "hbm_frac": workloads.algorithmic_bytes(shape, T, active) / (ms_per_step * 1e-3) / 1e9 / peaks["hbm_gbs"],
                   "algorithmic_tflops": workloads.algorithmic_flops(shape, T) / (ms_per_step * 1e-3) / 1e12},
     }
-    prof_path = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(prof_path):
-        try:
-            tr = json.load(open(prof_path))
-            roofline["traffic"] = tr.get(dom + ("_tc" if used_tc else "_stream"), {}).get("dram_bytes_per_launch")
-        except Exception:
-            pass
+    # DRAM bytes per launch of that kernel from its ncu capture (only captured for this workload)
+    if T == 512 and shape == synth.MoeShape():
+        roofline["traffic"] = workloads.NCU_DRAM_BYTES_PER_LAUNCH.get(dom + ("_tc" if used_tc else "_stream"))
 
     # ---- side runs: decode, 64 tokens, 4096 tokens ----
     extra = {}

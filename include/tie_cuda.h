@@ -206,11 +206,12 @@ uint64_t tie_cuda_launch_count(const tie_cuda_ctx *c);
  * call (read back from the device; synchronises). */
 int tie_cuda_last_active_experts(tie_cuda_ctx *c);
 /* Per-phase device times of a call, from CUDA events on the context's stream (off by default).
- * phase_ms[TIE_CUDA_N_PHASES]: router, dispatch sort, input split, gate/up product (+SwiGLU),
- * down product, combine — of the most recent tie_cuda_moe_ffn* / _block_inplace call.
+ * phase_ms[TIE_CUDA_N_PHASES]: router, dispatch sort, input split, gate/up product, SwiGLU pass
+ * (zero where the gate/up kernel applies it itself), down product, combine — of the most recent
+ * tie_cuda_moe_ffn* / _block_inplace call.
  * tie_cuda_get_profile synchronises; returns 1 if that call used the tensor-core kernels, 0 if
  * the streaming kernels, negative on error. */
-#define TIE_CUDA_N_PHASES 6
+#define TIE_CUDA_N_PHASES 7
 int tie_cuda_set_profiling(tie_cuda_ctx *c, int on);
 int tie_cuda_get_profile(tie_cuda_ctx *c, float *phase_ms);
 const char *tie_cuda_version(void);

@@ -187,7 +187,7 @@ int check_status(tie_cuda_ctx *c)
 }
 
 // Phase marks: 0 start, 1 router done, 2 dispatch sort done, 3 input split done, 4 gate/up done,
-// 5 down done, 6 combine done.
+// 5 SwiGLU pass done (only where it is a pass of its own), 6 down done, 7 combine done.
 void prof_mark(tie_cuda_ctx *c, int id)
 {
 	if (!c->prof_on)
@@ -230,14 +230,16 @@ int run_experts(tie_cuda_ctx *c, const Layer &L, const float *x_src, int src_div
 		prof_mark(c, 3);
 		TRY(launch_tc_gate_up(c, L, n_rows));
 		prof_mark(c, 4);
-		TRY(launch_tc_down(c, L, n_rows, y));
+		TRY(launch_tc_swiglu(c, L, n_rows));
 		prof_mark(c, 5);
+		TRY(launch_tc_down(c, L, n_rows, y));
+		prof_mark(c, 6);
 	} else {
 		prof_mark(c, 3);
 		TRY(launch_stream_gate_up(c, L, x_src, src_div, row_expert, n_rows, direct));
 		prof_mark(c, 4);
 		TRY(launch_stream_down(c, L, y, row_expert, n_rows, direct));
-		prof_mark(c, 5);
+		prof_mark(c, 6);
 	}
 	return TIE_CUDA_OK;
 }
@@ -267,15 +269,15 @@ int moe_ffn_device(tie_cuda_ctx *c, Layer &L, const float *x, float *out, int n_
 		TRY(launch_decode_gate_up(c, L, x, n_tokens));
 		prof_mark(c, 4);
 		TRY(launch_decode_down_combine(c, L, n_tokens, residual, out));
-		prof_mark(c, 5);
 		prof_mark(c, 6);
+		prof_mark(c, 7);
 		return TIE_CUDA_OK;
 	}
 	TRY(launch_router(c, x, L.router_w, bias_dev, n_tokens, s.logits, s.topk_idx, s.topk_w));
 	prof_mark(c, 1);
 	TRY(run_experts(c, L, x, c->cfg.top_k, s.topk_idx, n_tokens * c->cfg.top_k, s.y, flags));
 	TRY(launch_combine(c, s.y, s.topk_w, n_tokens, residual, out));
-	prof_mark(c, 6);
+	prof_mark(c, 7);
 	return TIE_CUDA_OK;
 }
 

@@ -44,6 +44,7 @@ int tc_setup(tie_cuda_ctx *c);
 int tc_make_weight_map(tie_cuda_ctx *c, DevTensor &t);
 bool tc_supported(const tie_cuda_ctx *c, const Layer &L);
 int launch_tc_gate_up(tie_cuda_ctx *c, const Layer &L, int n_rows);
+int launch_tc_swiglu(tie_cuda_ctx *c, const Layer &L, int n_rows);
 int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, float *y);
 // repack.cu
 int launch_repack_q6k_r8(tie_cuda_ctx *c, const uint8_t *raw, uint8_t *dst, size_t n_rows_total, int nb);

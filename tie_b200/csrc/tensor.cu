@@ -131,6 +131,8 @@ __device__ long long g_tc_trace[8][256];
 // another role / CTA has already reported a timeout.  After a first miss the thread lets the
 // hardware suspend it between polls, so that waiting roles do not take issue slots from the
 // producers.
+// BACKOFF_NS > 0: roles that can afford a few hundred cycles of extra latency also sleep between polls.
+template <int BACKOFF_NS = 0>
 __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, unsigned *status)
 {
 	if (ptx::mbar_try_wait(bar, parity))
@@ -138,6 +140,8 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
 	const long long t0 = clock64();
 	uint32_t spins = 0;
 	while (!ptx::mbar_try_wait_suspend(bar, parity, 20000u)) {
+		if (BACKOFF_NS > 0)
+			__nanosleep(BACKOFF_NS);
 		if (*abort_flag)
 			return false;
 		if (clock64() - t0 > TC_WAIT_CYCLES || ((++spins & 255u) == 0 && (*(volatile unsigned *)status & ST_WAIT_TIMEOUT))) {
@@ -150,11 +154,12 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
 }
 
 // One lane polls for its warp; the verdict is shared.
+template <int BACKOFF_NS = 0>
 __device__ __forceinline__ bool tc_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, unsigned *status, int lane)
 {
 	int ok = 1;
 	if (lane == 0)
-		ok = tc_wait(bar, parity, abort_flag, status) ? 1 : 0;
+		ok = tc_wait<BACKOFF_NS>(bar, parity, abort_flag, status) ? 1 : 0;
 	return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
@@ -607,7 +612,7 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 						__ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb, mrow & 7, sbi + 1))));
 				const uint32_t buf = g & (TC_NBUF - 1);
 				const long long tw = TCT_NOW();
-				if (!tc_wait_warp(ptx::smem_u32(&sh->pfull[buf]), (g / TC_NBUF) & 1u, abort_flag, status, lane)) {
+				if (!tc_wait_warp<100>(ptx::smem_u32(&sh->pfull[buf]), (g / TC_NBUF) & 1u, abort_flag, status, lane)) {
 					alive = false;
 					break;
 				}
@@ -819,7 +824,7 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 						ptx::tma_load_3d(xq_hi, item.n_box == 16 ? &tq16 : (item.n_box == 32 ? &tq32 : &tq64), xb, 0, item.row0, 0);
 					}
 					const long long tw = TCT_NOW();
-					if (it >= (uint32_t)TC_S && !tc_wait(ptx::smem_u32(&sh->empty[s]), ph ^ 1u, abort_flag, status)) {
+					if (it >= (uint32_t)TC_S && !tc_wait<100>(ptx::smem_u32(&sh->empty[s]), ph ^ 1u, abort_flag, status)) {
 						alive = false;
 						break;
 					}
@@ -853,7 +858,7 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 		for (int t = blockIdx.x; t < total && alive; t += stride_t, wtl++) {
 			const TcItem item = tc_item(t, wtl, s_items, m_tiles, tile_info, rows_per_matrix);
 			for (int sbi = 0; sbi < nb; sbi++) {
-				if (wc >= (uint32_t)Sm::NWB && !tc_wait_warp(ptx::smem_u32(&sh->wempty[wb]), wph ^ 1u, abort_flag, status, lane)) {
+				if (wc >= (uint32_t)Sm::NWB && !tc_wait_warp<100>(ptx::smem_u32(&sh->wempty[wb]), wph ^ 1u, abort_flag, status, lane)) {
 					alive = false;
 					break;
 				}
@@ -1035,15 +1040,19 @@ bool tc_supported(const tie_cuda_ctx *c, const Layer &L)
 }
 
 // xs_hi/xs_lo (and xq_hi/xq_lo for Q4_K) must hold the split inputs in sorted order; the sort must
-// have been run with TC_TOKEN_TILE.  Writes hs_hi/hs_lo (and hq_hi/hq_lo when the down matrix is Q4_K).
+// have been run with TC_TOKEN_TILE.  Gate and up run as independent 128-row tiles; the raw fp32
+// products go to the scratch s.y as [row][gate | up].
 int launch_tc_gate_up(tie_cuda_ctx *c, const Layer &L, int n_rows)
 {
-	// gate and up as independent 128-row tiles; raw fp32 products to a scratch [row][gate | up],
-	// then one element-wise SwiGLU + split pass
-	int rc = (L.gate.kind == W_Q4K) ? launch_tc_t<W_Q4K, true>(c, L.gate, &L.up, 0, c->s.y, 1.0f)
-					: launch_tc_t<W_Q6K_R8, true>(c, L.gate, &L.up, 0, c->s.y, 1.0f);
-	if (rc)
-		return rc;
+	(void)n_rows;
+	return (L.gate.kind == W_Q4K) ? launch_tc_t<W_Q4K, true>(c, L.gate, &L.up, 0, c->s.y, 1.0f)
+				      : launch_tc_t<W_Q6K_R8, true>(c, L.gate, &L.up, 0, c->s.y, 1.0f);
+}
+
+// Element-wise SwiGLU of the raw gate | up products, scaled and split into hs_hi/hs_lo (and
+// hq_hi/hq_lo when the down matrix is Q4_K).
+int launch_tc_swiglu(tie_cuda_ctx *c, const Layer &L, int n_rows)
+{
 	const bool sums = L.down.kind == W_Q4K;
 	return launch_swiglu_split(c, c->s.y, n_rows, L.gate.rows, TC_H_SCALE, c->s.hs_hi, c->s.hs_lo, sums ? c->s.hq_hi : nullptr,
 				   sums ? c->s.hq_lo : nullptr);

@@ -30,7 +30,7 @@ EXPORTS = [
     "tie_cuda_version", "tie_cuda_set_profiling", "tie_cuda_get_profile", "tie_cuda_moe_ep_dispatch",
     "tie_cuda_moe_ep_combine", "tie_cuda_route_noalloc",
 ]
-PHASES = ["router", "sort", "split", "gate_up", "down", "combine"]
+PHASES = ["router", "sort", "split", "gate_up", "swiglu", "down", "combine"]
 
 
 class TieCudaError(RuntimeError):

@@ -65,3 +65,9 @@ def algorithmic_bytes(shape: synth.MoeShape, n_tokens: int, active_experts: int)
 def algorithmic_flops(shape: synth.MoeShape, n_tokens: int) -> int:
     """One multiply-add per weight element per token (never the split passes)."""
     return n_tokens * shape.flops_per_token
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the two grouped GEMM kernels on the
+# 512-token prefill workload, from the ncu capture summarised in
+# profiles/grouped_gemm_sb_prefill512.md (bench.py reports them as roofline.traffic).
+NCU_DRAM_BYTES_PER_LAUNCH = {"gate_up_tc": None, "down_tc": None}
