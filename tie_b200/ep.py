@@ -6,7 +6,7 @@ The reference is a single process and has no counterpart.  Per block and rank:
   route (local, router replicated)                       -> top-k ids, weights
   dispatch: counting sort of the (token, slot) rows by expert id; since a rank owns a
             contiguous expert range this also groups rows by destination rank
-  all-to-all of per-rank row counts, then of the rows and their expert ids
+  all-to-all of the per-expert row counts (to each expert's owner), then of the rows
   expert rows on the owner (grouped mat-vec / GEMM over its local experts)
   all-to-all back in the same order
   combine: out[t] = sum_j w[t][j] * y[(t, j)], j ascending
@@ -74,17 +74,22 @@ class EpMoeBlock:
         send_expert = ops.empty((R,), torch.int32)
         counts = ops.empty((ops.E,), torch.int32)
         ops.dispatch(x, idx, send_rows, send_expert, counts)
-        # rows per destination rank, exchanged so every rank knows what it will receive
-        send_counts = counts.view(G, self.n_local).sum(dim=1).to(torch.int64)
-        recv_counts = torch.empty_like(send_counts)
-        dist.all_to_all_single(recv_counts, send_counts, group=self.group)
-        sc = send_counts.tolist()  # host sync: the split sizes are host arguments of the collective
-        rc = recv_counts.tolist()
+        # per-expert row counts go to the expert's owner: every rank then knows how many rows it
+        # receives from whom AND, the rows of a source being sorted by expert, which expert each
+        # received row belongs to (no second exchange for the ids)
+        recv_mat = torch.empty_like(counts)  # [source rank][local expert]
+        dist.all_to_all_single(recv_mat, counts, group=self.group)
+        send_counts = counts.view(G, self.n_local).sum(dim=1)
+        recv_counts = recv_mat.view(G, self.n_local).sum(dim=1)
+        both = torch.cat([send_counts, recv_counts]).tolist()  # host sync: split sizes are host arguments of the collective
+        sc, rc = both[:G], both[G:]
         n_recv = int(sum(rc))
         recv_rows = ops.empty((max(n_recv, 1), H), torch.float32)
-        recv_expert = ops.empty((max(n_recv, 1),), torch.int32)
         dist.all_to_all_single(recv_rows[:n_recv], send_rows, rc, sc, group=self.group)
-        dist.all_to_all_single(recv_expert[:n_recv], send_expert, rc, sc, group=self.group)
+        local_ids = torch.arange(self.rank * self.n_local, (self.rank + 1) * self.n_local, dtype=torch.int32, device=counts.device)
+        recv_expert = ops.empty((max(n_recv, 1),), torch.int32)
+        if n_recv:
+            recv_expert[:n_recv] = torch.repeat_interleave(local_ids.repeat(G), recv_mat.to(torch.int64), output_size=n_recv)
         y_recv = ops.empty((max(n_recv, 1), H), torch.float32)
         ops.expert_rows(recv_rows, recv_expert, n_recv, y_recv)
         y_sorted = ops.empty((R, H), torch.float32)
