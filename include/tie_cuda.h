@@ -52,6 +52,13 @@ extern "C" {
 #define TIE_CUDA_PATH_TENSOR (2u << 8) /* tcgen05 grouped GEMM (prefill) */
 #define TIE_CUDA_PATH_MASK (3u << 8)
 #define TIE_CUDA_PATH_LEGACY_STREAM (1u << 10) /* with PATH_STREAM: use the general streaming kernels even for 1-4 tokens */
+/* Routing of the LFM2-MoE branch (model_lfm2.c:438-473) instead of the Qwen3-MoE one
+ * (model_qwen3.c:421-436): sigmoid of the logits, top-k on sigmoid + router_bias (router_bias is
+ * then the layer's exp_probs_b selection bias, or NULL), gates = the unbiased sigmoids of the
+ * selected experts divided by (their sum + 1e-6).  The logits output of tie_cuda_moe_route then
+ * holds the sigmoid scores.  Accepted by tie_cuda_moe_route and tie_cuda_moe_ffn_biased; the
+ * expert kernels and the combine are the same. */
+#define TIE_CUDA_ROUTE_LFM2 (1u << 12)
 
 typedef struct tie_cuda_ctx tie_cuda_ctx;
 

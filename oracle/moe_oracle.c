@@ -463,6 +463,39 @@ void oracle_route(const oracle_layer_t *L, const float *x, int n_tokens, const f
 	}
 }
 
+/* LFM2-MoE routing (model_lfm2.c:438-473): sigmoid of the raw logits, selection on
+ * sigmoid + sel_bias (exp_probs_b, may be NULL) with the same find_top_k, gates = the UNBIASED
+ * sigmoid of the selected experts, L1-normalised with 1/(sum + 1e-6).  scores (optional)
+ * receives the sigmoid of every logit.  The reference is built with -ffast-math, so its two
+ * divisions are reciprocal estimates refined once: gates agree to a few ulp, not bit for bit. */
+void oracle_route_lfm2(const oracle_layer_t *L, const float *x, int n_tokens, const float *sel_bias, int *topk_idx,
+		       float *topk_w, float *scores)
+{
+	const int H = L->hidden, E = L->n_expert, K = L->top_k;
+#pragma omp parallel for schedule(static)
+	for (int t = 0; t < n_tokens; t++) {
+		float sg[E], sel[E], sc[K];
+		int *idx = topk_idx + (size_t)t * K;
+		float *w = topk_w + (size_t)t * K;
+		oracle_mat_vec_f32(x + (size_t)t * H, L->router_w, sg, H, 0, E);
+		for (int e = 0; e < E; e++) {
+			sg[e] = 1.0f / (1.0f + expf(-sg[e]));
+			sel[e] = sel_bias ? sg[e] + sel_bias[e] : sg[e];
+		}
+		if (scores)
+			memcpy(scores + (size_t)t * E, sg, sizeof(float) * E);
+		oracle_find_top_k(sel, E, K, idx, sc);
+		float sum = 0.0f;
+		for (int j = 0; j < K; j++) {
+			w[j] = sg[idx[j]];
+			sum += w[j];
+		}
+		const float inv = 1.0f / (sum + 1e-6f);
+		for (int j = 0; j < K; j++)
+			w[j] *= inv;
+	}
+}
+
 /* hidden += MoE(RMSNorm(hidden)) — model_qwen3.c:392-401, 403-471, 491 (math_avx2.c:731-751). */
 int oracle_moe_block_inplace(const oracle_layer_t *L, float *hidden, int n_tokens, const float *norm_w, float eps,
 			     float *normed, float *ffn_out, int *topk_idx, float *topk_w, int parallel)

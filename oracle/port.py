@@ -53,6 +53,8 @@ def lib() -> ctypes.CDLL:
         L.oracle_moe_ffn.restype = i32
         L.oracle_moe_ffn.argtypes = [vp, vp, i32, vp, vp, vp, vp, vp, i32]
         L.oracle_route.argtypes = [vp, vp, i32, vp, vp, vp, vp]
+        L.oracle_route_lfm2.argtypes = [vp, vp, i32, vp, vp, vp, vp]
+        L.oracle_route_lfm2.restype = None
         L.oracle_moe_block_inplace.restype = i32
         L.oracle_moe_block_inplace.argtypes = [vp, vp, i32, vp, f32, vp, vp, vp, vp, i32]
         L.oracle_expert_rows.restype = i32
@@ -115,6 +117,32 @@ class PortMoe:
         self.L.oracle_route(ctypes.byref(self.c), x.ctypes.data, T, _p(router_bias), idx.ctypes.data,
                             w.ctypes.data, logits.ctypes.data)
         return idx, w, logits
+
+    def route_lfm2(self, x, sel_bias=None):
+        """LFM2-MoE routing (model_lfm2.c:438-473): ids, L1-normalised sigmoid gates, sigmoid scores."""
+        s = self.shape
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        T = x.shape[0]
+        idx = np.empty((T, s.top_k), dtype=np.int32)
+        w = np.empty((T, s.top_k), dtype=np.float32)
+        scores = np.empty((T, s.n_expert), dtype=np.float32)
+        if sel_bias is not None:
+            sel_bias = np.ascontiguousarray(sel_bias, dtype=np.float32)
+        self.L.oracle_route_lfm2(ctypes.byref(self.c), x.ctypes.data, T, _p(sel_bias), idx.ctypes.data,
+                                 w.ctypes.data, scores.ctypes.data)
+        return idx, w, scores
+
+    def moe_ffn_lfm2(self, x, sel_bias=None):
+        """The LFM2-MoE branch (model_lfm2.c:414-498): LFM2 routing, the same expert FFNs, the
+        weighted accumulation in slot order."""
+        s = self.shape
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        idx, w, _ = self.route_lfm2(x, sel_bias)
+        y = self.expert_rows(np.repeat(x, s.top_k, axis=0), idx.reshape(-1)).reshape(x.shape[0], s.top_k, s.hidden)
+        out = np.zeros_like(x)
+        for j in range(s.top_k):
+            out += w[:, j:j + 1] * y[:, j, :]
+        return out, idx, w
 
     def moe_block_inplace(self, hidden, norm_w=None, eps=1e-6, parallel=2):
         s = self.shape

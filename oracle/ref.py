@@ -38,6 +38,8 @@ class RefMoe:
         L.tieref_set_layer.argtypes = [vp, vp, i32, vp, i32, vp, i32, vp]
         L.tieref_moe_ffn.restype = i32
         L.tieref_moe_ffn.argtypes = [vp, i32, vp, vp, vp, vp, vp]
+        L.tieref_route_lfm2.restype = i32
+        L.tieref_route_lfm2.argtypes = [vp, i32, vp, vp, vp, vp]
         L.tieref_moe_block_inplace.restype = i32
         L.tieref_moe_block_inplace.argtypes = [vp, i32, f32, vp, vp, vp, vp]
         L.tieref_mat_vec.argtypes = [vp, vp, i32, vp, i32, i32]
@@ -100,6 +102,22 @@ class RefMoe:
         if rc:
             raise RuntimeError(f"tieref_moe_ffn failed: {rc}")
         return (out, idx, w, logits) if want_logits else (out, idx, w)
+
+    def route_lfm2(self, x: np.ndarray, sel_bias: np.ndarray | None = None):
+        """Routing step of the LFM2-MoE branch (model_lfm2.c:438-473): ids, gates, sigmoid scores."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        T = x.shape[0]
+        idx = np.empty((T, self.top_k), dtype=np.int32)
+        w = np.empty((T, self.top_k), dtype=np.float32)
+        scores = np.empty((T, self.n_expert), dtype=np.float32)
+        bias_p = None
+        if sel_bias is not None:
+            sel_bias = np.ascontiguousarray(sel_bias, dtype=np.float32)
+            bias_p = sel_bias.ctypes.data
+        rc = self.L.tieref_route_lfm2(x.ctypes.data, T, bias_p, idx.ctypes.data, w.ctypes.data, scores.ctypes.data)
+        if rc:
+            raise RuntimeError(f"tieref_route_lfm2 failed: {rc}")
+        return idx, w, scores
 
     def moe_block_inplace(self, hidden: np.ndarray, eps: float = 1e-6):
         """hidden += MoE(RMSNorm(hidden)); returns (new_hidden, normed, ffn_out, idx, w)."""

@@ -227,6 +227,49 @@ void tieref_rms_norm(const float *x, const float *w, float *o, int size, float e
 	dispatch_rms_norm(&xs, &t, &os, size, eps);
 }
 
+/*
+ * The routing step of the LFM2-MoE branch (model_lfm2.c:438-473), whose statements sit inline in
+ * transformer_layer_lfm2: the reference's router mat-vec and find_top_k are called, the loops in
+ * between are restated here and compiled with the reference's flags.  sel_bias = exp_probs_b
+ * (may be NULL).  Outputs: topk_idx / topk_w [T x top_k], scores [T x n_expert] (sigmoid; optional).
+ */
+int tieref_route_lfm2(const float *x, int n_tokens, const float *sel_bias, int *topk_idx, float *topk_w, float *scores_out)
+{
+	struct TIEContext *ctx = &g.ctx;
+	LayerWeights *l = &g.layer;
+	const int H = g.hidden, E = g.n_expert, K = g.top_k;
+	for (int i = 0; i < n_tokens; i++) {
+		MemType xin = {.type = GGML_TYPE_F32, .data = (void *)(x + (size_t)i * H)};
+		float *scores = ctx->mem.expert_scores.data;
+		float selection_scores[E];
+		dispatch_mat_vec(ctx, &xin, &l->ffn_gate_inp, &ctx->mem.expert_scores, H, E, false);
+		for (int e = 0; e < E; e++)
+			scores[e] = 1.0f / (1.0f + expf(-scores[e]));
+		if (sel_bias) {
+			for (int e = 0; e < E; e++)
+				selection_scores[e] = scores[e] + sel_bias[e];
+		} else {
+			memcpy(selection_scores, scores, sizeof(float) * E);
+		}
+		ExpertChoice top[K];
+		find_top_k(selection_scores, E, K, top);
+		float gate_values[K];
+		float sum_weights = 0.0f;
+		for (int j = 0; j < K; j++) {
+			gate_values[j] = scores[top[j].index];
+			sum_weights += gate_values[j];
+		}
+		float inv_sum = 1.0f / (sum_weights + 1e-6f);
+		for (int j = 0; j < K; j++) {
+			topk_idx[(size_t)i * K + j] = top[j].index;
+			topk_w[(size_t)i * K + j] = gate_values[j] * inv_sum;
+		}
+		if (scores_out)
+			memcpy(scores_out + (size_t)i * E, scores, sizeof(float) * E);
+	}
+	return 0;
+}
+
 /* Wall-clock seconds for n_tokens tokens through tieref_moe_ffn (weights resident, pre-touched
  * by one untimed token).  Used as the CPU baseline next to the GPU number. */
 double tieref_time_moe_ffn(const float *x, int n_tokens, const float *router_bias, float *out)

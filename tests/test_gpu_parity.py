@@ -205,6 +205,88 @@ def test_down_tensor_as_q4k_and_gate_up_as_q6k(small_shape, ref_silu_table, port
         b.close()
 
 
+def test_tensor_path_odd_block_counts_and_all_tile_sizes(ref_silu_table, port_lib):
+    """Q4_K tensors with an odd number of super-blocks per row (3 and 1: the min phase pads its last
+    16-deep k step with zeros and one producer group has no block), token tiles of all three box
+    sizes (<= 16, <= 32, <= 64 rows) and an expert with more than one tile."""
+    from tie_b200 import moe
+    s = synth.MoeShape(hidden=768, n_expert=32, top_k=4, ffn_dim=256)
+    seed = 321
+    gu_blocks = s.ffn_dim * (s.hidden // 256)
+    dn_blocks = s.hidden * (s.ffn_dim // 256)
+    router = synth.normal_f32(seed, synth.STREAM_ROUTER, s.n_expert * s.hidden, 0.02).reshape(s.n_expert, s.hidden)
+    layer = synth.MoeLayer(s, router,
+                           synth.q4k_blocks(seed, synth.STREAM_GATE, s.n_expert * gu_blocks),
+                           synth.q4k_blocks(seed, synth.STREAM_UP, s.n_expert * gu_blocks),
+                           synth.q4k_blocks(seed, synth.STREAM_DOWN, s.n_expert * dn_blocks),
+                           gate_type=synth.GGML_Q4_K, up_type=synth.GGML_Q4_K, down_type=synth.GGML_Q4_K)
+    P = port_lib.PortMoe(layer, silu=ref_silu_table)
+    T = 200
+    x = synth.make_x(seed, T, s.hidden)
+    bias = np.zeros(s.n_expert, np.float32)
+    bias[5] = 3.0   # most tokens pick expert 5: more than 64 rows -> several tiles
+    bias[9] = 0.4
+    ref_out, idx, _ = P.moe_ffn(x, router_bias=bias)
+    counts = np.bincount(idx.ravel(), minlength=s.n_expert)
+    assert counts.max() > 64 and (counts <= 16).any() and ((counts > 16) & (counts <= 32)).any()
+    b = moe.MoeBackend(hidden=s.hidden, n_expert=s.n_expert, top_k=s.top_k, ffn_dim=s.ffn_dim, max_tokens=256,
+                       silu_table=ref_silu_table)
+    try:
+        b.upload_layer(0, layer)
+        for p in (moe.PATH_STREAM, moe.PATH_TENSOR):
+            _check_ffn(b.moe_ffn(0, x, router_bias=bias, path=p), ref_out)
+    finally:
+        b.close()
+
+
+def test_upload_from_gguf_file(tmp_path, small_shape, ref_silu_table, port_lib):
+    """Weights read from a GGUF file (mixed Q6_K / Q4_K down tensors per block) and uploaded from
+    the mapping give the same outputs as the oracle on the generated arrays."""
+    from tie_b200 import gguf, moe
+    from test_gguf import moe_model, write_gguf
+    kvs, tensors, layers = moe_model(small_shape, 2, seed=55, down_types=[synth.GGML_Q6_K, synth.GGML_Q4_K])
+    path = str(tmp_path / "model.gguf")
+    write_gguf(path, kvs, tensors)
+    x = synth.make_x(55, 48, small_shape.hidden)
+    with gguf.GgufFile(path) as g:
+        cfg = g.moe_config()
+        b = moe.MoeBackend(hidden=cfg["hidden"], n_expert=cfg["n_expert"], top_k=cfg["top_k"], ffn_dim=cfg["ffn_dim"],
+                           n_layers=cfg["n_layers"], max_tokens=64, silu_table=ref_silu_table)
+        try:
+            assert gguf.upload_model(b, g) == 2
+        finally:
+            pass
+    # the mapping is gone: the device copies are what the calls use
+    try:
+        for i, layer in enumerate(layers):
+            ref_out, _, _ = port_lib.PortMoe(layer, silu=ref_silu_table).moe_ffn(x)
+            for p in (moe.PATH_STREAM, moe.PATH_TENSOR):
+                _check_ffn(b.moe_ffn(i, x, path=p), ref_out)
+    finally:
+        b.close()
+
+
+def test_lfm2_routing_and_block(be, layer0, ref_silu_table, port_lib, golden):
+    """The second caller of the expert kernels (model_lfm2.c:414-498): sigmoid routing with a
+    selection bias and L1-normalised gates.  Selected experts identical to the compiled
+    reference's (fixture), gates to 1e-6 (CUDA expf vs glibc, -ffast-math reciprocals in the
+    reference), block outputs within the 1e-3 bound against the restatement."""
+    from tie_b200 import moe
+    g = golden("lfm2_route.npz")
+    x = synth.make_x(0, 64)
+    for bias, gi, gw in ((None, g["idx"], g["w"]), (g["bias"], g["idx_b"], g["w_b"])):
+        idx, w, scores = be.route(0, x, router_bias=bias, lfm2=True)
+        assert np.array_equal(idx, gi)
+        assert np.max(np.abs(w - gw) / gw) < 2e-6
+        assert np.max(np.abs(scores - g["scores"])) < 1e-6
+    P = port_lib.PortMoe(layer0, silu=ref_silu_table)
+    for T in (3, 64):
+        ref_out, ref_idx, _ = P.moe_ffn_lfm2(x[:T], g["bias"])
+        assert np.array_equal(ref_idx, g["idx_b"][:T])
+        for p in ((moe.PATH_AUTO, moe.PATH_STREAM) if T == 3 else (moe.PATH_STREAM, moe.PATH_TENSOR)):
+            _check_ffn(be.moe_ffn(0, x[:T], router_bias=g["bias"], path=p, lfm2=True), ref_out)
+
+
 # ---------------- the FFN half of a layer, residual stream on the device ----------------
 
 def test_block_inplace(be, layer0, golden):

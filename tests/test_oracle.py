@@ -161,6 +161,25 @@ def test_port_block_inplace(port_lib, layer0, ref_silu_table, golden):
     assert workloads.rel_rms_err(h, g["hidden_out"]).max() < 1e-5
 
 
+def test_port_lfm2_routing_against_reference_fixture(port_lib, layer0, ref_silu_table, golden):
+    """LFM2-MoE routing (model_lfm2.c:438-473): same experts in the same order as the compiled
+    reference; gates to a few ulp (the reference's two divisions are -ffast-math reciprocal
+    estimates, glibc expf on both sides)."""
+    g = golden("lfm2_route.npz")
+    P = _port(port_lib, layer0, ref_silu_table)
+    x = synth.make_x(0, 64)
+    idx, w, scores = P.route_lfm2(x)
+    assert np.array_equal(idx, g["idx"])
+    assert np.max(np.abs(w - g["w"]) / g["w"]) < 1e-6
+    assert np.max(np.abs(scores - g["scores"])) < 5e-7
+    idx_b, w_b, _ = P.route_lfm2(x, g["bias"])
+    assert np.array_equal(idx_b, g["idx_b"]) and (idx_b != idx).any()
+    assert np.max(np.abs(w_b - g["w_b"]) / g["w_b"]) < 1e-6
+    # gates are the unbiased sigmoids, L1-normalised with 1/(sum + 1e-6)
+    sel = np.take_along_axis(scores, idx_b, axis=1)
+    assert np.allclose(w_b, sel / (sel.sum(1, keepdims=True) + 1e-6), rtol=1e-6)
+
+
 def test_port_silu_table_close_to_reference(port_lib, ref_silu_table):
     """The restated table (IEEE division) vs the compiled reference's (reciprocal estimate)."""
     t = port_lib.silu_table()

@@ -256,11 +256,15 @@ int moe_ffn_device(tie_cuda_ctx *c, Layer &L, const float *x, float *out, int n_
 		   const float *residual, unsigned flags)
 {
 	Scratch &s = c->s;
+	const int lfm2 = (flags & TIE_CUDA_ROUTE_LFM2) ? 1 : 0;
 	prof_mark(c, 0);
 	// decode (1-4 tokens): three launches — router with fused selection, gate/up, down + combine
 	if ((flags & TIE_CUDA_PATH_MASK) != TIE_CUDA_PATH_TENSOR && !(flags & TIE_CUDA_PATH_LEGACY_STREAM) &&
 	    decode_supported(c, L, n_tokens)) {
-		TRY(launch_router_decode_fused(c, x, L.router_w, bias_dev, n_tokens, s.logits, s.topk_idx, s.topk_w));
+		if (lfm2)  // the LFM2 selection is a kernel of its own
+			TRY(launch_router(c, x, L.router_w, bias_dev, n_tokens, s.logits, s.topk_idx, s.topk_w, 1));
+		else
+			TRY(launch_router_decode_fused(c, x, L.router_w, bias_dev, n_tokens, s.logits, s.topk_idx, s.topk_w));
 		prof_mark(c, 1);
 		c->last_used_tc = false;
 		c->last_direct_rows = n_tokens * c->cfg.top_k;
@@ -273,7 +277,7 @@ int moe_ffn_device(tie_cuda_ctx *c, Layer &L, const float *x, float *out, int n_
 		prof_mark(c, 7);
 		return TIE_CUDA_OK;
 	}
-	TRY(launch_router(c, x, L.router_w, bias_dev, n_tokens, s.logits, s.topk_idx, s.topk_w));
+	TRY(launch_router(c, x, L.router_w, bias_dev, n_tokens, s.logits, s.topk_idx, s.topk_w, lfm2));
 	prof_mark(c, 1);
 	TRY(run_experts(c, L, x, c->cfg.top_k, s.topk_idx, n_tokens * c->cfg.top_k, s.y, flags));
 	TRY(launch_combine(c, s.y, s.topk_w, n_tokens, residual, out));
@@ -645,7 +649,7 @@ int tie_cuda_moe_ffn_biased(tie_cuda_ctx *c, int layer, const float *x, float *o
 	const size_t bytes = (size_t)n_tokens * c->cfg.hidden * sizeof(float);
 	const bool dev = flags & TIE_CUDA_DEVICE;
 	const bool graph = flags & TIE_CUDA_GRAPH;
-	const unsigned kflags = flags & (TIE_CUDA_DEVICE | TIE_CUDA_PATH_MASK);
+	const unsigned kflags = flags & (TIE_CUDA_DEVICE | TIE_CUDA_PATH_MASK | TIE_CUDA_PATH_LEGACY_STREAM | TIE_CUDA_ROUTE_LFM2);
 	const float *bias_dev = nullptr;
 	if (router_bias) {
 		if (dev) {
@@ -721,7 +725,8 @@ int tie_cuda_moe_route(tie_cuda_ctx *c, int layer, const float *x, int n_tokens,
 	const int H = c->cfg.hidden, E = c->cfg.n_expert, K = c->cfg.top_k;
 	Scratch &s = c->s;
 	if (flags & TIE_CUDA_DEVICE) {
-		TRY(launch_router(c, x, L->router_w, router_bias, n_tokens, logits ? logits : s.logits, topk_idx, topk_w));
+		TRY(launch_router(c, x, L->router_w, router_bias, n_tokens, logits ? logits : s.logits, topk_idx, topk_w,
+				  (flags & TIE_CUDA_ROUTE_LFM2) ? 1 : 0));
 		if (flags & TIE_CUDA_NO_SYNC)
 			return TIE_CUDA_OK;
 		return check_status(c);
@@ -732,7 +737,7 @@ int tie_cuda_moe_route(tie_cuda_ctx *c, int layer, const float *x, int n_tokens,
 		bias_dev = s.bias;
 	}
 	TRY(h2d(c, s.x, x, (size_t)n_tokens * H * sizeof(float), c->pin_x));
-	TRY(launch_router(c, s.x, L->router_w, bias_dev, n_tokens, s.logits, s.topk_idx, s.topk_w));
+	TRY(launch_router(c, s.x, L->router_w, bias_dev, n_tokens, s.logits, s.topk_idx, s.topk_w, (flags & TIE_CUDA_ROUTE_LFM2) ? 1 : 0));
 	TIE_CUDA_TRY(c, cudaMemcpyAsync(c->pin_idx, s.topk_idx, (size_t)n_tokens * K * sizeof(int), cudaMemcpyDeviceToHost, c->stream));
 	TIE_CUDA_TRY(c, cudaMemcpyAsync(c->pin_w, s.topk_w, (size_t)n_tokens * K * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
 	if (logits)

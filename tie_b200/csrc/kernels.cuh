@@ -6,7 +6,7 @@ namespace tie {
 
 // router.cu
 int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *bias, int n_tokens, float *logits,
-		  int *topk_idx, float *topk_w);
+		  int *topk_idx, float *topk_w, int lfm2 = 0);
 int router_setup(tie_cuda_ctx *c);
 int launch_router_decode_fused(tie_cuda_ctx *c, const float *x, const float *w, const float *bias, int n_tokens, float *logits,
 			       int *topk_idx, float *topk_w);

@@ -277,6 +277,75 @@ __global__ void __launch_bounds__(128) router_topk(const float *__restrict__ log
 	topk_softmax_warp(logits, warp, lane, n_expert, top_k, topk_idx, topk_w);
 }
 
+// LFM2-MoE routing (model_lfm2.c:438-473), one warp per token: s = sigmoid(logit) for every
+// expert, selection by the same arg-max rounds on s + sel_bias (exp_probs_b, may be null), gates =
+// the UNBIASED s of the selected experts, summed in slot order and scaled by 1/(sum + 1e-6).
+// logits is overwritten with the sigmoid scores (the reference does the same to expert_scores).
+__global__ void __launch_bounds__(128) router_topk_lfm2(float *__restrict__ logits, const float *__restrict__ sel_bias,
+							int n_tokens, int n_expert, int top_k, int *__restrict__ topk_idx,
+							float *__restrict__ topk_w)
+{
+	const int token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+	const int lane = threadIdx.x & 31;
+	if (token >= n_tokens)
+		return;
+	float *lg = logits + (size_t)token * n_expert;
+	float sg[8], v[8];
+	const int per = (n_expert + 31) / 32;
+#pragma unroll
+	for (int i = 0; i < 8; i++) {
+		const int e = lane + 32 * i;
+		const bool in = i < per && e < n_expert;
+		sg[i] = in ? __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-__ldcg(lg + e)))) : 0.0f;
+		v[i] = in ? (sel_bias ? __fadd_rn(sg[i], sel_bias[e]) : sg[i]) : -INFINITY;
+		if (in)
+			lg[e] = sg[i];
+	}
+	unsigned taken = 0;
+	float my_gate = 0.0f;
+	int my_idx = -1;
+	for (int r = 0; r < top_k; r++) {
+		float best = -INFINITY, best_sg = 0.0f;
+		int bi = 0x7fffffff;
+#pragma unroll
+		for (int i = 0; i < 8; i++) {
+			const int e = lane + 32 * i;
+			const bool ok = !(taken & (1u << i)) && i < per && e < n_expert;
+			// strictly greater wins; within a lane indices ascend, so ties keep the lower index
+			if (ok && (v[i] > best || bi == 0x7fffffff)) {
+				best = v[i];
+				best_sg = sg[i];
+				bi = e;
+			}
+		}
+#pragma unroll
+		for (int o = 16; o > 0; o >>= 1) {
+			const float ob = __shfl_xor_sync(0xffffffffu, best, o), os = __shfl_xor_sync(0xffffffffu, best_sg, o);
+			const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+			const bool take = (oi != 0x7fffffff) && (bi == 0x7fffffff || ob > best || (ob == best && oi < bi));
+			if (take) {
+				best = ob;
+				best_sg = os;
+				bi = oi;
+			}
+		}
+		if (bi != 0x7fffffff && (bi & 31) == lane)
+			taken |= 1u << (bi >> 5);
+		if (lane == r) {
+			my_gate = best_sg;
+			my_idx = (bi == 0x7fffffff) ? -1 : bi;
+		}
+	}
+	float sum = 0.0f;
+	for (int j = 0; j < top_k; j++)
+		sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, my_gate, j));
+	const float inv = __fdiv_rn(1.0f, __fadd_rn(sum, 1e-6f));
+	if (lane < top_k) {
+		topk_idx[(size_t)token * top_k + lane] = my_idx;
+		topk_w[(size_t)token * top_k + lane] = __fmul_rn(my_gate, inv);
+	}
+}
+
 // Decode: logits as in router_logits_decode, and the CTA that finishes last (a counter, no
 // waiting) runs the selection for all tokens, saving a launch on the latency-bound path.
 __global__ void __launch_bounds__(256) router_decode_fused(const float *__restrict__ x, const float *__restrict__ w,
@@ -357,10 +426,15 @@ __global__ void __launch_bounds__(256) router_decode_fused(const float *__restri
 		*counter = 0;
 }
 
+// lfm2 = 0: bias (optional) is added to the logits, top-k + softmax over the selected logits
+// (Qwen3-MoE).  lfm2 = 1: LFM2-MoE routing, bias (optional) is the selection bias exp_probs_b.
 int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *bias, int n_tokens, float *logits,
-		  int *topk_idx, float *topk_w)
+		  int *topk_idx, float *topk_w, int lfm2)
 {
 	const int H = c->cfg.hidden, E = c->cfg.n_expert, K = c->cfg.top_k;
+	const float *sel_bias = lfm2 ? bias : nullptr;
+	if (lfm2)
+		bias = nullptr;
 	if (n_tokens <= 8) {
 		size_t smem = ((size_t)H + (size_t)n_tokens * (H + 8)) * sizeof(float);
 		router_logits_decode<8><<<E, 64, smem, c->stream>>>(x, w, bias, logits, n_tokens, H, E);
@@ -384,8 +458,11 @@ int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *
 		TIE_CUDA_LAUNCHED(c);
 	}
 	const int warps_per_block = 4;
-	router_topk<<<(n_tokens + warps_per_block - 1) / warps_per_block, warps_per_block * 32, 0, c->stream>>>(
-		logits, n_tokens, E, K, topk_idx, topk_w);
+	const int topk_blocks = (n_tokens + warps_per_block - 1) / warps_per_block;
+	if (lfm2)
+		router_topk_lfm2<<<topk_blocks, warps_per_block * 32, 0, c->stream>>>(logits, sel_bias, n_tokens, E, K, topk_idx, topk_w);
+	else
+		router_topk<<<topk_blocks, warps_per_block * 32, 0, c->stream>>>(logits, n_tokens, E, K, topk_idx, topk_w);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }

@@ -17,6 +17,7 @@ LIB_PATH = os.path.join(_HERE, "libtie_cuda.so")
 HOST, DEVICE, NO_SYNC, GRAPH = 0, 1, 2, 4
 PATH_AUTO, PATH_STREAM, PATH_TENSOR = 0, 1 << 8, 2 << 8
 PATH_LEGACY_STREAM = 1 << 10
+ROUTE_LFM2 = 1 << 12  # LFM2-MoE routing: sigmoid, selection bias, L1-normalised gates (model_lfm2.c:438-473)
 OK, EINVAL, ENOTSUP, ENOMEM, ECUDA, ENODEV, EKERNEL, ETOOBIG = 0, -1, -2, -3, -4, -5, -6, -7
 
 # every symbol include/tie_cuda.h declares
@@ -226,18 +227,19 @@ class MoeBackend:
 
     # -- compute: numpy in / numpy out (host pointers) --
     def moe_ffn(self, layer_idx: int, x: np.ndarray, router_bias: np.ndarray | None = None, path: int = PATH_AUTO,
-                out: np.ndarray | None = None) -> np.ndarray:
+                out: np.ndarray | None = None, lfm2: bool = False) -> np.ndarray:
         x = np.ascontiguousarray(x, dtype=np.float32)
         if out is None:
             out = np.empty_like(x)
         if router_bias is not None:
             router_bias = np.ascontiguousarray(router_bias, dtype=np.float32)
         rc = self.L.tie_cuda_moe_ffn_biased(self.h, layer_idx, x.ctypes.data, out.ctypes.data, x.shape[0],
-                                            _ptr(router_bias), HOST | path)
+                                            _ptr(router_bias), HOST | path | (ROUTE_LFM2 if lfm2 else 0))
         self._check(rc, "tie_cuda_moe_ffn")
         return out
 
-    def route(self, layer_idx: int, x: np.ndarray, router_bias: np.ndarray | None = None, want_logits: bool = True):
+    def route(self, layer_idx: int, x: np.ndarray, router_bias: np.ndarray | None = None, want_logits: bool = True,
+              lfm2: bool = False):
         x = np.ascontiguousarray(x, dtype=np.float32)
         T = x.shape[0]
         idx = np.empty((T, self.top_k), dtype=np.int32)
@@ -246,7 +248,7 @@ class MoeBackend:
         if router_bias is not None:
             router_bias = np.ascontiguousarray(router_bias, dtype=np.float32)
         rc = self.L.tie_cuda_moe_route(self.h, layer_idx, x.ctypes.data, T, _ptr(router_bias), idx.ctypes.data,
-                                       w.ctypes.data, _ptr(logits), HOST)
+                                       w.ctypes.data, _ptr(logits), HOST | (ROUTE_LFM2 if lfm2 else 0))
         self._check(rc, "tie_cuda_moe_route")
         return idx, w, logits
 
