@@ -16,6 +16,7 @@
 namespace tie {
 
 constexpr int SORT_THREADS = 256;
+constexpr int SORT_RPT = 8;  // rows per thread and chunk in sort_place
 
 __global__ void __launch_bounds__(SORT_THREADS) sort_count(const int *__restrict__ row_expert, int n_rows, int first_expert,
 							   int n_local, int *__restrict__ counts, unsigned *__restrict__ status)
@@ -101,23 +102,41 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_place(const int *__restrict
 		for (int j = threadIdx.x; j * n_tile < cnt; j += SORT_THREADS)
 			tile_info[s_tiles + j] = make_int4(le, base + j * n_tile, min(n_tile, cnt - j * n_tile), 0);
 	}
+	// each thread takes SORT_RPT consecutive rows of a chunk, so ranks follow the row order:
+	// rank = rows of this expert in earlier chunks + in earlier threads (warp scan + warp totals)
+	// + earlier ones among the thread's own
 	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-	for (int r0 = 0; r0 < n_rows; r0 += SORT_THREADS) {
-		int r = r0 + threadIdx.x;
-		bool mine = (r < n_rows) && (row_expert[r] == e);
-		unsigned b = __ballot_sync(0xffffffffu, mine);
-		if (lane == 0)
-			wcnt[warp] = __popc(b);
+	constexpr int CHUNK = SORT_THREADS * SORT_RPT;
+	for (int r0 = 0; r0 < n_rows; r0 += CHUNK) {
+		const int rt = r0 + threadIdx.x * SORT_RPT;
+		unsigned m = 0;
+#pragma unroll
+		for (int i = 0; i < SORT_RPT; i++)
+			if (rt + i < n_rows && row_expert[rt + i] == e)
+				m |= 1u << i;
+		const int cnt = __popc(m);
+		int incl = cnt;
+#pragma unroll
+		for (int o = 1; o < 32; o <<= 1) {
+			const int v = __shfl_up_sync(0xffffffffu, incl, o);
+			if (lane >= o)
+				incl += v;
+		}
+		if (lane == 31)
+			wcnt[warp] = incl;
 		__syncthreads();
-		int before = 0, total = 0;
+		int before = incl - cnt, total = 0;
 #pragma unroll
 		for (int i = 0; i < SORT_THREADS / 32; i++) {
-			int cw = wcnt[i];
+			const int cw = wcnt[i];
 			before += (i < warp) ? cw : 0;
 			total += cw;
 		}
-		if (mine)
-			perm[base + before + __popc(b & ((1u << lane) - 1u))] = r;
+		int pos = base + before;
+#pragma unroll
+		for (int i = 0; i < SORT_RPT; i++)
+			if (m & (1u << i))
+				perm[pos++] = rt + i;
 		base += total;
 		__syncthreads();
 	}
