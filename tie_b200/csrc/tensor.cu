@@ -492,10 +492,10 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 					TCT_TRACE(0, it + 2 * grp + 1);
 				}
 				const long long tm = TCT_NOW();
-				ex.emit(2 * grp, 0, lane_base + TC_COL_A + 32u * sa);
-				ex.emit(2 * grp, 1, lane_base + TC_COL_A + 32u * sa);
-				ex.emit(2 * grp + 1, 0, lane_base + TC_COL_A + 32u * sb2);
-				ex.emit(2 * grp + 1, 1, lane_base + TC_COL_A + 32u * sb2);
+				// (kept as a loop: the expansion code stays small in the instruction cache)
+#pragma unroll 1
+				for (int q = 0; q < 4; q++)
+					ex.emit(2 * grp + (q >> 1), q & 1, lane_base + TC_COL_A + 32u * ((q >> 1) ? sb2 : sa));
 				ptx::tmem_st_wait();
 				TCT_ADD(2, tm);
 				ptx::tc_fence_before();
