@@ -46,6 +46,23 @@ def be_small(small_layer, small_shape, ref_silu_table):
 
 # ---------------- router: bit-exact ----------------
 
+def test_route_bit_exact_thousands_of_tokens(layer0, port0, ref_silu_table):
+    """From 2048 tokens on the batched router uses its 8 x 8 register-tile variant; ragged count."""
+    from tie_b200 import moe
+    n = 2048 + 37
+    x = synth.make_x(3, n)
+    ref_idx, ref_w, ref_logits = port0.route(x)
+    b = moe.MoeBackend(max_tokens=n, silu_table=ref_silu_table)
+    try:
+        b.upload_layer(0, layer0)
+        idx, w, logits = b.route(0, x)
+    finally:
+        b.close()
+    assert np.array_equal(logits.view(np.uint32), ref_logits.view(np.uint32))
+    assert np.array_equal(idx, ref_idx)
+    assert np.max(np.abs(w - ref_w)) < 2e-7
+
+
 @pytest.mark.parametrize("n_tokens", [1, 3, 8, 9, 64, 512])
 def test_route_bit_exact(be, port0, n_tokens):
     x = synth.make_x(0, n_tokens)

@@ -67,86 +67,95 @@ __global__ void __launch_bounds__(EPC * 8) router_logits_tile(const float *__res
 	}
 }
 
-// Batched token counts: CTA = 16 tokens x 32 experts; thread = one AVX2 lane l of a 4-token x
-// 8-expert tile (32 chains, each a strict i-ascending sequence of fused multiply-adds, so the
-// result stays bit-identical).  The limit of this kernel is shared-memory-to-register bandwidth
-// (one float per lane per cycle), so every loaded float must feed several multiply-adds from
-// registers: 12 loads per 32 multiply-adds here.  Operands are staged by cp.async in 128-float k
-// chunks (a 4-deep ring); a row pitch of KC+8 floats puts the 4 token groups of a warp on
-// disjoint banks.
-constexpr int RMT_TT = 16, RMT_TE = 32, RMT_KC = 128, RMT_PITCH = RMT_KC + 8;
+// Batched token counts: thread = one AVX2 lane l of a TPT-token x EPT-expert register tile (each
+// of its chains a strict i-ascending sequence of fused multiply-adds, so the result stays
+// bit-identical).  The limit of this kernel is shared-memory-to-register bandwidth (one float per
+// lane per cycle), so every loaded float must feed several multiply-adds from registers.
+// Operands are staged by cp.async in k chunks (a 4-deep ring); a row pitch of KC+8 floats puts
+// the 4 token groups of a warp on disjoint banks, and the 4 groups share their expert rows
+// (broadcast loads).
 constexpr int RMT_STAGES = 4;
-constexpr int RMT_SMEM = RMT_STAGES * (RMT_TT + RMT_TE) * RMT_PITCH * (int)sizeof(float);
 
-// EPT = experts per thread: 8 (128 threads) when there are enough tokens to fill the GPU with
-// such CTAs, 4 (256 threads, twice the warps per SM to hide latency) for a few hundred tokens.
-template <int EPT>
-__global__ void __launch_bounds__(8 * 4 * (RMT_TE / EPT)) router_logits_mt(const float *__restrict__ x, const float *__restrict__ w,
-									   const float *__restrict__ bias, float *__restrict__ logits,
-									   int n_tokens, int hidden, int n_expert)
+// TPT x EPT = tokens x experts per thread, TE = experts per CTA, KC = k chunk.  CTA = 4 TPT
+// tokens x TE experts, 8 x 4 x TE/EPT threads.
+//   <4, 4, 32, 128>: 16 x 32 tiles, 256 threads, 104 KB — a few hundred tokens (parallelism first);
+//   <8, 8, 64, 64>:  32 x 64 tiles, 256 threads, 108 KB, two CTAs per SM — thousands of tokens
+//                    (16 loads per 64 multiply-adds instead of 8 per 16).
+template <int TPT, int EPT, int TE, int KC>
+struct RmtCfg {
+	static constexpr int TT = 4 * TPT, PITCH = KC + 8, THREADS = 8 * 4 * (TE / EPT);
+	static constexpr int STAGE_FLOATS = (TT + TE) * PITCH;
+	static constexpr int SMEM = RMT_STAGES * STAGE_FLOATS * (int)sizeof(float);
+};
+
+template <int TPT, int EPT, int TE, int KC>
+__global__ void __launch_bounds__((RmtCfg<TPT, EPT, TE, KC>::THREADS))
+router_logits_mt(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias, float *__restrict__ logits,
+		 int n_tokens, int hidden, int n_expert)
 {
-	constexpr int RMT_THREADS = 8 * 4 * (RMT_TE / EPT);
+	using Cfg = RmtCfg<TPT, EPT, TE, KC>;
+	constexpr int TT = Cfg::TT, PITCH = Cfg::PITCH, THREADS = Cfg::THREADS;
 	extern __shared__ __align__(16) float rsm[];
-	const int t0 = blockIdx.x * RMT_TT, e0 = blockIdx.y * RMT_TE;
+	const int t0 = blockIdx.x * TT, e0 = blockIdx.y * TE;
 	const int l = threadIdx.x & 7;		// AVX2 lane
-	const int tg = (threadIdx.x >> 3) & 3;	// tokens tg, tg+4, tg+8, tg+12
+	const int tg = (threadIdx.x >> 3) & 3;	// tokens tg, tg+4, tg+8, ...
 	const int eg = threadIdx.x >> 5;	// experts EPT*eg .. EPT*eg+EPT-1 (one warp per expert group)
 	auto stage = [&](int buf, int k0) {
-		float *xs = rsm + buf * (RMT_TT + RMT_TE) * RMT_PITCH;
-		float *ws = xs + RMT_TT * RMT_PITCH;
-		for (int i = threadIdx.x; i < (RMT_TT + RMT_TE) * (RMT_KC / 4); i += RMT_THREADS) {
-			const int r = i / (RMT_KC / 4), c4 = i % (RMT_KC / 4);
+		float *xs = rsm + buf * Cfg::STAGE_FLOATS;
+		float *ws = xs + TT * PITCH;
+		for (int i = threadIdx.x; i < (TT + TE) * (KC / 4); i += THREADS) {
+			const int r = i / (KC / 4), c4 = i % (KC / 4);
 			const float *src;
 			float *dst;
-			if (r < RMT_TT) {
+			if (r < TT) {
 				const int t = min(t0 + r, n_tokens - 1);  // rows past the end are computed and dropped
 				src = x + (size_t)t * hidden + k0 + 4 * c4;
-				dst = xs + r * RMT_PITCH + 4 * c4;
+				dst = xs + r * PITCH + 4 * c4;
 			} else {
-				src = w + (size_t)(e0 + r - RMT_TT) * hidden + k0 + 4 * c4;
-				dst = ws + (r - RMT_TT) * RMT_PITCH + 4 * c4;
+				src = w + (size_t)(e0 + r - TT) * hidden + k0 + 4 * c4;
+				dst = ws + (r - TT) * PITCH + 4 * c4;
 			}
 			asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src)
 				     : "memory");
 		}
 		asm volatile("cp.async.commit_group;" ::: "memory");
 	};
-	float acc[4][EPT];  // [token j][expert b]
+	float acc[TPT][EPT];  // [token j][expert b]
 #pragma unroll
-	for (int j = 0; j < 4; j++)
+	for (int j = 0; j < TPT; j++)
 #pragma unroll
 		for (int b = 0; b < EPT; b++)
 			acc[j][b] = 0.0f;
-	const int n_chunks = hidden / RMT_KC;
+	const int n_chunks = hidden / KC;
 #pragma unroll
 	for (int c = 0; c < RMT_STAGES - 1; c++) {
 		if (c < n_chunks)
-			stage(c, c * RMT_KC);
+			stage(c, c * KC);
 		else
 			asm volatile("cp.async.commit_group;" ::: "memory");
 	}
 	for (int c = 0; c < n_chunks; c++) {
 		if (c + RMT_STAGES - 1 < n_chunks)
-			stage((c + RMT_STAGES - 1) % RMT_STAGES, (c + RMT_STAGES - 1) * RMT_KC);
+			stage((c + RMT_STAGES - 1) % RMT_STAGES, (c + RMT_STAGES - 1) * KC);
 		else
 			asm volatile("cp.async.commit_group;" ::: "memory");
 		asm volatile("cp.async.wait_group %0;" ::"n"(RMT_STAGES - 1) : "memory");
 		__syncthreads();
-		const float *xs = rsm + (c % RMT_STAGES) * (RMT_TT + RMT_TE) * RMT_PITCH;
-		const float *ws = xs + RMT_TT * RMT_PITCH;
-		const float *xp = xs + tg * RMT_PITCH + l;
-		const float *wp = ws + (EPT * eg) * RMT_PITCH + l;
-#pragma unroll 4
-		for (int i = 0; i < RMT_KC / 8; i++) {
-			float xv[4], wv[EPT];
+		const float *xs = rsm + (c % RMT_STAGES) * Cfg::STAGE_FLOATS;
+		const float *ws = xs + TT * PITCH;
+		const float *xp = xs + tg * PITCH + l;
+		const float *wp = ws + (EPT * eg) * PITCH + l;
+#pragma unroll 2
+		for (int i = 0; i < KC / 8; i++) {
+			float xv[TPT], wv[EPT];
 #pragma unroll
-			for (int j = 0; j < 4; j++)
-				xv[j] = xp[(4 * j) * RMT_PITCH + 8 * i];
+			for (int j = 0; j < TPT; j++)
+				xv[j] = xp[(4 * j) * PITCH + 8 * i];
 #pragma unroll
 			for (int b = 0; b < EPT; b++)
-				wv[b] = wp[b * RMT_PITCH + 8 * i];
+				wv[b] = wp[b * PITCH + 8 * i];
 #pragma unroll
-			for (int j = 0; j < 4; j++)
+			for (int j = 0; j < TPT; j++)
 #pragma unroll
 				for (int b = 0; b < EPT; b++)
 					acc[j][b] = __fmaf_rn(xv[j], wv[b], acc[j][b]);
@@ -154,7 +163,7 @@ __global__ void __launch_bounds__(8 * 4 * (RMT_TE / EPT)) router_logits_mt(const
 		__syncthreads();
 	}
 #pragma unroll
-	for (int j = 0; j < 4; j++) {
+	for (int j = 0; j < TPT; j++) {
 		const int t = t0 + tg + 4 * j;
 #pragma unroll
 		for (int b = 0; b < EPT; b++) {
@@ -439,12 +448,15 @@ int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *
 		size_t smem = ((size_t)H + (size_t)n_tokens * (H + 8)) * sizeof(float);
 		router_logits_decode<8><<<E, 64, smem, c->stream>>>(x, w, bias, logits, n_tokens, H, E);
 		TIE_CUDA_LAUNCHED(c);
-	} else if (E % RMT_TE == 0 && H % RMT_KC == 0) {
-		dim3 grid((n_tokens + RMT_TT - 1) / RMT_TT, E / RMT_TE);
-		if (n_tokens <= 1024)
-			router_logits_mt<4><<<grid, 256, RMT_SMEM, c->stream>>>(x, w, bias, logits, n_tokens, H, E);
-		else
-			router_logits_mt<8><<<grid, 128, RMT_SMEM, c->stream>>>(x, w, bias, logits, n_tokens, H, E);
+	} else if (E % 64 == 0 && H % 128 == 0 && n_tokens >= 2048) {
+		using Cfg = RmtCfg<8, 8, 64, 64>;
+		dim3 grid((n_tokens + Cfg::TT - 1) / Cfg::TT, E / 64);
+		router_logits_mt<8, 8, 64, 64><<<grid, Cfg::THREADS, Cfg::SMEM, c->stream>>>(x, w, bias, logits, n_tokens, H, E);
+		TIE_CUDA_LAUNCHED(c);
+	} else if (E % 32 == 0 && H % 128 == 0) {
+		using Cfg = RmtCfg<4, 4, 32, 128>;
+		dim3 grid((n_tokens + Cfg::TT - 1) / Cfg::TT, E / 32);
+		router_logits_mt<4, 4, 32, 128><<<grid, Cfg::THREADS, Cfg::SMEM, c->stream>>>(x, w, bias, logits, n_tokens, H, E);
 		TIE_CUDA_LAUNCHED(c);
 	} else if (n_tokens <= 512) {
 		constexpr int TT = 8, EPC = 16;
@@ -482,8 +494,10 @@ int router_setup(tie_cuda_ctx *c)
 {
 	TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_logits_decode<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
 	TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_decode_fused, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-	TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_logits_mt<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, RMT_SMEM));
-	TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_logits_mt<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, RMT_SMEM));
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_logits_mt<4, 4, 32, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+					     RmtCfg<4, 4, 32, 128>::SMEM));
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(router_logits_mt<8, 8, 64, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+					     RmtCfg<8, 8, 64, 64>::SMEM));
 	return TIE_CUDA_OK;
 }
 
