@@ -304,6 +304,25 @@ def test_lfm2_routing_and_block(be, layer0, ref_silu_table, port_lib, golden):
             _check_ffn(be.moe_ffn(0, x[:T], router_bias=g["bias"], path=p, lfm2=True), ref_out)
 
 
+def test_prefill_4096_tokens_sampled_rows(layer0, port0, ref_silu_table):
+    """The largest single-GPU configuration: every expert has several token tiles and a CTA of the
+    grouped GEMM walks more work items than it stages in shared memory.  The reference path is per
+    token, so a sample of rows is checked against the restatement run on those tokens alone."""
+    from tie_b200 import moe
+    T = 4096
+    x = synth.make_x(11, T)
+    rows = np.array([0, 1, 63, 64, 65, 511, 512, 1000, 2047, 2048, 3000, 4094, 4095])
+    ref_out, _, _ = port0.moe_ffn(x[rows])
+    b = moe.MoeBackend(max_tokens=T, silu_table=ref_silu_table)
+    try:
+        b.upload_layer(0, layer0)
+        out = b.moe_ffn(0, x, path=moe.PATH_TENSOR)
+    finally:
+        b.close()
+    assert np.isfinite(out).all()
+    _check_ffn(out[rows], ref_out)
+
+
 # ---------------- the FFN half of a layer, residual stream on the device ----------------
 
 def test_block_inplace(be, layer0, golden):
