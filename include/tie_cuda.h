@@ -159,6 +159,45 @@ int tie_cuda_moe_ep_dispatch(tie_cuda_ctx *c, const float *x, const int *topk_id
 int tie_cuda_moe_ep_combine(tie_cuda_ctx *c, const float *y_sorted, const float *topk_w, int n_tokens, float *out,
 			    unsigned flags);
 
+/* ---- expert parallelism over peer memory (the reference has no counterpart) ----
+ * One context per GPU (ep_rank / ep_size in the config; max_tokens = ep_size x the tokens one rank
+ * brings per step, so that the scratch holds the worst case of every row landing on one rank).
+ * Dispatch and combine are not collectives here: every rank exposes one region of its HBM, the
+ * owners' kernels read token rows straight out of the sources' regions and the sources read the
+ * expert outputs straight out of the owners' (plain loads over NVLink); ranks synchronise through
+ * step-numbered flags they store into each other's regions.  No host synchronisation per step.
+ *
+ * Set-up, once, collectively: tie_cuda_ep_ipc_handle() on every rank, exchange the 64-byte
+ * handles by any host channel, tie_cuda_ep_attach(handles, ep_size, TIE_CUDA_EP_PEER_IPC_HANDLES).
+ * Contexts of ONE process (several ranks emulated on one GPU, or one process driving several
+ * GPUs with peer access enabled) pass tie_cuda_ep_region() base pointers instead
+ * (TIE_CUDA_EP_PEER_POINTERS).  The entry of the calling rank itself is ignored.
+ *
+ * A step, on every rank, in this order (device pointers, TIE_CUDA_DEVICE; tensor-core path only):
+ *   tie_cuda_ep_publish  routes x [n_tokens][hidden] (0 <= n_tokens <= max_tokens / ep_size, may
+ *                        differ between ranks), sorts its rows by expert and announces them
+ *   tie_cuda_ep_compute  waits for every rank's announcement, gathers the rows of this rank's
+ *                        experts from their sources, runs gate/up, SwiGLU, down
+ *   tie_cuda_ep_gather   waits for every owner, out[t] = (residual[t] +) sum_j w[t][j] * y(t, j)
+ * tie_cuda_moe_ffn_ep is the three in a row.  Kernels of different ranks wait on one another, so
+ * ranks that share ONE GPU must enqueue phase by phase on one stream (all publishes, then all
+ * computes, then all gathers) — a wait is then always already satisfied; on separate GPUs the
+ * ranks run freely.  Every wait is bounded (tie_cuda_ep_set_timeout_ms, default 5 s): a rank that
+ * never arrives makes the others return TIE_CUDA_EKERNEL with their contexts usable; the group
+ * must then detach and attach again before its next step. */
+#define TIE_CUDA_EP_HANDLE_BYTES 64
+#define TIE_CUDA_EP_PEER_POINTERS 0
+#define TIE_CUDA_EP_PEER_IPC_HANDLES 1
+int tie_cuda_ep_region(tie_cuda_ctx *c, void **base, size_t *bytes);
+int tie_cuda_ep_ipc_handle(tie_cuda_ctx *c, void *handle /* TIE_CUDA_EP_HANDLE_BYTES */);
+int tie_cuda_ep_attach(tie_cuda_ctx *c, const void *const *peers, int n_peers, int kind);
+int tie_cuda_ep_detach(tie_cuda_ctx *c);
+int tie_cuda_ep_set_timeout_ms(tie_cuda_ctx *c, int ms);
+int tie_cuda_ep_publish(tie_cuda_ctx *c, int layer, const float *x, int n_tokens, const float *router_bias, unsigned flags);
+int tie_cuda_ep_compute(tie_cuda_ctx *c, int layer, unsigned flags);
+int tie_cuda_ep_gather(tie_cuda_ctx *c, float *out, const float *residual, unsigned flags);
+int tie_cuda_moe_ffn_ep(tie_cuda_ctx *c, int layer, const float *x, float *out, int n_tokens, unsigned flags);
+
 /* ---- math_dispatch.c rows (accel = 2) ----
  * Same argument meaning as the reference's kernels are CALLED with (math_dispatch.c:224,254):
  * (X, W_data, O, in_dim, start_row, end_row); X, O host fp32.  W must point into (or at) a

@@ -77,3 +77,86 @@ def test_exchange_matches_single_process_oracle(tokens, tmp_path):
     outs = [p.communicate(timeout=300)[0] for p in procs]
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and "EP_OK" in o, f"rank {r}:\n{o[-3000:]}"
+
+
+# The peer-memory path (csrc/ep.cu) has no row exchange: every rank derives the whole row layout
+# from the G x E count matrix.  Here two gloo ranks run ep.peer_layout (the host restatement of
+# that index arithmetic) with "peer memory" stood in by all_gather'ed arrays, and the combined
+# result must equal the single-process oracle: an error in the segment / output-position algebra
+# sends some row to the wrong expert or token.
+PEER_WORKER = r"""
+import os, sys
+sys.path.insert(0, %(root)r)
+import numpy as np, torch, torch.distributed as dist
+from tie_b200 import synth, workloads, ep
+from oracle import port
+
+rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%(port)d", rank=rank, world_size=world)
+shape = synth.MoeShape(hidden=512, n_expert=32, top_k=4, ffn_dim=256)
+layer = synth.make_layer(workloads.BASE_SEED + 1, shape)
+P = port.PortMoe(layer)
+K, H, E = shape.top_k, shape.hidden, shape.n_expert
+NL = E // world
+T = %(tokens)d + 3 * rank          # ragged: the ranks bring different token counts
+x = synth.make_x(workloads.BASE_SEED + 1, T, H, first_token=100 * rank)
+
+# publish: route, stable sort of the (token, slot) rows by expert, counts
+idx, w, _ = P.route(x)
+flat = idx.reshape(-1)
+ids = np.argsort(flat, kind="stable").astype(np.int32)
+inv = np.empty_like(ids); inv[ids] = np.arange(ids.size, dtype=np.int32)
+counts = np.bincount(flat, minlength=E).astype(np.int32)
+my_off = np.concatenate([[0], np.cumsum(counts)])
+
+def gather(obj):
+    out = [None] * world
+    dist.all_gather_object(out, obj)
+    return out
+
+peer_counts, peer_ids, peer_x = gather(counts), gather(ids), gather(x)   # what the owners read from the sources
+L = ep.peer_layout(np.stack(peer_counts), rank)
+
+# compute: rows of this rank's experts, gathered per segment from their sources
+n = L["n_rows"]
+rows = np.zeros((n, H), dtype=np.float32); experts = np.zeros(n, dtype=np.int32)
+for i in range(NL * world):
+    le, s = divmod(i, world)
+    b, e = int(L["seg_base"][i]), int(L["seg_base"][i + 1])
+    assert e - b == peer_counts[s][rank * NL + le]
+    for j in range(e - b):
+        rid = peer_ids[s][int(L["seg_src"][i]) + j]
+        rows[b + j] = peer_x[s][rid // K]
+        experts[b + j] = rank * NL + le
+y = P.expert_rows(rows, experts) if n else np.zeros((0, H), dtype=np.float32)
+peer_y = gather(y)                                                       # what the sources read from the owners
+
+# gather: out[t] = sum_j w[t][j] * y_owner[ybase[e] + inv[(t, j)] - my_off[e]], j ascending
+acc = np.zeros((T, H), dtype=np.float32)
+for t in range(T):
+    for j in range(K):
+        e = int(idx[t, j]); d = e // NL
+        pos = int(L["ybase"][e]) + int(inv[t * K + j]) - int(my_off[e])
+        acc[t] = (np.float64(w[t, j]) * peer_y[d][pos].astype(np.float64) + acc[t].astype(np.float64)).astype(np.float32)
+ref, _, _ = P.moe_ffn(x)
+err = float(workloads.rel_rms_err(acc, ref).max()) if T else 0.0
+assert err < 1e-6, err
+tot = torch.tensor([n]); dist.all_reduce(tot)
+assert int(tot.item()) == sum(int(c.sum()) for c in peer_counts)
+dist.barrier(); dist.destroy_process_group()
+print("EP_OK", rank, err)
+"""
+
+
+@pytest.mark.parametrize("tokens", [0, 11])
+def test_peer_layout_matches_single_process_oracle(tokens):
+    import socket
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    code = PEER_WORKER % dict(root=ROOT, port=port, tokens=tokens)
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", OMP_NUM_THREADS="2")
+        procs.append(subprocess.Popen([sys.executable, "-c", code], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and "EP_OK" in o, f"rank {r}:\n{o[-3000:]}"

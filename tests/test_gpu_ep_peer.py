@@ -1,0 +1,153 @@
+"""Expert parallelism over peer memory (tie_cuda_ep_*): G ranks emulated on ONE GPU as G contexts
+of this process that share a stream.  Their kernels wait on one another's flags, so the phases
+are enqueued rank by rank (all publishes, all computes, all gathers): every wait is already
+satisfied when its kernel runs, nothing ever spins on work that is queued behind it.
+
+The result must equal the single-context block on the concatenated tokens (same kernels, same
+arithmetic per row) and stay within the parity bound of the CPU restatement.
+"""
+import numpy as np
+import pytest
+
+from tie_b200 import synth, workloads
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-3
+
+
+_streams = []
+
+
+def _ranks(shape, layer_seed, G, t_max, silu):
+    import torch
+    from tie_b200 import moe
+    n_local = shape.n_expert // G
+    bes = []
+    stream = torch.cuda.Stream()  # ONE stream for all emulated ranks: their kernels run in enqueue order
+    _streams.append(stream)
+    for r in range(G):
+        b = moe.MoeBackend(hidden=shape.hidden, n_expert=shape.n_expert, top_k=shape.top_k, ffn_dim=shape.ffn_dim,
+                           max_tokens=t_max * G, silu_table=silu, ep_rank=r, ep_size=G)
+        b.upload_layer(0, synth.make_layer(layer_seed, shape, first_expert=r * n_local, n_local_expert=n_local))
+        b.set_stream(stream.cuda_stream)
+        bes.append(b)
+    bases = [b.ep_region()[0] for b in bes]
+    for b in bes:
+        b.ep_attach(bases, moe.EP_PEER_POINTERS)
+        b.ep_set_timeout_ms(200)
+    return bes
+
+
+def _step(bes, xs, outs, residuals=None):
+    from tie_b200 import moe
+    fl = moe.DEVICE | moe.NO_SYNC
+    for b, x in zip(bes, xs):
+        b.ep_publish_ptr(0, x if x.shape[0] else None, x.shape[0], None, fl)
+    for b in bes:
+        b.ep_compute(0, fl)
+    for i, (b, o) in enumerate(zip(bes, outs)):
+        b.ep_gather_ptr(o if o.shape[0] else None, None if residuals is None else residuals[i], fl)
+    for b in bes:
+        b.synchronize()
+
+
+@pytest.mark.parametrize("G,tokens", [(1, [48]), (2, [40, 23]), (4, [17, 0, 64, 5]), (8, [9, 31, 1, 0, 12, 64, 7, 20])])
+def test_emulated_ranks_small_shape(small_shape, small_layer, ref_silu_table, port_lib, G, tokens):
+    import torch
+    from tie_b200 import moe
+    shape = small_shape
+    seed = workloads.BASE_SEED + 1
+    bes = _ranks(shape, seed, G, 64, ref_silu_table)
+    one = moe.MoeBackend(hidden=shape.hidden, n_expert=shape.n_expert, top_k=shape.top_k, ffn_dim=shape.ffn_dim, max_tokens=256,
+                         silu_table=ref_silu_table)
+    try:
+        one.upload_layer(0, small_layer)
+        P = port_lib.PortMoe(small_layer, silu=ref_silu_table)
+        for step in range(3):  # the regions and flags are re-used step after step
+            first = 1000 * step
+            xh = [synth.make_x(7, n, shape.hidden, first_token=first + 100 * r) for r, n in enumerate(tokens)]
+            xs = [torch.from_numpy(x).cuda() for x in xh]
+            outs = [torch.full_like(x, float("nan")) for x in xs]
+            _step(bes, xs, outs)
+            x_all = np.concatenate(xh)
+            xa = torch.from_numpy(x_all).cuda()
+            oa = torch.empty_like(xa)
+            one.moe_ffn_ptr(0, xa, oa, x_all.shape[0], moe.DEVICE | moe.PATH_TENSOR)
+            got = np.concatenate([o.cpu().numpy() for o in outs])
+            assert np.isfinite(got).all()
+            # the same kernels computed every row: identical up to the grouping of rows into tiles
+            assert workloads.rel_rms_err(got, oa.cpu().numpy()).max() < 2e-5
+            ref, _, _ = P.moe_ffn(x_all)
+            assert workloads.rel_rms_err(got, ref).max() < TOL
+        assert sum(b.last_active_experts() for b in bes) <= shape.n_expert
+    finally:
+        for b in bes:
+            b.close()
+        one.close()
+
+
+def test_emulated_ranks_block_shape_with_residual(layer0, port0_ep, ref_silu_table):
+    import torch
+    shape = layer0.shape
+    G, tokens = 2, [96, 64]
+    bes = _ranks(shape, workloads.BASE_SEED, G, 128, ref_silu_table)
+    try:
+        xh = [synth.make_x(workloads.BASE_SEED, n, shape.hidden, first_token=200 * r) for r, n in enumerate(tokens)]
+        xs = [torch.from_numpy(x).cuda() for x in xh]
+        res = [torch.from_numpy(np.full_like(x, 0.5)).cuda() for x in xh]
+        outs = [torch.empty_like(x) for x in xs]
+        _step(bes, xs, outs, res)
+        x_all = np.concatenate(xh)
+        ref, _, _ = port0_ep.moe_ffn(x_all)
+        got = np.concatenate([o.cpu().numpy() for o in outs])
+        assert workloads.rel_rms_err(got - 0.5, ref).max() < TOL
+    finally:
+        for b in bes:
+            b.close()
+
+
+@pytest.fixture(scope="module")
+def port0_ep(port_lib, layer0, ref_silu_table):
+    return port_lib.PortMoe(layer0, silu=ref_silu_table)
+
+
+def test_absent_rank_times_out_and_reports(small_shape, ref_silu_table):
+    """A rank that never publishes: the others' waits run out (a flag nothing sets), the status
+    word carries the time-out, the call returns an error code and the context stays usable."""
+    import torch
+    from tie_b200 import moe
+    shape = small_shape
+    bes = _ranks(shape, workloads.BASE_SEED + 1, 2, 64, ref_silu_table)
+    try:
+        b = bes[0]
+        b.ep_set_timeout_ms(50)
+        x = torch.from_numpy(synth.make_x(3, 8, shape.hidden)).cuda()
+        out = torch.zeros_like(x)
+        b.ep_publish_ptr(0, x, 8, None, moe.DEVICE | moe.NO_SYNC)
+        with pytest.raises(moe.TieCudaError) as ei:
+            b.ep_compute(0, moe.DEVICE)  # rank 1 has not published
+        assert ei.value.code == moe.EKERNEL
+        with pytest.raises(moe.TieCudaError):
+            b.ep_gather_ptr(out, None, moe.DEVICE)  # rank 1 has not computed either
+        # the context still serves other calls
+        idx = torch.empty(8, shape.top_k, dtype=torch.int32, device="cuda")
+        w = torch.empty(8, shape.top_k, dtype=torch.float32, device="cuda")
+        b.route_ptr(0, x, 8, idx, w, None, None, moe.DEVICE)
+        assert int(idx.min()) >= 0
+    finally:
+        for b in bes:
+            b.close()
+
+
+def test_phase_order_is_checked(small_shape, ref_silu_table):
+    from tie_b200 import moe
+    bes = _ranks(small_shape, workloads.BASE_SEED + 1, 1, 64, ref_silu_table)
+    try:
+        with pytest.raises(moe.TieCudaError) as ei:
+            bes[0].ep_compute(0, moe.DEVICE)
+        assert ei.value.code == moe.EINVAL
+        with pytest.raises(moe.TieCudaError):
+            bes[0].ep_gather_ptr(None, None, moe.DEVICE)
+    finally:
+        bes[0].close()

@@ -360,6 +360,84 @@ int h2d(tie_cuda_ctx *c, void *dst, const void *src, size_t bytes, void *pin)
 	return TIE_CUDA_OK;
 }
 
+size_t align_up(size_t v, size_t a)
+{
+	return (v + a - 1) / a * a;
+}
+
+void ep_close_peers(tie_cuda_ctx *c)
+{
+	EpState &ep = c->ep;
+	for (int i = 0; i < EP_MAX_RANKS; i++) {
+		if (ep.opened[i] && ep.view.peer[i])
+			cudaIpcCloseMemHandle(ep.view.peer[i]);
+		ep.opened[i] = false;
+		ep.view.peer[i] = nullptr;
+	}
+	ep.attached = false;
+	ep.phase = 0;
+	ep.step_tokens = -1;
+}
+
+void ep_release(tie_cuda_ctx *c)
+{
+	EpState &ep = c->ep;
+	ep_close_peers(c);
+	void *ptrs[] = {ep.region, ep.n_rows, ep.seg_base, ep.seg_src, ep.ybase};
+	for (void *p : ptrs)
+		if (p)
+			cudaFree(p);
+	ep = EpState();
+}
+
+// Allocates the region peers map, on first use.
+int ep_region(tie_cuda_ctx *c)
+{
+	EpState &ep = c->ep;
+	if (ep.region)
+		return TIE_CUDA_OK;
+	const int G = c->cfg.ep_size;
+	if (G > EP_MAX_RANKS || c->cfg.n_expert > 256 || c->cfg.max_tokens % G)
+		return TIE_CUDA_ENOTSUP;
+	EpView &v = ep.view;
+	v = EpView();
+	v.n_ranks = G;
+	v.rank = c->cfg.ep_rank;
+	v.n_local = c->n_local;
+	v.n_expert = c->cfg.n_expert;
+	v.top_k = c->cfg.top_k;
+	v.hidden = c->cfg.hidden;
+	v.t_max = c->cfg.max_tokens / G;
+	v.rows_cap = (long long)c->s.rows_cap;
+	size_t off = 0;
+	v.off_xs = off;
+	off = align_up(off + (size_t)v.t_max * v.hidden * sizeof(float), 256);
+	v.off_ids = off;
+	off = align_up(off + (size_t)v.t_max * v.top_k * sizeof(int), 256);
+	v.off_counts = off;
+	off = align_up(off + (size_t)v.n_expert * sizeof(int), 256);
+	v.off_pub = off;
+	off = align_up(off + EP_MAX_RANKS * sizeof(unsigned), 256);
+	v.off_done = off;
+	off = align_up(off + EP_MAX_RANKS * sizeof(unsigned), 256);
+	v.off_y = off;
+	off = align_up(off + (size_t)v.rows_cap * v.hidden * sizeof(float), 256);
+	TIE_CUDA_TRY(c, cudaMalloc(reinterpret_cast<void **>(&ep.region), off));
+	ep.region_bytes = off;
+	// flags (and everything before y) start at zero; y is written before it is read
+	TIE_CUDA_TRY(c, cudaMemset(ep.region, 0, v.off_y));
+	TRY(dev_alloc(c, &ep.n_rows, 1));
+	TRY(dev_alloc(c, &ep.seg_base, v.n_expert + 1));
+	TRY(dev_alloc(c, &ep.seg_src, v.n_expert));
+	TRY(dev_alloc(c, &ep.ybase, v.n_expert));
+	TIE_CUDA_TRY(c, cudaMemset(ep.n_rows, 0, sizeof(int)));
+	TIE_CUDA_TRY(c, cudaDeviceSynchronize());
+	int khz = 0;
+	TIE_CUDA_TRY(c, cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, c->device));
+	ep.wait_cycles = 5000ll * khz;	// 5 s
+	return TIE_CUDA_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -529,6 +607,7 @@ void tie_cuda_destroy(tie_cuda_ctx *c)
 		cudaFree(c->extra[i]);
 	free(c->extra);
 	free(c->regs);
+	ep_release(c);
 	delete c;
 }
 
@@ -802,6 +881,185 @@ int tie_cuda_moe_ep_combine(tie_cuda_ctx *c, const float *y_sorted, const float 
 		return TIE_CUDA_EINVAL;
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
 	TRY(launch_combine(c, y_sorted, topk_w, n_tokens, nullptr, out, c->s.ep_inv));
+	if (flags & TIE_CUDA_NO_SYNC)
+		return TIE_CUDA_OK;
+	return check_status(c);
+}
+
+// ---- expert parallelism over peer memory (ep.cu) ----
+
+int tie_cuda_ep_region(tie_cuda_ctx *c, void **base, size_t *bytes)
+{
+	if (!c)
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	TRY(ep_region(c));
+	if (base)
+		*base = c->ep.region;
+	if (bytes)
+		*bytes = c->ep.region_bytes;
+	return TIE_CUDA_OK;
+}
+
+int tie_cuda_ep_ipc_handle(tie_cuda_ctx *c, void *handle)
+{
+	static_assert(sizeof(cudaIpcMemHandle_t) == TIE_CUDA_EP_HANDLE_BYTES, "handle size");
+	if (!c || !handle)
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	TRY(ep_region(c));
+	cudaIpcMemHandle_t h;
+	TIE_CUDA_TRY(c, cudaIpcGetMemHandle(&h, c->ep.region));
+	memcpy(handle, &h, sizeof(h));
+	return TIE_CUDA_OK;
+}
+
+int tie_cuda_ep_attach(tie_cuda_ctx *c, const void *const *peers, int n_peers, int kind)
+{
+	if (!c || !peers || n_peers != c->cfg.ep_size || (kind != TIE_CUDA_EP_PEER_POINTERS && kind != TIE_CUDA_EP_PEER_IPC_HANDLES))
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	TRY(ep_region(c));
+	EpState &ep = c->ep;
+	if (ep.attached)
+		return TIE_CUDA_EINVAL;
+	for (int i = 0; i < n_peers; i++) {
+		if (i == c->cfg.ep_rank) {
+			ep.view.peer[i] = ep.region;
+			continue;
+		}
+		if (!peers[i]) {
+			ep_close_peers(c);
+			return TIE_CUDA_EINVAL;
+		}
+		if (kind == TIE_CUDA_EP_PEER_POINTERS) {
+			ep.view.peer[i] = static_cast<uint8_t *>(const_cast<void *>(peers[i]));
+		} else {
+			cudaIpcMemHandle_t h;
+			memcpy(&h, peers[i], sizeof(h));
+			void *p = nullptr;
+			cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+			if (e != cudaSuccess) {
+				snprintf(c->cuda_err, sizeof(c->cuda_err), "cudaIpcOpenMemHandle(rank %d): %s", i, cudaGetErrorString(e));
+				cudaGetLastError();
+				ep_close_peers(c);
+				return TIE_CUDA_ECUDA;
+			}
+			ep.view.peer[i] = static_cast<uint8_t *>(p);
+			ep.opened[i] = true;
+		}
+	}
+	ep.attached = true;
+	ep.step = 0;
+	ep.phase = 0;
+	return TIE_CUDA_OK;
+}
+
+int tie_cuda_ep_detach(tie_cuda_ctx *c)
+{
+	if (!c)
+		return TIE_CUDA_EINVAL;
+	cudaSetDevice(c->device);
+	if (c->stream)
+		cudaStreamSynchronize(c->stream);
+	ep_close_peers(c);
+	return TIE_CUDA_OK;
+}
+
+int tie_cuda_ep_set_timeout_ms(tie_cuda_ctx *c, int ms)
+{
+	if (!c || ms <= 0)
+		return TIE_CUDA_EINVAL;
+	int khz = 0;
+	TIE_CUDA_TRY(c, cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, c->device));
+	c->ep.wait_cycles = (long long)ms * khz;
+	return TIE_CUDA_OK;
+}
+
+int tie_cuda_ep_publish(tie_cuda_ctx *c, int layer, const float *x, int n_tokens, const float *router_bias, unsigned flags)
+{
+	Layer *L;
+	TRY(get_layer(c, layer, &L));
+	EpState &ep = c->ep;
+	if (!(flags & TIE_CUDA_DEVICE) || !ep.attached || ep.phase != 0 || n_tokens < 0 || n_tokens > ep.view.t_max || (n_tokens && !x))
+		return TIE_CUDA_EINVAL;
+	if (!tc_supported(c, *L))
+		return TIE_CUDA_ENOTSUP;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	Scratch &s = c->s;
+	const EpView &v = ep.view;
+	const int R = n_tokens * c->cfg.top_k;
+	if (n_tokens)
+		TRY(launch_router(c, x, L->router_w, router_bias, n_tokens, s.logits, s.topk_idx, s.topk_w,
+				  (flags & TIE_CUDA_ROUTE_LFM2) ? 1 : 0));
+	SortBufs b = {reinterpret_cast<int *>(ep.region + v.off_counts),
+		      s.ep_offsets,
+		      s.ep_tile_start,
+		      s.ep_active,
+		      s.ep_n_active,
+		      reinterpret_cast<int *>(ep.region + v.off_ids),
+		      nullptr,
+		      s.ep_inv};
+	TRY(launch_sort(c, s.topk_idx, R, 128, 0, c->cfg.n_expert, b));
+	float *xs = reinterpret_cast<float *>(ep.region + v.off_xs);
+	if (n_tokens && x != xs)
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(xs, x, (size_t)n_tokens * v.hidden * sizeof(float), cudaMemcpyDeviceToDevice, c->stream));
+	ep.step++;
+	TRY(launch_ep_signal(c, 0, ep.step));
+	ep.phase = 1;
+	ep.step_tokens = n_tokens;
+	if (flags & TIE_CUDA_NO_SYNC)
+		return TIE_CUDA_OK;
+	return check_status(c);
+}
+
+int tie_cuda_ep_compute(tie_cuda_ctx *c, int layer, unsigned flags)
+{
+	Layer *L;
+	TRY(get_layer(c, layer, &L));
+	EpState &ep = c->ep;
+	if (!ep.attached || ep.phase != 1)
+		return TIE_CUDA_EINVAL;
+	if (!tc_supported(c, *L))
+		return TIE_CUDA_ENOTSUP;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	TRY(launch_ep_index(c, ep.step));
+	TRY(launch_ep_split_rows(c, L->gate.kind == W_Q4K));
+	TRY(launch_tc_gate_up(c, *L, 0));
+	TRY(launch_tc_swiglu(c, *L, c->sm_count * 8, ep.n_rows));
+	TRY(launch_tc_down(c, *L, 0, reinterpret_cast<float *>(ep.region + ep.view.off_y), true));
+	TRY(launch_ep_signal(c, 1, ep.step));
+	c->last_used_tc = true;
+	c->last_direct_rows = -1;
+	ep.phase = 2;
+	if (flags & TIE_CUDA_NO_SYNC)
+		return TIE_CUDA_OK;
+	return check_status(c);
+}
+
+int tie_cuda_ep_gather(tie_cuda_ctx *c, float *out, const float *residual, unsigned flags)
+{
+	if (!c)
+		return TIE_CUDA_EINVAL;
+	EpState &ep = c->ep;
+	if (!ep.attached || ep.phase != 2 || (ep.step_tokens > 0 && !out))
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	// (a rank without tokens still waits for its peers: they read its counts during compute)
+	TRY(launch_ep_combine(c, ep.step, ep.step_tokens, residual, out));
+	ep.phase = 0;
+	ep.step_tokens = -1;
+	if (flags & TIE_CUDA_NO_SYNC)
+		return TIE_CUDA_OK;
+	return check_status(c);
+}
+
+int tie_cuda_moe_ffn_ep(tie_cuda_ctx *c, int layer, const float *x, float *out, int n_tokens, unsigned flags)
+{
+	const unsigned inner = flags | TIE_CUDA_NO_SYNC;
+	TRY(tie_cuda_ep_publish(c, layer, x, n_tokens, nullptr, inner));
+	TRY(tie_cuda_ep_compute(c, layer, inner));
+	TRY(tie_cuda_ep_gather(c, out, nullptr, inner));
 	if (flags & TIE_CUDA_NO_SYNC)
 		return TIE_CUDA_OK;
 	return check_status(c);

@@ -82,6 +82,27 @@ struct Scratch {
 	size_t rows_pad = 0;			    // Rpad
 };
 
+// Expert parallelism over peer memory (ep.cu).  EpView is what the kernels get by value.
+constexpr int EP_MAX_RANKS = 16;
+struct EpView {
+	uint8_t *peer[EP_MAX_RANKS];  // region base of every rank, as mapped into this process
+	size_t off_xs, off_ids, off_counts, off_pub, off_done, off_y;
+	long long rows_cap;  // rows of y (and of this context's scratch)
+	int n_ranks, rank, n_local, n_expert, top_k, hidden, t_max;
+};
+struct EpState {
+	EpView view = {};
+	uint8_t *region = nullptr;
+	size_t region_bytes = 0;
+	bool opened[EP_MAX_RANKS] = {false};  // mappings this context opened (CUDA IPC) and must close
+	bool attached = false;
+	unsigned step = 0;	    // number of the last published step
+	int step_tokens = -1;	    // tokens of the step between publish and gather, else -1
+	int phase = 0;		    // 0 idle, 1 published, 2 computed
+	long long wait_cycles = 0;  // budget of every flag wait
+	int *n_rows = nullptr, *seg_base = nullptr, *seg_src = nullptr, *ybase = nullptr;
+};
+
 }  // namespace tie
 
 struct tie_cuda_ctx {
@@ -137,6 +158,7 @@ struct tie_cuda_ctx {
 	// small per-call device buffers for the dispatch rows
 	float *row_x = nullptr, *row_o = nullptr;
 	size_t row_cap = 0;
+	tie::EpState ep;
 };
 
 namespace tie {

@@ -19,6 +19,7 @@ int launch_router_rows(tie_cuda_ctx *c, const float *x, const float *w, int n_ro
 struct SortBufs {
 	int *counts, *offsets, *tile_start, *active, *n_active, *perm;
 	int4 *tile_info;  // optional: one entry per token tile (expert, first sorted row, rows, 0)
+	int *inv = nullptr;  // optional: row id -> sorted position
 };
 int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile);
 int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile, int first_expert, int n_expert,
@@ -37,15 +38,22 @@ int launch_gather_rows(tie_cuda_ctx *c, const float *x, const int *row_expert, c
 int launch_split_rows(tie_cuda_ctx *c, const float *x, const int *perm, int src_div, int n_rows, int n_cols, __half *hi,
 		      __half *lo, __half *q_hi, __half *q_lo);
 int launch_swiglu(tie_cuda_ctx *c, float *gate, const float *up, int n);
+// n_rows_dev != null: the row count is read on the device and n_rows CTAs stride over the rows
 int launch_swiglu_split(tie_cuda_ctx *c, const float *gu, int n_rows, int ffn, float scale, __half *hi, __half *lo, __half *q_hi,
-			__half *q_lo);
+			__half *q_lo, const int *n_rows_dev = nullptr);
 // tensor.cu
 int tc_setup(tie_cuda_ctx *c);
 int tc_make_weight_map(tie_cuda_ctx *c, DevTensor &t);
 bool tc_supported(const tie_cuda_ctx *c, const Layer &L);
 int launch_tc_gate_up(tie_cuda_ctx *c, const Layer &L, int n_rows);
-int launch_tc_swiglu(tie_cuda_ctx *c, const Layer &L, int n_rows);
-int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, float *y);
+int launch_tc_swiglu(tie_cuda_ctx *c, const Layer &L, int n_rows, const int *n_rows_dev = nullptr);
+// sorted_out: y[p] instead of y[perm[p]]
+int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, float *y, bool sorted_out = false);
+// ep.cu
+int launch_ep_signal(tie_cuda_ctx *c, int which, unsigned step);
+int launch_ep_index(tie_cuda_ctx *c, unsigned step);
+int launch_ep_split_rows(tie_cuda_ctx *c, bool sums);
+int launch_ep_combine(tie_cuda_ctx *c, unsigned step, int n_tokens, const float *residual, float *out);
 // repack.cu
 int launch_repack_q6k_r8(tie_cuda_ctx *c, const uint8_t *raw, uint8_t *dst, size_t n_rows_total, int nb);
 

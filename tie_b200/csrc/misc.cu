@@ -143,9 +143,11 @@ __global__ void __launch_bounds__(256) gather_rows(const float *__restrict__ x, 
 __global__ void __launch_bounds__(256) swiglu_split_rows(const float *__restrict__ gu, int ffn, float scale,
 							 const float *__restrict__ silu, __half *__restrict__ hi,
 							 __half *__restrict__ lo, __half *__restrict__ q_hi,
-							 __half *__restrict__ q_lo, int q_cols)
+							 __half *__restrict__ q_lo, int q_cols, const int *__restrict__ n_rows_dev)
 {
-	const size_t r = blockIdx.x;
+	// one row per CTA, or (row count on the device) the CTAs stride over the rows
+	const size_t n_rows = n_rows_dev ? (size_t)*n_rows_dev : gridDim.x;
+	for (size_t r = blockIdx.x; r < n_rows; r += gridDim.x) {
 	const float *g = gu + r * 2 * ffn, *u = g + ffn;
 	__half2 *hr = reinterpret_cast<__half2 *>(hi + r * ffn);
 	__half2 *lr = reinterpret_cast<__half2 *>(lo + r * ffn);
@@ -161,6 +163,7 @@ __global__ void __launch_bounds__(256) swiglu_split_rows(const float *__restrict
 		lr[k / 2 + 1] = __floats2half2_rn(h1 - fb.x, h3 - fb.y);
 		if (q_hi)
 			store_subblock_sum((h0 + h1) + (h2 + h3), k, q_hi + r * q_cols, q_lo + r * q_cols);
+	}
 	}
 }
 
@@ -213,9 +216,9 @@ int launch_gather_rows(tie_cuda_ctx *c, const float *x, const int *row_expert, c
 }
 
 int launch_swiglu_split(tie_cuda_ctx *c, const float *gu, int n_rows, int ffn, float scale, __half *hi, __half *lo, __half *q_hi,
-			__half *q_lo)
+			__half *q_lo, const int *n_rows_dev)
 {
-	swiglu_split_rows<<<n_rows, 256, 0, c->stream>>>(gu, ffn, scale, c->silu, hi, lo, q_hi, q_lo, xq_cols(ffn));
+	swiglu_split_rows<<<n_rows, 256, 0, c->stream>>>(gu, ffn, scale, c->silu, hi, lo, q_hi, q_lo, xq_cols(ffn), n_rows_dev);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }

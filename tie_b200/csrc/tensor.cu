@@ -658,7 +658,7 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 			// rows of this work item: lanes hold consecutive output columns (coalesced 128-byte stores)
 			int rid = 0;
 			if (!RAW && lane < ntok && tok0 + lane < item.n_valid)
-				rid = perm[item.row0 + tok0 + lane];
+				rid = perm ? perm[item.row0 + tok0 + lane] : item.row0 + tok0 + lane;
 #pragma unroll
 			for (int j = 0; j < TC_NT / 2; j++) {
 				const int n = tok0 + j;
@@ -1014,7 +1014,8 @@ int tc_setup(tie_cuda_ctx *c)
 
 // arr: 0 = the split inputs x (gate/up), 1 = the split activations h (down).
 template <WKind KIND, bool RAW>
-static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1, int arr, float *y, float out_scale)
+static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1, int arr, float *y, float out_scale,
+		       bool sorted_out = false)
 {
 	Scratch &s = c->s;
 	const int m_tiles = (RAW ? 2 : 1) * t0.rows / TC_BM;
@@ -1023,7 +1024,8 @@ static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1
 	grouped_gemm_sb<KIND, RAW><<<c->sm_count, TC_THREADS, TcSmem<KIND>::SMEM, c->stream>>>(
 		c->tmap[arr * 3], c->tmap[arr * 3 + 1], c->tmap[arr * 3 + 2], c->tmap[(2 + arr) * 3], c->tmap[(2 + arr) * 3 + 1],
 		c->tmap[(2 + arr) * 3 + 2], w0m, w1m, t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride,
-		t0.k, s.tile_info, s.tile_start, c->n_local, m_tiles, y, s.perm, RAW ? 2 * t0.rows : t0.rows, out_scale, s.status, t0.rows);
+		t0.k, s.tile_info, s.tile_start, c->n_local, m_tiles, y, sorted_out ? nullptr : s.perm, RAW ? 2 * t0.rows : t0.rows, out_scale, s.status,
+		t0.rows);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
@@ -1051,20 +1053,20 @@ int launch_tc_gate_up(tie_cuda_ctx *c, const Layer &L, int n_rows)
 
 // Element-wise SwiGLU of the raw gate | up products, scaled and split into hs_hi/hs_lo (and
 // hq_hi/hq_lo when the down matrix is Q4_K).
-int launch_tc_swiglu(tie_cuda_ctx *c, const Layer &L, int n_rows)
+int launch_tc_swiglu(tie_cuda_ctx *c, const Layer &L, int n_rows, const int *n_rows_dev)
 {
 	const bool sums = L.down.kind == W_Q4K;
 	return launch_swiglu_split(c, c->s.y, n_rows, L.gate.rows, TC_H_SCALE, c->s.hs_hi, c->s.hs_lo, sums ? c->s.hq_hi : nullptr,
-				   sums ? c->s.hq_lo : nullptr);
+				   sums ? c->s.hq_lo : nullptr, n_rows_dev);
 }
 
-// reads hs_hi/hs_lo; writes y[perm[p]].
-int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, float *y)
+// reads hs_hi/hs_lo; writes y[perm[p]] (sorted_out: y[p]).
+int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, float *y, bool sorted_out)
 {
 	(void)n_rows;
 	if (L.down.kind == W_Q4K)
-		return launch_tc_t<W_Q4K, false>(c, L.down, nullptr, 1, y, 1.0f / TC_H_SCALE);
-	return launch_tc_t<W_Q6K_R8, false>(c, L.down, nullptr, 1, y, 1.0f / TC_H_SCALE);
+		return launch_tc_t<W_Q4K, false>(c, L.down, nullptr, 1, y, 1.0f / TC_H_SCALE, sorted_out);
+	return launch_tc_t<W_Q6K_R8, false>(c, L.down, nullptr, 1, y, 1.0f / TC_H_SCALE, sorted_out);
 }
 
 }  // namespace tie

@@ -101,6 +101,59 @@ class EpMoeBlock:
         return out
 
 
+def peer_layout(counts, rank: int, n_tile: int = 64):
+    """Host restatement of the row layout the peer-memory path derives on the device (ep_index in
+    csrc/ep.cu) from the G x E matrix counts[s][e] = rows of source rank s for global expert e.
+
+    Returns a dict with, for `rank` (owner of experts [rank*NL, (rank+1)*NL)):
+      offsets[NL+1]   first sorted row of each local expert (rows ordered by expert, then source)
+      tiles           (local expert, first row, rows) per token tile of n_tile rows
+      seg_base[NL*G+1], seg_src[NL*G]  segment le*G+s: its first row here, its first entry in s's id list
+      ybase[E]        where the owner of expert e puts this rank's rows of e (row index in the owner's y)
+    """
+    counts = np.asarray(counts, dtype=np.int64)
+    G, E = counts.shape
+    NL = E // G
+    fe = rank * NL
+    tot = counts.sum(axis=0)
+    offsets = np.concatenate([[0], np.cumsum(tot[fe:fe + NL])])
+    tiles = [(le, int(offsets[le]) + j, int(min(n_tile, tot[fe + le] - j)))
+             for le in range(NL) for j in range(0, int(tot[fe + le]), n_tile)]
+    src_off = np.concatenate([np.zeros((G, 1), dtype=np.int64), np.cumsum(counts, axis=1)], axis=1)  # [G][E+1]
+    seg_base = np.zeros(NL * G + 1, dtype=np.int64)
+    seg_src = np.zeros(NL * G, dtype=np.int64)
+    for le in range(NL):
+        for s in range(G):
+            seg_base[le * G + s] = offsets[le] + counts[:s, fe + le].sum()
+            seg_src[le * G + s] = src_off[s, fe + le]
+    seg_base[NL * G] = offsets[NL]
+    ybase = np.zeros(E, dtype=np.int64)
+    for e in range(E):
+        d = e // NL
+        ybase[e] = tot[d * NL:e].sum() + counts[:rank, e].sum()
+    return {"offsets": offsets, "tiles": tiles, "seg_base": seg_base, "seg_src": seg_src, "ybase": ybase,
+            "n_rows": int(offsets[NL])}
+
+
+class PeerEpMoeBlock:
+    """One expert-parallel MoE block on this rank over peer memory (tie_cuda_ep_*): no collective
+    and no host synchronisation per step.  torch.distributed is used once, to exchange the IPC
+    handles of the ranks' regions."""
+
+    def __init__(self, be, dist, group=None):
+        from . import moe
+        self.be, self.moe = be, moe
+        G = dist.get_world_size(group)
+        handles = [None] * G
+        dist.all_gather_object(handles, be.ep_ipc_handle(), group=group)
+        be.ep_attach(handles, moe.EP_PEER_IPC_HANDLES)
+        dist.barrier(group=group)  # every rank has mapped every region before the first flag is written
+
+    def forward(self, x, out):
+        self.be.moe_ffn_ep_ptr(0, x, out, x.shape[0], self.moe.DEVICE | self.moe.NO_SYNC)
+        return out
+
+
 def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
     """bench.py --gpus N under torchrun: weak scaling, `tokens_per_rank` tokens on every rank,
     experts sharded.  Rank 0 prints the JSON line."""

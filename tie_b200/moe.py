@@ -29,8 +29,12 @@ EXPORTS = [
     "tie_cuda_mat_vec_row_f32_q4k_f32", "tie_cuda_mat_vec_row_f32_q6k_f32", "tie_cuda_mat_vec_row_f32_f32_f32",
     "tie_cuda_swiglu_f32_f32", "tie_cuda_dispatch_status", "tie_cuda_launch_count", "tie_cuda_last_active_experts",
     "tie_cuda_version", "tie_cuda_set_profiling", "tie_cuda_get_profile", "tie_cuda_moe_ep_dispatch",
-    "tie_cuda_moe_ep_combine", "tie_cuda_route_noalloc",
+    "tie_cuda_moe_ep_combine", "tie_cuda_route_noalloc", "tie_cuda_ep_region", "tie_cuda_ep_ipc_handle",
+    "tie_cuda_ep_attach", "tie_cuda_ep_detach", "tie_cuda_ep_set_timeout_ms", "tie_cuda_ep_publish", "tie_cuda_ep_compute",
+    "tie_cuda_ep_gather", "tie_cuda_moe_ffn_ep",
 ]
+EP_HANDLE_BYTES = 64
+EP_PEER_POINTERS, EP_PEER_IPC_HANDLES = 0, 1
 PHASES = ["router", "sort", "split", "gate_up", "swiglu", "down", "combine"]
 
 
@@ -119,6 +123,24 @@ def load_library() -> ctypes.CDLL:
     L.tie_cuda_set_profiling.argtypes = [vp, i32]
     L.tie_cuda_get_profile.restype = i32
     L.tie_cuda_get_profile.argtypes = [vp, vp]
+    L.tie_cuda_ep_region.restype = i32
+    L.tie_cuda_ep_region.argtypes = [vp, ctypes.POINTER(vp), ctypes.POINTER(ctypes.c_size_t)]
+    L.tie_cuda_ep_ipc_handle.restype = i32
+    L.tie_cuda_ep_ipc_handle.argtypes = [vp, vp]
+    L.tie_cuda_ep_attach.restype = i32
+    L.tie_cuda_ep_attach.argtypes = [vp, ctypes.POINTER(vp), i32, i32]
+    L.tie_cuda_ep_detach.restype = i32
+    L.tie_cuda_ep_detach.argtypes = [vp]
+    L.tie_cuda_ep_set_timeout_ms.restype = i32
+    L.tie_cuda_ep_set_timeout_ms.argtypes = [vp, i32]
+    L.tie_cuda_ep_publish.restype = i32
+    L.tie_cuda_ep_publish.argtypes = [vp, i32, vp, i32, vp, u32]
+    L.tie_cuda_ep_compute.restype = i32
+    L.tie_cuda_ep_compute.argtypes = [vp, i32, u32]
+    L.tie_cuda_ep_gather.restype = i32
+    L.tie_cuda_ep_gather.argtypes = [vp, vp, vp, u32]
+    L.tie_cuda_moe_ffn_ep.restype = i32
+    L.tie_cuda_moe_ffn_ep.argtypes = [vp, i32, vp, vp, i32, u32]
     _lib = L
     return L
 
@@ -282,6 +304,50 @@ class MoeBackend:
     def ep_combine_ptr(self, y_sorted, topk_w, n_tokens: int, out, flags: int = DEVICE):
         rc = self.L.tie_cuda_moe_ep_combine(self.h, _ptr(y_sorted), _ptr(topk_w), n_tokens, _ptr(out), flags)
         self._check(rc, "tie_cuda_moe_ep_combine")
+
+    # -- expert parallelism over peer memory --
+    def ep_region(self):
+        """(device address, bytes) of the region this rank exposes to its peers."""
+        base, nbytes = ctypes.c_void_p(), ctypes.c_size_t()
+        self._check(self.L.tie_cuda_ep_region(self.h, ctypes.byref(base), ctypes.byref(nbytes)), "tie_cuda_ep_region")
+        return int(base.value), int(nbytes.value)
+
+    def ep_ipc_handle(self) -> bytes:
+        buf = ctypes.create_string_buffer(EP_HANDLE_BYTES)
+        self._check(self.L.tie_cuda_ep_ipc_handle(self.h, buf), "tie_cuda_ep_ipc_handle")
+        return buf.raw
+
+    def ep_attach(self, peers, kind: int):
+        """peers: per rank, a device address (EP_PEER_POINTERS) or a 64-byte handle (EP_PEER_IPC_HANDLES)."""
+        n = len(peers)
+        arr = (ctypes.c_void_p * n)()
+        keep = []
+        for i, p in enumerate(peers):
+            if kind == EP_PEER_IPC_HANDLES:
+                b = ctypes.create_string_buffer(bytes(p), EP_HANDLE_BYTES)
+                keep.append(b)
+                arr[i] = ctypes.cast(b, ctypes.c_void_p).value
+            else:
+                arr[i] = p
+        self._check(self.L.tie_cuda_ep_attach(self.h, arr, n, kind), "tie_cuda_ep_attach")
+
+    def ep_detach(self):
+        self._check(self.L.tie_cuda_ep_detach(self.h), "tie_cuda_ep_detach")
+
+    def ep_set_timeout_ms(self, ms: int):
+        self._check(self.L.tie_cuda_ep_set_timeout_ms(self.h, ms), "tie_cuda_ep_set_timeout_ms")
+
+    def ep_publish_ptr(self, layer_idx: int, x, n_tokens: int, router_bias=None, flags: int = DEVICE):
+        self._check(self.L.tie_cuda_ep_publish(self.h, layer_idx, _ptr(x), n_tokens, _ptr(router_bias), flags), "tie_cuda_ep_publish")
+
+    def ep_compute(self, layer_idx: int, flags: int = DEVICE):
+        self._check(self.L.tie_cuda_ep_compute(self.h, layer_idx, flags), "tie_cuda_ep_compute")
+
+    def ep_gather_ptr(self, out, residual=None, flags: int = DEVICE):
+        self._check(self.L.tie_cuda_ep_gather(self.h, _ptr(out), _ptr(residual), flags), "tie_cuda_ep_gather")
+
+    def moe_ffn_ep_ptr(self, layer_idx: int, x, out, n_tokens: int, flags: int = DEVICE):
+        self._check(self.L.tie_cuda_moe_ffn_ep(self.h, layer_idx, _ptr(x), _ptr(out), n_tokens, flags), "tie_cuda_moe_ffn_ep")
 
     # -- math_dispatch rows --
     def make_current(self):
