@@ -221,6 +221,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--ep-exchange", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: dispatch/combine over peer memory (default) or by NCCL all-to-all")
     ap.add_argument("--no-extra", action="store_true", help="skip the decode / 64 / 4096-token side runs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--stack-layers", type=int, default=48, help="blocks of the stack side run (0 = skip)")

@@ -151,3 +151,33 @@ def test_phase_order_is_checked(small_shape, ref_silu_table):
             bes[0].ep_gather_ptr(None, None, moe.DEVICE)
     finally:
         bes[0].close()
+
+
+def test_whole_step_replayed_from_a_graph(small_shape, small_layer, ref_silu_table):
+    """tie_cuda_moe_ffn_ep with TIE_CUDA_GRAPH on a group of one rank: the step number advances on
+    the device, so the replayed launches keep working step after step, with x in the region."""
+    import torch
+    from tie_b200 import moe
+    shape = small_shape
+    bes = _ranks(shape, workloads.BASE_SEED + 1, 1, 64, ref_silu_table)
+    one = moe.MoeBackend(hidden=shape.hidden, n_expert=shape.n_expert, top_k=shape.top_k, ffn_dim=shape.ffn_dim, max_tokens=64,
+                         silu_table=ref_silu_table)
+    try:
+        one.upload_layer(0, small_layer)
+        b = bes[0]
+        x = torch.empty(40, shape.hidden, device="cuda")
+        out = torch.empty_like(x)
+        ref = torch.empty_like(x)
+        launches = []
+        for step in range(4):
+            x.copy_(torch.from_numpy(synth.make_x(11, 40, shape.hidden, first_token=50 * step)))
+            torch.cuda.synchronize()
+            l0 = b.launch_count
+            b.moe_ffn_ep_ptr(0, x, out, 40, moe.DEVICE | moe.GRAPH)
+            launches.append(b.launch_count - l0)
+            one.moe_ffn_ptr(0, x, ref, 40, moe.DEVICE | moe.PATH_TENSOR)
+            assert workloads.rel_rms_err(out.cpu().numpy(), ref.cpu().numpy()).max() < 2e-5
+        assert len(set(launches)) == 1 and launches[0] >= 10
+    finally:
+        bes[0].close()
+        one.close()

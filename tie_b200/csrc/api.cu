@@ -377,13 +377,22 @@ void ep_close_peers(tie_cuda_ctx *c)
 	ep.attached = false;
 	ep.phase = 0;
 	ep.step_tokens = -1;
+	// graphs of whole steps hold the peers' addresses
+	for (int i = 0; i < c->n_graphs;) {
+		if (c->graphs[i].kind == 5) {
+			cudaGraphExecDestroy(c->graphs[i].exec);
+			c->graphs[i] = c->graphs[--c->n_graphs];
+		} else {
+			i++;
+		}
+	}
 }
 
 void ep_release(tie_cuda_ctx *c)
 {
 	EpState &ep = c->ep;
 	ep_close_peers(c);
-	void *ptrs[] = {ep.region, ep.n_rows, ep.seg_base, ep.seg_src, ep.ybase};
+	void *ptrs[] = {ep.region, ep.n_rows, ep.seg_base, ep.seg_src, ep.ybase, ep.step_dev};
 	for (void *p : ptrs)
 		if (p)
 			cudaFree(p);
@@ -430,6 +439,8 @@ int ep_region(tie_cuda_ctx *c)
 	TRY(dev_alloc(c, &ep.seg_base, v.n_expert + 1));
 	TRY(dev_alloc(c, &ep.seg_src, v.n_expert));
 	TRY(dev_alloc(c, &ep.ybase, v.n_expert));
+	TRY(dev_alloc(c, &ep.step_dev, 1));
+	TIE_CUDA_TRY(c, cudaMemset(ep.step_dev, 0, sizeof(unsigned)));
 	TIE_CUDA_TRY(c, cudaMemset(ep.n_rows, 0, sizeof(int)));
 	TIE_CUDA_TRY(c, cudaDeviceSynchronize());
 	int khz = 0;
@@ -598,6 +609,7 @@ void tie_cuda_destroy(tie_cuda_ctx *c)
 			cudaFreeHost(p);
 	for (int i = 0; i < c->n_graphs; i++)
 		cudaGraphExecDestroy(c->graphs[i].exec);
+	c->n_graphs = 0;
 	for (int i = 0; i < 8; i++)
 		if (c->prof_ev[i])
 			cudaEventDestroy(c->prof_ev[i]);
@@ -950,7 +962,6 @@ int tie_cuda_ep_attach(tie_cuda_ctx *c, const void *const *peers, int n_peers, i
 		}
 	}
 	ep.attached = true;
-	ep.step = 0;
 	ep.phase = 0;
 	return TIE_CUDA_OK;
 }
@@ -989,9 +1000,11 @@ int tie_cuda_ep_publish(tie_cuda_ctx *c, int layer, const float *x, int n_tokens
 	Scratch &s = c->s;
 	const EpView &v = ep.view;
 	const int R = n_tokens * c->cfg.top_k;
+	prof_mark(c, 0);
 	if (n_tokens)
 		TRY(launch_router(c, x, L->router_w, router_bias, n_tokens, s.logits, s.topk_idx, s.topk_w,
 				  (flags & TIE_CUDA_ROUTE_LFM2) ? 1 : 0));
+	prof_mark(c, 1);
 	SortBufs b = {reinterpret_cast<int *>(ep.region + v.off_counts),
 		      s.ep_offsets,
 		      s.ep_tile_start,
@@ -1004,8 +1017,8 @@ int tie_cuda_ep_publish(tie_cuda_ctx *c, int layer, const float *x, int n_tokens
 	float *xs = reinterpret_cast<float *>(ep.region + v.off_xs);
 	if (n_tokens && x != xs)
 		TIE_CUDA_TRY(c, cudaMemcpyAsync(xs, x, (size_t)n_tokens * v.hidden * sizeof(float), cudaMemcpyDeviceToDevice, c->stream));
-	ep.step++;
-	TRY(launch_ep_signal(c, 0, ep.step));
+	TRY(launch_ep_signal(c, 0));
+	prof_mark(c, 2);
 	ep.phase = 1;
 	ep.step_tokens = n_tokens;
 	if (flags & TIE_CUDA_NO_SYNC)
@@ -1023,12 +1036,16 @@ int tie_cuda_ep_compute(tie_cuda_ctx *c, int layer, unsigned flags)
 	if (!tc_supported(c, *L))
 		return TIE_CUDA_ENOTSUP;
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
-	TRY(launch_ep_index(c, ep.step));
+	TRY(launch_ep_index(c));
 	TRY(launch_ep_split_rows(c, L->gate.kind == W_Q4K));
+	prof_mark(c, 3);
 	TRY(launch_tc_gate_up(c, *L, 0));
+	prof_mark(c, 4);
 	TRY(launch_tc_swiglu(c, *L, c->sm_count * 8, ep.n_rows));
+	prof_mark(c, 5);
 	TRY(launch_tc_down(c, *L, 0, reinterpret_cast<float *>(ep.region + ep.view.off_y), true));
-	TRY(launch_ep_signal(c, 1, ep.step));
+	TRY(launch_ep_signal(c, 1));
+	prof_mark(c, 6);
 	c->last_used_tc = true;
 	c->last_direct_rows = -1;
 	ep.phase = 2;
@@ -1046,7 +1063,8 @@ int tie_cuda_ep_gather(tie_cuda_ctx *c, float *out, const float *residual, unsig
 		return TIE_CUDA_EINVAL;
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
 	// (a rank without tokens still waits for its peers: they read its counts during compute)
-	TRY(launch_ep_combine(c, ep.step, ep.step_tokens, residual, out));
+	TRY(launch_ep_combine(c, ep.step_tokens, residual, out));
+	prof_mark(c, 7);
 	ep.phase = 0;
 	ep.step_tokens = -1;
 	if (flags & TIE_CUDA_NO_SYNC)
@@ -1056,10 +1074,23 @@ int tie_cuda_ep_gather(tie_cuda_ctx *c, float *out, const float *residual, unsig
 
 int tie_cuda_moe_ffn_ep(tie_cuda_ctx *c, int layer, const float *x, float *out, int n_tokens, unsigned flags)
 {
-	const unsigned inner = flags | TIE_CUDA_NO_SYNC;
-	TRY(tie_cuda_ep_publish(c, layer, x, n_tokens, nullptr, inner));
-	TRY(tie_cuda_ep_compute(c, layer, inner));
-	TRY(tie_cuda_ep_gather(c, out, nullptr, inner));
+	if (!c || c->ep.phase != 0)
+		return TIE_CUDA_EINVAL;
+	const unsigned inner = (flags | TIE_CUDA_NO_SYNC) & ~TIE_CUDA_GRAPH;
+	// the step number lives on the device: a step's launches never change and replay from a graph
+	GraphKey k = {5, layer, n_tokens, x, out, nullptr, nullptr, inner};
+	TRY(run_maybe_graphed(c, flags & TIE_CUDA_GRAPH, k, [&]() -> int {
+		int rc = tie_cuda_ep_publish(c, layer, x, n_tokens, nullptr, inner);
+		if (!rc)
+			rc = tie_cuda_ep_compute(c, layer, inner);
+		if (!rc)
+			rc = tie_cuda_ep_gather(c, out, nullptr, inner);
+		if (rc) {  // nothing of a failed capture runs
+			c->ep.phase = 0;
+			c->ep.step_tokens = -1;
+		}
+		return rc;
+	}));
 	if (flags & TIE_CUDA_NO_SYNC)
 		return TIE_CUDA_OK;
 	return check_status(c);

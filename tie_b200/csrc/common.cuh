@@ -96,7 +96,7 @@ struct EpState {
 	size_t region_bytes = 0;
 	bool opened[EP_MAX_RANKS] = {false};  // mappings this context opened (CUDA IPC) and must close
 	bool attached = false;
-	unsigned step = 0;	    // number of the last published step
+	unsigned *step_dev = nullptr;  // [1] number of the last published step (advanced on the device)
 	int step_tokens = -1;	    // tokens of the step between publish and gather, else -1
 	int phase = 0;		    // 0 idle, 1 published, 2 computed
 	long long wait_cycles = 0;  // budget of every flag wait

@@ -67,9 +67,18 @@ __device__ __forceinline__ T *ep_ptr(const EpView &v, int rank, size_t off)
 	return reinterpret_cast<T *>(v.peer[rank] + off);
 }
 
-// One CTA: tells every peer that this rank's part of `step` is final.  which = 0: pub, 1: done.
-__global__ void ep_signal(EpView v, int which, unsigned step)
+// One CTA: tells every peer that this rank's part of the current step is final.  which = 0 (pub)
+// first advances the step counter, which = 1 (done) reads it.  The counter lives on the device so
+// that a step's launches take the same arguments every time (they can be replayed from a graph).
+__global__ void ep_signal(EpView v, int which, unsigned *__restrict__ step_dev)
 {
+	unsigned step = 0;
+	if (threadIdx.x == 0) {
+		step = *step_dev + (which ? 0u : 1u);
+		if (!which)
+			*step_dev = step;
+	}
+	step = __shfl_sync(0xffffffffu, step, 0);
 	const int d = threadIdx.x;
 	if (d < v.n_ranks) {
 		__threadfence_system();
@@ -79,28 +88,61 @@ __global__ void ep_signal(EpView v, int which, unsigned step)
 
 constexpr int EP_INDEX_THREADS = 256;
 
-// One CTA.  Outputs (this rank's scratch): counts/offsets/tile_start/tile_info/active/n_active
-// exactly as sort_place leaves them for the grouped product, n_rows, the segment table
-// seg_base[E+1] / seg_src[E] (segment i = le*G + s: first sorted row, first entry in s's ids)
-// and ybase[E]: where, in the owner's y, the first row of (this rank, expert e) will be.
+// Exclusive prefix sum of one value per thread over the CTA (EP_INDEX_THREADS threads); total
+// (optional) receives the sum.  wsum: EP_INDEX_THREADS / 32 ints of shared memory.
+__device__ __forceinline__ int ep_block_scan(int val, int *wsum, int *total = nullptr)
+{
+	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+	int incl = val;
+#pragma unroll
+	for (int o = 1; o < 32; o <<= 1) {
+		const int t = __shfl_up_sync(0xffffffffu, incl, o);
+		if (lane >= o)
+			incl += t;
+	}
+	__syncthreads();  // wsum may still be read by the previous scan
+	if (lane == 31)
+		wsum[warp] = incl;
+	__syncthreads();
+	int before = 0, all = 0;
+#pragma unroll
+	for (int i = 0; i < EP_INDEX_THREADS / 32; i++) {
+		const int w = wsum[i];
+		before += i < warp ? w : 0;
+		all += w;
+	}
+	if (total)
+		*total = all;
+	return before + incl - val;
+}
+
+// One CTA; thread i stands for expert i (n_expert <= EP_INDEX_THREADS).  Outputs (this rank's
+// scratch): counts/offsets/tile_start/tile_info/active/n_active exactly as sort_place leaves
+// them for the grouped product, n_rows, the segment table seg_base[E+1] / seg_src[E] (segment
+// i = le*G + s: first sorted row, first entry in s's ids) and ybase[E]: where, in the owner's y,
+// the first row of (this rank, expert e) will be.
 __global__ void __launch_bounds__(EP_INDEX_THREADS)
-ep_index(EpView v, unsigned step, long long budget, int n_tile, int *__restrict__ counts, int *__restrict__ offsets,
+ep_index(EpView v, const unsigned *__restrict__ step_dev, long long budget, int n_tile, int *__restrict__ counts, int *__restrict__ offsets,
 	 int *__restrict__ tile_start, int4 *__restrict__ tile_info, int *__restrict__ active, int *__restrict__ n_active,
 	 int *__restrict__ n_rows_out, int *__restrict__ seg_base, int *__restrict__ seg_src, int *__restrict__ ybase,
 	 unsigned *__restrict__ status)
 {
 	extern __shared__ int sm[];
+	__shared__ int wsum[EP_INDEX_THREADS / 32];
 	const int G = v.n_ranks, E = v.n_expert, NL = v.n_local, fe = v.rank * NL;
-	int *cnt = sm;		   // [G][E]
-	int *tot = cnt + G * E;	   // [E]   rows of expert e over all sources
-	int *loff = tot + E;	   // [NL + 1] exclusive prefix of tot over the local experts
-	int *ltile = loff + NL + 1;  // [NL + 1] same for token tiles
+	int *cnt = sm;		 // [G][E]  rows of source s for expert e
+	int *soff = cnt + G * E; // [G][E]  exclusive prefix of cnt over e: where e starts in s's id list
+	int *tpre = soff + G * E;  // [E + 1] exclusive prefix over e of the rows of e from all sources
 	const int tid = threadIdx.x;
+	const unsigned step = *step_dev;
 
 	bool ok = true;
 	if (tid < G)
 		ok = ep_wait_flag(ep_ptr<unsigned>(v, v.rank, v.off_pub) + tid, step, budget);
 	ok = __syncthreads_and(ok);
+	if (!ok && tid == 0)
+		atomicOr(status, ST_WAIT_TIMEOUT);
+	int n_rows = 0;
 	if (ok) {
 		const int row_max = v.t_max * v.top_k;
 		bool sane = true;
@@ -111,31 +153,26 @@ ep_index(EpView v, unsigned step, long long budget, int n_tile, int *__restrict_
 		}
 		ok = __syncthreads_and(sane);
 		if (ok) {
-			for (int e = tid; e < E; e += EP_INDEX_THREADS) {
-				int t = 0;
-				for (int s = 0; s < G; s++)
-					t += cnt[s * E + e];
-				tot[e] = t;
+			int tot = 0;
+			for (int s = 0; s < G; s++) {
+				const int c = tid < E ? cnt[s * E + tid] : 0;
+				const int pre = ep_block_scan(c, wsum);
+				if (tid < E)
+					soff[s * E + tid] = pre;
+				tot += c;
 			}
+			int all = 0;
+			const int pre = ep_block_scan(tot, wsum, &all);
+			if (tid < E)
+				tpre[tid] = pre;
+			if (tid == 0)
+				tpre[E] = all;
 			__syncthreads();
-			if (tid == 0) {
-				int o = 0, tl = 0;
-				for (int le = 0; le < NL; le++) {
-					loff[le] = o;
-					ltile[le] = tl;
-					o += tot[fe + le];
-					tl += (tot[fe + le] + n_tile - 1) / n_tile;
-				}
-				loff[NL] = o;
-				ltile[NL] = tl;
-			}
-			__syncthreads();
-			ok = (long long)loff[NL] <= v.rows_cap;
+			n_rows = tpre[fe + NL] - tpre[fe];
+			ok = (long long)n_rows <= v.rows_cap;
 		}
 		if (!ok && tid == 0)
 			atomicOr(status, ST_BAD_TILE);
-	} else if (tid == 0) {
-		atomicOr(status, ST_WAIT_TIMEOUT);
 	}
 	if (!ok) {  // an empty layout: the kernels that follow find no work
 		for (int le = tid; le <= NL; le += EP_INDEX_THREADS) {
@@ -157,55 +194,54 @@ ep_index(EpView v, unsigned step, long long budget, int n_tile, int *__restrict_
 		}
 		return;
 	}
-	// layout of the local experts
-	for (int le = tid; le <= NL; le += EP_INDEX_THREADS) {
-		offsets[le] = loff[le];
-		tile_start[le] = ltile[le];
-		if (le < NL) {
-			const int c = tot[fe + le];
-			counts[le] = c;
-			for (int j = 0; j * n_tile < c; j++)
-				tile_info[ltile[le] + j] = make_int4(le, loff[le] + j * n_tile, min(n_tile, c - j * n_tile), 0);
+	// layout of the local experts: thread le
+	const bool local = tid < NL;
+	const int e_loc = fe + tid;
+	const int c_loc = local ? tpre[e_loc + 1] - tpre[e_loc] : 0;
+	const int off_loc = local ? tpre[e_loc] - tpre[fe] : 0;
+	int all_tiles = 0, all_active = 0;
+	const int tile0 = ep_block_scan((c_loc + n_tile - 1) / n_tile, wsum, &all_tiles);
+	const int act0 = ep_block_scan(c_loc > 0 ? 1 : 0, wsum, &all_active);
+	if (local) {
+		counts[tid] = c_loc;
+		offsets[tid] = off_loc;
+		tile_start[tid] = tile0;
+		if (c_loc > 0)
+			active[act0] = tid;
+		for (int j = 0; j * n_tile < c_loc; j++)
+			tile_info[tile0 + j] = make_int4(tid, off_loc + j * n_tile, min(n_tile, c_loc - j * n_tile), 0);
+		// segments (le, s): where they start here, and where they start in the source's id list
+		int b = off_loc;
+		for (int s = 0; s < G; s++) {
+			seg_base[tid * G + s] = b;
+			seg_src[tid * G + s] = soff[s * E + e_loc];
+			b += cnt[s * E + e_loc];
 		}
 	}
 	if (tid == 0) {
-		int a = 0;
-		for (int le = 0; le < NL; le++)
-			if (tot[fe + le] > 0)
-				active[a++] = le;
-		*n_active = a;
-		*n_rows_out = loff[NL];
-		seg_base[NL * G] = loff[NL];
-	}
-	// segments (le, s): where they start here, and where they start in the source's id list
-	for (int i = tid; i < NL * G; i += EP_INDEX_THREADS) {
-		const int le = i / G, s = i % G, e = fe + le;
-		int b = loff[le];
-		for (int s2 = 0; s2 < s; s2++)
-			b += cnt[s2 * E + e];
-		int so = 0;
-		for (int e2 = 0; e2 < e; e2++)
-			so += cnt[s * E + e2];
-		seg_base[i] = b;
-		seg_src[i] = so;
+		offsets[NL] = n_rows;
+		tile_start[NL] = all_tiles;
+		*n_active = all_active;
+		*n_rows_out = n_rows;
+		seg_base[NL * G] = n_rows;
 	}
 	// where the owner of expert e puts this rank's rows of e
-	for (int e = tid; e < E; e += EP_INDEX_THREADS) {
-		const int d = e / NL;
-		int b = 0;
-		for (int e2 = d * NL; e2 < e; e2++)
-			b += tot[e2];
-		for (int s2 = 0; s2 < v.rank; s2++)
-			b += cnt[s2 * E + e];
-		ybase[e] = b;
+	if (tid < E) {
+		int b = tpre[tid] - tpre[tid / NL * NL];
+		for (int s = 0; s < v.rank; s++)
+			b += cnt[s * E + tid];
+		ybase[tid] = b;
 	}
 }
 
 constexpr int EP_SPLIT_THREADS = 256;
+constexpr int EP_SPLIT_F4 = 8;	// float4 loads a lane keeps in flight
 
 // Sorted row p of this rank = row j of segment (le, s): token ids[seg_src + j] / top_k of rank s.
 // Reads that token's fp32 row from rank s and writes the fp16 hi/lo operand row p (same
-// arithmetic and element order as split_rows).  Grid-stride over the rows; n_rows is on the device.
+// arithmetic and element order as split_rows).  One warp per row, EP_SPLIT_F4 16-byte loads in
+// flight per lane (the rows come over NVLink: latency is hidden by loads in flight, not by
+// occupancy); the warps stride over the rows, n_rows is on the device.
 __global__ void __launch_bounds__(EP_SPLIT_THREADS)
 ep_split_rows(EpView v, const int *__restrict__ n_rows_dev, const int *__restrict__ seg_base, const int *__restrict__ seg_src,
 	      __half *__restrict__ hi, __half *__restrict__ lo, __half *__restrict__ q_hi, __half *__restrict__ q_lo,
@@ -220,7 +256,9 @@ ep_split_rows(EpView v, const int *__restrict__ n_rows_dev, const int *__restric
 	}
 	__syncthreads();
 	const int n_rows = *n_rows_dev, H = v.hidden;
-	for (int p = blockIdx.x; p < n_rows; p += gridDim.x) {
+	const int lane = threadIdx.x & 31;
+	const int warps = gridDim.x * (EP_SPLIT_THREADS / 32);
+	for (int p = blockIdx.x * (EP_SPLIT_THREADS / 32) + (threadIdx.x >> 5); p < n_rows; p += warps) {
 		// last segment whose first row is <= p (empty segments share their successor's start)
 		int lo_i = 0, hi_i = n_seg;
 		while (hi_i - lo_i > 1) {
@@ -234,30 +272,39 @@ ep_split_rows(EpView v, const int *__restrict__ n_rows_dev, const int *__restric
 		const int id = __ldcg(ep_ptr<int>(v, s, v.off_ids) + s_src[lo_i] + (p - s_base[lo_i]));
 		const int token = id / v.top_k;
 		if (token < 0 || token >= v.t_max) {
-			if (threadIdx.x == 0)
+			if (lane == 0)
 				atomicOr(status, ST_BAD_TILE);
 			continue;
 		}
-		const float *xr = ep_ptr<float>(v, s, v.off_xs) + (size_t)token * H;
+		const float4 *xr = reinterpret_cast<const float4 *>(ep_ptr<float>(v, s, v.off_xs) + (size_t)token * H);
 		__half2 *hr = reinterpret_cast<__half2 *>(hi + (size_t)p * H);
 		__half2 *lr = reinterpret_cast<__half2 *>(lo + (size_t)p * H);
-		for (int k = threadIdx.x * 4; k < H; k += EP_SPLIT_THREADS * 4) {
-			const float4 x4 = __ldcg(reinterpret_cast<const float4 *>(xr + k));
-			const __half2 h0 = __floats2half2_rn(x4.x, x4.z), h1 = __floats2half2_rn(x4.y, x4.w);
-			const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
-			hr[k / 2] = h0;
-			hr[k / 2 + 1] = h1;
-			lr[k / 2] = __floats2half2_rn(x4.x - f0.x, x4.z - f0.y);
-			lr[k / 2 + 1] = __floats2half2_rn(x4.y - f1.x, x4.w - f1.y);
-			if (q_hi) {
-				float sum = (x4.x + x4.y) + (x4.z + x4.w);
+		for (int c0 = 0; c0 < H / 4; c0 += 32 * EP_SPLIT_F4) {
+			float4 x4[EP_SPLIT_F4];
+#pragma unroll
+			for (int i = 0; i < EP_SPLIT_F4; i++) {
+				const int c = c0 + i * 32 + lane;
+				x4[i] = c < H / 4 ? __ldcg(xr + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+			}
+#pragma unroll
+			for (int i = 0; i < EP_SPLIT_F4; i++) {
+				const int c = c0 + i * 32 + lane;  // float4 index; k = 4 c
+				const __half2 h0 = __floats2half2_rn(x4[i].x, x4[i].z), h1 = __floats2half2_rn(x4[i].y, x4[i].w);
+				const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+				float sum = (x4[i].x + x4[i].y) + (x4[i].z + x4[i].w);
 				sum += __shfl_xor_sync(0xffffffffu, sum, 1);
 				sum += __shfl_xor_sync(0xffffffffu, sum, 2);
 				sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-				if ((threadIdx.x & 7) == 0) {
-					const __half h = __float2half_rn(sum);
-					q_hi[(size_t)p * q_cols + (k >> 5)] = h;
-					q_lo[(size_t)p * q_cols + (k >> 5)] = __float2half_rn(sum - __half2float(h));
+				if (c < H / 4) {
+					hr[2 * c] = h0;
+					hr[2 * c + 1] = h1;
+					lr[2 * c] = __floats2half2_rn(x4[i].x - f0.x, x4[i].z - f0.y);
+					lr[2 * c + 1] = __floats2half2_rn(x4[i].y - f1.x, x4[i].w - f1.y);
+					if (q_hi && (lane & 7) == 0) {
+						const __half h = __float2half_rn(sum);
+						q_hi[(size_t)p * q_cols + (c >> 3)] = h;
+						q_lo[(size_t)p * q_cols + (c >> 3)] = __float2half_rn(sum - __half2float(h));
+					}
 				}
 			}
 		}
@@ -267,12 +314,13 @@ ep_split_rows(EpView v, const int *__restrict__ n_rows_dev, const int *__restric
 // out[t] = (residual[t] +) sum_j w[t][j] * y_owner[row of (t, j)], j ascending, fused multiply-add
 // from zero — the arithmetic of combine_rows, with each row read from its expert's owner.
 __global__ void __launch_bounds__(256)
-ep_combine_rows(EpView v, unsigned step, long long budget, int n_tokens, const int *__restrict__ topk_idx,
+ep_combine_rows(EpView v, const unsigned *__restrict__ step_dev, long long budget, int n_tokens, const int *__restrict__ topk_idx,
 		const float *__restrict__ topk_w, const int *__restrict__ inv, const int *__restrict__ src_off,
 		const int *__restrict__ ybase, const float *__restrict__ residual, float *__restrict__ out,
 		unsigned *__restrict__ status)
 {
 	const int t = blockIdx.x, K = v.top_k, H = v.hidden;
+	const unsigned step = *step_dev;
 	bool ok = true;
 	if ((int)threadIdx.x < v.n_ranks)
 		ok = ep_wait_flag(ep_ptr<unsigned>(v, v.rank, v.off_done) + threadIdx.x, step, budget);
@@ -331,19 +379,19 @@ ep_combine_rows(EpView v, unsigned step, long long budget, int n_tokens, const i
 	}
 }
 
-int launch_ep_signal(tie_cuda_ctx *c, int which, unsigned step)
+int launch_ep_signal(tie_cuda_ctx *c, int which)
 {
-	ep_signal<<<1, 32, 0, c->stream>>>(c->ep.view, which, step);
+	ep_signal<<<1, 32, 0, c->stream>>>(c->ep.view, which, c->ep.step_dev);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
 
-int launch_ep_index(tie_cuda_ctx *c, unsigned step)
+int launch_ep_index(tie_cuda_ctx *c)
 {
 	Scratch &s = c->s;
 	const EpView &v = c->ep.view;
-	const size_t smem = ((size_t)v.n_ranks * v.n_expert + v.n_expert + 2 * (v.n_local + 1)) * sizeof(int);
-	ep_index<<<1, EP_INDEX_THREADS, smem, c->stream>>>(v, step, c->ep.wait_cycles, TC_TOKEN_TILE, s.counts, s.offsets, s.tile_start,
+	const size_t smem = ((size_t)2 * v.n_ranks * v.n_expert + v.n_expert + 1) * sizeof(int);
+	ep_index<<<1, EP_INDEX_THREADS, smem, c->stream>>>(v, c->ep.step_dev, c->ep.wait_cycles, TC_TOKEN_TILE, s.counts, s.offsets, s.tile_start,
 							   s.tile_info, s.active, s.n_active, c->ep.n_rows, c->ep.seg_base,
 							   c->ep.seg_src, c->ep.ybase, s.status);
 	TIE_CUDA_LAUNCHED(c);
@@ -360,10 +408,10 @@ int launch_ep_split_rows(tie_cuda_ctx *c, bool sums)
 	return TIE_CUDA_OK;
 }
 
-int launch_ep_combine(tie_cuda_ctx *c, unsigned step, int n_tokens, const float *residual, float *out)
+int launch_ep_combine(tie_cuda_ctx *c, int n_tokens, const float *residual, float *out)
 {
 	Scratch &s = c->s;
-	ep_combine_rows<<<n_tokens > 0 ? n_tokens : 1, 256, 0, c->stream>>>(c->ep.view, step, c->ep.wait_cycles, n_tokens, s.topk_idx,
+	ep_combine_rows<<<n_tokens > 0 ? n_tokens : 1, 256, 0, c->stream>>>(c->ep.view, c->ep.step_dev, c->ep.wait_cycles, n_tokens, s.topk_idx,
 									     s.topk_w, s.ep_inv, s.ep_offsets, c->ep.ybase, residual,
 									     out, s.status);
 	TIE_CUDA_LAUNCHED(c);

@@ -50,10 +50,10 @@ int launch_tc_swiglu(tie_cuda_ctx *c, const Layer &L, int n_rows, const int *n_r
 // sorted_out: y[p] instead of y[perm[p]]
 int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, float *y, bool sorted_out = false);
 // ep.cu
-int launch_ep_signal(tie_cuda_ctx *c, int which, unsigned step);
-int launch_ep_index(tie_cuda_ctx *c, unsigned step);
+int launch_ep_signal(tie_cuda_ctx *c, int which);
+int launch_ep_index(tie_cuda_ctx *c);
 int launch_ep_split_rows(tie_cuda_ctx *c, bool sums);
-int launch_ep_combine(tie_cuda_ctx *c, unsigned step, int n_tokens, const float *residual, float *out);
+int launch_ep_combine(tie_cuda_ctx *c, int n_tokens, const float *residual, float *out);
 // repack.cu
 int launch_repack_q6k_r8(tie_cuda_ctx *c, const uint8_t *raw, uint8_t *dst, size_t n_rows_total, int nb);
 

@@ -149,9 +149,22 @@ class PeerEpMoeBlock:
         be.ep_attach(handles, moe.EP_PEER_IPC_HANDLES)
         dist.barrier(group=group)  # every rank has mapped every region before the first flag is written
 
-    def forward(self, x, out):
-        self.be.moe_ffn_ep_ptr(0, x, out, x.shape[0], self.moe.DEVICE | self.moe.NO_SYNC)
+    def forward(self, x, out, graph: bool = True):
+        """x, out: device tensors [n_tokens][hidden].  graph: replay the step's launches from a CUDA
+        graph (one per distinct (x, out, n_tokens))."""
+        flags = self.moe.DEVICE | self.moe.NO_SYNC | (self.moe.GRAPH if graph else 0)
+        self.be.moe_ffn_ep_ptr(0, x, out, x.shape[0], flags)
         return out
+
+    def token_buffer(self, torch, n_tokens: int):
+        """A [n_tokens][hidden] fp32 tensor over the part of this rank's region its peers read the
+        tokens from: a step whose x lives there skips the copy into the region."""
+        base, _ = self.be.ep_region()
+
+        class _View:
+            __cuda_array_interface__ = {"shape": (n_tokens, self.be.hidden), "typestr": "<f4", "data": (base, False), "version": 2}
+
+        return torch.as_tensor(_View(), device=torch.device("cuda", self.be.cfg.device))
 
 
 def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
@@ -176,20 +189,36 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
     be.set_stream(stream.cuda_stream)
-    blk = EpMoeBlock(CudaOps(be, torch), torch, dist)
+    exchange = getattr(args, "ep_exchange", "peer")
+    if exchange == "peer":
+        blk = PeerEpMoeBlock(be, dist)
+    else:
+        nccl_blk = EpMoeBlock(CudaOps(be, torch), torch, dist)
+
+        class _Adapter:
+            last = nccl_blk.last
+
+            def forward(self, x, out):
+                return nccl_blk.forward(x, out)
+
+        blk = _Adapter()
 
     x_host = torch.from_numpy(synth.make_x(workloads.BASE_SEED, T, first_token=rank * T)).pin_memory()
     out_host = torch.empty_like(x_host).pin_memory()
-    x_dev = x_host.cuda()
+    if exchange == "peer":
+        x_dev = blk.token_buffer(torch, T)  # the tokens are resident where the peers read them
+        x_dev.copy_(x_host)
+    else:
+        x_dev = x_host.cuda()
     out_dev = torch.empty_like(x_dev)
 
     def step():
         blk.forward(x_dev, out_dev)
 
     def step_e2e():
-        xd = x_host.to(x_dev.device, non_blocking=True)
-        o = blk.forward(xd)
-        out_host.copy_(o, non_blocking=True)
+        x_dev.copy_(x_host, non_blocking=True)
+        blk.forward(x_dev, out_dev)
+        out_host.copy_(out_dev, non_blocking=True)
         torch.cuda.current_stream().synchronize()
 
     for _ in range(args.warmup):
@@ -239,7 +268,10 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
                        "tokens_per_rank": T, "hidden": shape.hidden, "experts": shape.n_expert, "experts_per_rank": n_local,
                        "top_k": shape.top_k, "ffn_dim": shape.ffn_dim, "weights": "Q4_K gate/up, Q6_K down (random valid super-blocks)",
                        "l2": f"weights touched per step per rank ({392 // world} MB) plus exchanged rows; inputs rotate through all-to-all buffers",
-                       "parallelism": f"ep{world}", "collective": "NCCL all-to-all (torch.distributed) for dispatch and combine",
+                       "parallelism": f"ep{world}",
+                       "exchange": ("peer memory: owners load token rows from the sources' HBM, sources load outputs from the owners' "
+                                    "(no collective, no host synchronisation per step)") if exchange == "peer"
+                       else "NCCL all-to-all (torch.distributed) for dispatch and combine",
                        "seed": workloads.BASE_SEED},
             "clocks": clocks,
             "e2e": {"value": T * world / e2e_s, "unit": unit, "h2d_bytes_per_step": T * shape.hidden * 4 * world,
@@ -249,8 +281,8 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
                          "note": "per-kernel roofline is reported by the 1-GPU run; here: whole-block algorithmic TFLOP/s",
                          "algorithmic_tflops": flops / (ms_per_step * 1e-3) / 1e12},
             "cpu_baseline": None,
-            "exchange": {"rows_sent_rank0": blk.last.get("rows_sent"), "rows_received_rank0": blk.last.get("rows_received"),
-                         "bytes_per_row": shape.hidden * 4},
+            "exchange": {"rows_per_rank": T * shape.top_k, "bytes_per_row": shape.hidden * 4,
+                         "remote_fraction": (world - 1) / world},
         }
         print(json.dumps(line), flush=True)
     be.close()
