@@ -79,7 +79,7 @@ def test_exchange_matches_single_process_oracle(tokens, tmp_path):
         assert p.returncode == 0 and "EP_OK" in o, f"rank {r}:\n{o[-3000:]}"
 
 
-# The peer-memory path (csrc/ep.cu) has no row exchange: every rank derives the whole row layout
+# The peer-memory path (csrc/ep.cu) has no collective: every rank derives the whole row layout
 # from the G x E count matrix.  Here two gloo ranks run ep.peer_layout (the host restatement of
 # that index arithmetic) with "peer memory" stood in by all_gather'ed arrays, and the combined
 # result must equal the single-process oracle: an error in the segment / output-position algebra
@@ -105,9 +105,7 @@ x = synth.make_x(workloads.BASE_SEED + 1, T, H, first_token=100 * rank)
 idx, w, _ = P.route(x)
 flat = idx.reshape(-1)
 ids = np.argsort(flat, kind="stable").astype(np.int32)
-inv = np.empty_like(ids); inv[ids] = np.arange(ids.size, dtype=np.int32)
 counts = np.bincount(flat, minlength=E).astype(np.int32)
-my_off = np.concatenate([[0], np.cumsum(counts)])
 
 def gather(obj):
     out = [None] * world
@@ -117,9 +115,11 @@ def gather(obj):
 peer_counts, peer_ids, peer_x = gather(counts), gather(ids), gather(x)   # what the owners read from the sources
 L = ep.peer_layout(np.stack(peer_counts), rank)
 
-# compute: rows of this rank's experts, gathered per segment from their sources
+# compute: rows of this rank's experts, gathered per segment from their sources; every row
+# remembers (source rank, row id there): that is where its output is stored
 n = L["n_rows"]
 rows = np.zeros((n, H), dtype=np.float32); experts = np.zeros(n, dtype=np.int32)
+dst = np.zeros((n, 2), dtype=np.int64)
 for i in range(NL * world):
     le, s = divmod(i, world)
     b, e = int(L["seg_base"][i]), int(L["seg_base"][i + 1])
@@ -128,16 +128,22 @@ for i in range(NL * world):
         rid = peer_ids[s][int(L["seg_src"][i]) + j]
         rows[b + j] = peer_x[s][rid // K]
         experts[b + j] = rank * NL + le
+        dst[b + j] = (s, rid)
 y = P.expert_rows(rows, experts) if n else np.zeros((0, H), dtype=np.float32)
-peer_y = gather(y)                                                       # what the sources read from the owners
+delivered = gather((dst, y))                                             # the owners' stores into the sources' y
 
-# gather: out[t] = sum_j w[t][j] * y_owner[ybase[e] + inv[(t, j)] - my_off[e]], j ascending
+# gather: out[t] = sum_j w[t][j] * y[t*K + j], j ascending, on the rows the owners delivered
+y_mine = np.full((T * K, H), np.nan, dtype=np.float32)
+for d_dst, d_y in delivered:
+    for (s, rid), row in zip(d_dst, d_y):
+        if s == rank:
+            assert np.isnan(y_mine[rid]).all(), "row delivered twice"
+            y_mine[rid] = row
+assert not np.isnan(y_mine).any(), "row never delivered"
 acc = np.zeros((T, H), dtype=np.float32)
 for t in range(T):
     for j in range(K):
-        e = int(idx[t, j]); d = e // NL
-        pos = int(L["ybase"][e]) + int(inv[t * K + j]) - int(my_off[e])
-        acc[t] = (np.float64(w[t, j]) * peer_y[d][pos].astype(np.float64) + acc[t].astype(np.float64)).astype(np.float32)
+        acc[t] = (np.float64(w[t, j]) * y_mine[t * K + j].astype(np.float64) + acc[t].astype(np.float64)).astype(np.float32)
 ref, _, _ = P.moe_ffn(x)
 err = float(workloads.rel_rms_err(acc, ref).max()) if T else 0.0
 assert err < 1e-6, err

@@ -392,7 +392,7 @@ void ep_release(tie_cuda_ctx *c)
 {
 	EpState &ep = c->ep;
 	ep_close_peers(c);
-	void *ptrs[] = {ep.region, ep.n_rows, ep.seg_base, ep.seg_src, ep.ybase, ep.step_dev};
+	void *ptrs[] = {ep.region, ep.n_rows, ep.seg_base, ep.seg_src, ep.row_dst, ep.step_dev};
 	for (void *p : ptrs)
 		if (p)
 			cudaFree(p);
@@ -406,7 +406,8 @@ int ep_region(tie_cuda_ctx *c)
 	if (ep.region)
 		return TIE_CUDA_OK;
 	const int G = c->cfg.ep_size;
-	if (G > EP_MAX_RANKS || c->cfg.n_expert > 256 || c->cfg.max_tokens % G)
+	if (G > EP_MAX_RANKS || c->cfg.n_expert > 256 || c->cfg.max_tokens % G ||
+	    (long long)(c->cfg.max_tokens / G) * c->cfg.top_k >= (1 << 24))
 		return TIE_CUDA_ENOTSUP;
 	EpView &v = ep.view;
 	v = EpView();
@@ -430,7 +431,7 @@ int ep_region(tie_cuda_ctx *c)
 	v.off_done = off;
 	off = align_up(off + EP_MAX_RANKS * sizeof(unsigned), 256);
 	v.off_y = off;
-	off = align_up(off + (size_t)v.rows_cap * v.hidden * sizeof(float), 256);
+	off = align_up(off + (size_t)v.t_max * v.top_k * v.hidden * sizeof(float), 256);
 	TIE_CUDA_TRY(c, cudaMalloc(reinterpret_cast<void **>(&ep.region), off));
 	ep.region_bytes = off;
 	// flags (and everything before y) start at zero; y is written before it is read
@@ -438,7 +439,7 @@ int ep_region(tie_cuda_ctx *c)
 	TRY(dev_alloc(c, &ep.n_rows, 1));
 	TRY(dev_alloc(c, &ep.seg_base, v.n_expert + 1));
 	TRY(dev_alloc(c, &ep.seg_src, v.n_expert));
-	TRY(dev_alloc(c, &ep.ybase, v.n_expert));
+	TRY(dev_alloc(c, &ep.row_dst, (size_t)v.rows_cap));
 	TRY(dev_alloc(c, &ep.step_dev, 1));
 	TIE_CUDA_TRY(c, cudaMemset(ep.step_dev, 0, sizeof(unsigned)));
 	TIE_CUDA_TRY(c, cudaMemset(ep.n_rows, 0, sizeof(int)));
@@ -1011,8 +1012,7 @@ int tie_cuda_ep_publish(tie_cuda_ctx *c, int layer, const float *x, int n_tokens
 		      s.ep_active,
 		      s.ep_n_active,
 		      reinterpret_cast<int *>(ep.region + v.off_ids),
-		      nullptr,
-		      s.ep_inv};
+		      nullptr};
 	TRY(launch_sort(c, s.topk_idx, R, 128, 0, c->cfg.n_expert, b));
 	float *xs = reinterpret_cast<float *>(ep.region + v.off_xs);
 	if (n_tokens && x != xs)
@@ -1043,7 +1043,11 @@ int tie_cuda_ep_compute(tie_cuda_ctx *c, int layer, unsigned flags)
 	prof_mark(c, 4);
 	TRY(launch_tc_swiglu(c, *L, c->sm_count * 8, ep.n_rows));
 	prof_mark(c, 5);
-	TRY(launch_tc_down(c, *L, 0, reinterpret_cast<float *>(ep.region + ep.view.off_y), true));
+	EpDst dst;
+	for (int i = 0; i < ep.view.n_ranks; i++)
+		dst.y[i] = reinterpret_cast<float *>(ep.view.peer[i] + ep.view.off_y);
+	dst.row = ep.row_dst;
+	TRY(launch_tc_down_peer(c, *L, dst));
 	TRY(launch_ep_signal(c, 1));
 	prof_mark(c, 6);
 	c->last_used_tc = true;

@@ -87,8 +87,13 @@ constexpr int EP_MAX_RANKS = 16;
 struct EpView {
 	uint8_t *peer[EP_MAX_RANKS];  // region base of every rank, as mapped into this process
 	size_t off_xs, off_ids, off_counts, off_pub, off_done, off_y;
-	long long rows_cap;  // rows of y (and of this context's scratch)
+	long long rows_cap;  // rows of this context's scratch (the worst case of one step)
 	int n_ranks, rank, n_local, n_expert, top_k, hidden, t_max;
+};
+// Destinations of the down product's rows in an expert-parallel step (tensor.cu, PEER).
+struct EpDst {
+	float *y[EP_MAX_RANKS] = {nullptr};  // per rank: its [t_max * top_k][hidden] output rows
+	const unsigned *row = nullptr;	     // per sorted row: (rank << 24) | row id at that rank
 };
 struct EpState {
 	EpView view = {};
@@ -100,7 +105,8 @@ struct EpState {
 	int step_tokens = -1;	    // tokens of the step between publish and gather, else -1
 	int phase = 0;		    // 0 idle, 1 published, 2 computed
 	long long wait_cycles = 0;  // budget of every flag wait
-	int *n_rows = nullptr, *seg_base = nullptr, *seg_src = nullptr, *ybase = nullptr;
+	int *n_rows = nullptr, *seg_base = nullptr, *seg_src = nullptr;
+	unsigned *row_dst = nullptr;  // [rows_cap] per sorted row: (source rank << 24) | its row id there
 };
 
 }  // namespace tie

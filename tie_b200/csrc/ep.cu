@@ -8,25 +8,28 @@
 //   ids    int  [t_max*K]       its (token, slot) row ids grouped by GLOBAL expert (stable sort)
 //   counts int  [E]             rows per expert from this rank
 //   pub    u32  [G]             pub[s]  = step number, written BY rank s once xs/ids/counts are final
-//   done   u32  [G]             done[d] = step number, written BY rank d once its y rows are final
-//   y      fp32 [rows_cap][H]   outputs of the rows this rank's experts processed
+//   done   u32  [G]             done[d] = step number, written BY rank d once it has delivered its outputs
+//   y      fp32 [t_max*K][H]    expert outputs of THIS rank's rows, in (token, slot) order, written
+//                               by the owners of the experts
 //
-// A step (all ranks call the three phases in the same order with the same step number):
+// A step (all ranks call the three phases in the same order):
 //   publish  route + sort locally into the region, then store the step number into pub[r] of
 //            every peer (release, system scope)
 //   compute  ep_index waits (bounded) for all G pub flags, reads every peer's counts (G x E ints)
 //            and derives the whole row layout from them alone: the rows of local expert le from
 //            source s sit at offsets[le] + sum_{s'<s} cnt[s'][le] + j — the receiver needs no
-//            sort and no id exchange, and the source can compute where its rows' outputs will
-//            be.  ep_split_rows then gathers the token rows straight out of the peers' xs
-//            (plain loads over NVLink) into the fp16 hi/lo operand of the grouped product; the
-//            down product writes y into the region; done[r] is stored to every peer
-//   gather   ep_combine_rows waits (bounded) for the done flags and sums each token's top_k rows
-//            out of the owners' y with the gate weights, in slot order (model_qwen3.c:458-467)
+//            sort.  ep_split_rows then gathers the token rows straight out of the peers' xs
+//            (plain loads over NVLink) into the fp16 hi/lo operand of the grouped product and
+//            notes where each row came from; the down product's epilogue stores every output
+//            row into ITS SOURCE's y (plain stores over NVLink, overlapped with the product);
+//            done[r] is then stored to every peer
+//   gather   ep_combine_rows waits (bounded) for the done flags of all owners and sums each
+//            token's top_k rows of the local y with the gate weights, in slot order
+//            (model_qwen3.c:458-467)
 //
 // Re-use of the region is safe without further flags: a rank's publish of step n+1 follows its
-// own gather of step n in stream order, and a peer's compute of step n+1 (which overwrites y)
-// starts after it has seen every pub flag of step n+1.
+// own gather of step n in stream order, and a peer's compute of step n+1 (which overwrites that
+// rank's y) starts after it has seen every pub flag of step n+1.
 //
 // Peer data is read with ld.global.cg (never through the non-coherent path); flags with
 // ld.acquire.sys / st.release.sys.  Every wait is bounded by a cycle budget; on a time-out the
@@ -119,13 +122,11 @@ __device__ __forceinline__ int ep_block_scan(int val, int *wsum, int *total = nu
 // One CTA; thread i stands for expert i (n_expert <= EP_INDEX_THREADS).  Outputs (this rank's
 // scratch): counts/offsets/tile_start/tile_info/active/n_active exactly as sort_place leaves
 // them for the grouped product, n_rows, the segment table seg_base[E+1] / seg_src[E] (segment
-// i = le*G + s: first sorted row, first entry in s's ids) and ybase[E]: where, in the owner's y,
-// the first row of (this rank, expert e) will be.
+// i = le*G + s: first sorted row, first entry in s's ids).
 __global__ void __launch_bounds__(EP_INDEX_THREADS)
 ep_index(EpView v, const unsigned *__restrict__ step_dev, long long budget, int n_tile, int *__restrict__ counts, int *__restrict__ offsets,
 	 int *__restrict__ tile_start, int4 *__restrict__ tile_info, int *__restrict__ active, int *__restrict__ n_active,
-	 int *__restrict__ n_rows_out, int *__restrict__ seg_base, int *__restrict__ seg_src, int *__restrict__ ybase,
-	 unsigned *__restrict__ status)
+	 int *__restrict__ n_rows_out, int *__restrict__ seg_base, int *__restrict__ seg_src, unsigned *__restrict__ status)
 {
 	extern __shared__ int sm[];
 	__shared__ int wsum[EP_INDEX_THREADS / 32];
@@ -183,10 +184,8 @@ ep_index(EpView v, const unsigned *__restrict__ step_dev, long long budget, int 
 		}
 		for (int i = tid; i <= E; i += EP_INDEX_THREADS) {
 			seg_base[i] = 0;
-			if (i < E) {
+			if (i < E)
 				seg_src[i] = 0;
-				ybase[i] = -1;
-			}
 		}
 		if (tid == 0) {
 			*n_active = 0;
@@ -225,13 +224,6 @@ ep_index(EpView v, const unsigned *__restrict__ step_dev, long long budget, int 
 		*n_rows_out = n_rows;
 		seg_base[NL * G] = n_rows;
 	}
-	// where the owner of expert e puts this rank's rows of e
-	if (tid < E) {
-		int b = tpre[tid] - tpre[tid / NL * NL];
-		for (int s = 0; s < v.rank; s++)
-			b += cnt[s * E + tid];
-		ybase[tid] = b;
-	}
 }
 
 constexpr int EP_SPLIT_THREADS = 256;
@@ -239,13 +231,14 @@ constexpr int EP_SPLIT_F4 = 8;	// float4 loads a lane keeps in flight
 
 // Sorted row p of this rank = row j of segment (le, s): token ids[seg_src + j] / top_k of rank s.
 // Reads that token's fp32 row from rank s and writes the fp16 hi/lo operand row p (same
-// arithmetic and element order as split_rows).  One warp per row, EP_SPLIT_F4 16-byte loads in
+// arithmetic and element order as split_rows); row_dst[p] = (s << 24) | row id tells the down
+// product where the row's output goes.  One warp per row, EP_SPLIT_F4 16-byte loads in
 // flight per lane (the rows come over NVLink: latency is hidden by loads in flight, not by
 // occupancy); the warps stride over the rows, n_rows is on the device.
 __global__ void __launch_bounds__(EP_SPLIT_THREADS)
 ep_split_rows(EpView v, const int *__restrict__ n_rows_dev, const int *__restrict__ seg_base, const int *__restrict__ seg_src,
 	      __half *__restrict__ hi, __half *__restrict__ lo, __half *__restrict__ q_hi, __half *__restrict__ q_lo,
-	      int q_cols, unsigned *__restrict__ status)
+	      int q_cols, unsigned *__restrict__ row_dst, unsigned *__restrict__ status)
 {
 	__shared__ int s_base[257], s_src[256];
 	const int n_seg = v.n_local * v.n_ranks;  // = n_expert
@@ -271,11 +264,15 @@ ep_split_rows(EpView v, const int *__restrict__ n_rows_dev, const int *__restric
 		const int s = lo_i % v.n_ranks;
 		const int id = __ldcg(ep_ptr<int>(v, s, v.off_ids) + s_src[lo_i] + (p - s_base[lo_i]));
 		const int token = id / v.top_k;
-		if (token < 0 || token >= v.t_max) {
-			if (lane == 0)
+		if (id < 0 || token >= v.t_max) {
+			if (lane == 0) {
 				atomicOr(status, ST_BAD_TILE);
+				row_dst[p] = (unsigned)v.rank << 24;  // somewhere harmless: row 0 of this rank's own y
+			}
 			continue;
 		}
+		if (lane == 0)
+			row_dst[p] = ((unsigned)s << 24) | (unsigned)id;
 		const float4 *xr = reinterpret_cast<const float4 *>(ep_ptr<float>(v, s, v.off_xs) + (size_t)token * H);
 		__half2 *hr = reinterpret_cast<__half2 *>(hi + (size_t)p * H);
 		__half2 *lr = reinterpret_cast<__half2 *>(lo + (size_t)p * H);
@@ -311,12 +308,11 @@ ep_split_rows(EpView v, const int *__restrict__ n_rows_dev, const int *__restric
 	}
 }
 
-// out[t] = (residual[t] +) sum_j w[t][j] * y_owner[row of (t, j)], j ascending, fused multiply-add
-// from zero — the arithmetic of combine_rows, with each row read from its expert's owner.
+// out[t] = (residual[t] +) sum_j w[t][j] * y[t*top_k + j], j ascending, fused multiply-add from
+// zero — the arithmetic of combine_rows — once every owner has delivered (done flags).
 __global__ void __launch_bounds__(256)
-ep_combine_rows(EpView v, const unsigned *__restrict__ step_dev, long long budget, int n_tokens, const int *__restrict__ topk_idx,
-		const float *__restrict__ topk_w, const int *__restrict__ inv, const int *__restrict__ src_off,
-		const int *__restrict__ ybase, const float *__restrict__ residual, float *__restrict__ out,
+ep_combine_rows(EpView v, const unsigned *__restrict__ step_dev, long long budget, int n_tokens,
+		const float *__restrict__ topk_w, const float *__restrict__ residual, float *__restrict__ out,
 		unsigned *__restrict__ status)
 {
 	const int t = blockIdx.x, K = v.top_k, H = v.hidden;
@@ -332,36 +328,17 @@ ep_combine_rows(EpView v, const unsigned *__restrict__ step_dev, long long budge
 	}
 	if (t >= n_tokens)  // a rank without tokens only waits
 		return;
+	const float *y = ep_ptr<float>(v, v.rank, v.off_y) + (size_t)t * K * H;
 	float wj[MAX_TOP_K];
-	const float *yrow[MAX_TOP_K];
-	bool bad = false;
 #pragma unroll
-	for (int j = 0; j < MAX_TOP_K; j++) {
-		wj[j] = 0.f;
-		yrow[j] = nullptr;
-		if (j < K) {
-			const int e = topk_idx[(size_t)t * K + j];
-			const int d = e / v.n_local;
-			const long long pos = (long long)ybase[e] + inv[(size_t)t * K + j] - src_off[e];
-			if (ybase[e] < 0 || pos < 0 || pos >= v.rows_cap) {
-				bad = true;
-			} else {
-				wj[j] = topk_w[(size_t)t * K + j];
-				yrow[j] = ep_ptr<float>(v, d, v.off_y) + (size_t)pos * H;
-			}
-		}
-	}
-	if (bad) {
-		if (threadIdx.x == 0)
-			atomicOr(status, ST_BAD_TILE);
-		return;
-	}
+	for (int j = 0; j < MAX_TOP_K; j++)
+		wj[j] = j < K ? topk_w[(size_t)t * K + j] : 0.f;
 	for (int k = threadIdx.x * 4; k < H; k += blockDim.x * 4) {
 		float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
 		for (int j = 0; j < MAX_TOP_K; j++) {
 			if (j < K) {
-				const float4 y4 = __ldcg(reinterpret_cast<const float4 *>(yrow[j] + k));
+				const float4 y4 = __ldcg(reinterpret_cast<const float4 *>(y + (size_t)j * H + k));
 				acc.x = __fmaf_rn(wj[j], y4.x, acc.x);
 				acc.y = __fmaf_rn(wj[j], y4.y, acc.y);
 				acc.z = __fmaf_rn(wj[j], y4.z, acc.z);
@@ -393,7 +370,7 @@ int launch_ep_index(tie_cuda_ctx *c)
 	const size_t smem = ((size_t)2 * v.n_ranks * v.n_expert + v.n_expert + 1) * sizeof(int);
 	ep_index<<<1, EP_INDEX_THREADS, smem, c->stream>>>(v, c->ep.step_dev, c->ep.wait_cycles, TC_TOKEN_TILE, s.counts, s.offsets, s.tile_start,
 							   s.tile_info, s.active, s.n_active, c->ep.n_rows, c->ep.seg_base,
-							   c->ep.seg_src, c->ep.ybase, s.status);
+							   c->ep.seg_src, s.status);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
@@ -403,7 +380,8 @@ int launch_ep_split_rows(tie_cuda_ctx *c, bool sums)
 	Scratch &s = c->s;
 	ep_split_rows<<<c->sm_count * 8, EP_SPLIT_THREADS, 0, c->stream>>>(c->ep.view, c->ep.n_rows, c->ep.seg_base, c->ep.seg_src,
 									    s.xs_hi, s.xs_lo, sums ? s.xq_hi : nullptr,
-									    sums ? s.xq_lo : nullptr, xq_cols(c->cfg.hidden), s.status);
+									    sums ? s.xq_lo : nullptr, xq_cols(c->cfg.hidden), c->ep.row_dst,
+									    s.status);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
@@ -411,9 +389,8 @@ int launch_ep_split_rows(tie_cuda_ctx *c, bool sums)
 int launch_ep_combine(tie_cuda_ctx *c, int n_tokens, const float *residual, float *out)
 {
 	Scratch &s = c->s;
-	ep_combine_rows<<<n_tokens > 0 ? n_tokens : 1, 256, 0, c->stream>>>(c->ep.view, c->ep.step_dev, c->ep.wait_cycles, n_tokens, s.topk_idx,
-									     s.topk_w, s.ep_inv, s.ep_offsets, c->ep.ybase, residual,
-									     out, s.status);
+	ep_combine_rows<<<n_tokens > 0 ? n_tokens : 1, 256, 0, c->stream>>>(c->ep.view, c->ep.step_dev, c->ep.wait_cycles, n_tokens,
+									     s.topk_w, residual, out, s.status);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }

@@ -19,7 +19,6 @@ int launch_router_rows(tie_cuda_ctx *c, const float *x, const float *w, int n_ro
 struct SortBufs {
 	int *counts, *offsets, *tile_start, *active, *n_active, *perm;
 	int4 *tile_info;  // optional: one entry per token tile (expert, first sorted row, rows, 0)
-	int *inv = nullptr;  // optional: row id -> sorted position
 };
 int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile);
 int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile, int first_expert, int n_expert,
@@ -49,6 +48,7 @@ int launch_tc_gate_up(tie_cuda_ctx *c, const Layer &L, int n_rows);
 int launch_tc_swiglu(tie_cuda_ctx *c, const Layer &L, int n_rows, const int *n_rows_dev = nullptr);
 // sorted_out: y[p] instead of y[perm[p]]
 int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, float *y, bool sorted_out = false);
+int launch_tc_down_peer(tie_cuda_ctx *c, const Layer &L, const EpDst &dst);
 // ep.cu
 int launch_ep_signal(tie_cuda_ctx *c, int which);
 int launch_ep_index(tie_cuda_ctx *c);

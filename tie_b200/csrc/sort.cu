@@ -51,8 +51,7 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_place(const int *__restrict
 							   int n_local, const int *__restrict__ counts, int n_tile,
 							   int *__restrict__ offsets, int *__restrict__ tile_start,
 							   int *__restrict__ active, int *__restrict__ n_active,
-							   int *__restrict__ perm, int4 *__restrict__ tile_info,
-							   int *__restrict__ inv)
+							   int *__restrict__ perm, int4 *__restrict__ tile_info)
 {
 	__shared__ int s_off, s_tiles;
 	__shared__ int wcnt[SORT_THREADS / 32];
@@ -136,11 +135,8 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_place(const int *__restrict
 		int pos = base + before;
 #pragma unroll
 		for (int i = 0; i < SORT_RPT; i++)
-			if (m & (1u << i)) {
-				if (inv)
-					inv[rt + i] = pos;
+			if (m & (1u << i))
 				perm[pos++] = rt + i;
-			}
 		base += total;
 		__syncthreads();
 	}
@@ -152,7 +148,7 @@ int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile, 
 	sort_count<<<n_expert, SORT_THREADS, 0, c->stream>>>(row_expert, n_rows, first_expert, n_expert, b.counts, c->s.status);
 	TIE_CUDA_LAUNCHED(c);
 	sort_place<<<n_expert, SORT_THREADS, 0, c->stream>>>(row_expert, n_rows, first_expert, n_expert, b.counts, n_tile,
-							      b.offsets, b.tile_start, b.active, b.n_active, b.perm, b.tile_info, b.inv);
+							      b.offsets, b.tile_start, b.active, b.n_active, b.perm, b.tile_info);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }

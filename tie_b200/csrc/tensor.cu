@@ -331,7 +331,11 @@ struct Expander<W_Q6K_R8> {
 // Every role walks the same sequence of "phases": per work item the min phase (Q4_K; two ring
 // stages: hi and lo tiles of dmin*m) and then the super-blocks (four ring stages each).  Phase
 // number g selects the accumulator buffer (g % 4) and the MMA issuer (g % 2).
-template <WKind KIND, bool RAW>
+//
+// PEER (expert parallelism over peer memory, down product only): sorted row p belongs to row
+// dst.row[p] & 0xFFFFFF of rank dst.row[p] >> 24 and is stored there, into that rank's memory
+// (dst.y[rank], plain stores over NVLink, 128 contiguous bytes per warp and row).
+template <WKind KIND, bool RAW, bool PEER = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant__ CUtensorMap tm32,
 		const __grid_constant__ CUtensorMap tm64, const __grid_constant__ CUtensorMap tq16,
@@ -339,8 +343,9 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 		const __grid_constant__ CUtensorMap tw0, const __grid_constant__ CUtensorMap tw1, const uint8_t *__restrict__ w0,
 		const uint8_t *__restrict__ w1, size_t expert_stride, int k_dim, const int4 *__restrict__ tile_info,
 		const int *__restrict__ tile_start, int n_local, int m_tiles, float *__restrict__ y, const int *__restrict__ perm,
-		int out_stride, float out_scale, unsigned *__restrict__ status, int rows_per_matrix)
+		int out_stride, float out_scale, unsigned *__restrict__ status, int rows_per_matrix, const EpDst dst)
 {
+	static_assert(!(RAW && PEER), "peer destinations exist for the down product only");
 	using Sm = TcSmem<KIND>;
 	constexpr bool Q4 = KIND == W_Q4K;
 	extern __shared__ uint8_t smem_raw[];
@@ -657,8 +662,12 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 			const long long tst = TCT_NOW();
 			// rows of this work item: lanes hold consecutive output columns (coalesced 128-byte stores)
 			int rid = 0;
-			if (!RAW && lane < ntok && tok0 + lane < item.n_valid)
-				rid = perm ? perm[item.row0 + tok0 + lane] : item.row0 + tok0 + lane;
+			if (!RAW && lane < ntok && tok0 + lane < item.n_valid) {
+				if (PEER)
+					rid = (int)dst.row[item.row0 + tok0 + lane];
+				else
+					rid = perm ? perm[item.row0 + tok0 + lane] : item.row0 + tok0 + lane;
+			}
 #pragma unroll
 			for (int j = 0; j < TC_NT / 2; j++) {
 				const int n = tok0 + j;
@@ -666,6 +675,8 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 				if (j < ntok && n < item.n_valid) {
 					if (RAW)
 						y[(size_t)(item.row0 + n) * out_stride + (size_t)item.mat_sel * rows_per_matrix + mrow] = acc[j];
+					else if (PEER)
+						dst.y[(unsigned)rj >> 24][(size_t)(rj & 0xFFFFFF) * out_stride + mrow] = acc[j] * out_scale;
 					else
 						y[(size_t)rj * out_stride + mrow] = acc[j] * out_scale;
 				}
@@ -1008,24 +1019,28 @@ int tc_setup(tie_cuda_ctx *c)
 	TC_ATTR(W_Q6K_R8, false);
 	TC_ATTR(W_Q6K_R8, true);
 #undef TC_ATTR
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_sb<W_Q4K, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+					     TcSmem<W_Q4K>::SMEM));
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_sb<W_Q6K_R8, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+					     TcSmem<W_Q6K_R8>::SMEM));
 	c->tmaps_ok = true;
 	return TIE_CUDA_OK;
 }
 
 // arr: 0 = the split inputs x (gate/up), 1 = the split activations h (down).
-template <WKind KIND, bool RAW>
+template <WKind KIND, bool RAW, bool PEER = false>
 static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1, int arr, float *y, float out_scale,
-		       bool sorted_out = false)
+		       bool sorted_out = false, const EpDst *dst = nullptr)
 {
 	Scratch &s = c->s;
 	const int m_tiles = (RAW ? 2 : 1) * t0.rows / TC_BM;
 	const CUtensorMap &w0m = t0.map;
 	const CUtensorMap &w1m = t1 ? t1->map : t0.map;
-	grouped_gemm_sb<KIND, RAW><<<c->sm_count, TC_THREADS, TcSmem<KIND>::SMEM, c->stream>>>(
+	grouped_gemm_sb<KIND, RAW, PEER><<<c->sm_count, TC_THREADS, TcSmem<KIND>::SMEM, c->stream>>>(
 		c->tmap[arr * 3], c->tmap[arr * 3 + 1], c->tmap[arr * 3 + 2], c->tmap[(2 + arr) * 3], c->tmap[(2 + arr) * 3 + 1],
 		c->tmap[(2 + arr) * 3 + 2], w0m, w1m, t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride,
-		t0.k, s.tile_info, s.tile_start, c->n_local, m_tiles, y, sorted_out ? nullptr : s.perm, RAW ? 2 * t0.rows : t0.rows, out_scale, s.status,
-		t0.rows);
+		t0.k, s.tile_info, s.tile_start, c->n_local, m_tiles, y, sorted_out ? nullptr : s.perm, RAW ? 2 * t0.rows : t0.rows,
+		out_scale, s.status, t0.rows, dst ? *dst : EpDst());
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
@@ -1067,6 +1082,14 @@ int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, float *y, bool s
 	if (L.down.kind == W_Q4K)
 		return launch_tc_t<W_Q4K, false>(c, L.down, nullptr, 1, y, 1.0f / TC_H_SCALE, sorted_out);
 	return launch_tc_t<W_Q6K_R8, false>(c, L.down, nullptr, 1, y, 1.0f / TC_H_SCALE, sorted_out);
+}
+
+// The down product of an expert-parallel step: row p goes to the rank and row dst->row[p] names.
+int launch_tc_down_peer(tie_cuda_ctx *c, const Layer &L, const EpDst &dst)
+{
+	if (L.down.kind == W_Q4K)
+		return launch_tc_t<W_Q4K, false, true>(c, L.down, nullptr, 1, nullptr, 1.0f / TC_H_SCALE, true, &dst);
+	return launch_tc_t<W_Q6K_R8, false, true>(c, L.down, nullptr, 1, nullptr, 1.0f / TC_H_SCALE, true, &dst);
 }
 
 }  // namespace tie

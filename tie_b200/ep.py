@@ -109,7 +109,8 @@ def peer_layout(counts, rank: int, n_tile: int = 64):
       offsets[NL+1]   first sorted row of each local expert (rows ordered by expert, then source)
       tiles           (local expert, first row, rows) per token tile of n_tile rows
       seg_base[NL*G+1], seg_src[NL*G]  segment le*G+s: its first row here, its first entry in s's id list
-      ybase[E]        where the owner of expert e puts this rank's rows of e (row index in the owner's y)
+    Row j of segment (le, s) is row id ids_s[seg_src + j] of rank s: its token row is read from
+    there and its output is stored there, at that row id.
     """
     counts = np.asarray(counts, dtype=np.int64)
     G, E = counts.shape
@@ -127,12 +128,7 @@ def peer_layout(counts, rank: int, n_tile: int = 64):
             seg_base[le * G + s] = offsets[le] + counts[:s, fe + le].sum()
             seg_src[le * G + s] = src_off[s, fe + le]
     seg_base[NL * G] = offsets[NL]
-    ybase = np.zeros(E, dtype=np.int64)
-    for e in range(E):
-        d = e // NL
-        ybase[e] = tot[d * NL:e].sum() + counts[:rank, e].sum()
-    return {"offsets": offsets, "tiles": tiles, "seg_base": seg_base, "seg_src": seg_src, "ybase": ybase,
-            "n_rows": int(offsets[NL])}
+    return {"offsets": offsets, "tiles": tiles, "seg_base": seg_base, "seg_src": seg_src, "n_rows": int(offsets[NL])}
 
 
 class PeerEpMoeBlock:
