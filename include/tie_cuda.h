@@ -163,9 +163,10 @@ int tie_cuda_moe_ep_combine(tie_cuda_ctx *c, const float *y_sorted, const float 
  * One context per GPU (ep_rank / ep_size in the config; max_tokens = ep_size x the tokens one rank
  * brings per step, so that the scratch holds the worst case of every row landing on one rank).
  * Dispatch and combine are not collectives here: every rank exposes one region of its HBM, the
- * owners' kernels read token rows straight out of the sources' regions and the sources read the
- * expert outputs straight out of the owners' (plain loads over NVLink); ranks synchronise through
- * step-numbered flags they store into each other's regions.  No host synchronisation per step.
+ * owners' kernels read token rows straight out of the sources' regions and the down product
+ * stores every output row straight into its source's region (plain loads and stores over
+ * NVLink); ranks synchronise through step-numbered flags they store into each other's regions.
+ * No host synchronisation per step.
  *
  * Set-up, once, collectively: tie_cuda_ep_ipc_handle() on every rank, exchange the 64-byte
  * handles by any host channel, tie_cuda_ep_attach(handles, ep_size, TIE_CUDA_EP_PEER_IPC_HANDLES).
@@ -177,9 +178,13 @@ int tie_cuda_moe_ep_combine(tie_cuda_ctx *c, const float *y_sorted, const float 
  *   tie_cuda_ep_publish  routes x [n_tokens][hidden] (0 <= n_tokens <= max_tokens / ep_size, may
  *                        differ between ranks), sorts its rows by expert and announces them
  *   tie_cuda_ep_compute  waits for every rank's announcement, gathers the rows of this rank's
- *                        experts from their sources, runs gate/up, SwiGLU, down
+ *                        experts from their sources, runs gate/up, SwiGLU, down (outputs land at
+ *                        their sources)
  *   tie_cuda_ep_gather   waits for every owner, out[t] = (residual[t] +) sum_j w[t][j] * y(t, j)
- * tie_cuda_moe_ffn_ep is the three in a row.  Kernels of different ranks wait on one another, so
+ * tie_cuda_moe_ffn_ep is the three in a row; with TIE_CUDA_GRAPH the whole step is replayed from a
+ * CUDA graph (the step number advances on the device).  A step whose x is the start of this
+ * rank's region (tie_cuda_ep_region) skips the copy into it.
+ * Kernels of different ranks wait on one another, so
  * ranks that share ONE GPU must enqueue phase by phase on one stream (all publishes, then all
  * computes, then all gathers) — a wait is then always already satisfied; on separate GPUs the
  * ranks run freely.  Every wait is bounded (tie_cuda_ep_set_timeout_ms, default 5 s): a rank that

@@ -16,6 +16,8 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "_ref", "libtie_ref.so")
 LIB_NATIVE_PATH = os.path.join(_HERE, "_ref", "libtie_ref_native.so")
+# the same sources + the reference-side glue of tie_b200/dropin, linked with tie_b200/libtie_cuda.so
+LIB_DROPIN_PATH = os.path.join(_HERE, "_ref", "libtie_ref_dropin.so")
 
 
 def available(path: str = LIB_PATH) -> bool:
@@ -47,6 +49,12 @@ class RefMoe:
         L.tieref_rms_norm.argtypes = [vp, vp, vp, i32, f32]
         L.tieref_time_moe_ffn.restype = ctypes.c_double
         L.tieref_time_moe_ffn.argtypes = [vp, i32, vp, vp]
+        if hasattr(L, "tieref_dropin_load"):
+            L.tieref_dropin_load.restype = i32
+            L.tieref_dropin_load.argtypes = [i32, i32]
+            L.tieref_dropin_moe_ffn.restype = i32
+            L.tieref_dropin_moe_ffn.argtypes = [vp, i32, vp]
+            L.tieref_dropin_unload.restype = None
         self.L = L
         self.hidden, self.n_expert, self.top_k, self.ffn_dim = hidden, n_expert, top_k, ffn_dim
         if n_threads is None:
@@ -118,6 +126,25 @@ class RefMoe:
         if rc:
             raise RuntimeError(f"tieref_route_lfm2 failed: {rc}")
         return idx, w, scores
+
+    # -- the drop-in library only (LIB_DROPIN_PATH): the reference's structures driving the GPU backend --
+    def dropin_load(self, device: int = 0, max_tokens: int = 512):
+        """The glue's model_load hook on the layer given to set_layer (tie_cuda_qwen3_load)."""
+        rc = self.L.tieref_dropin_load(device, max_tokens)
+        if rc:
+            raise RuntimeError(f"tieref_dropin_load failed: {rc}")
+
+    def dropin_moe_ffn(self, x: np.ndarray) -> np.ndarray:
+        """The is_moe branch through the glue (tie_cuda_qwen3_moe_ffn): ctx->mem.normed_ffn_input -> ffn_down_output."""
+        x = np.ascontiguousarray(x, dtype=np.float32)
+        out = np.empty_like(x)
+        rc = self.L.tieref_dropin_moe_ffn(x.ctypes.data, x.shape[0], out.ctypes.data)
+        if rc:
+            raise RuntimeError(f"tieref_dropin_moe_ffn failed: {rc}")
+        return out
+
+    def dropin_unload(self):
+        self.L.tieref_dropin_unload()
 
     def moe_block_inplace(self, hidden: np.ndarray, eps: float = 1e-6):
         """hidden += MoE(RMSNorm(hidden)); returns (new_hidden, normed, ffn_out, idx, w)."""

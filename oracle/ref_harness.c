@@ -281,3 +281,48 @@ double tieref_time_moe_ffn(const float *x, int n_tokens, const float *router_bia
 	clock_gettime(CLOCK_MONOTONIC, &t1);
 	return (double)(t1.tv_sec - t0.tv_sec) + 1e-9 * (double)(t1.tv_nsec - t0.tv_nsec);
 }
+
+#ifdef TIE_DROPIN
+/*
+ * The drop-in proved against the reference's own structures: the same TIEContext / Model /
+ * LayerWeights the functions above drive, handed to the glue a maintainer would add to the
+ * reference tree (tie_b200/dropin/tie_cuda_qwen3.c).  Built only into
+ * oracle/_ref/libtie_ref_dropin.so, which links libtie_cuda.so.
+ */
+#include "tie_cuda_qwen3.h"
+
+static tie_cuda_ctx *g_cuda;
+static int g_cuda_cap;
+
+/* model_load's hook: device context + one-time upload of the layer set by tieref_set_layer. */
+int tieref_dropin_load(int device, int max_tokens)
+{
+	if (!g.ready || !g.layer.ffn_gate_exps.mem.data)
+		return -100;
+	if (g_cuda) {
+		tie_cuda_destroy(g_cuda);
+		g_cuda = NULL;
+	}
+	g_cuda_cap = max_tokens;
+	return tie_cuda_qwen3_load(&g.ctx, &g_cuda, device, max_tokens);
+}
+
+void tieref_dropin_unload(void)
+{
+	if (g_cuda)
+		tie_cuda_destroy(g_cuda);
+	g_cuda = NULL;
+}
+
+/* The is_moe branch through the glue: x is placed in ctx->mem.normed_ffn_input, the result is
+ * taken from ctx->mem.ffn_down_output (the buffers transformer_layer_qwen3 uses). */
+int tieref_dropin_moe_ffn(const float *x, int n_tokens, float *out)
+{
+	struct TIEContext *ctx = &g.ctx;
+	if (!g_cuda || n_tokens > g_cuda_cap)
+		return -100;
+	ctx->mem.normed_ffn_input = (MemType){.type = GGML_TYPE_F32, .data = (void *)x};
+	ctx->mem.ffn_down_output = (MemType){.type = GGML_TYPE_F32, .data = (void *)out};
+	return tie_cuda_qwen3_moe_ffn(ctx, g_cuda, 0, n_tokens);
+}
+#endif /* TIE_DROPIN */

@@ -86,3 +86,19 @@ def test_product_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".c", ".h")):
                 txt = open(os.path.join(base, f)).read()
                 assert "oracle" not in txt.replace("moe_oracle", "").lower() or f == "workloads.py" and False, (base, f)
+
+
+def test_reference_side_glue_compiles_against_the_reference_headers(tmp_path):
+    """tie_b200/dropin/tie_cuda_qwen3.c is written against the reference's own structures
+    (struct TIEContext, Model, LayerWeights, MemType): where the reference tree is present it must
+    compile as plain C with the reference's flags.  (Elsewhere the prebuilt
+    oracle/_ref/libtie_ref_dropin.so is what travels.)"""
+    ref_dir = os.environ.get("TIE_REF_DIR", "/root/reference")
+    if not os.path.exists(os.path.join(ref_dir, "engine.h")):
+        pytest.skip("reference tree not present")
+    src = os.path.join(ROOT, "tie_b200", "dropin", "tie_cuda_qwen3.c")
+    obj = tmp_path / "glue.o"
+    subprocess.check_call(["gcc", "-std=gnu11", "-Wall", "-Werror", "-Wno-pointer-sign", "-funsigned-char", "-c", src,
+                           "-I", ref_dir, "-I", os.path.join(ROOT, "include"), "-I", os.path.dirname(src), "-o", str(obj)])
+    syms = subprocess.check_output(["nm", "--defined-only", str(obj)], text=True)
+    assert "tie_cuda_qwen3_load" in syms and "tie_cuda_qwen3_moe_ffn" in syms

@@ -18,7 +18,6 @@ from __future__ import annotations
 
 import json
 import os
-import time
 
 import numpy as np
 
@@ -180,7 +179,9 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
     T = tokens_per_rank
     n_local = shape.n_expert // world
     layer = synth.make_layer(workloads.BASE_SEED, shape, first_expert=rank * n_local, n_local_expert=n_local)
-    be = moe.MoeBackend(max_tokens=T * world, device=local_rank, silu_table=moe.silu_table_default(), ep_rank=rank, ep_size=world)
+    STRONG_TOKENS = 8192  # side run: BASELINE's expert-parallel prefill, 8192 tokens in total whatever N
+    cap = max(T * world, STRONG_TOKENS)
+    be = moe.MoeBackend(max_tokens=cap, device=local_rank, silu_table=moe.silu_table_default(), ep_rank=rank, ep_size=world)
     be.upload_layer(0, layer)
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
@@ -239,17 +240,38 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
     clocks = sampler.stop() if rank == 0 else None
     total_ms = float(ms.item())
 
+    def timed(fn, n):
+        """ms per call of fn over n calls: CUDA events on this rank's stream, max over ranks."""
+        dist.barrier()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) / n
+
     for _ in range(args.warmup):
         step_e2e()
-    dist.barrier()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        step_e2e()
-    t1 = torch.tensor([time.perf_counter() - t0], device="cuda")
-    dist.all_reduce(t1, op=dist.ReduceOp.MAX)
-    e2e_s = float(t1.item()) / args.steps
+    e2e_s = timed(step_e2e, args.steps) * 1e-3
     be.synchronize()
+
+    strong = None
+    if exchange == "peer" and not getattr(args, "no_extra", False) and STRONG_TOKENS % world == 0:
+        T2 = STRONG_TOKENS // world
+        x2 = blk.token_buffer(torch, T2)
+        x2.copy_(torch.from_numpy(synth.make_x(workloads.BASE_SEED, T2, first_token=rank * T2)))
+        o2 = torch.empty_like(x2)
+        for _ in range(3):
+            blk.forward(x2, o2)
+        ms2 = timed(lambda: blk.forward(x2, o2), max(5, args.steps // 2))
+        strong = {"tokens": STRONG_TOKENS, "tokens_per_rank": T2, "scaling": "strong", "ms_per_step": ms2,
+                  "tokens_per_s": STRONG_TOKENS / (ms2 * 1e-3),
+                  "algorithmic_tflops": workloads.algorithmic_flops(shape, STRONG_TOKENS) / (ms2 * 1e-3) / 1e12}
+        be.synchronize()
 
     if rank == 0:
         peaks = load_peaks()
@@ -263,9 +285,10 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
             "config": {"workload": "prefill_512_tokens_per_rank_one_block_expert_parallel", "tokens": T * world,
                        "tokens_per_rank": T, "hidden": shape.hidden, "experts": shape.n_expert, "experts_per_rank": n_local,
                        "top_k": shape.top_k, "ffn_dim": shape.ffn_dim, "weights": "Q4_K gate/up, Q6_K down (random valid super-blocks)",
-                       "l2": f"weights touched per step per rank ({392 // world} MB) plus exchanged rows; inputs rotate through all-to-all buffers",
+                       "l2": f"weights touched per step per rank: {392 // world} MB plus {T * shape.top_k * shape.hidden * 8 // 2**20} MB of rows "
+                             "(larger than L2 from N = 1 to 2; at N >= 4 the weights of a rank fit in L2, as they would in deployment)",
                        "parallelism": f"ep{world}",
-                       "exchange": ("peer memory: owners load token rows from the sources' HBM, sources load outputs from the owners' "
+                       "exchange": ("peer memory: owners load token rows from the sources' HBM and store output rows into the sources' "
                                     "(no collective, no host synchronisation per step)") if exchange == "peer"
                        else "NCCL all-to-all (torch.distributed) for dispatch and combine",
                        "seed": workloads.BASE_SEED},
@@ -278,7 +301,11 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
                          "algorithmic_tflops": flops / (ms_per_step * 1e-3) / 1e12},
             "cpu_baseline": None,
             "exchange": {"rows_per_rank": T * shape.top_k, "bytes_per_row": shape.hidden * 4,
-                         "remote_fraction": (world - 1) / world},
+                         "remote_fraction": (world - 1) / world,
+                         "nvlink_bytes_per_rank_and_direction": int(T * shape.top_k * shape.hidden * 4 * (world - 1) / world),
+                         "nvlink_floor_us": 2 * T * shape.top_k * shape.hidden * 4 * (world - 1) / world / 770e9 * 1e6,
+                         "note": "floor = dispatch + combine bytes of one rank / measured 770 GB/s per direction"},
+            "extra": {"prefill_8192_tokens_total": strong},
         }
         print(json.dumps(line), flush=True)
     be.close()
