@@ -214,6 +214,15 @@ int tie_cuda_make_current(tie_cuda_ctx *c);
 /* Upload a stand-alone weight tensor (rows of in_dim inputs; F32, Q4_K or Q6_K) so that the rows
  * below can find it by host address (model_load_tensor, model.c:198-235, for non-MoE tensors). */
 int tie_cuda_register_tensor(tie_cuda_ctx *c, const void *host_ptr, size_t n_bytes, int ggml_type, int in_dim);
+/* dispatch_mat_mat (math_dispatch.c:304-370: O[i] = W . X[i] for the batch_len rows of X, the
+ * reference runs its mat-vec row kernels per row) for a Q4_K / Q6_K tensor registered with
+ * tie_cuda_register_tensor, on the tensor-core kernel of the expert products (the tensor is one
+ * "expert" owning every row) — the dense FFN and attention projections of a prompt batch.
+ * W: the registered host address; X [batch_len][in_dim], O [batch_len][out_dim] fp32, host or
+ * device per flags.  Supported: in_dim equal to the context's hidden or ffn_dim, out_dim a
+ * multiple of 128, batch_len <= max_tokens * top_k; otherwise TIE_CUDA_ENOTSUP / _ETOOBIG. */
+int tie_cuda_mat_mat(tie_cuda_ctx *c, const void *W, const float *X, float *O, int batch_len, int in_dim, int out_dim,
+		     unsigned flags);
 void tie_cuda_mat_vec_row_f32_q4k_f32(const void *X, const void *W, void *O, int in_dim, int start_row, int end_row);
 void tie_cuda_mat_vec_row_f32_q6k_f32(const void *X, const void *W, void *O, int in_dim, int start_row, int end_row);
 void tie_cuda_mat_vec_row_f32_f32_f32(const void *X, const void *W, void *O, int in_dim, int start_row, int end_row);

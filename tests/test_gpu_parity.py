@@ -432,6 +432,31 @@ def test_dispatch_rows(be, layer0, port_lib, ref_silu_table):
     assert np.array_equal(bits(lg), bits(lg_ref))
 
 
+@pytest.mark.parametrize("ggml_type,in_dim,out_dim,batch", [(12, 2048, 4096, 100), (14, 2048, 512, 37), (12, 768, 2048, 64),
+                                                             (14, 768, 256, 1)])
+def test_dense_mat_mat_on_the_grouped_product(be, port_lib, ggml_type, in_dim, out_dim, batch):
+    """dispatch_mat_mat (math_dispatch.c:304) for stand-alone Q4_K / Q6_K tensors — attention
+    q/k/v-shaped [4096|512 x 2048] and FFN-shaped ones — against the restatement's mat-vec per row."""
+    import torch
+    from tie_b200 import moe
+    nb = out_dim * (in_dim // 256)
+    w = synth.q4k_blocks(77, 9, nb) if ggml_type == 12 else synth.q6k_blocks(77, 9, nb)
+    w = np.ascontiguousarray(w)
+    be.register_tensor(w, ggml_type, in_dim)
+    x = synth.make_x(3, batch, in_dim)
+    ref = np.stack([port_lib.mat_vec(x[i], w, ggml_type, in_dim, out_dim) for i in range(batch)])
+    got = be.mat_mat(w, x, np.empty((batch, out_dim), dtype=np.float32), batch, in_dim, out_dim)  # host pointers
+    scale = np.sqrt((ref.astype(np.float64) ** 2).mean(axis=1, keepdims=True))
+    assert (np.abs(got - ref) / scale).max() < TOL
+    xd = torch.from_numpy(x).cuda()
+    od = torch.empty(batch, out_dim, device="cuda")
+    be.mat_mat(w, xd, od, batch, in_dim, out_dim, moe.DEVICE)
+    assert np.array_equal(bits(od.cpu().numpy()), bits(got))
+    with pytest.raises(moe.TieCudaError) as ei:  # an in_dim the split arrays are not laid out for
+        be.mat_mat(w, x, got, batch, in_dim + 256, out_dim)
+    assert ei.value.code == moe.EINVAL
+
+
 def test_errors_are_codes_not_exits(be):
     from tie_b200 import moe
     x = np.zeros((1, 2048), dtype=np.float32)

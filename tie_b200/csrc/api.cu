@@ -147,7 +147,8 @@ int upload_tensor(tie_cuda_ctx *c, DevTensor &t, const void *host, int type, int
 	return tc_make_weight_map(c, t);
 }
 
-int add_reg(tie_cuda_ctx *c, const void *host, size_t bytes, const uint8_t *dev, int type, WKind kind, int rows, int k)
+int add_reg(tie_cuda_ctx *c, const void *host, size_t bytes, const uint8_t *dev, int type, WKind kind, int rows, int k,
+	    DevTensor *dense = nullptr)
 {
 	if (c->n_regs == c->cap_regs) {
 		int nc = c->cap_regs ? c->cap_regs * 2 : 64;
@@ -157,7 +158,7 @@ int add_reg(tie_cuda_ctx *c, const void *host, size_t bytes, const uint8_t *dev,
 		c->regs = static_cast<decltype(c->regs)>(p);
 		c->cap_regs = nc;
 	}
-	c->regs[c->n_regs++] = {host, bytes, dev, type, kind, rows, k};
+	c->regs[c->n_regs++] = {host, bytes, dev, type, kind, rows, k, dense};
 	return TIE_CUDA_OK;
 }
 
@@ -619,6 +620,8 @@ void tie_cuda_destroy(tie_cuda_ctx *c)
 	for (int i = 0; i < c->n_extra; i++)
 		cudaFree(c->extra[i]);
 	free(c->extra);
+	for (int i = 0; i < c->n_regs; i++)
+		delete c->regs[i].dense;
 	free(c->regs);
 	ep_release(c);
 	delete c;
@@ -1159,7 +1162,75 @@ int tie_cuda_register_tensor(tie_cuda_ctx *c, const void *host_ptr, size_t n_byt
 		TIE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
 	}
 	c->weight_bytes += n_bytes;
-	return add_reg(c, host_ptr, n_bytes, dev, ggml_type, kind, (int)rows, in_dim);
+	DevTensor *dense = nullptr;
+	if (ggml_type != TIE_GGML_TYPE_F32) {  // the view tie_cuda_mat_mat takes: one "expert" holding every row
+		dense = new DevTensor();
+		dense->ptr = dev;
+		dense->ggml_type = ggml_type;
+		dense->kind = kind;
+		dense->rows = (int)rows;
+		dense->k = in_dim;
+		dense->expert_stride = n_bytes;
+		dense->bytes = n_bytes;
+		dense->host_ptr = host_ptr;
+		int rc = tc_make_weight_map(c, *dense, 1);
+		if (rc) {
+			delete dense;
+			return rc;
+		}
+	}
+	return add_reg(c, host_ptr, n_bytes, dev, ggml_type, kind, (int)rows, in_dim, dense);
+}
+
+int tie_cuda_mat_mat(tie_cuda_ctx *c, const void *w_host, const float *x, float *o, int batch_len, int in_dim, int out_dim,
+		     unsigned flags)
+{
+	if (!c || !w_host || !x || !o || batch_len <= 0 || in_dim <= 0 || out_dim <= 0)
+		return TIE_CUDA_EINVAL;
+	const tie_cuda_ctx::Reg *reg = nullptr;
+	for (int i = 0; i < c->n_regs; i++)
+		if (c->regs[i].host == w_host)
+			reg = &c->regs[i];
+	if (!reg || reg->k != in_dim || reg->rows != out_dim)
+		return TIE_CUDA_EINVAL;
+	int arr = 0;
+	if (!reg->dense || !tc_dense_supported(c, *reg->dense, &arr))
+		return TIE_CUDA_ENOTSUP;
+	Scratch &s = c->s;
+	const size_t T = c->cfg.max_tokens, H = c->cfg.hidden, F = c->cfg.ffn_dim;
+	const size_t y_cap = s.rows_cap * (H > 2 * F ? H : 2 * F);
+	if ((size_t)batch_len > s.rows_cap || (size_t)batch_len * out_dim > y_cap)
+		return TIE_CUDA_ETOOBIG;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	const bool dev = flags & TIE_CUDA_DEVICE;
+	const float *x_dev = x;
+	float *o_dev = o;
+	if (!dev) {
+		if ((size_t)batch_len * in_dim > T * H)
+			return TIE_CUDA_ETOOBIG;
+		TRY(h2d(c, s.x, x, (size_t)batch_len * in_dim * sizeof(float), c->pin_x));
+		x_dev = s.x;
+		o_dev = s.y;
+	}
+	// one "expert" owning every row: the tile table of the grouped product, rows in input order
+	TIE_CUDA_TRY(c, cudaMemsetAsync(s.row_expert, 0, (size_t)batch_len * sizeof(int), c->stream));
+	SortBufs b = {s.counts, s.offsets, s.tile_start, s.active, s.n_active, s.perm, s.tile_info};
+	TRY(launch_sort(c, s.row_expert, batch_len, TC_TOKEN_TILE, 0, 1, b));
+	const bool sums = reg->dense->kind == W_Q4K;
+	if (arr == 0)
+		TRY(launch_split_rows(c, x_dev, nullptr, 1, batch_len, in_dim, s.xs_hi, s.xs_lo, sums ? s.xq_hi : nullptr,
+				      sums ? s.xq_lo : nullptr));
+	else
+		TRY(launch_split_rows(c, x_dev, nullptr, 1, batch_len, in_dim, s.hs_hi, s.hs_lo, sums ? s.hq_hi : nullptr,
+				      sums ? s.hq_lo : nullptr));
+	TRY(launch_tc_dense(c, *reg->dense, arr, o_dev));
+	if (!dev) {
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(o, o_dev, (size_t)batch_len * out_dim * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
+		return check_status(c);
+	}
+	if (flags & TIE_CUDA_NO_SYNC)
+		return TIE_CUDA_OK;
+	return check_status(c);
 }
 
 static int ensure_row_buffers(tie_cuda_ctx *c, size_t n)

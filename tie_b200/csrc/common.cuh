@@ -145,6 +145,7 @@ struct tie_cuda_ctx {
 		int type;
 		tie::WKind kind;
 		int rows, k;
+		tie::DevTensor *dense;	// stand-alone quantised tensors: the view the tensor-core path takes (or null)
 	} *regs = nullptr;
 	int n_regs = 0, cap_regs = 0;
 	// standalone tensors uploaded through tie_cuda_register_tensor

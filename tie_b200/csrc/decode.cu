@@ -22,6 +22,9 @@
 namespace tie {
 
 constexpr int DEC_THREADS = 256;
+// gate/up: 16 warps per SM — the reduction out of shared memory is latency-bound (dependent
+// unpack -> fma chains), so twice the warps per scheduler halve its time
+constexpr int DEC_GU_THREADS = 512;
 constexpr long long DEC_WAIT_CYCLES = 1ll << 30;
 
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
@@ -71,7 +74,7 @@ __device__ __forceinline__ void pdl_trigger()
 constexpr int DEC_MAX_CHUNKS = 8;
 
 template <WKind KIND, int K>
-__global__ void __launch_bounds__(DEC_THREADS, 1)
+__global__ void __launch_bounds__(DEC_GU_THREADS, 1)
 decode_gate_up(const uint8_t *__restrict__ wg, const uint8_t *__restrict__ wu, size_t expert_stride, int rows_per_expert,
 	       int rows_per_tile, const float *__restrict__ x, int top_k, const int *__restrict__ topk_idx, float *__restrict__ h,
 	       int first_expert, int n_local, const float *__restrict__ silu, unsigned *__restrict__ status)
@@ -80,7 +83,7 @@ decode_gate_up(const uint8_t *__restrict__ wg, const uint8_t *__restrict__ wu, s
 	constexpr int LPR = PARTS > 16 ? 32 : (PARTS > 8 ? 16 : (PARTS > 4 ? 8 : 4));
 	constexpr int RPW = 32 / LPR;
 	constexpr int NB = K / QK_K;
-	constexpr int ROWS_PER_PASS = (DEC_THREADS / 32) * RPW;
+	constexpr int ROWS_PER_PASS = (DEC_GU_THREADS / 32) * RPW;
 	constexpr int CH = ROWS_PER_PASS > 16 ? ROWS_PER_PASS : 16;  // rows per copy chunk (own barrier): a pass never spans two
 	extern __shared__ __align__(128) uint8_t dsm[];
 	__shared__ uint64_t bar[DEC_MAX_CHUNKS];
@@ -118,7 +121,7 @@ decode_gate_up(const uint8_t *__restrict__ wg, const uint8_t *__restrict__ wu, s
 		}
 	}
 	const float *xrow = x + (size_t)(slot / top_k) * K;
-	stage_x_lane_major<KIND, LPR>(xrow, xs, PARTS, threadIdx.x, DEC_THREADS);
+	stage_x_lane_major<KIND, LPR>(xrow, xs, PARTS, threadIdx.x, DEC_GU_THREADS);
 	__syncthreads();  // also publishes the barrier initialisation
 	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 	const int sub = lane / LPR, part = lane % LPR;
@@ -279,7 +282,7 @@ static int launch_dec_gu_t(tie_cuda_ctx *c, const Layer &L, const float *x, int 
 	TIE_CUDA_TRY(c, cudaFuncSetAttribute(decode_gate_up<KIND, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_MAX_SMEM));
 	cudaLaunchConfig_t cfg = {};
 	cfg.gridDim = dim3(tiles, n_rows);
-	cfg.blockDim = dim3(DEC_THREADS);
+	cfg.blockDim = dim3(DEC_GU_THREADS);
 	cfg.dynamicSmemBytes = smem;
 	cfg.stream = c->stream;
 	cudaLaunchAttribute attr[1];

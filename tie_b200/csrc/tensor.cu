@@ -967,14 +967,16 @@ static int make_tmap(tie_cuda_ctx *c, CUtensorMap *tm, void *base, size_t rows, 
 
 // Byte map of an expert tensor for the weight loader.  Q4_K: [experts x rows][row bytes], box = one
 // 144-byte block x 128 rows.  Q6_K: [groups][8 rows][row records], box = one 208-byte record x 8 x 16.
-int tc_make_weight_map(tie_cuda_ctx *c, DevTensor &t)
+int tc_make_weight_map(tie_cuda_ctx *c, DevTensor &t, int n_experts)
 {
+	if (n_experts <= 0)
+		n_experts = c->n_local;
 	t.has_map = false;
 	if (t.rows % TC_BM || t.k % QK_K)
 		return TIE_CUDA_OK;
 	const int nb = t.k / QK_K;
 	if (t.kind == W_Q4K) {
-		int rc = encode_2d(c, &t.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, t.ptr, (size_t)t.rows * c->n_local, (size_t)nb * Q4K_BYTES,
+		int rc = encode_2d(c, &t.map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, t.ptr, (size_t)t.rows * n_experts, (size_t)nb * Q4K_BYTES,
 				   Q4K_BYTES, TC_BM, CU_TENSOR_MAP_SWIZZLE_NONE);
 		if (rc)
 			return rc;
@@ -984,7 +986,7 @@ int tc_make_weight_map(tie_cuda_ctx *c, DevTensor &t)
 			snprintf(c->cuda_err, sizeof(c->cuda_err), "cuTensorMapEncodeTiled entry point not found");
 			return TIE_CUDA_ECUDA;
 		}
-		cuuint64_t dims[3] = {(cuuint64_t)nb * Q6K_RECORD, 8, (cuuint64_t)t.rows * c->n_local / 8};
+		cuuint64_t dims[3] = {(cuuint64_t)nb * Q6K_RECORD, 8, (cuuint64_t)t.rows * n_experts / 8};
 		cuuint64_t strides[2] = {(cuuint64_t)nb * Q6K_RECORD, (cuuint64_t)q6k_r8_group_bytes(nb)};
 		cuuint32_t box[3] = {Q6K_RECORD, 8, TC_BM / 8};
 		cuuint32_t estr[3] = {1, 1, 1};
@@ -1030,16 +1032,18 @@ int tc_setup(tie_cuda_ctx *c)
 // arr: 0 = the split inputs x (gate/up), 1 = the split activations h (down).
 template <WKind KIND, bool RAW, bool PEER = false>
 static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1, int arr, float *y, float out_scale,
-		       bool sorted_out = false, const EpDst *dst = nullptr)
+		       bool sorted_out = false, const EpDst *dst = nullptr, int n_experts = -1)
 {
 	Scratch &s = c->s;
+	if (n_experts <= 0)
+		n_experts = c->n_local;
 	const int m_tiles = (RAW ? 2 : 1) * t0.rows / TC_BM;
 	const CUtensorMap &w0m = t0.map;
 	const CUtensorMap &w1m = t1 ? t1->map : t0.map;
 	grouped_gemm_sb<KIND, RAW, PEER><<<c->sm_count, TC_THREADS, TcSmem<KIND>::SMEM, c->stream>>>(
 		c->tmap[arr * 3], c->tmap[arr * 3 + 1], c->tmap[arr * 3 + 2], c->tmap[(2 + arr) * 3], c->tmap[(2 + arr) * 3 + 1],
 		c->tmap[(2 + arr) * 3 + 2], w0m, w1m, t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride,
-		t0.k, s.tile_info, s.tile_start, c->n_local, m_tiles, y, sorted_out ? nullptr : s.perm, RAW ? 2 * t0.rows : t0.rows,
+		t0.k, s.tile_info, s.tile_start, n_experts, m_tiles, y, sorted_out ? nullptr : s.perm, RAW ? 2 * t0.rows : t0.rows,
 		out_scale, s.status, t0.rows, dst ? *dst : EpDst());
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
@@ -1082,6 +1086,29 @@ int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, float *y, bool s
 	if (L.down.kind == W_Q4K)
 		return launch_tc_t<W_Q4K, false>(c, L.down, nullptr, 1, y, 1.0f / TC_H_SCALE, sorted_out);
 	return launch_tc_t<W_Q6K_R8, false>(c, L.down, nullptr, 1, y, 1.0f / TC_H_SCALE, sorted_out);
+}
+
+// A dense tensor (one "expert") on the grouped product: y[p][row] = sum_k w[row][k] x[p][k] for
+// the rows staged in the split arrays of `arr` (0: x arrays, k = hidden; 1: h arrays, k = ffn_dim);
+// the tile table must describe one expert holding all rows.
+bool tc_dense_supported(const tie_cuda_ctx *c, const DevTensor &t, int *arr)
+{
+	if (!c->tmaps_ok || !tc_tensor_ok(t))
+		return false;
+	if (t.k == c->cfg.hidden)
+		*arr = 0;
+	else if (t.k == c->cfg.ffn_dim)
+		*arr = 1;
+	else
+		return false;
+	return true;
+}
+
+int launch_tc_dense(tie_cuda_ctx *c, const DevTensor &t, int arr, float *y)
+{
+	if (t.kind == W_Q4K)
+		return launch_tc_t<W_Q4K, false>(c, t, nullptr, arr, y, 1.0f, true, nullptr, 1);
+	return launch_tc_t<W_Q6K_R8, false>(c, t, nullptr, arr, y, 1.0f, true, nullptr, 1);
 }
 
 // The down product of an expert-parallel step: row p goes to the rank and row dst->row[p] names.

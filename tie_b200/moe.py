@@ -31,7 +31,7 @@ EXPORTS = [
     "tie_cuda_version", "tie_cuda_set_profiling", "tie_cuda_get_profile", "tie_cuda_moe_ep_dispatch",
     "tie_cuda_moe_ep_combine", "tie_cuda_route_noalloc", "tie_cuda_ep_region", "tie_cuda_ep_ipc_handle",
     "tie_cuda_ep_attach", "tie_cuda_ep_detach", "tie_cuda_ep_set_timeout_ms", "tie_cuda_ep_publish", "tie_cuda_ep_compute",
-    "tie_cuda_ep_gather", "tie_cuda_moe_ffn_ep",
+    "tie_cuda_ep_gather", "tie_cuda_moe_ffn_ep", "tie_cuda_mat_mat",
 ]
 EP_HANDLE_BYTES = 64
 EP_PEER_POINTERS, EP_PEER_IPC_HANDLES = 0, 1
@@ -141,6 +141,8 @@ def load_library() -> ctypes.CDLL:
     L.tie_cuda_ep_gather.argtypes = [vp, vp, vp, u32]
     L.tie_cuda_moe_ffn_ep.restype = i32
     L.tie_cuda_moe_ffn_ep.argtypes = [vp, i32, vp, vp, i32, u32]
+    L.tie_cuda_mat_mat.restype = i32
+    L.tie_cuda_mat_mat.argtypes = [vp, vp, vp, vp, i32, i32, i32, u32]
     _lib = L
     return L
 
@@ -356,6 +358,12 @@ class MoeBackend:
     def register_tensor(self, host: np.ndarray, ggml_type: int, in_dim: int):
         rc = self.L.tie_cuda_register_tensor(self.h, host.ctypes.data, host.nbytes, ggml_type, in_dim)
         self._check(rc, "tie_cuda_register_tensor")
+
+    def mat_mat(self, w_host: np.ndarray, x, out, batch_len: int, in_dim: int, out_dim: int, flags: int = 0):
+        """dispatch_mat_mat on a registered Q4_K / Q6_K tensor (w_host: the array given to register_tensor)."""
+        rc = self.L.tie_cuda_mat_mat(self.h, w_host.ctypes.data, _ptr(x), _ptr(out), batch_len, in_dim, out_dim, flags)
+        self._check(rc, "tie_cuda_mat_mat")
+        return out
 
     def dispatch_mat_vec(self, x: np.ndarray, w_host_ptr: int, ggml_type: int, in_dim: int, start_row: int, end_row: int,
                          out: np.ndarray | None = None) -> np.ndarray:
