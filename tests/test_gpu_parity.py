@@ -155,6 +155,32 @@ def test_prefill512(be, golden, port0, path):
     _check_ffn(out, ref_out)
 
 
+def test_one_kernel_decode_equals_the_three_kernel_chain(be, be_small, small_shape, port0):
+    """One token: the cooperative single-kernel step (default) and the chain of three decode
+    kernels run the same per-lane arithmetic in the same order: identical bits, launch counts 1 / 3,
+    also when replayed from a graph many times (the grid barriers' epoch advances on the device)."""
+    import torch
+    from tie_b200 import moe
+    for b, hidden, seed in ((be, 2048, 21), (be_small, small_shape.hidden, 22)):
+        for rep in range(3):
+            x = torch.from_numpy(synth.make_x(seed + rep, 1, hidden)).cuda()
+            o1, o3 = torch.empty_like(x), torch.empty_like(x)
+            l0 = b.launch_count
+            b.moe_ffn_ptr(0, x, o1, 1, moe.DEVICE)
+            l1 = b.launch_count
+            b.moe_ffn_ptr(0, x, o3, 1, moe.DEVICE | moe.PATH_DECODE_CHAIN)
+            l3 = b.launch_count
+            assert (l1 - l0, l3 - l1) == (1, 3)
+            assert np.array_equal(bits(o1.cpu().numpy()), bits(o3.cpu().numpy()))
+            for _ in range(5):
+                og = torch.zeros_like(x)
+                b.moe_ffn_ptr(0, x, og, 1, moe.DEVICE | moe.GRAPH)
+                assert np.array_equal(bits(og.cpu().numpy()), bits(o1.cpu().numpy()))
+    x = synth.make_x(23, 1)
+    ref, _, _ = port0.moe_ffn(x)
+    assert workloads.rel_rms_err(be.moe_ffn(0, x), ref).max() < TOL  # host pointers, default (one-kernel) path
+
+
 def test_auto_path_and_determinism(be):
     x = synth.make_x(0, 512)
     a = be.moe_ffn(0, x)

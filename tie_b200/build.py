@@ -8,7 +8,7 @@ import sys
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.path.join(_HERE, "libtie_cuda.so")
-SOURCES = ["api.cu", "router.cu", "sort.cu", "stream.cu", "tensor.cu", "misc.cu", "repack.cu", "decode.cu", "ep.cu"]
+SOURCES = ["api.cu", "router.cu", "sort.cu", "stream.cu", "tensor.cu", "misc.cu", "repack.cu", "decode.cu", "decode_fused.cu", "ep.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-cudart", "static",

@@ -71,6 +71,8 @@ int alloc_scratch(tie_cuda_ctx *c)
 	TRY(dev_alloc(c, &s.status, 1));
 	TRY(dev_alloc(c, &s.counter, 1));
 	TIE_CUDA_TRY(c, cudaMemset(s.counter, 0, sizeof(int)));
+	TRY(dev_alloc(c, &s.dec_sync, 2));
+	TIE_CUDA_TRY(c, cudaMemset(s.dec_sync, 0, 2 * sizeof(unsigned)));
 	TRY(dev_alloc(c, &s.row_expert, R));
 	TRY(dev_alloc(c, &s.ep_counts, E));
 	TRY(dev_alloc(c, &s.ep_offsets, E + 1));
@@ -182,6 +184,8 @@ int check_status(tie_cuda_ctx *c)
 			 (st & ST_BAD_EXPERT) ? "expert id out of range " : "", (st & ST_WAIT_TIMEOUT) ? "barrier wait timed out " : "",
 			 (st & ST_BAD_TILE) ? "tile bookkeeping " : "");
 		cudaMemsetAsync(c->s.status, 0, sizeof(unsigned), c->stream);
+		if (st & ST_WAIT_TIMEOUT)  // a grid barrier of the one-kernel decode step may have been left half-counted
+			cudaMemsetAsync(c->s.dec_sync, 0, 2 * sizeof(unsigned), c->stream);
 		return TIE_CUDA_EKERNEL;
 	}
 	return TIE_CUDA_OK;
@@ -259,6 +263,16 @@ int moe_ffn_device(tie_cuda_ctx *c, Layer &L, const float *x, float *out, int n_
 	Scratch &s = c->s;
 	const int lfm2 = (flags & TIE_CUDA_ROUTE_LFM2) ? 1 : 0;
 	prof_mark(c, 0);
+	const bool decode_paths = (flags & TIE_CUDA_PATH_MASK) != TIE_CUDA_PATH_TENSOR && !(flags & TIE_CUDA_PATH_LEGACY_STREAM);
+	// one token: the whole block as one cooperative kernel
+	if (decode_paths && !lfm2 && !(flags & TIE_CUDA_PATH_DECODE_CHAIN) && decode_fused_supported(c, L, n_tokens)) {
+		TRY(launch_decode_fused(c, L, x, bias_dev, residual, out));
+		c->last_used_tc = false;
+		c->last_direct_rows = c->cfg.top_k;
+		for (int i = 1; i <= 7; i++)
+			prof_mark(c, i);
+		return TIE_CUDA_OK;
+	}
 	// decode (1-4 tokens): three launches — router with fused selection, gate/up, down + combine
 	if ((flags & TIE_CUDA_PATH_MASK) != TIE_CUDA_PATH_TENSOR && !(flags & TIE_CUDA_PATH_LEGACY_STREAM) &&
 	    decode_supported(c, L, n_tokens)) {
@@ -534,6 +548,7 @@ int tie_cuda_init(tie_cuda_ctx **out, const tie_cuda_config *cfg)
 	c->cfg.silu_table = nullptr;
 	c->device = cfg->device;
 	c->sm_count = prop.multiProcessorCount;
+	c->coop_ok = prop.cooperativeLaunch != 0;
 	c->n_local = cfg->n_expert / cfg->ep_size;
 	c->first_expert = cfg->ep_rank * c->n_local;
 	int rc = TIE_CUDA_OK;
@@ -601,7 +616,7 @@ void tie_cuda_destroy(tie_cuda_ctx *c)
 	void *dev_ptrs[] = {s.x,     s.out,   s.logits, s.bias,  s.topk_idx, s.topk_w, s.counts, s.offsets, s.tile_start, s.active, s.n_active,
 			    s.perm,  s.h,     s.y,	s.xs_hi, s.hs_hi,  s.status,  s.counter, s.row_expert, c->silu,  c->row_x,
 			    c->row_o, s.ep_counts, s.ep_offsets, s.ep_tile_start, s.ep_active, s.ep_n_active, s.ep_perm, s.ep_inv,
-			    s.tile_info, s.xq_hi, s.hq_hi};
+			    s.tile_info, s.xq_hi, s.hq_hi, s.dec_sync};
 	for (void *p : dev_ptrs)
 		if (p)
 			cudaFree(p);
@@ -744,7 +759,8 @@ int tie_cuda_moe_ffn_biased(tie_cuda_ctx *c, int layer, const float *x, float *o
 	const size_t bytes = (size_t)n_tokens * c->cfg.hidden * sizeof(float);
 	const bool dev = flags & TIE_CUDA_DEVICE;
 	const bool graph = flags & TIE_CUDA_GRAPH;
-	const unsigned kflags = flags & (TIE_CUDA_DEVICE | TIE_CUDA_PATH_MASK | TIE_CUDA_PATH_LEGACY_STREAM | TIE_CUDA_ROUTE_LFM2);
+	const unsigned kflags = flags & (TIE_CUDA_DEVICE | TIE_CUDA_PATH_MASK | TIE_CUDA_PATH_LEGACY_STREAM | TIE_CUDA_ROUTE_LFM2 |
+					 TIE_CUDA_PATH_DECODE_CHAIN);
 	const float *bias_dev = nullptr;
 	if (router_bias) {
 		if (dev) {
@@ -799,7 +815,8 @@ int tie_cuda_moe_block_inplace(tie_cuda_ctx *c, int layer, float *hidden_dev, in
 	if (!hidden_dev || n_tokens <= 0 || n_tokens > c->cfg.max_tokens || c->cfg.ep_size != 1)
 		return TIE_CUDA_EINVAL;
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
-	GraphKey k = {3, layer, n_tokens, hidden_dev, nullptr, nullptr, nullptr, flags & TIE_CUDA_PATH_MASK};
+	GraphKey k = {3, layer, n_tokens, hidden_dev, nullptr, nullptr, nullptr,
+		      flags & (TIE_CUDA_PATH_MASK | TIE_CUDA_PATH_LEGACY_STREAM | TIE_CUDA_PATH_DECODE_CHAIN)};
 	TRY(run_maybe_graphed(c, flags & TIE_CUDA_GRAPH, k, [&]() -> int {
 		TRY(launch_rms_norm(c, hidden_dev, L->norm_w, c->s.x, n_tokens));
 		return moe_ffn_device(c, *L, c->s.x, hidden_dev, n_tokens, nullptr, hidden_dev, flags);

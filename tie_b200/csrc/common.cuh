@@ -74,6 +74,7 @@ struct Scratch {
 	__half *hq_hi = nullptr, *hq_lo = nullptr;  // [Rpad][xq_cols(F)]
 	unsigned *status = nullptr;		    // [1]
 	int *counter = nullptr;			    // [1] last-CTA counter of the fused decode router (zero at rest)
+	unsigned *dec_sync = nullptr;		    // [2] arrivals and epoch of the one-kernel decode step's grid barriers
 	int *row_expert = nullptr;		    // [R] staging for expert_rows
 	// expert-parallel dispatch state (sort of this rank's rows over ALL experts)
 	int *ep_counts = nullptr, *ep_offsets = nullptr, *ep_tile_start = nullptr, *ep_active = nullptr, *ep_n_active = nullptr;
@@ -115,6 +116,7 @@ struct tie_cuda_ctx {
 	tie_cuda_config cfg;
 	int device = 0;
 	int sm_count = 0;
+	bool coop_ok = false;  // cooperative launches available
 	cudaStream_t own_stream = nullptr;
 	cudaStream_t stream = nullptr;
 	float *silu = nullptr;	// device [8192]

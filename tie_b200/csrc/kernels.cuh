@@ -15,6 +15,9 @@ bool decode_supported(const tie_cuda_ctx *c, const Layer &L, int n_tokens);
 int launch_decode_gate_up(tie_cuda_ctx *c, const Layer &L, const float *x, int n_tokens);
 int launch_decode_down_combine(tie_cuda_ctx *c, const Layer &L, int n_tokens, const float *residual, float *out);
 int launch_router_rows(tie_cuda_ctx *c, const float *x, const float *w, int n_rows, int in_dim, float *out);
+// decode_fused.cu
+bool decode_fused_supported(tie_cuda_ctx *c, const Layer &L, int n_tokens);
+int launch_decode_fused(tie_cuda_ctx *c, const Layer &L, const float *x, const float *bias, const float *residual, float *out);
 // sort.cu
 struct SortBufs {
 	int *counts, *offsets, *tile_start, *active, *n_active, *perm;

@@ -17,6 +17,7 @@ LIB_PATH = os.path.join(_HERE, "libtie_cuda.so")
 HOST, DEVICE, NO_SYNC, GRAPH = 0, 1, 2, 4
 PATH_AUTO, PATH_STREAM, PATH_TENSOR = 0, 1 << 8, 2 << 8
 PATH_LEGACY_STREAM = 1 << 10
+PATH_DECODE_CHAIN = 1 << 11  # one token: three chained decode kernels instead of the single cooperative one
 ROUTE_LFM2 = 1 << 12  # LFM2-MoE routing: sigmoid, selection bias, L1-normalised gates (model_lfm2.c:438-473)
 OK, EINVAL, ENOTSUP, ENOMEM, ECUDA, ENODEV, EKERNEL, ETOOBIG = 0, -1, -2, -3, -4, -5, -6, -7
 
