@@ -259,6 +259,23 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
     e2e_s = timed(step_e2e, args.steps) * 1e-3
     be.synchronize()
 
+    # per-phase device times of rank 0 (CUDA events inside the library; the steps run without a graph,
+    # and every rank starts them together, so waits for peers show up in the phase that waits)
+    phases = None
+    if exchange == "peer":
+        be.set_profiling(True)
+        acc = None
+        n_prof = 10
+        for _ in range(n_prof):
+            dist.barrier()
+            blk.forward(x_dev, out_dev)
+            prof, _ = be.get_profile()
+            acc = prof if acc is None else {k: acc[k] + v for k, v in prof.items()}
+        be.set_profiling(False)
+        names = {"router": "router", "sort": "sort + publish", "split": "layout + remote row gather", "gate_up": "gate/up product",
+                 "swiglu": "SwiGLU pass", "down": "down product (stores rows to their sources)", "combine": "wait for owners + combine"}
+        phases = {names[k]: v / n_prof for k, v in acc.items()}
+
     strong = None
     if exchange == "peer" and not getattr(args, "no_extra", False) and STRONG_TOKENS % world == 0:
         T2 = STRONG_TOKENS // world
@@ -304,7 +321,8 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
                          "remote_fraction": (world - 1) / world,
                          "nvlink_bytes_per_rank_and_direction": int(T * shape.top_k * shape.hidden * 4 * (world - 1) / world),
                          "nvlink_floor_us": 2 * T * shape.top_k * shape.hidden * 4 * (world - 1) / world / 770e9 * 1e6,
-                         "note": "floor = dispatch + combine bytes of one rank / measured 770 GB/s per direction"},
+                         "note": "floor = dispatch + combine bytes of one rank / measured 770 GB/s per direction",
+                         "phases_ms_rank0": phases},
             "extra": {"prefill_8192_tokens_total": strong},
         }
         print(json.dumps(line), flush=True)

@@ -87,6 +87,7 @@ def _main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("workload", choices=["decode1", "batch64", "prefill512"])
     ap.add_argument("--steps", type=int, default=4)
+    ap.add_argument("--chain", action="store_true", help="decode1: the three chained decode kernels instead of the one-kernel step")
     args = ap.parse_args()
     n_tokens = {"decode1": 1, "batch64": 64, "prefill512": 512}[args.workload]
     be = moe.MoeBackend(max_tokens=n_tokens, silu_table=moe.silu_table_default())
@@ -99,7 +100,7 @@ def _main() -> None:
     flush = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device="cuda")  # 256 MB > L2
     for _ in range(args.steps):
         flush.zero_()
-        be.moe_ffn_ptr(0, x, out, n_tokens, moe.DEVICE)
+        be.moe_ffn_ptr(0, x, out, n_tokens, moe.DEVICE | (moe.PATH_DECODE_CHAIN if args.chain else 0))
     be.synchronize()
     be.close()
     print(f"{args.workload}: {args.steps} passes ok")
