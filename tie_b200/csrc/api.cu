@@ -266,12 +266,16 @@ int moe_ffn_device(tie_cuda_ctx *c, Layer &L, const float *x, float *out, int n_
 	const bool decode_paths = (flags & TIE_CUDA_PATH_MASK) != TIE_CUDA_PATH_TENSOR && !(flags & TIE_CUDA_PATH_LEGACY_STREAM);
 	// one token: the whole block as one cooperative kernel
 	if (decode_paths && !lfm2 && !(flags & TIE_CUDA_PATH_DECODE_CHAIN) && decode_fused_supported(c, L, n_tokens)) {
-		TRY(launch_decode_fused(c, L, x, bias_dev, residual, out));
-		c->last_used_tc = false;
-		c->last_direct_rows = c->cfg.top_k;
-		for (int i = 1; i <= 7; i++)
-			prof_mark(c, i);
-		return TIE_CUDA_OK;
+		const int rc = launch_decode_fused(c, L, x, bias_dev, residual, out);
+		if (rc != TIE_CUDA_ENOTSUP) {  // (not supported after all: the chain below)
+			if (rc)
+				return rc;
+			c->last_used_tc = false;
+			c->last_direct_rows = c->cfg.top_k;
+			for (int i = 1; i <= 7; i++)
+				prof_mark(c, i);
+			return TIE_CUDA_OK;
+		}
 	}
 	// decode (1-4 tokens): three launches — router with fused selection, gate/up, down + combine
 	if ((flags & TIE_CUDA_PATH_MASK) != TIE_CUDA_PATH_TENSOR && !(flags & TIE_CUDA_PATH_LEGACY_STREAM) &&

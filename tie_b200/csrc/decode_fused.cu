@@ -475,7 +475,14 @@ static int df_launch(tie_cuda_ctx *c, const Layer &L, const float *x, const floa
 	attr[0].val.cooperative = 1;
 	cfg.attrs = attr;
 	cfg.numAttrs = 1;
-	TIE_CUDA_TRY(c, cudaLaunchKernelEx(&cfg, kern, a));
+	const cudaError_t e = cudaLaunchKernelEx(&cfg, kern, a);
+	if (e == cudaErrorCooperativeLaunchTooLarge || e == cudaErrorNotSupported) {
+		// the grid cannot be co-resident here (a shared or partitioned GPU): the caller takes the chain
+		cudaGetLastError();
+		c->coop_ok = false;
+		return TIE_CUDA_ENOTSUP;
+	}
+	TIE_CUDA_TRY(c, e);
 	c->launches++;
 	return TIE_CUDA_OK;
 }
