@@ -203,6 +203,9 @@ int tie_cuda_ep_publish(tie_cuda_ctx *c, int layer, const float *x, int n_tokens
 int tie_cuda_ep_compute(tie_cuda_ctx *c, int layer, unsigned flags);
 int tie_cuda_ep_gather(tie_cuda_ctx *c, float *out, const float *residual, unsigned flags);
 int tie_cuda_moe_ffn_ep(tie_cuda_ctx *c, int layer, const float *x, float *out, int n_tokens, unsigned flags);
+/* hidden += MoE(RMSNorm(hidden)) for this rank's tokens, as tie_cuda_moe_block_inplace, with the
+ * experts spread over the ranks (the layer's ffn_norm_w must have been uploaded). */
+int tie_cuda_moe_block_inplace_ep(tie_cuda_ctx *c, int layer, float *hidden_dev, int n_tokens, unsigned flags);
 
 /* ---- math_dispatch.c rows (accel = 2) ----
  * Same argument meaning as the reference's kernels are CALLED with (math_dispatch.c:224,254):

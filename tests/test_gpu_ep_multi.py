@@ -42,6 +42,19 @@ for step, T in enumerate([96, 128, 1 + 40 * rank, 64]):       # ragged third ste
     err = float(workloads.rel_rms_err(od.cpu().numpy(), ref).max())
     assert err < 1e-3, (step, err)
     worst = max(worst, err)
+# two chained blocks in place (RMSNorm, experts over both GPUs, residual), each step one graph replay
+h_host = synth.make_x(workloads.BASE_SEED + 9, 64, shape.hidden, first_token=300 * rank)
+hd = torch.from_numpy(h_host).cuda()
+for rep in range(2):
+    stream.synchronize(); dist.barrier()
+    be.moe_block_inplace_ep_ptr(0, hd, 64, moe.DEVICE | moe.NO_SYNC | moe.GRAPH)
+be.synchronize()
+R = port.PortMoe(synth.make_layer(workloads.BASE_SEED, shape), silu=silu)
+want = h_host.copy()
+for rep in range(2):
+    want = R.moe_block_inplace(want)[0]
+err = float(workloads.rel_rms_err(hd.cpu().numpy(), want).max())
+assert err < 1e-3, ("block_inplace_ep", err)
 dist.barrier()
 be.close()
 dist.destroy_process_group()

@@ -181,3 +181,32 @@ def test_whole_step_replayed_from_a_graph(small_shape, small_layer, ref_silu_tab
     finally:
         bes[0].close()
         one.close()
+
+
+def test_block_inplace_ep_one_rank_group(small_shape, small_layer, ref_silu_table):
+    """hidden += MoE(RMSNorm(hidden)) through tie_cuda_moe_block_inplace_ep (one call, one graph per
+    step; the normed tokens are written straight into the region) on a group of one rank equals
+    tie_cuda_moe_block_inplace.  (Ranks that share one GPU must interleave their phases, so larger
+    groups of this one-call entry point are tested on separate GPUs.)"""
+    import torch
+    from tie_b200 import moe
+    shape = small_shape
+    norm_w = (1.0 + 0.1 * np.cos(np.arange(shape.hidden))).astype(np.float32)
+    solo = _ranks(shape, workloads.BASE_SEED + 1, 1, 64, ref_silu_table)
+    one = moe.MoeBackend(hidden=shape.hidden, n_expert=shape.n_expert, top_k=shape.top_k, ffn_dim=shape.ffn_dim, max_tokens=64,
+                         silu_table=ref_silu_table)
+    try:
+        solo[0].upload_layer(0, small_layer, ffn_norm_w=norm_w)
+        one.upload_layer(0, small_layer, ffn_norm_w=norm_w)
+        got = torch.empty(64, shape.hidden, device="cuda")
+        for step in range(3):  # the later passes replay the graph
+            h0 = torch.from_numpy(synth.make_x(31 + step, 64, shape.hidden)).cuda()
+            want = h0.clone()
+            one.moe_block_inplace_ptr(0, want, 64, moe.DEVICE | moe.PATH_TENSOR)
+            got.copy_(h0)
+            torch.cuda.synchronize()
+            solo[0].moe_block_inplace_ep_ptr(0, got, 64, moe.DEVICE | moe.GRAPH)
+            assert workloads.rel_rms_err(got.cpu().numpy(), want.cpu().numpy()).max() < 2e-5
+    finally:
+        solo[0].close()
+        one.close()

@@ -398,7 +398,7 @@ void ep_close_peers(tie_cuda_ctx *c)
 	ep.step_tokens = -1;
 	// graphs of whole steps hold the peers' addresses
 	for (int i = 0; i < c->n_graphs;) {
-		if (c->graphs[i].kind == 5) {
+		if (c->graphs[i].kind == 5 || c->graphs[i].kind == 6) {
 			cudaGraphExecDestroy(c->graphs[i].exec);
 			c->graphs[i] = c->graphs[--c->n_graphs];
 		} else {
@@ -1114,6 +1114,37 @@ int tie_cuda_moe_ffn_ep(tie_cuda_ctx *c, int layer, const float *x, float *out, 
 		if (!rc)
 			rc = tie_cuda_ep_gather(c, out, nullptr, inner);
 		if (rc) {  // nothing of a failed capture runs
+			c->ep.phase = 0;
+			c->ep.step_tokens = -1;
+		}
+		return rc;
+	}));
+	if (flags & TIE_CUDA_NO_SYNC)
+		return TIE_CUDA_OK;
+	return check_status(c);
+}
+
+int tie_cuda_moe_block_inplace_ep(tie_cuda_ctx *c, int layer, float *hidden_dev, int n_tokens, unsigned flags)
+{
+	Layer *L;
+	TRY(get_layer(c, layer, &L));
+	EpState &ep = c->ep;
+	if (!ep.attached || ep.phase != 0 || n_tokens < 0 || n_tokens > ep.view.t_max || (n_tokens && !hidden_dev))
+		return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	const unsigned inner = (flags | TIE_CUDA_NO_SYNC | TIE_CUDA_DEVICE) & ~TIE_CUDA_GRAPH;
+	float *xs = reinterpret_cast<float *>(ep.region + ep.view.off_xs);
+	GraphKey k = {6, layer, n_tokens, hidden_dev, nullptr, nullptr, nullptr, inner};
+	TRY(run_maybe_graphed(c, flags & TIE_CUDA_GRAPH, k, [&]() -> int {
+		// the normed tokens go straight to where the peers read them
+		int rc = n_tokens ? launch_rms_norm(c, hidden_dev, L->norm_w, xs, n_tokens) : TIE_CUDA_OK;
+		if (!rc)
+			rc = tie_cuda_ep_publish(c, layer, xs, n_tokens, nullptr, inner);
+		if (!rc)
+			rc = tie_cuda_ep_compute(c, layer, inner);
+		if (!rc)
+			rc = tie_cuda_ep_gather(c, hidden_dev, hidden_dev, inner);
+		if (rc) {
 			c->ep.phase = 0;
 			c->ep.step_tokens = -1;
 		}

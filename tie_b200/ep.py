@@ -290,6 +290,44 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
                   "algorithmic_tflops": workloads.algorithmic_flops(shape, STRONG_TOKENS) / (ms2 * 1e-3) / 1e12}
         be.synchronize()
 
+    # side run: the 48-block stack (BASELINE's last configuration), a 4096-token prefill with the
+    # tokens and the experts of every block spread over the ranks; h += MoE(RMSNorm(h)) per block
+    stack = None
+    n_layers = getattr(args, "stack_layers", 0)
+    if exchange == "peer" and not getattr(args, "no_extra", False) and n_layers > 0 and 4096 % world == 0:
+        T3 = 4096 // world
+        be.synchronize()
+        be2 = moe.MoeBackend(max_tokens=4096, device=local_rank, silu_table=moe.silu_table_default(), ep_rank=rank, ep_size=world,
+                             n_layers=n_layers)
+        ones = np.ones(shape.hidden, dtype=np.float32)
+        for l in range(n_layers):
+            be2.upload_layer(l, synth.make_layer(workloads.STACK_BASE_SEED + l, shape, first_expert=rank * n_local,
+                                                 n_local_expert=n_local), ffn_norm_w=ones)
+        be2.set_stream(stream.cuda_stream)
+        PeerEpMoeBlock(be2, dist)
+        h0 = torch.from_numpy(synth.make_x(workloads.STACK_BASE_SEED, T3, first_token=rank * T3)).cuda()
+        h = h0.clone()
+        fl = moe.DEVICE | moe.NO_SYNC | moe.GRAPH
+
+        def stack_pass():
+            for l in range(n_layers):
+                be2.moe_block_inplace_ep_ptr(l, h, T3, fl)
+
+        for _ in range(2):
+            h.copy_(h0)
+            stack_pass()
+        be2.synchronize()
+        h.copy_(h0)
+        ms3 = timed(stack_pass, 3)
+        be2.synchronize()
+        finite = bool(torch.isfinite(h).all().item())
+        fl3 = workloads.algorithmic_flops(shape, 4096) * n_layers
+        stack = {"layers": n_layers, "tokens": 4096, "tokens_per_rank": T3, "scaling": "strong", "ms": ms3,
+                 "tokens_per_s": 4096 / (ms3 * 1e-3), "algorithmic_tflops": fl3 / (ms3 * 1e-3) / 1e12, "finite": finite,
+                 "weight_bytes_per_rank": be2.weight_bytes}
+        dist.barrier()
+        be2.close()
+
     if rank == 0:
         peaks = load_peaks()
         ms_per_step = total_ms / args.steps
@@ -323,7 +361,7 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
                          "nvlink_floor_us": 2 * T * shape.top_k * shape.hidden * 4 * (world - 1) / world / 770e9 * 1e6,
                          "note": "floor = dispatch + combine bytes of one rank / measured 770 GB/s per direction",
                          "phases_ms_rank0": phases},
-            "extra": {"prefill_8192_tokens_total": strong},
+            "extra": {"prefill_8192_tokens_total": strong, "stack_prefill_4096_tokens": stack},
         }
         print(json.dumps(line), flush=True)
     be.close()

@@ -33,6 +33,7 @@ EXPORTS = [
     "tie_cuda_moe_ep_combine", "tie_cuda_route_noalloc", "tie_cuda_ep_region", "tie_cuda_ep_ipc_handle",
     "tie_cuda_ep_attach", "tie_cuda_ep_detach", "tie_cuda_ep_set_timeout_ms", "tie_cuda_ep_publish", "tie_cuda_ep_compute",
     "tie_cuda_ep_gather", "tie_cuda_moe_ffn_ep", "tie_cuda_mat_mat",
+    "tie_cuda_moe_block_inplace_ep",
 ]
 EP_HANDLE_BYTES = 64
 EP_PEER_POINTERS, EP_PEER_IPC_HANDLES = 0, 1
@@ -142,6 +143,8 @@ def load_library() -> ctypes.CDLL:
     L.tie_cuda_ep_gather.argtypes = [vp, vp, vp, u32]
     L.tie_cuda_moe_ffn_ep.restype = i32
     L.tie_cuda_moe_ffn_ep.argtypes = [vp, i32, vp, vp, i32, u32]
+    L.tie_cuda_moe_block_inplace_ep.restype = i32
+    L.tie_cuda_moe_block_inplace_ep.argtypes = [vp, i32, vp, i32, u32]
     L.tie_cuda_mat_mat.restype = i32
     L.tie_cuda_mat_mat.argtypes = [vp, vp, vp, vp, i32, i32, i32, u32]
     _lib = L
@@ -351,6 +354,10 @@ class MoeBackend:
 
     def moe_ffn_ep_ptr(self, layer_idx: int, x, out, n_tokens: int, flags: int = DEVICE):
         self._check(self.L.tie_cuda_moe_ffn_ep(self.h, layer_idx, _ptr(x), _ptr(out), n_tokens, flags), "tie_cuda_moe_ffn_ep")
+
+    def moe_block_inplace_ep_ptr(self, layer_idx: int, hidden, n_tokens: int, flags: int = DEVICE):
+        rc = self.L.tie_cuda_moe_block_inplace_ep(self.h, layer_idx, _ptr(hidden), n_tokens, flags)
+        self._check(rc, "tie_cuda_moe_block_inplace_ep")
 
     # -- math_dispatch rows --
     def make_current(self):
