@@ -244,6 +244,13 @@ def test_down_tensor_as_q4k_and_gate_up_as_q6k(small_shape, ref_silu_table, port
         b.upload_layer(0, layer)
         for p in (moe.PATH_STREAM, moe.PATH_TENSOR):
             _check_ffn(b.moe_ffn(0, x, path=p), ref_out)
+        # the decode kernels with these kinds: one token (the one-kernel step, then the chain), three tokens
+        l0 = b.launch_count
+        one = b.moe_ffn(0, x[:1])
+        assert b.launch_count - l0 == 1
+        _check_ffn(one, ref_out[:1])
+        _check_ffn(b.moe_ffn(0, x[:1], path=moe.PATH_DECODE_CHAIN), ref_out[:1])
+        _check_ffn(b.moe_ffn(0, x[:3]), ref_out[:3])
     finally:
         b.close()
 
