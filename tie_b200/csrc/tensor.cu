@@ -482,9 +482,8 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 				slot_of(2 * grp + 1, sb2, phb);
 				const long long te = TCT_NOW();
 				bool ok = true;
+				// (ring stages are handed back in pairs — one commit per two stages — on the odd stage's barrier)
 				if (it + 2 * grp >= (uint32_t)TC_S)
-					ok = tc_wait_warp(ptx::smem_u32(&sh->empty[sa]), pha ^ 1u, abort_flag, status, lane);
-				if (ok && it + 2 * grp + 1 >= (uint32_t)TC_S)
 					ok = tc_wait_warp(ptx::smem_u32(&sh->empty[sb2]), phb ^ 1u, abort_flag, status, lane);
 				if (!ok) {
 					alive = false;
@@ -531,8 +530,6 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 				slot_of(1, s1, ph1);
 				bool ok = true;
 				if (it >= (uint32_t)TC_S)
-					ok = tc_wait_warp(ptx::smem_u32(&sh->empty[s0]), ph0 ^ 1u, abort_flag, status, lane);
-				if (ok && it + 1 >= (uint32_t)TC_S)
 					ok = tc_wait_warp(ptx::smem_u32(&sh->empty[s1]), ph1 ^ 1u, abort_flag, status, lane);
 				if (!ok) {
 					alive = false;
@@ -763,8 +760,7 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 							ptx::mma_f16_ts_if(dP, ah + 8 * kk, xl + 2 * kk, idesc, 1u, leader);
 						ptx::mma_f16_ts_if(dP, al + 8 * kk, xh + 2 * kk, idesc_hi, 1u, leader);
 					}
-					ptx::mma_commit_if(ptx::smem_u32(&sh->empty[s0]), leader);
-					ptx::mma_commit_if(ptx::smem_u32(&sh->empty[s1]), leader);
+					ptx::mma_commit_if(ptx::smem_u32(&sh->empty[s1]), leader);  // both stages (a commit costs an MMA's issue time)
 					ptx::mma_commit_if(ptx::smem_u32(&sh->xempty), leader);
 					ptx::mma_commit_if(ptx::smem_u32(&sh->pfull[buf]), leader);
 					TCT_TRACE(3, gst - 2);
@@ -795,7 +791,8 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 						if (!concat)
 							ptx::mma_f16_ts_if(dP, a + 8 * kk, bl + 2 * kk, idesc, 1u, leader);
 					}
-					ptx::mma_commit_if(ptx::smem_u32(&sh->empty[s]), leader);
+					if (q4 & 1)  // stages go back to the producers and the token loader in pairs
+						ptx::mma_commit_if(ptx::smem_u32(&sh->empty[s]), leader);
 					TCT_ADD(3, ti);
 					TCT_TRACE(3, gst);
 					advance(1);
@@ -835,7 +832,7 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 						ptx::tma_load_3d(xq_hi, item.n_box == 16 ? &tq16 : (item.n_box == 32 ? &tq32 : &tq64), xb, 0, item.row0, 0);
 					}
 					const long long tw = TCT_NOW();
-					if (it >= (uint32_t)TC_S && !tc_wait<100>(ptx::smem_u32(&sh->empty[s]), ph ^ 1u, abort_flag, status)) {
+					if (it >= (uint32_t)TC_S && !tc_wait<100>(ptx::smem_u32(&sh->empty[s | 1]), ph ^ 1u, abort_flag, status)) {
 						alive = false;
 						break;
 					}
