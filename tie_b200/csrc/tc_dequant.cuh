@@ -52,10 +52,6 @@ __device__ __forceinline__ Q4kConsts q4k_int_consts(int s_lo, int s_hi)
 // lo[0] = bytes (0, 2), lo[1] = bytes (1, 3) of the low nibbles; hi[] the same of the high ones.
 __device__ __forceinline__ void q4k_int_word(uint32_t w, const Q4kConsts &c, uint32_t lo[2], uint32_t hi[2])
 {
-#ifdef TC_EXP_NOALU
-	lo[0] = w; lo[1] = w; hi[0] = w; hi[1] = w;
-	return;
-#endif
 	const uint32_t w8 = w >> 8;
 	lo[0] = h2_bits(__hfma2(bits_h2((w & 0x000F000Fu) | 0x64006400u), c.sl, c.cl));
 	lo[1] = h2_bits(__hfma2(bits_h2((w8 & 0x000F000Fu) | 0x64006400u), c.sl, c.cl));
@@ -67,10 +63,6 @@ __device__ __forceinline__ void q4k_int_word(uint32_t w, const Q4kConsts &c, uin
 // out[1] = bytes (1, 3).  s = half2(sc), c = half2(-96 sc).
 __device__ __forceinline__ void q6k_int_word(uint32_t q, __half2 s, __half2 c, uint32_t out[2])
 {
-#ifdef TC_EXP_NOALU
-	out[0] = q; out[1] = q;
-	return;
-#endif
 	out[0] = h2_bits(__hfma2(bits_h2(((q << 4) & 0x03F003F0u) | 0x54005400u), s, c));
 	out[1] = h2_bits(__hfma2(bits_h2(((q >> 4) & 0x03F003F0u) | 0x54005400u), s, c));
 }

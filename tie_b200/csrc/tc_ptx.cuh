@@ -183,10 +183,6 @@ __device__ __forceinline__ void mma_f16_ts_if(uint32_t d_tmem, uint32_t a_tmem, 
 // 4 consecutive 32-bit columns of this thread's TMEM lane.
 __device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
 {
-#ifdef TC_EXP_NOST
-	asm volatile("" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-	return;
-#endif
 	asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d)
 		     : "memory");
 }
