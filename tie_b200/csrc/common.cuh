@@ -135,7 +135,7 @@ struct tie_cuda_ctx {
 	bool prof_on = false;
 	cudaEvent_t prof_ev[8] = {nullptr};
 	bool prof_set[8] = {false};
-	char cuda_err[256] = {0};
+	char cuda_err[1024] = {0};
 	// tensor maps for the tcgen05 path: (x, h, sums of x, sums of h) x (16-, 32-, 64-row boxes)
 	CUtensorMap tmap[12];
 	bool tmaps_ok = false;
