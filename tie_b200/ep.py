@@ -162,6 +162,34 @@ class PeerEpMoeBlock:
         return torch.as_tensor(_View(), device=torch.device("cuda", self.be.cfg.device))
 
 
+NVLINK_GBS = 770.0  # measured peer-copy rate per direction on this pool's B200s
+
+
+def _step_roofline(shape, tokens_per_rank, world, ms_per_step, flops_total, peaks):
+    rows = tokens_per_rank * shape.top_k
+    nvlink_bytes = rows * shape.hidden * 4 * (world - 1) / world
+    hbm_bytes = (shape.n_expert // world) * shape.expert_bytes + shape.router_bytes + 2 * tokens_per_rank * shape.hidden * 4
+    t_nvlink = nvlink_bytes / (NVLINK_GBS * 1e9)
+    t_hbm = hbm_bytes / (peaks["hbm_gbs"] * 1e9)
+    t_tensor = (flops_total / world) / (peaks["bf16_tflops"] * 1e12)
+    floors = {"nvlink": t_nvlink, "hbm": t_hbm, "tensor": t_tensor}
+    bound = max(floors, key=floors.get)
+    t = ms_per_step * 1e-3
+    if bound == "nvlink":
+        achieved, peak, unit = nvlink_bytes / t / 1e9, NVLINK_GBS, "GB/s"
+    elif bound == "hbm":
+        achieved, peak, unit = hbm_bytes / t / 1e9, peaks["hbm_gbs"], "GB/s"
+    else:
+        achieved, peak, unit = flops_total / world / t / 1e12, peaks["bf16_tflops"], "TFLOP/s"
+    return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak, "traffic": None,
+            "floors_us": {k: v * 1e6 for k, v in floors.items()},
+            "nvlink": {"bytes_per_direction": nvlink_bytes, "achieved_gbs": nvlink_bytes / t / 1e9, "peak_gbs": NVLINK_GBS},
+            "note": "one rank's whole step against the slowest of its floors (rows over NVLink in one direction at the measured "
+                    "770 GB/s peer copy, algorithmic HBM bytes at the measured copy rate, flops at the measured bf16 GEMM rate); "
+                    "the per-kernel HBM roofline is reported by the 1-GPU run",
+            "algorithmic_tflops": flops_total / t / 1e12}
+
+
 def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
     """bench.py --gpus N under torchrun: weak scaling, `tokens_per_rank` tokens on every rank,
     experts sharded.  Rank 0 prints the JSON line."""
@@ -351,9 +379,10 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
             "e2e": {"value": T * world / e2e_s, "unit": unit, "h2d_bytes_per_step": T * shape.hidden * 4 * world,
                     "d2h_bytes_per_step": T * shape.hidden * 4 * world, "ms_per_step": e2e_s * 1e3},
             "gpu_launches": int(launches),
-            "roofline": {"bound": "hbm", "achieved": None, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": None, "traffic": None,
-                         "note": "per-kernel roofline is reported by the 1-GPU run; here: whole-block algorithmic TFLOP/s",
-                         "algorithmic_tflops": flops / (ms_per_step * 1e-3) / 1e12},
+            # the whole step of one rank against the slower of its three floors: rows over NVLink (one
+            # direction: rows in and rows out travel opposite ways), its share of the packed weights and
+            # its rows' operands from HBM, its flops on the tensor cores
+            "roofline": _step_roofline(shape, T, world, ms_per_step, flops, peaks),
             "cpu_baseline": None,
             "exchange": {"rows_per_rank": T * shape.top_k, "bytes_per_row": shape.hidden * 4,
                          "remote_fraction": (world - 1) / world,
