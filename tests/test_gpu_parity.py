@@ -369,6 +369,28 @@ def test_block_inplace(be, layer0, golden):
     _check_ffn(out, g["hidden_out"], tol=TOL)
 
 
+def test_block_inplace_one_token_norm_inside_the_one_kernel_step(be, layer0, golden):
+    """One token: the RMSNorm runs inside the cooperative decode kernel (one launch for
+    h += MoE(RMSNorm(h))); identical bits to the RMSNorm kernel + three-kernel chain."""
+    import torch
+    from tie_b200 import moe
+    g = golden("block_inplace.npz")
+    be.upload_layer(1, layer0, ffn_norm_w=g["norm_w"])
+    h0 = torch.from_numpy(g["hidden_in"][:1].copy()).cuda()
+    a, b = h0.clone(), h0.clone()
+    l0 = be.launch_count
+    be.moe_block_inplace_ptr(1, a, 1, moe.DEVICE)
+    l1 = be.launch_count
+    be.moe_block_inplace_ptr(1, b, 1, moe.DEVICE | moe.PATH_DECODE_CHAIN)
+    assert (l1 - l0, be.launch_count - l1) == (1, 4)
+    assert np.array_equal(bits(a.cpu().numpy()), bits(b.cpu().numpy()))
+    _check_ffn(a.cpu().numpy(), g["hidden_out"][:1], tol=TOL)
+    for _ in range(3):  # graph replay, in place: each pass feeds the next
+        be.moe_block_inplace_ptr(1, a, 1, moe.DEVICE | moe.GRAPH)
+        be.moe_block_inplace_ptr(1, b, 1, moe.DEVICE | moe.GRAPH | moe.PATH_DECODE_CHAIN)
+    assert np.array_equal(bits(a.cpu().numpy()), bits(b.cpu().numpy()))
+
+
 def test_two_blocks_chained_teacher_forced(be, layer0, port_lib, ref_silu_table):
     """Two blocks back to back on the device (prefill- and decode-sized), each block checked
     against the oracle fed with the GPU's own input to that block (teacher forcing: a 1e-7

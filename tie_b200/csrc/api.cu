@@ -822,6 +822,19 @@ int tie_cuda_moe_block_inplace(tie_cuda_ctx *c, int layer, float *hidden_dev, in
 	GraphKey k = {3, layer, n_tokens, hidden_dev, nullptr, nullptr, nullptr,
 		      flags & (TIE_CUDA_PATH_MASK | TIE_CUDA_PATH_LEGACY_STREAM | TIE_CUDA_PATH_DECODE_CHAIN)};
 	TRY(run_maybe_graphed(c, flags & TIE_CUDA_GRAPH, k, [&]() -> int {
+		// one token: the RMSNorm is part of the one-kernel step
+		if ((flags & TIE_CUDA_PATH_MASK) != TIE_CUDA_PATH_TENSOR &&
+		    !(flags & (TIE_CUDA_PATH_LEGACY_STREAM | TIE_CUDA_PATH_DECODE_CHAIN | TIE_CUDA_ROUTE_LFM2)) &&
+		    decode_fused_supported(c, *L, n_tokens)) {
+			const int rc = launch_decode_fused(c, *L, hidden_dev, nullptr, hidden_dev, hidden_dev, L->norm_w, c->cfg.norm_eps);
+			if (rc != TIE_CUDA_ENOTSUP) {
+				if (!rc) {
+					c->last_used_tc = false;
+					c->last_direct_rows = c->cfg.top_k;
+				}
+				return rc;
+			}
+		}
 		TRY(launch_rms_norm(c, hidden_dev, L->norm_w, c->s.x, n_tokens));
 		return moe_ffn_device(c, *L, c->s.x, hidden_dev, n_tokens, nullptr, hidden_dev, flags);
 	}));

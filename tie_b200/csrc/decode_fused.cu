@@ -60,18 +60,21 @@ struct DfShared {
 	float lg[256];	// the logits (n_expert <= 256)
 	unsigned base;
 	int ok;
+	float inv;  // 1 / rms of the row (RMSNorm in the kernel)
 };
 
 struct DfArgs {
 	const uint8_t *wg, *wu, *wd;
 	size_t stride_gu, stride_dn;  // bytes per expert
 	const float *x, *router_w, *bias, *residual, *silu;
+	const float *norm_w;  // norm_eps >= 0: x is the un-normed hidden row, RMSNorm (weights norm_w or 1) happens in the kernel
+	float norm_eps;
 	float *logits, *h, *out, *topk_w;
 	int *topk_idx;
 	unsigned *status, *sync;  // sync[0]: arrivals, sync[1]: epoch
 	int n_expert, top_k, first_expert, n_local;
 	int rpt_gu, tiles_gu, rpt_dn, tiles_dn;
-	uint32_t off_b, off_c, off_v;  // shared-memory offsets of the down tiles, the staged x, the slot products
+	uint32_t off_b, off_c, off_v, off_n;  // shared-memory offsets: down tiles, staged x, slot products, normed x
 };
 
 __device__ __forceinline__ unsigned df_ld_acquire(const unsigned *p)
@@ -154,13 +157,41 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 		sh.base = df_ld_acquire(a.sync + 1);
 	}
 
+	// ---------------- (RMSNorm of the row, every CTA for itself: rms_norm_f32_f32_f32_avx2, math_avx2.c:56-97) ----------------
+	const float *xin = a.x;
+	if (a.norm_eps >= 0.0f) {
+		float *xn = reinterpret_cast<float *>(dsm + a.off_n);
+		for (int i = tid; i < K / 4; i += DF_THREADS)
+			reinterpret_cast<float4 *>(xn)[i] = __ldcg(reinterpret_cast<const float4 *>(a.x) + i);  // (the row is overwritten in place at the end)
+		__syncthreads();
+		if (warp == 0) {
+			float acc = 0.0f;
+			if (lane < 8) {
+#pragma unroll 16
+				for (int i = 0; i < K / 8; i++) {
+					const float v = xn[8 * i + lane];
+					acc = __fmaf_rn(v, v, acc);
+				}
+			}
+			const float ss = hsum8_lanes(acc);  // (l + l4), then + 1, then + 2: the reference's tree
+			if (lane == 0)
+				sh.inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), a.norm_eps)));
+		}
+		__syncthreads();
+		const float inv = sh.inv;
+		for (int i = tid; i < K; i += DF_THREADS)
+			xn[i] = __fmul_rn(__fmul_rn(xn[i], a.norm_w ? a.norm_w[i] : 1.0f), inv);
+		__syncthreads();
+		xin = xn;
+	}
+
 	// ---------------- R: one router logit per CTA ----------------
 	if (cta < a.n_expert) {
 		float *ws = reinterpret_cast<float *>(dsm), *xr = ws + K;
 		const float4 *w4 = reinterpret_cast<const float4 *>(a.router_w + (size_t)cta * K);
-		const float4 *x4 = reinterpret_cast<const float4 *>(a.x);
+		const float4 *x4 = reinterpret_cast<const float4 *>(xin);
 		for (int i = tid; i < K / 4; i += DF_THREADS) {
-			const float4 wv = __ldg(w4 + i), xv = __ldg(x4 + i);
+			const float4 wv = __ldg(w4 + i), xv = x4[i];
 			reinterpret_cast<float4 *>(ws)[i] = wv;
 			reinterpret_cast<float4 *>(xr)[i] = xv;
 		}
@@ -181,7 +212,7 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 		}
 	}
 	if (gu_role)
-		stage_x_lane_major<KG, DK::LPR>(a.x, xs, DK::PARTS, tid, DF_THREADS);
+		stage_x_lane_major<KG, DK::LPR>(xin, xs, DK::PARTS, tid, DF_THREADS);
 	const unsigned base = (__syncthreads(), sh.base);
 	DF_STAMP(1);
 	if (!df_grid_barrier(a.sync, base + (unsigned)G, &sh, a.status))
@@ -387,7 +418,7 @@ static size_t df_row_bytes(int k)
 
 struct DfPlan {
 	int rpt_gu, tiles_gu, rpt_dn, tiles_dn, grid;
-	size_t smem, off_b, off_c, off_v;
+	size_t smem, off_b, off_c, off_v, off_n;
 	bool ok;
 };
 
@@ -419,14 +450,15 @@ static DfPlan df_plan(const tie_cuda_ctx *c)
 	p.off_b = (area_a + 127) / 128 * 128;
 	p.off_c = (p.off_b + (size_t)top_k * tile_dn + 127) / 128 * 128;
 	p.off_v = p.off_c + (size_t)DfDims<K>::LPR * 64 * sizeof(float);
-	p.smem = p.off_v + (size_t)top_k * p.rpt_dn * sizeof(float);
+	p.off_n = (p.off_v + (size_t)top_k * p.rpt_dn * sizeof(float) + 15) / 16 * 16;
+	p.smem = p.off_n + (size_t)K * sizeof(float);
 	p.ok = p.smem <= 220 * 1024;
 	return p;
 }
 
 template <WKind KG, int K, WKind KD, int F>
 static int df_launch(tie_cuda_ctx *c, const Layer &L, const float *x, const float *bias, const float *residual, float *out,
-		     bool query_only)
+		     bool query_only, const float *norm_w, float norm_eps)
 {
 	const DfPlan p = df_plan<KG, K, KD, F>(c);
 	if (!p.ok)
@@ -463,6 +495,9 @@ static int df_launch(tie_cuda_ctx *c, const Layer &L, const float *x, const floa
 	a.off_b = (uint32_t)p.off_b;
 	a.off_c = (uint32_t)p.off_c;
 	a.off_v = (uint32_t)p.off_v;
+	a.off_n = (uint32_t)p.off_n;
+	a.norm_w = norm_w;
+	a.norm_eps = norm_eps;
 	auto kern = decode1_fused<KG, K, KD, F>;
 	TIE_CUDA_TRY(c, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
 	cudaLaunchConfig_t cfg = {};
@@ -491,7 +526,7 @@ static int df_launch(tie_cuda_ctx *c, const Layer &L, const float *x, const floa
 #define TIE_DF_SHAPES(X) X(2048, 768) X(512, 256)
 
 static int df_dispatch(tie_cuda_ctx *c, const Layer &L, const float *x, const float *bias, const float *residual, float *out,
-		       bool query_only)
+		       bool query_only, const float *norm_w = nullptr, float norm_eps = -1.0f)
 {
 	if (L.gate.kind != L.up.kind)
 		return TIE_CUDA_ENOTSUP;
@@ -499,12 +534,12 @@ static int df_dispatch(tie_cuda_ctx *c, const Layer &L, const float *x, const fl
 #define X(KK, FF)                                                                                                              \
 	if (K == KK && F == FF) {                                                                                              \
 		if (L.gate.kind == W_Q4K && L.down.kind == W_Q6K_R8)                                                           \
-			return df_launch<W_Q4K, KK, W_Q6K_R8, FF>(c, L, x, bias, residual, out, query_only);                    \
+			return df_launch<W_Q4K, KK, W_Q6K_R8, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps);                    \
 		if (L.gate.kind == W_Q4K && L.down.kind == W_Q4K)                                                              \
-			return df_launch<W_Q4K, KK, W_Q4K, FF>(c, L, x, bias, residual, out, query_only);                      \
+			return df_launch<W_Q4K, KK, W_Q4K, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps);                      \
 		if (L.gate.kind == W_Q6K_R8 && L.down.kind == W_Q6K_R8)                                                        \
-			return df_launch<W_Q6K_R8, KK, W_Q6K_R8, FF>(c, L, x, bias, residual, out, query_only);                \
-		return df_launch<W_Q6K_R8, KK, W_Q4K, FF>(c, L, x, bias, residual, out, query_only);                           \
+			return df_launch<W_Q6K_R8, KK, W_Q6K_R8, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps);                \
+		return df_launch<W_Q6K_R8, KK, W_Q4K, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps);                           \
 	}
 	TIE_DF_SHAPES(X)
 #undef X
@@ -518,9 +553,11 @@ bool decode_fused_supported(tie_cuda_ctx *c, const Layer &L, int n_tokens)
 	return df_dispatch(c, L, nullptr, nullptr, nullptr, nullptr, true) == TIE_CUDA_OK;
 }
 
-int launch_decode_fused(tie_cuda_ctx *c, const Layer &L, const float *x, const float *bias, const float *residual, float *out)
+// norm_eps >= 0: x is the un-normed hidden row; the kernel applies RMSNorm (norm_w, or weight 1) first.
+int launch_decode_fused(tie_cuda_ctx *c, const Layer &L, const float *x, const float *bias, const float *residual, float *out,
+			const float *norm_w, float norm_eps)
 {
-	return df_dispatch(c, L, x, bias, residual, out, false);
+	return df_dispatch(c, L, x, bias, residual, out, false, norm_w, norm_eps);
 }
 
 }  // namespace tie

@@ -17,7 +17,8 @@ int launch_decode_down_combine(tie_cuda_ctx *c, const Layer &L, int n_tokens, co
 int launch_router_rows(tie_cuda_ctx *c, const float *x, const float *w, int n_rows, int in_dim, float *out);
 // decode_fused.cu
 bool decode_fused_supported(tie_cuda_ctx *c, const Layer &L, int n_tokens);
-int launch_decode_fused(tie_cuda_ctx *c, const Layer &L, const float *x, const float *bias, const float *residual, float *out);
+int launch_decode_fused(tie_cuda_ctx *c, const Layer &L, const float *x, const float *bias, const float *residual, float *out,
+			const float *norm_w = nullptr, float norm_eps = -1.0f);
 // sort.cu
 struct SortBufs {
 	int *counts, *offsets, *tile_start, *active, *n_active, *perm;
