@@ -358,6 +358,18 @@ def main():
                            "algorithmic_tflops": fl_ops / (ms * 1e-3) / 1e12,
                            "tensor_frac": fl_ops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
                            "l2": "flushed between steps" if fl else "weights 392 MB > 126 MB L2"}
+            if tt == 1:
+                # the same call as the reference's decode loop makes it: host pointers, synchronous
+                xh = torch.from_numpy(synth.make_x(workloads.BASE_SEED, 1)).pin_memory()
+                oh = torch.empty_like(xh).pin_memory()
+                for _ in range(5):
+                    be.moe_ffn_ptr(0, xh, oh, 1, moe.HOST | moe.GRAPH)
+                t0 = time.perf_counter()
+                for _ in range(steps):
+                    be.moe_ffn_ptr(0, xh, oh, 1, moe.HOST | moe.GRAPH)
+                e2e_us = (time.perf_counter() - t0) / steps * 1e6
+                extra[name]["e2e_host_pointers"] = {"us_per_step": e2e_us, "tokens_per_s": 1e6 / e2e_us,
+                                                    "note": "8 KB in, 8 KB out, L2 warm (no flush between calls)"}
 
     # ---- side run: the 48-block stack, h += MoE(RMSNorm(h)) per block, residual stream on the device ----
     if not args.no_extra and args.stack_layers > 0:

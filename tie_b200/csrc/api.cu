@@ -98,6 +98,8 @@ int alloc_scratch(tie_cuda_ctx *c)
 	TIE_CUDA_TRY(c, cudaMallocHost(reinterpret_cast<void **>(&c->pin_idx), R * sizeof(int)));
 	TIE_CUDA_TRY(c, cudaMallocHost(reinterpret_cast<void **>(&c->pin_w), R * sizeof(float)));
 	TIE_CUDA_TRY(c, cudaMallocHost(reinterpret_cast<void **>(&c->pin_logits), T * E * sizeof(float)));
+	TIE_CUDA_TRY(c, cudaMallocHost(reinterpret_cast<void **>(&c->pin_status), sizeof(unsigned)));
+	*c->pin_status = 0;
 	return TIE_CUDA_OK;
 }
 
@@ -174,11 +176,26 @@ bool is_pinned_host(const void *p)
 	return a.type == cudaMemoryTypeHost;
 }
 
+int report_status(tie_cuda_ctx *c, unsigned st);
+
 int check_status(tie_cuda_ctx *c)
 {
 	unsigned st = 0;
 	TIE_CUDA_TRY(c, cudaMemcpyAsync(&st, c->s.status, sizeof(st), cudaMemcpyDeviceToHost, c->stream));
 	TIE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+	return report_status(c, st);
+}
+
+// The status word was copied to pinned memory by the stream's last operation (host-pointer calls:
+// one synchronisation for the results and the status together).
+int check_status_pinned(tie_cuda_ctx *c)
+{
+	TIE_CUDA_TRY(c, cudaStreamSynchronize(c->stream));
+	return report_status(c, *static_cast<volatile unsigned *>(c->pin_status));
+}
+
+int report_status(tie_cuda_ctx *c, unsigned st)
+{
 	if (st) {
 		snprintf(c->cuda_err, sizeof(c->cuda_err), "device status word 0x%x (%s%s%s)", st,
 			 (st & ST_BAD_EXPERT) ? "expert id out of range " : "", (st & ST_WAIT_TIMEOUT) ? "barrier wait timed out " : "",
@@ -624,7 +641,7 @@ void tie_cuda_destroy(tie_cuda_ctx *c)
 	for (void *p : dev_ptrs)
 		if (p)
 			cudaFree(p);
-	void *pin_ptrs[] = {c->pin_x, c->pin_out, c->pin_idx, c->pin_w, c->pin_logits};
+	void *pin_ptrs[] = {c->pin_x, c->pin_out, c->pin_idx, c->pin_w, c->pin_logits, c->pin_status};
 	for (void *p : pin_ptrs)
 		if (p)
 			cudaFreeHost(p);
@@ -799,9 +816,10 @@ int tie_cuda_moe_ffn_biased(tie_cuda_ctx *c, int layer, const float *x, float *o
 		TIE_CUDA_TRY(c, cudaMemcpyAsync(c->s.x, src, bytes, cudaMemcpyHostToDevice, c->stream));
 		TRY(moe_ffn_device(c, *L, c->s.x, c->s.out, n_tokens, bias_dev, nullptr, flags));
 		TIE_CUDA_TRY(c, cudaMemcpyAsync(dst, c->s.out, bytes, cudaMemcpyDeviceToHost, c->stream));
+		TIE_CUDA_TRY(c, cudaMemcpyAsync(c->pin_status, c->s.status, sizeof(unsigned), cudaMemcpyDeviceToHost, c->stream));
 		return TIE_CUDA_OK;
 	}));
-	TRY(check_status(c));
+	TRY(check_status_pinned(c));
 	if (!out_pinned)
 		memcpy(out, c->pin_out, bytes);
 	return TIE_CUDA_OK;

@@ -127,6 +127,7 @@ struct tie_cuda_ctx {
 	float *pin_x = nullptr, *pin_out = nullptr;
 	int *pin_idx = nullptr;
 	float *pin_w = nullptr, *pin_logits = nullptr;
+	unsigned *pin_status = nullptr;
 	size_t weight_bytes = 0;
 	uint64_t launches = 0;
 	int last_direct_rows = -1;
