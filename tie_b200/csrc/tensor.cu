@@ -157,6 +157,9 @@ __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile 
 template <int BACKOFF_NS = 0>
 __device__ __forceinline__ bool tc_wait_warp(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, unsigned *status, int lane)
 {
+	// usually the barrier has flipped already: every lane tests once and the warp votes, without diverging
+	if (__all_sync(0xffffffffu, ptx::mbar_try_wait(bar, parity)))
+		return true;
 	int ok = 1;
 	if (lane == 0)
 		ok = tc_wait<BACKOFF_NS>(bar, parity, abort_flag, status) ? 1 : 0;
@@ -771,10 +774,16 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 				}
 				for (int q4 = 0; q4 < TC_SPB; q4++) {
 					const long long tb = TCT_NOW();
-					bool ok = tc_wait(ptx::smem_u32(&sh->bfull[s]), ph, abort_flag, status);
+					// both tests issued back to back; the bounded waits only when one of them fails
+					const bool okb = ptx::mbar_try_wait(ptx::smem_u32(&sh->bfull[s]), ph);
+					const bool okf = ptx::mbar_try_wait(ptx::smem_u32(&sh->full[s]), ph);
+					bool ok = true;
+					if (!okb)
+						ok = tc_wait(ptx::smem_u32(&sh->bfull[s]), ph, abort_flag, status);
 					TCT_ADD(1, tb);
 					const long long tf = TCT_NOW();
-					ok = ok && tc_wait(ptx::smem_u32(&sh->full[s]), ph, abort_flag, status);
+					if (ok && !okf)
+						ok = tc_wait(ptx::smem_u32(&sh->full[s]), ph, abort_flag, status);
 					if (!__all_sync(0xffffffffu, ok)) {
 						alive = false;
 						break;
