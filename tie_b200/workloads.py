@@ -70,7 +70,7 @@ def algorithmic_flops(shape: synth.MoeShape, n_tokens: int) -> int:
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the two grouped GEMM kernels on the
 # 512-token prefill workload, from the ncu capture summarised in
 # profiles/grouped_gemm_sb_prefill512.md (bench.py reports them as roofline.traffic).
-NCU_DRAM_BYTES_PER_LAUNCH = {"gate_up_tc": 282011136, "down_tc": 197603072}
+NCU_DRAM_BYTES_PER_LAUNCH = {"gate_up_tc": 282442752, "down_tc": 197401600}
 
 
 def _main() -> None:
