@@ -190,7 +190,10 @@ int tie_cuda_moe_ep_combine(tie_cuda_ctx *c, const float *y_sorted, const float 
  * computes, then all gathers) — a wait is then always already satisfied; on separate GPUs the
  * ranks run freely.  Every wait is bounded (tie_cuda_ep_set_timeout_ms, default 5 s): a rank that
  * never arrives makes the others return TIE_CUDA_EKERNEL with their contexts usable; the group
- * must then detach and attach again before its next step. */
+ * must then detach and attach again before its next step.  tie_cuda_ep_attach starts a new
+ * epoch (step counter and flags of the calling rank's region back to zero), so attach is
+ * collective: all ranks detach, host barrier, all ranks attach, host barrier, first publish —
+ * the barriers keep a peer's flag store from crossing a rank's reset. */
 #define TIE_CUDA_EP_HANDLE_BYTES 64
 #define TIE_CUDA_EP_PEER_POINTERS 0
 #define TIE_CUDA_EP_PEER_IPC_HANDLES 1
@@ -251,15 +254,18 @@ int tie_cuda_dispatch_status(void); /* 0, or the TIE_CUDA_E* of the last failing
  *
  * The caller passes every input and output (device memory on the current device): x
  * [n_tokens][hidden], router_w [n_expert][hidden], router_bias [n_expert] or NULL, topk_idx /
- * topk_w [n_tokens][top_k].  Work is enqueued on cuda_stream (NULL = legacy default stream)
- * and the call returns without synchronising.
+ * topk_w [n_tokens][top_k].  x and router_w are read with 128-bit loads and must be 16-byte
+ * aligned (rows then are, hidden being a multiple of 8); the other pointers 4-byte aligned.  A
+ * pointer that is not gets TIE_CUDA_EINVAL, not a fault on the device.  Work is enqueued on
+ * cuda_stream (NULL = legacy default stream) and the call returns without synchronising.
  *
  * The first call on each device looks up the device address of the scratch array and sets a
  * kernel attribute (the device must be current); that first call should come before any stream
- * capture.  All calls on a device share the one scratch array: it keeps the previous call's
- * contents (every element a call reads it has written first, so nothing needs clearing), and two
- * calls whose kernels overlap on the GPU (for instance on different streams) race on it.
- * Serialise them. */
+ * capture.  Host threads may make their first calls concurrently (the set-up is done under a
+ * lock, once per device).  All calls on a device share the one scratch array: it keeps the
+ * previous call's contents (every element a call reads it has written first, so nothing needs
+ * clearing), and two calls whose kernels overlap on the GPU (for instance on different streams,
+ * or from two host threads) race on it.  Serialise them. */
 int tie_cuda_route_noalloc(const float *x_dev, const float *router_w_dev, const float *router_bias_dev, int n_tokens,
 			   int hidden, int n_expert, int top_k, int *topk_idx_dev, float *topk_w_dev, void *cuda_stream);
 

@@ -165,3 +165,87 @@ def test_library_exports_what_the_header_declares():
     out = subprocess.check_output(["nm", "-D", "--defined-only", gguf.build()], text=True)
     exported = {l.split()[-1] for l in out.splitlines() if " T " in l and "tie_gguf_" in l}
     assert declared == exported == set(gguf.EXPORTS)
+
+
+# ---- the same file through the reference's own parser ----
+
+def _ref_gguf_lib():
+    """The compiled reference (oracle/_ref/libtie_ref.so holds its gguf.c unmodified), or None."""
+    import ctypes
+    from oracle import ref
+    if not ref.available():
+        return None
+    L = ctypes.CDLL(ref.LIB_PATH)
+    L.gguf_model_parse.restype = ctypes.c_void_p
+    L.gguf_model_parse.argtypes = [ctypes.c_char_p]
+    L.gguf_get_tensor.restype = ctypes.c_void_p
+    L.gguf_get_tensor.argtypes = [ctypes.c_void_p, ctypes.c_char_p]
+    L.gguf_metadata_get_value.restype = ctypes.c_int
+    L.gguf_metadata_get_value.argtypes = [ctypes.c_void_p, ctypes.c_char_p, ctypes.c_void_p]
+    L.gguf_metadata_get_string.restype = ctypes.c_char_p
+    L.gguf_metadata_get_string.argtypes = [ctypes.c_void_p, ctypes.c_char_p]
+    L.gguf_model_close.argtypes = [ctypes.c_void_p]
+    return L
+
+
+def test_reader_agrees_with_the_reference_parser_on_the_same_file(tmp_path):
+    """One file, two readers: the reference's gguf_model_parse / gguf_get_tensor (gguf.c:892-1047,
+    compiled unmodified into oracle/_ref) and tie_gguf_open.  Tensor types, dims, byte sizes, the
+    position of every MoE tensor in the file and its bytes must agree, and so must the metadata
+    keys the Qwen3-MoE loader reads (model_qwen3.c:54-63).  The reference places the data section
+    on a 32-byte boundary whatever general.alignment says (gguf.c:941), so the file uses 32."""
+    import ctypes
+    L = _ref_gguf_lib()
+    if L is None:
+        pytest.skip("oracle/_ref/libtie_ref.so not built (needs the reference sources)")
+
+    class RefTensor(ctypes.Structure):  # GGUFTensor, gguf.h:82-90
+        _fields_ = [("name", ctypes.c_char_p), ("dimensions", ctypes.c_uint64 * 4), ("n_dims", ctypes.c_uint32),
+                    ("type", ctypes.c_uint32), ("data", ctypes.c_void_p), ("offset", ctypes.c_int64), ("size", ctypes.c_size_t)]
+
+    class RefModel(ctypes.Structure):  # struct GGUFModel, main.h:79-94 (leading fields)
+        _fields_ = [("fd", ctypes.c_int), ("file_size", ctypes.c_size_t), ("mapped_data", ctypes.c_void_p), ("fptr", ctypes.c_void_p),
+                    ("metadata_num", ctypes.c_uint64), ("tensor_count", ctypes.c_uint64), ("tensor_loaded", ctypes.c_uint64),
+                    ("tensor_data_offset", ctypes.c_uint64)]
+
+    kvs, tensors, _ = moe_model(SHAPE, 2, down_types=[synth.GGML_Q6_K, synth.GGML_Q4_K])
+    # real model files carry general.basename, and the reference's detect_architecture (model.c:65-96)
+    # reads it without a NULL check for the "qwen3" family
+    kvs = kvs + [("general.basename", "str", "Qwen3")]
+    p = str(tmp_path / "m.gguf")
+    write_gguf(p, kvs, tensors, version=3, align=32)
+    raw = open(p, "rb").read()
+    rg = L.gguf_model_parse(p.encode())
+    assert rg, "the reference's parser refused the file"
+    try:
+        rm = RefModel.from_address(rg)
+        with gguf.GgufFile(p) as g:
+            assert rm.tensor_count == g.n_tensors and rm.metadata_num == g.n_kv and rm.file_size == len(raw)
+            # metadata of model_qwen3.c:54-63, read the way the reference's loader does (memcpy of the stored value)
+            cfg = g.moe_config()
+            for key, want in (("qwen3moe.block_count", cfg["n_layers"]), ("qwen3moe.embedding_length", cfg["hidden"]),
+                              ("qwen3moe.expert_count", cfg["n_expert"]), ("qwen3moe.expert_used_count", cfg["top_k"]),
+                              ("qwen3moe.expert_feed_forward_length", cfg["ffn_dim"])):
+                v = ctypes.c_uint32(0)
+                assert L.gguf_metadata_get_value(rg, key.encode(), ctypes.byref(v)) == 0
+                assert v.value == want == g.get_int(key)
+            eps = ctypes.c_float(0)
+            assert L.gguf_metadata_get_value(rg, b"qwen3moe.attention.layer_norm_rms_epsilon", ctypes.byref(eps)) == 0
+            assert eps.value == np.float32(cfg["norm_eps"])
+            assert L.gguf_metadata_get_string(rg, b"general.architecture").decode() == cfg["arch"]
+            names = [f"blk.{i}.{t}.weight" for i in range(2)
+                     for t in ("ffn_gate_inp", "ffn_gate_exps", "ffn_up_exps", "ffn_down_exps", "ffn_norm", "attn_q")]
+            for name in names + ["token_embd.weight"]:
+                rt_p = L.gguf_get_tensor(rg, name.encode())
+                assert rt_p, name
+                rt = RefTensor.from_address(rt_p)
+                data, typ, dims = g.tensor(name)
+                assert typ == rt.type and rt.n_dims == len(dims) and list(rt.dimensions[:rt.n_dims]) == dims, name
+                assert data.nbytes == rt.size, name
+                off = rt.data - rm.mapped_data  # where the reference reads the tensor from
+                assert off == rm.tensor_data_offset + rt.offset
+                mine = np.frombuffer(data, dtype=np.uint8) if not isinstance(data, np.ndarray) else data.view(np.uint8).reshape(-1)
+                assert bytes(mine[:64]) == raw[off:off + 64] and bytes(mine[-64:]) == raw[off + rt.size - 64:off + rt.size], name
+                assert bytes(mine) == raw[off:off + rt.size], name
+    finally:
+        L.gguf_model_close(rg)

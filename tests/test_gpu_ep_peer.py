@@ -140,6 +140,47 @@ def test_absent_rank_times_out_and_reports(small_shape, ref_silu_table):
             b.close()
 
 
+def test_group_recovers_after_a_time_out_by_detach_and_attach(small_shape, small_layer, ref_silu_table, port_lib):
+    """After an absent-rank time-out the ranks' step numbers differ (rank 0 published, rank 1 did
+    not) and rank 0's flags are stale.  Detach + attach on every rank starts a new epoch: the next
+    step is correct, on both ranks, and so is the one after it."""
+    import torch
+    from tie_b200 import moe
+    shape = small_shape
+    bes = _ranks(shape, workloads.BASE_SEED + 1, 2, 64, ref_silu_table)
+    try:
+        # one good step, so that flags and counters are non-zero before the failure
+        xh = [synth.make_x(5, n, shape.hidden, first_token=10 * r) for r, n in enumerate([12, 7])]
+        xs = [torch.from_numpy(x).cuda() for x in xh]
+        outs = [torch.empty_like(x) for x in xs]
+        _step(bes, xs, outs)
+        bes[0].ep_set_timeout_ms(50)
+        bes[0].ep_publish_ptr(0, xs[0], 12, None, moe.DEVICE | moe.NO_SYNC)
+        with pytest.raises(moe.TieCudaError) as ei:
+            bes[0].ep_compute(0, moe.DEVICE)  # rank 1 never published this step
+        assert ei.value.code == moe.EKERNEL
+        # recovery as the header prescribes: all detach, (host barrier), all attach, (host barrier)
+        for b in bes:
+            b.ep_detach()
+        bases = [b.ep_region()[0] for b in bes]
+        for b in bes:
+            b.ep_attach(bases, moe.EP_PEER_POINTERS)
+            b.ep_set_timeout_ms(200)
+        P = port_lib.PortMoe(small_layer, silu=ref_silu_table)
+        for step in range(2):
+            xh = [synth.make_x(6 + step, n, shape.hidden, first_token=10 * r) for r, n in enumerate([9, 20])]
+            xs = [torch.from_numpy(x).cuda() for x in xh]
+            outs = [torch.full_like(x, float("nan")) for x in xs]
+            _step(bes, xs, outs)
+            ref, _, _ = P.moe_ffn(np.concatenate(xh))
+            got = np.concatenate([o.cpu().numpy() for o in outs])
+            assert np.isfinite(got).all()
+            assert workloads.rel_rms_err(got, ref).max() < TOL
+    finally:
+        for b in bes:
+            b.close()
+
+
 def test_phase_order_is_checked(small_shape, ref_silu_table):
     from tie_b200 import moe
     bes = _ranks(small_shape, workloads.BASE_SEED + 1, 1, 64, ref_silu_table)

@@ -487,6 +487,46 @@ def test_dispatch_rows(be, layer0, port_lib, ref_silu_table):
     assert np.array_equal(bits(lg), bits(lg_ref))
 
 
+def test_dispatch_rows_from_several_host_threads(be, layer0):
+    """The reference's threaded dispatcher (math_dispatch.c:262-283) hands disjoint row slices of one
+    mat-vec to its pool workers, which call the row function at the same time.  Eight host threads
+    do that here (ctypes releases the GIL during the call); every slice must equal the rows of a
+    single whole-range call, bit for bit, for Q4_K, Q6_K (slices that start inside a group of 8
+    rows of the re-ordered layout) and F32."""
+    import threading
+    be.make_current()
+    s = layer0.shape
+    x = synth.make_x(0, 1)[0]
+    h = synth.make_x(1, 1, s.ffn_dim)[0]
+    e = 3
+    gsz, dsz = s.gate_bytes_per_expert, s.down_bytes_per_expert
+    cases = [(x, layer0.gate.ctypes.data + e * gsz, 12, 2048, 768), (h, layer0.down.ctypes.data + e * dsz, 14, 768, 2048),
+             (x, layer0.router_w.ctypes.data, 0, 2048, 128)]
+    for vec, wptr, typ, in_dim, rows in cases:
+        whole = be.dispatch_mat_vec(vec, wptr, typ, in_dim, 0, rows)
+        n_thr = 8
+        cuts = [rows * i // n_thr for i in range(n_thr + 1)]
+        if typ == 14:
+            cuts = [c + (3 if 0 < c < rows else 0) for c in cuts]  # slice starts off the 8-row groups
+        out = np.full(rows, np.nan, dtype=np.float32)
+        errs = []
+
+        def work(a, b):
+            try:
+                for _ in range(3):
+                    be.dispatch_mat_vec(vec, wptr, typ, in_dim, a, b, out=out)
+            except Exception as ex:  # noqa: BLE001
+                errs.append(ex)
+
+        th = [threading.Thread(target=work, args=(cuts[i], cuts[i + 1])) for i in range(n_thr)]
+        for t in th:
+            t.start()
+        for t in th:
+            t.join()
+        assert not errs, errs
+        assert np.array_equal(bits(out), bits(whole))
+
+
 @pytest.mark.parametrize("ggml_type,in_dim,out_dim,batch", [(12, 2048, 4096, 100), (14, 2048, 512, 37), (12, 768, 2048, 64),
                                                              (14, 768, 256, 1)])
 def test_dense_mat_mat_on_the_grouped_product(be, port_lib, ggml_type, in_dim, out_dim, batch):

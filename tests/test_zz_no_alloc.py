@@ -1,8 +1,10 @@
 """GPU test of tie_cuda_route_noalloc, the routing entry point for callers that must not
 allocate (a serving loop that bans allocator calls after start-up, an application with a fixed
-memory budget).  Its logits scratch is a fixed array inside the library, so the test checks two
-things a user of it relies on: it gives the same answer as the context-based tie_cuda_moe_route,
-and it keeps doing so on a second call that finds the first call's data still in the scratch.
+memory budget).  Its logits scratch is a fixed array inside the library, so the test checks the
+things a user of it relies on: it gives the same answer as the context-based tie_cuda_moe_route
+and as the CPU restatement of the reference's router, it keeps doing so on a second call that
+finds the first call's data still in the scratch, and a misaligned pointer is refused on the
+host instead of faulting on the device.
 
 Collected last on purpose (file name), and self-contained: it passes alone in a fresh process
 and after every other test."""
@@ -27,12 +29,13 @@ def _route_noalloc(L, x, router, bias, n_tokens, hidden, n_expert, top_k, torch)
     return idx.cpu().numpy(), w.cpu().numpy()
 
 
-def test_route_noalloc_matches_context_route_on_two_calls_in_a_row(layer0, ref_silu_table):
+def test_route_noalloc_matches_context_route_on_two_calls_in_a_row(layer0, ref_silu_table, port_lib):
     import torch
     from tie_b200 import moe
     L = moe.load_library()
     s = layer0.shape
     be = moe.MoeBackend(max_tokens=64, silu_table=ref_silu_table)
+    oracle = port_lib.PortMoe(layer0, silu=ref_silu_table)
     try:
         be.upload_layer(0, layer0)
         router = torch.from_numpy(layer0.router_w).cuda()
@@ -47,6 +50,10 @@ def test_route_noalloc_matches_context_route_on_two_calls_in_a_row(layer0, ref_s
                                             s.top_k, torch)
             assert np.array_equal(got_idx, want_idx)
             assert np.abs(got_w - want_w).max() <= 2e-7  # the tolerance the router tests use for gate weights
+            # and directly against the CPU restatement of the reference's router (find_top_k + softmax)
+            ref_idx, ref_w, _ = oracle.route(x, bias)
+            assert np.array_equal(got_idx, ref_idx)
+            assert np.abs(got_w - ref_w).max() <= 2e-7
     finally:
         be.close()
 
@@ -65,3 +72,9 @@ def test_route_noalloc_rejects_sizes_beyond_its_scratch(layer0):
     assert rc == moe.ETOOBIG
     rc = L.tie_cuda_route_noalloc(None, router.data_ptr(), None, 4, 2048, 128, 8, idx.data_ptr(), w.data_ptr(), None)
     assert rc == moe.EINVAL
+    # x / router one float off a 16-byte boundary: refused on the host (the kernels load 128 bits at a time)
+    rc = L.tie_cuda_route_noalloc(x.data_ptr() + 4, router.data_ptr(), None, 4, 2048, 128, 8, idx.data_ptr(), w.data_ptr(), None)
+    assert rc == moe.EINVAL
+    rc = L.tie_cuda_route_noalloc(x.data_ptr(), router.data_ptr() + 8, None, 4, 2048, 128, 8, idx.data_ptr(), w.data_ptr(), None)
+    assert rc == moe.EINVAL
+    torch.cuda.synchronize()

@@ -4,6 +4,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -14,7 +15,7 @@ using namespace tie;
 namespace {
 
 tie_cuda_ctx *g_current = nullptr;
-int g_dispatch_status = 0;
+std::atomic<int> g_dispatch_status{0};
 std::mutex g_mutex;
 
 size_t block_bytes(int ggml_type)
@@ -164,6 +165,32 @@ int add_reg(tie_cuda_ctx *c, const void *host, size_t bytes, const uint8_t *dev,
 	}
 	c->regs[c->n_regs++] = {host, bytes, dev, type, kind, rows, k, dense};
 	return TIE_CUDA_OK;
+}
+
+// Before a layer's tensors are replaced: cached CUDA graphs of calls on that layer hold the old
+// device pointers and tensor maps, and the dispatch-row registry the old device copies.
+void forget_layer(tie_cuda_ctx *c, int layer, const Layer &L)
+{
+	if (c->stream)
+		cudaStreamSynchronize(c->stream);
+	for (int i = 0; i < c->n_graphs;) {
+		if (c->graphs[i].layer == layer) {
+			cudaGraphExecDestroy(c->graphs[i].exec);
+			c->graphs[i] = c->graphs[--c->n_graphs];
+		} else {
+			i++;
+		}
+	}
+	const uint8_t *old[4] = {reinterpret_cast<const uint8_t *>(L.router_w), L.gate.ptr, L.up.ptr, L.down.ptr};
+	for (int i = 0; i < c->n_regs;) {
+		bool hit = false;
+		for (const uint8_t *p : old)
+			hit = hit || (p && c->regs[i].dev == p);
+		if (hit && !c->regs[i].dense)
+			c->regs[i] = c->regs[--c->n_regs];
+		else
+			i++;
+	}
 }
 
 bool is_pinned_host(const void *p)
@@ -744,12 +771,15 @@ int tie_cuda_upload_moe_layer(tie_cuda_ctx *c, int layer, const void *router_w_f
 	const int H = c->cfg.hidden, E = c->cfg.n_expert, F = c->cfg.ffn_dim;
 	if (!block_bytes(gate_type) || !block_bytes(up_type) || !block_bytes(down_type))
 		return TIE_CUDA_ENOTSUP;
+	if (L.uploaded || L.router_w)
+		forget_layer(c, layer, L);  // a re-upload: nothing may keep pointing at the tensors about to be freed
 	L.uploaded = false;
-	if (!L.router_w)
+	if (!L.router_w) {
 		TRY(dev_alloc(c, &L.router_w, (size_t)E * H));
+		c->weight_bytes += (size_t)E * H * sizeof(float);
+	}
 	TIE_CUDA_TRY(c, cudaMemcpyAsync(L.router_w, router_w_f32, (size_t)E * H * sizeof(float), cudaMemcpyHostToDevice, c->stream));
 	L.router_host = router_w_f32;
-	c->weight_bytes += (size_t)E * H * sizeof(float);
 	if (ffn_norm_w) {
 		if (!L.norm_w)
 			TRY(dev_alloc(c, &L.norm_w, (size_t)H));
@@ -838,7 +868,7 @@ int tie_cuda_moe_block_inplace(tie_cuda_ctx *c, int layer, float *hidden_dev, in
 		return TIE_CUDA_EINVAL;
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
 	GraphKey k = {3, layer, n_tokens, hidden_dev, nullptr, nullptr, nullptr,
-		      flags & (TIE_CUDA_PATH_MASK | TIE_CUDA_PATH_LEGACY_STREAM | TIE_CUDA_PATH_DECODE_CHAIN)};
+		      flags & (TIE_CUDA_PATH_MASK | TIE_CUDA_PATH_LEGACY_STREAM | TIE_CUDA_PATH_DECODE_CHAIN | TIE_CUDA_ROUTE_LFM2)};
 	TRY(run_maybe_graphed(c, flags & TIE_CUDA_GRAPH, k, [&]() -> int {
 		// one token: the RMSNorm is part of the one-kernel step
 		if ((flags & TIE_CUDA_PATH_MASK) != TIE_CUDA_PATH_TENSOR &&
@@ -1016,6 +1046,23 @@ int tie_cuda_ep_attach(tie_cuda_ctx *c, const void *const *peers, int n_peers, i
 			ep.view.peer[i] = static_cast<uint8_t *>(p);
 			ep.opened[i] = true;
 		}
+	}
+	// An attach starts a new epoch: the step counter and the flags the peers store into this rank's
+	// region go back to zero, so that a group that re-forms after a time-out (where the ranks' step
+	// numbers differ and stale flags are left behind) agrees again.  The caller separates the
+	// attaches of all ranks from the first publish by a host barrier (a peer's first flag must not
+	// arrive before this reset), and the detaches of all ranks from the attaches by another.
+	cudaError_t e = cudaMemsetAsync(ep.step_dev, 0, sizeof(unsigned), c->stream);
+	if (e == cudaSuccess)
+		e = cudaMemsetAsync(ep.region + ep.view.off_pub, 0, EP_MAX_RANKS * sizeof(unsigned), c->stream);
+	if (e == cudaSuccess)
+		e = cudaMemsetAsync(ep.region + ep.view.off_done, 0, EP_MAX_RANKS * sizeof(unsigned), c->stream);
+	if (e == cudaSuccess)
+		e = cudaStreamSynchronize(c->stream);
+	if (e != cudaSuccess) {
+		snprintf(c->cuda_err, sizeof(c->cuda_err), "ep_attach: %s", cudaGetErrorString(e));
+		ep_close_peers(c);
+		return TIE_CUDA_ECUDA;
 	}
 	ep.attached = true;
 	ep.phase = 0;
@@ -1332,13 +1379,23 @@ static int ensure_row_buffers(tie_cuda_ctx *c, size_t n)
 	return TIE_CUDA_OK;
 }
 
+// One slice [start_row, end_row) of a mat-vec, as the reference's dispatcher calls its row kernels
+// (math_dispatch.c:224, 254; the threaded dispatcher, :262-283, calls them concurrently from its
+// pool workers with disjoint slices).  The slices of one context share its staging buffers,
+// stream and status word, so a call holds the context's row lock from the first buffer use to
+// the read-back of the status; only the rows of the slice are launched.
 static int dispatch_mat_vec_row(const void *X, const void *W, void *O, int in_dim, int start_row, int end_row, int type)
 {
-	tie_cuda_ctx *c = g_current;
+	tie_cuda_ctx *c;
+	{
+		std::lock_guard<std::mutex> lk(g_mutex);
+		c = g_current;
+	}
 	if (!c)
 		return TIE_CUDA_EINVAL;
 	if (!X || !W || !O || in_dim <= 0 || start_row < 0 || end_row <= start_row)
 		return TIE_CUDA_EINVAL;
+	std::lock_guard<std::mutex> row_lock(c->row_mutex);
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
 	const uint8_t *w = static_cast<const uint8_t *>(W);
 	const tie_cuda_ctx::Reg *reg = nullptr;
@@ -1355,18 +1412,23 @@ static int dispatch_mat_vec_row(const void *X, const void *W, void *O, int in_di
 	size_t row_bytes = (type == TIE_GGML_TYPE_F32) ? (size_t)in_dim * 4 : (size_t)(in_dim / QK_K) * block_bytes(type);
 	if (off % row_bytes)
 		return TIE_CUDA_EINVAL;
-	if (reg->kind == W_Q6K_R8 && type != TIE_GGML_TYPE_F32 && (off / row_bytes) % 8)
+	const bool r8 = reg->kind == W_Q6K_R8 && type != TIE_GGML_TYPE_F32;
+	if (r8 && (off / row_bytes) % 8)
 		return TIE_CUDA_ENOTSUP;
 	if (off + (size_t)end_row * row_bytes > reg->bytes)
 		return TIE_CUDA_EINVAL;
-	size_t need = (size_t)((in_dim > end_row) ? in_dim : end_row);
+	// the re-ordered Q6_K layout is addressed by groups of 8 rows: start at the slice's group
+	const int first = r8 ? (start_row & ~7) : start_row;
+	const int n_rows = end_row - first;
+	size_t need = (size_t)((in_dim > n_rows) ? in_dim : n_rows);
 	TRY(ensure_row_buffers(c, need));
 	TIE_CUDA_TRY(c, cudaMemcpyAsync(c->row_x, X, (size_t)in_dim * sizeof(float), cudaMemcpyHostToDevice, c->stream));
+	const uint8_t *w_dev = reg->dev + off + (size_t)first * row_bytes;
 	if (type == TIE_GGML_TYPE_F32)
-		TRY(launch_router_rows(c, c->row_x, reinterpret_cast<const float *>(reg->dev + off), end_row, in_dim, c->row_o));
+		TRY(launch_router_rows(c, c->row_x, reinterpret_cast<const float *>(w_dev), n_rows, in_dim, c->row_o));
 	else
-		TRY(launch_stream_matvec(c, reg->dev + off, reg->kind, in_dim, end_row, c->row_x, c->row_o));
-	TIE_CUDA_TRY(c, cudaMemcpyAsync(static_cast<float *>(O) + start_row, c->row_o + start_row,
+		TRY(launch_stream_matvec(c, w_dev, reg->kind, in_dim, n_rows, c->row_x, c->row_o));
+	TIE_CUDA_TRY(c, cudaMemcpyAsync(static_cast<float *>(O) + start_row, c->row_o + (start_row - first),
 					(size_t)(end_row - start_row) * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
 	return check_status(c);
 }
@@ -1394,10 +1456,15 @@ void tie_cuda_mat_vec_row_f32_f32_f32(const void *X, const void *W, void *O, int
 
 void tie_cuda_swiglu_f32_f32(void *gate, const void *up, int size)
 {
-	tie_cuda_ctx *c = g_current;
+	tie_cuda_ctx *c;
+	{
+		std::lock_guard<std::mutex> lk(g_mutex);
+		c = g_current;
+	}
 	auto run = [&]() -> int {
 		if (!c || !gate || !up || size <= 0)
 			return TIE_CUDA_EINVAL;
+		std::lock_guard<std::mutex> row_lock(c->row_mutex);
 		TIE_CUDA_TRY(c, cudaSetDevice(c->device));
 		TRY(ensure_row_buffers(c, (size_t)size));
 		TIE_CUDA_TRY(c, cudaMemcpyAsync(c->row_x, gate, (size_t)size * sizeof(float), cudaMemcpyHostToDevice, c->stream));

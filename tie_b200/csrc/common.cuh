@@ -7,6 +7,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <mutex>
+
 #include "../../include/tie_cuda.h"
 
 namespace tie {
@@ -168,6 +170,7 @@ struct tie_cuda_ctx {
 	// small per-call device buffers for the dispatch rows
 	float *row_x = nullptr, *row_o = nullptr;
 	size_t row_cap = 0;
+	std::mutex row_mutex;  // the dispatch rows may be called from several host threads at once
 	tie::EpState ep;
 };
 

@@ -101,7 +101,12 @@ __global__ void __launch_bounds__(256) split_rows(const float *__restrict__ x, c
 						  __half *__restrict__ q_hi, __half *__restrict__ q_lo, int q_cols)
 {
 	const int p = blockIdx.x;
-	const int src = perm ? perm[p] / src_div : p;
+	// (after a call with row experts out of range the sort has placed fewer rows than the grid has
+	// CTAs and the tail of perm is stale: an entry that is no row id of this call reads row 0)
+	unsigned rid = perm ? (unsigned)perm[p] : (unsigned)p;
+	if (perm && rid >= gridDim.x)
+		rid = 0;
+	const int src = perm ? (int)rid / src_div : p;
 	const float *xr = x + (size_t)src * n_cols;
 	__half2 *hr = reinterpret_cast<__half2 *>(hi + (size_t)p * n_cols);
 	__half2 *lr = reinterpret_cast<__half2 *>(lo + (size_t)p * n_cols);
@@ -127,7 +132,9 @@ __global__ void __launch_bounds__(256) gather_rows(const float *__restrict__ x, 
 						   float *__restrict__ rows_out, int *__restrict__ expert_out, int *__restrict__ inv)
 {
 	const int p = blockIdx.x;
-	const int rid = perm[p];
+	int rid = perm[p];
+	if ((unsigned)rid >= gridDim.x)  // stale entry behind the rows the sort placed (an expert id was out of range)
+		rid = 0;
 	const float4 *xr = reinterpret_cast<const float4 *>(x + (size_t)(rid / src_div) * n_cols);
 	float4 *orow = reinterpret_cast<float4 *>(rows_out + (size_t)p * n_cols);
 	for (int k = threadIdx.x; k < n_cols / 4; k += blockDim.x)
@@ -186,6 +193,8 @@ int launch_rms_norm(tie_cuda_ctx *c, const float *x, const float *w, float *o, i
 	const int H = c->cfg.hidden;
 	const int wpb = 4;
 	size_t smem = (size_t)wpb * H * sizeof(float);
+	if (smem > 48 * 1024)  // the kernel runs within the default dynamic shared-memory limit
+		return TIE_CUDA_ENOTSUP;
 	rms_norm_rows<<<(n_tokens + wpb - 1) / wpb, wpb * 32, smem, c->stream>>>(x, w, o, n_tokens, H, c->cfg.norm_eps);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;

@@ -8,6 +8,8 @@
 // is what makes the top-k selection identical (the 8th/9th logit gap can be a few ulp).
 // find_top_k: engine.c:891-914 (strict '>': ties keep the lower expert index, output sorted by
 // score descending).  softmax: engine.c:864-888 over the k selected raw logits.
+#include <mutex>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -379,6 +381,8 @@ int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *
 		bias = nullptr;
 	if (n_tokens <= 8) {
 		size_t smem = ((size_t)H + (size_t)n_tokens * (H + 8)) * sizeof(float);
+		if (smem > 200 * 1024)	// the limit router_setup opts this kernel into
+			return TIE_CUDA_ENOTSUP;
 		router_logits_decode<8><<<E, 64, smem, c->stream>>>(x, w, bias, logits, n_tokens, H, E);
 		TIE_CUDA_LAUNCHED(c);
 	} else if (E % 64 == 0 && H % 128 == 0 && n_tokens >= 2048) {
@@ -464,6 +468,7 @@ static __device__ __align__(256) float g_route_scratch[TIE_ROUTE_NOALLOC_MAX_TOK
 namespace {
 constexpr int NOALLOC_MAX_DEVICES = 64;
 float *g_route_scratch_addr[NOALLOC_MAX_DEVICES] = {nullptr};  // device address of the array, per device
+std::mutex g_route_scratch_mutex;			       // first calls of several host threads set up one at a time
 }
 
 extern "C" int tie_cuda_route_noalloc(const float *x_dev, const float *router_w_dev, const float *router_bias_dev, int n_tokens,
@@ -473,6 +478,13 @@ extern "C" int tie_cuda_route_noalloc(const float *x_dev, const float *router_w_
 	if (!x_dev || !router_w_dev || !topk_idx_dev || !topk_w_dev || n_tokens <= 0 || hidden <= 0 || hidden % 8 || n_expert <= 0 ||
 	    n_expert % 16 || top_k <= 0 || top_k > MAX_TOP_K || top_k > n_expert)
 		return TIE_CUDA_EINVAL;
+	// the kernels read x and the router matrix with 128-bit loads: an address that is not a
+	// multiple of 16 bytes would be a misaligned-address fault on the device, so it is refused here
+	if ((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(router_w_dev)) & 15u)
+		return TIE_CUDA_EINVAL;
+	if ((reinterpret_cast<uintptr_t>(topk_idx_dev) | reinterpret_cast<uintptr_t>(topk_w_dev) |
+	     reinterpret_cast<uintptr_t>(router_bias_dev)) & 3u)
+		return TIE_CUDA_EINVAL;
 	if (n_tokens > TIE_ROUTE_NOALLOC_MAX_TOKENS || n_expert > TIE_ROUTE_NOALLOC_MAX_EXPERTS)
 		return TIE_CUDA_ETOOBIG;
 	const size_t smem = ((size_t)hidden + (size_t)n_tokens * (hidden + 8)) * sizeof(float);
@@ -481,9 +493,12 @@ extern "C" int tie_cuda_route_noalloc(const float *x_dev, const float *router_w_
 	int dev = -1;
 	if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES)
 		return TIE_CUDA_ENODEV;
+	std::unique_lock<std::mutex> setup_lock(g_route_scratch_mutex);
 	if (!g_route_scratch_addr[dev]) {
 		// First call on this device: resolve the array's DEVICE address.  In host code the name
 		// g_route_scratch is only a handle for the runtime, not an address a kernel can use.
+		// (Host threads that make their first call at the same time take turns here; the lock
+		// orders the set-up only, not the kernels: overlapping calls still race on the array.)
 		float *p = nullptr;
 		if (cudaGetSymbolAddress(reinterpret_cast<void **>(&p), g_route_scratch) != cudaSuccess || !p) {
 			cudaGetLastError();
@@ -497,6 +512,7 @@ extern "C" int tie_cuda_route_noalloc(const float *x_dev, const float *router_w_
 		g_route_scratch_addr[dev] = p;
 	}
 	float *logits = g_route_scratch_addr[dev];
+	setup_lock.unlock();
 	cudaStream_t st = static_cast<cudaStream_t>(cuda_stream);
 	if (n_tokens <= 8) {
 		router_logits_decode<8><<<n_expert, 64, smem, st>>>(x_dev, router_w_dev, router_bias_dev, logits, n_tokens, hidden, n_expert);

@@ -33,6 +33,12 @@ int tie_cuda_qwen3_load(struct TIEContext *ctx, tie_cuda_ctx **out, int device, 
 		const LayerWeights *l = &m->layers[i];
 		if (!l->ffn_gate_exps.mem.data) /* a dense layer of a mixed model: stays on the CPU path */
 			continue;
+		/* the upload copies the router as F32 [n_expert][hidden]: a file that stores it in another
+		 * type (F16, BF16) would be read past its end */
+		if (l->ffn_gate_inp.mem.type != GGML_TYPE_F32) {
+			tie_cuda_destroy(c);
+			return TIE_CUDA_ENOTSUP;
+		}
 		rc = tie_cuda_upload_moe_layer(c, i, l->ffn_gate_inp.mem.data, l->ffn_gate_exps.mem.data,
 					       (int)l->ffn_gate_exps.mem.type, l->ffn_up_exps.mem.data, (int)l->ffn_up_exps.mem.type,
 					       l->ffn_down_exps.mem.data, (int)l->ffn_down_exps.mem.type,
