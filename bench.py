@@ -6,15 +6,21 @@
 One "step" = one pass of the MoE block over one batch of synthetic tokens.  The workload at N=1
 is the 512-token prefill of one Qwen3-30B-A3B-shaped block (hidden 2048, 128 experts, top-8,
 expert FFN 768, Q4_K gate/up, Q6_K down), the configuration the metric is quoted on; with N>1
-ranks the experts are sharded (128/N per GPU) and every rank brings its own 512 tokens
-(expert parallelism, dispatch and combine by all-to-all over NCCL).  Prints ONE JSON line.
+ranks the experts are sharded (128/N per GPU) and every rank brings its own 512 tokens (expert
+parallelism; dispatch and combine are loads and stores over peer memory inside the kernels that
+consume and produce the rows — torch.distributed/NCCL only bootstraps and times; the NCCL
+all-to-all variant stays behind --ep-exchange nccl).  Prints ONE JSON line.
 
 value      tokens/s of the whole job, inputs resident in HBM, CUDA-event timed on the launching stream
 e2e        the same through the reference-facing C-ABI call with HOST buffers (H2D and D2H inside)
 roofline   the dominant kernel (gate/up product) against the measured HBM peak
 cpu_baseline  the reference's own AVX2 path (oracle/_ref) — or the C restatement when that
            library is absent — timed on this box's host cores on a bounded sample
-extra      decode (1 token), 64-token and 4096-token runs of the same block
+extra      decode (1 token), 64-, 4096- and 8192-token runs of the same block, the 48-block stack
+parity     (N > 1) sampled output rows of every rank against the CPU restatement, outside the timed regions
+
+    python bench.py --only decode1|batch64|prefill512|prefill4096 [--passes N]
+runs a few passes of one workload and nothing else (the command the profiler captures quote).
 """
 from __future__ import annotations
 
@@ -36,6 +42,12 @@ METRIC = "Qwen3-30B-A3B MoE-block tokens/s (decode & prefill), % of HBM/tensor r
 UNIT = "tokens/s"
 PREFILL_TOKENS = 512
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the two grouped-GEMM launches of the
+# 512-token workload, from the ncu capture of `python bench.py --only prefill512`; a change to that
+# kernel needs a new capture (the traffic is set by the packed weights and the operand arrays, not
+# by the kernel's schedule, and has stayed within 1 % over the kernel's revisions).
+NCU_DRAM_BYTES_PER_LAUNCH = {"gate_up": 282442752, "down": 197401600}
+NCU_DRAM_SOURCE = "ncu capture of grouped_gemm_sb on `bench.py --only prefill512`"
 
 
 def load_peaks():
@@ -101,11 +113,23 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+def config_of(shape, tokens, world=1):
+    """The workload description both arms print."""
+    cfg = {"workload": "prefill_512_tokens_one_block" if world == 1 else "prefill_512_tokens_per_rank_one_block_expert_parallel",
+           "tokens": tokens, "hidden": shape.hidden, "experts": shape.n_expert, "top_k": shape.top_k, "ffn_dim": shape.ffn_dim,
+           "weights": "Q4_K gate/up, Q6_K down (random valid super-blocks)", "seed": 0}
+    if world > 1:
+        cfg.update({"tokens_per_rank": tokens // world, "experts_per_rank": shape.n_expert // world, "parallelism": f"ep{world}"})
+    else:
+        cfg["parallelism"] = "1 GPU"
+    return cfg
+
+
 def host_threads():
     return min(os.cpu_count() or 8, 32)
 
 
-def cpu_reference_runner(layer, silu):
+def cpu_reference_runner(layer, silu=None):
     """(callable(x, bias) -> seconds, kind, cores).  The reference's own compiled AVX2 path when
     oracle/_ref was built, else the C restatement with the same shape of parallelism (the top-8
     experts of one token at a time, model_qwen3.c:446-456)."""
@@ -120,36 +144,102 @@ def cpu_reference_runner(layer, silu):
     return (lambda x, bias=None: P.time_moe_ffn(x, bias)), "port", min(8, host_threads())
 
 
+def cpu_baseline_leg(layer, silu, budget_s=10.0):
+    """The CPU baseline beside a GPU line: 64-token samples of the same block and inputs for about
+    budget_s seconds."""
+    from tie_b200 import synth, workloads
+    run, kind, cores = cpu_reference_runner(layer, silu)
+    sample_tokens = 64
+    reps, t = 0, 0.0
+    xs = synth.make_x(workloads.BASE_SEED, sample_tokens)
+    run(xs[:8])
+    while t < budget_s and reps < 64:
+        t += run(xs)
+        reps += 1
+    return {"value": sample_tokens * reps / t, "unit": UNIT, "cores": cores, "kind": kind,
+            "sample": f"{reps} x {sample_tokens} tokens of the same block and inputs ({t:.1f} s); the reference path is per-token, so the rate does not depend on batch size",
+            "host_cpus": os.cpu_count()}
+
+
+def make_row_checker():
+    """row_checker(seed, x_rows, got_rows, block) for the multi-GPU run: the CPU restatement of the
+    reference's MoE branch (oracle/port: the checker, never the thing measured) applied to a few
+    rows; returns max over rows of max_k|got - want| / rms_k(want)."""
+    from oracle import port
+    from tie_b200 import moe, synth, workloads
+    port.build()
+    cache = {}
+
+    def check(seed, x_rows, got_rows, block):
+        if seed not in cache:
+            cache.clear()
+            cache[seed] = port.PortMoe(synth.make_layer(seed, synth.MoeShape()), silu=moe.silu_table_default())
+        P = cache[seed]
+        if block:
+            want = P.moe_block_inplace(np.array(x_rows, dtype=np.float32), norm_w=None, eps=1e-6)[0]
+        else:
+            want, _, _ = P.moe_ffn(x_rows)
+        return float(workloads.rel_rms_err(got_rows, want).max())
+
+    return check
+
+
 def run_reference_arm(args):
     """--impl reference: the reference's CPU implementation of the same metric and config, on the
-    host cores.  Each step is a bounded sample (64 of the 512 tokens: the reference is strictly
-    per-token, model_qwen3.c:415, so its tokens/s does not depend on the batch size)."""
+    host cores, nothing of this package's CUDA side loaded.  A step is the 512 tokens of the
+    workload (with N > 1 ranks the job's tokens are N x 512; the step stays a 512-token sample of
+    them: the reference is strictly per-token, model_qwen3.c:415, so its tokens/s does not depend
+    on the batch size).  ms_per_step is the time of what ran."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from tie_b200 import moe, synth, workloads
-    layer = synth.make_layer(workloads.BASE_SEED)
-    silu = moe.silu_table_default()
-    run, kind, cores = cpu_reference_runner(layer, silu)
-    sample = 64
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    from tie_b200 import synth, workloads
+    shape = synth.MoeShape()
+    layer = synth.make_layer(workloads.BASE_SEED, shape)
+    run, kind, cores = cpu_reference_runner(layer)
+    sample = PREFILL_TOKENS
     x = synth.make_x(workloads.BASE_SEED, sample)
-    for _ in range(max(1, args.warmup)):
-        run(x[:8])
+    for _ in range(max(1, min(args.warmup, 3))):
+        run(x[:64])
     t = 0.0
     for _ in range(args.steps):
         t += run(x)
     tok_s = sample * args.steps / t
+    note = f"all {sample} tokens of the workload per step" if world == 1 else \
+        f"{sample} of the job's {sample * world} tokens per step (per-token path: the rate is batch-independent)"
     line = {
         "impl": "reference", "metric": METRIC, "value": tok_s, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps * (PREFILL_TOKENS / sample), "higher_is_better": True,
+        "warmup": args.warmup, "ms_per_step": 1e3 * t / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "prefill_512_tokens_one_block", "tokens": PREFILL_TOKENS, "hidden": 2048, "experts": 128,
-                   "top_k": 8, "ffn_dim": 768, "weights": "Q4_K gate/up, Q6_K down"},
-        "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": cores, "kind": kind,
-                         "sample": f"{sample} of the {PREFILL_TOKENS} tokens per step (per-token path: rate is batch-independent)"},
+        "config": config_of(shape, PREFILL_TOKENS * world, world),
+        "cpu_baseline": {"value": tok_s, "unit": UNIT, "cores": cores, "kind": kind, "sample": note},
         "e2e": {"value": tok_s, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+def run_only(args):
+    """--only: a few passes of ONE workload through the C ABI on cuda:0 with nothing else around
+    them (after the one-off upload the kernels of the passes are the process's only launches)."""
+    import torch
+    from tie_b200 import moe, synth, workloads
+    n_tokens = {"decode1": 1, "batch64": 64, "prefill512": 512, "prefill4096": 4096}[args.only]
+    be = moe.MoeBackend(max_tokens=n_tokens, silu_table=moe.silu_table_default())
+    be.upload_layer(0, synth.make_layer(workloads.BASE_SEED))
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    be.set_stream(stream.cuda_stream)
+    x = torch.from_numpy(synth.make_x(workloads.BASE_SEED, n_tokens)).cuda()
+    out = torch.empty_like(x)
+    flush = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device="cuda")  # 256 MB > L2
+    flags = moe.DEVICE | (moe.PATH_DECODE_CHAIN if args.chain else 0)
+    for _ in range(args.passes):
+        flush.zero_()
+        be.moe_ffn_ptr(0, x, out, n_tokens, flags)
+    be.synchronize()
+    be.close()
+    print(f"{args.only}: {args.passes} passes ok")
 
 
 def run_stack(n_layers, silu, device, peaks, torch, prefill_tokens=4096, decode_steps=256):
@@ -226,11 +316,18 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the decode / 64 / 4096-token side runs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--stack-layers", type=int, default=48, help="blocks of the stack side run (0 = skip)")
+    ap.add_argument("--only", choices=["decode1", "batch64", "prefill512", "prefill4096"],
+                    help="run a few passes of one workload and nothing else (for profiler captures)")
+    ap.add_argument("--passes", type=int, default=4, help="--only: number of passes")
+    ap.add_argument("--chain", action="store_true", help="--only decode1: the three chained decode kernels instead of the one-kernel step")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.only:
+        run_only(args)
         return
 
     import torch
@@ -241,7 +338,7 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
         from tie_b200 import ep
-        ep.bench_main(args, METRIC, UNIT, PREFILL_TOKENS, load_peaks, ClockSampler)
+        ep.bench_main(args, METRIC, UNIT, PREFILL_TOKENS, load_peaks, ClockSampler, config_of, cpu_baseline_leg, make_row_checker())
         return
 
     if not torch.cuda.is_available():
@@ -253,7 +350,7 @@ def main():
 
     layer = synth.make_layer(workloads.BASE_SEED, shape)
     silu = moe.silu_table_default()
-    be = moe.MoeBackend(max_tokens=4096, device=local_rank, silu_table=silu)
+    be = moe.MoeBackend(max_tokens=8192, device=local_rank, silu_table=silu)
     be.upload_layer(0, layer)
     stream = torch.cuda.Stream()
     torch.cuda.set_stream(stream)
@@ -327,8 +424,9 @@ def main():
                   "algorithmic_tflops": workloads.algorithmic_flops(shape, T) / (ms_per_step * 1e-3) / 1e12},
     }
     # DRAM bytes per launch of that kernel from its ncu capture (only captured for this workload)
-    if T == 512 and shape == synth.MoeShape():
-        roofline["traffic"] = workloads.NCU_DRAM_BYTES_PER_LAUNCH.get(dom + ("_tc" if used_tc else "_stream"))
+    if T == 512 and shape == synth.MoeShape() and used_tc:
+        roofline["traffic"] = NCU_DRAM_BYTES_PER_LAUNCH.get(dom)
+        roofline["traffic_source"] = NCU_DRAM_SOURCE
 
     # ---- side runs: decode, 64 tokens, 4096 tokens ----
     extra = {}
@@ -338,7 +436,8 @@ def main():
         def flush():
             flush_buf.fill_(1)
 
-        for name, tt, steps, fl in (("decode_1_token", 1, 200, flush), ("batch_64_tokens", 64, 50, flush), ("prefill_4096_tokens", 4096, 10, None)):
+        for name, tt, steps, fl in (("decode_1_token", 1, 200, flush), ("batch_64_tokens", 64, 50, flush), ("prefill_4096_tokens", 4096, 10, None),
+                                    ("prefill_8192_tokens_total", 8192, 6, None)):
             xd = torch.from_numpy(synth.make_x(workloads.BASE_SEED, tt)).cuda()
             od = torch.empty_like(xd)
 
@@ -376,30 +475,17 @@ def main():
         extra["stack"] = run_stack(args.stack_layers, silu, local_rank, peaks, torch)
 
     # ---- CPU baseline on this box's host cores (bounded sample) ----
-    cpu = None
-    if not args.no_cpu:
-        run, kind, cores = cpu_reference_runner(layer, silu)
-        sample_tokens = 64
-        reps = 0
-        t = 0.0
-        xs = synth.make_x(workloads.BASE_SEED, sample_tokens)
-        run(xs[:8])
-        while t < 10.0 and reps < 64:
-            t += run(xs)
-            reps += 1
-        cpu = {"value": sample_tokens * reps / t, "unit": UNIT, "cores": cores, "kind": kind,
-               "sample": f"{reps} x {sample_tokens} tokens of the same block and inputs ({t:.1f} s); the reference path is per-token, so the rate does not depend on batch size",
-               "host_cpus": os.cpu_count()}
+    cpu = None if args.no_cpu else cpu_baseline_leg(layer, silu)
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "prefill_512_tokens_one_block", "tokens": T, "hidden": shape.hidden, "experts": shape.n_expert,
-                   "top_k": shape.top_k, "ffn_dim": shape.ffn_dim, "weights": "Q4_K gate/up, Q6_K down (random valid super-blocks)",
-                   "arithmetic": "packed weights dequantised on the fly; fp16 hi/lo split operands, 3 tcgen05.mma per k-step, fp32 accumulate",
-                   "l2": "weights touched per step (392 MB) exceed the 126 MB L2; no flush", "seed": workloads.BASE_SEED,
-                   "parallelism": "1 GPU"},
+        "config": config_of(shape, T),
+        "config_detail": {"arithmetic": "packed weights expanded on the fly to exact integer fp16 operands (block factors applied in fp32 per "
+                                        "super-block); activations split into fp16 hi + lo: one tcgen05.mma per 16-wide k step over the stacked "
+                                        "hi|lo rows for tiles of up to 64 tokens, two for larger tiles; fp32 accumulate",
+                          "l2": "weights touched per step (392 MB) exceed the 126 MB L2; no flush"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu, "extra": extra,
     }
     print(json.dumps(line), flush=True)

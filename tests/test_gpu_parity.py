@@ -415,6 +415,38 @@ def test_two_blocks_chained_teacher_forced(be, layer0, port_lib, ref_silu_table)
         b.close()
 
 
+def test_all_48_blocks_of_the_stack_teacher_forced(port_lib, ref_silu_table):
+    """The whole 48-block stack (independent seeded weights per block, h += MoE(RMSNorm(h)), norm
+    weight 1, eps 1e-6) on 1 token (the one-kernel decode step with the RMSNorm inside) and on 4
+    tokens (the decode kernels), the residual stream staying on the device from block to block.
+    Every block is checked against the CPU restatement fed with the GPU's own input to that block.
+    One layer slot is re-uploaded per block, so cached graphs of the previous block's weights must
+    have been dropped by the upload."""
+    import torch
+    from tie_b200 import moe
+    ones = np.ones(2048, dtype=np.float32)
+    b = moe.MoeBackend(max_tokens=8, silu_table=ref_silu_table, n_layers=1)
+    try:
+        hs = {T: torch.from_numpy(synth.make_x(workloads.STACK_BASE_SEED, T)).cuda() for T in (1, 4)}
+        worst = 0.0
+        for l in range(48):
+            layer = synth.make_layer(workloads.STACK_BASE_SEED + l)
+            b.upload_layer(0, layer, ffn_norm_w=ones)
+            P = port_lib.PortMoe(layer, silu=ref_silu_table)
+            for T, h in hs.items():
+                h_in = h.cpu().numpy()
+                b.moe_block_inplace_ptr(0, h, T, moe.DEVICE | moe.GRAPH)
+                want = P.moe_block_inplace(h_in, norm_w=ones, eps=1e-6)[0]
+                got = h.cpu().numpy()
+                assert np.isfinite(got).all(), (l, T)
+                err = float(workloads.rel_rms_err(got, want).max())
+                assert err <= TOL, (l, T, err)
+                worst = max(worst, err)
+        assert worst > 0.0  # (the two sides are different arithmetic: an exact zero would mean the check compared a value with itself)
+    finally:
+        b.close()
+
+
 # ---------------- expert-parallel building blocks ----------------
 
 def test_expert_rows_and_combine(be, port0, golden):

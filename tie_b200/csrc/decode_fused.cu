@@ -30,6 +30,8 @@
 #include "tc_ptx.cuh"
 #include "decode_common.cuh"
 #include "router_topk.cuh"
+#define TIE_TIMING_DF_OWNER
+#include "timing.cuh"
 
 namespace tie {
 
@@ -37,20 +39,6 @@ constexpr int DF_THREADS = 512;
 constexpr int DF_MAX_CHUNKS = 8;
 constexpr int DF_MAX_PASSES = 4;
 constexpr long long DF_WAIT_CYCLES = 1ll << 30;
-
-#ifdef DF_TIMING
-__device__ unsigned long long g_df_stamps[16];
-#define DF_STAMP(i)                                                                   \
-	do {                                                                          \
-		if (blockIdx.x == 0 && threadIdx.x == 0) {                            \
-			unsigned long long t_;                                        \
-			asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));        \
-			g_df_stamps[i] = t_;                                          \
-		}                                                                     \
-	} while (0)
-#else
-#define DF_STAMP(i)
-#endif
 
 struct DfShared {
 	uint64_t bar_gu[DF_MAX_CHUNKS];
@@ -561,13 +549,3 @@ int launch_decode_fused(tie_cuda_ctx *c, const Layer &L, const float *x, const f
 }
 
 }  // namespace tie
-
-#ifdef DF_TIMING
-// Debug builds only: globaltimer stamps (ns) of CTA 0 at the phase boundaries of the last launch.
-extern "C" int tie_debug_df_stamps(unsigned long long *out)
-{
-	if (cudaDeviceSynchronize() != cudaSuccess)
-		return -1;
-	return cudaMemcpyFromSymbol(out, tie::g_df_stamps, sizeof(unsigned long long) * 16) == cudaSuccess ? 0 : -1;
-}
-#endif

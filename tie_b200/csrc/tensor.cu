@@ -40,6 +40,8 @@
 #include "kernels.cuh"
 #include "tc_dequant.cuh"
 #include "tc_ptx.cuh"
+#define TIE_TIMING_TC_OWNER
+#include "timing.cuh"
 
 namespace tie {
 
@@ -100,32 +102,6 @@ struct TcShared {
 	uint32_t abort;
 };
 static_assert(sizeof(TcShared) <= 512, "barrier block");
-
-// Optional cycle accounting per role (compile with -DTC_TIMING): lane 0 of one warp per role adds
-// its clock64() deltas to g_tc_cycles; tie_debug_tc_cycles() reads and clears them.
-#ifdef TC_TIMING
-__device__ unsigned long long g_tc_cycles[32];
-__device__ long long g_tc_trace[8][256];
-#define TCT_TRACE(r, i)                                            \
-	do {                                                       \
-		if (RAW && blockIdx.x == 0 && (i) < 256u && lane == 0)    \
-			g_tc_trace[r][i] = clock64();              \
-	} while (0)
-#define TCT_DECL(n) long long tct_[n] = {0}
-#define TCT_NOW() clock64()
-#define TCT_ADD(i, t0) tct_[i] += clock64() - (t0)
-#define TCT_FLUSH(base, n)                                                          \
-	do {                                                                        \
-		for (int i_ = 0; i_ < (n); i_++)                                    \
-			atomicAdd(&g_tc_cycles[(base) + i_], (unsigned long long)tct_[i_]); \
-	} while (0)
-#else
-#define TCT_DECL(n)
-#define TCT_NOW() 0ll
-#define TCT_ADD(i, t0) (void)(t0)
-#define TCT_FLUSH(base, n)
-#define TCT_TRACE(r, i)
-#endif
 
 // Bounded wait: false (and the abort flag raised) when the barrier does not flip in time or
 // another role / CTA has already reported a timeout.  After a first miss the thread lets the
@@ -1122,22 +1098,3 @@ int launch_tc_down_peer(tie_cuda_ctx *c, const Layer &L, const EpDst &dst)
 }
 
 }  // namespace tie
-
-#ifdef TC_TIMING
-// Debug builds only: copies out and clears the role cycle counters (32 values).
-extern "C" int tie_debug_tc_cycles(unsigned long long *out)
-{
-	unsigned long long zero[32] = {0};
-	if (cudaDeviceSynchronize() != cudaSuccess)
-		return -1;
-	if (cudaMemcpyFromSymbol(out, tie::g_tc_cycles, sizeof(zero)) != cudaSuccess)
-		return -1;
-	return cudaMemcpyToSymbol(tie::g_tc_cycles, zero, sizeof(zero)) == cudaSuccess ? 0 : -1;
-}
-extern "C" int tie_debug_tc_trace(long long *out)
-{
-	if (cudaDeviceSynchronize() != cudaSuccess)
-		return -1;
-	return cudaMemcpyFromSymbol(out, tie::g_tc_trace, sizeof(long long) * 8 * 256) == cudaSuccess ? 0 : -1;
-}
-#endif

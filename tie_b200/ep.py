@@ -1,18 +1,24 @@
 """Expert parallelism for the MoE block: one process per GPU, experts sharded 128/G per rank,
-tokens data-parallel, dispatch and combine by all-to-all over NCCL (torch.distributed).
+tokens data-parallel.  The reference is a single process and has no counterpart.
 
-The reference is a single process and has no counterpart.  Per block and rank:
+Two exchanges are implemented:
 
-  route (local, router replicated)                       -> top-k ids, weights
-  dispatch: counting sort of the (token, slot) rows by expert id; since a rank owns a
-            contiguous expert range this also groups rows by destination rank
-  all-to-all of the per-expert row counts (to each expert's owner), then of the rows
-  expert rows on the owner (grouped mat-vec / GEMM over its local experts)
-  all-to-all back in the same order
-  combine: out[t] = sum_j w[t][j] * y[(t, j)], j ascending
+PeerEpMoeBlock (default)  dispatch and combine over peer memory (tie_cuda_ep_*): every rank exposes
+    one region of its HBM; the owners' kernels load token rows straight from the sources' regions
+    and the down product stores every output row straight into its source's region (plain loads and
+    stores over NVLink), synchronised by step-numbered flags.  No collective and no host
+    synchronisation per step; torch.distributed only exchanges the IPC handles once.
 
-The exchange logic is written against a small `ops` interface so that it can run on CPU ranks
-(gloo) with stand-in ops in the tests; on GPUs `CudaOps` forwards to the C ABI.
+EpMoeBlock (baseline)     the same step with NCCL collectives (torch.distributed):
+      route (local, router replicated)                       -> top-k ids, weights
+      dispatch: counting sort of the (token, slot) rows by expert id; since a rank owns a
+                contiguous expert range this also groups rows by destination rank
+      all-to-all of the per-expert row counts (to each expert's owner), then of the rows
+      expert rows on the owner (grouped mat-vec / GEMM over its local experts)
+      all-to-all back in the same order
+      combine: out[t] = sum_j w[t][j] * y[(t, j)], j ascending
+    Its exchange logic is written against a small `ops` interface so that it can run on CPU ranks
+    (gloo) with stand-in ops in the tests; on GPUs `CudaOps` forwards to the C ABI.
 """
 from __future__ import annotations
 
@@ -190,9 +196,22 @@ def _step_roofline(shape, tokens_per_rank, world, ms_per_step, flops_total, peak
             "algorithmic_tflops": flops_total / t / 1e12}
 
 
-def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
+def sample_rows(n_rows: int, n: int = 8):
+    """Row indices checked after a benchmark run: first, last and evenly spaced ones between."""
+    if n_rows <= n:
+        return list(range(n_rows))
+    return sorted({0, n_rows - 1, *[(i * (n_rows - 1)) // (n - 1) for i in range(1, n - 1)]})
+
+
+PARITY_TOL = 1e-3
+
+
+def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler, config_of, cpu_baseline_leg, row_checker):
     """bench.py --gpus N under torchrun: weak scaling, `tokens_per_rank` tokens on every rank,
-    experts sharded.  Rank 0 prints the JSON line."""
+    experts sharded.  Rank 0 prints the JSON line.  row_checker(seed, x_rows, got_rows, block) ->
+    max over the rows of max_k|got - want| / rms_k(want), `want` from the caller's CPU checker
+    (block: the rows are residual-stream rows of h += MoE(RMSNorm(h))); it is called outside the
+    timed regions on a few rows of every rank."""
     import torch
     import torch.distributed as dist
 
@@ -304,11 +323,28 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
                  "swiglu": "SwiGLU pass", "down": "down product (stores rows to their sources)", "combine": "wait for owners + combine"}
         phases = {names[k]: v / n_prof for k, v in acc.items()}
 
+    # ---- parity of this rank's output rows against the CPU checker (outside every timed region) ----
+    parity_rows, parity_err = 0, 0.0
+
+    def check(seed, x_rows_host, got_dev, rows, block=False):
+        nonlocal parity_rows, parity_err
+        got = got_dev[rows].cpu().numpy()
+        err = float(row_checker(seed, x_rows_host[rows], got, block))
+        parity_rows += len(rows)
+        parity_err = max(parity_err, err)
+        return err
+
+    out_dev.fill_(float("nan"))
+    step()
+    torch.cuda.synchronize()
+    parity_detail = {"weak_step": check(workloads.BASE_SEED, x_host.numpy(), out_dev, sample_rows(T))}
+
     strong = None
     if exchange == "peer" and not getattr(args, "no_extra", False) and STRONG_TOKENS % world == 0:
         T2 = STRONG_TOKENS // world
         x2 = blk.token_buffer(torch, T2)
-        x2.copy_(torch.from_numpy(synth.make_x(workloads.BASE_SEED, T2, first_token=rank * T2)))
+        x2_host = synth.make_x(workloads.BASE_SEED, T2, first_token=rank * T2)
+        x2.copy_(torch.from_numpy(x2_host))
         o2 = torch.empty_like(x2)
         for _ in range(3):
             blk.forward(x2, o2)
@@ -317,6 +353,10 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
                   "tokens_per_s": STRONG_TOKENS / (ms2 * 1e-3),
                   "algorithmic_tflops": workloads.algorithmic_flops(shape, STRONG_TOKENS) / (ms2 * 1e-3) / 1e12}
         be.synchronize()
+        o2.fill_(float("nan"))
+        blk.forward(x2, o2)
+        torch.cuda.synchronize()
+        parity_detail["strong_8192_step"] = check(workloads.BASE_SEED, x2_host, o2, sample_rows(T2))
 
     # side run: the 48-block stack (BASELINE's last configuration), a 4096-token prefill with the
     # tokens and the experts of every block spread over the ranks; h += MoE(RMSNorm(h)) per block
@@ -333,7 +373,8 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
                                                  n_local_expert=n_local), ffn_norm_w=ones)
         be2.set_stream(stream.cuda_stream)
         PeerEpMoeBlock(be2, dist)
-        h0 = torch.from_numpy(synth.make_x(workloads.STACK_BASE_SEED, T3, first_token=rank * T3)).cuda()
+        h0_host = synth.make_x(workloads.STACK_BASE_SEED, T3, first_token=rank * T3)
+        h0 = torch.from_numpy(h0_host).cuda()
         h = h0.clone()
         fl = moe.DEVICE | moe.NO_SYNC | moe.GRAPH
 
@@ -353,8 +394,27 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
         stack = {"layers": n_layers, "tokens": 4096, "tokens_per_rank": T3, "scaling": "strong", "ms": ms3,
                  "tokens_per_s": 4096 / (ms3 * 1e-3), "algorithmic_tflops": fl3 / (ms3 * 1e-3) / 1e12, "finite": finite,
                  "weight_bytes_per_rank": be2.weight_bytes}
+        # block 0 alone on fresh rows, against the checker's h + MoE(RMSNorm(h))
+        h.copy_(h0)
+        be2.moe_block_inplace_ep_ptr(0, h, T3, fl)
+        be2.synchronize()
+        parity_detail["stack_block_0"] = check(workloads.STACK_BASE_SEED, h0_host, h, sample_rows(T3), block=True)
         dist.barrier()
         be2.close()
+
+    pt = torch.tensor([parity_err, float(parity_rows)], device="cuda", dtype=torch.float64)
+    perr = pt[:1].clone()
+    prow = pt[1:].clone()
+    dist.all_reduce(perr, op=dist.ReduceOp.MAX)
+    dist.all_reduce(prow, op=dist.ReduceOp.SUM)
+    parity = {"max_rel_rms": float(perr.item()), "rows": int(prow.item()), "tol": PARITY_TOL,
+              "checker": "CPU restatement of the reference's MoE branch (bit-identical to the compiled reference), "
+                         "sampled rows of every rank: first, last, evenly spaced",
+              "rank0": parity_detail}
+    cpu = None
+    if rank == 0 and not getattr(args, "no_cpu", False):
+        cpu = cpu_baseline_leg(synth.make_layer(workloads.BASE_SEED, shape), moe.silu_table_default())
+    dist.barrier()
 
     if rank == 0:
         peaks = load_peaks()
@@ -365,16 +425,13 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
             "data": "synthetic",
-            "config": {"workload": "prefill_512_tokens_per_rank_one_block_expert_parallel", "tokens": T * world,
-                       "tokens_per_rank": T, "hidden": shape.hidden, "experts": shape.n_expert, "experts_per_rank": n_local,
-                       "top_k": shape.top_k, "ffn_dim": shape.ffn_dim, "weights": "Q4_K gate/up, Q6_K down (random valid super-blocks)",
-                       "l2": f"weights touched per step per rank: {392 // world} MB plus {T * shape.top_k * shape.hidden * 8 // 2**20} MB of rows "
-                             "(larger than L2 from N = 1 to 2; at N >= 4 the weights of a rank fit in L2, as they would in deployment)",
-                       "parallelism": f"ep{world}",
-                       "exchange": ("peer memory: owners load token rows from the sources' HBM and store output rows into the sources' "
-                                    "(no collective, no host synchronisation per step)") if exchange == "peer"
-                       else "NCCL all-to-all (torch.distributed) for dispatch and combine",
-                       "seed": workloads.BASE_SEED},
+            "config": config_of(shape, T * world, world),
+            "config_detail": {
+                "l2": f"weights touched per step per rank: {392 // world} MB plus {T * shape.top_k * shape.hidden * 8 // 2**20} MB of rows "
+                      "(larger than L2 from N = 1 to 2; at N >= 4 the weights of a rank fit in L2, as they would in deployment)",
+                "exchange": ("peer memory: owners load token rows from the sources' HBM and store output rows into the sources' "
+                             "(no collective, no host synchronisation per step)") if exchange == "peer"
+                else "NCCL all-to-all (torch.distributed) for dispatch and combine"},
             "clocks": clocks,
             "e2e": {"value": T * world / e2e_s, "unit": unit, "h2d_bytes_per_step": T * shape.hidden * 4 * world,
                     "d2h_bytes_per_step": T * shape.hidden * 4 * world, "ms_per_step": e2e_s * 1e3},
@@ -383,7 +440,8 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
             # direction: rows in and rows out travel opposite ways), its share of the packed weights and
             # its rows' operands from HBM, its flops on the tensor cores
             "roofline": _step_roofline(shape, T, world, ms_per_step, flops, peaks),
-            "cpu_baseline": None,
+            "cpu_baseline": cpu,
+            "parity": parity,
             "exchange": {"rows_per_rank": T * shape.top_k, "bytes_per_row": shape.hidden * 4,
                          "remote_fraction": (world - 1) / world,
                          "nvlink_bytes_per_rank_and_direction": int(T * shape.top_k * shape.hidden * 4 * (world - 1) / world),
@@ -395,3 +453,5 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler):
         print(json.dumps(line), flush=True)
     be.close()
     dist.destroy_process_group()
+    if not (parity["max_rel_rms"] <= PARITY_TOL):
+        raise SystemExit(f"expert-parallel outputs differ from the CPU checker: {parity}")

@@ -65,46 +65,3 @@ def algorithmic_bytes(shape: synth.MoeShape, n_tokens: int, active_experts: int)
 def algorithmic_flops(shape: synth.MoeShape, n_tokens: int) -> int:
     """One multiply-add per weight element per token (never the split passes)."""
     return n_tokens * shape.flops_per_token
-
-
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the two grouped GEMM kernels on the
-# 512-token prefill workload, from the ncu capture summarised in
-# profiles/grouped_gemm_sb_prefill512.md (bench.py reports them as roofline.traffic).
-NCU_DRAM_BYTES_PER_LAUNCH = {"gate_up_tc": 282442752, "down_tc": 197401600}
-
-
-def _main() -> None:
-    """`python -m tie_b200.workloads decode1|batch64|prefill512 [--steps N]`: a few passes of one
-    workload through the C ABI on cuda:0 with nothing else around them — the command the
-    profiler captures (the kernels of the pass are then the only launches of the process after
-    the one-off upload)."""
-    import argparse
-
-    import torch
-
-    from . import moe
-
-    ap = argparse.ArgumentParser()
-    ap.add_argument("workload", choices=["decode1", "batch64", "prefill512"])
-    ap.add_argument("--steps", type=int, default=4)
-    ap.add_argument("--chain", action="store_true", help="decode1: the three chained decode kernels instead of the one-kernel step")
-    args = ap.parse_args()
-    n_tokens = {"decode1": 1, "batch64": 64, "prefill512": 512}[args.workload]
-    be = moe.MoeBackend(max_tokens=n_tokens, silu_table=moe.silu_table_default())
-    be.upload_layer(0, synth.make_layer(BASE_SEED))
-    stream = torch.cuda.Stream()
-    torch.cuda.set_stream(stream)
-    be.set_stream(stream.cuda_stream)
-    x = torch.from_numpy(synth.make_x(BASE_SEED, n_tokens)).cuda()
-    out = torch.empty_like(x)
-    flush = torch.empty(64 * 1024 * 1024, dtype=torch.float32, device="cuda")  # 256 MB > L2
-    for _ in range(args.steps):
-        flush.zero_()
-        be.moe_ffn_ptr(0, x, out, n_tokens, moe.DEVICE | (moe.PATH_DECODE_CHAIN if args.chain else 0))
-    be.synchronize()
-    be.close()
-    print(f"{args.workload}: {args.steps} passes ok")
-
-
-if __name__ == "__main__":
-    _main()
