@@ -60,6 +60,14 @@ extern "C" {
  * holds the sigmoid scores.  Accepted by tie_cuda_moe_route and tie_cuda_moe_ffn_biased; the
  * expert kernels and the combine are the same. */
 #define TIE_CUDA_ROUTE_LFM2 (1u << 12)
+/* Expert-parallel decode (tie_cuda_ep_publish, tie_cuda_moe_ffn_ep, tie_cuda_moe_block_inplace_ep):
+ * the 1 to 4 tokens of the call are REPLICATED — every rank passes the same rows — instead of
+ * each rank bringing tokens of its own.  Every rank routes them itself (the router is replicated
+ * and bit-exact, so all ranks select the same experts), computes the slots whose experts it owns
+ * and stores their down rows into every rank's region; every rank then combines all slots in the
+ * reference's slot order and ends up with the same complete output rows.  n_tokens must be the
+ * same on all ranks. */
+#define TIE_CUDA_EP_REPLICATED (1u << 13)
 
 typedef struct tie_cuda_ctx tie_cuda_ctx;
 
@@ -182,6 +190,10 @@ int tie_cuda_moe_ep_combine(tie_cuda_ctx *c, const float *y_sorted, const float 
  *                        experts from their sources, runs gate/up, SwiGLU, down (outputs land at
  *                        their sources)
  *   tie_cuda_ep_gather   waits for every owner, out[t] = (residual[t] +) sum_j w[t][j] * y(t, j)
+ * With TIE_CUDA_EP_REPLICATED in the flags of tie_cuda_ep_publish the step is the decode form:
+ * the same 1 to 4 tokens on every rank (no dispatch: publish only routes and announces the step;
+ * compute runs gate/up and down for the locally owned slots and stores the down rows to all
+ * ranks; gather combines).  Prefill and decode steps may alternate freely.
  * tie_cuda_moe_ffn_ep is the three in a row; with TIE_CUDA_GRAPH the whole step is replayed from a
  * CUDA graph (the step number advances on the device).  A step whose x is the start of this
  * rank's region (tie_cuda_ep_region) skips the copy into it.

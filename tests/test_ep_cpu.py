@@ -166,3 +166,63 @@ def test_peer_layout_matches_single_process_oracle(tokens):
     outs = [p.communicate(timeout=300)[0] for p in procs]
     for r, (p, o) in enumerate(zip(procs, outs)):
         assert p.returncode == 0 and "EP_OK" in o, f"rank {r}:\n{o[-3000:]}"
+
+
+# Decode under expert parallelism keeps the tokens replicated: every rank routes the same token,
+# computes the down rows of the slots whose experts it owns and hands them to every rank; each rank
+# then combines ALL slots in slot order.  Two gloo ranks do that with the CPU restatement standing
+# in for the kernels and all_gather for the peer stores: every slot must be delivered exactly once,
+# and the result must be the single-process oracle's, bit for bit (same order of additions).
+DECODE_WORKER = r"""
+import os, sys
+sys.path.insert(0, %(root)r)
+import numpy as np, torch, torch.distributed as dist
+from tie_b200 import synth, workloads
+from oracle import port
+
+rank = int(os.environ["RANK"]); world = int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", init_method="tcp://127.0.0.1:%(port)d", rank=rank, world_size=world)
+shape = synth.MoeShape(hidden=512, n_expert=32, top_k=4, ffn_dim=256)
+layer = synth.make_layer(workloads.BASE_SEED + 1, shape)
+P = port.PortMoe(layer)
+K, H, E = shape.top_k, shape.hidden, shape.n_expert
+NL = E // world
+T = %(tokens)d
+x = synth.make_x(workloads.BASE_SEED + 1, T, H, first_token=40)       # the SAME tokens on every rank
+idx, w, _ = P.route(x)                                                 # redundant routing
+flat = idx.reshape(-1)
+mine = np.nonzero((flat >= rank * NL) & (flat < (rank + 1) * NL))[0]   # (token, slot) rows this rank owns
+y_loc = P.expert_rows(x[mine // K], flat[mine]) if mine.size else np.zeros((0, H), dtype=np.float32)
+parts = [None] * world
+dist.all_gather_object(parts, (mine, y_loc))                           # the stores into every rank's y rows
+y = np.full((T * K, H), np.nan, dtype=np.float32)
+for rows, vals in parts:
+    for r, v in zip(rows, vals):
+        assert np.isnan(y[r]).all(), "slot delivered twice"
+        y[r] = v
+assert not np.isnan(y).any(), "slot never delivered"
+acc = np.zeros((T, H), dtype=np.float32)
+for t in range(T):
+    for j in range(K):
+        acc[t] = (np.float64(w[t, j]) * y[t * K + j].astype(np.float64) + acc[t].astype(np.float64)).astype(np.float32)
+ref, ref_idx, _ = P.moe_ffn(x)
+assert np.array_equal(idx, ref_idx)
+err = float(workloads.rel_rms_err(acc, ref).max())
+assert err < 1e-6, err
+dist.barrier(); dist.destroy_process_group()
+print("EP_OK", rank, err)
+"""
+
+
+@pytest.mark.parametrize("tokens", [1, 4])
+def test_replicated_decode_matches_single_process_oracle(tokens):
+    import socket
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); port = s.getsockname()[1]; s.close()
+    code = DECODE_WORKER % dict(root=ROOT, port=port, tokens=tokens)
+    procs = []
+    for r in range(2):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE="2", OMP_NUM_THREADS="2")
+        procs.append(subprocess.Popen([sys.executable, "-c", code], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=300)[0] for p in procs]
+    for r, (p, o) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0 and "EP_OK" in o, f"rank {r}:\n{o[-3000:]}"

@@ -181,6 +181,61 @@ def test_group_recovers_after_a_time_out_by_detach_and_attach(small_shape, small
             b.close()
 
 
+def _decode_step(bes, x, outs, residual=None):
+    """One decode step on replicated tokens, phases enqueued rank by rank (the ranks share a GPU)."""
+    from tie_b200 import moe
+    fl = moe.DEVICE | moe.NO_SYNC
+    n = x.shape[0]
+    for b in bes:
+        b.ep_publish_ptr(0, x, n, None, fl | moe.EP_REPLICATED)
+    for b in bes:
+        b.ep_compute(0, fl)
+    for b, o in zip(bes, outs):
+        b.ep_gather_ptr(o, residual, fl)
+    for b in bes:
+        b.synchronize()
+
+
+@pytest.mark.parametrize("G", [1, 2, 4, 8])
+@pytest.mark.parametrize("n_tokens", [1, 3])
+def test_replicated_decode_emulated_ranks(layer0, port0_ep, ref_silu_table, G, n_tokens):
+    """Expert-parallel decode (TIE_CUDA_EP_REPLICATED) of the Qwen3-30B-A3B-shaped block: every rank
+    gets the same rows and must end with the same complete outputs — bit-identical to the one-GPU
+    decode kernels (same per-slot products, combined in the same slot order) and within the parity
+    bound of the CPU restatement.  Three steps over the same regions; prefill steps in between use
+    the same flags."""
+    import torch
+    from tie_b200 import moe
+    shape = layer0.shape
+    bes = _ranks(shape, workloads.BASE_SEED, G, 8, ref_silu_table)
+    one = moe.MoeBackend(max_tokens=8, silu_table=ref_silu_table)
+    try:
+        one.upload_layer(0, layer0)
+        for step in range(3):
+            xh = synth.make_x(workloads.BASE_SEED, n_tokens, shape.hidden, first_token=17 * step)
+            x = torch.from_numpy(xh).cuda()
+            outs = [torch.full_like(x, float("nan")) for _ in bes]
+            res = torch.full_like(x, 0.25) if step == 1 else None
+            _decode_step(bes, x, outs, res)
+            want = torch.empty_like(x)
+            one.moe_ffn_ptr(0, x, want, n_tokens, moe.DEVICE | moe.PATH_DECODE_CHAIN)
+            w = want.cpu().numpy() + (0.25 if step == 1 else 0.0)
+            ref, _, _ = port0_ep.moe_ffn(xh)
+            for o in outs:
+                got = o.cpu().numpy()
+                if step != 1:
+                    assert np.array_equal(got.view(np.uint32), w.astype(np.float32).view(np.uint32))
+                assert workloads.rel_rms_err(got - (0.25 if step == 1 else 0.0), ref).max() < TOL
+            if step == 0 and G > 1:  # a prefill-form step between decode steps
+                xs = [torch.from_numpy(synth.make_x(9, 5, shape.hidden, first_token=10 * r)).cuda() for r in range(G)]
+                po = [torch.empty_like(t) for t in xs]
+                _step(bes, xs, po)
+    finally:
+        for b in bes:
+            b.close()
+        one.close()
+
+
 def test_phase_order_is_checked(small_shape, ref_silu_table):
     from tie_b200 import moe
     bes = _ranks(small_shape, workloads.BASE_SEED + 1, 1, 64, ref_silu_table)

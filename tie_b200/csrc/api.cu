@@ -1097,12 +1097,33 @@ int tie_cuda_ep_publish(tie_cuda_ctx *c, int layer, const float *x, int n_tokens
 	EpState &ep = c->ep;
 	if (!(flags & TIE_CUDA_DEVICE) || !ep.attached || ep.phase != 0 || n_tokens < 0 || n_tokens > ep.view.t_max || (n_tokens && !x))
 		return TIE_CUDA_EINVAL;
+	if (flags & TIE_CUDA_EP_REPLICATED) {
+		// decode on replicated tokens: announce the step, route; nothing is dispatched
+		if (n_tokens < 1 || n_tokens > 4 || (flags & TIE_CUDA_ROUTE_LFM2))
+			return TIE_CUDA_EINVAL;
+		if (!decode_supported(c, *L, n_tokens))
+			return TIE_CUDA_ENOTSUP;
+		TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+		prof_mark(c, 0);
+		TRY(launch_ep_signal(c, 0));
+		TRY(launch_router_decode_fused(c, x, L->router_w, router_bias, n_tokens, c->s.logits, c->s.topk_idx, c->s.topk_w));
+		prof_mark(c, 1);
+		prof_mark(c, 2);
+		ep.phase = 1;
+		ep.step_tokens = n_tokens;
+		ep.replicated = true;
+		ep.rep_x = x;
+		if (flags & TIE_CUDA_NO_SYNC)
+			return TIE_CUDA_OK;
+		return check_status(c);
+	}
 	if (!tc_supported(c, *L))
 		return TIE_CUDA_ENOTSUP;
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
 	Scratch &s = c->s;
 	const EpView &v = ep.view;
 	const int R = n_tokens * c->cfg.top_k;
+	ep.replicated = false;
 	prof_mark(c, 0);
 	if (n_tokens)
 		TRY(launch_router(c, x, L->router_w, router_bias, n_tokens, s.logits, s.topk_idx, s.topk_w,
@@ -1135,6 +1156,21 @@ int tie_cuda_ep_compute(tie_cuda_ctx *c, int layer, unsigned flags)
 	EpState &ep = c->ep;
 	if (!ep.attached || ep.phase != 1)
 		return TIE_CUDA_EINVAL;
+	if (ep.replicated) {
+		TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+		prof_mark(c, 3);
+		TRY(launch_decode_gate_up(c, *L, ep.rep_x, ep.step_tokens, true));
+		prof_mark(c, 4);
+		TRY(launch_decode_down_peer(c, *L, ep.step_tokens));
+		TRY(launch_ep_signal(c, 1));
+		prof_mark(c, 6);
+		c->last_used_tc = false;
+		c->last_direct_rows = ep.step_tokens * c->cfg.top_k;
+		ep.phase = 2;
+		if (flags & TIE_CUDA_NO_SYNC)
+			return TIE_CUDA_OK;
+		return check_status(c);
+	}
 	if (!tc_supported(c, *L))
 		return TIE_CUDA_ENOTSUP;
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
@@ -1173,6 +1209,7 @@ int tie_cuda_ep_gather(tie_cuda_ctx *c, float *out, const float *residual, unsig
 	prof_mark(c, 7);
 	ep.phase = 0;
 	ep.step_tokens = -1;
+	ep.replicated = false;
 	if (flags & TIE_CUDA_NO_SYNC)
 		return TIE_CUDA_OK;
 	return check_status(c);
@@ -1211,7 +1248,8 @@ int tie_cuda_moe_block_inplace_ep(tie_cuda_ctx *c, int layer, float *hidden_dev,
 		return TIE_CUDA_EINVAL;
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
 	const unsigned inner = (flags | TIE_CUDA_NO_SYNC | TIE_CUDA_DEVICE) & ~TIE_CUDA_GRAPH;
-	float *xs = reinterpret_cast<float *>(ep.region + ep.view.off_xs);
+	// (decode on replicated tokens: the normed rows stay in this rank's scratch, nobody else reads them)
+	float *xs = (flags & TIE_CUDA_EP_REPLICATED) ? c->s.x : reinterpret_cast<float *>(ep.region + ep.view.off_xs);
 	GraphKey k = {6, layer, n_tokens, hidden_dev, nullptr, nullptr, nullptr, inner};
 	TRY(run_maybe_graphed(c, flags & TIE_CUDA_GRAPH, k, [&]() -> int {
 		// the normed tokens go straight to where the peers read them

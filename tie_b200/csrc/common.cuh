@@ -107,6 +107,8 @@ struct EpState {
 	unsigned *step_dev = nullptr;  // [1] number of the last published step (advanced on the device)
 	int step_tokens = -1;	    // tokens of the step between publish and gather, else -1
 	int phase = 0;		    // 0 idle, 1 published, 2 computed
+	bool replicated = false;    // the step between publish and gather runs on tokens every rank holds (decode)
+	const float *rep_x = nullptr;  // ... and these are they
 	long long wait_cycles = 0;  // budget of every flag wait
 	int *n_rows = nullptr, *seg_base = nullptr, *seg_src = nullptr;
 	unsigned *row_dst = nullptr;  // [rows_cap] per sorted row: (source rank << 24) | its row id there

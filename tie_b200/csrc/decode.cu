@@ -28,7 +28,7 @@ template <WKind KIND, int K>
 __global__ void __launch_bounds__(DEC_GU_THREADS, 1)
 decode_gate_up(const uint8_t *__restrict__ wg, const uint8_t *__restrict__ wu, size_t expert_stride, int rows_per_expert,
 	       int rows_per_tile, const float *__restrict__ x, int top_k, const int *__restrict__ topk_idx, float *__restrict__ h,
-	       int first_expert, int n_local, const float *__restrict__ silu, unsigned *__restrict__ status)
+	       int first_expert, int n_local, const float *__restrict__ silu, unsigned *__restrict__ status, int n_expert_all)
 {
 	constexpr int PARTS = K / 64;
 	constexpr int LPR = PARTS > 16 ? 32 : (PARTS > 8 ? 16 : (PARTS > 4 ? 8 : 4));
@@ -50,9 +50,11 @@ decode_gate_up(const uint8_t *__restrict__ wg, const uint8_t *__restrict__ wu, s
 	}
 	pdl_wait();	// the router's top-k (and x) are visible from here on
 	pdl_trigger();	// the down kernel may start fetching its weights
-	const int le = topk_idx[slot] - first_expert;
+	const int ge = topk_idx[slot];
+	const int le = ge - first_expert;
 	if (le < 0 || le >= n_local) {
-		if (threadIdx.x == 0 && blockIdx.x == 0)
+		// n_expert_all > 0 (expert-parallel decode on replicated tokens): the slot belongs to another rank
+		if (!(n_expert_all > 0 && ge >= 0 && ge < n_expert_all) && threadIdx.x == 0 && blockIdx.x == 0)
 			atomicOr(status, ST_BAD_EXPERT);
 		return;
 	}
@@ -207,6 +209,125 @@ decode_down_combine(const uint8_t *__restrict__ wd, size_t expert_stride, int ro
 	}
 }
 
+// Expert-parallel decode on replicated tokens: every rank has routed the same tokens to the same
+// experts; this rank reduces the down rows of the slots whose expert it owns and stores each
+// unweighted row value into the y rows (token, slot) of EVERY rank's region (plain stores over
+// NVLink, 64 bytes per tile, slot and rank).  The combine (ep_combine_rows) then runs on every rank
+// over all slots in slot order — the reference's order (model_qwen3.c:458-467), so the result is
+// bit-identical to the one-GPU decode kernels.  A peer's y rows of the previous step may only be
+// overwritten once that peer has started this step (its pub flag): the CTA waits for all pub
+// flags first (bounded; they are words of this rank's own region).
+template <WKind KIND, int K>
+__global__ void __launch_bounds__(DEC_THREADS, 1)
+decode_down_peer(const uint8_t *__restrict__ wd, size_t expert_stride, int rows_per_expert, int rows_per_tile,
+		 const float *__restrict__ h, int top_k, const int *__restrict__ topk_idx, const EpView v,
+		 const unsigned *__restrict__ step_dev, long long budget, int first_expert, int n_local, unsigned *__restrict__ status)
+{
+	constexpr int PARTS = K / 64;
+	constexpr int LPR = PARTS > 16 ? 32 : (PARTS > 8 ? 16 : (PARTS > 4 ? 8 : 4));
+	constexpr int RPW = 32 / LPR;
+	constexpr int NB = K / QK_K;
+	constexpr int ROWS_PER_PASS = (DEC_THREADS / 32) * RPW;
+	constexpr int MAX_PASSES = 4;
+	extern __shared__ __align__(128) uint8_t dsm[];
+	__shared__ uint64_t bar[MAX_TOP_K];
+	__shared__ int s_le[MAX_TOP_K];
+	const int t = blockIdx.y;
+	const int r0 = blockIdx.x * rows_per_tile;
+	const int r1 = min(r0 + rows_per_tile, rows_per_expert);
+	const uint32_t tile_bytes = (uint32_t)(tile_offset<KIND>(NB, r1) - tile_offset<KIND>(NB, r0));
+	float *hs = reinterpret_cast<float *>(dsm + (size_t)top_k * tile_bytes);
+	if (threadIdx.x == 0) {
+		for (int j = 0; j < top_k; j++)
+			ptx::mbar_init(ptx::smem_u32(&bar[j]), 1);
+		ptx::fence_barrier_init();
+		ptx::fence_proxy_async_smem();
+		bool bad = false;
+		for (int j = 0; j < top_k; j++) {
+			const int ge = topk_idx[t * top_k + j];
+			const int le = ge - first_expert;
+			bad |= (ge < 0 || ge >= v.n_expert);
+			s_le[j] = (le >= 0 && le < n_local) ? le : -1;
+		}
+		if (bad) {
+			for (int j = 0; j < top_k; j++)
+				s_le[j] = -1;
+			if (blockIdx.x == 0)
+				atomicOr(status, ST_BAD_EXPERT);
+		}
+		for (int j = 0; j < top_k; j++) {
+			if (s_le[j] < 0)
+				continue;
+			const uint32_t ba = ptx::smem_u32(&bar[j]);
+			ptx::mbar_arrive_expect_tx(ba, tile_bytes);
+			bulk_g2s(ptx::smem_u32(dsm + (size_t)j * tile_bytes), wd + (size_t)s_le[j] * expert_stride + tile_offset<KIND>(NB, r0),
+				 tile_bytes, ba);
+		}
+	}
+	pdl_wait();  // h of the gate/up kernel is visible from here on
+	// every rank has started this step: its y rows of the previous step are combined and may be overwritten
+	const unsigned step = *step_dev;
+	bool ok = true;
+	if ((int)threadIdx.x < v.n_ranks) {
+		const unsigned *flag = reinterpret_cast<const unsigned *>(v.peer[v.rank] + v.off_pub) + threadIdx.x;
+		const long long t0 = clock64();
+		for (;;) {
+			unsigned f;
+			asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(f) : "l"(flag) : "memory");
+			if ((int)(f - step) >= 0)
+				break;
+			if (clock64() - t0 > budget) {
+				ok = false;
+				break;
+			}
+			__nanosleep(100);
+		}
+	}
+	ok = __syncthreads_and(ok);  // (also publishes the barrier initialisation and s_le)
+	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+	const int sub = lane / LPR, part = lane % LPR;
+	const bool lane_on = part < PARTS;
+	if (!ok && threadIdx.x == 0)
+		atomicOr(status, ST_WAIT_TIMEOUT);
+	for (int j = 0; j < top_k; j++) {
+		if (s_le[j] < 0)
+			continue;  // (uniform over the CTA)
+		if (!ok) {  // leave, but not with copies in flight
+			if (threadIdx.x == 0)
+				dec_wait(ptx::smem_u32(&bar[j]), status);
+			continue;
+		}
+		stage_x_lane_major<KIND, LPR>(h + (size_t)(t * top_k + j) * K, hs, PARTS, threadIdx.x, DEC_THREADS);
+		__syncthreads();
+		float xr[64], sx[4];
+		if (lane_on)
+			load_x_lane_major<KIND, LPR>(hs, part, xr, sx);
+		if (!dec_wait(ptx::smem_u32(&bar[j]), status))
+			ok = false;
+		ok = __syncthreads_and(ok);  // hs is free again; a failed wait is seen by all
+		if (!ok)
+			continue;
+		const uint8_t *vd = dsm + (size_t)j * tile_bytes - tile_offset<KIND>(NB, r0);
+#pragma unroll
+		for (int p = 0; p < MAX_PASSES; p++) {
+			const int row = r0 + p * ROWS_PER_PASS + warp * RPW + sub;
+			if (r0 + p * ROWS_PER_PASS >= r1)
+				break;
+			float val = 0.f;
+			if (lane_on && row < r1)
+				val = PartDot<KIND>::dot(PartDot<KIND>::template load<true>(vd, NB, row, part), part, xr, sx);
+#pragma unroll
+			for (int o = LPR / 2; o > 0; o >>= 1)
+				val += __shfl_xor_sync(0xffffffffu, val, o);
+			if (part == 0 && row < r1) {
+				const size_t at = (size_t)(t * top_k + j) * rows_per_expert + row;
+				for (int r = 0; r < v.n_ranks; r++)
+					reinterpret_cast<float *>(v.peer[r] + v.off_y)[at] = val;
+			}
+		}
+	}
+}
+
 // ---- host side ----
 
 constexpr int DEC_MAX_SMEM = 200 * 1024;
@@ -218,7 +339,7 @@ static size_t row_bytes_of(int k)
 }
 
 template <WKind KIND, int K>
-static int launch_dec_gu_t(tie_cuda_ctx *c, const Layer &L, const float *x, int n_rows)
+static int launch_dec_gu_t(tie_cuda_ctx *c, const Layer &L, const float *x, int n_rows, int n_expert_all)
 {
 	const int rows = L.gate.rows;
 	const size_t rb = row_bytes_of<KIND>(K);
@@ -243,7 +364,7 @@ static int launch_dec_gu_t(tie_cuda_ctx *c, const Layer &L, const float *x, int 
 	cfg.numAttrs = 1;
 	TIE_CUDA_TRY(c, cudaLaunchKernelEx(&cfg, decode_gate_up<KIND, K>, (const uint8_t *)L.gate.ptr, (const uint8_t *)L.up.ptr,
 					   L.gate.expert_stride, rows, rpt, x, c->cfg.top_k, (const int *)c->s.topk_idx, c->s.h,
-					   c->first_expert, c->n_local, (const float *)c->silu, c->s.status));
+					   c->first_expert, c->n_local, (const float *)c->silu, c->s.status, n_expert_all));
 	c->launches++;
 	return TIE_CUDA_OK;
 }
@@ -276,6 +397,34 @@ static int launch_dec_dn_t(tie_cuda_ctx *c, const Layer &L, int n_tokens, const 
 	return TIE_CUDA_OK;
 }
 
+template <WKind KIND, int K>
+static int launch_dec_dn_peer_t(tie_cuda_ctx *c, const Layer &L, int n_tokens)
+{
+	const int rows = L.down.rows, top_k = c->cfg.top_k;
+	const size_t rb = row_bytes_of<KIND>(K);
+	const int rpt = 16;
+	const size_t smem = (size_t)top_k * rpt * rb + (size_t)2 * 2 * K * 4;
+	if (smem > (size_t)DEC_MAX_SMEM)
+		return TIE_CUDA_ENOTSUP;
+	const int tiles = (rows + rpt - 1) / rpt;
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(decode_down_peer<KIND, K>, cudaFuncAttributeMaxDynamicSharedMemorySize, DEC_MAX_SMEM));
+	cudaLaunchConfig_t cfg = {};
+	cfg.gridDim = dim3(tiles, n_tokens);
+	cfg.blockDim = dim3(DEC_THREADS);
+	cfg.dynamicSmemBytes = smem;
+	cfg.stream = c->stream;
+	cudaLaunchAttribute attr[1];
+	attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+	attr[0].val.programmaticStreamSerializationAllowed = 1;
+	cfg.attrs = attr;
+	cfg.numAttrs = 1;
+	TIE_CUDA_TRY(c, cudaLaunchKernelEx(&cfg, decode_down_peer<KIND, K>, (const uint8_t *)L.down.ptr, L.down.expert_stride, rows, rpt,
+					   (const float *)c->s.h, top_k, (const int *)c->s.topk_idx, c->ep.view,
+					   (const unsigned *)c->ep.step_dev, c->ep.wait_cycles, c->first_expert, c->n_local, c->s.status));
+	c->launches++;
+	return TIE_CUDA_OK;
+}
+
 #define TIE_DEC_DIMS(X) X(256) X(512) X(768) X(1024) X(2048)
 
 bool decode_supported(const tie_cuda_ctx *c, const Layer &L, int n_tokens)
@@ -286,13 +435,14 @@ bool decode_supported(const tie_cuda_ctx *c, const Layer &L, int n_tokens)
 }
 
 // x [n_tokens][hidden] -> h [(token, slot)][ffn] (sorted nowhere: rows are the top-k entries themselves)
-int launch_decode_gate_up(tie_cuda_ctx *c, const Layer &L, const float *x, int n_tokens)
+int launch_decode_gate_up(tie_cuda_ctx *c, const Layer &L, const float *x, int n_tokens, bool foreign_slots_ok)
 {
 	const int n_rows = n_tokens * c->cfg.top_k;
+	const int nea = foreign_slots_ok ? c->cfg.n_expert : 0;
 	switch (L.gate.k) {
 #define X(KK)                                                                                                   \
 	case KK:                                                                                                \
-		return L.gate.kind == W_Q4K ? launch_dec_gu_t<W_Q4K, KK>(c, L, x, n_rows) : launch_dec_gu_t<W_Q6K_R8, KK>(c, L, x, n_rows);
+		return L.gate.kind == W_Q4K ? launch_dec_gu_t<W_Q4K, KK>(c, L, x, n_rows, nea) : launch_dec_gu_t<W_Q6K_R8, KK>(c, L, x, n_rows, nea);
 		TIE_DEC_DIMS(X)
 #undef X
 	default:
@@ -308,6 +458,20 @@ int launch_decode_down_combine(tie_cuda_ctx *c, const Layer &L, int n_tokens, co
 	case KK:                                                                                                       \
 		return L.down.kind == W_Q4K ? launch_dec_dn_t<W_Q4K, KK>(c, L, n_tokens, residual, out)                \
 					    : launch_dec_dn_t<W_Q6K_R8, KK>(c, L, n_tokens, residual, out);
+		TIE_DEC_DIMS(X)
+#undef X
+	default:
+		return TIE_CUDA_ENOTSUP;
+	}
+}
+
+// h (local slots) -> the y rows of every rank's region (expert-parallel decode on replicated tokens)
+int launch_decode_down_peer(tie_cuda_ctx *c, const Layer &L, int n_tokens)
+{
+	switch (L.down.k) {
+#define X(KK)                                                                                              \
+	case KK:                                                                                           \
+		return L.down.kind == W_Q4K ? launch_dec_dn_peer_t<W_Q4K, KK>(c, L, n_tokens) : launch_dec_dn_peer_t<W_Q6K_R8, KK>(c, L, n_tokens);
 		TIE_DEC_DIMS(X)
 #undef X
 	default:

@@ -12,7 +12,9 @@ int launch_router_decode_fused(tie_cuda_ctx *c, const float *x, const float *w, 
 			       int *topk_idx, float *topk_w);
 // decode.cu
 bool decode_supported(const tie_cuda_ctx *c, const Layer &L, int n_tokens);
-int launch_decode_gate_up(tie_cuda_ctx *c, const Layer &L, const float *x, int n_tokens);
+// foreign_slots_ok: slots whose expert another rank owns are skipped instead of reported
+int launch_decode_gate_up(tie_cuda_ctx *c, const Layer &L, const float *x, int n_tokens, bool foreign_slots_ok = false);
+int launch_decode_down_peer(tie_cuda_ctx *c, const Layer &L, int n_tokens);
 int launch_decode_down_combine(tie_cuda_ctx *c, const Layer &L, int n_tokens, const float *residual, float *out);
 int launch_router_rows(tie_cuda_ctx *c, const float *x, const float *w, int n_rows, int in_dim, float *out);
 // decode_fused.cu

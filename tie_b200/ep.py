@@ -399,6 +399,35 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler, co
         be2.moe_block_inplace_ep_ptr(0, h, T3, fl)
         be2.synchronize()
         parity_detail["stack_block_0"] = check(workloads.STACK_BASE_SEED, h0_host, h, sample_rows(T3), block=True)
+
+        # batch-1 decode through the same stack: the token is replicated, every rank routes it, runs
+        # the selected experts it owns and all ranks combine the eight slots (TIE_CUDA_EP_REPLICATED)
+        d0_host = synth.make_x(workloads.STACK_BASE_SEED, 1)
+        d0 = torch.from_numpy(d0_host).cuda()
+        d = d0.clone()
+        fd = fl | moe.EP_REPLICATED
+        decode_steps = 256
+
+        def decode_pass():
+            for l in range(n_layers):
+                be2.moe_block_inplace_ep_ptr(l, d, 1, fd)
+
+        for _ in range(3):
+            decode_pass()
+        be2.synchronize()
+        d.copy_(d0)
+        ms4 = timed(decode_pass, decode_steps)
+        be2.synchronize()
+        by = workloads.algorithmic_bytes(shape, 1, shape.top_k) * n_layers
+        stack["decode"] = {"steps": decode_steps, "us_per_token": ms4 * 1e3, "tokens_per_s": 1.0 / (ms4 * 1e-3),
+                           "algorithmic_bytes_per_token": by, "hbm_gbs_all_ranks": by / (ms4 * 1e-3) / 1e9,
+                           "finite": bool(torch.isfinite(d).all().item()),
+                           "note": "token replicated, redundant routing, each rank runs the selected experts it owns, "
+                                   "down rows stored to every rank, slot-order combine on every rank"}
+        d.copy_(d0)
+        be2.moe_block_inplace_ep_ptr(0, d, 1, fd)
+        be2.synchronize()
+        parity_detail["stack_decode_block_0"] = check(workloads.STACK_BASE_SEED, d0_host, d, [0], block=True)
         dist.barrier()
         be2.close()
 
