@@ -124,10 +124,16 @@ def test_few_tokens_decode_kernels_and_general_streaming_kernels(be, port0, n_to
     _check_ffn(be.moe_ffn(0, x, path=moe.PATH_STREAM | moe.PATH_LEGACY_STREAM), ref_out, tol=1e-5)
 
 
-@pytest.mark.parametrize("path", ["stream", "tensor"])
-def test_batch64_uniform_and_skewed(be, golden, port0, path):
+def _path_flags(path):
+    """stream: CUDA-core streaming kernels; tensor: the grouped GEMM as CTA pairs (the default where
+    the 128-row tiles pair up); tensor_single: one CTA per 128-row tile."""
     from tie_b200 import moe
-    p = moe.PATH_STREAM if path == "stream" else moe.PATH_TENSOR
+    return {"stream": moe.PATH_STREAM, "tensor": moe.PATH_TENSOR, "tensor_single": moe.PATH_TENSOR | moe.PATH_NO_PAIR}[path]
+
+
+@pytest.mark.parametrize("path", ["stream", "tensor", "tensor_single"])
+def test_batch64_uniform_and_skewed(be, golden, port0, path):
+    p = _path_flags(path)
     x = synth.make_x(0, 64)
     ref_out, _, _ = port0.moe_ffn(x)
     g = golden("batch64.npz")
@@ -141,10 +147,9 @@ def test_batch64_uniform_and_skewed(be, golden, port0, path):
     _check_ffn(out_s[gs["rows"]], gs["out_rows"])
 
 
-@pytest.mark.parametrize("path", ["tensor", "stream"])
+@pytest.mark.parametrize("path", ["tensor", "tensor_single", "stream"])
 def test_prefill512(be, golden, port0, path):
-    from tie_b200 import moe
-    p = moe.PATH_STREAM if path == "stream" else moe.PATH_TENSOR
+    p = _path_flags(path)
     x = synth.make_x(0, 512)
     g = golden("prefill512.npz")
     out = be.moe_ffn(0, x, path=p)
@@ -283,7 +288,7 @@ def test_tensor_path_odd_block_counts_and_all_tile_sizes(ref_silu_table, port_li
                        silu_table=ref_silu_table)
     try:
         b.upload_layer(0, layer)
-        for p in (moe.PATH_STREAM, moe.PATH_TENSOR):
+        for p in (moe.PATH_STREAM, moe.PATH_TENSOR, moe.PATH_TENSOR | moe.PATH_NO_PAIR):
             _check_ffn(b.moe_ffn(0, x, router_bias=bias, path=p), ref_out)
     finally:
         b.close()

@@ -265,6 +265,7 @@ int run_experts(tie_cuda_ctx *c, const Layer &L, const float *x_src, int src_div
 	} else {
 		use_tc = tc_supported(c, L) && n_rows >= 2 * c->n_local;
 	}
+	c->tc_no_pair = (flags & TIE_CUDA_PATH_NO_PAIR) != 0;
 	const int direct = (!use_tc && n_rows <= c->cfg.top_k && src_div == c->cfg.top_k) ? 1 : 0;
 	const int n_tile = TC_TOKEN_TILE;
 	c->last_direct_rows = direct ? n_rows : -1;
@@ -811,7 +812,7 @@ int tie_cuda_moe_ffn_biased(tie_cuda_ctx *c, int layer, const float *x, float *o
 	const bool dev = flags & TIE_CUDA_DEVICE;
 	const bool graph = flags & TIE_CUDA_GRAPH;
 	const unsigned kflags = flags & (TIE_CUDA_DEVICE | TIE_CUDA_PATH_MASK | TIE_CUDA_PATH_LEGACY_STREAM | TIE_CUDA_ROUTE_LFM2 |
-					 TIE_CUDA_PATH_DECODE_CHAIN);
+					 TIE_CUDA_PATH_DECODE_CHAIN | TIE_CUDA_PATH_NO_PAIR);
 	const float *bias_dev = nullptr;
 	if (router_bias) {
 		if (dev) {
@@ -868,7 +869,8 @@ int tie_cuda_moe_block_inplace(tie_cuda_ctx *c, int layer, float *hidden_dev, in
 		return TIE_CUDA_EINVAL;
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
 	GraphKey k = {3, layer, n_tokens, hidden_dev, nullptr, nullptr, nullptr,
-		      flags & (TIE_CUDA_PATH_MASK | TIE_CUDA_PATH_LEGACY_STREAM | TIE_CUDA_PATH_DECODE_CHAIN | TIE_CUDA_ROUTE_LFM2)};
+		      flags & (TIE_CUDA_PATH_MASK | TIE_CUDA_PATH_LEGACY_STREAM | TIE_CUDA_PATH_DECODE_CHAIN | TIE_CUDA_ROUTE_LFM2 |
+			       TIE_CUDA_PATH_NO_PAIR)};
 	TRY(run_maybe_graphed(c, flags & TIE_CUDA_GRAPH, k, [&]() -> int {
 		// one token: the RMSNorm is part of the one-kernel step
 		if ((flags & TIE_CUDA_PATH_MASK) != TIE_CUDA_PATH_TENSOR &&
@@ -1174,6 +1176,7 @@ int tie_cuda_ep_compute(tie_cuda_ctx *c, int layer, unsigned flags)
 	if (!tc_supported(c, *L))
 		return TIE_CUDA_ENOTSUP;
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	c->tc_no_pair = (flags & TIE_CUDA_PATH_NO_PAIR) != 0;
 	TRY(launch_ep_index(c));
 	TRY(launch_ep_split_rows(c, L->gate.kind == W_Q4K));
 	prof_mark(c, 3);
@@ -1370,6 +1373,7 @@ int tie_cuda_mat_mat(tie_cuda_ctx *c, const void *w_host, const float *x, float 
 	if ((size_t)batch_len > s.rows_cap || (size_t)batch_len * out_dim > y_cap)
 		return TIE_CUDA_ETOOBIG;
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	c->tc_no_pair = (flags & TIE_CUDA_PATH_NO_PAIR) != 0;
 	const bool dev = flags & TIE_CUDA_DEVICE;
 	const float *x_dev = x;
 	float *o_dev = o;

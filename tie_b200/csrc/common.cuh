@@ -143,7 +143,10 @@ struct tie_cuda_ctx {
 	char cuda_err[1024] = {0};
 	// tensor maps for the tcgen05 path: (x, h, sums of x, sums of h) x (16-, 32-, 64-row boxes)
 	CUtensorMap tmap[12];
+	CUtensorMap tmap_half[12];  // the same with boxes of one half (hi or lo): what a CTA of a pair fetches
 	bool tmaps_ok = false;
+	int tc_pairs = 0;	    // CTA pairs the device holds at once (0: the pair kernels are not used)
+	bool tc_no_pair = false;    // this call asked for the single-CTA grouped GEMM (TIE_CUDA_PATH_NO_PAIR)
 	// host registry for dispatch rows
 	struct Reg {
 		const void *host;

@@ -222,6 +222,111 @@ __device__ __forceinline__ void tmem_ld_wait()
 	asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// ---- CTA pairs (clusters of two CTAs, tcgen05 cta_group::2) ----
+// One tcgen05.mma.cta_group::2, issued by a thread of the even-ranked ("leader") CTA, multiplies
+// 256 rows: rows 0..127 are the A tile in the leader's tensor memory and accumulate into the
+// leader's, rows 128..255 the peer's; the N columns of B come half from each CTA's shared memory
+// (the same offset in both).  Barriers that count arrivals from both CTAs live in the leader.
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+	uint32_t r;
+	asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+	return r;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+	asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The shared::cluster address of the same variable in the leader CTA of the pair (for the leader: its own).
+__device__ __forceinline__ uint32_t leader_addr(uint32_t local_smem_addr)
+{
+	return local_smem_addr & 0xFEFFFFFFu;
+}
+// Arrival on a barrier of the leader CTA, from either CTA of the pair.  Relaxed: what the arrival
+// announces (tensor-memory stores or loads of the arriving thread) is complete before it
+// (tcgen05.wait), and no generic-proxy memory is handed over — a cluster-scope release here was
+// measured to cost the arriving warp about a thousand cycles.
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t local_bar)
+{
+	asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(leader_addr(local_bar)) : "memory");
+}
+// try_wait that also orders the peer CTA's writes (its tensor-memory stores, its arrivals).
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity)
+{
+	uint32_t ok;
+	asm volatile(
+		"{\n\t"
+		".reg .pred p;\n\t"
+		"mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+		"selp.u32 %0, 1, 0, p;\n\t"
+		"}"
+		: "=r"(ok)
+		: "r"(bar), "r"(parity)
+		: "memory");
+	return ok != 0;
+}
+__device__ __forceinline__ bool mbar_try_wait_suspend_cluster(uint32_t bar, uint32_t parity, uint32_t ns)
+{
+	uint32_t ok;
+	asm volatile(
+		"{\n\t"
+		".reg .pred p;\n\t"
+		"mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+		"selp.u32 %0, 1, 0, p;\n\t"
+		"}"
+		: "=r"(ok)
+		: "r"(bar), "r"(parity), "r"(ns)
+		: "memory");
+	return ok != 0;
+}
+// TMA tile load into THIS CTA's shared memory whose completion bytes are counted on the barrier at
+// the same address in the LEADER CTA (no multicast: one destination, one barrier).
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap *tmap, uint32_t local_bar, int x, int y, int z)
+{
+	asm volatile(
+		"cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+		"l"(reinterpret_cast<uint64_t>(tmap)), "r"(leader_addr(local_bar)), "r"(x), "r"(y), "r"(z)
+		: "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t ncols)
+{
+	asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair()
+{
+	asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols)
+{
+	asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem of both CTAs] (+)= A[tmem of both CTAs] * B[shared memory of both CTAs]; lanes with issue != 0 issue.
+__device__ __forceinline__ void mma_f16_ts_pair_if(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate,
+						   uint32_t issue)
+{
+	asm volatile(
+		"{\n\t"
+		".reg .pred p, q;\n\t"
+		"setp.ne.b32 p, %4, 0;\n\t"
+		"setp.ne.b32 q, %5, 0;\n\t"
+		"@q tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+		"}" ::"r"(d_tmem),
+		"r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(issue)
+		: "memory");
+}
+// One arrival on the barrier at this address in BOTH CTAs of the pair once the MMAs issued so far retire.
+__device__ __forceinline__ void mma_commit_pair_if(uint32_t bar, uint32_t issue)
+{
+	asm volatile(
+		"{\n\t"
+		".reg .pred q;\n\t"
+		"setp.ne.b32 q, %1, 0;\n\t"
+		"@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %2;\n\t"
+		"}" ::"r"(bar),
+		"r"(issue), "h"((uint16_t)3)
+		: "memory");
+}
+
 // Shared-memory matrix descriptor, K-major operand, 128-byte swizzle: rows of 64 fp16 (128 B),
 // 8-row groups 1024 B apart (stride byte offset), tile base 1024-byte aligned.  Advancing the
 // start address by 32 B selects the next 16-wide k slice inside the swizzled row.

@@ -36,6 +36,17 @@
 // All hand-offs go through mbarriers (tcgen05.commit on the MMA side).  Every wait is bounded: on
 // a timeout the CTA raises ST_WAIT_TIMEOUT in the status word, all roles leave their loops, tensor
 // memory is released and the kernel returns.
+//
+// PAIR: the kernel runs as clusters of two CTAs (two SMs) that share a token tile and take two
+// neighbouring 128-row weight tiles.  Each CTA loads, expands and drains its own weight tile as
+// above, but the MMAs are issued once for both by the even-ranked CTA (tcgen05.mma.cta_group::2,
+// M = 256): the instruction issue rate of one thread, which bounds the single-CTA form (an MMA
+// costs its issuer ~130 cycles whatever its size), is spent on twice the rows, and the token
+// operand is split between the two CTAs' shared memories — the leader holds the hi rows of the
+// tile, its peer the lo rows, so one MMA per k step covers both (N = 2 x rows) and each CTA
+// fetches half the operand bytes.  Barriers that collect arrivals from both CTAs live in the
+// leader (remote mbarrier arrivals; TMA loads of the peer count their bytes there); the MMA
+// completions are committed to both CTAs at once.  No copy is delivered to more than one CTA.
 #include "common.cuh"
 #include "kernels.cuh"
 #include "tc_dequant.cuh"
@@ -54,7 +65,7 @@ constexpr int TC_DWARPS = 8;		  // drain warps
 constexpr int TC_MWARPS = 2;		  // MMA issuer warps: one per accumulator buffer
 constexpr int TC_THREADS = (TC_PWARPS + TC_DWARPS + TC_MWARPS + 2) * 32;  // + token loader + weight loader
 constexpr int TC_S = 8;	    // ring stages: weight tiles in tensor memory, token tiles in shared memory
-constexpr int TC_NBUF = 4;  // accumulator buffers (two per MMA issuer)
+constexpr int TC_NBUF = 4;  // accumulator buffers of 64 columns (two per MMA issuer); pairs: two of 128 columns
 constexpr int TC_NDS = 8;   // block-factor hand-off buffers (producers -> drain warps)
 constexpr long long TC_WAIT_CYCLES = 1ll << 30;	 // about half a second of SM clocks
 constexpr float TC_H_SCALE = 1.0f / 256.0f;	 // keeps SwiGLU outputs inside fp16 range; exact (power of two)
@@ -89,7 +100,8 @@ struct TcSmem {
 
 struct TcShared {
 	uint64_t full[TC_S];	      // weight stage written by its producer group
-	uint64_t bfull[TC_S];	      // token tiles of the stage landed (TMA transaction bytes)
+	uint64_t bfull[2 * TC_S];     // token tiles of the stage landed (TMA transaction bytes); pairs: a ring of its own, 16 deep
+	uint64_t bempty[4];	      // pairs: the four token stages of a super-block consumed
 	uint64_t empty[TC_S];	      // stage consumed by the MMAs (both operands)
 	uint64_t wfull[TC_NWB_MAX];   // packed super-block landed
 	uint64_t wempty[TC_NWB_MAX];  // ... and expanded
@@ -108,14 +120,15 @@ static_assert(sizeof(TcShared) <= 512, "barrier block");
 // hardware suspend it between polls, so that waiting roles do not take issue slots from the
 // producers.
 // BACKOFF_NS > 0: roles that can afford a few hundred cycles of extra latency also sleep between polls.
-template <int BACKOFF_NS = 0>
+// CL: the barrier collects arrivals of the peer CTA of a pair (acquire at cluster scope).
+template <int BACKOFF_NS = 0, bool CL = false>
 __device__ __forceinline__ bool tc_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag, unsigned *status)
 {
-	if (ptx::mbar_try_wait(bar, parity))
+	if (CL ? ptx::mbar_try_wait_cluster(bar, parity) : ptx::mbar_try_wait(bar, parity))
 		return true;
 	const long long t0 = clock64();
 	uint32_t spins = 0;
-	while (!ptx::mbar_try_wait_suspend(bar, parity, 20000u)) {
+	while (!(CL ? ptx::mbar_try_wait_suspend_cluster(bar, parity, 20000u) : ptx::mbar_try_wait_suspend(bar, parity, 20000u))) {
 		if (BACKOFF_NS > 0)
 			__nanosleep(BACKOFF_NS);
 		if (*abort_flag)
@@ -148,11 +161,15 @@ struct TcItem {
 // tl: how many work items of this CTA precede t; the first TC_ITEMS token-tile records of a CTA
 // are staged in shared memory (s_items) when the kernel starts.
 constexpr int TC_ITEMS = 48;
-__device__ __forceinline__ TcItem tc_item(int t, int tl, const int4 *s_items, int m_tiles, const int4 *__restrict__ tile_info,
-					  int rows_per_matrix)
+// m_items: work items per token tile (128-row tiles, or pairs of them); a CTA of a pair takes the
+// tile 2 * item + its rank.
+template <bool PAIR>
+__device__ __forceinline__ TcItem tc_item(int t, int tl, const int4 *s_items, int m_items, const int4 *__restrict__ tile_info,
+					  int rows_per_matrix, uint32_t rank)
 {
 	TcItem it;
-	const int slot = t / m_tiles, mt = t - slot * m_tiles;
+	const int slot = t / m_items, mi = t - slot * m_items;
+	const int mt = PAIR ? 2 * mi + (int)rank : mi;
 	const int4 ti = tl < TC_ITEMS ? s_items[tl] : __ldg(tile_info + slot);
 	it.le = ti.x;
 	it.row0 = ti.y;
@@ -310,7 +327,7 @@ struct Expander<W_Q6K_R8> {
 // PEER (expert parallelism over peer memory, down product only): sorted row p belongs to row
 // dst.row[p] & 0xFFFFFF of rank dst.row[p] >> 24 and is stored there, into that rank's memory
 // (dst.y[rank], plain stores over NVLink, 128 contiguous bytes per warp and row).
-template <WKind KIND, bool RAW, bool PEER = false>
+template <WKind KIND, bool RAW, bool PEER = false, bool PAIR = false>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant__ CUtensorMap tm32,
 		const __grid_constant__ CUtensorMap tm64, const __grid_constant__ CUtensorMap tq16,
@@ -329,16 +346,24 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 #ifdef TC_TIMING
 	const long long tct_kernel_start = clock64();
 #endif
+	// a pair walks the work items together: its index among the pairs, and this CTA's rank in it
+	const uint32_t rank = PAIR ? ptx::cluster_ctarank() : 0u;
+	const int walker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+	const int stride_t = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+	const int m_items = PAIR ? m_tiles / 2 : m_tiles;
+	constexpr int NBUF = PAIR ? 2 : TC_NBUF;	 // accumulator buffers ...
+	constexpr uint32_t PW = PAIR ? 128u : 64u;	 // ... and their width in tensor-memory columns
 	if (threadIdx.x == 0)
-		s_total = (*(volatile unsigned *)status & ST_WAIT_TIMEOUT) ? 0 : tile_start[n_local] * m_tiles;
+		s_total = (*(volatile unsigned *)status & ST_WAIT_TIMEOUT) ? 0 : tile_start[n_local] * m_items;
 	__syncthreads();
+	// (a CTA of a pair never returns early: its peer would wait for it at the cluster barrier below)
 	const int total = s_total;
-	if ((int)blockIdx.x >= total)
+	if (!PAIR && walker >= total)
 		return;
 	if (threadIdx.x < TC_ITEMS) {
-		const int t = blockIdx.x + threadIdx.x * gridDim.x;
+		const int t = walker + threadIdx.x * stride_t;
 		if (t < total)
-			s_items[threadIdx.x] = tile_info[t / m_tiles];
+			s_items[threadIdx.x] = tile_info[t / m_items];
 	}
 	const int nb = k_dim / QK_K;
 	const int k_iters = k_dim / TC_BK;
@@ -351,24 +376,30 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 	float2 *ds = reinterpret_cast<float2 *>(smem + Sm::OFF_DS);  // [TC_NDS][128] (d, dmin) of the rows (Q4_K)
 	const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-	// token tiles of ring stage s: n_box hi rows, directly followed by n_box lo rows
-	auto b_hi = [&](int s) -> uint32_t { return tiles + s * TC_B_STAGE; };
+	// token tiles of ring stage s: n_box hi rows, directly followed by n_box lo rows.  Pairs: a CTA
+	// holds one half of a tile (8 KB at most), in a ring of its own of 2 x TC_S stages — the
+	// operand of four super-blocks in flight: the fetch of a stage needs the other CTA's consent
+	// (barrier round trips between two SMs), which a ring in step with the weight stages exposes.
+	auto b_hi = [&](int s) -> uint32_t { return tiles + s * (PAIR ? TC_B_STAGE / 2 : TC_B_STAGE); };
 	const uint32_t xq_hi = tiles + Sm::OFF_XQ;
 	auto w_buf = [&](int wb) -> uint32_t { return tiles + Sm::OFF_W + wb * Sm::WBUF; };
 
 	if (threadIdx.x == 0) {
 		for (int s = 0; s < TC_S; s++) {
-			ptx::mbar_init(ptx::smem_u32(&sh->full[s]), TC_PWARPS / 2);
+			ptx::mbar_init(ptx::smem_u32(&sh->full[s]), (PAIR ? 2 : 1) * TC_PWARPS / 2);
 			ptx::mbar_init(ptx::smem_u32(&sh->empty[s]), 1);
 			ptx::mbar_init(ptx::smem_u32(&sh->bfull[s]), 1);
+			ptx::mbar_init(ptx::smem_u32(&sh->bfull[TC_S + s]), 1);
 		}
+		for (int s = 0; s < 4; s++)
+			ptx::mbar_init(ptx::smem_u32(&sh->bempty[s]), 1);
 		for (int s = 0; s < Sm::NWB; s++) {
 			ptx::mbar_init(ptx::smem_u32(&sh->wfull[s]), 1);
 			ptx::mbar_init(ptx::smem_u32(&sh->wempty[s]), TC_PWARPS);
 		}
 		for (int s = 0; s < TC_NBUF; s++) {
 			ptx::mbar_init(ptx::smem_u32(&sh->pfull[s]), 1);
-			ptx::mbar_init(ptx::smem_u32(&sh->pempty[s]), TC_DWARPS);
+			ptx::mbar_init(ptx::smem_u32(&sh->pempty[s]), (PAIR ? 2 : 1) * TC_DWARPS);
 		}
 		ptx::mbar_init(ptx::smem_u32(&sh->xfull), 1);
 		ptx::mbar_init(ptx::smem_u32(&sh->xempty), 1);
@@ -378,9 +409,14 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 		ptx::fence_proxy_async_smem();
 	}
 	constexpr int W_MMA0 = TC_PWARPS + TC_DWARPS, W_TOK = W_MMA0 + TC_MWARPS, W_WGT = W_TOK + 1;
-	if (warp == W_MMA0) {  // the first MMA warp owns the tensor-memory allocation
-		ptx::tmem_alloc(ptx::smem_u32(&sh->tmem_base), TC_TMEM_COLS);
-		ptx::tmem_relinquish();
+	if (warp == W_MMA0) {  // the first MMA warp owns the tensor-memory allocation (pairs: one warp of each CTA, together)
+		if (PAIR) {
+			ptx::tmem_alloc_pair(ptx::smem_u32(&sh->tmem_base), TC_TMEM_COLS);
+			ptx::tmem_relinquish_pair();
+		} else {
+			ptx::tmem_alloc(ptx::smem_u32(&sh->tmem_base), TC_TMEM_COLS);
+			ptx::tmem_relinquish();
+		}
 	}
 	if (warp == W_TOK && lane == 0) {
 		ptx::prefetch_tmap(&tm16);
@@ -399,10 +435,18 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 	}
 	ptx::tc_fence_before();
 	__syncthreads();
+	if (PAIR)
+		ptx::cluster_sync_all();  // both CTAs' barriers are initialised before either signals the other's
 	ptx::tc_fence_after();
 	const uint32_t tmem = sh->tmem_base;
 	volatile uint32_t *abort_flag = &sh->abort;
-	const int stride_t = gridDim.x;
+	// arrival on a barrier that the MMA issuers (in the leader CTA of a pair) wait on
+	auto arrive_issuer = [&](uint64_t *bar) {
+		if (PAIR)
+			ptx::mbar_arrive_leader(ptx::smem_u32(bar));
+		else
+			ptx::mbar_arrive(ptx::smem_u32(bar));
+	};
 
 	if (warp < TC_PWARPS) {
 		// ================= producers: packed blocks (shared memory) -> integer A tiles (tensor memory) =================
@@ -430,7 +474,7 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 		// [grp * hb, grp * hb + hb) of its row and keeps their headers as the super-blocks pass by
 		const int hb = (nb + 1) >> 1;
 		uint4 mh[4];
-		for (int t = blockIdx.x; t < total && alive; t += stride_t) {
+		for (int t = walker; t < total && alive; t += stride_t) {
 			for (int sbi = 0; sbi < nb && alive; sbi++) {
 				const long long tw = TCT_NOW();
 				if (!tc_wait_warp(ptx::smem_u32(&sh->wfull[wb]), wph, abort_flag, status, lane)) {
@@ -480,8 +524,8 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 				ptx::tc_fence_before();
 				__syncwarp();
 				if (lane == 0) {
-					ptx::mbar_arrive(ptx::smem_u32(&sh->full[sa]));
-					ptx::mbar_arrive(ptx::smem_u32(&sh->full[sb2]));
+					arrive_issuer(&sh->full[sa]);
+					arrive_issuer(&sh->full[sb2]);
 					// the packed super-block is expanded by this warp: hand the buffer back to the weight loader
 					ptx::mbar_arrive(ptx::smem_u32(&sh->wempty[wb]));
 				}
@@ -534,7 +578,7 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 				}
 				mph ^= 1u;
 				if (lane == 0)
-					ptx::mbar_arrive(ptx::smem_u32(&sh->full[grp ? s1 : s0]));
+					arrive_issuer(&sh->full[grp ? s1 : s0]);
 				it += 2;
 				slot_of(2, s, ph);
 				g++;
@@ -561,13 +605,14 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 		TCT_DECL(4);
 		const long long tct_start = TCT_NOW();
 		int dtl = 0;
-		for (int t = blockIdx.x; t < total && alive; t += stride_t, dtl++) {
-			const TcItem item = tc_item(t, dtl, s_items, m_tiles, tile_info, rows_per_matrix);
+		for (int t = walker; t < total && alive; t += stride_t, dtl++) {
+			const TcItem item = tc_item<PAIR>(t, dtl, s_items, m_items, tile_info, rows_per_matrix, rank);
 			const int mrow = item.m0 + lrow;
 			// Tokens of this warp: half of the tile's token range, in chunks of 16 accumulator columns.
-			// A tile of up to 32 tokens has its hi and lo products side by side in one accumulator
-			// (columns j and n_box + j, one MMA per k step); a larger tile has them summed by two MMAs.
-			const bool concat = item.n_box <= 32;
+			// A tile of up to 32 tokens (any tile of a pair) has its hi and lo products side by side in
+			// one accumulator (columns j and n_box + j, one MMA per k step); a larger tile of the
+			// single-CTA form has them summed by two MMAs.
+			const bool concat = PAIR || item.n_box <= 32;
 			const int ntok = item.n_box == 64 ? 32 : 16;
 			const int tok0 = chalf * ntok;
 			float acc[TC_NT / 2];
@@ -587,9 +632,9 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 				if (!Q4 && sbi + 1 < nb)
 					dnext = half_bits_to_float(
 						__ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb, mrow & 7, sbi + 1))));
-				const uint32_t buf = g & (TC_NBUF - 1);
+				const uint32_t buf = g & (NBUF - 1);
 				const long long tw = TCT_NOW();
-				if (!tc_wait_warp<100>(ptx::smem_u32(&sh->pfull[buf]), (g / TC_NBUF) & 1u, abort_flag, status, lane)) {
+				if (!tc_wait_warp<100>(ptx::smem_u32(&sh->pfull[buf]), (g / NBUF) & 1u, abort_flag, status, lane)) {
 					alive = false;
 					break;
 				}
@@ -600,30 +645,27 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 				ptx::tc_fence_after();
 				if (Q4 && sbi < nb)
 					scale = ds[(g & (TC_NDS - 1)) * TC_BM + lrow].x;
-				const bool two = tok0 + 16 < item.n_mma && ntok == 32;	// second chunk of 16 columns in use
-				if (tok0 < item.n_mma) {				// warp-uniform
-					uint32_t p[16], p2[16];
-					ptx::tmem_ld16(tlane + TC_COL_P + 64u * buf + tok0, p);
-					if (concat)
-						ptx::tmem_ld16(tlane + TC_COL_P + 64u * buf + item.n_box + tok0, p2);
-					else if (two)
-						ptx::tmem_ld16(tlane + TC_COL_P + 64u * buf + tok0 + 16, p2);
-					ptx::tmem_ld_wait();
+				const uint32_t pcol = tlane + TC_COL_P + PW * buf;
 #pragma unroll
-					for (int j = 0; j < 16; j++) {
-						if (concat) {
-							acc[j] = __fmaf_rn(scale, __uint_as_float(p[j]) + __uint_as_float(p2[j]), acc[j]);
-						} else {
-							acc[j] = __fmaf_rn(scale, __uint_as_float(p[j]), acc[j]);
-							if (two)
-								acc[16 + j] = __fmaf_rn(scale, __uint_as_float(p2[j]), acc[16 + j]);
+				for (int ch = 0; ch < 2; ch++) {  // chunks of 16 accumulator columns
+					const int c0 = tok0 + 16 * ch;
+					if (ch * 16 < ntok && c0 < item.n_mma) {  // warp-uniform
+						uint32_t p[16], p2[16];
+						ptx::tmem_ld16(pcol + c0, p);
+						if (concat)
+							ptx::tmem_ld16(pcol + item.n_box + c0, p2);
+						ptx::tmem_ld_wait();
+#pragma unroll
+						for (int j = 0; j < 16; j++) {
+							const float v = concat ? __uint_as_float(p[j]) + __uint_as_float(p2[j]) : __uint_as_float(p[j]);
+							acc[16 * ch + j] = __fmaf_rn(scale, v, acc[16 * ch + j]);
 						}
 					}
 				}
 				ptx::tc_fence_before();
 				__syncwarp();
 				if (lane == 0)
-					ptx::mbar_arrive(ptx::smem_u32(&sh->pempty[buf]));
+					arrive_issuer(&sh->pempty[buf]);
 				TCT_ADD(1, tl);
 				if (warp == TC_PWARPS)
 					TCT_TRACE(5, g);
@@ -664,9 +706,26 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 		// issuers run concurrently on different buffers.  The whole warp walks the loop (warp-uniform
 		// addresses and descriptors); lane 0 issues.
 		const uint32_t mw = warp - W_MMA0;
-		const uint32_t leader = (lane == 0) ? 1u : 0u;
+		// (pairs: the MMAs of both CTAs are issued by the even-ranked one; its peer's issuer warps idle)
+		// (one issuer alternating between two accumulator buffers was measured slower than two issuers with
+		// one buffer each: the ring round trips of a single consumer are exposed)
+		const uint32_t leader = (lane == 0 && rank == 0) ? 1u : 0u;
+		const bool issuing = rank == 0;
+		auto mma = [&](uint32_t d, uint32_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+			if (PAIR)
+				ptx::mma_f16_ts_pair_if(d, a, b, idesc, accumulate, leader);
+			else
+				ptx::mma_f16_ts_if(d, a, b, idesc, accumulate, leader);
+		};
+		auto commit = [&](uint64_t *bar) {
+			if (PAIR)
+				ptx::mma_commit_pair_if(ptx::smem_u32(bar), leader);
+			else
+				ptx::mma_commit_if(ptx::smem_u32(bar), leader);
+		};
 		int s = 0;
 		uint32_t ph = 0, g = 0, tl = 0, gst = 0;
+		uint32_t bg = 0;  // pairs: super-blocks so far (the token ring holds four of them)
 		bool alive = true;
 		TCT_DECL(8);
 		const long long tct_start = TCT_NOW();
@@ -678,35 +737,40 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 				ph ^= 1u;
 			}
 		};
-		for (int t = blockIdx.x; t < total && alive; t += stride_t, tl++) {
+		for (int t = walker; t < total && alive && issuing; t += stride_t, tl++) {
 			const long long tth = TCT_NOW();
-			const TcItem item = tc_item(t, (int)tl, s_items, m_tiles, tile_info, rows_per_matrix);
+			const TcItem item = tc_item<PAIR>(t, (int)tl, s_items, m_items, tile_info, rows_per_matrix, rank);
 			// up to 32 tokens: hi and lo rows are one N = 2 n_box operand (one MMA per k step);
-			// more: two MMAs of N = n_mma on the hi rows and on the lo rows behind them
-			const bool concat = item.n_box <= 32;
-			const uint32_t idesc = ptx::umma_idesc_f16(TC_BM, concat ? 2 * item.n_box : item.n_mma);
-			const uint32_t idesc_hi = ptx::umma_idesc_f16(TC_BM, concat ? item.n_box : item.n_mma);  // hi rows only
+			// more: two MMAs of N = n_mma on the hi rows and on the lo rows behind them.
+			// Pairs: always one MMA, the hi rows from the leader's shared memory and the lo rows from its peer's.
+			const bool concat = PAIR || item.n_box <= 32;
+			const uint32_t idesc = ptx::umma_idesc_f16(PAIR ? 2 * TC_BM : TC_BM, concat ? 2 * item.n_box : item.n_mma);
+			// min phase, second product: the hi sums only (a pair cannot address one CTA's half: it takes
+			// both, which adds the negligible lo x lo term)
+			const uint32_t idesc_hi = PAIR ? idesc : ptx::umma_idesc_f16(TC_BM, concat ? item.n_box : item.n_mma);
 			const uint32_t lo_off = (uint32_t)item.n_box * 128u;
 			TCT_ADD(6, tth + (long long)(lo_off & 0u));
 			for (int sbi = 0; sbi < (Q4 ? nb + 1 : nb) && alive; sbi++) {
-				const uint32_t buf = g & (TC_NBUF - 1);
+				const uint32_t buf = g & (NBUF - 1);
 				const bool min_phase = Q4 && sbi == nb;
 				const int n_st = min_phase ? 2 : TC_SPB;
 				if ((g & 1u) != mw) {  // the other issuer's phase: skip its stages
 					advance(n_st);
 					g++;
+					if (!min_phase)
+						bg++;
 					continue;
 				}
 				const long long tpe = TCT_NOW();
-				if (g >= (uint32_t)TC_NBUF) {
-					const bool ok = tc_wait(ptx::smem_u32(&sh->pempty[buf]), ((g / TC_NBUF) & 1u) ^ 1u, abort_flag, status);
+				if (g >= (uint32_t)NBUF) {
+					const bool ok = tc_wait(ptx::smem_u32(&sh->pempty[buf]), ((g / NBUF) & 1u) ^ 1u, abort_flag, status);
 					if (!__all_sync(0xffffffffu, ok)) {
 						alive = false;
 						break;
 					}
 				}
 				TCT_ADD(0, tpe);
-				const uint32_t dP = tmem + TC_COL_P + 64u * buf;
+				const uint32_t dP = tmem + TC_COL_P + PW * buf;
 				if (min_phase) {
 					// ---- min phase: D = A_hi.[X_hi | X_lo] + A_lo.X_hi over the sub-block sums ----
 					const long long tmp0 = TCT_NOW();
@@ -730,14 +794,14 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 					const uint64_t xh = ptx::umma_desc_sw128(xq_hi), xl = ptx::umma_desc_sw128(xq_hi + lo_off);
 					const uint32_t ah = tmem + TC_COL_A + 32u * s0, al = tmem + TC_COL_A + 32u * s1;
 					for (int kk = 0; kk < min_k16; kk++) {
-						ptx::mma_f16_ts_if(dP, ah + 8 * kk, xh + 2 * kk, idesc, kk > 0 ? 1u : 0u, leader);
+						mma(dP, ah + 8 * kk, xh + 2 * kk, idesc, kk > 0 ? 1u : 0u);
 						if (!concat)
-							ptx::mma_f16_ts_if(dP, ah + 8 * kk, xl + 2 * kk, idesc, 1u, leader);
-						ptx::mma_f16_ts_if(dP, al + 8 * kk, xh + 2 * kk, idesc_hi, 1u, leader);
+							mma(dP, ah + 8 * kk, xl + 2 * kk, idesc, 1u);
+						mma(dP, al + 8 * kk, xh + 2 * kk, idesc_hi, 1u);
 					}
-					ptx::mma_commit_if(ptx::smem_u32(&sh->empty[s1]), leader);  // both stages (a commit costs an MMA's issue time)
-					ptx::mma_commit_if(ptx::smem_u32(&sh->xempty), leader);
-					ptx::mma_commit_if(ptx::smem_u32(&sh->pfull[buf]), leader);
+					commit(&sh->empty[s1]);	 // both stages (a commit costs an MMA's issue time)
+					commit(&sh->xempty);
+					commit(&sh->pfull[buf]);
 					TCT_TRACE(3, gst - 2);
 					TCT_TRACE(3, gst - 1);
 					TCT_ADD(7, tmp0);
@@ -746,12 +810,15 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 				}
 				for (int q4 = 0; q4 < TC_SPB; q4++) {
 					const long long tb = TCT_NOW();
+					// the token stage: the ring slot itself, or (pairs) slot q4 of the super-block's group in the token ring
+					const int bs = PAIR ? (int)(bg & 3u) * TC_SPB + q4 : s;
+					const uint32_t bph = PAIR ? (bg >> 2) & 1u : ph;
 					// both tests issued back to back; the bounded waits only when one of them fails
-					const bool okb = ptx::mbar_try_wait(ptx::smem_u32(&sh->bfull[s]), ph);
+					const bool okb = ptx::mbar_try_wait(ptx::smem_u32(&sh->bfull[bs]), bph);
 					const bool okf = ptx::mbar_try_wait(ptx::smem_u32(&sh->full[s]), ph);
 					bool ok = true;
 					if (!okb)
-						ok = tc_wait(ptx::smem_u32(&sh->bfull[s]), ph, abort_flag, status);
+						ok = tc_wait(ptx::smem_u32(&sh->bfull[bs]), bph, abort_flag, status);
 					TCT_ADD(1, tb);
 					const long long tf = TCT_NOW();
 					if (ok && !okf)
@@ -764,24 +831,27 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 					TCT_TRACE(2, gst);
 					const long long ti = TCT_NOW();
 					ptx::tc_fence_after();
-					const uint64_t bh = ptx::umma_desc_sw128(b_hi(s)), bl = ptx::umma_desc_sw128(b_hi(s) + lo_off);
+					const uint64_t bh = ptx::umma_desc_sw128(b_hi(bs)), bl = ptx::umma_desc_sw128(b_hi(bs) + lo_off);
 					const uint32_t a = tmem + TC_COL_A + 32u * s;
 #pragma unroll
 					for (int kk = 0; kk < TC_BK / 16; kk++) {
-						ptx::mma_f16_ts_if(dP, a + 8 * kk, bh + 2 * kk, idesc, (q4 > 0 || kk > 0) ? 1u : 0u, leader);
+						mma(dP, a + 8 * kk, bh + 2 * kk, idesc, (q4 > 0 || kk > 0) ? 1u : 0u);
 						if (!concat)
-							ptx::mma_f16_ts_if(dP, a + 8 * kk, bl + 2 * kk, idesc, 1u, leader);
+							mma(dP, a + 8 * kk, bl + 2 * kk, idesc, 1u);
 					}
 					if (q4 & 1)  // stages go back to the producers and the token loader in pairs
-						ptx::mma_commit_if(ptx::smem_u32(&sh->empty[s]), leader);
+						commit(&sh->empty[s]);
 					TCT_ADD(3, ti);
 					TCT_TRACE(3, gst);
 					advance(1);
 				}
 				if (!alive)
 					break;
-				ptx::mma_commit_if(ptx::smem_u32(&sh->pfull[buf]), leader);
+				if (PAIR)  // the super-block's token stages go back to both CTAs' token loaders
+					commit(&sh->bempty[bg & 3u]);
+				commit(&sh->pfull[buf]);
 				g++;
+				bg++;
 			}
 		}
 		TCT_ADD(4, tct_start);
@@ -792,25 +862,66 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 		if (lane == 0) {
 			int s = 0;
 			uint32_t ph = 0, it = 0, tl = 0;
+			uint32_t bgl = 0;  // pairs: super-blocks fetched so far
 			bool alive = true;
 			TCT_DECL(3);
 			const long long tct_start = TCT_NOW();
-			for (int t = blockIdx.x; t < total && alive; t += stride_t, tl++) {
-				const TcItem item = tc_item(t, (int)tl, s_items, m_tiles, tile_info, rows_per_matrix);
-				const uint32_t box_bytes = 2u * (uint32_t)item.n_box * 128u;  // hi + lo rows of one 64-k box
+			for (int t = walker; t < total && alive; t += stride_t, tl++) {
+				const TcItem item = tc_item<PAIR>(t, (int)tl, s_items, m_items, tile_info, rows_per_matrix, rank);
+				// hi + lo rows of one 64-k box.  A pair splits them: the leader fetches the hi rows, its peer the
+				// lo rows (the same box of the operand's other half), each into its own shared memory; all the
+				// bytes are counted on the leader's barrier, whose token loader announces them.
+				const uint32_t box_bytes = 2u * (uint32_t)item.n_box * 128u;
 				const CUtensorMap *tmp = item.n_box == 16 ? &tm16 : (item.n_box == 32 ? &tm32 : &tm64);
-				// the two stages of the min phase (after the super-blocks) carry no token tiles: they only
-				// keep the barrier phases in step; the sub-block sums they need are fetched once the first
-				// super-block's tiles are on their way (the previous work item's min phase is long over then)
-				for (int ki = 0; ki < k_iters + (Q4 ? 2 : 0); ki++) {
-					if (Q4 && ki == (k_iters > TC_SPB ? TC_SPB : 0)) {
-						if (tl >= 1u && !tc_wait(ptx::smem_u32(&sh->xempty), (tl & 1u) ^ 1u, abort_flag, status)) {
+				// the sub-block sums of the work item (Q4_K) are fetched once the first super-block's tiles are on
+				// their way (the previous work item's min phase is long over then)
+				auto fetch_sums = [&]() -> bool {
+					if (tl >= 1u && !tc_wait(ptx::smem_u32(&sh->xempty), (tl & 1u) ^ 1u, abort_flag, status))
+						return false;
+					const uint32_t xb = ptx::smem_u32(&sh->xfull);
+					const CUtensorMap *tqp = item.n_box == 16 ? &tq16 : (item.n_box == 32 ? &tq32 : &tq64);
+					if (PAIR) {
+						if (rank == 0)
+							ptx::mbar_arrive_expect_tx(xb, box_bytes);
+						ptx::tma_load_3d_pair(xq_hi, tqp, xb, 0, item.row0, (int)rank);
+					} else {
+						ptx::mbar_arrive_expect_tx(xb, box_bytes);
+						ptx::tma_load_3d(xq_hi, tqp, xb, 0, item.row0, 0);
+					}
+					return true;
+				};
+				if (PAIR) {
+					// the token ring of a pair: groups of four stages (one super-block), handed back per group
+					for (int sbi = 0; sbi < nb && alive; sbi++) {
+						if (Q4 && sbi == (nb > 1 ? 1 : 0) && !fetch_sums()) {
 							alive = false;
 							break;
 						}
-						const uint32_t xb = ptx::smem_u32(&sh->xfull);
-						ptx::mbar_arrive_expect_tx(xb, box_bytes);
-						ptx::tma_load_3d(xq_hi, item.n_box == 16 ? &tq16 : (item.n_box == 32 ? &tq32 : &tq64), xb, 0, item.row0, 0);
+						const uint32_t q = bgl & 3u;
+						const long long tw = TCT_NOW();
+						if (bgl >= 4u && !tc_wait<100>(ptx::smem_u32(&sh->bempty[q]), ((bgl >> 2) & 1u) ^ 1u, abort_flag, status)) {
+							alive = false;
+							break;
+						}
+						TCT_ADD(0, tw);
+						const long long ti = TCT_NOW();
+						for (int q4 = 0; q4 < TC_SPB; q4++) {
+							const int bs = (int)q * TC_SPB + q4;
+							const uint32_t fb = ptx::smem_u32(&sh->bfull[bs]);
+							if (rank == 0)
+								ptx::mbar_arrive_expect_tx(fb, box_bytes);
+							ptx::tma_load_3d_pair(b_hi(bs), tmp, fb, (sbi * TC_SPB + q4) * TC_BK, item.row0, (int)rank);
+						}
+						TCT_ADD(1, ti);
+						bgl++;
+					}
+				} else {
+				// the two stages of the min phase (after the super-blocks) carry no token tiles: they only
+				// keep the barrier phases in step
+				for (int ki = 0; ki < k_iters + (Q4 ? 2 : 0); ki++) {
+					if (Q4 && ki == (k_iters > TC_SPB ? TC_SPB : 0) && !fetch_sums()) {
+						alive = false;
+						break;
 					}
 					const long long tw = TCT_NOW();
 					if (it >= (uint32_t)TC_S && !tc_wait<100>(ptx::smem_u32(&sh->empty[s | 1]), ph ^ 1u, abort_flag, status)) {
@@ -834,6 +945,7 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 						ph ^= 1u;
 					}
 				}
+				}
 			}
 			TCT_ADD(2, tct_start);
 			TCT_FLUSH(24, 3);
@@ -844,8 +956,8 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 		uint32_t wph = 0, wc = 0;
 		bool alive = true;
 		int wtl = 0;
-		for (int t = blockIdx.x; t < total && alive; t += stride_t, wtl++) {
-			const TcItem item = tc_item(t, wtl, s_items, m_tiles, tile_info, rows_per_matrix);
+		for (int t = walker; t < total && alive; t += stride_t, wtl++) {
+			const TcItem item = tc_item<PAIR>(t, wtl, s_items, m_items, tile_info, rows_per_matrix, rank);
 			for (int sbi = 0; sbi < nb; sbi++) {
 				if (wc >= (uint32_t)Sm::NWB && !tc_wait_warp<100>(ptx::smem_u32(&sh->wempty[wb]), wph ^ 1u, abort_flag, status, lane)) {
 					alive = false;
@@ -877,8 +989,14 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 	}
 	ptx::tc_fence_before();
 	__syncthreads();
-	if (warp == W_MMA0)
-		ptx::tmem_dealloc(tmem, TC_TMEM_COLS);
+	if (PAIR)
+		ptx::cluster_sync_all();  // neither CTA leaves while its peer may still signal its barriers or read its memories
+	if (warp == W_MMA0) {
+		if (PAIR)
+			ptx::tmem_dealloc_pair(tmem, TC_TMEM_COLS);
+		else
+			ptx::tmem_dealloc(tmem, TC_TMEM_COLS);
+	}
 }
 
 // ---- host side ----
@@ -923,7 +1041,9 @@ static int encode_2d(tie_cuda_ctx *c, CUtensorMap *tm, CUtensorMapDataType type,
 
 // Split fp16 operand [hi | lo][rows][cols] (lo array right behind hi), box = 64 columns x box_rows
 // rows x 2, 128-byte swizzle: hi rows land first in shared memory, the lo rows directly behind.
-static int make_tmap(tie_cuda_ctx *c, CUtensorMap *tm, void *base, size_t rows, size_t cols, unsigned box_rows)
+// depth 2: one box brings the hi rows and the lo rows; depth 1: the box is one half (a CTA of a
+// pair fetches the half its rank names with the third coordinate).
+static int make_tmap(tie_cuda_ctx *c, CUtensorMap *tm, void *base, size_t rows, size_t cols, unsigned box_rows, unsigned depth = 2)
 {
 	PFN_encodeTiled enc = get_encode_fn();
 	if (!enc) {
@@ -932,7 +1052,7 @@ static int make_tmap(tie_cuda_ctx *c, CUtensorMap *tm, void *base, size_t rows, 
 	}
 	cuuint64_t dims[3] = {(cuuint64_t)cols, (cuuint64_t)rows, 2};
 	cuuint64_t strides[2] = {(cuuint64_t)cols * 2, (cuuint64_t)rows * cols * 2};
-	cuuint32_t box[3] = {(cuuint32_t)TC_BK, box_rows, 2};
+	cuuint32_t box[3] = {(cuuint32_t)TC_BK, box_rows, depth};
 	cuuint32_t estr[3] = {1, 1, 1};
 	CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
 			 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -989,6 +1109,8 @@ int tc_setup(tie_cuda_ctx *c)
 	for (int a = 0; a < 4; a++)
 		for (int b = 0; b < 3; b++) {
 			int rc = make_tmap(c, &c->tmap[a * 3 + b], bases[a], s.rows_pad, cols[a], 16u << b);
+			if (!rc)
+				rc = make_tmap(c, &c->tmap_half[a * 3 + b], bases[a], s.rows_pad, cols[a], 16u << b, 1);
 			if (rc)
 				return rc;
 		}
@@ -1003,6 +1125,37 @@ int tc_setup(tie_cuda_ctx *c)
 					     TcSmem<W_Q4K>::SMEM));
 	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_sb<W_Q6K_R8, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
 					     TcSmem<W_Q6K_R8>::SMEM));
+	// the CTA-pair forms; how many pairs the device holds at once sizes their (persistent) grids
+#define TC_ATTR_PAIR(KIND, RAW, PEER)                                                                                          \
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_sb<KIND, RAW, PEER, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+					     TcSmem<KIND>::SMEM));                                                             \
+	TIE_CUDA_TRY(c, cudaFuncSetAttribute(grouped_gemm_sb<KIND, RAW, PEER, true>, cudaFuncAttributeNonPortableClusterSizeAllowed, 0))
+	TC_ATTR_PAIR(W_Q4K, false, false);
+	TC_ATTR_PAIR(W_Q4K, true, false);
+	TC_ATTR_PAIR(W_Q4K, false, true);
+	TC_ATTR_PAIR(W_Q6K_R8, false, false);
+	TC_ATTR_PAIR(W_Q6K_R8, true, false);
+	TC_ATTR_PAIR(W_Q6K_R8, false, true);
+#undef TC_ATTR_PAIR
+	{
+		cudaLaunchConfig_t cfg = {};
+		cfg.gridDim = dim3(c->sm_count & ~1);
+		cfg.blockDim = dim3(TC_THREADS);
+		cfg.dynamicSmemBytes = TcSmem<W_Q4K>::SMEM;
+		cudaLaunchAttribute attr[1];
+		attr[0].id = cudaLaunchAttributeClusterDimension;
+		attr[0].val.clusterDim.x = 2;
+		attr[0].val.clusterDim.y = 1;
+		attr[0].val.clusterDim.z = 1;
+		cfg.attrs = attr;
+		cfg.numAttrs = 1;
+		int n_clusters = 0;
+		if (cudaOccupancyMaxActiveClusters(&n_clusters, grouped_gemm_sb<W_Q4K, true, false, true>, &cfg) != cudaSuccess) {
+			cudaGetLastError();
+			n_clusters = 0;
+		}
+		c->tc_pairs = n_clusters < c->sm_count / 2 ? n_clusters : c->sm_count / 2;
+	}
 	c->tmaps_ok = true;
 	return TIE_CUDA_OK;
 }
@@ -1018,11 +1171,36 @@ static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1
 	const int m_tiles = (RAW ? 2 : 1) * t0.rows / TC_BM;
 	const CUtensorMap &w0m = t0.map;
 	const CUtensorMap &w1m = t1 ? t1->map : t0.map;
+	const uint8_t *w1p = t1 ? t1->ptr : nullptr;
+	const int *perm = sorted_out ? nullptr : s.perm;
+	const int out_stride = RAW ? 2 * t0.rows : t0.rows;
+	const EpDst d = dst ? *dst : EpDst();
+	// pairs of CTAs (one MMA issue for two 128-row tiles) where the 128-row tiles pair up
+	if (c->tc_pairs > 0 && !c->tc_no_pair && m_tiles % 2 == 0) {
+		const CUtensorMap *tm = c->tmap_half;
+		cudaLaunchConfig_t cfg = {};
+		cfg.gridDim = dim3(2 * c->tc_pairs);
+		cfg.blockDim = dim3(TC_THREADS);
+		cfg.dynamicSmemBytes = TcSmem<KIND>::SMEM;
+		cfg.stream = c->stream;
+		cudaLaunchAttribute attr[1];
+		attr[0].id = cudaLaunchAttributeClusterDimension;
+		attr[0].val.clusterDim.x = 2;
+		attr[0].val.clusterDim.y = 1;
+		attr[0].val.clusterDim.z = 1;
+		cfg.attrs = attr;
+		cfg.numAttrs = 1;
+		TIE_CUDA_TRY(c, cudaLaunchKernelEx(&cfg, grouped_gemm_sb<KIND, RAW, PEER, true>, tm[arr * 3], tm[arr * 3 + 1], tm[arr * 3 + 2],
+						   tm[(2 + arr) * 3], tm[(2 + arr) * 3 + 1], tm[(2 + arr) * 3 + 2], w0m, w1m, (const uint8_t *)t0.ptr, w1p,
+						   t0.expert_stride, t0.k, (const int4 *)s.tile_info, (const int *)s.tile_start, n_experts, m_tiles, y, perm,
+						   out_stride, out_scale, s.status, t0.rows, d));
+		c->launches++;
+		return TIE_CUDA_OK;
+	}
 	grouped_gemm_sb<KIND, RAW, PEER><<<c->sm_count, TC_THREADS, TcSmem<KIND>::SMEM, c->stream>>>(
 		c->tmap[arr * 3], c->tmap[arr * 3 + 1], c->tmap[arr * 3 + 2], c->tmap[(2 + arr) * 3], c->tmap[(2 + arr) * 3 + 1],
-		c->tmap[(2 + arr) * 3 + 2], w0m, w1m, t0.ptr, t1 ? t1->ptr : nullptr, t0.expert_stride,
-		t0.k, s.tile_info, s.tile_start, n_experts, m_tiles, y, sorted_out ? nullptr : s.perm, RAW ? 2 * t0.rows : t0.rows,
-		out_scale, s.status, t0.rows, dst ? *dst : EpDst());
+		c->tmap[(2 + arr) * 3 + 2], w0m, w1m, t0.ptr, w1p, t0.expert_stride, t0.k, s.tile_info, s.tile_start, n_experts, m_tiles, y, perm,
+		out_stride, out_scale, s.status, t0.rows, d);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }

@@ -19,6 +19,7 @@ PATH_AUTO, PATH_STREAM, PATH_TENSOR = 0, 1 << 8, 2 << 8
 PATH_LEGACY_STREAM = 1 << 10
 PATH_DECODE_CHAIN = 1 << 11  # one token: three chained decode kernels instead of the single cooperative one
 ROUTE_LFM2 = 1 << 12  # LFM2-MoE routing: sigmoid, selection bias, L1-normalised gates (model_lfm2.c:438-473)
+PATH_NO_PAIR = 1 << 14  # tensor path: single-CTA grouped GEMM instead of CTA pairs
 EP_REPLICATED = 1 << 13  # expert-parallel decode: the same 1-4 tokens on every rank
 OK, EINVAL, ENOTSUP, ENOMEM, ECUDA, ENODEV, EKERNEL, ETOOBIG = 0, -1, -2, -3, -4, -5, -6, -7
 
