@@ -261,17 +261,15 @@ def run_stack(n_layers, silu, device, peaks, torch, prefill_tokens=4096, decode_
     for name, T, reps in (("prefill", prefill_tokens, 3), ("decode", 1, decode_steps)):
         h0 = torch.from_numpy(synth.make_x(workloads.STACK_BASE_SEED, T)).cuda()
         h = h0.clone()
-        for _ in range(2):  # warm-up passes also record the graphs
+        for _ in range(2):  # warm-up passes also record the graph
             h.copy_(h0)
-            for l in range(n_layers):
-                be.moe_block_inplace_ptr(l, h, T, flags)
+            be.moe_stack_inplace_ptr(0, n_layers, h, T, flags)
         be.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         h.copy_(h0)
         e0.record()
         for _ in range(reps):
-            for l in range(n_layers):
-                be.moe_block_inplace_ptr(l, h, T, flags)
+            be.moe_stack_inplace_ptr(0, n_layers, h, T, flags)
         e1.record()
         torch.cuda.synchronize()
         be.synchronize()

@@ -420,6 +420,49 @@ def test_two_blocks_chained_teacher_forced(be, layer0, port_lib, ref_silu_table)
         b.close()
 
 
+def test_stack_call_equals_the_per_layer_calls(layer0, ref_silu_table):
+    """tie_cuda_moe_stack_inplace over three layers: one token runs as ONE launch (router rows of the
+    next layer prefetched, a grid barrier between layers) and must leave the same bits as three
+    tie_cuda_moe_block_inplace calls; so must a replay from its CUDA graph, and a 5-token batch
+    (which takes the per-layer sequence inside the call)."""
+    import torch
+    from tie_b200 import moe
+    b = moe.MoeBackend(max_tokens=8, silu_table=ref_silu_table, n_layers=3)
+    try:
+        norm = (1.0 + 0.05 * np.sin(np.arange(2048))).astype(np.float32)
+        b.upload_layer(0, layer0, ffn_norm_w=norm)
+        b.upload_layer(1, synth.make_layer(workloads.STACK_BASE_SEED + 1), ffn_norm_w=np.ones(2048, np.float32))
+        b.upload_layer(2, synth.make_layer(workloads.STACK_BASE_SEED + 2), ffn_norm_w=norm)
+        for T in (1, 5):
+            h0 = torch.from_numpy(synth.make_x(workloads.STACK_BASE_SEED, T)).cuda()
+            want = h0.clone()
+            for l in range(3):
+                b.moe_block_inplace_ptr(l, want, T, moe.DEVICE)
+            l0 = b.launch_count
+            got = h0.clone()
+            b.moe_stack_inplace_ptr(0, 3, got, T, moe.DEVICE)
+            if T == 1:
+                assert b.launch_count - l0 == 1
+            assert np.array_equal(bits(got.cpu().numpy()), bits(want.cpu().numpy()))
+            g = h0.clone()
+            for rep in range(3):  # capture, then replays; the epoch of the grid barriers advances on the device
+                g.copy_(h0)
+                b.moe_stack_inplace_ptr(0, 3, g, T, moe.DEVICE | moe.GRAPH)
+                assert np.array_equal(bits(g.cpu().numpy()), bits(want.cpu().numpy())), rep
+        # a sub-range, and arguments out of range
+        h = torch.from_numpy(synth.make_x(5, 1)).cuda()
+        w = h.clone()
+        b.moe_block_inplace_ptr(1, w, 1, moe.DEVICE)
+        b.moe_block_inplace_ptr(2, w, 1, moe.DEVICE)
+        b.moe_stack_inplace_ptr(1, 2, h, 1, moe.DEVICE)
+        assert np.array_equal(bits(h.cpu().numpy()), bits(w.cpu().numpy()))
+        with pytest.raises(moe.TieCudaError) as ei:
+            b.moe_stack_inplace_ptr(2, 2, h, 1, moe.DEVICE)
+        assert ei.value.code == moe.EINVAL
+    finally:
+        b.close()
+
+
 def test_all_48_blocks_of_the_stack_teacher_forced(port_lib, ref_silu_table):
     """The whole 48-block stack (independent seeded weights per block, h += MoE(RMSNorm(h)), norm
     weight 1, eps 1e-6) on 1 token (the one-kernel decode step with the RMSNorm inside) and on 4

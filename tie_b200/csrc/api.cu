@@ -174,7 +174,7 @@ void forget_layer(tie_cuda_ctx *c, int layer, const Layer &L)
 	if (c->stream)
 		cudaStreamSynchronize(c->stream);
 	for (int i = 0; i < c->n_graphs;) {
-		if (c->graphs[i].layer == layer) {
+		if (c->graphs[i].layer == layer || c->graphs[i].kind == 8) {  // (a stack graph spans several layers)
 			cudaGraphExecDestroy(c->graphs[i].exec);
 			c->graphs[i] = c->graphs[--c->n_graphs];
 		} else {
@@ -613,6 +613,9 @@ int tie_cuda_init(tie_cuda_ctx **out, const tie_cuda_config *cfg)
 	c->layers = new (std::nothrow) Layer[cfg->n_layers];
 	if (!c->layers)
 		return fail(TIE_CUDA_ENOMEM);
+	if (cudaMalloc(reinterpret_cast<void **>(&c->df_table), sizeof(DfLayer) * cfg->n_layers) != cudaSuccess ||
+	    cudaMemset(c->df_table, 0, sizeof(DfLayer) * cfg->n_layers) != cudaSuccess)
+		return fail(TIE_CUDA_ENOMEM);
 	float *tab = static_cast<float *>(malloc(SILU_N * sizeof(float)));
 	if (!tab)
 		return fail(TIE_CUDA_ENOMEM);
@@ -665,7 +668,7 @@ void tie_cuda_destroy(tie_cuda_ctx *c)
 	void *dev_ptrs[] = {s.x,     s.out,   s.logits, s.bias,  s.topk_idx, s.topk_w, s.counts, s.offsets, s.tile_start, s.active, s.n_active,
 			    s.perm,  s.h,     s.y,	s.xs_hi, s.hs_hi,  s.status,  s.counter, s.row_expert, c->silu,  c->row_x,
 			    c->row_o, s.ep_counts, s.ep_offsets, s.ep_tile_start, s.ep_active, s.ep_n_active, s.ep_perm, s.ep_inv,
-			    s.tile_info, s.xq_hi, s.hq_hi, s.dec_sync};
+			    s.tile_info, s.xq_hi, s.hq_hi, s.dec_sync, c->df_table};
 	for (void *p : dev_ptrs)
 		if (p)
 			cudaFree(p);
@@ -796,6 +799,8 @@ int tie_cuda_upload_moe_layer(tie_cuda_ctx *c, int layer, const void *router_w_f
 	TRY(add_reg(c, gate_exps, L.gate.bytes, L.gate.ptr, gate_type, L.gate.kind, F, H));
 	TRY(add_reg(c, up_exps, L.up.bytes, L.up.ptr, up_type, L.up.kind, F, H));
 	TRY(add_reg(c, down_exps, L.down.bytes, L.down.ptr, down_type, L.down.kind, H, F));
+	const DfLayer entry = {L.gate.ptr, L.up.ptr, L.down.ptr, L.router_w, ffn_norm_w ? L.norm_w : nullptr};
+	TIE_CUDA_TRY(c, cudaMemcpy(c->df_table + layer, &entry, sizeof(entry), cudaMemcpyHostToDevice));
 	L.uploaded = true;
 	return TIE_CUDA_OK;
 }
@@ -887,6 +892,59 @@ int tie_cuda_moe_block_inplace(tie_cuda_ctx *c, int layer, float *hidden_dev, in
 		}
 		TRY(launch_rms_norm(c, hidden_dev, L->norm_w, c->s.x, n_tokens));
 		return moe_ffn_device(c, *L, c->s.x, hidden_dev, n_tokens, nullptr, hidden_dev, flags);
+	}));
+	if (flags & TIE_CUDA_NO_SYNC)
+		return TIE_CUDA_OK;
+	return check_status(c);
+}
+
+int tie_cuda_moe_stack_inplace(tie_cuda_ctx *c, int first_layer, int n_layers, float *hidden_dev, int n_tokens, unsigned flags)
+{
+	if (!c || n_layers <= 0 || first_layer < 0 || first_layer + n_layers > c->cfg.n_layers || !hidden_dev || n_tokens <= 0 ||
+	    n_tokens > c->cfg.max_tokens || c->cfg.ep_size != 1)
+		return TIE_CUDA_EINVAL;
+	for (int l = first_layer; l < first_layer + n_layers; l++)
+		if (!c->layers[l].uploaded)
+			return TIE_CUDA_EINVAL;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	const unsigned pflags = flags & (TIE_CUDA_PATH_MASK | TIE_CUDA_PATH_LEGACY_STREAM | TIE_CUDA_PATH_DECODE_CHAIN | TIE_CUDA_ROUTE_LFM2 |
+					 TIE_CUDA_PATH_NO_PAIR);
+	const bool decode_paths = (pflags & TIE_CUDA_PATH_MASK) != TIE_CUDA_PATH_TENSOR &&
+				  !(pflags & (TIE_CUDA_PATH_LEGACY_STREAM | TIE_CUDA_PATH_DECODE_CHAIN | TIE_CUDA_ROUTE_LFM2));
+	// one token: the whole stack as one launch where the layers share tensor types (the kernel is built per type pair)
+	const Layer &L0 = c->layers[first_layer];
+	bool one_launch = n_tokens == 1 && n_layers > 1 && decode_paths && decode_fused_supported(c, L0, 1);
+	for (int l = first_layer + 1; l < first_layer + n_layers && one_launch; l++) {
+		const Layer &L = c->layers[l];
+		one_launch = L.gate.kind == L0.gate.kind && L.up.kind == L0.up.kind && L.down.kind == L0.down.kind &&
+			     L.gate.expert_stride == L0.gate.expert_stride && L.down.expert_stride == L0.down.expert_stride;
+	}
+	GraphKey k = {8, first_layer, n_tokens, hidden_dev, nullptr, nullptr, reinterpret_cast<const void *>((size_t)n_layers), pflags};
+	TRY(run_maybe_graphed(c, flags & TIE_CUDA_GRAPH, k, [&]() -> int {
+		if (one_launch) {
+			const int rc = launch_decode_fused_stack(c, first_layer, n_layers, hidden_dev);
+			if (rc != TIE_CUDA_ENOTSUP) {
+				if (!rc) {
+					c->last_used_tc = false;
+					c->last_direct_rows = c->cfg.top_k;
+				}
+				return rc;
+			}
+		}
+		for (int l = first_layer; l < first_layer + n_layers; l++) {
+			Layer &L = c->layers[l];
+			if (decode_paths && decode_fused_supported(c, L, n_tokens)) {
+				const int rc = launch_decode_fused(c, L, hidden_dev, nullptr, hidden_dev, hidden_dev, L.norm_w, c->cfg.norm_eps);
+				if (rc != TIE_CUDA_ENOTSUP) {
+					if (rc)
+						return rc;
+					continue;
+				}
+			}
+			TRY(launch_rms_norm(c, hidden_dev, L.norm_w, c->s.x, n_tokens));
+			TRY(moe_ffn_device(c, L, c->s.x, hidden_dev, n_tokens, nullptr, hidden_dev, pflags));
+		}
+		return TIE_CUDA_OK;
 	}));
 	if (flags & TIE_CUDA_NO_SYNC)
 		return TIE_CUDA_OK;

@@ -52,6 +52,14 @@ struct Layer {
 	const void *router_host = nullptr;
 };
 
+// Weights of one layer as the one-token decode kernel reads them when it walks a stack of layers
+// (device pointers; one entry per layer in the context's device table).
+struct DfLayer {
+	const uint8_t *wg, *wu, *wd;
+	const float *router_w;
+	const float *norm_w;  // or null: weight 1
+};
+
 // Scratch arena of one context, sized for max_tokens.
 struct Scratch {
 	float *x = nullptr;	    // [T][H]   staged input (host mode) / normed input (block mode)
@@ -125,6 +133,7 @@ struct tie_cuda_ctx {
 	cudaStream_t stream = nullptr;
 	float *silu = nullptr;	// device [8192]
 	tie::Layer *layers = nullptr;
+	tie::DfLayer *df_table = nullptr;  // device [n_layers]: the layers' weight pointers (stack decode)
 	tie::Scratch s;
 	int first_expert = 0, n_local = 0;
 	// pinned staging for host-pointer calls

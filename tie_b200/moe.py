@@ -27,7 +27,7 @@ OK, EINVAL, ENOTSUP, ENOMEM, ECUDA, ENODEV, EKERNEL, ETOOBIG = 0, -1, -2, -3, -4
 EXPORTS = [
     "tie_cuda_init", "tie_cuda_destroy", "tie_cuda_strerror", "tie_cuda_last_cuda_error", "tie_cuda_set_stream",
     "tie_cuda_synchronize", "tie_cuda_silu_table_default", "tie_cuda_upload_moe_layer", "tie_cuda_weight_bytes",
-    "tie_cuda_moe_ffn", "tie_cuda_moe_block_inplace", "tie_cuda_moe_route", "tie_cuda_moe_ffn_biased",
+    "tie_cuda_moe_ffn", "tie_cuda_moe_block_inplace", "tie_cuda_moe_stack_inplace", "tie_cuda_moe_route", "tie_cuda_moe_ffn_biased",
     "tie_cuda_moe_expert_rows", "tie_cuda_moe_combine", "tie_cuda_make_current", "tie_cuda_register_tensor",
     "tie_cuda_mat_vec_row_f32_q4k_f32", "tie_cuda_mat_vec_row_f32_q6k_f32", "tie_cuda_mat_vec_row_f32_f32_f32",
     "tie_cuda_swiglu_f32_f32", "tie_cuda_dispatch_status", "tie_cuda_launch_count", "tie_cuda_last_active_experts",
@@ -95,6 +95,8 @@ def load_library() -> ctypes.CDLL:
     L.tie_cuda_moe_ffn_biased.argtypes = [vp, i32, vp, vp, i32, vp, u32]
     L.tie_cuda_moe_block_inplace.restype = i32
     L.tie_cuda_moe_block_inplace.argtypes = [vp, i32, vp, i32, u32]
+    L.tie_cuda_moe_stack_inplace.restype = i32
+    L.tie_cuda_moe_stack_inplace.argtypes = [vp, i32, i32, vp, i32, u32]
     L.tie_cuda_moe_route.restype = i32
     L.tie_cuda_moe_route.argtypes = [vp, i32, vp, i32, vp, vp, vp, vp, u32]
     L.tie_cuda_moe_expert_rows.restype = i32
@@ -290,6 +292,10 @@ class MoeBackend:
     def moe_block_inplace_ptr(self, layer_idx: int, hidden, n_tokens: int, flags: int = DEVICE):
         rc = self.L.tie_cuda_moe_block_inplace(self.h, layer_idx, _ptr(hidden), n_tokens, flags)
         self._check(rc, "tie_cuda_moe_block_inplace")
+
+    def moe_stack_inplace_ptr(self, first_layer: int, n_layers: int, hidden, n_tokens: int, flags: int = DEVICE):
+        rc = self.L.tie_cuda_moe_stack_inplace(self.h, first_layer, n_layers, _ptr(hidden), n_tokens, flags)
+        self._check(rc, "tie_cuda_moe_stack_inplace")
 
     def route_ptr(self, layer_idx: int, x, n_tokens: int, topk_idx, topk_w, logits=None, router_bias=None, flags: int = DEVICE):
         rc = self.L.tie_cuda_moe_route(self.h, layer_idx, _ptr(x), n_tokens, _ptr(router_bias), _ptr(topk_idx),
