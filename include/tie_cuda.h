@@ -138,9 +138,9 @@ int tie_cuda_moe_block_inplace(tie_cuda_ctx *c, int layer, float *hidden_dev, in
 /* The same for n_layers consecutive layers, first_layer first: hidden += MoE_l(RMSNorm_l(hidden)) layer
  * after layer, the residual stream staying on the device — the FFN halves of a stack of MoE blocks
  * with nothing between them (a model's attention halves, model_qwen3.c:303-389, are not part of
- * this library; a caller that has them calls tie_cuda_moe_block_inplace per layer).  One token on
- * layers of equal tensor types runs as ONE kernel launch for the whole stack; any other case is
- * the per-layer sequence.  With TIE_CUDA_GRAPH the whole stack replays from one CUDA graph. */
+ * this library; a caller that has them calls tie_cuda_moe_block_inplace per layer).  The layers'
+ * kernels are enqueued back to back; with TIE_CUDA_GRAPH the whole stack replays from ONE CUDA
+ * graph (one launch call per token instead of one per layer). */
 int tie_cuda_moe_stack_inplace(tie_cuda_ctx *c, int first_layer, int n_layers, float *hidden_dev, int n_tokens, unsigned flags);
 
 /* Router only: dispatch_mat_vec on ffn_gate_inp (model_qwen3.c:431, math_avx2.c:228-256),

@@ -421,10 +421,9 @@ def test_two_blocks_chained_teacher_forced(be, layer0, port_lib, ref_silu_table)
 
 
 def test_stack_call_equals_the_per_layer_calls(layer0, ref_silu_table):
-    """tie_cuda_moe_stack_inplace over three layers: one token runs as ONE launch (router rows of the
-    next layer prefetched, a grid barrier between layers) and must leave the same bits as three
-    tie_cuda_moe_block_inplace calls; so must a replay from its CUDA graph, and a 5-token batch
-    (which takes the per-layer sequence inside the call)."""
+    """tie_cuda_moe_stack_inplace over three layers must leave the same bits as three
+    tie_cuda_moe_block_inplace calls, for one token (one cooperative kernel per layer) and for a
+    5-token batch; so must replays of the whole stack from its one CUDA graph."""
     import torch
     from tie_b200 import moe
     b = moe.MoeBackend(max_tokens=8, silu_table=ref_silu_table, n_layers=3)
@@ -438,11 +437,8 @@ def test_stack_call_equals_the_per_layer_calls(layer0, ref_silu_table):
             want = h0.clone()
             for l in range(3):
                 b.moe_block_inplace_ptr(l, want, T, moe.DEVICE)
-            l0 = b.launch_count
             got = h0.clone()
             b.moe_stack_inplace_ptr(0, 3, got, T, moe.DEVICE)
-            if T == 1:
-                assert b.launch_count - l0 == 1
             assert np.array_equal(bits(got.cpu().numpy()), bits(want.cpu().numpy()))
             g = h0.clone()
             for rep in range(3):  # capture, then replays; the epoch of the grid barriers advances on the device

@@ -911,7 +911,8 @@ int tie_cuda_moe_stack_inplace(tie_cuda_ctx *c, int first_layer, int n_layers, f
 					 TIE_CUDA_PATH_NO_PAIR);
 	const bool decode_paths = (pflags & TIE_CUDA_PATH_MASK) != TIE_CUDA_PATH_TENSOR &&
 				  !(pflags & (TIE_CUDA_PATH_LEGACY_STREAM | TIE_CUDA_PATH_DECODE_CHAIN | TIE_CUDA_ROUTE_LFM2));
-	// one token: the whole stack as one launch where the layers share tensor types (the kernel is built per type pair)
+	// (one token through all layers in ONE launch is tried first where the layers share tensor types;
+	// launch_decode_fused_stack reports "not supported" while that kernel is not built)
 	const Layer &L0 = c->layers[first_layer];
 	bool one_launch = n_tokens == 1 && n_layers > 1 && decode_paths && decode_fused_supported(c, L0, 1);
 	for (int l = first_layer + 1; l < first_layer + n_layers && one_launch; l++) {

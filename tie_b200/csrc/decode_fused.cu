@@ -24,12 +24,6 @@
 // the last CTA of every launch advances), so the launch arguments never change and the kernel
 // replays from a CUDA graph.  Every spin is bounded; a CTA that gives up flags the status word,
 // waits (bounded) for its own copies in flight and returns.
-//
-// A STACK of blocks, hidden += MoE_l(RMSNorm_l(hidden)) for consecutive layers l, runs as ONE launch:
-// the phases above repeat per layer with a third grid barrier between layers (the next RMSNorm
-// reads the row every CTA has just written a piece of).  The router row a CTA needs for layer
-// l + 1 is requested (bulk copy into its own buffer) when layer l's weight tiles are, so that
-// phase R of the next layer finds it in shared memory.
 #include "common.cuh"
 #include "kernels.cuh"
 #include "partdot.cuh"
@@ -49,7 +43,6 @@ constexpr long long DF_WAIT_CYCLES = 1ll << 30;
 struct DfShared {
 	uint64_t bar_gu[DF_MAX_CHUNKS];
 	uint64_t bar_dn[MAX_TOP_K];
-	uint64_t bar_r;	 // this CTA's router row (of the next layer) has landed
 	int idx[MAX_TOP_K];
 	float w[MAX_TOP_K], score[MAX_TOP_K];
 	float lg[256];	// the logits (n_expert <= 256)
@@ -59,19 +52,17 @@ struct DfShared {
 };
 
 struct DfArgs {
-	DfLayer first;		 // the first (or only) layer ...
-	const DfLayer *more;	 // ... and, for a stack, the table of the layers that follow it (n_layers - 1 entries)
-	int n_layers;
+	const uint8_t *wg, *wu, *wd;
 	size_t stride_gu, stride_dn;  // bytes per expert
-	const float *x, *bias, *residual, *silu;
-	// norm_eps >= 0: x is the un-normed hidden row, RMSNorm (weights norm_w or 1) happens in the kernel
+	const float *x, *router_w, *bias, *residual, *silu;
+	const float *norm_w;  // norm_eps >= 0: x is the un-normed hidden row, RMSNorm (weights norm_w or 1) happens in the kernel
 	float norm_eps;
 	float *logits, *h, *out, *topk_w;
 	int *topk_idx;
 	unsigned *status, *sync;  // sync[0]: arrivals, sync[1]: epoch
 	int n_expert, top_k, first_expert, n_local;
 	int rpt_gu, tiles_gu, rpt_dn, tiles_dn;
-	uint32_t off_b, off_c, off_v, off_n, off_r;  // shared-memory offsets: down tiles, staged x, slot products, normed x, router row
+	uint32_t off_b, off_c, off_v, off_n;  // shared-memory offsets: down tiles, staged x, slot products, normed x
 };
 
 __device__ __forceinline__ unsigned df_ld_acquire(const unsigned *p)
@@ -101,25 +92,6 @@ __device__ __forceinline__ bool df_grid_barrier(unsigned *counter, unsigned targ
 	}
 	__syncthreads();
 	return sh->ok != 0;
-}
-
-// Bounded wait on a copy barrier in its phase `parity` (the barriers complete once per layer).
-__device__ __forceinline__ bool df_wait(uint32_t bar, uint32_t parity, unsigned *status)
-{
-	long long t0 = 0;
-	uint32_t spins = 0;
-	while (!ptx::mbar_try_wait(bar, parity)) {
-		if ((++spins & 1023u) == 0) {
-			const long long now = clock64();
-			if (t0 == 0)
-				t0 = now;
-			if (now - t0 > DF_WAIT_CYCLES) {
-				atomicOr(status, ST_WAIT_TIMEOUT);
-				return false;
-			}
-		}
-	}
-	return true;
 }
 
 template <WKind KIND, int LPR>
@@ -162,8 +134,6 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 	const int n_chunks = gu_role ? (g1 - g0 + CH - 1) / CH : 0;
 	const uint32_t tile_gu = (uint32_t)(tile_offset<KG>(DK::NB, g1) - tile_offset<KG>(DK::NB, g0));
 	const uint32_t tile_dn = dn_role ? (uint32_t)(tile_offset<KD>(DF::NB, d1) - tile_offset<KD>(DF::NB, d0)) : 0;
-	const bool r_role = cta < a.n_expert;
-	float *wr = reinterpret_cast<float *>(dsm + a.off_r);  // this CTA's router row
 
 	DF_STAMP(0);
 	if (tid == 0) {
@@ -171,298 +141,258 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 			ptx::mbar_init(ptx::smem_u32(&sh.bar_gu[c]), 1);
 		for (int j = 0; j < MAX_TOP_K; j++)
 			ptx::mbar_init(ptx::smem_u32(&sh.bar_dn[j]), 1);
-		ptx::mbar_init(ptx::smem_u32(&sh.bar_r), 1);
 		ptx::fence_barrier_init();
-		ptx::fence_proxy_async_smem();
 		sh.base = df_ld_acquire(a.sync + 1);
-		if (r_role) {  // the first layer's router row: in flight under the RMSNorm
-			const uint32_t ba = ptx::smem_u32(&sh.bar_r);
-			ptx::mbar_arrive_expect_tx(ba, (uint32_t)(K * sizeof(float)));
-			bulk_g2s(ptx::smem_u32(wr), a.first.router_w + (size_t)cta * K, (uint32_t)(K * sizeof(float)), ba);
+	}
+
+	// ---------------- (RMSNorm of the row, every CTA for itself: rms_norm_f32_f32_f32_avx2, math_avx2.c:56-97) ----------------
+	const float *xin = a.x;
+	if (a.norm_eps >= 0.0f) {
+		float *xn = reinterpret_cast<float *>(dsm + a.off_n);
+		for (int i = tid; i < K / 4; i += DF_THREADS)
+			reinterpret_cast<float4 *>(xn)[i] = __ldcg(reinterpret_cast<const float4 *>(a.x) + i);  // (the row is overwritten in place at the end)
+		__syncthreads();
+		if (warp == 0) {
+			float acc = 0.0f;
+			if (lane < 8) {
+#pragma unroll 16
+				for (int i = 0; i < K / 8; i++) {
+					const float v = xn[8 * i + lane];
+					acc = __fmaf_rn(v, v, acc);
+				}
+			}
+			const float ss = hsum8_lanes(acc);  // (l + l4), then + 1, then + 2: the reference's tree
+			if (lane == 0)
+				sh.inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), a.norm_eps)));
+		}
+		__syncthreads();
+		const float inv = sh.inv;
+		for (int i = tid; i < K; i += DF_THREADS)
+			xn[i] = __fmul_rn(__fmul_rn(xn[i], a.norm_w ? a.norm_w[i] : 1.0f), inv);
+		__syncthreads();
+		xin = xn;
+	}
+
+	// ---------------- R: one router logit per CTA ----------------
+	if (cta < a.n_expert) {
+		float *ws = reinterpret_cast<float *>(dsm), *xr = ws + K;
+		const float4 *w4 = reinterpret_cast<const float4 *>(a.router_w + (size_t)cta * K);
+		const float4 *x4 = reinterpret_cast<const float4 *>(xin);
+		for (int i = tid; i < K / 4; i += DF_THREADS) {
+			const float4 wv = __ldg(w4 + i), xv = x4[i];
+			reinterpret_cast<float4 *>(ws)[i] = wv;
+			reinterpret_cast<float4 *>(xr)[i] = xv;
+		}
+		__syncthreads();
+		if (warp == 0) {
+			float acc = 0.0f;
+			if (lane < 8) {
+#pragma unroll 16
+				for (int i = 0; i < K / 8; i++)
+					acc = __fmaf_rn(xr[8 * i + lane], ws[8 * i + lane], acc);
+			}
+			float r = hsum8_lanes(acc);
+			if (lane == 0) {
+				if (a.bias)
+					r = __fadd_rn(r, a.bias[cta]);
+				__stcg(a.logits + cta, r);
+			}
 		}
 	}
+	if (gu_role)
+		stage_x_lane_major<KG, DK::LPR>(xin, xs, DK::PARTS, tid, DF_THREADS);
 	const unsigned base = (__syncthreads(), sh.base);
-	const unsigned G3 = 3u * (unsigned)G;
-	bool r_in_flight = r_role;  // (thread 0's view: a router-row copy of this CTA has been requested and not waited for)
+	DF_STAMP(1);
+	if (!df_grid_barrier(a.sync, base + (unsigned)G, &sh, a.status))
+		return;	 // nothing of this CTA is in flight yet
+	DF_STAMP(2);
 
-	for (int l = 0; l < a.n_layers; l++) {
-		const DfLayer L = l == 0 ? a.first : a.more[l - 1];
-		const uint32_t par = (uint32_t)l & 1u;	 // phase of the copy barriers: each completes once per layer
-		const unsigned lbase = base + (unsigned)l * G3;
-
-		// ---------------- (RMSNorm of the row, every CTA for itself: rms_norm_f32_f32_f32_avx2, math_avx2.c:56-97) ----------------
-		const float *xin = a.x;
-		if (a.norm_eps >= 0.0f) {
-			float *xn = reinterpret_cast<float *>(dsm + a.off_n);
-			for (int i = tid; i < K / 4; i += DF_THREADS)
-				reinterpret_cast<float4 *>(xn)[i] = __ldcg(reinterpret_cast<const float4 *>(a.x) + i);  // (the row is overwritten in place at the end)
-			__syncthreads();
-			if (warp == 0) {
-				float acc = 0.0f;
-				if (lane < 8) {
-#pragma unroll 16
-					for (int i = 0; i < K / 8; i++) {
-						const float v = xn[8 * i + lane];
-						acc = __fmaf_rn(v, v, acc);
-					}
-				}
-				const float ss = hsum8_lanes(acc);  // (l + l4), then + 1, then + 2: the reference's tree
-				if (lane == 0)
-					sh.inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)K), a.norm_eps)));
-			}
-			__syncthreads();
-			const float inv = sh.inv;
-			for (int i = tid; i < K; i += DF_THREADS)
-				xn[i] = __fmul_rn(__fmul_rn(xn[i], L.norm_w ? L.norm_w[i] : 1.0f), inv);
-			__syncthreads();
-			xin = xn;
+	// ---------------- selection (every CTA for itself) and all weight requests ----------------
+	// find_top_k (engine.c:891-914) orders by (score descending, index ascending) — a total order, so
+	// the slot of an expert is the number of experts ahead of it: one thread per expert counts them.
+	if (tid < a.n_expert)
+		sh.lg[tid] = __ldcg(a.logits + tid);
+	__syncthreads();
+	if (tid < a.n_expert) {
+		const float v = sh.lg[tid];
+		int rank = 0;
+		for (int e = 0; e < a.n_expert; e++) {
+			const float o = sh.lg[e];
+			rank += (o > v || (o == v && e < tid)) ? 1 : 0;
 		}
-
-		// ---------------- R: one router logit per CTA ----------------
-		bool alive = true;
-		if (r_role) {
-			float *xr = reinterpret_cast<float *>(dsm);  // x as the logit chain reads it (the normed row is read in place)
-			if (a.norm_eps < 0.0f) {
-				const float4 *x4 = reinterpret_cast<const float4 *>(xin);
-				for (int i = tid; i < K / 4; i += DF_THREADS)
-					reinterpret_cast<float4 *>(xr)[i] = x4[i];
-				__syncthreads();
-			} else {
-				xr = const_cast<float *>(xin);
-			}
-			if (warp == 0) {
-				alive = df_wait(ptx::smem_u32(&sh.bar_r), par, a.status);  // the router row (requested a layer ago)
-				float acc = 0.0f;
-				if (lane < 8 && alive) {
-#pragma unroll 16
-					for (int i = 0; i < K / 8; i++)
-						acc = __fmaf_rn(xr[8 * i + lane], wr[8 * i + lane], acc);
-				}
-				float r = hsum8_lanes(acc);
-				if (lane == 0 && alive) {
-					if (a.bias)
-						r = __fadd_rn(r, a.bias[cta]);
-					__stcg(a.logits + cta, r);
-				}
-			}
-			r_in_flight = false;
+		if (rank < top_k) {
+			sh.idx[rank] = tid;
+			sh.score[rank] = v;
 		}
-		if (gu_role)
-			stage_x_lane_major<KG, DK::LPR>(xin, xs, DK::PARTS, tid, DF_THREADS);
-		alive = __syncthreads_and(alive);
-		DF_STAMP(1);
-		if (!alive || !df_grid_barrier(a.sync, lbase + (unsigned)G, &sh, a.status))
-			return;	 // nothing of this CTA is in flight now
-		DF_STAMP(2);
-
-		// ---------------- selection (every CTA for itself) and all weight requests ----------------
-		// find_top_k (engine.c:891-914) orders by (score descending, index ascending) — a total order, so
-		// the slot of an expert is the number of experts ahead of it: one thread per expert counts them.
-		if (tid < a.n_expert)
-			sh.lg[tid] = __ldcg(a.logits + tid);
-		__syncthreads();
-		if (tid < a.n_expert) {
-			const float v = sh.lg[tid];
-			int rank = 0;
-			for (int e = 0; e < a.n_expert; e++) {
-				const float o = sh.lg[e];
-				rank += (o > v || (o == v && e < tid)) ? 1 : 0;
+	}
+	__syncthreads();
+	if (warp == 0) {  // softmax (engine.c:864-888) with the arithmetic of topk_softmax_warp
+		const float my_score = lane < top_k ? sh.score[lane] : 0.0f;
+		const float mx = __shfl_sync(0xffffffffu, my_score, 0);
+		const float ex = (lane < top_k) ? expf(__fsub_rn(my_score, mx)) : 0.0f;
+		float sum = 0.0f;
+		for (int j = 0; j < top_k; j++)
+			sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, ex, j));
+		const float inv = __fdiv_rn(1.0f, sum);
+		if (lane < top_k)
+			sh.w[lane] = __fmul_rn(ex, inv);
+	}
+	__syncthreads();
+	bool bad = false;
+	for (int j = 0; j < top_k; j++) {
+		const int le = sh.idx[j] - a.first_expert;
+		bad |= (le < 0 || le >= a.n_local);
+	}
+	if (cta == 0 && tid < top_k) {
+		a.topk_idx[tid] = sh.idx[tid];
+		a.topk_w[tid] = sh.w[tid];
+	}
+	if (bad && cta == 0 && tid == 0)
+		atomicOr(a.status, ST_BAD_EXPERT);
+	uint8_t *sg = dsm, *su = dsm + tile_gu, *sd = dsm + a.off_b;
+	// one issuing thread per copy group (issuing a bulk copy costs ~100 cycles): warp c < 8 the
+	// gate/up chunk c, warp 8 + j the down tile of slot j
+	if (lane == 0 && !bad) {
+		ptx::fence_proxy_async_smem();	// the tile area held the router's staging
+		if (warp < DF_MAX_CHUNKS) {
+			const int c = warp;
+			if (gu_role && c < n_chunks) {
+				const size_t eb = (size_t)(sh.idx[slot] - a.first_expert) * a.stride_gu;
+				const int c0 = g0 + c * CH, c1 = min(c0 + CH, g1);
+				const size_t o0 = tile_offset<KG>(DK::NB, c0), o1 = tile_offset<KG>(DK::NB, c1);
+				const uint32_t bytes = (uint32_t)(o1 - o0), rel = (uint32_t)(o0 - tile_offset<KG>(DK::NB, g0));
+				const uint32_t ba = ptx::smem_u32(&sh.bar_gu[c]);
+				ptx::mbar_arrive_expect_tx(ba, 2 * bytes);
+				bulk_g2s(ptx::smem_u32(sg + rel), a.wg + eb + o0, bytes, ba);
+				bulk_g2s(ptx::smem_u32(su + rel), a.wu + eb + o0, bytes, ba);
 			}
-			if (rank < top_k) {
-				sh.idx[rank] = tid;
-				sh.score[rank] = v;
+		} else {
+			const int j = warp - DF_MAX_CHUNKS;
+			if (dn_role && j < top_k) {
+				const uint32_t ba = ptx::smem_u32(&sh.bar_dn[j]);
+				ptx::mbar_arrive_expect_tx(ba, tile_dn);
+				bulk_g2s(ptx::smem_u32(sd + (size_t)j * tile_dn),
+					 a.wd + (size_t)(sh.idx[j] - a.first_expert) * a.stride_dn + tile_offset<KD>(DF::NB, d0), tile_dn, ba);
 			}
 		}
-		__syncthreads();
-		if (warp == 0) {  // softmax (engine.c:864-888) with the arithmetic of topk_softmax_warp
-			const float my_score = lane < top_k ? sh.score[lane] : 0.0f;
-			const float mx = __shfl_sync(0xffffffffu, my_score, 0);
-			const float ex = (lane < top_k) ? expf(__fsub_rn(my_score, mx)) : 0.0f;
-			float sum = 0.0f;
-			for (int j = 0; j < top_k; j++)
-				sum = __fadd_rn(sum, __shfl_sync(0xffffffffu, ex, j));
-			const float inv = __fdiv_rn(1.0f, sum);
-			if (lane < top_k)
-				sh.w[lane] = __fmul_rn(ex, inv);
-		}
-		__syncthreads();
-		bool bad = false;
-		for (int j = 0; j < top_k; j++) {
-			const int le = sh.idx[j] - a.first_expert;
-			bad |= (le < 0 || le >= a.n_local);
-		}
-		if (cta == 0 && tid < top_k && l == a.n_layers - 1) {
-			a.topk_idx[tid] = sh.idx[tid];
-			a.topk_w[tid] = sh.w[tid];
-		}
-		if (bad && cta == 0 && tid == 0)
-			atomicOr(a.status, ST_BAD_EXPERT);
-		uint8_t *sg = dsm, *su = dsm + tile_gu, *sd = dsm + a.off_b;
-		// one issuing thread per copy group (issuing a bulk copy costs ~100 cycles): warp c < 8 the
-		// gate/up chunk c, warp 8 + j the down tile of slot j
-		if (lane == 0 && !bad) {
-			ptx::fence_proxy_async_smem();	// the tile area held the router's staging / the previous layer's staged rows
-			if (warp < DF_MAX_CHUNKS) {
-				const int c = warp;
-				if (gu_role && c < n_chunks) {
-					const size_t eb = (size_t)(sh.idx[slot] - a.first_expert) * a.stride_gu;
-					const int c0 = g0 + c * CH, c1 = min(c0 + CH, g1);
-					const size_t o0 = tile_offset<KG>(DK::NB, c0), o1 = tile_offset<KG>(DK::NB, c1);
-					const uint32_t bytes = (uint32_t)(o1 - o0), rel = (uint32_t)(o0 - tile_offset<KG>(DK::NB, g0));
-					const uint32_t ba = ptx::smem_u32(&sh.bar_gu[c]);
-					ptx::mbar_arrive_expect_tx(ba, 2 * bytes);
-					bulk_g2s(ptx::smem_u32(sg + rel), L.wg + eb + o0, bytes, ba);
-					bulk_g2s(ptx::smem_u32(su + rel), L.wu + eb + o0, bytes, ba);
-				}
-			} else {
-				const int j = warp - DF_MAX_CHUNKS;
-				if (dn_role && j < top_k) {
-					const uint32_t ba = ptx::smem_u32(&sh.bar_dn[j]);
-					ptx::mbar_arrive_expect_tx(ba, tile_dn);
-					bulk_g2s(ptx::smem_u32(sd + (size_t)j * tile_dn),
-						 L.wd + (size_t)(sh.idx[j] - a.first_expert) * a.stride_dn + tile_offset<KD>(DF::NB, d0), tile_dn, ba);
-				}
-			}
-		}
-		// the next layer's router row (the buffer was last read before the barrier above)
-		const bool r_next = r_role && l + 1 < a.n_layers && !bad;
-		if (tid == 0 && r_next) {
-			ptx::fence_proxy_async_smem();
-			const uint32_t ba = ptx::smem_u32(&sh.bar_r);
-			ptx::mbar_arrive_expect_tx(ba, (uint32_t)(K * sizeof(float)));
-			bulk_g2s(ptx::smem_u32(wr), a.more[l].router_w + (size_t)cta * K, (uint32_t)(K * sizeof(float)), ba);
-			r_in_flight = true;
-		}
-		// waits (bounded) for every copy this CTA requested: before it gives up, and harmless otherwise
-		auto drain = [&]() {
-			if (bad)
-				return;
-			for (int c = 0; c < n_chunks; c++)
-				df_wait(ptx::smem_u32(&sh.bar_gu[c]), par, a.status);
-			if (dn_role)
-				for (int j = 0; j < top_k; j++)
-					df_wait(ptx::smem_u32(&sh.bar_dn[j]), par, a.status);
-			if (r_in_flight)
-				df_wait(ptx::smem_u32(&sh.bar_r), par ^ 1u, a.status);
-		};
-
-		// ---------------- G: gate, up, SwiGLU ----------------
-		DF_STAMP(3);
-		if (gu_role && !bad) {
-			const int sub = lane / DK::LPR, part = lane % DK::LPR;
-			const bool lane_on = part < DK::PARTS;
-			float xr[64], sx[4];
-			if (lane_on)
-				load_x_lane_major<KG, DK::LPR>(xs, part, xr, sx);
-			const uint8_t *vg = sg - tile_offset<KG>(DK::NB, g0), *vu = su - tile_offset<KG>(DK::NB, g0);
-			float *hrow = a.h + (size_t)slot * F;
-			int waited = -1;
-			for (int rp = g0; rp < g1 && alive; rp += DK::RPP) {
-				const int chunk = (rp - g0) / CH;
-				if (chunk != waited) {
-					alive = df_wait(ptx::smem_u32(&sh.bar_gu[chunk]), par, a.status);
-					waited = chunk;
-					if (!alive)
-						break;
-				}
-				const int row = rp + warp * DK::RPW + sub;
-				float vgv = 0.f, vuv = 0.f;
-				if (lane_on && row < g1) {
-					vgv = PartDot<KG>::dot(PartDot<KG>::template load<true>(vg, DK::NB, row, part), part, xr, sx);
-					vuv = PartDot<KG>::dot(PartDot<KG>::template load<true>(vu, DK::NB, row, part), part, xr, sx);
-				}
-#pragma unroll
-				for (int o = DK::LPR / 2; o > 0; o >>= 1) {
-					vgv += __shfl_xor_sync(0xffffffffu, vgv, o);
-					vuv += __shfl_xor_sync(0xffffffffu, vuv, o);
-				}
-				if (part == 0 && row < g1)
-					__stcg(hrow + row, swiglu_lut(a.silu, vgv, vuv));
-			}
-		}
-		alive = __syncthreads_and(alive);
-		DF_STAMP(4);
-		if (!alive) {  // a copy never landed: leave, but not with copies in flight
-			if (tid == 0)
-				drain();
+	}
+	// waits (bounded) for every copy this CTA requested: before it gives up, and harmless otherwise
+	auto drain = [&]() {
+		if (bad)
 			return;
-		}
-		if (!df_grid_barrier(a.sync, lbase + 2u * (unsigned)G, &sh, a.status)) {
-			if (tid == 0)
-				drain();
-			return;
-		}
-
-		// ---------------- D: down + combine ----------------
-		DF_STAMP(5);
-		if (dn_role && !bad) {
-			float *hs = reinterpret_cast<float *>(dsm);  // top_k lane-major rows of h (the gate/up tiles are done with)
-			float *vbuf = reinterpret_cast<float *>(dsm + a.off_v);
-			constexpr int XS_T = DF::LPR * 64;
+		for (int c = 0; c < n_chunks; c++)
+			dec_wait(ptx::smem_u32(&sh.bar_gu[c]), a.status);
+		if (dn_role)
 			for (int j = 0; j < top_k; j++)
-				df_stage_lane_major_cg<KD, DF::LPR>(a.h + (size_t)j * F, hs + (size_t)j * XS_T, DF::PARTS, tid);
-			__syncthreads();
-			const int sub = lane / DF::LPR, part = lane % DF::LPR;
-			const bool lane_on = part < DF::PARTS;
-			const int rows = d1 - d0;
-			// rows of a pass are split into warp groups when the tile is shorter than a pass: each group
-			// takes every n_groups-th slot
-			const int n_groups = a.rpt_dn >= DF::RPP ? 1 : DF::RPP / a.rpt_dn;
-			const int span = DF::RPP / n_groups;
-			const int vr = warp * DF::RPW + sub;
-			const int grp = vr / span, lr0 = vr % span;
-			const int passes = (a.rpt_dn + span - 1) / span;
-			for (int j = grp; j < top_k && alive; j += n_groups) {
-				float xr[64], sx[4];
-				if (lane_on)
-					load_x_lane_major<KD, DF::LPR>(hs + (size_t)j * XS_T, part, xr, sx);
-				alive = df_wait(ptx::smem_u32(&sh.bar_dn[j]), par, a.status);
+				dec_wait(ptx::smem_u32(&sh.bar_dn[j]), a.status);
+	};
+
+	// ---------------- G: gate, up, SwiGLU ----------------
+	DF_STAMP(3);
+	bool alive = true;
+	if (gu_role && !bad) {
+		const int sub = lane / DK::LPR, part = lane % DK::LPR;
+		const bool lane_on = part < DK::PARTS;
+		float xr[64], sx[4];
+		if (lane_on)
+			load_x_lane_major<KG, DK::LPR>(xs, part, xr, sx);
+		const uint8_t *vg = sg - tile_offset<KG>(DK::NB, g0), *vu = su - tile_offset<KG>(DK::NB, g0);
+		float *hrow = a.h + (size_t)slot * F;
+		int waited = -1;
+		for (int rp = g0; rp < g1 && alive; rp += DK::RPP) {
+			const int chunk = (rp - g0) / CH;
+			if (chunk != waited) {
+				alive = dec_wait(ptx::smem_u32(&sh.bar_gu[chunk]), a.status);
+				waited = chunk;
 				if (!alive)
 					break;
-				const uint8_t *vd = sd + (size_t)j * tile_dn - tile_offset<KD>(DF::NB, d0);
-				for (int p = 0; p < passes; p++) {
-					const int lr = p * span + lr0;
-					float v = 0.f;
-					if (lane_on && lr < rows)
-						v = PartDot<KD>::dot(PartDot<KD>::template load<true>(vd, DF::NB, d0 + lr, part), part, xr, sx);
-#pragma unroll
-					for (int o = DF::LPR / 2; o > 0; o >>= 1)
-						v += __shfl_xor_sync(0xffffffffu, v, o);
-					if (part == 0 && lr < rows)
-						vbuf[j * a.rpt_dn + lr] = v;
-				}
 			}
-			alive = __syncthreads_and(alive);
-			if (alive) {
-				for (int lr = tid; lr < rows; lr += DF_THREADS) {
-					float acc = 0.f;
-					for (int j = 0; j < top_k; j++)
-						acc = __fmaf_rn(sh.w[j], vbuf[j * a.rpt_dn + lr], acc);	 // slot order, from zero
-					if (a.residual)
-						acc = __fadd_rn(a.residual[d0 + lr], acc);
-					__stcg(a.out + d0 + lr, acc);
-				}
+			const int row = rp + warp * DK::RPW + sub;
+			float vgv = 0.f, vuv = 0.f;
+			if (lane_on && row < g1) {
+				vgv = PartDot<KG>::dot(PartDot<KG>::template load<true>(vg, DK::NB, row, part), part, xr, sx);
+				vuv = PartDot<KG>::dot(PartDot<KG>::template load<true>(vu, DK::NB, row, part), part, xr, sx);
+			}
+#pragma unroll
+			for (int o = DK::LPR / 2; o > 0; o >>= 1) {
+				vgv += __shfl_xor_sync(0xffffffffu, vgv, o);
+				vuv += __shfl_xor_sync(0xffffffffu, vuv, o);
+			}
+			if (part == 0 && row < g1)
+				__stcg(hrow + row, swiglu_lut(a.silu, vgv, vuv));
+		}
+	}
+	alive = __syncthreads_and(alive);
+	DF_STAMP(4);
+	if (!alive) {  // a copy never landed: leave, but not with copies in flight
+		if (tid == 0)
+			drain();
+		return;
+	}
+	if (!df_grid_barrier(a.sync, base + 2u * (unsigned)G, &sh, a.status)) {
+		if (tid == 0)
+			drain();
+		return;
+	}
+
+	// ---------------- D: down + combine ----------------
+	DF_STAMP(5);
+	if (dn_role && !bad) {
+		float *hs = reinterpret_cast<float *>(dsm);  // top_k lane-major rows of h (the gate/up tiles are done with)
+		float *vbuf = reinterpret_cast<float *>(dsm + a.off_v);
+		constexpr int XS_T = DF::LPR * 64;
+		for (int j = 0; j < top_k; j++)
+			df_stage_lane_major_cg<KD, DF::LPR>(a.h + (size_t)j * F, hs + (size_t)j * XS_T, DF::PARTS, tid);
+		__syncthreads();
+		const int sub = lane / DF::LPR, part = lane % DF::LPR;
+		const bool lane_on = part < DF::PARTS;
+		const int rows = d1 - d0;
+		// rows of a pass are split into warp groups when the tile is shorter than a pass: each group
+		// takes every n_groups-th slot
+		const int n_groups = a.rpt_dn >= DF::RPP ? 1 : DF::RPP / a.rpt_dn;
+		const int span = DF::RPP / n_groups;
+		const int vr = warp * DF::RPW + sub;
+		const int grp = vr / span, lr0 = vr % span;
+		const int passes = (a.rpt_dn + span - 1) / span;
+		for (int j = grp; j < top_k && alive; j += n_groups) {
+			float xr[64], sx[4];
+			if (lane_on)
+				load_x_lane_major<KD, DF::LPR>(hs + (size_t)j * XS_T, part, xr, sx);
+			alive = dec_wait(ptx::smem_u32(&sh.bar_dn[j]), a.status);
+			if (!alive)
+				break;
+			const uint8_t *vd = sd + (size_t)j * tile_dn - tile_offset<KD>(DF::NB, d0);
+			for (int p = 0; p < passes; p++) {
+				const int lr = p * span + lr0;
+				float v = 0.f;
+				if (lane_on && lr < rows)
+					v = PartDot<KD>::dot(PartDot<KD>::template load<true>(vd, DF::NB, d0 + lr, part), part, xr, sx);
+#pragma unroll
+				for (int o = DF::LPR / 2; o > 0; o >>= 1)
+					v += __shfl_xor_sync(0xffffffffu, v, o);
+				if (part == 0 && lr < rows)
+					vbuf[j * a.rpt_dn + lr] = v;
 			}
 		}
 		alive = __syncthreads_and(alive);
-		DF_STAMP(6);
-		if (!alive) {
-			if (tid == 0)
-				drain();
-			return;
-		}
-		if (l + 1 < a.n_layers) {
-			// the row is complete once every CTA has stored its rows: the next layer's RMSNorm reads all of it
-			if (!df_grid_barrier(a.sync, lbase + G3, &sh, a.status)) {
-				if (tid == 0)
-					drain();
-				return;
+		if (alive) {
+			for (int lr = tid; lr < rows; lr += DF_THREADS) {
+				float acc = 0.f;
+				for (int j = 0; j < top_k; j++)
+					acc = __fmaf_rn(sh.w[j], vbuf[j * a.rpt_dn + lr], acc);	 // slot order, from zero
+				if (a.residual)
+					acc = __fadd_rn(a.residual[d0 + lr], acc);
+				a.out[d0 + lr] = acc;
 			}
-		} else if (tid == 0) {
-			// the last CTA out advances the epoch for the next launch
-			if (atomicAdd(a.sync, 1u) == lbase + G3 - 1u)
-				atomicExch(a.sync + 1, lbase + G3);
 		}
+	}
+	__syncthreads();
+	DF_STAMP(6);
+	if (tid == 0) {
+		drain();
+		// the last CTA out advances the epoch for the next launch
+		if (alive && atomicAdd(a.sync, 1u) == base + 3u * (unsigned)G - 1u)
+			atomicExch(a.sync + 1, base + 3u * (unsigned)G);
 	}
 }
 
@@ -476,7 +406,7 @@ static size_t df_row_bytes(int k)
 
 struct DfPlan {
 	int rpt_gu, tiles_gu, rpt_dn, tiles_dn, grid;
-	size_t smem, off_b, off_c, off_v, off_n, off_r;
+	size_t smem, off_b, off_c, off_v, off_n;
 	bool ok;
 };
 
@@ -509,27 +439,14 @@ static DfPlan df_plan(const tie_cuda_ctx *c)
 	p.off_c = (p.off_b + (size_t)top_k * tile_dn + 127) / 128 * 128;
 	p.off_v = p.off_c + (size_t)DfDims<K>::LPR * 64 * sizeof(float);
 	p.off_n = (p.off_v + (size_t)top_k * p.rpt_dn * sizeof(float) + 15) / 16 * 16;
-	p.off_r = p.off_n + (size_t)K * sizeof(float);
-	p.smem = p.off_r + (size_t)K * sizeof(float);
+	p.smem = p.off_n + (size_t)K * sizeof(float);
 	p.ok = p.smem <= 220 * 1024;
 	return p;
 }
 
-static DfLayer df_layer_of(const Layer &L, const float *norm_w)
-{
-	DfLayer d;
-	d.wg = L.gate.ptr;
-	d.wu = L.up.ptr;
-	d.wd = L.down.ptr;
-	d.router_w = L.router_w;
-	d.norm_w = norm_w;
-	return d;
-}
-
-// n_layers > 1: the layers after L are read from the context's device table (entries layer + 1 ...).
 template <WKind KG, int K, WKind KD, int F>
 static int df_launch(tie_cuda_ctx *c, const Layer &L, const float *x, const float *bias, const float *residual, float *out,
-		     bool query_only, const float *norm_w, float norm_eps, int n_layers = 1)
+		     bool query_only, const float *norm_w, float norm_eps)
 {
 	const DfPlan p = df_plan<KG, K, KD, F>(c);
 	if (!p.ok)
@@ -538,12 +455,13 @@ static int df_launch(tie_cuda_ctx *c, const Layer &L, const float *x, const floa
 		return TIE_CUDA_OK;
 	Scratch &s = c->s;
 	DfArgs a = {};
-	a.first = df_layer_of(L, norm_w);
-	a.n_layers = n_layers;
-	a.more = n_layers > 1 ? c->df_table + ((&L - c->layers) + 1) : nullptr;
+	a.wg = L.gate.ptr;
+	a.wu = L.up.ptr;
+	a.wd = L.down.ptr;
 	a.stride_gu = L.gate.expert_stride;
 	a.stride_dn = L.down.expert_stride;
 	a.x = x;
+	a.router_w = L.router_w;
 	a.bias = bias;
 	a.residual = residual;
 	a.silu = c->silu;
@@ -566,7 +484,7 @@ static int df_launch(tie_cuda_ctx *c, const Layer &L, const float *x, const floa
 	a.off_c = (uint32_t)p.off_c;
 	a.off_v = (uint32_t)p.off_v;
 	a.off_n = (uint32_t)p.off_n;
-	a.off_r = (uint32_t)p.off_r;
+	a.norm_w = norm_w;
 	a.norm_eps = norm_eps;
 	auto kern = decode1_fused<KG, K, KD, F>;
 	TIE_CUDA_TRY(c, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
@@ -596,7 +514,7 @@ static int df_launch(tie_cuda_ctx *c, const Layer &L, const float *x, const floa
 #define TIE_DF_SHAPES(X) X(2048, 768) X(512, 256)
 
 static int df_dispatch(tie_cuda_ctx *c, const Layer &L, const float *x, const float *bias, const float *residual, float *out,
-		       bool query_only, const float *norm_w = nullptr, float norm_eps = -1.0f, int n_layers = 1)
+		       bool query_only, const float *norm_w = nullptr, float norm_eps = -1.0f)
 {
 	if (L.gate.kind != L.up.kind)
 		return TIE_CUDA_ENOTSUP;
@@ -604,12 +522,12 @@ static int df_dispatch(tie_cuda_ctx *c, const Layer &L, const float *x, const fl
 #define X(KK, FF)                                                                                                              \
 	if (K == KK && F == FF) {                                                                                              \
 		if (L.gate.kind == W_Q4K && L.down.kind == W_Q6K_R8)                                                           \
-			return df_launch<W_Q4K, KK, W_Q6K_R8, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps, n_layers);                    \
+			return df_launch<W_Q4K, KK, W_Q6K_R8, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps);                    \
 		if (L.gate.kind == W_Q4K && L.down.kind == W_Q4K)                                                              \
-			return df_launch<W_Q4K, KK, W_Q4K, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps, n_layers);                      \
+			return df_launch<W_Q4K, KK, W_Q4K, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps);                      \
 		if (L.gate.kind == W_Q6K_R8 && L.down.kind == W_Q6K_R8)                                                        \
-			return df_launch<W_Q6K_R8, KK, W_Q6K_R8, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps, n_layers);                \
-		return df_launch<W_Q6K_R8, KK, W_Q4K, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps, n_layers);                           \
+			return df_launch<W_Q6K_R8, KK, W_Q6K_R8, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps);                \
+		return df_launch<W_Q6K_R8, KK, W_Q4K, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps);                           \
 	}
 	TIE_DF_SHAPES(X)
 #undef X
@@ -630,13 +548,12 @@ int launch_decode_fused(tie_cuda_ctx *c, const Layer &L, const float *x, const f
 	return df_dispatch(c, L, x, bias, residual, out, false, norm_w, norm_eps);
 }
 
-// One token through n_layers consecutive blocks starting at `layer`, hidden += MoE_l(RMSNorm_l(hidden)),
-// as one launch.  The layers must be uploaded with equal tensor types (the caller checks) and listed
-// in the context's device table.
-int launch_decode_fused_stack(tie_cuda_ctx *c, int layer, int n_layers, float *hidden)
+// One token through consecutive layers as ONE launch: not built (the layer loop inside the kernel
+// pushed the reductions' activation registers into local memory and doubled the step's time); the
+// caller runs the per-layer kernels from one CUDA graph instead.
+int launch_decode_fused_stack(tie_cuda_ctx *, int, int, float *)
 {
-	const Layer &L = c->layers[layer];
-	return df_dispatch(c, L, hidden, nullptr, hidden, hidden, false, L.norm_w, c->cfg.norm_eps, n_layers);
+	return TIE_CUDA_ENOTSUP;
 }
 
 }  // namespace tie
