@@ -247,8 +247,10 @@ int tie_cuda_register_tensor(tie_cuda_ctx *c, const void *host_ptr, size_t n_byt
  * tie_cuda_register_tensor, on the tensor-core kernel of the expert products (the tensor is one
  * "expert" owning every row) — the dense FFN and attention projections of a prompt batch.
  * W: the registered host address; X [batch_len][in_dim], O [batch_len][out_dim] fp32, host or
- * device per flags.  Supported: in_dim equal to the context's hidden or ffn_dim, out_dim a
- * multiple of 128, batch_len <= max_tokens * top_k; otherwise TIE_CUDA_ENOTSUP / _ETOOBIG. */
+ * device per flags.  Supported: any in_dim that is a multiple of 256 (a Q4_K tensor with more than
+ * 2048 inputs runs as one launch per 2048 of them, each adding to O), out_dim a multiple of 128;
+ * batch_len is bounded by the context's operand scratch viewed with rows of in_dim values
+ * (about max_tokens * top_k * hidden / in_dim rows); otherwise TIE_CUDA_ENOTSUP / _ETOOBIG. */
 int tie_cuda_mat_mat(tie_cuda_ctx *c, const void *W, const float *X, float *O, int batch_len, int in_dim, int out_dim,
 		     unsigned flags);
 void tie_cuda_mat_vec_row_f32_q4k_f32(const void *X, const void *W, void *O, int in_dim, int start_row, int end_row);

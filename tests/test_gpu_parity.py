@@ -604,10 +604,16 @@ def test_dispatch_rows_from_several_host_threads(be, layer0):
 
 
 @pytest.mark.parametrize("ggml_type,in_dim,out_dim,batch", [(12, 2048, 4096, 100), (14, 2048, 512, 37), (12, 768, 2048, 64),
-                                                             (14, 768, 256, 1)])
+                                                             (14, 768, 256, 1),
+                                                             # the attention output projection of this model (model_qwen3.c:384): 4096 -> 2048;
+                                                             # Q4_K rows of 16 super-blocks run as two launches of 8
+                                                             (12, 4096, 2048, 70), (14, 4096, 2048, 33),
+                                                             # other widths: 5 and 24 super-blocks per row, an odd number of 128-row tiles
+                                                             (12, 1280, 384, 50), (14, 1024, 640, 17), (12, 6144, 256, 40)])
 def test_dense_mat_mat_on_the_grouped_product(be, port_lib, ggml_type, in_dim, out_dim, batch):
     """dispatch_mat_mat (math_dispatch.c:304) for stand-alone Q4_K / Q6_K tensors — attention
-    q/k/v-shaped [4096|512 x 2048] and FFN-shaped ones — against the restatement's mat-vec per row."""
+    q/k/v-shaped [4096|512 x 2048], the attention output projection [2048 x 4096], FFN-shaped and
+    odd-sized ones — against the restatement's mat-vec per row."""
     import torch
     from tie_b200 import moe
     nb = out_dim * (in_dim // 256)
@@ -623,9 +629,14 @@ def test_dense_mat_mat_on_the_grouped_product(be, port_lib, ggml_type, in_dim, o
     od = torch.empty(batch, out_dim, device="cuda")
     be.mat_mat(w, xd, od, batch, in_dim, out_dim, moe.DEVICE)
     assert np.array_equal(bits(od.cpu().numpy()), bits(got))
-    with pytest.raises(moe.TieCudaError) as ei:  # an in_dim the split arrays are not laid out for
+    with pytest.raises(moe.TieCudaError) as ei:  # not the registered tensor's shape
         be.mat_mat(w, x, got, batch, in_dim + 256, out_dim)
     assert ei.value.code == moe.EINVAL
+    # the MoE path of the context is undisturbed by the dense call's use of its operand scratch
+    xs = synth.make_x(0, 40)
+    a = be.moe_ffn(0, xs, path=moe.PATH_TENSOR)
+    be.mat_mat(w, x, got, batch, in_dim, out_dim)
+    assert np.array_equal(bits(be.moe_ffn(0, xs, path=moe.PATH_TENSOR)), bits(a))
 
 
 def test_errors_are_codes_not_exits(be):

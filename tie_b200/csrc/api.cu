@@ -687,8 +687,11 @@ void tie_cuda_destroy(tie_cuda_ctx *c)
 	for (int i = 0; i < c->n_extra; i++)
 		cudaFree(c->extra[i]);
 	free(c->extra);
-	for (int i = 0; i < c->n_regs; i++)
+	for (int i = 0; i < c->n_regs; i++) {
+		if (c->regs[i].dense)
+			delete c->regs[i].dense->view;
 		delete c->regs[i].dense;
+	}
 	free(c->regs);
 	ep_release(c);
 	delete c;
@@ -1404,7 +1407,10 @@ int tie_cuda_register_tensor(tie_cuda_ctx *c, const void *host_ptr, size_t n_byt
 		dense->bytes = n_bytes;
 		dense->host_ptr = host_ptr;
 		int rc = tc_make_weight_map(c, *dense, 1);
+		if (!rc && dense->has_map)
+			rc = tc_make_dense_view(c, *dense);
 		if (rc) {
+			delete dense->view;
 			delete dense;
 			return rc;
 		}
@@ -1423,13 +1429,14 @@ int tie_cuda_mat_mat(tie_cuda_ctx *c, const void *w_host, const float *x, float 
 			reg = &c->regs[i];
 	if (!reg || reg->k != in_dim || reg->rows != out_dim)
 		return TIE_CUDA_EINVAL;
-	int arr = 0;
-	if (!reg->dense || !tc_dense_supported(c, *reg->dense, &arr))
+	if (!reg->dense || !tc_dense_supported(c, *reg->dense))
 		return TIE_CUDA_ENOTSUP;
 	Scratch &s = c->s;
+	const DenseView &v = *reg->dense->view;
 	const size_t T = c->cfg.max_tokens, H = c->cfg.hidden, F = c->cfg.ffn_dim;
 	const size_t y_cap = s.rows_cap * (H > 2 * F ? H : 2 * F);
-	if ((size_t)batch_len > s.rows_cap || (size_t)batch_len * out_dim > y_cap)
+	// (a token box of up to 64 rows may start at the last row: keep that much of the view beyond the batch)
+	if ((size_t)batch_len > s.rows_cap || (size_t)batch_len + 64 > v.rows || (size_t)batch_len * out_dim > y_cap)
 		return TIE_CUDA_ETOOBIG;
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
 	c->tc_no_pair = (flags & TIE_CUDA_PATH_NO_PAIR) != 0;
@@ -1447,14 +1454,22 @@ int tie_cuda_mat_mat(tie_cuda_ctx *c, const void *w_host, const float *x, float 
 	TIE_CUDA_TRY(c, cudaMemsetAsync(s.row_expert, 0, (size_t)batch_len * sizeof(int), c->stream));
 	SortBufs b = {s.counts, s.offsets, s.tile_start, s.active, s.n_active, s.perm, s.tile_info};
 	TRY(launch_sort(c, s.row_expert, batch_len, TC_TOKEN_TILE, 0, 1, b));
+	// the batch, split into fp16 hi + lo (and its sub-block sums for Q4_K), in the tensor's view of the x arrays.
+	// Columns of the sums that the row length leaves unused are read as padding of a 16-deep k step
+	// and must be zero, in this view and, afterwards, in the context's own.
 	const bool sums = reg->dense->kind == W_Q4K;
-	if (arr == 0)
-		TRY(launch_split_rows(c, x_dev, nullptr, 1, batch_len, in_dim, s.xs_hi, s.xs_lo, sums ? s.xq_hi : nullptr,
-				      sums ? s.xq_lo : nullptr));
-	else
-		TRY(launch_split_rows(c, x_dev, nullptr, 1, batch_len, in_dim, s.hs_hi, s.hs_lo, sums ? s.hq_hi : nullptr,
-				      sums ? s.hq_lo : nullptr));
-	TRY(launch_tc_dense(c, *reg->dense, arr, o_dev));
+	const size_t q_bytes = (size_t)batch_len * xq_cols(in_dim) * sizeof(__half);
+	if (sums) {
+		TIE_CUDA_TRY(c, cudaMemsetAsync(s.xq_hi, 0, q_bytes, c->stream));
+		TIE_CUDA_TRY(c, cudaMemsetAsync(s.xq_hi + v.q_lo_off, 0, q_bytes, c->stream));
+	}
+	TRY(launch_split_rows(c, x_dev, nullptr, 1, batch_len, in_dim, s.xs_hi, s.xs_hi + v.lo_off, sums ? s.xq_hi : nullptr,
+			      sums ? s.xq_hi + v.q_lo_off : nullptr));
+	TRY(launch_tc_dense(c, *reg->dense, o_dev));
+	if (sums) {
+		TIE_CUDA_TRY(c, cudaMemsetAsync(s.xq_hi, 0, q_bytes, c->stream));
+		TIE_CUDA_TRY(c, cudaMemsetAsync(s.xq_hi + v.q_lo_off, 0, q_bytes, c->stream));
+	}
 	if (!dev) {
 		TIE_CUDA_TRY(c, cudaMemcpyAsync(o, o_dev, (size_t)batch_len * out_dim * sizeof(float), cudaMemcpyDeviceToHost, c->stream));
 		return check_status(c);

@@ -31,6 +31,13 @@ constexpr unsigned ST_BAD_TILE = 4u;	  // tile bookkeeping out of range
 //  count, 208-byte (row, block) records with every 48-byte quant chunk 16-byte aligned.
 enum WKind : int { W_Q4K = 0, W_Q6K_R8 = 1 };
 
+// A stand-alone (dense) tensor's view of the context's split-operand scratch, with row length k.
+struct DenseView {
+	CUtensorMap full[6], half[6];  // [0-2] operand boxes of 16/32/64 rows, [3-5] sub-block sums; (hi, lo) in one box / one half per box
+	size_t rows = 0;	       // rows the view holds
+	size_t lo_off = 0, q_lo_off = 0;  // element offsets of the lo halves behind the hi halves
+};
+
 struct DevTensor {
 	uint8_t *ptr = nullptr;	 // device
 	int ggml_type = -1;
@@ -42,6 +49,7 @@ struct DevTensor {
 	const void *host_ptr = nullptr;	 // for the dispatch-row registry
 	CUtensorMap map;	 // Q4_K: byte map for the tensor-core path's weight loader
 	bool has_map = false;
+	DenseView *view = nullptr;  // stand-alone tensors only (owned)
 };
 
 struct Layer {

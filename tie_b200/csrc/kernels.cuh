@@ -50,8 +50,9 @@ int launch_swiglu_split(tie_cuda_ctx *c, const float *gu, int n_rows, int ffn, f
 // tensor.cu
 int tc_setup(tie_cuda_ctx *c);
 int tc_make_weight_map(tie_cuda_ctx *c, DevTensor &t, int n_experts = -1);  // default: the context's local experts
-bool tc_dense_supported(const tie_cuda_ctx *c, const DevTensor &t, int *arr);
-int launch_tc_dense(tie_cuda_ctx *c, const DevTensor &t, int arr, float *y);
+bool tc_dense_supported(const tie_cuda_ctx *c, const DevTensor &t);
+int tc_make_dense_view(tie_cuda_ctx *c, DevTensor &t);
+int launch_tc_dense(tie_cuda_ctx *c, const DevTensor &t, float *y);
 bool tc_supported(const tie_cuda_ctx *c, const Layer &L);
 int launch_tc_gate_up(tie_cuda_ctx *c, const Layer &L, int n_rows);
 int launch_tc_swiglu(tie_cuda_ctx *c, const Layer &L, int n_rows, const int *n_rows_dev = nullptr);

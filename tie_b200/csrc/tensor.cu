@@ -56,6 +56,10 @@
 
 namespace tie {
 
+#ifndef TC_EMIT_UNROLL
+#define TC_EMIT_UNROLL 2
+#endif
+constexpr int TC_EMIT_UNROLL_N = TC_EMIT_UNROLL;  // unrolling of the producers' expansion loop
 constexpr int TC_BM = 128;
 constexpr int TC_BK = 64;
 constexpr int TC_SPB = QK_K / TC_BK;	  // stages per super-block
@@ -324,6 +328,12 @@ struct Expander<W_Q6K_R8> {
 // stages: hi and lo tiles of dmin*m) and then the super-blocks (four ring stages each).  Phase
 // number g selects the accumulator buffer (g % 4) and the MMA issuer (g % 2).
 //
+// A launch covers the super-blocks [sb0, sb0 + k_dim / 256) of rows that hold nb_total of them
+// (k_dim is the launch's share of the input dimension); accumulate != 0 adds to what y already
+// holds.  The expert products pass (0, k / 256, 0); a dense Q4_K tensor with more than 2048 inputs
+// runs as several launches of at most 8 super-blocks (the min phase takes the sub-block sums of
+// one 64-wide tile).
+//
 // PEER (expert parallelism over peer memory, down product only): sorted row p belongs to row
 // dst.row[p] & 0xFFFFFF of rank dst.row[p] >> 24 and is stored there, into that rank's memory
 // (dst.y[rank], plain stores over NVLink, 128 contiguous bytes per warp and row).
@@ -335,7 +345,8 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 		const __grid_constant__ CUtensorMap tw0, const __grid_constant__ CUtensorMap tw1, const uint8_t *__restrict__ w0,
 		const uint8_t *__restrict__ w1, size_t expert_stride, int k_dim, const int4 *__restrict__ tile_info,
 		const int *__restrict__ tile_start, int n_local, int m_tiles, float *__restrict__ y, const int *__restrict__ perm,
-		int out_stride, float out_scale, unsigned *__restrict__ status, int rows_per_matrix, const EpDst dst)
+		int out_stride, float out_scale, unsigned *__restrict__ status, int rows_per_matrix, const EpDst dst,
+		const int sb0, const int nb_total, const int accumulate)
 {
 	static_assert(!(RAW && PEER), "peer destinations exist for the down product only");
 	using Sm = TcSmem<KIND>;
@@ -515,8 +526,8 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 					TCT_TRACE(0, it + 2 * grp + 1);
 				}
 				const long long tm = TCT_NOW();
-				// (kept as a loop: the expansion code stays small in the instruction cache)
-#pragma unroll 1
+				// (a loop unrolled twice: two expansions in flight hide their latencies; fully unrolled it is no faster)
+#pragma unroll TC_EMIT_UNROLL_N
 				for (int q = 0; q < 4; q++)
 					ex.emit(2 * grp + (q >> 1), q & 1, lane_base + TC_COL_A + 32u * ((q >> 1) ? sb2 : sa));
 				ptx::tmem_st_wait();
@@ -623,15 +634,15 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 			const uint8_t *grp = nullptr;
 			float dnext = 0.0f;
 			if (!Q4) {
-				grp = (item.mat_sel ? w1 : w0) + (size_t)item.le * expert_stride + (size_t)(mrow >> 3) * q6k_r8_group_bytes(nb);
-				dnext = half_bits_to_float(__ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb, mrow & 7, 0))));
+				grp = (item.mat_sel ? w1 : w0) + (size_t)item.le * expert_stride + (size_t)(mrow >> 3) * q6k_r8_group_bytes(nb_total);
+				dnext = half_bits_to_float(__ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb_total, mrow & 7, sb0))));
 			}
 			// the phase after the last super-block is the min phase (Q4_K): its sums enter with factor -1
 			for (int sbi = 0; sbi < (Q4 ? nb + 1 : nb); sbi++) {
 				float scale = Q4 ? -1.0f : dnext;
 				if (!Q4 && sbi + 1 < nb)
 					dnext = half_bits_to_float(
-						__ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb, mrow & 7, sbi + 1))));
+						__ldg(reinterpret_cast<const unsigned short *>(grp + q6k_r8_d_off(nb_total, mrow & 7, sb0 + sbi + 1))));
 				const uint32_t buf = g & (NBUF - 1);
 				const long long tw = TCT_NOW();
 				if (!tc_wait_warp<100>(ptx::smem_u32(&sh->pfull[buf]), (g / NBUF) & 1u, abort_flag, status, lane)) {
@@ -687,12 +698,14 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 				const int n = tok0 + j;
 				const int rj = RAW ? 0 : __shfl_sync(0xffffffffu, rid, j);
 				if (j < ntok && n < item.n_valid) {
-					if (RAW)
+					if (RAW) {
 						y[(size_t)(item.row0 + n) * out_stride + (size_t)item.mat_sel * rows_per_matrix + mrow] = acc[j];
-					else if (PEER)
+					} else if (PEER) {
 						dst.y[(unsigned)rj >> 24][(size_t)(rj & 0xFFFFFF) * out_stride + mrow] = acc[j] * out_scale;
-					else
-						y[(size_t)rj * out_stride + mrow] = acc[j] * out_scale;
+					} else {
+						float *yp = y + (size_t)rj * out_stride + mrow;
+						*yp = accumulate ? __fadd_rn(*yp, acc[j] * out_scale) : acc[j] * out_scale;
+					}
 				}
 			}
 			TCT_ADD(2, tst);
@@ -883,10 +896,10 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 					if (PAIR) {
 						if (rank == 0)
 							ptx::mbar_arrive_expect_tx(xb, box_bytes);
-						ptx::tma_load_3d_pair(xq_hi, tqp, xb, 0, item.row0, (int)rank);
+						ptx::tma_load_3d_pair(xq_hi, tqp, xb, sb0 * 8, item.row0, (int)rank);
 					} else {
 						ptx::mbar_arrive_expect_tx(xb, box_bytes);
-						ptx::tma_load_3d(xq_hi, tqp, xb, 0, item.row0, 0);
+						ptx::tma_load_3d(xq_hi, tqp, xb, sb0 * 8, item.row0, 0);
 					}
 					return true;
 				};
@@ -910,7 +923,7 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 							const uint32_t fb = ptx::smem_u32(&sh->bfull[bs]);
 							if (rank == 0)
 								ptx::mbar_arrive_expect_tx(fb, box_bytes);
-							ptx::tma_load_3d_pair(b_hi(bs), tmp, fb, (sbi * TC_SPB + q4) * TC_BK, item.row0, (int)rank);
+							ptx::tma_load_3d_pair(b_hi(bs), tmp, fb, ((sb0 + sbi) * TC_SPB + q4) * TC_BK, item.row0, (int)rank);
 						}
 						TCT_ADD(1, ti);
 						bgl++;
@@ -936,7 +949,7 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 					} else {
 						// one box: 64 k x n_box rows x (hi, lo); a thread can issue a TMA only every ~100 cycles
 						ptx::mbar_arrive_expect_tx(fb, box_bytes);
-						ptx::tma_load_3d(b_hi(s), tmp, fb, ki * TC_BK, item.row0, 0);
+						ptx::tma_load_3d(b_hi(s), tmp, fb, (sb0 * TC_SPB + ki) * TC_BK, item.row0, 0);
 					}
 					TCT_ADD(1, ti);
 					it++;
@@ -967,10 +980,10 @@ grouped_gemm_sb(const __grid_constant__ CUtensorMap tm16, const __grid_constant_
 				if (lane == 0) {
 					ptx::mbar_arrive_expect_tx(bar, Sm::WBUF);
 					if (Q4)	 // box = (one block, 128 rows)
-						ptx::tma_load_2d(w_buf(wb), item.mat_sel ? &tw1 : &tw0, bar, sbi * Q4K_BYTES,
+						ptx::tma_load_2d(w_buf(wb), item.mat_sel ? &tw1 : &tw0, bar, (sb0 + sbi) * Q4K_BYTES,
 								 item.le * rows_per_matrix + item.m0);
 					else  // box = (one record, 8 rows of a group, 16 groups)
-						ptx::tma_load_3d(w_buf(wb), item.mat_sel ? &tw1 : &tw0, bar, sbi * TC_Q6_ROW, 0,
+						ptx::tma_load_3d(w_buf(wb), item.mat_sel ? &tw1 : &tw0, bar, (sb0 + sbi) * TC_Q6_ROW, 0,
 								 (item.le * rows_per_matrix + item.m0) >> 3);
 				}
 				wc++;
@@ -1163,7 +1176,8 @@ int tc_setup(tie_cuda_ctx *c)
 // arr: 0 = the split inputs x (gate/up), 1 = the split activations h (down).
 template <WKind KIND, bool RAW, bool PEER = false>
 static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1, int arr, float *y, float out_scale,
-		       bool sorted_out = false, const EpDst *dst = nullptr, int n_experts = -1)
+		       bool sorted_out = false, const EpDst *dst = nullptr, int n_experts = -1, const DenseView *view = nullptr,
+		       int sb0 = 0, int n_sb = 0, int accumulate = 0)
 {
 	Scratch &s = c->s;
 	if (n_experts <= 0)
@@ -1175,9 +1189,13 @@ static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1
 	const int *perm = sorted_out ? nullptr : s.perm;
 	const int out_stride = RAW ? 2 * t0.rows : t0.rows;
 	const EpDst d = dst ? *dst : EpDst();
+	const int nb_total = t0.k / QK_K;
+	const int k_dim = (n_sb > 0 ? n_sb : nb_total) * QK_K;
+	// a dense tensor brings the maps of its own view of the operand scratch (entries 0-2 operand, 3-5 sums)
+	const CUtensorMap *mh = view ? view->half : c->tmap_half + arr * 3, *mhq = view ? view->half + 3 : c->tmap_half + (2 + arr) * 3;
+	const CUtensorMap *mf = view ? view->full : c->tmap + arr * 3, *mfq = view ? view->full + 3 : c->tmap + (2 + arr) * 3;
 	// pairs of CTAs (one MMA issue for two 128-row tiles) where the 128-row tiles pair up
 	if (c->tc_pairs > 0 && !c->tc_no_pair && m_tiles % 2 == 0) {
-		const CUtensorMap *tm = c->tmap_half;
 		cudaLaunchConfig_t cfg = {};
 		cfg.gridDim = dim3(2 * c->tc_pairs);
 		cfg.blockDim = dim3(TC_THREADS);
@@ -1190,17 +1208,16 @@ static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1
 		attr[0].val.clusterDim.z = 1;
 		cfg.attrs = attr;
 		cfg.numAttrs = 1;
-		TIE_CUDA_TRY(c, cudaLaunchKernelEx(&cfg, grouped_gemm_sb<KIND, RAW, PEER, true>, tm[arr * 3], tm[arr * 3 + 1], tm[arr * 3 + 2],
-						   tm[(2 + arr) * 3], tm[(2 + arr) * 3 + 1], tm[(2 + arr) * 3 + 2], w0m, w1m, (const uint8_t *)t0.ptr, w1p,
-						   t0.expert_stride, t0.k, (const int4 *)s.tile_info, (const int *)s.tile_start, n_experts, m_tiles, y, perm,
-						   out_stride, out_scale, s.status, t0.rows, d));
+		TIE_CUDA_TRY(c, cudaLaunchKernelEx(&cfg, grouped_gemm_sb<KIND, RAW, PEER, true>, mh[0], mh[1], mh[2], mhq[0], mhq[1], mhq[2], w0m, w1m,
+						   (const uint8_t *)t0.ptr, w1p, t0.expert_stride, k_dim, (const int4 *)s.tile_info,
+						   (const int *)s.tile_start, n_experts, m_tiles, y, perm, out_stride, out_scale, s.status, t0.rows, d,
+						   sb0, nb_total, accumulate));
 		c->launches++;
 		return TIE_CUDA_OK;
 	}
 	grouped_gemm_sb<KIND, RAW, PEER><<<c->sm_count, TC_THREADS, TcSmem<KIND>::SMEM, c->stream>>>(
-		c->tmap[arr * 3], c->tmap[arr * 3 + 1], c->tmap[arr * 3 + 2], c->tmap[(2 + arr) * 3], c->tmap[(2 + arr) * 3 + 1],
-		c->tmap[(2 + arr) * 3 + 2], w0m, w1m, t0.ptr, w1p, t0.expert_stride, t0.k, s.tile_info, s.tile_start, n_experts, m_tiles, y, perm,
-		out_stride, out_scale, s.status, t0.rows, d);
+		mf[0], mf[1], mf[2], mfq[0], mfq[1], mfq[2], w0m, w1m, t0.ptr, w1p, t0.expert_stride, k_dim, s.tile_info, s.tile_start, n_experts,
+		m_tiles, y, perm, out_stride, out_scale, s.status, t0.rows, d, sb0, nb_total, accumulate);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
@@ -1244,27 +1261,60 @@ int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, float *y, bool s
 	return launch_tc_t<W_Q6K_R8, false>(c, L.down, nullptr, 1, y, 1.0f / TC_H_SCALE, sorted_out);
 }
 
-// A dense tensor (one "expert") on the grouped product: y[p][row] = sum_k w[row][k] x[p][k] for
-// the rows staged in the split arrays of `arr` (0: x arrays, k = hidden; 1: h arrays, k = ffn_dim);
-// the tile table must describe one expert holding all rows.
-bool tc_dense_supported(const tie_cuda_ctx *c, const DevTensor &t, int *arr)
+// A dense tensor (one "expert") on the grouped product: y[p][row] = sum_k w[row][k] x[p][k].  The
+// split operand of the batch lives in the context's x arrays, VIEWED with the tensor's own row
+// length k (any multiple of 256): hi rows at the array's start, lo rows rows_view * k behind, the
+// sub-block sums likewise in the sums array; the tensor carries the tensor maps of that view.
+bool tc_dense_supported(const tie_cuda_ctx *c, const DevTensor &t)
 {
-	if (!c->tmaps_ok || !tc_tensor_ok(t))
-		return false;
-	if (t.k == c->cfg.hidden)
-		*arr = 0;
-	else if (t.k == c->cfg.ffn_dim)
-		*arr = 1;
-	else
-		return false;
-	return true;
+	return c->tmaps_ok && t.has_map && t.view && t.rows % TC_BM == 0 && t.k % QK_K == 0;
 }
 
-int launch_tc_dense(tie_cuda_ctx *c, const DevTensor &t, int arr, float *y)
+int tc_make_dense_view(tie_cuda_ctx *c, DevTensor &t)
 {
-	if (t.kind == W_Q4K)
-		return launch_tc_t<W_Q4K, false>(c, t, nullptr, arr, y, 1.0f, true, nullptr, 1);
-	return launch_tc_t<W_Q6K_R8, false>(c, t, nullptr, arr, y, 1.0f, true, nullptr, 1);
+	Scratch &s = c->s;
+	const size_t H = c->cfg.hidden, K = t.k, XH = xq_cols((int)H), XK = xq_cols((int)K);
+	DenseView *v = new (std::nothrow) DenseView();
+	if (!v)
+		return TIE_CUDA_ENOMEM;
+	const size_t rows_x = s.rows_pad * H / K, rows_q = s.rows_pad * XH / XK;
+	v->rows = rows_x < rows_q ? rows_x : rows_q;
+	v->lo_off = v->rows * K;
+	v->q_lo_off = v->rows * XK;
+	for (int b = 0; b < 3 && v->rows >= 64; b++) {
+		int rc = make_tmap(c, &v->full[b], s.xs_hi, v->rows, K, 16u << b);
+		if (!rc)
+			rc = make_tmap(c, &v->half[b], s.xs_hi, v->rows, K, 16u << b, 1);
+		if (!rc)
+			rc = make_tmap(c, &v->full[3 + b], s.xq_hi, v->rows, XK, 16u << b);
+		if (!rc)
+			rc = make_tmap(c, &v->half[3 + b], s.xq_hi, v->rows, XK, 16u << b, 1);
+		if (rc) {
+			delete v;
+			return rc;
+		}
+	}
+	if (v->rows < 64) {  // the scratch of this context cannot hold a single tile of such rows
+		delete v;
+		return TIE_CUDA_OK;
+	}
+	t.view = v;
+	return TIE_CUDA_OK;
+}
+
+int launch_tc_dense(tie_cuda_ctx *c, const DevTensor &t, float *y)
+{
+	const int nb = t.k / QK_K;
+	// Q4_K: at most 8 super-blocks (64 sub-block sums) per launch; later launches add to y
+	const int step = t.kind == W_Q4K ? 8 : nb;
+	for (int sb0 = 0; sb0 < nb; sb0 += step) {
+		const int n_sb = nb - sb0 < step ? nb - sb0 : step;
+		int rc = t.kind == W_Q4K ? launch_tc_t<W_Q4K, false>(c, t, nullptr, 0, y, 1.0f, true, nullptr, 1, t.view, sb0, n_sb, sb0 > 0)
+					 : launch_tc_t<W_Q6K_R8, false>(c, t, nullptr, 0, y, 1.0f, true, nullptr, 1, t.view, sb0, n_sb, sb0 > 0);
+		if (rc)
+			return rc;
+	}
+	return TIE_CUDA_OK;
 }
 
 // The down product of an expert-parallel step: row p goes to the rank and row dst->row[p] names.
