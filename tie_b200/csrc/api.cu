@@ -57,6 +57,8 @@ int alloc_scratch(tie_cuda_ctx *c)
 	TRY(dev_alloc(c, &s.active, E));
 	TRY(dev_alloc(c, &s.n_active, 1));
 	TRY(dev_alloc(c, &s.perm, R));
+	s.sort_hist_cap = ((R + SORT_SLICE - 1) / SORT_SLICE + 1) * E;
+	TRY(dev_alloc(c, &s.sort_hist, s.sort_hist_cap));
 	TRY(dev_alloc(c, &s.h, R * F));
 	TRY(dev_alloc(c, &s.y, R * (H > 2 * F ? H : 2 * F)));  // also holds the raw gate|up products of the tensor path
 	// hi and lo halves of each split array share one allocation (lo right behind hi): one 3-D TMA box fetches both
@@ -668,7 +670,7 @@ void tie_cuda_destroy(tie_cuda_ctx *c)
 	void *dev_ptrs[] = {s.x,     s.out,   s.logits, s.bias,  s.topk_idx, s.topk_w, s.counts, s.offsets, s.tile_start, s.active, s.n_active,
 			    s.perm,  s.h,     s.y,	s.xs_hi, s.hs_hi,  s.status,  s.counter, s.row_expert, c->silu,  c->row_x,
 			    c->row_o, s.ep_counts, s.ep_offsets, s.ep_tile_start, s.ep_active, s.ep_n_active, s.ep_perm, s.ep_inv,
-			    s.tile_info, s.xq_hi, s.hq_hi, s.dec_sync, c->df_table};
+			    s.tile_info, s.xq_hi, s.hq_hi, s.dec_sync, c->df_table, s.sort_hist};
 	for (void *p : dev_ptrs)
 		if (p)
 			cudaFree(p);

@@ -19,6 +19,7 @@ constexpr int Q6K_BYTES = 210;	  // sizeof(block_q6_k), gguf.h:101-106
 constexpr int MAX_TOP_K = 8;
 constexpr int TC_TOKEN_TILE = 64;  // rows of one expert per token tile of the tensor-core path
 constexpr int SILU_N = TIE_CUDA_SILU_TABLE_SIZE;
+constexpr int SORT_SLICE = 256;   // rows per CTA of the dispatch sort
 
 // Device status word bits (set by kernels instead of trapping).
 constexpr unsigned ST_BAD_EXPERT = 1u;	  // expert id outside this context's range
@@ -83,6 +84,8 @@ struct Scratch {
 	int *active = nullptr;	    // [E]  compact list of experts with rows
 	int *n_active = nullptr;    // [1]
 	int *perm = nullptr;	    // [R]  sorted position -> row id
+	int *sort_hist = nullptr;   // [slices][experts] rows per (slice of SORT_SLICE rows, expert)
+	size_t sort_hist_cap = 0;
 	float *h = nullptr;	    // [R][F]  fp32 activations (stream path), sorted order
 	float *y = nullptr;	    // [R][H]  per-row expert outputs, row-id order
 	__half *xs_hi = nullptr, *xs_lo = nullptr;  // [Rpad][H]  split inputs, sorted order

@@ -120,7 +120,7 @@ __device__ __forceinline__ int ep_block_scan(int val, int *wsum, int *total = nu
 }
 
 // One CTA; thread i stands for expert i (n_expert <= EP_INDEX_THREADS).  Outputs (this rank's
-// scratch): counts/offsets/tile_start/tile_info/active/n_active exactly as sort_place leaves
+// scratch): counts/offsets/tile_start/tile_info/active/n_active exactly as sort_scatter leaves
 // them for the grouped product, n_rows, the segment table seg_base[E+1] / seg_src[E] (segment
 // i = le*G + s: first sorted row, first entry in s's ids).
 __global__ void __launch_bounds__(EP_INDEX_THREADS)

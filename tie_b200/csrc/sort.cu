@@ -5,150 +5,166 @@
 // out to 8 pool threads (model_qwen3.c:415-456).  Here all (token, slot) rows are grouped by
 // expert so that each expert's weights are streamed once per call.
 //
-// Pass 1 (grid = experts): each CTA counts the rows of its expert (ballot + popc, plain sums).
-// Pass 2 (grid = experts): each CTA turns the counts into its exclusive offset (a warp scan over
-// all experts — every CTA repeats it, it is 128 values), then walks the rows in order and writes
-// its rows' ids at offset + rank, rank from a block-wide ballot prefix.  Rows of one expert keep
-// their original order (stable), so the result does not depend on scheduling.
+// The rows are cut into slices of SORT_SLICE rows, one CTA per slice, one row per thread; a warp
+// finds the rows of equal expert among its 32 (match_any) and every row is read twice:
+// Pass 1 (sort_hist): each CTA counts its slice's rows per expert (per-warp counters written by
+//   one lane per expert, then plain sums) into hist[slice][expert].
+// Pass 2 (sort_scatter): each CTA adds up the histograms — the rows of an expert in all slices
+//   (its count), in the slices before its own (where its rows start inside the expert's range) —
+//   scans the counts over the experts into offsets, and writes each row's id at offset + rows of
+//   that expert in earlier slices, earlier warps and earlier lanes.  Rows of one expert keep their
+//   original order (stable), so the result does not depend on scheduling.  The first CTA also
+//   writes the tables the grouped products read (counts, offsets, token tiles).
+// The depth of both passes does not grow with the row count (the previous form, one CTA per
+// expert scanning all rows, grew with rows x experts per CTA).
 #include "common.cuh"
 #include "kernels.cuh"
 
 namespace tie {
 
 constexpr int SORT_THREADS = 256;
-constexpr int SORT_RPT = 8;  // rows per thread and chunk in sort_place
+constexpr int SORT_WARPS = SORT_THREADS / 32;
+static_assert(SORT_SLICE == SORT_THREADS, "one row per thread: a warp owns 32 consecutive rows of the slice");
+constexpr int SORT_MAX_E = 256;
 
-__global__ void __launch_bounds__(SORT_THREADS) sort_count(const int *__restrict__ row_expert, int n_rows, int first_expert,
-							   int n_local, int *__restrict__ counts, unsigned *__restrict__ status)
+// The thread's row of the slice: its expert in local numbering, or -1 (no row / id out of range),
+// the lanes of its warp that hold a row of the same expert (in row order: lane order), and, into
+// cnt[warp][expert], how many rows of each expert the warp holds (written by one lane per expert:
+// the counters of a warp are its own, nothing is added atomically).
+__device__ __forceinline__ int sort_my_row(const int *__restrict__ row_expert, int n_rows, int first_expert, int n_local,
+					   int (*cnt)[SORT_MAX_E], unsigned &same, unsigned *status)
 {
-	__shared__ int wsum[SORT_THREADS / 32];
-	const int e = first_expert + blockIdx.x;
-	int cnt = 0;
-	bool bad = false;
-	for (int r = threadIdx.x; r < n_rows; r += SORT_THREADS) {
-		int re = row_expert[r];
-		cnt += (re == e);
-		if (blockIdx.x == 0 && (re < first_expert || re >= first_expert + n_local))
-			bad = true;
+	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+	for (int i = threadIdx.x; i < SORT_WARPS * SORT_MAX_E; i += SORT_THREADS)
+		(&cnt[0][0])[i] = 0;
+	const int r = blockIdx.x * SORT_SLICE + threadIdx.x;
+	int le = -1;
+	if (r < n_rows) {
+		le = row_expert[r] - first_expert;
+		if (le < 0 || le >= n_local) {
+			le = -1;
+			if (status)
+				atomicOr(status, ST_BAD_EXPERT);
+		}
 	}
-	if (bad)
-		atomicOr(status, ST_BAD_EXPERT);
-#pragma unroll
-	for (int o = 16; o > 0; o >>= 1)
-		cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
-	if ((threadIdx.x & 31) == 0)
-		wsum[threadIdx.x >> 5] = cnt;
 	__syncthreads();
-	if (threadIdx.x == 0) {
+	same = __match_any_sync(0xffffffffu, le);
+	if (le >= 0 && (same & ((1u << lane) - 1u)) == 0)  // the first lane of its group
+		cnt[warp][le] = __popc(same);
+	__syncthreads();
+	return le;
+}
+
+__global__ void __launch_bounds__(SORT_THREADS) sort_hist(const int *__restrict__ row_expert, int n_rows, int first_expert,
+							  int n_local, int *__restrict__ hist, unsigned *__restrict__ status)
+{
+	__shared__ int cnt[SORT_WARPS][SORT_MAX_E];
+	unsigned same;
+	sort_my_row(row_expert, n_rows, first_expert, n_local, cnt, same, status);
+	const int e = threadIdx.x;
+	if (e < n_local) {
 		int t = 0;
-		for (int i = 0; i < SORT_THREADS / 32; i++)
-			t += wsum[i];
-		counts[blockIdx.x] = t;
+#pragma unroll
+		for (int w = 0; w < SORT_WARPS; w++)
+			t += cnt[w][e];
+		hist[(size_t)blockIdx.x * n_local + e] = t;
 	}
 }
 
-__global__ void __launch_bounds__(SORT_THREADS) sort_place(const int *__restrict__ row_expert, int n_rows, int first_expert,
-							   int n_local, const int *__restrict__ counts, int n_tile,
-							   int *__restrict__ offsets, int *__restrict__ tile_start,
-							   int *__restrict__ active, int *__restrict__ n_active,
-							   int *__restrict__ perm, int4 *__restrict__ tile_info)
+__global__ void __launch_bounds__(SORT_THREADS) sort_scatter(const int *__restrict__ row_expert, int n_rows, int first_expert,
+							     int n_local, const int *__restrict__ hist, int n_tile,
+							     int *__restrict__ counts, int *__restrict__ offsets, int *__restrict__ tile_start,
+							     int *__restrict__ active, int *__restrict__ n_active, int *__restrict__ perm,
+							     int4 *__restrict__ tile_info)
 {
-	__shared__ int s_off, s_tiles;
-	__shared__ int wcnt[SORT_THREADS / 32];
-	const int le = blockIdx.x;
-	const int e = first_expert + le;
-	// exclusive prefix over experts < le, by warp 0 (n_local <= 256: 8 per lane)
-	if (threadIdx.x < 32) {
-		int off = 0, tiles = 0, act = 0, tot = 0, ttiles = 0, tact = 0;
-		for (int i = threadIdx.x; i < n_local; i += 32) {
-			int cnt = counts[i];
-			int tl = (cnt + n_tile - 1) / n_tile;
-			if (i < le) {
-				off += cnt;
-				tiles += tl;
-				act += (cnt > 0);
-			}
-			tot += cnt;
-			ttiles += tl;
-			tact += (cnt > 0);
+	__shared__ int cnt[SORT_WARPS][SORT_MAX_E];  // rows of expert e in warp w's 32 rows; then: where they start
+	__shared__ int wsum[3][SORT_WARPS];
+	unsigned same;
+	const int le = sort_my_row(row_expert, n_rows, first_expert, n_local, cnt, same, nullptr);
+	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+	const int e = threadIdx.x;  // thread e stands for expert e
+	int total = 0, before = 0;
+	if (e < n_local) {
+		for (int b = 0; b < (int)gridDim.x; b++) {
+			const int h = hist[(size_t)b * n_local + e];
+			total += h;
+			before += b < (int)blockIdx.x ? h : 0;
 		}
+	}
+	// exclusive scans over the experts: rows, token tiles, experts with rows
+	const int tl = (total + n_tile - 1) / n_tile, act = total > 0 ? 1 : 0;
+	int v[3] = {total, tl, act}, incl[3];
 #pragma unroll
-		for (int o = 16; o > 0; o >>= 1) {
-			off += __shfl_xor_sync(0xffffffffu, off, o);
-			tiles += __shfl_xor_sync(0xffffffffu, tiles, o);
-			act += __shfl_xor_sync(0xffffffffu, act, o);
-			tot += __shfl_xor_sync(0xffffffffu, tot, o);
-			ttiles += __shfl_xor_sync(0xffffffffu, ttiles, o);
-			tact += __shfl_xor_sync(0xffffffffu, tact, o);
+	for (int k = 0; k < 3; k++) {
+		incl[k] = v[k];
+#pragma unroll
+		for (int o = 1; o < 32; o <<= 1) {
+			const int t = __shfl_up_sync(0xffffffffu, incl[k], o);
+			if (lane >= o)
+				incl[k] += t;
 		}
-		if (threadIdx.x == 0) {
-			s_off = off;
-			s_tiles = tiles;
-			offsets[le] = off;
-			tile_start[le] = tiles;
-			if (counts[le] > 0)
-				active[act] = le;
-			if (le == n_local - 1) {
-				offsets[n_local] = tot;
-				tile_start[n_local] = ttiles;
-				*n_active = tact;
-			}
+		if (lane == 31)
+			wsum[k][warp] = incl[k];
+	}
+	__syncthreads();
+	int excl[3], all[3];
+#pragma unroll
+	for (int k = 0; k < 3; k++) {
+		int bw = 0, a = 0;
+#pragma unroll
+		for (int i = 0; i < SORT_WARPS; i++) {
+			const int w = wsum[k][i];
+			bw += i < warp ? w : 0;
+			a += w;
+		}
+		excl[k] = bw + incl[k] - v[k];
+		all[k] = a;
+	}
+	if (e < n_local) {
+		// first sorted position of warp w's rows of expert e: the expert's range, the slices before this
+		// one, the warps before w
+		int pos = excl[0] + before;
+#pragma unroll
+		for (int w = 0; w < SORT_WARPS; w++) {
+			const int c = cnt[w][e];
+			cnt[w][e] = pos;
+			pos += c;
+		}
+	}
+	if (blockIdx.x == 0) {
+		if (e < n_local) {
+			counts[e] = total;
+			offsets[e] = excl[0];
+			tile_start[e] = excl[1];
+			if (total > 0)
+				active[excl[2]] = e;
+			if (tile_info)
+				for (int j = 0; j * n_tile < total; j++)
+					tile_info[excl[1] + j] = make_int4(e, excl[0] + j * n_tile, min(n_tile, total - j * n_tile), 0);
+		}
+		if (e == 0) {
+			offsets[n_local] = all[0];
+			tile_start[n_local] = all[1];
+			*n_active = all[2];
 		}
 	}
 	__syncthreads();
-	int base = s_off;
-	if (tile_info) {  // the token tiles of this expert
-		const int cnt = counts[le];
-		for (int j = threadIdx.x; j * n_tile < cnt; j += SORT_THREADS)
-			tile_info[s_tiles + j] = make_int4(le, base + j * n_tile, min(n_tile, cnt - j * n_tile), 0);
-	}
-	// each thread takes SORT_RPT consecutive rows of a chunk, so ranks follow the row order:
-	// rank = rows of this expert in earlier chunks + in earlier threads (warp scan + warp totals)
-	// + earlier ones among the thread's own
-	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-	constexpr int CHUNK = SORT_THREADS * SORT_RPT;
-	for (int r0 = 0; r0 < n_rows; r0 += CHUNK) {
-		const int rt = r0 + threadIdx.x * SORT_RPT;
-		unsigned m = 0;
-#pragma unroll
-		for (int i = 0; i < SORT_RPT; i++)
-			if (rt + i < n_rows && row_expert[rt + i] == e)
-				m |= 1u << i;
-		const int cnt = __popc(m);
-		int incl = cnt;
-#pragma unroll
-		for (int o = 1; o < 32; o <<= 1) {
-			const int v = __shfl_up_sync(0xffffffffu, incl, o);
-			if (lane >= o)
-				incl += v;
-		}
-		if (lane == 31)
-			wcnt[warp] = incl;
-		__syncthreads();
-		int before = incl - cnt, total = 0;
-#pragma unroll
-		for (int i = 0; i < SORT_THREADS / 32; i++) {
-			const int cw = wcnt[i];
-			before += (i < warp) ? cw : 0;
-			total += cw;
-		}
-		int pos = base + before;
-#pragma unroll
-		for (int i = 0; i < SORT_RPT; i++)
-			if (m & (1u << i))
-				perm[pos++] = rt + i;
-		base += total;
-		__syncthreads();
-	}
+	if (le >= 0)  // rows of one expert keep their order: slices, warps and lanes are all in row order
+		perm[cnt[warp][le] + __popc(same & ((1u << lane) - 1u))] = blockIdx.x * SORT_SLICE + threadIdx.x;
 }
 
 int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile, int first_expert, int n_expert,
 		const SortBufs &b)
 {
-	sort_count<<<n_expert, SORT_THREADS, 0, c->stream>>>(row_expert, n_rows, first_expert, n_expert, b.counts, c->s.status);
+	if (n_expert > 256)
+		return TIE_CUDA_ENOTSUP;
+	const int n_slices = n_rows > 0 ? (n_rows + SORT_SLICE - 1) / SORT_SLICE : 1;  // (no rows: one CTA writes the empty tables)
+	if ((size_t)n_slices * n_expert > c->s.sort_hist_cap)
+		return TIE_CUDA_EINVAL;
+	sort_hist<<<n_slices, SORT_THREADS, 0, c->stream>>>(row_expert, n_rows, first_expert, n_expert, c->s.sort_hist, c->s.status);
 	TIE_CUDA_LAUNCHED(c);
-	sort_place<<<n_expert, SORT_THREADS, 0, c->stream>>>(row_expert, n_rows, first_expert, n_expert, b.counts, n_tile,
-							      b.offsets, b.tile_start, b.active, b.n_active, b.perm, b.tile_info);
+	sort_scatter<<<n_slices, SORT_THREADS, 0, c->stream>>>(row_expert, n_rows, first_expert, n_expert, c->s.sort_hist, n_tile, b.counts,
+								b.offsets, b.tile_start, b.active, b.n_active, b.perm, b.tile_info);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }

@@ -1195,7 +1195,10 @@ static int launch_tc_t(tie_cuda_ctx *c, const DevTensor &t0, const DevTensor *t1
 	const CUtensorMap *mh = view ? view->half : c->tmap_half + arr * 3, *mhq = view ? view->half + 3 : c->tmap_half + (2 + arr) * 3;
 	const CUtensorMap *mf = view ? view->full : c->tmap + arr * 3, *mfq = view ? view->full + 3 : c->tmap + (2 + arr) * 3;
 	// pairs of CTAs (one MMA issue for two 128-row tiles) where the 128-row tiles pair up
-	if (c->tc_pairs > 0 && !c->tc_no_pair && m_tiles % 2 == 0) {
+	// (measured at 64, 512 and 4096 tokens: pairs win on rows of 8 super-blocks — gate/up, 15 % faster —
+	// and lose on rows of 3 — down, 7 % slower: with few super-blocks per work item the pair's
+	// hand-offs between two SMs are not amortised)
+	if (c->tc_pairs > 0 && !c->tc_no_pair && m_tiles % 2 == 0 && k_dim >= 4 * QK_K) {
 		cudaLaunchConfig_t cfg = {};
 		cfg.gridDim = dim3(2 * c->tc_pairs);
 		cfg.blockDim = dim3(TC_THREADS);
