@@ -237,7 +237,13 @@ int tie_cuda_moe_block_inplace_ep(tie_cuda_ctx *c, int layer, float *hidden_dev,
  * host tensor registered by tie_cuda_upload_moe_layer / tie_cuda_register_tensor; the device
  * copy is found by host address.  They use the context made current by tie_cuda_make_current
  * (the reference's dispatch signatures carry no context) and return nothing, like the
- * reference's; failures are reported through tie_cuda_dispatch_status(). */
+ * reference's; failures are reported through tie_cuda_dispatch_status().
+ * Threading: unlike the context entry points above, these rows may be called from several host
+ * threads at once — the reference's threaded dispatcher (math_dispatch.c:262-283) gives each pool
+ * worker a disjoint [start_row, end_row) slice of one mat-vec.  A call holds the current
+ * context's row lock from its first use of the staging buffers to the read-back of the status
+ * word, and computes the rows of its slice only.  tie_cuda_make_current itself is not meant to
+ * race with calls in flight. */
 int tie_cuda_make_current(tie_cuda_ctx *c);
 /* Upload a stand-alone weight tensor (rows of in_dim inputs; F32, Q4_K or Q6_K) so that the rows
  * below can find it by host address (model_load_tensor, model.c:198-235, for non-MoE tensors). */
