@@ -639,6 +639,42 @@ def test_dense_mat_mat_on_the_grouped_product(be, port_lib, ggml_type, in_dim, o
     assert np.array_equal(bits(be.moe_ffn(0, xs, path=moe.PATH_TENSOR)), bits(a))
 
 
+def test_two_host_buffer_calls_in_flight(be, port0):
+    """tie_cuda_moe_ffn_submit / _wait: the same result as the synchronous host-buffer call, with two
+    calls in flight on alternating slots (different inputs, different token counts), over several
+    rounds (the later rounds replay the slots' CUDA graphs); a busy slot, pageable memory and a bad
+    slot number are refused."""
+    import torch
+    from tie_b200 import moe
+    xs = [torch.from_numpy(synth.make_x(0, n, first_token=f)).pin_memory() for n, f in ((96, 0), (40, 300))]
+    outs = [torch.empty_like(x).pin_memory() for x in xs]
+    want = [be.moe_ffn(0, x.numpy()) for x in xs]
+    for rnd in range(3):
+        for o in outs:
+            o.fill_(float("nan"))
+        be.moe_ffn_submit(0, xs[0], outs[0], xs[0].shape[0], 0, moe.GRAPH)
+        be.moe_ffn_submit(0, xs[1], outs[1], xs[1].shape[0], 1, moe.GRAPH)
+        with pytest.raises(moe.TieCudaError) as ei:  # slot 0 is still in flight
+            be.moe_ffn_submit(0, xs[0], outs[0], xs[0].shape[0], 0, moe.GRAPH)
+        assert ei.value.code == moe.EINVAL
+        be.moe_ffn_wait(0)
+        be.moe_ffn_wait(1)
+        for o, w in zip(outs, want):
+            assert np.array_equal(bits(o.numpy()), bits(w)), rnd
+    ref, _, _ = port0.moe_ffn(xs[1].numpy())
+    _check_ffn(outs[1].numpy(), ref)
+    with pytest.raises(moe.TieCudaError) as ei:
+        be.moe_ffn_wait(0)  # nothing in flight
+    assert ei.value.code == moe.EINVAL
+    pageable = torch.zeros(4, 2048)
+    with pytest.raises(moe.TieCudaError) as ei:
+        be.moe_ffn_submit(0, pageable, outs[0], 4, 0)
+    assert ei.value.code == moe.ENOTSUP
+    with pytest.raises(moe.TieCudaError) as ei:
+        be.moe_ffn_submit(0, xs[0], outs[0], 96, 2)
+    assert ei.value.code == moe.EINVAL
+
+
 def test_errors_are_codes_not_exits(be):
     from tie_b200 import moe
     x = np.zeros((1, 2048), dtype=np.float32)

@@ -678,6 +678,21 @@ void tie_cuda_destroy(tie_cuda_ctx *c)
 	for (void *p : pin_ptrs)
 		if (p)
 			cudaFreeHost(p);
+	for (auto &sl : c->slots) {
+		if (sl.x)
+			cudaFree(sl.x);
+		if (sl.out)
+			cudaFree(sl.out);
+		if (sl.pin_status)
+			cudaFreeHost(sl.pin_status);
+		for (cudaEvent_t ev : {sl.in, sl.done, sl.outd})
+			if (ev)
+				cudaEventDestroy(ev);
+	}
+	if (c->h2d_stream)
+		cudaStreamDestroy(c->h2d_stream);
+	if (c->d2h_stream)
+		cudaStreamDestroy(c->d2h_stream);
 	for (int i = 0; i < c->n_graphs; i++)
 		cudaGraphExecDestroy(c->graphs[i].exec);
 	c->n_graphs = 0;
@@ -869,6 +884,79 @@ int tie_cuda_moe_ffn_biased(tie_cuda_ctx *c, int layer, const float *x, float *o
 int tie_cuda_moe_ffn(tie_cuda_ctx *c, int layer, const float *x, float *out, int n_tokens, unsigned flags)
 {
 	return tie_cuda_moe_ffn_biased(c, layer, x, out, n_tokens, nullptr, flags);
+}
+
+// ---- two host-buffer calls in flight ----
+// The copies of a call run on streams of their own: the input copy of call k+1 and the result copy
+// of call k-1 overlap the kernels of call k (which stay on the context's stream, one call after
+// the other: they share the scratch).  Slot staging and events are created on first use.
+static int slot_setup(tie_cuda_ctx *c, tie_cuda_ctx::Slot &sl)
+{
+	if (sl.x)
+		return TIE_CUDA_OK;
+	const size_t n = (size_t)c->cfg.max_tokens * c->cfg.hidden;
+	if (!c->h2d_stream) {
+		TIE_CUDA_TRY(c, cudaStreamCreateWithFlags(&c->h2d_stream, cudaStreamNonBlocking));
+		TIE_CUDA_TRY(c, cudaStreamCreateWithFlags(&c->d2h_stream, cudaStreamNonBlocking));
+	}
+	TRY(dev_alloc(c, &sl.x, n));
+	TRY(dev_alloc(c, &sl.out, n));
+	TIE_CUDA_TRY(c, cudaMallocHost(reinterpret_cast<void **>(&sl.pin_status), sizeof(unsigned)));
+	TIE_CUDA_TRY(c, cudaEventCreateWithFlags(&sl.in, cudaEventDisableTiming));
+	TIE_CUDA_TRY(c, cudaEventCreateWithFlags(&sl.done, cudaEventDisableTiming));
+	TIE_CUDA_TRY(c, cudaEventCreateWithFlags(&sl.outd, cudaEventDisableTiming));
+	return TIE_CUDA_OK;
+}
+
+int tie_cuda_moe_ffn_submit(tie_cuda_ctx *c, int layer, const float *x_host, float *out_host, int n_tokens, int slot, unsigned flags)
+{
+	Layer *L;
+	TRY(get_layer(c, layer, &L));
+	if (!x_host || !out_host || n_tokens <= 0 || n_tokens > c->cfg.max_tokens || c->cfg.ep_size != 1 || slot < 0 || slot > 1 ||
+	    (flags & TIE_CUDA_DEVICE) || c->stream == nullptr)
+		return TIE_CUDA_EINVAL;
+	tie_cuda_ctx::Slot &sl = c->slots[slot];
+	if (sl.busy)  // the previous call on this slot has not been waited for
+		return TIE_CUDA_EINVAL;
+	// (pageable memory would make the copies synchronous: the point of the call is lost, so it is refused)
+	if (!is_pinned_host(x_host) || !is_pinned_host(out_host))
+		return TIE_CUDA_ENOTSUP;
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	TRY(slot_setup(c, sl));
+	const size_t bytes = (size_t)n_tokens * c->cfg.hidden * sizeof(float);
+	// input: after the kernels of this slot's previous call have read its x (they precede `done`)
+	if (sl.done)
+		TIE_CUDA_TRY(c, cudaStreamWaitEvent(c->h2d_stream, sl.done, 0));
+	TIE_CUDA_TRY(c, cudaMemcpyAsync(sl.x, x_host, bytes, cudaMemcpyHostToDevice, c->h2d_stream));
+	TIE_CUDA_TRY(c, cudaEventRecord(sl.in, c->h2d_stream));
+	// kernels: after the input has landed and this slot's previous result has left the device
+	TIE_CUDA_TRY(c, cudaStreamWaitEvent(c->stream, sl.in, 0));
+	TIE_CUDA_TRY(c, cudaStreamWaitEvent(c->stream, sl.outd, 0));
+	const unsigned dflags = (flags & ~(TIE_CUDA_HOST | TIE_CUDA_NO_SYNC)) | TIE_CUDA_DEVICE;
+	const unsigned kflags = dflags & (TIE_CUDA_DEVICE | TIE_CUDA_PATH_MASK | TIE_CUDA_PATH_LEGACY_STREAM | TIE_CUDA_ROUTE_LFM2 |
+					  TIE_CUDA_PATH_DECODE_CHAIN | TIE_CUDA_PATH_NO_PAIR);
+	GraphKey k = {1, layer, n_tokens, sl.x, sl.out, nullptr, nullptr, kflags};
+	TRY(run_maybe_graphed(c, flags & TIE_CUDA_GRAPH, k,
+			      [&]() { return moe_ffn_device(c, *L, sl.x, sl.out, n_tokens, nullptr, nullptr, dflags); }));
+	TIE_CUDA_TRY(c, cudaEventRecord(sl.done, c->stream));
+	// result and status word
+	TIE_CUDA_TRY(c, cudaStreamWaitEvent(c->d2h_stream, sl.done, 0));
+	TIE_CUDA_TRY(c, cudaMemcpyAsync(out_host, sl.out, bytes, cudaMemcpyDeviceToHost, c->d2h_stream));
+	TIE_CUDA_TRY(c, cudaMemcpyAsync(sl.pin_status, c->s.status, sizeof(unsigned), cudaMemcpyDeviceToHost, c->d2h_stream));
+	TIE_CUDA_TRY(c, cudaEventRecord(sl.outd, c->d2h_stream));
+	sl.busy = true;
+	return TIE_CUDA_OK;
+}
+
+int tie_cuda_moe_ffn_wait(tie_cuda_ctx *c, int slot)
+{
+	if (!c || slot < 0 || slot > 1 || !c->slots[slot].busy)
+		return TIE_CUDA_EINVAL;
+	tie_cuda_ctx::Slot &sl = c->slots[slot];
+	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
+	TIE_CUDA_TRY(c, cudaEventSynchronize(sl.outd));
+	sl.busy = false;
+	return report_status(c, *static_cast<volatile unsigned *>(sl.pin_status));
 }
 
 int tie_cuda_moe_block_inplace(tie_cuda_ctx *c, int layer, float *hidden_dev, int n_tokens, unsigned flags)

@@ -152,6 +152,15 @@ struct tie_cuda_ctx {
 	int *pin_idx = nullptr;
 	float *pin_w = nullptr, *pin_logits = nullptr;
 	unsigned *pin_status = nullptr;
+	// host-buffer calls in flight (tie_cuda_moe_ffn_submit / _wait): per slot a device copy of x and of
+	// the result, a pinned status word and the events that order the copy streams with the compute stream
+	struct Slot {
+		float *x = nullptr, *out = nullptr;
+		unsigned *pin_status = nullptr;
+		cudaEvent_t in = nullptr, done = nullptr, outd = nullptr;
+		bool busy = false;
+	} slots[2];
+	cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
 	size_t weight_bytes = 0;
 	uint64_t launches = 0;
 	int last_direct_rows = -1;

@@ -27,7 +27,7 @@ OK, EINVAL, ENOTSUP, ENOMEM, ECUDA, ENODEV, EKERNEL, ETOOBIG = 0, -1, -2, -3, -4
 EXPORTS = [
     "tie_cuda_init", "tie_cuda_destroy", "tie_cuda_strerror", "tie_cuda_last_cuda_error", "tie_cuda_set_stream",
     "tie_cuda_synchronize", "tie_cuda_silu_table_default", "tie_cuda_upload_moe_layer", "tie_cuda_weight_bytes",
-    "tie_cuda_moe_ffn", "tie_cuda_moe_block_inplace", "tie_cuda_moe_stack_inplace", "tie_cuda_moe_route", "tie_cuda_moe_ffn_biased",
+    "tie_cuda_moe_ffn", "tie_cuda_moe_ffn_submit", "tie_cuda_moe_ffn_wait", "tie_cuda_moe_block_inplace", "tie_cuda_moe_stack_inplace", "tie_cuda_moe_route", "tie_cuda_moe_ffn_biased",
     "tie_cuda_moe_expert_rows", "tie_cuda_moe_combine", "tie_cuda_make_current", "tie_cuda_register_tensor",
     "tie_cuda_mat_vec_row_f32_q4k_f32", "tie_cuda_mat_vec_row_f32_q6k_f32", "tie_cuda_mat_vec_row_f32_f32_f32",
     "tie_cuda_swiglu_f32_f32", "tie_cuda_dispatch_status", "tie_cuda_launch_count", "tie_cuda_last_active_experts",
@@ -95,6 +95,10 @@ def load_library() -> ctypes.CDLL:
     L.tie_cuda_moe_ffn_biased.argtypes = [vp, i32, vp, vp, i32, vp, u32]
     L.tie_cuda_moe_block_inplace.restype = i32
     L.tie_cuda_moe_block_inplace.argtypes = [vp, i32, vp, i32, u32]
+    L.tie_cuda_moe_ffn_submit.restype = i32
+    L.tie_cuda_moe_ffn_submit.argtypes = [vp, i32, vp, vp, i32, i32, u32]
+    L.tie_cuda_moe_ffn_wait.restype = i32
+    L.tie_cuda_moe_ffn_wait.argtypes = [vp, i32]
     L.tie_cuda_moe_stack_inplace.restype = i32
     L.tie_cuda_moe_stack_inplace.argtypes = [vp, i32, i32, vp, i32, u32]
     L.tie_cuda_moe_route.restype = i32
@@ -292,6 +296,15 @@ class MoeBackend:
     def moe_block_inplace_ptr(self, layer_idx: int, hidden, n_tokens: int, flags: int = DEVICE):
         rc = self.L.tie_cuda_moe_block_inplace(self.h, layer_idx, _ptr(hidden), n_tokens, flags)
         self._check(rc, "tie_cuda_moe_block_inplace")
+
+    def moe_ffn_submit(self, layer_idx: int, x_host, out_host, n_tokens: int, slot: int, flags: int = 0):
+        """x_host / out_host: pinned host tensors or arrays; returns at once (see tie_cuda_moe_ffn_submit)."""
+        rc = self.L.tie_cuda_moe_ffn_submit(self.h, layer_idx, _ptr(x_host), _ptr(out_host), n_tokens, slot, flags)
+        self._check(rc, "tie_cuda_moe_ffn_submit")
+
+    def moe_ffn_wait(self, slot: int):
+        rc = self.L.tie_cuda_moe_ffn_wait(self.h, slot)
+        self._check(rc, "tie_cuda_moe_ffn_wait")
 
     def moe_stack_inplace_ptr(self, first_layer: int, n_layers: int, hidden, n_tokens: int, flags: int = DEVICE):
         rc = self.L.tie_cuda_moe_stack_inplace(self.h, first_layer, n_layers, _ptr(hidden), n_tokens, flags)
