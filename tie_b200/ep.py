@@ -303,8 +303,56 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler, co
 
     for _ in range(args.warmup):
         step_e2e()
-    e2e_s = timed(step_e2e, args.steps) * 1e-3
+    e2e_sync_s = timed(step_e2e, args.steps) * 1e-3
     be.synchronize()
+    e2e_s, e2e_how = e2e_sync_s, "one step at a time: copy in, step, copy out in series"
+    if exchange == "peer":
+        # two steps in flight on alternating device and host buffers: every step still copies its tokens in
+        # and its result out inside the timed region, and the host waits for each step's result; the copies
+        # run on streams of their own and overlap the neighbouring steps' kernels
+        cs = torch.cuda.current_stream()
+        hs, ds = torch.cuda.Stream(), torch.cuda.Stream()
+        xb = [torch.empty(T, shape.hidden, device="cuda") for _ in range(2)]
+        ob = [torch.empty_like(b) for b in xb]
+        xh = [x_host, x_host.clone().pin_memory()]
+        oh = [out_host, torch.empty_like(out_host).pin_memory()]
+        ev_in, ev_done, ev_out = ([torch.cuda.Event() for _ in range(2)] for _ in range(3))
+
+        def pipelined(n=1):
+            for i in range(n):
+                k = i & 1
+                with torch.cuda.stream(hs):
+                    hs.wait_event(ev_done[k])
+                    xb[k].copy_(xh[k], non_blocking=True)
+                    ev_in[k].record(hs)
+                cs.wait_event(ev_in[k])
+                cs.wait_event(ev_out[k])
+                blk.forward(xb[k], ob[k])
+                ev_done[k].record(cs)
+                with torch.cuda.stream(ds):
+                    ds.wait_event(ev_done[k])
+                    oh[k].copy_(ob[k], non_blocking=True)
+                    ev_out[k].record(ds)
+                if i:
+                    ev_out[(i - 1) & 1].synchronize()  # the previous step's result is in host memory
+            ev_out[(n - 1) & 1].synchronize()
+            cs.wait_event(ev_out[0])
+            cs.wait_event(ev_out[1])
+
+        pipelined(max(args.warmup, 4))
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        pipelined(args.steps)
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item()) / args.steps * 1e-3
+        e2e_how = "two steps in flight on alternating buffers (copies on streams of their own, host waits for every step's result)"
+        assert torch.equal(oh[0], oh[1]) and bool(torch.isfinite(oh[1]).all())
+        be.synchronize()
 
     # per-phase device times of rank 0 (CUDA events inside the library; the steps run without a graph,
     # and every rank starts them together, so waits for peers show up in the phase that waits)
@@ -463,7 +511,8 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler, co
                 else "NCCL all-to-all (torch.distributed) for dispatch and combine"},
             "clocks": clocks,
             "e2e": {"value": T * world / e2e_s, "unit": unit, "h2d_bytes_per_step": T * shape.hidden * 4 * world,
-                    "d2h_bytes_per_step": T * shape.hidden * 4 * world, "ms_per_step": e2e_s * 1e3},
+                    "d2h_bytes_per_step": T * shape.hidden * 4 * world, "ms_per_step": e2e_s * 1e3, "how": e2e_how,
+                    "synchronous_call": {"value": T * world / e2e_sync_s, "ms_per_step": e2e_sync_s * 1e3}},
             "gpu_launches": int(launches),
             # the whole step of one rank against the slower of its three floors: rows over NVLink (one
             # direction: rows in and rows out travel opposite ways), its share of the packed weights and
