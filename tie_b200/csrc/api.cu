@@ -490,6 +490,10 @@ int ep_region(tie_cuda_ctx *c)
 	off = align_up(off + (size_t)v.t_max * v.hidden * sizeof(float), 256);
 	v.off_ids = off;
 	off = align_up(off + (size_t)v.t_max * v.top_k * sizeof(int), 256);
+	v.off_topk = off;
+	off = align_up(off + (size_t)v.t_max * v.top_k * sizeof(int), 256);
+	v.off_inv = off;
+	off = align_up(off + (size_t)v.t_max * v.top_k * sizeof(int), 256);
 	v.off_counts = off;
 	off = align_up(off + (size_t)v.n_expert * sizeof(int), 256);
 	v.off_pub = off;
@@ -1279,8 +1283,11 @@ int tie_cuda_ep_publish(tie_cuda_ctx *c, int layer, const float *x, int n_tokens
 	const int R = n_tokens * c->cfg.top_k;
 	ep.replicated = false;
 	prof_mark(c, 0);
+	// the selected experts go where the peers can read them: the owner of a token's first row on a GPU
+	// looks up the token's other rows there
+	int *topk_pub = reinterpret_cast<int *>(ep.region + v.off_topk);
 	if (n_tokens)
-		TRY(launch_router(c, x, L->router_w, router_bias, n_tokens, s.logits, s.topk_idx, s.topk_w,
+		TRY(launch_router(c, x, L->router_w, router_bias, n_tokens, s.logits, topk_pub, s.topk_w,
 				  (flags & TIE_CUDA_ROUTE_LFM2) ? 1 : 0));
 	prof_mark(c, 1);
 	SortBufs b = {reinterpret_cast<int *>(ep.region + v.off_counts),
@@ -1290,7 +1297,10 @@ int tie_cuda_ep_publish(tie_cuda_ctx *c, int layer, const float *x, int n_tokens
 		      s.ep_n_active,
 		      reinterpret_cast<int *>(ep.region + v.off_ids),
 		      nullptr};
-	TRY(launch_sort(c, s.topk_idx, R, 128, 0, c->cfg.n_expert, b));
+	b.inv = reinterpret_cast<int *>(ep.region + v.off_inv);
+	b.owner_div = c->n_local;
+	b.top_k = c->cfg.top_k;
+	TRY(launch_sort(c, topk_pub, R, 128, 0, c->cfg.n_expert, b));
 	float *xs = reinterpret_cast<float *>(ep.region + v.off_xs);
 	if (n_tokens && x != xs)
 		TIE_CUDA_TRY(c, cudaMemcpyAsync(xs, x, (size_t)n_tokens * v.hidden * sizeof(float), cudaMemcpyDeviceToDevice, c->stream));

@@ -106,9 +106,13 @@ struct Scratch {
 
 // Expert parallelism over peer memory (ep.cu).  EpView is what the kernels get by value.
 constexpr int EP_MAX_RANKS = 16;
+// Bit of an entry of a rank's published row-id list: the row is the first of its token's rows (in
+// slot order) that goes to the GPU that owns its expert — that GPU fetches the token once, for
+// this row, and fills the token's other rows there from the same fetch.
+constexpr int EP_FIRST_OF_TOKEN = 1 << 30;
 struct EpView {
 	uint8_t *peer[EP_MAX_RANKS];  // region base of every rank, as mapped into this process
-	size_t off_xs, off_ids, off_counts, off_pub, off_done, off_y;
+	size_t off_xs, off_ids, off_topk, off_inv, off_counts, off_pub, off_done, off_y;
 	long long rows_cap;  // rows of this context's scratch (the worst case of one step)
 	int n_ranks, rank, n_local, n_expert, top_k, hidden, t_max;
 };

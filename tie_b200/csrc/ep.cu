@@ -5,7 +5,10 @@
 // [r*E/G, (r+1)*E/G).  Every rank exposes one "region" of its HBM to its peers (CUDA IPC):
 //
 //   xs     fp32 [t_max][H]      this rank's tokens of the current step
-//   ids    int  [t_max*K]       its (token, slot) row ids grouped by GLOBAL expert (stable sort)
+//   ids    int  [t_max*K]       its (token, slot) row ids grouped by GLOBAL expert (stable sort);
+//                               EP_FIRST_OF_TOKEN marks a token's first row for the owner's GPU
+//   topk   int  [t_max*K]       the selected experts of its tokens, in slot order
+//   inv    int  [t_max*K]       where each (token, slot) row stands in ids
 //   counts int  [E]             rows per expert from this rank
 //   pub    u32  [G]             pub[s]  = step number, written BY rank s once xs/ids/counts are final
 //   done   u32  [G]             done[d] = step number, written BY rank d once it has delivered its outputs
@@ -19,8 +22,9 @@
 //            and derives the whole row layout from them alone: the rows of local expert le from
 //            source s sit at offsets[le] + sum_{s'<s} cnt[s'][le] + j — the receiver needs no
 //            sort.  ep_split_rows then gathers the token rows straight out of the peers' xs
-//            (plain loads over NVLink) into the fp16 hi/lo operand of the grouped product and
-//            notes where each row came from; the down product's epilogue stores every output
+//            (plain loads over NVLink; a token crosses once per GPU, not once per selected
+//            expert) into the fp16 hi/lo operand of the grouped product and notes where each
+//            row came from; the down product's epilogue stores every output
 //            row into ITS SOURCE's y (plain stores over NVLink, overlapped with the product);
 //            done[r] is then stored to every peer
 //   gather   ep_combine_rows waits (bounded) for the done flags of all owners and sums each
@@ -229,12 +233,15 @@ ep_index(EpView v, const unsigned *__restrict__ step_dev, long long budget, int 
 constexpr int EP_SPLIT_THREADS = 256;
 constexpr int EP_SPLIT_F4 = 8;	// float4 loads a lane keeps in flight
 
-// Sorted row p of this rank = row j of segment (le, s): token ids[seg_src + j] / top_k of rank s.
-// Reads that token's fp32 row from rank s and writes the fp16 hi/lo operand row p (same
-// arithmetic and element order as split_rows); row_dst[p] = (s << 24) | row id tells the down
-// product where the row's output goes.  One warp per row, EP_SPLIT_F4 16-byte loads in
-// flight per lane (the rows come over NVLink: latency is hidden by loads in flight, not by
-// occupancy); the warps stride over the rows, n_rows is on the device.
+// Sorted row p of this rank = row j of segment (le, s): entry ids[seg_src + j] of rank s, token
+// id / top_k.  row_dst[p] = (s << 24) | row id tells the down product where the row's output goes.
+// A token whose selected experts include several of this rank's is fetched ONCE: the warp of the
+// token's first row here (EP_FIRST_OF_TOKEN in the entry, set by the source's sort) reads the fp32
+// row from rank s, together with the token's expert ids and the places of its rows in s's list,
+// and writes the fp16 hi/lo operand rows (same arithmetic and element order as split_rows) of all
+// of the token's rows here; the warps of the other rows only note row_dst.  One warp per row,
+// EP_SPLIT_F4 16-byte loads in flight per lane (the rows come over NVLink: latency is hidden by
+// loads in flight, not by occupancy); the warps stride over the rows, n_rows is on the device.
 __global__ void __launch_bounds__(EP_SPLIT_THREADS)
 ep_split_rows(EpView v, const int *__restrict__ n_rows_dev, const int *__restrict__ seg_base, const int *__restrict__ seg_src,
 	      __half *__restrict__ hi, __half *__restrict__ lo, __half *__restrict__ q_hi, __half *__restrict__ q_lo,
@@ -248,7 +255,7 @@ ep_split_rows(EpView v, const int *__restrict__ n_rows_dev, const int *__restric
 			s_src[i] = seg_src[i];
 	}
 	__syncthreads();
-	const int n_rows = *n_rows_dev, H = v.hidden;
+	const int n_rows = *n_rows_dev, H = v.hidden, K = v.top_k, fe = v.rank * v.n_local;
 	const int lane = threadIdx.x & 31;
 	const int warps = gridDim.x * (EP_SPLIT_THREADS / 32);
 	for (int p = blockIdx.x * (EP_SPLIT_THREADS / 32) + (threadIdx.x >> 5); p < n_rows; p += warps) {
@@ -262,9 +269,10 @@ ep_split_rows(EpView v, const int *__restrict__ n_rows_dev, const int *__restric
 				hi_i = mid;
 		}
 		const int s = lo_i % v.n_ranks;
-		const int id = __ldcg(ep_ptr<int>(v, s, v.off_ids) + s_src[lo_i] + (p - s_base[lo_i]));
-		const int token = id / v.top_k;
-		if (id < 0 || token >= v.t_max) {
+		const int entry = __ldcg(ep_ptr<int>(v, s, v.off_ids) + s_src[lo_i] + (p - s_base[lo_i]));
+		const int id = entry & ~EP_FIRST_OF_TOKEN;
+		const int token = id / K;
+		if (entry < 0 || token >= v.t_max) {
 			if (lane == 0) {
 				atomicOr(status, ST_BAD_TILE);
 				row_dst[p] = (unsigned)v.rank << 24;  // somewhere harmless: row 0 of this rank's own y
@@ -273,9 +281,23 @@ ep_split_rows(EpView v, const int *__restrict__ n_rows_dev, const int *__restric
 		}
 		if (lane == 0)
 			row_dst[p] = ((unsigned)s << 24) | (unsigned)id;
+		if (!(entry & EP_FIRST_OF_TOKEN))
+			continue;  // filled by the warp of the token's first row here
+		// the token's rows here: lane j < K looks at slot j
+		int pj = -1;
+		if (lane < K) {
+			const int ej = __ldcg(ep_ptr<int>(v, s, v.off_topk) + token * K + lane) - fe;
+			if (ej >= 0 && ej < v.n_local) {
+				const int seg = ej * v.n_ranks + s;
+				const int q = s_base[seg] + (__ldcg(ep_ptr<int>(v, s, v.off_inv) + token * K + lane) - s_src[seg]);
+				if (q >= s_base[seg] && q < s_base[seg + 1])
+					pj = q;
+				else
+					atomicOr(status, ST_BAD_TILE);
+			}
+		}
+		const unsigned mine = __ballot_sync(0xffffffffu, pj >= 0);
 		const float4 *xr = reinterpret_cast<const float4 *>(ep_ptr<float>(v, s, v.off_xs) + (size_t)token * H);
-		__half2 *hr = reinterpret_cast<__half2 *>(hi + (size_t)p * H);
-		__half2 *lr = reinterpret_cast<__half2 *>(lo + (size_t)p * H);
 		for (int c0 = 0; c0 < H / 4; c0 += 32 * EP_SPLIT_F4) {
 			float4 x4[EP_SPLIT_F4];
 #pragma unroll
@@ -288,19 +310,25 @@ ep_split_rows(EpView v, const int *__restrict__ n_rows_dev, const int *__restric
 				const int c = c0 + i * 32 + lane;  // float4 index; k = 4 c
 				const __half2 h0 = __floats2half2_rn(x4[i].x, x4[i].z), h1 = __floats2half2_rn(x4[i].y, x4[i].w);
 				const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+				const __half2 l0 = __floats2half2_rn(x4[i].x - f0.x, x4[i].z - f0.y);
+				const __half2 l1 = __floats2half2_rn(x4[i].y - f1.x, x4[i].w - f1.y);
+				const uint2 hv = make_uint2(*reinterpret_cast<const uint32_t *>(&h0), *reinterpret_cast<const uint32_t *>(&h1));
+				const uint2 lv = make_uint2(*reinterpret_cast<const uint32_t *>(&l0), *reinterpret_cast<const uint32_t *>(&l1));
 				float sum = (x4[i].x + x4[i].y) + (x4[i].z + x4[i].w);
 				sum += __shfl_xor_sync(0xffffffffu, sum, 1);
 				sum += __shfl_xor_sync(0xffffffffu, sum, 2);
 				sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-				if (c < H / 4) {
-					hr[2 * c] = h0;
-					hr[2 * c + 1] = h1;
-					lr[2 * c] = __floats2half2_rn(x4[i].x - f0.x, x4[i].z - f0.y);
-					lr[2 * c + 1] = __floats2half2_rn(x4[i].y - f1.x, x4[i].w - f1.y);
-					if (q_hi && (lane & 7) == 0) {
-						const __half h = __float2half_rn(sum);
-						q_hi[(size_t)p * q_cols + (c >> 3)] = h;
-						q_lo[(size_t)p * q_cols + (c >> 3)] = __float2half_rn(sum - __half2float(h));
+				const __half sh = __float2half_rn(sum);
+				const __half sl = __float2half_rn(sum - __half2float(sh));
+				for (unsigned m = mine; m; m &= m - 1u) {
+					const size_t q = (size_t)__shfl_sync(0xffffffffu, pj, __ffs(m) - 1);
+					if (c < H / 4) {
+						reinterpret_cast<uint2 *>(hi + q * H)[c] = hv;
+						reinterpret_cast<uint2 *>(lo + q * H)[c] = lv;
+						if (q_hi && (lane & 7) == 0) {
+							q_hi[q * q_cols + (c >> 3)] = sh;
+							q_lo[q * q_cols + (c >> 3)] = sl;
+						}
 					}
 				}
 			}

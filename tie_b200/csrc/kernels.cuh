@@ -26,6 +26,10 @@ int launch_decode_fused_stack(tie_cuda_ctx *c, int layer, int n_layers, float *h
 struct SortBufs {
 	int *counts, *offsets, *tile_start, *active, *n_active, *perm;
 	int4 *tile_info;  // optional: one entry per token tile (expert, first sorted row, rows, 0)
+	// optional (expert-parallel publish): inv[row id] = where the row stands in perm, and, with
+	// owner_div = experts per GPU and top_k > 0, EP_FIRST_OF_TOKEN set in the entries of perm
+	int *inv = nullptr;
+	int owner_div = 0, top_k = 0;
 };
 int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile);
 int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile, int first_expert, int n_expert,

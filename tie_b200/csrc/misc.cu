@@ -77,51 +77,84 @@ __global__ void __launch_bounds__(256) combine_rows(const float *__restrict__ y,
 	}
 }
 
-// Sum of v over the 8 lanes that hold one 32-wide sub-block (4 consecutive k per lane); the first
-// lane of the group stores it split into fp16 hi + lo.
-__device__ __forceinline__ void store_subblock_sum(float v, int k, __half *__restrict__ q_hi, __half *__restrict__ q_lo)
+// Eight consecutive values v[0..7] (k = k0 .. k0+7, k0 a multiple of 8) -> their fp16 hi and lo
+// halves (hi = rn16(v), lo = rn16(v - hi)) in the operand order [k0, k2, k1, k3] per group of 4, as
+// one 16-byte store each; optionally the sum over the 32-wide sub-block the values belong to (four
+// neighbouring lanes hold one sub-block), split the same way.
+__device__ __forceinline__ void split8_store(const float v[8], int k0, __half *__restrict__ hi_row, __half *__restrict__ lo_row,
+					     __half *__restrict__ q_hi_row, __half *__restrict__ q_lo_row, int lane)
 {
-	v += __shfl_xor_sync(0xffffffffu, v, 1);
-	v += __shfl_xor_sync(0xffffffffu, v, 2);
-	v += __shfl_xor_sync(0xffffffffu, v, 4);
-	if ((threadIdx.x & 7) == 0) {
-		const __half h = __float2half_rn(v);
-		q_hi[k >> 5] = h;
-		q_lo[k >> 5] = __float2half_rn(v - __half2float(h));
+	uint32_t h[4], l[4];
+#pragma unroll
+	for (int g = 0; g < 2; g++) {
+		const float a = v[4 * g], b = v[4 * g + 1], c = v[4 * g + 2], d = v[4 * g + 3];
+		const __half2 h0 = __floats2half2_rn(a, c), h1 = __floats2half2_rn(b, d);
+		const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+		const __half2 l0 = __floats2half2_rn(a - f0.x, c - f0.y), l1 = __floats2half2_rn(b - f1.x, d - f1.y);
+		h[2 * g] = *reinterpret_cast<const uint32_t *>(&h0);
+		h[2 * g + 1] = *reinterpret_cast<const uint32_t *>(&h1);
+		l[2 * g] = *reinterpret_cast<const uint32_t *>(&l0);
+		l[2 * g + 1] = *reinterpret_cast<const uint32_t *>(&l1);
+	}
+	*reinterpret_cast<uint4 *>(hi_row + k0) = make_uint4(h[0], h[1], h[2], h[3]);
+	*reinterpret_cast<uint4 *>(lo_row + k0) = make_uint4(l[0], l[1], l[2], l[3]);
+	if (q_hi_row) {
+		float sum = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+		sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+		sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+		if ((lane & 3) == 0) {
+			const __half hs = __float2half_rn(sum);
+			q_hi_row[k0 >> 5] = hs;
+			q_lo_row[k0 >> 5] = __float2half_rn(sum - __half2float(hs));
+		}
 	}
 }
+
+constexpr int ROWS_WARPS = 8;  // warps per CTA of the row passes: one row per warp at a time
 
 // Gather rows into expert-sorted order and split each fp32 value v into fp16 hi + lo
 // (hi = rn16(v), lo = rn16(v - hi)): hi+lo carries 22 significand bits, which the tensor-core
 // scheme needs to stay within the 1e-3 parity bound.  q_hi/q_lo (optional, q_cols per row): the
 // sums of the row over its 32-wide sub-blocks, split the same way (the Q4_K "min" term).
-// n_cols must be a multiple of 128 (whole warps per loop trip).
-__global__ void __launch_bounds__(256) split_rows(const float *__restrict__ x, const int *__restrict__ perm, int src_div,
-						  int n_cols, __half *__restrict__ hi, __half *__restrict__ lo,
-						  __half *__restrict__ q_hi, __half *__restrict__ q_lo, int q_cols)
+// A warp takes 1024 columns of a row at a time: eight values per lane and step (16-byte loads and
+// stores), four steps' loads in flight; n_cols must be a multiple of 256.
+__global__ void __launch_bounds__(ROWS_WARPS * 32) split_rows(const float *__restrict__ x, const int *__restrict__ perm, int src_div,
+							      int n_rows, int n_cols, __half *__restrict__ hi, __half *__restrict__ lo,
+							      __half *__restrict__ q_hi, __half *__restrict__ q_lo, int q_cols)
 {
-	const int p = blockIdx.x;
-	// (after a call with row experts out of range the sort has placed fewer rows than the grid has
-	// CTAs and the tail of perm is stale: an entry that is no row id of this call reads row 0)
-	unsigned rid = perm ? (unsigned)perm[p] : (unsigned)p;
-	if (perm && rid >= gridDim.x)
-		rid = 0;
-	const int src = perm ? (int)rid / src_div : p;
-	const float *xr = x + (size_t)src * n_cols;
-	__half2 *hr = reinterpret_cast<__half2 *>(hi + (size_t)p * n_cols);
-	__half2 *lr = reinterpret_cast<__half2 *>(lo + (size_t)p * n_cols);
-	for (int k = threadIdx.x * 4; k < n_cols; k += blockDim.x * 4) {
-		float4 v = *reinterpret_cast<const float4 *>(xr + k);
-		// stored order within a group of 4 is [k0, k2, k1, k3], the order the weight tiles use
-		__half2 h0 = __floats2half2_rn(v.x, v.z), h1 = __floats2half2_rn(v.y, v.w);
-		float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
-		__half2 l0 = __floats2half2_rn(v.x - f0.x, v.z - f0.y), l1 = __floats2half2_rn(v.y - f1.x, v.w - f1.y);
-		hr[k / 2] = h0;
-		hr[k / 2 + 1] = h1;
-		lr[k / 2] = l0;
-		lr[k / 2 + 1] = l1;
-		if (q_hi)
-			store_subblock_sum((v.x + v.y) + (v.z + v.w), k, q_hi + (size_t)p * q_cols, q_lo + (size_t)p * q_cols);
+	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+	const int upr = (n_cols + 1023) >> 10;	// units of 1024 columns per row
+	for (int un = blockIdx.x * ROWS_WARPS + warp; un < n_rows * upr; un += gridDim.x * ROWS_WARPS) {
+		const int p = un / upr;
+		// (after a call with row experts out of range the sort has placed fewer rows than it was given and
+		// the tail of perm is stale: an entry that is no row id of this call reads row 0)
+		unsigned rid = perm ? (unsigned)perm[p] : (unsigned)p;
+		if (perm && rid >= (unsigned)n_rows)
+			rid = 0;
+		const int src = perm ? (int)rid / src_div : p;
+		const float *xr = x + (size_t)src * n_cols;
+		__half *hr = hi + (size_t)p * n_cols, *lr = lo + (size_t)p * n_cols;
+		__half *qh = q_hi ? q_hi + (size_t)p * q_cols : nullptr, *ql = q_hi ? q_lo + (size_t)p * q_cols : nullptr;
+		{
+			const int k0 = (un - p * upr) * 1024 + lane * 8;
+			float4 v[4][2];
+#pragma unroll
+			for (int i = 0; i < 4; i++) {
+				const int k = k0 + i * 256;
+				if (k < n_cols) {
+					v[i][0] = *reinterpret_cast<const float4 *>(xr + k);
+					v[i][1] = *reinterpret_cast<const float4 *>(xr + k + 4);
+				}
+			}
+#pragma unroll
+			for (int i = 0; i < 4; i++) {
+				const int k = k0 + i * 256;
+				if (k < n_cols) {  // (uniform over the warp: n_cols is a multiple of 256)
+					const float f[8] = {v[i][0].x, v[i][0].y, v[i][0].z, v[i][0].w, v[i][1].x, v[i][1].y, v[i][1].z, v[i][1].w};
+					split8_store(f, k, hr, lr, qh, ql, lane);
+				}
+			}
+		}
 	}
 }
 
@@ -147,30 +180,37 @@ __global__ void __launch_bounds__(256) gather_rows(const float *__restrict__ x, 
 
 // gu [row][gate(ffn) | up(ffn)] fp32 -> h = SwiGLU(gate, up) * scale, split into fp16 hi + lo and
 // stored in the k order of the tensor-core operand tiles ([k0, k2, k1, k3] per group of 4).
-__global__ void __launch_bounds__(256) swiglu_split_rows(const float *__restrict__ gu, int ffn, float scale,
-							 const float *__restrict__ silu, __half *__restrict__ hi,
-							 __half *__restrict__ lo, __half *__restrict__ q_hi,
-							 __half *__restrict__ q_lo, int q_cols, const int *__restrict__ n_rows_dev)
+// The warps stride over units of 256 columns of a row, with the 32 KB table in shared memory (two
+// look-ups per element: from global memory they were what bound the pass).  ffn must be a multiple
+// of 256.
+__global__ void __launch_bounds__(ROWS_WARPS * 32) swiglu_split_rows(const float *__restrict__ gu, int ffn, float scale,
+								     const float *__restrict__ silu, __half *__restrict__ hi,
+								     __half *__restrict__ lo, __half *__restrict__ q_hi,
+								     __half *__restrict__ q_lo, int q_cols,
+								     const int *__restrict__ n_rows_dev, int n_rows_host)
 {
-	// one row per CTA, or (row count on the device) the CTAs stride over the rows
-	const size_t n_rows = n_rows_dev ? (size_t)*n_rows_dev : gridDim.x;
-	for (size_t r = blockIdx.x; r < n_rows; r += gridDim.x) {
-	const float *g = gu + r * 2 * ffn, *u = g + ffn;
-	__half2 *hr = reinterpret_cast<__half2 *>(hi + r * ffn);
-	__half2 *lr = reinterpret_cast<__half2 *>(lo + r * ffn);
-	for (int k = threadIdx.x * 4; k < ffn; k += blockDim.x * 4) {
-		const float4 gv = *reinterpret_cast<const float4 *>(g + k), uv = *reinterpret_cast<const float4 *>(u + k);
-		const float h0 = swiglu_lut(silu, gv.x, uv.x) * scale, h1 = swiglu_lut(silu, gv.y, uv.y) * scale;
-		const float h2 = swiglu_lut(silu, gv.z, uv.z) * scale, h3 = swiglu_lut(silu, gv.w, uv.w) * scale;
-		const __half2 a = __floats2half2_rn(h0, h2), b = __floats2half2_rn(h1, h3);
-		const float2 fa = __half22float2(a), fb = __half22float2(b);
-		hr[k / 2] = a;
-		hr[k / 2 + 1] = b;
-		lr[k / 2] = __floats2half2_rn(h0 - fa.x, h2 - fa.y);
-		lr[k / 2 + 1] = __floats2half2_rn(h1 - fb.x, h3 - fb.y);
-		if (q_hi)
-			store_subblock_sum((h0 + h1) + (h2 + h3), k, q_hi + r * q_cols, q_lo + r * q_cols);
-	}
+	__shared__ float tab[SILU_N];
+	for (int i = threadIdx.x; i < SILU_N / 4; i += blockDim.x)
+		reinterpret_cast<float4 *>(tab)[i] = __ldg(reinterpret_cast<const float4 *>(silu) + i);
+	__syncthreads();
+	const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+	const size_t n_rows = n_rows_dev ? (size_t)*n_rows_dev : (size_t)n_rows_host;
+	const size_t upr = (size_t)(ffn >> 8);
+	for (size_t un = (size_t)blockIdx.x * ROWS_WARPS + warp; un < n_rows * upr; un += (size_t)gridDim.x * ROWS_WARPS) {
+		const size_t r = un / upr;
+		const float *g = gu + r * 2 * ffn, *u = g + ffn;
+		__half *hr = hi + r * ffn, *lr = lo + r * ffn;
+		__half *qh = q_hi ? q_hi + r * q_cols : nullptr, *ql = q_hi ? q_lo + r * q_cols : nullptr;
+		{
+			const int k = (int)(un - r * upr) * 256 + lane * 8;
+			const float4 g0 = *reinterpret_cast<const float4 *>(g + k), g1 = *reinterpret_cast<const float4 *>(g + k + 4);
+			const float4 u0 = *reinterpret_cast<const float4 *>(u + k), u1 = *reinterpret_cast<const float4 *>(u + k + 4);
+			const float f[8] = {swiglu_lut(tab, g0.x, u0.x) * scale, swiglu_lut(tab, g0.y, u0.y) * scale,
+					    swiglu_lut(tab, g0.z, u0.z) * scale, swiglu_lut(tab, g0.w, u0.w) * scale,
+					    swiglu_lut(tab, g1.x, u1.x) * scale, swiglu_lut(tab, g1.y, u1.y) * scale,
+					    swiglu_lut(tab, g1.z, u1.z) * scale, swiglu_lut(tab, g1.w, u1.w) * scale};
+			split8_store(f, k, hr, lr, qh, ql, lane);
+		}
 	}
 }
 
@@ -211,7 +251,13 @@ int launch_combine(tie_cuda_ctx *c, const float *y, const float *topk_w, int n_t
 int launch_split_rows(tie_cuda_ctx *c, const float *x, const int *perm, int src_div, int n_rows, int n_cols, __half *hi,
 		      __half *lo, __half *q_hi, __half *q_lo)
 {
-	split_rows<<<n_rows, 256, 0, c->stream>>>(x, perm, src_div, n_cols, hi, lo, q_hi, q_lo, xq_cols(n_cols));
+	if (n_cols % 256)
+		return TIE_CUDA_ENOTSUP;
+	const int want = (n_rows * ((n_cols + 1023) / 1024) + ROWS_WARPS - 1) / ROWS_WARPS, cap = c->sm_count * 8;
+	if (n_rows <= 0)
+		return TIE_CUDA_OK;
+	split_rows<<<want < cap ? want : cap, ROWS_WARPS * 32, 0, c->stream>>>(x, perm, src_div, n_rows, n_cols, hi, lo, q_hi, q_lo,
+										xq_cols(n_cols));
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
@@ -227,7 +273,13 @@ int launch_gather_rows(tie_cuda_ctx *c, const float *x, const int *row_expert, c
 int launch_swiglu_split(tie_cuda_ctx *c, const float *gu, int n_rows, int ffn, float scale, __half *hi, __half *lo, __half *q_hi,
 			__half *q_lo, const int *n_rows_dev)
 {
-	swiglu_split_rows<<<n_rows, 256, 0, c->stream>>>(gu, ffn, scale, c->silu, hi, lo, q_hi, q_lo, xq_cols(ffn), n_rows_dev);
+	if (ffn % 256)
+		return TIE_CUDA_ENOTSUP;
+	// (n_rows_dev: the row count is read on the device and n_rows is the grid the caller wants)
+	const int want = (n_rows * (ffn / 256) + ROWS_WARPS - 1) / ROWS_WARPS, cap = c->sm_count * 4;
+	const int grid = n_rows_dev ? n_rows : (want < cap ? want : cap);
+	swiglu_split_rows<<<grid > 0 ? grid : 1, ROWS_WARPS * 32, 0, c->stream>>>(gu, ffn, scale, c->silu, hi, lo, q_hi, q_lo, xq_cols(ffn),
+										   n_rows_dev, n_rows);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }

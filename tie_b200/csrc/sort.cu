@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_scatter(const int *__restri
 							     int n_local, const int *__restrict__ hist, int n_tile,
 							     int *__restrict__ counts, int *__restrict__ offsets, int *__restrict__ tile_start,
 							     int *__restrict__ active, int *__restrict__ n_active, int *__restrict__ perm,
-							     int4 *__restrict__ tile_info)
+							     int4 *__restrict__ tile_info, int *__restrict__ inv, int owner_div, int top_k)
 {
 	__shared__ int cnt[SORT_WARPS][SORT_MAX_E];  // rows of expert e in warp w's 32 rows; then: where they start
 	__shared__ int wsum[3][SORT_WARPS];
@@ -149,8 +149,24 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_scatter(const int *__restri
 		}
 	}
 	__syncthreads();
-	if (le >= 0)  // rows of one expert keep their order: slices, warps and lanes are all in row order
-		perm[cnt[warp][le] + __popc(same & ((1u << lane) - 1u))] = blockIdx.x * SORT_SLICE + threadIdx.x;
+	if (le >= 0) {	// rows of one expert keep their order: slices, warps and lanes are all in row order
+		const int r = blockIdx.x * SORT_SLICE + threadIdx.x;
+		const int pos = cnt[warp][le] + __popc(same & ((1u << lane) - 1u));
+		int entry = r;
+		if (owner_div > 0) {
+			// no earlier slot of the token has an expert of the same owner
+			const int slot = r % top_k, owner = le / owner_div;
+			bool first = true;
+			for (int j = 0; j < slot; j++) {
+				const int ej = row_expert[r - slot + j] - first_expert;
+				first = first && !(ej >= 0 && ej < n_local && ej / owner_div == owner);
+			}
+			entry |= first ? EP_FIRST_OF_TOKEN : 0;
+		}
+		perm[pos] = entry;
+		if (inv)
+			inv[r] = pos;
+	}
 }
 
 int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile, int first_expert, int n_expert,
@@ -164,7 +180,8 @@ int launch_sort(tie_cuda_ctx *c, const int *row_expert, int n_rows, int n_tile, 
 	sort_hist<<<n_slices, SORT_THREADS, 0, c->stream>>>(row_expert, n_rows, first_expert, n_expert, c->s.sort_hist, c->s.status);
 	TIE_CUDA_LAUNCHED(c);
 	sort_scatter<<<n_slices, SORT_THREADS, 0, c->stream>>>(row_expert, n_rows, first_expert, n_expert, c->s.sort_hist, n_tile, b.counts,
-								b.offsets, b.tile_start, b.active, b.n_active, b.perm, b.tile_info);
+								b.offsets, b.tile_start, b.active, b.n_active, b.perm, b.tile_info, b.inv,
+								b.top_k > 0 ? b.owner_div : 0, b.top_k);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
