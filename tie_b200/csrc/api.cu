@@ -1032,7 +1032,8 @@ int tie_cuda_moe_stack_inplace(tie_cuda_ctx *c, int first_layer, int n_layers, f
 		for (int l = first_layer; l < first_layer + n_layers; l++) {
 			Layer &L = c->layers[l];
 			if (decode_paths && decode_fused_supported(c, L, n_tokens)) {
-				const int rc = launch_decode_fused(c, L, hidden_dev, nullptr, hidden_dev, hidden_dev, L.norm_w, c->cfg.norm_eps);
+				const Layer *next = l + 1 < first_layer + n_layers ? &c->layers[l + 1] : nullptr;
+				const int rc = launch_decode_fused(c, L, hidden_dev, nullptr, hidden_dev, hidden_dev, L.norm_w, c->cfg.norm_eps, next);
 				if (rc != TIE_CUDA_ENOTSUP) {
 					if (rc)
 						return rc;

@@ -59,6 +59,10 @@ struct DfArgs {
 	float norm_eps;
 	float *logits, *h, *out, *topk_w;
 	int *topk_idx;
+	// bytes the NEXT launch reads first (the following block's router matrix), or nullptr: requested into
+	// L2 while this block's down products run; whole 16-byte units
+	const uint8_t *next;
+	uint32_t next_bytes;
 	unsigned *status, *sync;  // sync[0]: arrivals, sync[1]: epoch
 	int n_expert, top_k, first_expert, n_local;
 	int rpt_gu, tiles_gu, rpt_dn, tiles_dn;
@@ -337,6 +341,13 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 
 	// ---------------- D: down + combine ----------------
 	DF_STAMP(5);
+	if (a.next && tid == 0) {  // this CTA's share of the next block's first bytes -> L2
+		const uint32_t per = ((a.next_bytes + G - 1) / G + 15u) & ~15u, o = per * (uint32_t)cta;
+		if (o < a.next_bytes) {
+			const uint32_t n = min(per, a.next_bytes - o);
+			asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(a.next + o), "r"(n) : "memory");
+		}
+	}
 	if (dn_role && !bad) {
 		float *hs = reinterpret_cast<float *>(dsm);  // top_k lane-major rows of h (the gate/up tiles are done with)
 		float *vbuf = reinterpret_cast<float *>(dsm + a.off_v);
@@ -446,7 +457,7 @@ static DfPlan df_plan(const tie_cuda_ctx *c)
 
 template <WKind KG, int K, WKind KD, int F>
 static int df_launch(tie_cuda_ctx *c, const Layer &L, const float *x, const float *bias, const float *residual, float *out,
-		     bool query_only, const float *norm_w, float norm_eps)
+		     bool query_only, const float *norm_w, float norm_eps, const Layer *next)
 {
 	const DfPlan p = df_plan<KG, K, KD, F>(c);
 	if (!p.ok)
@@ -486,6 +497,10 @@ static int df_launch(tie_cuda_ctx *c, const Layer &L, const float *x, const floa
 	a.off_n = (uint32_t)p.off_n;
 	a.norm_w = norm_w;
 	a.norm_eps = norm_eps;
+	if (next && next->router_w) {
+		a.next = reinterpret_cast<const uint8_t *>(next->router_w);
+		a.next_bytes = (uint32_t)((size_t)c->cfg.n_expert * K * sizeof(float));
+	}
 	auto kern = decode1_fused<KG, K, KD, F>;
 	TIE_CUDA_TRY(c, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024));
 	cudaLaunchConfig_t cfg = {};
@@ -514,7 +529,7 @@ static int df_launch(tie_cuda_ctx *c, const Layer &L, const float *x, const floa
 #define TIE_DF_SHAPES(X) X(2048, 768) X(512, 256)
 
 static int df_dispatch(tie_cuda_ctx *c, const Layer &L, const float *x, const float *bias, const float *residual, float *out,
-		       bool query_only, const float *norm_w = nullptr, float norm_eps = -1.0f)
+		       bool query_only, const float *norm_w = nullptr, float norm_eps = -1.0f, const Layer *next = nullptr)
 {
 	if (L.gate.kind != L.up.kind)
 		return TIE_CUDA_ENOTSUP;
@@ -522,12 +537,12 @@ static int df_dispatch(tie_cuda_ctx *c, const Layer &L, const float *x, const fl
 #define X(KK, FF)                                                                                                              \
 	if (K == KK && F == FF) {                                                                                              \
 		if (L.gate.kind == W_Q4K && L.down.kind == W_Q6K_R8)                                                           \
-			return df_launch<W_Q4K, KK, W_Q6K_R8, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps);                    \
+			return df_launch<W_Q4K, KK, W_Q6K_R8, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps, next);                    \
 		if (L.gate.kind == W_Q4K && L.down.kind == W_Q4K)                                                              \
-			return df_launch<W_Q4K, KK, W_Q4K, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps);                      \
+			return df_launch<W_Q4K, KK, W_Q4K, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps, next);                      \
 		if (L.gate.kind == W_Q6K_R8 && L.down.kind == W_Q6K_R8)                                                        \
-			return df_launch<W_Q6K_R8, KK, W_Q6K_R8, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps);                \
-		return df_launch<W_Q6K_R8, KK, W_Q4K, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps);                           \
+			return df_launch<W_Q6K_R8, KK, W_Q6K_R8, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps, next);                \
+		return df_launch<W_Q6K_R8, KK, W_Q4K, FF>(c, L, x, bias, residual, out, query_only, norm_w, norm_eps, next);                           \
 	}
 	TIE_DF_SHAPES(X)
 #undef X
@@ -542,10 +557,11 @@ bool decode_fused_supported(tie_cuda_ctx *c, const Layer &L, int n_tokens)
 }
 
 // norm_eps >= 0: x is the un-normed hidden row; the kernel applies RMSNorm (norm_w, or weight 1) first.
+// next: the block that runs after this one (its router matrix is requested into L2 meanwhile), or nullptr.
 int launch_decode_fused(tie_cuda_ctx *c, const Layer &L, const float *x, const float *bias, const float *residual, float *out,
-			const float *norm_w, float norm_eps)
+			const float *norm_w, float norm_eps, const Layer *next)
 {
-	return df_dispatch(c, L, x, bias, residual, out, false, norm_w, norm_eps);
+	return df_dispatch(c, L, x, bias, residual, out, false, norm_w, norm_eps, next);
 }
 
 // One token through consecutive layers as ONE launch: not built (the layer loop inside the kernel

@@ -20,7 +20,7 @@ int launch_router_rows(tie_cuda_ctx *c, const float *x, const float *w, int n_ro
 // decode_fused.cu
 bool decode_fused_supported(tie_cuda_ctx *c, const Layer &L, int n_tokens);
 int launch_decode_fused(tie_cuda_ctx *c, const Layer &L, const float *x, const float *bias, const float *residual, float *out,
-			const float *norm_w = nullptr, float norm_eps = -1.0f);
+			const float *norm_w = nullptr, float norm_eps = -1.0f, const Layer *next = nullptr);
 int launch_decode_fused_stack(tie_cuda_ctx *c, int layer, int n_layers, float *hidden);
 // sort.cu
 struct SortBufs {
