@@ -310,6 +310,8 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 				waited = chunk;
 				if (!alive)
 					break;
+				if (chunk == 0)
+					DF_STAMP(7);
 			}
 			const int row = rp + warp * DK::RPW + sub;
 			float vgv = 0.f, vuv = 0.f;
@@ -325,6 +327,7 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 			if (part == 0 && row < g1)
 				__stcg(hrow + row, swiglu_lut(a.silu, vgv, vuv));
 		}
+		DF_STAMP(8);
 	}
 	alive = __syncthreads_and(alive);
 	DF_STAMP(4);
@@ -355,6 +358,7 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 		for (int j = 0; j < top_k; j++)
 			df_stage_lane_major_cg<KD, DF::LPR>(a.h + (size_t)j * F, hs + (size_t)j * XS_T, DF::PARTS, tid);
 		__syncthreads();
+		DF_STAMP(9);
 		const int sub = lane / DF::LPR, part = lane % DF::LPR;
 		const bool lane_on = part < DF::PARTS;
 		const int rows = d1 - d0;
@@ -385,6 +389,7 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 					vbuf[j * a.rpt_dn + lr] = v;
 			}
 		}
+		DF_STAMP(10);
 		alive = __syncthreads_and(alive);
 		if (alive) {
 			for (int lr = tid; lr < rows; lr += DF_THREADS) {
