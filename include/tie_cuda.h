@@ -54,7 +54,6 @@ extern "C" {
 #define TIE_CUDA_PATH_LEGACY_STREAM (1u << 10) /* with PATH_STREAM: use the general streaming kernels even for 1-4 tokens */
 #define TIE_CUDA_PATH_DECODE_CHAIN (1u << 11) /* one token: the chain of three decode kernels instead of the single cooperative one */
 #define TIE_CUDA_PATH_NO_PAIR (1u << 14) /* tensor path: one CTA per 128-row tile instead of CTA pairs sharing one MMA issue (M = 256) */
-#define TIE_CUDA_EP_OVERLAP (1u << 15) /* expert-parallel step: every rank runs on a GPU of its own — the copy of the peers' tokens runs beside the router and the sort */
 /* Routing of the LFM2-MoE branch (model_lfm2.c:438-473) instead of the Qwen3-MoE one
  * (model_qwen3.c:421-436): sigmoid of the logits, top-k on sigmoid + router_bias (router_bias is
  * then the layer's exp_probs_b selection bias, or NULL), gates = the unbiased sigmoids of the

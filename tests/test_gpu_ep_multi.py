@@ -28,12 +28,10 @@ T_MAX = 128
 be = moe.MoeBackend(max_tokens=T_MAX * world, device=rank, silu_table=silu, ep_rank=rank, ep_size=world)
 be.upload_layer(0, synth.make_layer(workloads.BASE_SEED, shape, first_expert=rank * n_local, n_local_expert=n_local))
 stream = torch.cuda.Stream(); torch.cuda.set_stream(stream); be.set_stream(stream.cuda_stream)
-blk = ep.PeerEpMoeBlock(be, dist, one_gpu_per_rank=True)  # steps 0-3: the peers' tokens are copied beside the router
+blk = ep.PeerEpMoeBlock(be, dist)
 P = port.PortMoe(synth.make_layer(workloads.BASE_SEED, shape), silu=silu)
 worst = 0.0
-for step, T in enumerate([96, 128, 1 + 40 * rank, 64, 80]):   # ragged third step
-    if step == 4:
-        blk.step_flags = 0                                     # ... and once on the step's own stream
+for step, T in enumerate([96, 128, 1 + 40 * rank, 64]):       # ragged third step
     x = synth.make_x(workloads.BASE_SEED + step, T, shape.hidden, first_token=500 * rank)
     xd = torch.from_numpy(x).cuda(); od = torch.full_like(xd, float("nan"))
     stream.synchronize()

@@ -459,7 +459,7 @@ void ep_release(tie_cuda_ctx *c)
 {
 	EpState &ep = c->ep;
 	ep_close_peers(c);
-	void *ptrs[] = {ep.region, ep.n_rows, ep.seg_base, ep.seg_src, ep.row_dst, ep.step_dev, ep.x_all};
+	void *ptrs[] = {ep.region, ep.n_rows, ep.seg_base, ep.seg_src, ep.row_dst, ep.step_dev};
 	for (void *p : ptrs)
 		if (p)
 			cudaFree(p);
@@ -489,6 +489,8 @@ int ep_region(tie_cuda_ctx *c)
 	size_t off = 0;
 	v.off_xs = off;
 	off = align_up(off + (size_t)v.t_max * v.hidden * sizeof(float), 256);
+	v.off_xall = off;
+	off = align_up(off + (size_t)G * v.t_max * v.hidden * sizeof(float), 256);
 	v.off_ids = off;
 	off = align_up(off + (size_t)v.t_max * v.top_k * sizeof(int), 256);
 	v.off_topk = off;
@@ -501,22 +503,17 @@ int ep_region(tie_cuda_ctx *c)
 	off = align_up(off + EP_MAX_RANKS * sizeof(unsigned), 256);
 	v.off_done = off;
 	off = align_up(off + EP_MAX_RANKS * sizeof(unsigned), 256);
-	v.off_xpub = off;
-	off = align_up(off + EP_MAX_RANKS * sizeof(unsigned), 256);
-	v.off_ntok = off;
-	off = align_up(off + sizeof(int), 256);
 	v.off_y = off;
 	off = align_up(off + (size_t)v.t_max * v.top_k * v.hidden * sizeof(float), 256);
 	TIE_CUDA_TRY(c, cudaMalloc(reinterpret_cast<void **>(&ep.region), off));
 	ep.region_bytes = off;
-	// flags (and everything before y) start at zero; y is written before it is read
-	TIE_CUDA_TRY(c, cudaMemset(ep.region, 0, v.off_y));
+	// flags (and the small tables) start at zero; the token and output rows are written before they are read
+	TIE_CUDA_TRY(c, cudaMemset(ep.region + v.off_ids, 0, v.off_y - v.off_ids));
 	TRY(dev_alloc(c, &ep.n_rows, 1));
 	TRY(dev_alloc(c, &ep.seg_base, v.n_expert + 1));
 	TRY(dev_alloc(c, &ep.seg_src, v.n_expert));
 	TRY(dev_alloc(c, &ep.row_dst, (size_t)v.rows_cap));
 	TRY(dev_alloc(c, &ep.step_dev, 1));
-	TRY(dev_alloc(c, &ep.x_all, (size_t)G * v.t_max * v.hidden));
 	TIE_CUDA_TRY(c, cudaMemset(ep.step_dev, 0, sizeof(unsigned)));
 	TIE_CUDA_TRY(c, cudaMemset(ep.n_rows, 0, sizeof(int)));
 	TIE_CUDA_TRY(c, cudaDeviceSynchronize());
@@ -1223,8 +1220,6 @@ int tie_cuda_ep_attach(tie_cuda_ctx *c, const void *const *peers, int n_peers, i
 	if (e == cudaSuccess)
 		e = cudaMemsetAsync(ep.region + ep.view.off_done, 0, EP_MAX_RANKS * sizeof(unsigned), c->stream);
 	if (e == cudaSuccess)
-		e = cudaMemsetAsync(ep.region + ep.view.off_xpub, 0, EP_MAX_RANKS * sizeof(unsigned), c->stream);
-	if (e == cudaSuccess)
 		e = cudaStreamSynchronize(c->stream);
 	if (e != cudaSuccess) {
 		snprintf(c->cuda_err, sizeof(c->cuda_err), "ep_attach: %s", cudaGetErrorString(e));
@@ -1272,7 +1267,7 @@ int tie_cuda_ep_publish(tie_cuda_ctx *c, int layer, const float *x, int n_tokens
 			return TIE_CUDA_ENOTSUP;
 		TIE_CUDA_TRY(c, cudaSetDevice(c->device));
 		prof_mark(c, 0);
-		TRY(launch_ep_signal(c, 0, true));
+		TRY(launch_ep_signal(c, 0));
 		TRY(launch_router_decode_fused(c, x, L->router_w, router_bias, n_tokens, c->s.logits, c->s.topk_idx, c->s.topk_w));
 		prof_mark(c, 1);
 		prof_mark(c, 2);
@@ -1292,22 +1287,19 @@ int tie_cuda_ep_publish(tie_cuda_ctx *c, int layer, const float *x, int n_tokens
 	const int R = n_tokens * c->cfg.top_k;
 	ep.replicated = false;
 	prof_mark(c, 0);
-	// The tokens first: they do not depend on the routing.  Once they are announced every rank copies
-	// every other rank's into local memory — by extra CTAs of the router's kernel where the caller
-	// says that the ranks run on GPUs of their own (on one GPU those CTAs would wait for launches
-	// that come after them), else by a launch of its own before the rows are laid out.
-	float *xs = reinterpret_cast<float *>(ep.region + v.off_xs);
-	if (n_tokens && x != xs)
-		TIE_CUDA_TRY(c, cudaMemcpyAsync(xs, x, (size_t)n_tokens * v.hidden * sizeof(float), cudaMemcpyDeviceToDevice, c->stream));
-	TRY(launch_ep_signal(c, 2, true, n_tokens));
-	ep.overlap = false;
 	// the selected experts go where the peers can read them: the owner of a token's first row on a GPU
 	// looks up the token's other rows there
 	int *topk_pub = reinterpret_cast<int *>(ep.region + v.off_topk);
+	// The tokens do not depend on the routing: they go to every rank's memory beside the router, as
+	// extra CTAs of its kernel (or, for shapes whose router kernel cannot take them along, as a launch
+	// of its own); the pub flag below announces them together with the row lists.
 	if (n_tokens) {
-		const EpFetch fetch = ep_fetch_args(c);
+		const EpPush push = ep_push_args(c, x, n_tokens);
+		bool taken = false;
 		TRY(launch_router(c, x, L->router_w, router_bias, n_tokens, s.logits, topk_pub, s.topk_w, (flags & TIE_CUDA_ROUTE_LFM2) ? 1 : 0,
-				  (flags & TIE_CUDA_EP_OVERLAP) ? &fetch : nullptr, &ep.overlap));
+				  &push, &taken));
+		if (!taken)
+			TRY(launch_ep_push_tokens(c, x, n_tokens));
 	}
 	prof_mark(c, 1);
 	SortBufs b = {reinterpret_cast<int *>(ep.region + v.off_counts),
@@ -1321,7 +1313,7 @@ int tie_cuda_ep_publish(tie_cuda_ctx *c, int layer, const float *x, int n_tokens
 	b.owner_div = c->n_local;
 	b.top_k = c->cfg.top_k;
 	TRY(launch_sort(c, topk_pub, R, 128, 0, c->cfg.n_expert, b));
-	TRY(launch_ep_signal(c, 0, false));
+	TRY(launch_ep_signal(c, 0));
 	prof_mark(c, 2);
 	ep.phase = 1;
 	ep.step_tokens = n_tokens;
@@ -1343,7 +1335,7 @@ int tie_cuda_ep_compute(tie_cuda_ctx *c, int layer, unsigned flags)
 		TRY(launch_decode_gate_up(c, *L, ep.rep_x, ep.step_tokens, true));
 		prof_mark(c, 4);
 		TRY(launch_decode_down_peer(c, *L, ep.step_tokens));
-		TRY(launch_ep_signal(c, 1, false));
+		TRY(launch_ep_signal(c, 1));
 		prof_mark(c, 6);
 		c->last_used_tc = false;
 		c->last_direct_rows = ep.step_tokens * c->cfg.top_k;
@@ -1357,8 +1349,6 @@ int tie_cuda_ep_compute(tie_cuda_ctx *c, int layer, unsigned flags)
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));
 	c->tc_no_pair = (flags & TIE_CUDA_PATH_NO_PAIR) != 0;
 	TRY(launch_ep_index(c));
-	if (!ep.overlap)  // (else the router's kernel has fetched the peers' tokens)
-		TRY(launch_ep_gather_tokens(c));
 	TRY(launch_ep_split_rows(c, L->gate.kind == W_Q4K));
 	prof_mark(c, 3);
 	TRY(launch_tc_gate_up(c, *L, 0));
@@ -1370,7 +1360,7 @@ int tie_cuda_ep_compute(tie_cuda_ctx *c, int layer, unsigned flags)
 		dst.y[i] = reinterpret_cast<float *>(ep.view.peer[i] + ep.view.off_y);
 	dst.row = ep.row_dst;
 	TRY(launch_tc_down_peer(c, *L, dst));
-	TRY(launch_ep_signal(c, 1, false));
+	TRY(launch_ep_signal(c, 1));
 	prof_mark(c, 6);
 	c->last_used_tc = true;
 	c->last_direct_rows = -1;

@@ -112,7 +112,7 @@ constexpr int EP_MAX_RANKS = 16;
 constexpr int EP_FIRST_OF_TOKEN = 1 << 30;
 struct EpView {
 	uint8_t *peer[EP_MAX_RANKS];  // region base of every rank, as mapped into this process
-	size_t off_xs, off_ids, off_topk, off_inv, off_counts, off_pub, off_done, off_xpub, off_ntok, off_y;
+	size_t off_xs, off_xall, off_ids, off_topk, off_inv, off_counts, off_pub, off_done, off_y;
 	long long rows_cap;  // rows of this context's scratch (the worst case of one step)
 	int n_ranks, rank, n_local, n_expert, top_k, hidden, t_max;
 };
@@ -135,10 +135,6 @@ struct EpState {
 	long long wait_cycles = 0;  // budget of every flag wait
 	int *n_rows = nullptr, *seg_base = nullptr, *seg_src = nullptr;
 	unsigned *row_dst = nullptr;  // [rows_cap] per sorted row: (source rank << 24) | its row id there
-	// this rank's copy of every rank's tokens of the step ([n_ranks][t_max][hidden], its own slot unused),
-	// fetched by extra CTAs of the router's kernel (TIE_CUDA_EP_OVERLAP) or by ep_gather_tokens
-	float *x_all = nullptr;
-	bool overlap = false;  // the router's kernel of the step between publish and compute has fetched them
 };
 
 }  // namespace tie

@@ -10,24 +10,23 @@
 //   topk   int  [t_max*K]       the selected experts of its tokens, in slot order
 //   inv    int  [t_max*K]       where each (token, slot) row stands in ids
 //   counts int  [E]             rows per expert from this rank
-//   xpub   u32  [G]             xpub[s] = step number, written BY rank s once its xs (and ntok) are final
-//   ntok   int                  tokens of this rank in the step
-//   pub    u32  [G]             pub[s]  = step number, written BY rank s once ids/counts are final
+//   x_all  fp32 [G][t_max][H]   slot s: the tokens of rank s of the current step, stored BY rank s
+//   pub    u32  [G]             pub[s]  = step number, written BY rank s once its slot of every x_all and
+//                               its ids/counts are final
 //   done   u32  [G]             done[d] = step number, written BY rank d once it has delivered its outputs
 //   y      fp32 [t_max*K][H]    expert outputs of THIS rank's rows, in (token, slot) order, written
 //                               by the owners of the experts
 //
 // A step (all ranks call the three phases in the same order):
-//   publish  tokens into the region, xpub[r] to every peer (release, system scope); ep_gather_tokens
-//            (on a side stream, beside what follows) copies the peers' tokens into local memory as
-//            they are announced; route + sort locally into the region, then pub[r] to every peer
+//   publish  route + sort locally into the region while extra CTAs of the router's kernel store this
+//            rank's tokens into its slot of every rank's x_all (plain stores over NVLink), then
+//            store the step number into pub[r] of every peer (release, system scope)
 //   compute  ep_index waits (bounded) for all G pub flags, reads every peer's counts (G x E ints)
 //            and derives the whole row layout from them alone: the rows of local expert le from
 //            source s sit at offsets[le] + sum_{s'<s} cnt[s'][le] + j — the receiver needs no
-//            sort.  ep_split_rows then lays the token rows out (from the local copy of the peers'
-//            tokens; the row lists come straight out of the peers' regions, plain loads over
-//            NVLink) as the fp16 hi/lo operand of the grouped product and notes where each row
-//            came from; the down product's epilogue stores every output
+//            sort.  ep_split_rows then lays the token rows out (from x_all, local memory; the row
+//            lists come straight out of the peers' regions, plain loads over NVLink) as the fp16
+//            hi/lo operand of the grouped product and notes where each row came from; the down product's epilogue stores every output
 //            row into ITS SOURCE's y (plain stores over NVLink, overlapped with the product);
 //            done[r] is then stored to every peer
 //   gather   ep_combine_rows waits (bounded) for the done flags of all owners and sums each
@@ -47,37 +46,32 @@
 
 namespace tie {
 
-// One CTA: tells every peer that a part of this rank's step is final.  which = 2 (xpub): its
-// tokens (and their number, stored here) — 0 (pub): its row lists — 1 (done): the outputs it owed.
-// The first signal of a step advances the step counter (new_step), the others read it.  The
-// counter lives on the device so that a step's launches take the same arguments every time (they
-// can be replayed from a graph).
-__global__ void ep_signal(EpView v, int which, int new_step, int n_tokens, unsigned *__restrict__ step_dev)
+// One CTA: tells every peer that this rank's part of the current step is final.  which = 0 (pub)
+// first advances the step counter, which = 1 (done) reads it.  The counter lives on the device so
+// that a step's launches take the same arguments every time (they can be replayed from a graph).
+__global__ void ep_signal(EpView v, int which, unsigned *__restrict__ step_dev)
 {
 	unsigned step = 0;
 	if (threadIdx.x == 0) {
-		step = *step_dev + (new_step ? 1u : 0u);
-		if (new_step)
+		step = *step_dev + (which ? 0u : 1u);
+		if (!which)
 			*step_dev = step;
-		if (which == 2)
-			*ep_ptr<int>(v, v.rank, v.off_ntok) = n_tokens;
 	}
 	step = __shfl_sync(0xffffffffu, step, 0);
 	const int d = threadIdx.x;
 	if (d < v.n_ranks) {
-		const size_t off = which == 2 ? v.off_xpub : (which ? v.off_done : v.off_pub);
 		__threadfence_system();
-		st_release_sys(ep_ptr<unsigned>(v, d, off) + v.rank, step);
+		st_release_sys(ep_ptr<unsigned>(v, d, which ? v.off_done : v.off_pub) + v.rank, step);
 	}
 }
 
-constexpr int EP_FETCH_THREADS = 256;
+constexpr int EP_PUSH_THREADS = 256;
 
-// The fetch of the peers' tokens as a launch of its own (where it does not ride along with the
-// router kernel): ep_fetch_tokens_cta on every CTA.
-__global__ void __launch_bounds__(EP_FETCH_THREADS) ep_gather_tokens(EpFetch f)
+// The hand-over of this rank's tokens as a launch of its own (where it does not ride along with
+// the router's kernel): ep_push_tokens_cta on every CTA.
+__global__ void __launch_bounds__(EP_PUSH_THREADS) ep_push_tokens(EpPush f)
 {
-	ep_fetch_tokens_cta(f, blockIdx.x, gridDim.x);
+	ep_push_tokens_cta(f, blockIdx.x, gridDim.x);
 }
 
 constexpr int EP_INDEX_THREADS = 256;
@@ -230,9 +224,9 @@ constexpr int EP_SPLIT_F4 = 8;	// float4 loads a lane keeps in flight
 // EP_SPLIT_F4 16-byte loads in flight per lane (the rows come over NVLink: latency is hidden by
 // loads in flight, not by occupancy); the warps stride over the rows, n_rows is on the device.
 __global__ void __launch_bounds__(EP_SPLIT_THREADS)
-ep_split_rows(EpView v, const float *__restrict__ x_all, const int *__restrict__ n_rows_dev, const int *__restrict__ seg_base,
-	      const int *__restrict__ seg_src, __half *__restrict__ hi, __half *__restrict__ lo, __half *__restrict__ q_hi,
-	      __half *__restrict__ q_lo, int q_cols, unsigned *__restrict__ row_dst, unsigned *__restrict__ status)
+ep_split_rows(EpView v, const int *__restrict__ n_rows_dev, const int *__restrict__ seg_base, const int *__restrict__ seg_src,
+	      __half *__restrict__ hi, __half *__restrict__ lo, __half *__restrict__ q_hi, __half *__restrict__ q_lo,
+	      int q_cols, unsigned *__restrict__ row_dst, unsigned *__restrict__ status)
 {
 	__shared__ int s_base[257], s_src[256];
 	const int n_seg = v.n_local * v.n_ranks;  // = n_expert
@@ -284,9 +278,8 @@ ep_split_rows(EpView v, const float *__restrict__ x_all, const int *__restrict__
 			}
 		}
 		const unsigned mine = __ballot_sync(0xffffffffu, pj >= 0);
-		// the token: this rank's own, or its local copy of rank s's (ep_gather_tokens)
-		const float *xs_s = s == v.rank ? ep_ptr<float>(v, s, v.off_xs) : x_all + (size_t)s * v.t_max * H;
-		const float4 *xr = reinterpret_cast<const float4 *>(xs_s + (size_t)token * H);
+		// the token: slot s of this rank's x_all, where rank s has stored its tokens
+		const float4 *xr = reinterpret_cast<const float4 *>(ep_ptr<float>(v, v.rank, v.off_xall) + ((size_t)s * v.t_max + token) * H);
 		for (int c0 = 0; c0 < H / 4; c0 += 32 * EP_SPLIT_F4) {
 			float4 x4[EP_SPLIT_F4];
 #pragma unroll
@@ -373,27 +366,27 @@ ep_combine_rows(EpView v, const unsigned *__restrict__ step_dev, long long budge
 	}
 }
 
-int launch_ep_signal(tie_cuda_ctx *c, int which, bool new_step, int n_tokens)
+int launch_ep_signal(tie_cuda_ctx *c, int which)
 {
-	ep_signal<<<1, 32, 0, c->stream>>>(c->ep.view, which, new_step ? 1 : 0, n_tokens, c->ep.step_dev);
+	ep_signal<<<1, 32, 0, c->stream>>>(c->ep.view, which, c->ep.step_dev);
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
 
-EpFetch ep_fetch_args(tie_cuda_ctx *c)
+EpPush ep_push_args(tie_cuda_ctx *c, const float *x, int n_tokens)
 {
-	EpFetch f;
+	EpPush f;
 	f.v = c->ep.view;
-	f.step_dev = c->ep.step_dev;
-	f.budget = c->ep.wait_cycles;
-	f.x_all = c->ep.x_all;
-	f.status = c->s.status;
+	f.x = x;
+	f.n_tokens = n_tokens;
 	return f;
 }
 
-int launch_ep_gather_tokens(tie_cuda_ctx *c)
+int launch_ep_push_tokens(tie_cuda_ctx *c, const float *x, int n_tokens)
 {
-	ep_gather_tokens<<<c->sm_count * 2, EP_FETCH_THREADS, 0, c->stream>>>(ep_fetch_args(c));
+	if (n_tokens <= 0)
+		return TIE_CUDA_OK;
+	ep_push_tokens<<<c->sm_count, EP_PUSH_THREADS, 0, c->stream>>>(ep_push_args(c, x, n_tokens));
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }
@@ -413,7 +406,7 @@ int launch_ep_index(tie_cuda_ctx *c)
 int launch_ep_split_rows(tie_cuda_ctx *c, bool sums)
 {
 	Scratch &s = c->s;
-	ep_split_rows<<<c->sm_count * 8, EP_SPLIT_THREADS, 0, c->stream>>>(c->ep.view, c->ep.x_all, c->ep.n_rows, c->ep.seg_base, c->ep.seg_src,
+	ep_split_rows<<<c->sm_count * 8, EP_SPLIT_THREADS, 0, c->stream>>>(c->ep.view, c->ep.n_rows, c->ep.seg_base, c->ep.seg_src,
 									    s.xs_hi, s.xs_lo, sums ? s.xq_hi : nullptr,
 									    sums ? s.xq_lo : nullptr, xq_cols(c->cfg.hidden), c->ep.row_dst,
 									    s.status);

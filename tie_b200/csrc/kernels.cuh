@@ -5,9 +5,9 @@
 namespace tie {
 
 // router.cu
-struct EpFetch;
+struct EpPush;
 int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *bias, int n_tokens, float *logits,
-		  int *topk_idx, float *topk_w, int lfm2 = 0, const EpFetch *fetch = nullptr, bool *fetch_taken = nullptr);
+		  int *topk_idx, float *topk_w, int lfm2 = 0, const EpPush *push = nullptr, bool *push_taken = nullptr);
 int router_setup(tie_cuda_ctx *c);
 int launch_router_decode_fused(tie_cuda_ctx *c, const float *x, const float *w, const float *bias, int n_tokens, float *logits,
 			       int *topk_idx, float *topk_w);
@@ -65,9 +65,9 @@ int launch_tc_swiglu(tie_cuda_ctx *c, const Layer &L, int n_rows, const int *n_r
 int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, float *y, bool sorted_out = false);
 int launch_tc_down_peer(tie_cuda_ctx *c, const Layer &L, const EpDst &dst);
 // ep.cu
-int launch_ep_signal(tie_cuda_ctx *c, int which, bool new_step, int n_tokens = 0);
-int launch_ep_gather_tokens(tie_cuda_ctx *c);
-EpFetch ep_fetch_args(tie_cuda_ctx *c);  // (ep_dev.cuh defines EpFetch)
+int launch_ep_signal(tie_cuda_ctx *c, int which);
+int launch_ep_push_tokens(tie_cuda_ctx *c, const float *x, int n_tokens);
+EpPush ep_push_args(tie_cuda_ctx *c, const float *x, int n_tokens);  // (ep_dev.cuh defines EpPush)
 int launch_ep_index(tie_cuda_ctx *c);
 int launch_ep_split_rows(tie_cuda_ctx *c, bool sums);
 int launch_ep_combine(tie_cuda_ctx *c, int n_tokens, const float *residual, float *out);

@@ -87,15 +87,15 @@ struct RmtCfg {
 template <int TPT, int EPT, int TE, int KC>
 __global__ void __launch_bounds__((RmtCfg<TPT, EPT, TE, KC>::THREADS), 2)
 router_logits_mt(const float *__restrict__ x, const float *__restrict__ w, const float *__restrict__ bias, float *__restrict__ logits,
-		 int n_tokens, int hidden, int n_expert, const EpFetch fetch)
+		 int n_tokens, int hidden, int n_expert, const EpPush push)
 {
 	using Cfg = RmtCfg<TPT, EPT, TE, KC>;
 	constexpr int TT = Cfg::TT, PITCH = Cfg::PITCH, THREADS = Cfg::THREADS;
 	extern __shared__ __align__(16) float rsm[];
-	// Expert-parallel steps: one more row of CTAs (blockIdx.y past the expert tiles) copies the peers'
-	// tokens into local memory while the others compute the logits; it shares nothing with them.
-	if (fetch.x_all && (int)blockIdx.y * TE >= n_expert) {
-		ep_fetch_tokens_cta(fetch, blockIdx.x, gridDim.x);
+	// Expert-parallel steps: one more row of CTAs (blockIdx.y past the expert tiles) stores this rank's
+	// tokens into every rank's memory while the others compute the logits; it shares nothing with them.
+	if (push.x && (int)blockIdx.y * TE >= n_expert) {
+		ep_push_tokens_cta(push, blockIdx.x, gridDim.x);
 		return;
 	}
 	const int t0 = blockIdx.x * TT, e0 = blockIdx.y * TE;
@@ -379,17 +379,17 @@ __global__ void __launch_bounds__(256) router_decode_fused(const float *__restri
 
 // lfm2 = 0: bias (optional) is added to the logits, top-k + softmax over the selected logits
 // (Qwen3-MoE).  lfm2 = 1: LFM2-MoE routing, bias (optional) is the selection bias exp_probs_b.
-// fetch (expert-parallel steps): the kernel of the logits takes the copy of the peers' tokens along as
-// extra CTAs where it can; *fetch_taken tells whether it did.
+// push (expert-parallel steps): the kernel of the logits takes the hand-over of this rank's tokens to
+// its peers along as extra CTAs where it can; *push_taken tells whether it did.
 int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *bias, int n_tokens, float *logits,
-		  int *topk_idx, float *topk_w, int lfm2, const EpFetch *fetch, bool *fetch_taken)
+		  int *topk_idx, float *topk_w, int lfm2, const EpPush *push, bool *push_taken)
 {
 	const int H = c->cfg.hidden, E = c->cfg.n_expert, K = c->cfg.top_k;
-	EpFetch f = {};
-	if (fetch)
-		f = *fetch;
-	if (fetch_taken)
-		*fetch_taken = false;
+	EpPush f = {};
+	if (push)
+		f = *push;
+	if (push_taken)
+		*push_taken = false;
 	const float *sel_bias = lfm2 ? bias : nullptr;
 	if (lfm2)
 		bias = nullptr;
@@ -401,17 +401,17 @@ int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *
 		TIE_CUDA_LAUNCHED(c);
 	} else if (E % 64 == 0 && H % 128 == 0 && n_tokens >= 2048) {
 		using Cfg = RmtCfg<8, 8, 64, 64>;
-		dim3 grid((n_tokens + Cfg::TT - 1) / Cfg::TT, E / 64 + (fetch ? 1 : 0));
+		dim3 grid((n_tokens + Cfg::TT - 1) / Cfg::TT, E / 64 + (push ? 1 : 0));
 		router_logits_mt<8, 8, 64, 64><<<grid, Cfg::THREADS, Cfg::SMEM, c->stream>>>(x, w, bias, logits, n_tokens, H, E, f);
-		if (fetch_taken)
-			*fetch_taken = fetch != nullptr;
+		if (push_taken)
+			*push_taken = push != nullptr;
 		TIE_CUDA_LAUNCHED(c);
 	} else if (E % 32 == 0 && H % 128 == 0) {
 		using Cfg = RmtCfg<4, 4, 32, 128>;
-		dim3 grid((n_tokens + Cfg::TT - 1) / Cfg::TT, E / 32 + (fetch ? 1 : 0));
+		dim3 grid((n_tokens + Cfg::TT - 1) / Cfg::TT, E / 32 + (push ? 1 : 0));
 		router_logits_mt<4, 4, 32, 128><<<grid, Cfg::THREADS, Cfg::SMEM, c->stream>>>(x, w, bias, logits, n_tokens, H, E, f);
-		if (fetch_taken)
-			*fetch_taken = fetch != nullptr;
+		if (push_taken)
+			*push_taken = push != nullptr;
 		TIE_CUDA_LAUNCHED(c);
 	} else if (n_tokens <= 512) {
 		constexpr int TT = 8, EPC = 16;

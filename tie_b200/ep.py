@@ -141,13 +141,9 @@ class PeerEpMoeBlock:
     and no host synchronisation per step.  torch.distributed is used once, to exchange the IPC
     handles of the ranks' regions."""
 
-    def __init__(self, be, dist, group=None, one_gpu_per_rank: bool = False):
-        """one_gpu_per_rank: every rank of the group runs on a GPU of its own (the torchrun layout).  Each
-        rank then copies its peers' tokens beside its router and sort (TIE_CUDA_EP_OVERLAP); ranks that
-        share a GPU must leave it off: the copy kernel would wait for launches queued behind it."""
+    def __init__(self, be, dist, group=None):
         from . import moe
         self.be, self.moe = be, moe
-        self.step_flags = moe.EP_OVERLAP if one_gpu_per_rank else 0
         G = dist.get_world_size(group)
         handles = [None] * G
         dist.all_gather_object(handles, be.ep_ipc_handle(), group=group)
@@ -157,7 +153,7 @@ class PeerEpMoeBlock:
     def forward(self, x, out, graph: bool = True):
         """x, out: device tensors [n_tokens][hidden].  graph: replay the step's launches from a CUDA
         graph (one per distinct (x, out, n_tokens))."""
-        flags = self.moe.DEVICE | self.moe.NO_SYNC | (self.moe.GRAPH if graph else 0) | self.step_flags
+        flags = self.moe.DEVICE | self.moe.NO_SYNC | (self.moe.GRAPH if graph else 0)
         self.be.moe_ffn_ep_ptr(0, x, out, x.shape[0], flags)
         return out
 
@@ -238,9 +234,8 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler, co
     torch.cuda.set_stream(stream)
     be.set_stream(stream.cuda_stream)
     exchange = getattr(args, "ep_exchange", "peer")
-    own_gpus = torch.cuda.device_count() >= world  # one rank per GPU (the layout torchrun gives)
     if exchange == "peer":
-        blk = PeerEpMoeBlock(be, dist, one_gpu_per_rank=own_gpus)
+        blk = PeerEpMoeBlock(be, dist)
     else:
         nccl_blk = EpMoeBlock(CudaOps(be, torch), torch, dist)
 
@@ -425,11 +420,11 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler, co
             be2.upload_layer(l, synth.make_layer(workloads.STACK_BASE_SEED + l, shape, first_expert=rank * n_local,
                                                  n_local_expert=n_local), ffn_norm_w=ones)
         be2.set_stream(stream.cuda_stream)
-        PeerEpMoeBlock(be2, dist, one_gpu_per_rank=own_gpus)
+        PeerEpMoeBlock(be2, dist)
         h0_host = synth.make_x(workloads.STACK_BASE_SEED, T3, first_token=rank * T3)
         h0 = torch.from_numpy(h0_host).cuda()
         h = h0.clone()
-        fl = moe.DEVICE | moe.NO_SYNC | moe.GRAPH | (moe.EP_OVERLAP if own_gpus else 0)
+        fl = moe.DEVICE | moe.NO_SYNC | moe.GRAPH
 
         def stack_pass():
             for l in range(n_layers):

@@ -21,7 +21,6 @@ PATH_DECODE_CHAIN = 1 << 11  # one token: three chained decode kernels instead o
 ROUTE_LFM2 = 1 << 12  # LFM2-MoE routing: sigmoid, selection bias, L1-normalised gates (model_lfm2.c:438-473)
 PATH_NO_PAIR = 1 << 14  # tensor path: single-CTA grouped GEMM instead of CTA pairs
 EP_REPLICATED = 1 << 13  # expert-parallel decode: the same 1-4 tokens on every rank
-EP_OVERLAP = 1 << 15  # expert-parallel step with one GPU per rank: the peers' tokens are copied beside the router and the sort
 OK, EINVAL, ENOTSUP, ENOMEM, ECUDA, ENODEV, EKERNEL, ETOOBIG = 0, -1, -2, -3, -4, -5, -6, -7
 
 # every symbol include/tie_cuda.h declares
