@@ -4,9 +4,9 @@ tokens data-parallel.  The reference is a single process and has no counterpart.
 Two exchanges are implemented:
 
 PeerEpMoeBlock (default)  dispatch and combine over peer memory (tie_cuda_ep_*): every rank exposes
-    one region of its HBM; the owners' kernels load token rows straight from the sources' regions
-    and the down product stores every output row straight into its source's region (plain loads and
-    stores over NVLink), synchronised by step-numbered flags.  No collective and no host
+    one region of its HBM; a rank stores its tokens into every rank's region while it routes them,
+    and the down product stores every output row straight into its source's region (plain stores
+    over NVLink; only the small row lists are loaded), synchronised by step-numbered flags.  No collective and no host
     synchronisation per step; torch.distributed only exchanges the IPC handles once.
 
 EpMoeBlock (baseline)     the same step with NCCL collectives (torch.distributed):
@@ -158,8 +158,8 @@ class PeerEpMoeBlock:
         return out
 
     def token_buffer(self, torch, n_tokens: int):
-        """A [n_tokens][hidden] fp32 tensor over the part of this rank's region its peers read the
-        tokens from: a step whose x lives there skips the copy into the region."""
+        """A [n_tokens][hidden] fp32 tensor over the token buffer at the start of this rank's region
+        (where tie_cuda_moe_block_inplace_ep writes the normed rows)."""
         base, _ = self.be.ep_region()
 
         class _View:
@@ -171,9 +171,15 @@ class PeerEpMoeBlock:
 NVLINK_GBS = 770.0  # measured peer-copy rate per direction on this pool's B200s
 
 
+def _nvlink_bytes_per_direction(shape, tokens_per_rank, world):
+    """What one rank sends (and, by symmetry, receives) per step: its tokens to every peer, and the
+    output rows it computed for other ranks' tokens ((world-1)/world of its rows on average)."""
+    row = shape.hidden * 4
+    return tokens_per_rank * row * (world - 1) + tokens_per_rank * shape.top_k * row * (world - 1) / world
+
+
 def _step_roofline(shape, tokens_per_rank, world, ms_per_step, flops_total, peaks):
-    rows = tokens_per_rank * shape.top_k
-    nvlink_bytes = rows * shape.hidden * 4 * (world - 1) / world
+    nvlink_bytes = _nvlink_bytes_per_direction(shape, tokens_per_rank, world)
     hbm_bytes = (shape.n_expert // world) * shape.expert_bytes + shape.router_bytes + 2 * tokens_per_rank * shape.hidden * 4
     t_nvlink = nvlink_bytes / (NVLINK_GBS * 1e9)
     t_hbm = hbm_bytes / (peaks["hbm_gbs"] * 1e9)
@@ -190,7 +196,7 @@ def _step_roofline(shape, tokens_per_rank, world, ms_per_step, flops_total, peak
     return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit, "frac": achieved / peak, "traffic": None,
             "floors_us": {k: v * 1e6 for k, v in floors.items()},
             "nvlink": {"bytes_per_direction": nvlink_bytes, "achieved_gbs": nvlink_bytes / t / 1e9, "peak_gbs": NVLINK_GBS},
-            "note": "one rank's whole step against the slowest of its floors (rows over NVLink in one direction at the measured "
+            "note": "one rank's whole step against the slowest of its floors (tokens and output rows over NVLink in one direction at the measured "
                     "770 GB/s peer copy, algorithmic HBM bytes at the measured copy rate, flops at the measured bf16 GEMM rate); "
                     "the per-kernel HBM roofline is reported by the 1-GPU run",
             "algorithmic_tflops": flops_total / t / 1e12}
@@ -367,7 +373,7 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler, co
             prof, _ = be.get_profile()
             acc = prof if acc is None else {k: acc[k] + v for k, v in prof.items()}
         be.set_profiling(False)
-        names = {"router": "router", "sort": "sort + publish", "split": "layout + remote row gather", "gate_up": "gate/up product",
+        names = {"router": "router (+ tokens to the peers)", "sort": "sort + publish", "split": "wait for the peers' lists + row layout", "gate_up": "gate/up product",
                  "swiglu": "SwiGLU pass", "down": "down product (stores rows to their sources)", "combine": "wait for owners + combine"}
         phases = {names[k]: v / n_prof for k, v in acc.items()}
 
@@ -506,8 +512,8 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler, co
             "config_detail": {
                 "l2": f"weights touched per step per rank: {392 // world} MB plus {T * shape.top_k * shape.hidden * 8 // 2**20} MB of rows "
                       "(larger than L2 from N = 1 to 2; at N >= 4 the weights of a rank fit in L2, as they would in deployment)",
-                "exchange": ("peer memory: owners load token rows from the sources' HBM and store output rows into the sources' "
-                             "(no collective, no host synchronisation per step)") if exchange == "peer"
+                "exchange": ("peer memory: a rank stores its tokens into every rank's HBM beside its router, owners store output rows "
+                             "into the sources' (no collective, no host synchronisation per step)") if exchange == "peer"
                 else "NCCL all-to-all (torch.distributed) for dispatch and combine"},
             "clocks": clocks,
             "e2e": {"value": T * world / e2e_s, "unit": unit, "h2d_bytes_per_step": T * shape.hidden * 4 * world,
@@ -522,9 +528,9 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler, co
             "parity": parity,
             "exchange": {"rows_per_rank": T * shape.top_k, "bytes_per_row": shape.hidden * 4,
                          "remote_fraction": (world - 1) / world,
-                         "nvlink_bytes_per_rank_and_direction": int(T * shape.top_k * shape.hidden * 4 * (world - 1) / world),
-                         "nvlink_floor_us": 2 * T * shape.top_k * shape.hidden * 4 * (world - 1) / world / 770e9 * 1e6,
-                         "note": "floor = dispatch + combine bytes of one rank / measured 770 GB/s per direction",
+                         "nvlink_bytes_per_rank_and_direction": int(_nvlink_bytes_per_direction(shape, T, world)),
+                         "nvlink_floor_us": _nvlink_bytes_per_direction(shape, T, world) / (NVLINK_GBS * 1e9) * 1e6,
+                         "note": "floor = tokens to every peer + output rows to their sources, of one rank / measured 770 GB/s per direction",
                          "phases_ms_rank0": phases},
             "extra": {"prefill_8192_tokens_total": strong, "stack_prefill_4096_tokens": stack},
         }
