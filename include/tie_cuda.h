@@ -195,11 +195,12 @@ int tie_cuda_moe_ep_combine(tie_cuda_ctx *c, const float *y_sorted, const float 
 /* ---- expert parallelism over peer memory (the reference has no counterpart) ----
  * One context per GPU (ep_rank / ep_size in the config; max_tokens = ep_size x the tokens one rank
  * brings per step, so that the scratch holds the worst case of every row landing on one rank).
- * Dispatch and combine are not collectives here: every rank exposes one region of its HBM, the
- * owners' kernels read token rows straight out of the sources' regions and the down product
- * stores every output row straight into its source's region (plain loads and stores over
- * NVLink); ranks synchronise through step-numbered flags they store into each other's regions.
- * No host synchronisation per step.
+ * Dispatch and combine are not collectives here: every rank exposes one region of its HBM, a
+ * rank stores its tokens into every rank's region while it routes them, the owners read the
+ * (small) row lists out of the sources' regions and the down product stores every output row
+ * straight into its source's region (plain stores and loads over NVLink); ranks synchronise
+ * through step-numbered flags they store into each other's regions.  No host synchronisation
+ * per step.
  *
  * Set-up, once, collectively: tie_cuda_ep_ipc_handle() on every rank, exchange the 64-byte
  * handles by any host channel, tie_cuda_ep_attach(handles, ep_size, TIE_CUDA_EP_PEER_IPC_HANDLES).
@@ -209,18 +210,18 @@ int tie_cuda_moe_ep_combine(tie_cuda_ctx *c, const float *y_sorted, const float 
  *
  * A step, on every rank, in this order (device pointers, TIE_CUDA_DEVICE; tensor-core path only):
  *   tie_cuda_ep_publish  routes x [n_tokens][hidden] (0 <= n_tokens <= max_tokens / ep_size, may
- *                        differ between ranks), sorts its rows by expert and announces them
- *   tie_cuda_ep_compute  waits for every rank's announcement, gathers the rows of this rank's
- *                        experts from their sources, runs gate/up, SwiGLU, down (outputs land at
- *                        their sources)
+ *                        differ between ranks) and hands it to every rank meanwhile, sorts its
+ *                        rows by expert and announces the step
+ *   tie_cuda_ep_compute  waits for every rank's announcement, lays out the rows of this rank's
+ *                        experts (tokens from its own memory, row lists from their sources), runs
+ *                        gate/up, SwiGLU, down (outputs land at their sources)
  *   tie_cuda_ep_gather   waits for every owner, out[t] = (residual[t] +) sum_j w[t][j] * y(t, j)
  * With TIE_CUDA_EP_REPLICATED in the flags of tie_cuda_ep_publish the step is the decode form:
  * the same 1 to 4 tokens on every rank (no dispatch: publish only routes and announces the step;
  * compute runs gate/up and down for the locally owned slots and stores the down rows to all
  * ranks; gather combines).  Prefill and decode steps may alternate freely.
  * tie_cuda_moe_ffn_ep is the three in a row; with TIE_CUDA_GRAPH the whole step is replayed from a
- * CUDA graph (the step number advances on the device).  A step whose x is the start of this
- * rank's region (tie_cuda_ep_region) skips the copy into it.
+ * CUDA graph (the step number advances on the device).
  * Kernels of different ranks wait on one another, so
  * ranks that share ONE GPU must enqueue phase by phase on one stream (all publishes, then all
  * computes, then all gathers) — a wait is then always already satisfied; on separate GPUs the

@@ -216,13 +216,14 @@ constexpr int EP_SPLIT_F4 = 8;	// float4 loads a lane keeps in flight
 
 // Sorted row p of this rank = row j of segment (le, s): entry ids[seg_src + j] of rank s, token
 // id / top_k.  row_dst[p] = (s << 24) | row id tells the down product where the row's output goes.
-// A token whose selected experts include several of this rank's is fetched ONCE: the warp of the
-// token's first row here (EP_FIRST_OF_TOKEN in the entry, set by the source's sort) reads the fp32
-// row from rank s, together with the token's expert ids and the places of its rows in s's list,
-// and writes the fp16 hi/lo operand rows (same arithmetic and element order as split_rows) of all
-// of the token's rows here; the warps of the other rows only note row_dst.  One warp per row,
-// EP_SPLIT_F4 16-byte loads in flight per lane (the rows come over NVLink: latency is hidden by
-// loads in flight, not by occupancy); the warps stride over the rows, n_rows is on the device.
+// The token itself is in this rank's x_all (slot s), where rank s has stored it.  A token whose
+// selected experts include several of this rank's is read ONCE: the warp of the token's first
+// row here (EP_FIRST_OF_TOKEN in the entry, set by the source's sort) reads the fp32 row,
+// together with the token's expert ids and the places of its rows in s's list (from rank s, over
+// NVLink: a few bytes), and writes the fp16 hi/lo operand rows (same arithmetic and element order
+// as split_rows) of all of the token's rows here; the warps of the other rows only note row_dst.
+// One warp per row, EP_SPLIT_F4 16-byte loads in flight per lane; the warps stride over the rows,
+// n_rows is on the device.
 __global__ void __launch_bounds__(EP_SPLIT_THREADS)
 ep_split_rows(EpView v, const int *__restrict__ n_rows_dev, const int *__restrict__ seg_base, const int *__restrict__ seg_src,
 	      __half *__restrict__ hi, __half *__restrict__ lo, __half *__restrict__ q_hi, __half *__restrict__ q_lo,

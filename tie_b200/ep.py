@@ -256,7 +256,7 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler, co
     x_host = torch.from_numpy(synth.make_x(workloads.BASE_SEED, T, first_token=rank * T)).pin_memory()
     out_host = torch.empty_like(x_host).pin_memory()
     if exchange == "peer":
-        x_dev = blk.token_buffer(torch, T)  # the tokens are resident where the peers read them
+        x_dev = blk.token_buffer(torch, T)  # (any device buffer would do: the step hands the tokens to the peers itself)
         x_dev.copy_(x_host)
     else:
         x_dev = x_host.cuda()
