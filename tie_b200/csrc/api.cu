@@ -499,6 +499,8 @@ int ep_region(tie_cuda_ctx *c)
 	off = align_up(off + (size_t)v.t_max * v.top_k * sizeof(int), 256);
 	v.off_counts = off;
 	off = align_up(off + (size_t)v.n_expert * sizeof(int), 256);
+	v.off_cntall = off;
+	off = align_up(off + (size_t)G * v.n_expert * sizeof(int), 256);
 	v.off_pub = off;
 	off = align_up(off + EP_MAX_RANKS * sizeof(unsigned), 256);
 	v.off_done = off;

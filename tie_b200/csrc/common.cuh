@@ -112,7 +112,7 @@ constexpr int EP_MAX_RANKS = 16;
 constexpr int EP_FIRST_OF_TOKEN = 1 << 30;
 struct EpView {
 	uint8_t *peer[EP_MAX_RANKS];  // region base of every rank, as mapped into this process
-	size_t off_xs, off_xall, off_ids, off_topk, off_inv, off_counts, off_pub, off_done, off_y;
+	size_t off_xs, off_xall, off_ids, off_topk, off_inv, off_counts, off_cntall, off_pub, off_done, off_y;
 	long long rows_cap;  // rows of this context's scratch (the worst case of one step)
 	int n_ranks, rank, n_local, n_expert, top_k, hidden, t_max;
 };

@@ -10,6 +10,7 @@
 //   topk   int  [t_max*K]       the selected experts of its tokens, in slot order
 //   inv    int  [t_max*K]       where each (token, slot) row stands in ids
 //   counts int  [E]             rows per expert from this rank
+//   cnt_all int [G][E]          row s: the counts of rank s, stored BY rank s with its pub flag
 //   x_all  fp32 [G][t_max][H]   slot s: the tokens of rank s of the current step, stored BY rank s
 //   pub    u32  [G]             pub[s]  = step number, written BY rank s once its slot of every x_all and
 //                               its ids/counts are final
@@ -21,8 +22,8 @@
 //   publish  route + sort locally into the region while extra CTAs of the router's kernel store this
 //            rank's tokens into its slot of every rank's x_all (plain stores over NVLink), then
 //            store the step number into pub[r] of every peer (release, system scope)
-//   compute  ep_index waits (bounded) for all G pub flags, reads every peer's counts (G x E ints)
-//            and derives the whole row layout from them alone: the rows of local expert le from
+//   compute  ep_index waits (bounded) for all G pub flags, reads the G x E count matrix (local)
+//            and derives the whole row layout from it alone: the rows of local expert le from
 //            source s sit at offsets[le] + sum_{s'<s} cnt[s'][le] + j — the receiver needs no
 //            sort.  ep_split_rows then lays the token rows out (from x_all, local memory; the row
 //            lists come straight out of the peers' regions, plain loads over NVLink) as the fp16
@@ -58,6 +59,17 @@ __global__ void ep_signal(EpView v, int which, unsigned *__restrict__ step_dev)
 			*step_dev = step;
 	}
 	step = __shfl_sync(0xffffffffu, step, 0);
+	if (!which) {
+		// this rank's rows per expert go to every rank's count matrix (row `rank`): the owners derive
+		// their layout from local memory
+		const int *cnt = ep_ptr<int>(v, v.rank, v.off_counts);
+		for (int e = threadIdx.x; e < v.n_expert; e += 32) {
+			const int c = __ldcg(cnt + e);
+			for (int j = 0; j < v.n_ranks; j++)
+				ep_ptr<int>(v, (v.rank + j) % v.n_ranks, v.off_cntall)[(size_t)v.rank * v.n_expert + e] = c;
+		}
+		__syncwarp();
+	}
 	const int d = threadIdx.x;
 	if (d < v.n_ranks) {
 		__threadfence_system();
@@ -132,21 +144,42 @@ ep_index(EpView v, const unsigned *__restrict__ step_dev, long long budget, int 
 	if (ok) {
 		const int row_max = v.t_max * v.top_k;
 		bool sane = true;
+		const int *cnt_all = ep_ptr<int>(v, v.rank, v.off_cntall);  // row s: stored here by rank s with its pub flag
 		for (int i = tid; i < G * E; i += EP_INDEX_THREADS) {
-			const int c = __ldcg(ep_ptr<int>(v, i / E, v.off_counts) + i % E);
+			const int c = __ldcg(cnt_all + i);
 			sane = sane && c >= 0 && c <= row_max;
 			cnt[i] = c;
 		}
 		ok = __syncthreads_and(sane);
 		if (ok) {
-			int tot = 0;
-			for (int s = 0; s < G; s++) {
-				const int c = tid < E ? cnt[s * E + tid] : 0;
-				const int pre = ep_block_scan(c, wsum);
-				if (tid < E)
-					soff[s * E + tid] = pre;
-				tot += c;
+			// where expert e starts in source s's id list: one warp per source, a lane takes a run of experts
+			const int lane = tid & 31, per = (E + 31) / 32;  // per <= 8 (E <= 256)
+			for (int s = tid >> 5; s < G; s += EP_INDEX_THREADS / 32) {
+				int run = 0;
+				for (int k = 0; k < per; k++) {
+					const int e = lane * per + k;
+					run += e < E ? cnt[s * E + e] : 0;
+				}
+				int incl = run;
+#pragma unroll
+				for (int o = 1; o < 32; o <<= 1) {
+					const int t = __shfl_up_sync(0xffffffffu, incl, o);
+					if (lane >= o)
+						incl += t;
+				}
+				int pre = incl - run;
+				for (int k = 0; k < per; k++) {
+					const int e = lane * per + k;
+					if (e < E) {
+						soff[s * E + e] = pre;
+						pre += cnt[s * E + e];
+					}
+				}
 			}
+			int tot = 0;
+			if (tid < E)
+				for (int s = 0; s < G; s++)
+					tot += cnt[s * E + tid];
 			int all = 0;
 			const int pre = ep_block_scan(tot, wsum, &all);
 			if (tid < E)
