@@ -394,25 +394,27 @@ def main():
     # step with host buffers of its own): every step still copies its 4 MB in and its 4 MB out inside
     # the timed region, and its result is complete in host memory when its wait returns; the copies of
     # neighbouring steps overlap the kernels
-    xh = [x_host, x_host.clone().pin_memory()]
-    oh = [out_host, torch.empty_like(out_host).pin_memory()]
+    DEPTH = 3  # calls in flight
+    xh = [x_host] + [x_host.clone().pin_memory() for _ in range(DEPTH - 1)]
+    oh = [out_host] + [torch.empty_like(out_host).pin_memory() for _ in range(DEPTH - 1)]
     hflags = moe.HOST | moe.GRAPH
 
     def pipelined(n):
-        be.moe_ffn_submit(0, xh[0], oh[0], T, 0, hflags)
-        for i in range(1, n):
-            be.moe_ffn_submit(0, xh[i & 1], oh[i & 1], T, i & 1, hflags)
-            be.moe_ffn_wait((i - 1) & 1)
-        be.moe_ffn_wait((n - 1) & 1)
+        for i in range(n):
+            if i >= DEPTH:
+                be.moe_ffn_wait(i % DEPTH)  # the call that used this slot DEPTH steps ago: its result is in host memory
+            be.moe_ffn_submit(0, xh[i % DEPTH], oh[i % DEPTH], T, i % DEPTH, hflags)
+        for i in range(max(n - DEPTH, 0), n):
+            be.moe_ffn_wait(i % DEPTH)
 
     pipelined(max(args.warmup, 4))
     t0 = time.perf_counter()
     pipelined(args.steps)
     e2e_s = (time.perf_counter() - t0) / args.steps
-    assert torch.equal(oh[0], oh[1]) and bool(torch.isfinite(oh[1]).all())  # both slots ran the same inputs
+    assert all(torch.equal(oh[0], o) for o in oh[1:]) and bool(torch.isfinite(oh[0]).all())  # all slots ran the same inputs
     e2e = {"value": T / e2e_s, "unit": UNIT, "h2d_bytes_per_step": T * shape.hidden * 4, "d2h_bytes_per_step": T * shape.hidden * 4,
            "ms_per_step": e2e_s * 1e3,
-           "how": "tie_cuda_moe_ffn_submit / _wait, two calls in flight on alternating slots (pinned host buffers)",
+           "how": f"tie_cuda_moe_ffn_submit / _wait, {DEPTH} calls in flight on slots used in turn (pinned host buffers)",
            "synchronous_call": {"value": T / sync_s, "ms_per_step": sync_s * 1e3,
                                 "how": "tie_cuda_moe_ffn(TIE_CUDA_HOST), one call at a time: copy in, kernels, copy out in series"}}
 

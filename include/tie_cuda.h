@@ -130,18 +130,20 @@ size_t tie_cuda_weight_bytes(const tie_cuda_ctx *c);
  * Requires ep_size == 1. */
 int tie_cuda_moe_ffn(tie_cuda_ctx *c, int layer, const float *x, float *out, int n_tokens, unsigned flags);
 
-/* Two host-buffer calls in flight (the reference has no counterpart: its layer call is synchronous).
+/* Several host-buffer calls in flight (the reference has no counterpart: its layer call is synchronous).
  * tie_cuda_moe_ffn_submit enqueues what tie_cuda_moe_ffn(.., TIE_CUDA_HOST) does — copy x in, the
  * block, copy the result out — and returns; tie_cuda_moe_ffn_wait(slot) returns when out_host of
  * that slot's call is complete (and reports the call's kernel status).  The copies run on
- * streams of their own, so with the two slots used alternately the input copy of the next call
+ * streams of their own, so with two or three slots used in turn the input copy of the next call
  * and the result copy of the previous one overlap the current call's kernels: a host that
  * streams independent batches through a layer pays max(kernels, copy in, copy out) per batch
- * instead of their sum.  slot is 0 or 1; a slot takes its next call after its wait; x_host and
+ * instead of their sum.  slot is 0 .. TIE_CUDA_N_SLOTS - 1 (a slot's staging buffers are allocated
+ * at its first use); a slot takes its next call after its wait; x_host and
  * out_host must be page-locked (TIE_CUDA_ENOTSUP otherwise) and must stay untouched until the
  * wait; the context must run on a stream of its own (not the legacy default stream).  flags:
  * TIE_CUDA_GRAPH, TIE_CUDA_PATH_*.  Kernels of different calls never overlap (they share the
  * context's scratch). */
+#define TIE_CUDA_N_SLOTS 4
 int tie_cuda_moe_ffn_submit(tie_cuda_ctx *c, int layer, const float *x_host, float *out_host, int n_tokens, int slot, unsigned flags);
 int tie_cuda_moe_ffn_wait(tie_cuda_ctx *c, int slot);
 

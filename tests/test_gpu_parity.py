@@ -671,8 +671,19 @@ def test_two_host_buffer_calls_in_flight(be, port0):
         be.moe_ffn_submit(0, pageable, outs[0], 4, 0)
     assert ei.value.code == moe.ENOTSUP
     with pytest.raises(moe.TieCudaError) as ei:
-        be.moe_ffn_submit(0, xs[0], outs[0], 96, 2)
+        be.moe_ffn_submit(0, xs[0], outs[0], 96, moe.N_SLOTS)
     assert ei.value.code == moe.EINVAL
+    # three calls in flight on slots used in turn
+    for o in outs:
+        o.fill_(float("nan"))
+    third = torch.empty_like(outs[0]).pin_memory()
+    be.moe_ffn_submit(0, xs[0], outs[0], 96, 0, moe.GRAPH)
+    be.moe_ffn_submit(0, xs[1], outs[1], 40, 1, moe.GRAPH)
+    be.moe_ffn_submit(0, xs[0], third, 96, 2, moe.GRAPH)
+    for slot in range(3):
+        be.moe_ffn_wait(slot)
+    assert np.array_equal(bits(outs[0].numpy()), bits(want[0])) and np.array_equal(bits(outs[1].numpy()), bits(want[1]))
+    assert np.array_equal(bits(third.numpy()), bits(want[0]))
 
 
 def test_errors_are_codes_not_exits(be):

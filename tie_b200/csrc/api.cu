@@ -895,7 +895,7 @@ int tie_cuda_moe_ffn(tie_cuda_ctx *c, int layer, const float *x, float *out, int
 	return tie_cuda_moe_ffn_biased(c, layer, x, out, n_tokens, nullptr, flags);
 }
 
-// ---- two host-buffer calls in flight ----
+// ---- several host-buffer calls in flight ----
 // The copies of a call run on streams of their own: the input copy of call k+1 and the result copy
 // of call k-1 overlap the kernels of call k (which stay on the context's stream, one call after
 // the other: they share the scratch).  Slot staging and events are created on first use.
@@ -921,7 +921,7 @@ int tie_cuda_moe_ffn_submit(tie_cuda_ctx *c, int layer, const float *x_host, flo
 {
 	Layer *L;
 	TRY(get_layer(c, layer, &L));
-	if (!x_host || !out_host || n_tokens <= 0 || n_tokens > c->cfg.max_tokens || c->cfg.ep_size != 1 || slot < 0 || slot > 1 ||
+	if (!x_host || !out_host || n_tokens <= 0 || n_tokens > c->cfg.max_tokens || c->cfg.ep_size != 1 || slot < 0 || slot >= TIE_CUDA_N_SLOTS ||
 	    (flags & TIE_CUDA_DEVICE) || c->stream == nullptr)
 		return TIE_CUDA_EINVAL;
 	tie_cuda_ctx::Slot &sl = c->slots[slot];
@@ -959,7 +959,7 @@ int tie_cuda_moe_ffn_submit(tie_cuda_ctx *c, int layer, const float *x_host, flo
 
 int tie_cuda_moe_ffn_wait(tie_cuda_ctx *c, int slot)
 {
-	if (!c || slot < 0 || slot > 1 || !c->slots[slot].busy)
+	if (!c || slot < 0 || slot >= TIE_CUDA_N_SLOTS || !c->slots[slot].busy)
 		return TIE_CUDA_EINVAL;
 	tie_cuda_ctx::Slot &sl = c->slots[slot];
 	TIE_CUDA_TRY(c, cudaSetDevice(c->device));

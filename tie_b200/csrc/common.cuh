@@ -163,7 +163,7 @@ struct tie_cuda_ctx {
 		unsigned *pin_status = nullptr;
 		cudaEvent_t in = nullptr, done = nullptr, outd = nullptr;
 		bool busy = false;
-	} slots[2];
+	} slots[TIE_CUDA_N_SLOTS];
 	cudaStream_t h2d_stream = nullptr, d2h_stream = nullptr;
 	size_t weight_bytes = 0;
 	uint64_t launches = 0;

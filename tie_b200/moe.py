@@ -21,6 +21,7 @@ PATH_DECODE_CHAIN = 1 << 11  # one token: three chained decode kernels instead o
 ROUTE_LFM2 = 1 << 12  # LFM2-MoE routing: sigmoid, selection bias, L1-normalised gates (model_lfm2.c:438-473)
 PATH_NO_PAIR = 1 << 14  # tensor path: single-CTA grouped GEMM instead of CTA pairs
 EP_REPLICATED = 1 << 13  # expert-parallel decode: the same 1-4 tokens on every rank
+N_SLOTS = 4  # TIE_CUDA_N_SLOTS: host-buffer calls that can be in flight (moe_ffn_submit / moe_ffn_wait)
 OK, EINVAL, ENOTSUP, ENOMEM, ECUDA, ENODEV, EKERNEL, ETOOBIG = 0, -1, -2, -3, -4, -5, -6, -7
 
 # every symbol include/tie_cuda.h declares
