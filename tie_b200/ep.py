@@ -313,20 +313,23 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler, co
     be.synchronize()
     e2e_s, e2e_how = e2e_sync_s, "one step at a time: copy in, step, copy out in series"
     if exchange == "peer":
-        # two steps in flight on alternating device and host buffers: every step still copies its tokens in
-        # and its result out inside the timed region, and the host waits for each step's result; the copies
-        # run on streams of their own and overlap the neighbouring steps' kernels
+        # three steps in flight on device and host buffers used in turn: every step still copies its tokens
+        # in and its result out inside the timed region, and the host waits for each step's result; the
+        # copies run on streams of their own and overlap the neighbouring steps' kernels
+        DEPTH = 3
         cs = torch.cuda.current_stream()
         hs, ds = torch.cuda.Stream(), torch.cuda.Stream()
-        xb = [torch.empty(T, shape.hidden, device="cuda") for _ in range(2)]
+        xb = [torch.empty(T, shape.hidden, device="cuda") for _ in range(DEPTH)]
         ob = [torch.empty_like(b) for b in xb]
-        xh = [x_host, x_host.clone().pin_memory()]
-        oh = [out_host, torch.empty_like(out_host).pin_memory()]
-        ev_in, ev_done, ev_out = ([torch.cuda.Event() for _ in range(2)] for _ in range(3))
+        xh = [x_host] + [x_host.clone().pin_memory() for _ in range(DEPTH - 1)]
+        oh = [out_host] + [torch.empty_like(out_host).pin_memory() for _ in range(DEPTH - 1)]
+        ev_in, ev_done, ev_out = ([torch.cuda.Event() for _ in range(DEPTH)] for _ in range(3))
 
         def pipelined(n=1):
             for i in range(n):
-                k = i & 1
+                k = i % DEPTH
+                if i >= DEPTH:
+                    ev_out[k].synchronize()  # the result of the step that used these buffers is in host memory
                 with torch.cuda.stream(hs):
                     hs.wait_event(ev_done[k])
                     xb[k].copy_(xh[k], non_blocking=True)
@@ -339,11 +342,9 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler, co
                     ds.wait_event(ev_done[k])
                     oh[k].copy_(ob[k], non_blocking=True)
                     ev_out[k].record(ds)
-                if i:
-                    ev_out[(i - 1) & 1].synchronize()  # the previous step's result is in host memory
-            ev_out[(n - 1) & 1].synchronize()
-            cs.wait_event(ev_out[0])
-            cs.wait_event(ev_out[1])
+            for k in range(DEPTH):
+                ev_out[k].synchronize()
+                cs.wait_event(ev_out[k])
 
         pipelined(max(args.warmup, 4))
         torch.cuda.synchronize()
@@ -356,8 +357,8 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler, co
         t = torch.tensor([a.elapsed_time(b)], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item()) / args.steps * 1e-3
-        e2e_how = "two steps in flight on alternating buffers (copies on streams of their own, host waits for every step's result)"
-        assert torch.equal(oh[0], oh[1]) and bool(torch.isfinite(oh[1]).all())
+        e2e_how = f"{DEPTH} steps in flight on buffers used in turn (copies on streams of their own, host waits for every step's result)"
+        assert all(torch.equal(oh[0], o) for o in oh[1:]) and bool(torch.isfinite(oh[0]).all())
         be.synchronize()
 
     # per-phase device times of rank 0 (CUDA events inside the library; the steps run without a graph,
