@@ -71,6 +71,11 @@ __global__ void __launch_bounds__(EPC * 8) router_logits_tile(const float *__res
 // the 4 token groups of a warp on disjoint banks, and the 4 groups share their expert rows
 // (broadcast loads).
 constexpr int RMT_STAGES = 4;
+// Rows of CTAs a launch adds for the hand-over of the tokens in an expert-parallel step.  One row
+// (32 CTAs at 512 tokens) was measured best: its stores run at ~490 GB/s and lengthen the kernel by
+// 10 us at 4 GPUs (29 us at 8); four rows lengthen it by 18 us at 4 GPUs — the extra CTAs take
+// load/store slots from the logits' CTAs they share the SMs with.
+constexpr int RMT_PUSH_ROWS = 1;
 
 // TPT x EPT = tokens x experts per thread, TE = experts per CTA, KC = k chunk.  CTA = 4 TPT
 // tokens x TE experts, 8 x 4 x TE/EPT threads.
@@ -92,10 +97,12 @@ router_logits_mt(const float *__restrict__ x, const float *__restrict__ w, const
 	using Cfg = RmtCfg<TPT, EPT, TE, KC>;
 	constexpr int TT = Cfg::TT, PITCH = Cfg::PITCH, THREADS = Cfg::THREADS;
 	extern __shared__ __align__(16) float rsm[];
-	// Expert-parallel steps: one more row of CTAs (blockIdx.y past the expert tiles) stores this rank's
-	// tokens into every rank's memory while the others compute the logits; it shares nothing with them.
+	// Expert-parallel steps: RMT_PUSH_ROWS more rows of CTAs (blockIdx.y past the expert tiles) store this
+	// rank's tokens into every rank's memory while the others compute the logits; they share nothing
+	// with them.
 	if (push.x && (int)blockIdx.y * TE >= n_expert) {
-		ep_push_tokens_cta(push, blockIdx.x, gridDim.x);
+		const int row = (int)blockIdx.y - n_expert / TE;
+		ep_push_tokens_cta(push, row * (int)gridDim.x + (int)blockIdx.x, RMT_PUSH_ROWS * (int)gridDim.x);
 		return;
 	}
 	const int t0 = blockIdx.x * TT, e0 = blockIdx.y * TE;
@@ -401,14 +408,14 @@ int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *
 		TIE_CUDA_LAUNCHED(c);
 	} else if (E % 64 == 0 && H % 128 == 0 && n_tokens >= 2048) {
 		using Cfg = RmtCfg<8, 8, 64, 64>;
-		dim3 grid((n_tokens + Cfg::TT - 1) / Cfg::TT, E / 64 + (push ? 1 : 0));
+		dim3 grid((n_tokens + Cfg::TT - 1) / Cfg::TT, E / 64 + (push ? RMT_PUSH_ROWS : 0));
 		router_logits_mt<8, 8, 64, 64><<<grid, Cfg::THREADS, Cfg::SMEM, c->stream>>>(x, w, bias, logits, n_tokens, H, E, f);
 		if (push_taken)
 			*push_taken = push != nullptr;
 		TIE_CUDA_LAUNCHED(c);
 	} else if (E % 32 == 0 && H % 128 == 0) {
 		using Cfg = RmtCfg<4, 4, 32, 128>;
-		dim3 grid((n_tokens + Cfg::TT - 1) / Cfg::TT, E / 32 + (push ? 1 : 0));
+		dim3 grid((n_tokens + Cfg::TT - 1) / Cfg::TT, E / 32 + (push ? RMT_PUSH_ROWS : 0));
 		router_logits_mt<4, 4, 32, 128><<<grid, Cfg::THREADS, Cfg::SMEM, c->stream>>>(x, w, bias, logits, n_tokens, H, E, f);
 		if (push_taken)
 			*push_taken = push != nullptr;
