@@ -413,6 +413,7 @@ EpPush ep_push_args(tie_cuda_ctx *c, const float *x, int n_tokens)
 	f.v = c->ep.view;
 	f.x = x;
 	f.n_tokens = n_tokens;
+	f.n_ctas = 0;
 	return f;
 }
 

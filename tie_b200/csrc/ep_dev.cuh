@@ -36,7 +36,7 @@ __device__ __forceinline__ T *ep_ptr(const EpView &v, int rank, size_t off)
 	return reinterpret_cast<T *>(v.peer[rank] + off);
 }
 
-constexpr int EP_PUSH_F4 = 8;  // 16-byte loads a thread keeps in flight (each is stored to every rank)
+constexpr int EP_PUSH_F4 = 16;  // 16-byte loads a thread keeps in flight (each is stored to every rank)
 
 // What the CTAs that hand this rank's tokens to its peers need (by value in the kernel
 // parameters); x == nullptr: nothing to push.
@@ -44,6 +44,7 @@ struct EpPush {
 	EpView v;
 	const float *x;	 // this rank's tokens of the step [n_tokens][hidden]
 	int n_tokens;
+	int n_ctas;  // CTAs that take part (set by the launcher)
 };
 
 // CTA `cta` of `n_ctas` (all threads of the CTA call): stores this rank's tokens into slot `rank`

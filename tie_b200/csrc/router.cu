@@ -71,11 +71,17 @@ __global__ void __launch_bounds__(EPC * 8) router_logits_tile(const float *__res
 // the 4 token groups of a warp on disjoint banks, and the 4 groups share their expert rows
 // (broadcast loads).
 constexpr int RMT_STAGES = 4;
-// Rows of CTAs a launch adds for the hand-over of the tokens in an expert-parallel step.  One row
-// (32 CTAs at 512 tokens) was measured best: its stores run at ~490 GB/s and lengthen the kernel by
-// 10 us at 4 GPUs (29 us at 8); four rows lengthen it by 18 us at 4 GPUs — the extra CTAs take
-// load/store slots from the logits' CTAs they share the SMs with.
+// The hand-over of the tokens in an expert-parallel step rides along as one more row of CTAs, of
+// which as many work as there are SMs the logits' CTAs leave free (at least 16): CTAs that share an
+// SM with the logits take load/store slots from them (32 working CTAs lengthened the kernel by 10 us
+// at 4 GPUs, 128 by 18 us).
 constexpr int RMT_PUSH_ROWS = 1;
+static int rmt_push_ctas(const tie_cuda_ctx *c, int logits_ctas, int most)
+{
+	int n = c->sm_count - logits_ctas;
+	n = n < 16 ? 16 : n;
+	return n < most ? n : most;
+}
 
 // TPT x EPT = tokens x experts per thread, TE = experts per CTA, KC = k chunk.  CTA = 4 TPT
 // tokens x TE experts, 8 x 4 x TE/EPT threads.
@@ -101,8 +107,9 @@ router_logits_mt(const float *__restrict__ x, const float *__restrict__ w, const
 	// rank's tokens into every rank's memory while the others compute the logits; they share nothing
 	// with them.
 	if (push.x && (int)blockIdx.y * TE >= n_expert) {
-		const int row = (int)blockIdx.y - n_expert / TE;
-		ep_push_tokens_cta(push, row * (int)gridDim.x + (int)blockIdx.x, RMT_PUSH_ROWS * (int)gridDim.x);
+		const int row = (int)blockIdx.y - n_expert / TE, cta = row * (int)gridDim.x + (int)blockIdx.x;
+		if (cta < push.n_ctas)
+			ep_push_tokens_cta(push, cta, push.n_ctas);
 		return;
 	}
 	const int t0 = blockIdx.x * TT, e0 = blockIdx.y * TE;
@@ -409,6 +416,7 @@ int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *
 	} else if (E % 64 == 0 && H % 128 == 0 && n_tokens >= 2048) {
 		using Cfg = RmtCfg<8, 8, 64, 64>;
 		dim3 grid((n_tokens + Cfg::TT - 1) / Cfg::TT, E / 64 + (push ? RMT_PUSH_ROWS : 0));
+		f.n_ctas = rmt_push_ctas(c, grid.x * (E / 64), grid.x * RMT_PUSH_ROWS);
 		router_logits_mt<8, 8, 64, 64><<<grid, Cfg::THREADS, Cfg::SMEM, c->stream>>>(x, w, bias, logits, n_tokens, H, E, f);
 		if (push_taken)
 			*push_taken = push != nullptr;
@@ -416,6 +424,7 @@ int launch_router(tie_cuda_ctx *c, const float *x, const float *w, const float *
 	} else if (E % 32 == 0 && H % 128 == 0) {
 		using Cfg = RmtCfg<4, 4, 32, 128>;
 		dim3 grid((n_tokens + Cfg::TT - 1) / Cfg::TT, E / 32 + (push ? RMT_PUSH_ROWS : 0));
+		f.n_ctas = rmt_push_ctas(c, grid.x * (E / 32), grid.x * RMT_PUSH_ROWS);
 		router_logits_mt<4, 4, 32, 128><<<grid, Cfg::THREADS, Cfg::SMEM, c->stream>>>(x, w, bias, logits, n_tokens, H, E, f);
 		if (push_taken)
 			*push_taken = push != nullptr;
