@@ -463,12 +463,6 @@ void ep_release(tie_cuda_ctx *c)
 	for (void *p : ptrs)
 		if (p)
 			cudaFree(p);
-	if (ep.ev_fork)
-		cudaEventDestroy(ep.ev_fork);
-	if (ep.ev_join)
-		cudaEventDestroy(ep.ev_join);
-	if (ep.side)
-		cudaStreamDestroy(ep.side);
 	ep = EpState();
 }
 
@@ -522,9 +516,6 @@ int ep_region(tie_cuda_ctx *c)
 	TRY(dev_alloc(c, &ep.seg_src, v.n_expert));
 	TRY(dev_alloc(c, &ep.row_dst, (size_t)v.rows_cap));
 	TRY(dev_alloc(c, &ep.step_dev, 1));
-	TIE_CUDA_TRY(c, cudaStreamCreateWithFlags(&ep.side, cudaStreamNonBlocking));
-	TIE_CUDA_TRY(c, cudaEventCreateWithFlags(&ep.ev_fork, cudaEventDisableTiming));
-	TIE_CUDA_TRY(c, cudaEventCreateWithFlags(&ep.ev_join, cudaEventDisableTiming));
 	TIE_CUDA_TRY(c, cudaMemset(ep.step_dev, 0, sizeof(unsigned)));
 	TIE_CUDA_TRY(c, cudaMemset(ep.n_rows, 0, sizeof(int)));
 	TIE_CUDA_TRY(c, cudaDeviceSynchronize());
@@ -1301,16 +1292,16 @@ int tie_cuda_ep_publish(tie_cuda_ctx *c, int layer, const float *x, int n_tokens
 	// the selected experts go where the peers can read them: the owner of a token's first row on a GPU
 	// looks up the token's other rows there
 	int *topk_pub = reinterpret_cast<int *>(ep.region + v.off_topk);
-	// The tokens do not depend on the routing: a small kernel on a stream of its own stores them into
-	// every rank's memory beside the router and the sort (29 MB at 8 GPUs take ~60 us over NVLink, the
-	// router alone 33); the pub flag below follows the join, so it announces them together with the row
-	// lists.  The kernel waits for nothing, so ranks that share one GPU may run it too.
+	// The tokens do not depend on the routing: they go to every rank's memory beside the router, as
+	// extra CTAs of its kernel (or, for shapes whose router kernel cannot take them along, as a launch
+	// of its own); the pub flag below announces them together with the row lists.
 	if (n_tokens) {
-		TIE_CUDA_TRY(c, cudaEventRecord(ep.ev_fork, c->stream));
-		TIE_CUDA_TRY(c, cudaStreamWaitEvent(ep.side, ep.ev_fork, 0));
-		TRY(launch_ep_push_tokens(c, x, n_tokens, ep.side));
-		TIE_CUDA_TRY(c, cudaEventRecord(ep.ev_join, ep.side));
-		TRY(launch_router(c, x, L->router_w, router_bias, n_tokens, s.logits, topk_pub, s.topk_w, (flags & TIE_CUDA_ROUTE_LFM2) ? 1 : 0));
+		const EpPush push = ep_push_args(c, x, n_tokens);
+		bool taken = false;
+		TRY(launch_router(c, x, L->router_w, router_bias, n_tokens, s.logits, topk_pub, s.topk_w, (flags & TIE_CUDA_ROUTE_LFM2) ? 1 : 0,
+				  &push, &taken));
+		if (!taken)
+			TRY(launch_ep_push_tokens(c, x, n_tokens));
 	}
 	prof_mark(c, 1);
 	SortBufs b = {reinterpret_cast<int *>(ep.region + v.off_counts),
@@ -1324,8 +1315,6 @@ int tie_cuda_ep_publish(tie_cuda_ctx *c, int layer, const float *x, int n_tokens
 	b.owner_div = c->n_local;
 	b.top_k = c->cfg.top_k;
 	TRY(launch_sort(c, topk_pub, R, 128, 0, c->cfg.n_expert, b));
-	if (n_tokens)
-		TIE_CUDA_TRY(c, cudaStreamWaitEvent(c->stream, ep.ev_join, 0));
 	TRY(launch_ep_signal(c, 0));
 	prof_mark(c, 2);
 	ep.phase = 1;

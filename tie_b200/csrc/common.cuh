@@ -135,9 +135,6 @@ struct EpState {
 	long long wait_cycles = 0;  // budget of every flag wait
 	int *n_rows = nullptr, *seg_base = nullptr, *seg_src = nullptr;
 	unsigned *row_dst = nullptr;  // [rows_cap] per sorted row: (source rank << 24) | its row id there
-	// the hand-over of this rank's tokens to its peers runs on a stream of its own beside the router and the sort
-	cudaStream_t side = nullptr;
-	cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 };
 
 }  // namespace tie

@@ -417,13 +417,11 @@ EpPush ep_push_args(tie_cuda_ctx *c, const float *x, int n_tokens)
 	return f;
 }
 
-// (20 CTAs: about what the router's kernel leaves free at 512 and at 2048 tokens; more CTAs do not
-// store faster over NVLink — ~490 GB/s either way — and take load/store slots from the kernels beside them)
-int launch_ep_push_tokens(tie_cuda_ctx *c, const float *x, int n_tokens, cudaStream_t stream)
+int launch_ep_push_tokens(tie_cuda_ctx *c, const float *x, int n_tokens)
 {
 	if (n_tokens <= 0)
 		return TIE_CUDA_OK;
-	ep_push_tokens<<<20, EP_PUSH_THREADS, 0, stream>>>(ep_push_args(c, x, n_tokens));
+	ep_push_tokens<<<c->sm_count, EP_PUSH_THREADS, 0, c->stream>>>(ep_push_args(c, x, n_tokens));
 	TIE_CUDA_LAUNCHED(c);
 	return TIE_CUDA_OK;
 }

@@ -66,7 +66,7 @@ int launch_tc_down(tie_cuda_ctx *c, const Layer &L, int n_rows, float *y, bool s
 int launch_tc_down_peer(tie_cuda_ctx *c, const Layer &L, const EpDst &dst);
 // ep.cu
 int launch_ep_signal(tie_cuda_ctx *c, int which);
-int launch_ep_push_tokens(tie_cuda_ctx *c, const float *x, int n_tokens, cudaStream_t stream);
+int launch_ep_push_tokens(tie_cuda_ctx *c, const float *x, int n_tokens);
 EpPush ep_push_args(tie_cuda_ctx *c, const float *x, int n_tokens);  // (ep_dev.cuh defines EpPush)
 int launch_ep_index(tie_cuda_ctx *c);
 int launch_ep_split_rows(tie_cuda_ctx *c, bool sums);
