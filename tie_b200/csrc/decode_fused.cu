@@ -48,6 +48,7 @@ struct DfShared {
 	float lg[256];	// the logits (n_expert <= 256)
 	unsigned base;
 	int ok;
+	int dn_req[MAX_TOP_K];	// the down tile of slot j has been requested
 	float inv;  // 1 / rms of the row (RMSNorm in the kernel)
 };
 
@@ -143,8 +144,10 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 	if (tid == 0) {
 		for (int c = 0; c < DF_MAX_CHUNKS; c++)
 			ptx::mbar_init(ptx::smem_u32(&sh.bar_gu[c]), 1);
-		for (int j = 0; j < MAX_TOP_K; j++)
+		for (int j = 0; j < MAX_TOP_K; j++) {
 			ptx::mbar_init(ptx::smem_u32(&sh.bar_dn[j]), 1);
+			sh.dn_req[j] = 0;
+		}
 		ptx::fence_barrier_init();
 		sh.base = df_ld_acquire(a.sync + 1);
 	}
@@ -255,7 +258,21 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 		atomicOr(a.status, ST_BAD_EXPERT);
 	uint8_t *sg = dsm, *su = dsm + tile_gu, *sd = dsm + a.off_b;
 	// one issuing thread per copy group (issuing a bulk copy costs ~100 cycles): warp c < 8 the
-	// gate/up chunk c, warp 8 + j the down tile of slot j
+	// gate/up chunk c, warp 8 + j the down tile of slot j.  The down tiles are requested once the
+	// first gate/up chunk has landed: asked for together with the gate/up tiles they shared the HBM
+	// bandwidth with them and the first chunk arrived a microsecond later; they still have the whole
+	// gate/up phase to arrive in.
+	auto request_down = [&]() {  // lane 0 of warp 8 + j
+		const int j = warp - DF_MAX_CHUNKS;
+		if (dn_role && j >= 0 && j < top_k) {
+			const uint32_t ba = ptx::smem_u32(&sh.bar_dn[j]);
+			sh.dn_req[j] = 1;
+			ptx::fence_proxy_async_smem();
+			ptx::mbar_arrive_expect_tx(ba, tile_dn);
+			bulk_g2s(ptx::smem_u32(sd + (size_t)j * tile_dn),
+				 a.wd + (size_t)(sh.idx[j] - a.first_expert) * a.stride_dn + tile_offset<KD>(DF::NB, d0), tile_dn, ba);
+		}
+	};
 	if (lane == 0 && !bad) {
 		ptx::fence_proxy_async_smem();	// the tile area held the router's staging
 		if (warp < DF_MAX_CHUNKS) {
@@ -270,14 +287,8 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 				bulk_g2s(ptx::smem_u32(sg + rel), a.wg + eb + o0, bytes, ba);
 				bulk_g2s(ptx::smem_u32(su + rel), a.wu + eb + o0, bytes, ba);
 			}
-		} else {
-			const int j = warp - DF_MAX_CHUNKS;
-			if (dn_role && j < top_k) {
-				const uint32_t ba = ptx::smem_u32(&sh.bar_dn[j]);
-				ptx::mbar_arrive_expect_tx(ba, tile_dn);
-				bulk_g2s(ptx::smem_u32(sd + (size_t)j * tile_dn),
-					 a.wd + (size_t)(sh.idx[j] - a.first_expert) * a.stride_dn + tile_offset<KD>(DF::NB, d0), tile_dn, ba);
-			}
+		} else if (!gu_role) {
+			request_down();	 // (a CTA without gate/up rows: nothing to wait for)
 		}
 	}
 	// waits (bounded) for every copy this CTA requested: before it gives up, and harmless otherwise
@@ -288,7 +299,8 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 			dec_wait(ptx::smem_u32(&sh.bar_gu[c]), a.status);
 		if (dn_role)
 			for (int j = 0; j < top_k; j++)
-				dec_wait(ptx::smem_u32(&sh.bar_dn[j]), a.status);
+				if (sh.dn_req[j])
+					dec_wait(ptx::smem_u32(&sh.bar_dn[j]), a.status);
 	};
 
 	// ---------------- G: gate, up, SwiGLU ----------------
@@ -310,8 +322,11 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 				waited = chunk;
 				if (!alive)
 					break;
-				if (chunk == 0)
+				if (chunk == 0) {
 					DF_STAMP(7);
+					if (lane == 0 && warp >= DF_MAX_CHUNKS)
+						request_down();
+				}
 			}
 			const int row = rp + warp * DK::RPW + sub;
 			float vgv = 0.f, vuv = 0.f;
