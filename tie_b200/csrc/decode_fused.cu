@@ -377,23 +377,22 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 		const int sub = lane / DF::LPR, part = lane % DF::LPR;
 		const bool lane_on = part < DF::PARTS;
 		const int rows = d1 - d0;
-		// rows of a pass are split into warp groups when the tile is shorter than a pass: each group
-		// takes every n_groups-th slot
-		const int n_groups = a.rpt_dn >= DF::RPP ? 1 : DF::RPP / a.rpt_dn;
-		const int span = DF::RPP / n_groups;
-		const int vr = warp * DF::RPW + sub;
-		const int grp = vr / span, lr0 = vr % span;
-		const int passes = (a.rpt_dn + span - 1) / span;
-		for (int j = grp; j < top_k && alive; j += n_groups) {
+		// A (warp, sub-row) unit keeps ONE slot for the whole phase — its slice of that slot's h stays in
+		// registers — and walks the rows of the tile: the units of slot j are j, j + top_k, ..., the
+		// k-th of them takes rows k, k + n_j, ... (loading the activations once per unit instead of once
+		// per slot and unit leaves only the packed rows to fetch inside the loop).
+		const int unit = warp * DF::RPW + sub;	// (a pass has at least 16 units, a token at most 8 slots)
+		{
+			const int j = unit % top_k, r0 = unit / top_k;
+			const int n_j = (DF::RPP - 1 - j) / top_k + 1;		    // units that share slot j
+			const int trips = (rows + DF::RPP / top_k - 1) / (DF::RPP / top_k);  // the same for every lane of a warp
 			float xr[64], sx[4];
 			if (lane_on)
 				load_x_lane_major<KD, DF::LPR>(hs + (size_t)j * XS_T, part, xr, sx);
-			alive = dec_wait(ptx::smem_u32(&sh.bar_dn[j]), a.status);
-			if (!alive)
-				break;
+			alive = __all_sync(0xffffffffu, dec_wait(ptx::smem_u32(&sh.bar_dn[j]), a.status));
 			const uint8_t *vd = sd + (size_t)j * tile_dn - tile_offset<KD>(DF::NB, d0);
-			for (int p = 0; p < passes; p++) {
-				const int lr = p * span + lr0;
+			for (int i = 0; i < trips && alive; i++) {
+				const int lr = r0 + i * n_j;
 				float v = 0.f;
 				if (lane_on && lr < rows)
 					v = PartDot<KD>::dot(PartDot<KD>::template load<true>(vd, DF::NB, d0 + lr, part), part, xr, sx);
