@@ -46,7 +46,7 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 # 512-token workload, from the ncu capture of `python bench.py --only prefill512`; a change to that
 # kernel needs a new capture (the traffic is set by the packed weights and the operand arrays, not
 # by the kernel's schedule, and has stayed within 1 % over the kernel's revisions).
-NCU_DRAM_BYTES_PER_LAUNCH = {"gate_up": 282442752, "down": 197401600}
+NCU_DRAM_BYTES_PER_LAUNCH = {"gate_up": 261247744 + 19478784, "down": 177839104 + 20242688}  # read + written
 NCU_DRAM_SOURCE = "ncu capture of grouped_gemm_sb on `bench.py --only prefill512`"
 
 
