@@ -315,7 +315,14 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 		const uint8_t *vg = sg - tile_offset<KG>(DK::NB, g0), *vu = su - tile_offset<KG>(DK::NB, g0);
 		float *hrow = a.h + (size_t)slot * F;
 		int waited = -1;
-		for (int rp = g0; rp < g1 && alive; rp += DK::RPP) {
+		// The table look-ups of a row's SwiGLU are two dependent loads: done at the end of every pass they
+		// stall the warp before its next pass.  After the reduction every lane of a row holds the sums, so
+		// lane p of the row keeps those of pass p and all passes' look-ups are issued together at the end
+		// (as long as a row has at least as many lanes as the tile has passes).
+		const bool defer = (g1 - g0 + DK::RPP - 1) / DK::RPP <= DK::LPR;
+		float keep_g = 0.f, keep_u = 0.f;
+		int keep_row = -1, pass = 0;
+		for (int rp = g0; rp < g1 && alive; rp += DK::RPP, pass++) {
 			const int chunk = (rp - g0) / CH;
 			if (chunk != waited) {
 				alive = dec_wait(ptx::smem_u32(&sh.bar_gu[chunk]), a.status);
@@ -339,9 +346,18 @@ __global__ void __launch_bounds__(DF_THREADS, 1) decode1_fused(const DfArgs a)
 				vgv += __shfl_xor_sync(0xffffffffu, vgv, o);
 				vuv += __shfl_xor_sync(0xffffffffu, vuv, o);
 			}
-			if (part == 0 && row < g1)
+			if (defer) {
+				if (part == pass && row < g1) {
+					keep_g = vgv;
+					keep_u = vuv;
+					keep_row = row;
+				}
+			} else if (part == 0 && row < g1) {
 				__stcg(hrow + row, swiglu_lut(a.silu, vgv, vuv));
+			}
 		}
+		if (keep_row >= 0 && alive)
+			__stcg(hrow + keep_row, swiglu_lut(a.silu, keep_g, keep_u));
 		DF_STAMP(8);
 	}
 	alive = __syncthreads_and(alive);
