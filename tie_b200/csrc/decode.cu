@@ -86,7 +86,12 @@ decode_gate_up(const uint8_t *__restrict__ wg, const uint8_t *__restrict__ wu, s
 	const uint8_t *vg = sg - tile_offset<KIND>(NB, r0), *vu = su - tile_offset<KIND>(NB, r0);
 	float *hrow = h + (size_t)slot * rows_per_expert;
 	int waited = -1;
-	for (int rp = r0; rp < r1; rp += ROWS_PER_PASS) {
+	// (the SwiGLU table look-ups of all passes go out together at the end: lane p of a row keeps the
+	// sums of pass p, which every lane of the row holds after the reduction)
+	const bool defer = (r1 - r0 + ROWS_PER_PASS - 1) / ROWS_PER_PASS <= LPR;
+	float keep_g = 0.f, keep_u = 0.f;
+	int keep_row = -1, pass = 0;
+	for (int rp = r0; rp < r1; rp += ROWS_PER_PASS, pass++) {
 		const int chunk = (rp - r0) / CH;
 		if (chunk != waited) {	// rows of a pass share a chunk; chunks arrive in order
 			if (!dec_wait(ptx::smem_u32(&bar[chunk]), status))
@@ -104,9 +109,18 @@ decode_gate_up(const uint8_t *__restrict__ wg, const uint8_t *__restrict__ wu, s
 			vgv += __shfl_xor_sync(0xffffffffu, vgv, o);
 			vuv += __shfl_xor_sync(0xffffffffu, vuv, o);
 		}
-		if (part == 0 && row < r1)
+		if (defer) {
+			if (part == pass && row < r1) {
+				keep_g = vgv;
+				keep_u = vuv;
+				keep_row = row;
+			}
+		} else if (part == 0 && row < r1) {
 			hrow[row] = swiglu_lut(silu, vgv, vuv);
+		}
 	}
+	if (keep_row >= 0)
+		hrow[keep_row] = swiglu_lut(silu, keep_g, keep_u);
 }
 
 template <WKind KIND, int K>
