@@ -171,6 +171,30 @@ class PeerEpMoeBlock:
 NVLINK_GBS = 770.0  # measured peer-copy rate per direction on this pool's B200s
 
 
+def bind_host_threads_to_gpu(torch, device_index: int):
+    """Keeps this process on the CPU cores next to its GPU (the affinity NVML reports for the device),
+    so that the pinned host buffers it allocates afterwards and the threads that fill them sit on the
+    GPU's side of the machine.  Reads NVML only; changes nothing but this process's own affinity.
+    Returns the number of cores kept, or None where NVML or the call is unavailable."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        props = torch.cuda.get_device_properties(device_index)
+        bus_id = f"{props.pci_domain_id:08x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus_id.encode())
+        allowed = os.sched_getaffinity(0)
+        n_cpu = max(max(allowed) + 1, os.cpu_count() or 1)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (n_cpu + 63) // 64)
+        near = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+        cores = near & allowed
+        if not cores:
+            return None
+        os.sched_setaffinity(0, cores)
+        return len(cores)
+    except Exception:
+        return None
+
+
 def _nvlink_bytes_per_direction(shape, tokens_per_rank, world):
     """What one rank sends (and, by symmetry, receives) per step: its tokens to every peer, and the
     output rows it computed for other ranks' tokens ((world-1)/world of its rows on average)."""
@@ -227,6 +251,7 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler, co
     rank = int(os.environ["RANK"])
     local_rank = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local_rank)
+    near_cores = bind_host_threads_to_gpu(torch, local_rank)  # before any pinned allocation
     dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     shape = synth.MoeShape()
     T = tokens_per_rank
@@ -515,7 +540,8 @@ def bench_main(args, metric, unit, tokens_per_rank, load_peaks, ClockSampler, co
                       "(larger than L2 from N = 1 to 2; at N >= 4 the weights of a rank fit in L2, as they would in deployment)",
                 "exchange": ("peer memory: a rank stores its tokens into every rank's HBM beside its router, owners store output rows "
                              "into the sources' (no collective, no host synchronisation per step)") if exchange == "peer"
-                else "NCCL all-to-all (torch.distributed) for dispatch and combine"},
+                else "NCCL all-to-all (torch.distributed) for dispatch and combine",
+                "host": f"rank 0 bound to the {near_cores} cores next to its GPU" if near_cores else "no core binding"},
             "clocks": clocks,
             "e2e": {"value": T * world / e2e_s, "unit": unit, "h2d_bytes_per_step": T * shape.hidden * 4 * world,
                     "d2h_bytes_per_step": T * shape.hidden * 4 * world, "ms_per_step": e2e_s * 1e3, "how": e2e_how,
